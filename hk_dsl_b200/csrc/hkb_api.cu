@@ -1,0 +1,90 @@
+// Host-only entry points: the split planner, scratch sizing, device facts, status text.
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "../../include/hkb.h"
+
+thread_local int hkb_tls_cuda_error = 0;
+
+namespace {
+
+struct DeviceFacts {
+  std::once_flag once;
+  int sm_count = 0;
+};
+DeviceFacts g_facts[64];
+
+}  // namespace
+
+extern "C" int hkb_sm_count(int device) {
+  if (device < 0) {
+    if (cudaGetDevice(&device) != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+  }
+  if (device >= 64) return 0;
+  DeviceFacts& f = g_facts[device];
+  std::call_once(f.once, [&] {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) {
+      (void)cudaGetLastError();
+      n = 0;
+    }
+    f.sm_count = n;
+  });
+  return f.sm_count;
+}
+
+// Enough CTAs for two four-warp CTAs an SM, four waves deep so that sequences of
+// unequal length even out; a power of two (each count is one plan a captured graph keeps).
+// hk-dsl aims at 256 one-warp workgroups on a 96-CU card (python/hk/ops/paged.py:838-864);
+// the shape of the rule -- ceil(target / (requests * kv heads)), capped by the pages and a
+// maximum -- is the same, the target is B200's.
+extern "C" int hkb_plan_splits(int num_seqs, int num_kv_heads, int max_tiles, int sm_count) {
+  if (sm_count <= 0) sm_count = 148;
+  const long long have = (long long)(num_seqs > 0 ? num_seqs : 1) * (num_kv_heads > 0 ? num_kv_heads : 1);
+  const long long target = (long long)sm_count * 2 * 4;
+  long long want = (target + have - 1) / have;
+  // at least 8 tiles (128 tokens) a split: below that a split costs more than it hides
+  long long cap = max_tiles > 0 ? (max_tiles + 7) / 8 : 1;
+  if (cap > HKB_MAX_SPLITS) cap = HKB_MAX_SPLITS;
+  if (want > cap) want = cap;
+  if (want < 1) want = 1;
+  int p = 1;
+  while ((long long)p * 2 <= want) p *= 2;  // round down to a power of two
+  return p;
+}
+
+extern "C" size_t hkb_scratch_lse_offset(int num_seqs, int num_q_heads, int head_dim, int num_splits) {
+  if (num_seqs <= 0 || num_q_heads <= 0 || head_dim <= 0 || num_splits <= 0) return 0;
+  size_t b = (size_t)num_seqs * num_splits * num_q_heads * head_dim * sizeof(float);
+  return (b + 255) & ~(size_t)255;
+}
+
+extern "C" size_t hkb_scratch_bytes(int num_seqs, int num_q_heads, int head_dim, int num_splits) {
+  if (num_seqs <= 0 || num_q_heads <= 0 || head_dim <= 0 || num_splits <= 0) return 0;
+  size_t lse = (size_t)num_seqs * num_splits * num_q_heads * sizeof(float);
+  return hkb_scratch_lse_offset(num_seqs, num_q_heads, head_dim, num_splits) + ((lse + 255) & ~(size_t)255);
+}
+
+extern "C" const char* hkb_strerror(int code) {
+  switch (code) {
+    case HKB_OK: return "ok";
+    case HKB_ERR_NULL: return "a required pointer is NULL";
+    case HKB_ERR_HEAD_DIM: return "head_dim is not one this build has a kernel for (64, 128)";
+    case HKB_ERR_BLOCK_SIZE: return "block_size is not a positive multiple of 16";
+    case HKB_ERR_GROUP: return "query heads are not a multiple of kv heads, or more than 16 a kv head";
+    case HKB_ERR_DTYPE: return "kv_dtype is neither bf16 (0) nor fp8-e4m3 (1)";
+    case HKB_ERR_STRIDE: return "a stride breaks the 16-byte alignment of a row";
+    case HKB_ERR_ALIGN: return "a base pointer is not aligned as the kernels read it";
+    case HKB_ERR_SPLITS: return "num_splits out of range, or split scratch missing";
+    case HKB_ERR_SIZE: return "a count is negative or past a launch limit";
+    case HKB_ERR_SCALE: return "an fp8 cache needs k_scale and v_scale";
+    case HKB_ERR_UNSUPPORTED: return "no kernel for this combination of head_dim, dtype and group";
+    case HKB_ERR_CUDA: return "CUDA reported an error at launch (hkb_last_cuda_error)";
+    default: return "unknown hkb status";
+  }
+}
+
+extern "C" int hkb_last_cuda_error(void) { return hkb_tls_cuda_error; }
+
+extern "C" int hkb_version(void) { return HKB_VERSION; }

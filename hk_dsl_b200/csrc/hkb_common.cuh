@@ -1,0 +1,63 @@
+// Device helpers shared by the hkb kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/hkb.h"
+
+namespace hkb {
+
+constexpr int TILE_TOKENS = 16;  // tokens per KV tile: one 16-token page, or a 16-token slice of a larger one
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// 16-byte asynchronous global->shared copy that bypasses L1 (KV is read once).
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+// Two bf16 packed in 32 bits -> two floats (exact: bf16 is the top half of an fp32).
+__device__ __forceinline__ float bf16lo(uint32_t x) { return __uint_as_float(x << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t x) { return __uint_as_float(x & 0xffff0000u); }
+
+// Two e4m3 in the low 16 bits -> two floats (exact), through the f16x2 convert.
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint16_t x) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(h2) : "h"(x));
+  __half2 h = *reinterpret_cast<__half2*>(&h2);
+  return __half22float2(h);
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Position of 16-byte chunk `c` of row `r` inside a shared-memory tile whose rows
+// are ROW_BYTES long: chunks are XOR-swizzled by the row so that eight rows read
+// at the same column (ldmatrix) and eight columns of one row are both conflict-free.
+template <int ROW_BYTES>
+__device__ __forceinline__ uint32_t tile_off(int r, int c) {
+  return static_cast<uint32_t>(r * ROW_BYTES + ((c ^ (r & 7)) << 4));
+}
+
+}  // namespace hkb

@@ -1,0 +1,219 @@
+// Host entry points of the paged decode (walk + LSE merge), the merge kernel, and
+// the dispatch from (head_dim, kv dtype, GQA group) to a walk instantiation.
+#include "hkb_walk_cc.cuh"
+#include "hkb_walk_mma.cuh"
+
+extern thread_local int hkb_tls_cuda_error;
+
+namespace hkb {
+
+// ---------------------------------------------------------------------------------
+// LSE merge. grid = (q heads, sequences), D/4 threads: a thread owns 4 output dims and
+// reads every live part's float4. Latency-bound at decode sizes (a few microseconds).
+// Weights follow the normalised-partial convention (python/hk/ops/paged.py:394-458):
+// w_p = exp(lse_p - max lse); the numerator takes w_p * out_p, the denominator w_p.
+// ---------------------------------------------------------------------------------
+struct MergeArgs {
+  void* out;
+  int64_t out_stride_tok, out_stride_head;
+  int out_is_f32;
+  float* out_lse;
+  const float* part_out;
+  int64_t part_stride_p, part_stride_seq;
+  const float* part_lse;
+  int64_t lse_stride_p, lse_stride_seq;
+  int num_parts, num_q_heads, head_dim;
+  const int* seq_lens;
+  const int* q_start;
+};
+
+__global__ void merge_kernel(const MergeArgs a) {
+  const int h = blockIdx.x, seq = blockIdx.y;
+  const int d = threadIdx.x * 4;
+  int row = seq;
+  if (a.q_start) {
+    row = __ldg(a.q_start + seq);
+    if (__ldg(a.q_start + seq + 1) <= row) return;
+  }
+  const bool empty = a.seq_lens && __ldg(a.seq_lens + seq) <= 0;
+  const float* lse = a.part_lse + (int64_t)seq * a.lse_stride_seq + h;
+  float mx = -INFINITY;
+  if (!empty)
+    for (int p = 0; p < a.num_parts; ++p) mx = fmaxf(mx, __ldg(lse + (int64_t)p * a.lse_stride_p));
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float den = 0.f;
+  if (mx != -INFINITY) {
+    const float* po = a.part_out + (int64_t)seq * a.part_stride_seq + (int64_t)h * a.head_dim + d;
+    for (int p = 0; p < a.num_parts; ++p) {
+      const float lp = __ldg(lse + (int64_t)p * a.lse_stride_p);
+      if (lp == -INFINITY) continue;  // an empty part's memory is never read
+      const float w = __expf(lp - mx);
+      const float4 x = __ldg(reinterpret_cast<const float4*>(po + (int64_t)p * a.part_stride_p));
+      acc.x = fmaf(w, x.x, acc.x); acc.y = fmaf(w, x.y, acc.y);
+      acc.z = fmaf(w, x.z, acc.z); acc.w = fmaf(w, x.w, acc.w);
+      den += w;
+    }
+  }
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+  const int64_t off = (int64_t)row * a.out_stride_tok + (int64_t)h * a.out_stride_head + d;
+  if (a.out_is_f32) {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + off) = acc;
+  } else {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.out) + off) = pk;
+  }
+  if (a.out_lse && threadIdx.x == 0)
+    a.out_lse[(int64_t)row * a.num_q_heads + h] = den > 0.f ? mx + __logf(den) : -INFINITY;
+}
+
+// ---------------------------------------------------------------------------------
+// Launch helpers
+// ---------------------------------------------------------------------------------
+template <typename K>
+static int launch_walk(K kernel, int smem_bytes, int threads, dim3 grid, const DecodeArgs& a, cudaStream_t st) {
+  // Opt in to more than 48 KB of dynamic shared memory once per device for this kernel.
+  static bool armed[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess && dev >= 0 && dev < 64 && !armed[dev]) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e == cudaSuccess) armed[dev] = true;
+  }
+  if (e == cudaSuccess) {
+    kernel<<<grid, threads, smem_bytes, st>>>(a);
+    e = cudaGetLastError();
+  }
+  if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
+  return HKB_OK;
+}
+
+// CUDA-core walk: GH query heads a pass, ceil(group / GH) passes a kv head.
+template <int D, bool FP8>
+static int dispatch_cc(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
+  constexpr int WARPS = 4;
+  constexpr int NST = FP8 ? 4 : 3;
+  int gh;
+  switch (a.group) {
+    case 1: gh = 1; break;
+    case 2: gh = 2; break;
+    case 3: case 5: case 6: gh = 3; break;
+    default: gh = 4; break;
+  }
+  const int chunks = (a.group + gh - 1) / gh;
+  dim3 grid(a.num_splits, a.num_kv_heads * chunks, num_seqs);
+#define HKB_CC(GH_)                                                                               \
+  case GH_:                                                                                       \
+    return launch_walk(walk_cc_kernel<D, FP8, GH_, WARPS, NST>, WalkCC<D, FP8, GH_, WARPS, NST>::SMEM_BYTES, \
+                       WARPS * 32, grid, a, st);
+  switch (gh) {
+    HKB_CC(1) HKB_CC(2) HKB_CC(3) HKB_CC(4)
+  }
+#undef HKB_CC
+  return HKB_ERR_UNSUPPORTED;
+}
+
+// Tensor-core walk for groups of 8 to 16: NT 8-head column tiles a CTA.
+template <int D, bool FP8>
+static int dispatch_mma(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
+  constexpr int WARPS = 4;
+  constexpr int NST = FP8 ? 4 : 3;
+  dim3 grid(a.num_splits, a.num_kv_heads, num_seqs);
+  if (a.group <= 8)
+    return launch_walk(walk_mma_kernel<D, FP8, 1, WARPS, NST>, WalkMMA<D, FP8, 1, WARPS, NST>::SMEM_BYTES,
+                       WARPS * 32, grid, a, st);
+  return launch_walk(walk_mma_kernel<D, FP8, 2, WARPS, NST>, WalkMMA<D, FP8, 2, WARPS, NST>::SMEM_BYTES,
+                     WARPS * 32, grid, a, st);
+}
+
+}  // namespace hkb
+
+extern "C" int hkb_paged_decode(void* out, int64_t out_stride_tok, int64_t out_stride_head,
+                                const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                                hkb_cache_t kc, hkb_cache_t vc,
+                                const int32_t* block_table, int64_t table_stride, int max_pages,
+                                const int32_t* seq_lens, const int32_t* q_start,
+                                int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                                int block_size, float scale, int kv_dtype,
+                                const float* k_scale, const float* v_scale,
+                                int num_splits, float* part_out, float* part_lse, void* stream) {
+  using namespace hkb;
+  if (num_seqs < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || max_pages < 0) return HKB_ERR_SIZE;
+  if (num_seqs == 0) return HKB_OK;
+  if (num_seqs > 65535 * 16 || num_splits > 0x7fffffff) return HKB_ERR_SIZE;
+  if (!out || !q || !kc.ptr || !vc.ptr || !block_table || !seq_lens) return HKB_ERR_NULL;
+  if (head_dim != 64 && head_dim != 128) return HKB_ERR_HEAD_DIM;
+  if (block_size <= 0 || block_size % TILE_TOKENS) return HKB_ERR_BLOCK_SIZE;
+  if (num_q_heads % num_kv_heads) return HKB_ERR_GROUP;
+  const int group = num_q_heads / num_kv_heads;
+  if (group > HKB_MAX_GROUP) return HKB_ERR_GROUP;
+  if (kv_dtype != HKB_KV_BF16 && kv_dtype != HKB_KV_FP8_E4M3) return HKB_ERR_DTYPE;
+  const bool fp8 = kv_dtype == HKB_KV_FP8_E4M3;
+  if (fp8 && (!k_scale || !v_scale)) return HKB_ERR_SCALE;
+  if (fp8 && head_dim != 128) return HKB_ERR_UNSUPPORTED;
+  if (num_splits < 1 || num_splits > HKB_MAX_SPLITS) return HKB_ERR_SPLITS;
+  if (num_splits > 1 && (!part_out || !part_lse)) return HKB_ERR_SPLITS;
+  if (max_pages < 1 || kc.num_blocks < 1 || vc.num_blocks < 1) return HKB_ERR_SIZE;
+  if (num_seqs > 65535 || num_kv_heads * 2 > 65535) return HKB_ERR_SIZE;
+  const int es = fp8 ? 1 : 2;
+  // every 16-byte chunk of a KV row, a q row and an out row must be 16-byte aligned
+  const int64_t kv_strides = kc.stride_block | kc.stride_token | kc.stride_head | vc.stride_block |
+                             vc.stride_token | vc.stride_head;
+  if ((kv_strides * es) % 16) return HKB_ERR_STRIDE;
+  if ((q_stride_tok | q_stride_head) % 8) return HKB_ERR_STRIDE;
+  if (((uintptr_t)kc.ptr | (uintptr_t)vc.ptr | (uintptr_t)q) % 16) return HKB_ERR_ALIGN;
+  if ((uintptr_t)out % 2 || (part_out && (uintptr_t)part_out % 16)) return HKB_ERR_ALIGN;
+
+  DecodeArgs a;
+  a.out = (__nv_bfloat16*)out; a.out_stride_tok = out_stride_tok; a.out_stride_head = out_stride_head;
+  a.q = (const __nv_bfloat16*)q; a.q_stride_tok = q_stride_tok; a.q_stride_head = q_stride_head;
+  a.k = (const uint8_t*)kc.ptr; a.v = (const uint8_t*)vc.ptr;
+  a.k_stride_block = kc.stride_block * es; a.k_stride_token = kc.stride_token * es; a.k_stride_head = kc.stride_head * es;
+  a.v_stride_block = vc.stride_block * es; a.v_stride_token = vc.stride_token * es; a.v_stride_head = vc.stride_head * es;
+  const int64_t nb = kc.num_blocks < vc.num_blocks ? kc.num_blocks : vc.num_blocks;
+  a.num_blocks = nb > 0x7fffffff ? 0x7fffffff : (int)nb;
+  a.block_table = block_table; a.table_stride = table_stride; a.max_pages = max_pages;
+  a.seq_lens = seq_lens; a.q_start = q_start;
+  a.num_q_heads = num_q_heads; a.num_kv_heads = num_kv_heads; a.group = group;
+  a.tiles_per_page = block_size / TILE_TOKENS;
+  a.scale = scale; a.k_scale = k_scale; a.v_scale = v_scale;
+  a.num_splits = num_splits; a.part_out = part_out; a.part_lse = part_lse;
+  cudaStream_t st = (cudaStream_t)stream;
+
+  const bool mma = group >= 8;
+  if (head_dim == 128) {
+    if (fp8) return mma ? dispatch_mma<128, true>(a, num_seqs, st) : dispatch_cc<128, true>(a, num_seqs, st);
+    return mma ? dispatch_mma<128, false>(a, num_seqs, st) : dispatch_cc<128, false>(a, num_seqs, st);
+  }
+  return mma ? dispatch_mma<64, false>(a, num_seqs, st) : dispatch_cc<64, false>(a, num_seqs, st);
+}
+
+extern "C" int hkb_merge(void* out, int64_t out_stride_tok, int64_t out_stride_head, int out_is_f32,
+                         float* out_lse,
+                         const float* part_out, int64_t part_stride_p, int64_t part_stride_seq,
+                         const float* part_lse, int64_t lse_stride_p, int64_t lse_stride_seq,
+                         int num_parts, int num_seqs, int num_q_heads, int head_dim,
+                         const int32_t* seq_lens, const int32_t* q_start, void* stream) {
+  using namespace hkb;
+  if (num_seqs < 0 || num_q_heads <= 0 || num_parts < 1) return HKB_ERR_SIZE;
+  if (num_seqs == 0) return HKB_OK;
+  if (!out || !part_out || !part_lse) return HKB_ERR_NULL;
+  if (head_dim <= 0 || head_dim % 4 || head_dim > 1024) return HKB_ERR_HEAD_DIM;
+  if (num_seqs > 65535) return HKB_ERR_SIZE;
+  if ((part_stride_p | part_stride_seq) % 4 || (out_stride_tok | out_stride_head) % 4) return HKB_ERR_STRIDE;
+  if ((uintptr_t)part_out % 16 || (uintptr_t)out % (out_is_f32 ? 16 : 8)) return HKB_ERR_ALIGN;
+  MergeArgs a;
+  a.out = out; a.out_stride_tok = out_stride_tok; a.out_stride_head = out_stride_head;
+  a.out_is_f32 = out_is_f32; a.out_lse = out_lse;
+  a.part_out = part_out; a.part_stride_p = part_stride_p; a.part_stride_seq = part_stride_seq;
+  a.part_lse = part_lse; a.lse_stride_p = lse_stride_p; a.lse_stride_seq = lse_stride_seq;
+  a.num_parts = num_parts; a.num_q_heads = num_q_heads; a.head_dim = head_dim;
+  a.seq_lens = seq_lens; a.q_start = q_start;
+  merge_kernel<<<dim3(num_q_heads, num_seqs), head_dim / 4, 0, (cudaStream_t)stream>>>(a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
+  return HKB_OK;
+}

@@ -1,0 +1,104 @@
+// Shared pieces of the paged decode walk: launch arguments, the per-warp KV tile
+// pipeline (cp.async ring in shared memory) and the page-id prefetcher.
+#pragma once
+
+#include "hkb_common.cuh"
+
+namespace hkb {
+
+struct DecodeArgs {
+  __nv_bfloat16* out;
+  int64_t out_stride_tok, out_stride_head;
+  const __nv_bfloat16* q;
+  int64_t q_stride_tok, q_stride_head;
+  const uint8_t* k;  // cache bases; strides below are in BYTES
+  const uint8_t* v;
+  int64_t k_stride_block, k_stride_token, k_stride_head;
+  int64_t v_stride_block, v_stride_token, v_stride_head;
+  int num_blocks;  // page ids are clamped to [0, num_blocks)
+  const int* block_table;
+  int64_t table_stride;
+  int max_pages;
+  const int* seq_lens;
+  const int* q_start;
+  int num_q_heads, num_kv_heads, group;
+  int tiles_per_page;  // block_size / 16
+  float scale;
+  const float* k_scale;
+  const float* v_scale;
+  int num_splits;
+  float* part_out;
+  float* part_lse;
+};
+
+// The range of 16-token tiles split `split` of a sequence with `n_tiles` tiles walks:
+// contiguous, ceil(n_tiles / splits) each, as hk-dsl cuts it (python/hk/ops/paged.py:552-559).
+__device__ __forceinline__ void split_range(int n_tiles, int splits, int split, int& lo, int& hi) {
+  const int per = max((n_tiles + splits - 1) / splits, 1);
+  lo = min(n_tiles, split * per);
+  hi = min(n_tiles, lo + per);
+}
+
+// One warp's view of the KV stream of a (sequence, kv head): issues the cp.async
+// copies of tile `t` (K rows then V rows) into ring stage `stage`. Page ids come
+// from `PageIds`, which keeps 32 ids a batch in registers, one batch ahead, so that
+// the table read is never on the critical path of a copy.
+template <int ROWB>
+struct TileLoader {
+  static constexpr int CPR = ROWB / 16;              // 16-byte chunks per row
+  static constexpr int TILE_BYTES = TILE_TOKENS * ROWB;
+  static constexpr int ITERS = TILE_TOKENS * CPR / 32;
+  const uint8_t* kbase;  // + kv head offset
+  const uint8_t* vbase;
+  int64_t ksb, kst, vsb, vst;
+  int tiles_per_page, num_blocks;
+
+  __device__ __forceinline__ void issue(uint32_t smem_stage, int tile, int page_id, int lane) const {
+    const int sub = tile % tiles_per_page;
+    const int id = min(max(page_id, 0), num_blocks - 1);
+    const uint8_t* kp = kbase + (int64_t)id * ksb + (int64_t)(sub * TILE_TOKENS) * kst;
+    const uint8_t* vp = vbase + (int64_t)id * vsb + (int64_t)(sub * TILE_TOKENS) * vst;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int x = it * 32 + lane;
+      const int r = x / CPR, c = x % CPR;
+      cp_async16(smem_stage + tile_off<ROWB>(r, c), kp + (int64_t)r * kst + c * 16);
+    }
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int x = it * 32 + lane;
+      const int r = x / CPR, c = x % CPR;
+      cp_async16(smem_stage + TILE_BYTES + tile_off<ROWB>(r, c), vp + (int64_t)r * vst + c * 16);
+    }
+  }
+};
+
+struct PageIds {
+  const int* row;  // this sequence's block-table row
+  int max_pages, tiles_per_page, t_hi;
+  int base;        // first tile of the batch held in `cur`
+  int cur, nxt;
+
+  __device__ __forceinline__ int fetch(int first_tile, int lane) const {
+    const int t = first_tile + lane;
+    if (t >= t_hi) return 0;
+    const int p = min(t / tiles_per_page, max_pages - 1);
+    return __ldg(row + p);
+  }
+  __device__ __forceinline__ void init(int t_lo, int lane) {
+    base = t_lo;
+    cur = fetch(base, lane);
+    nxt = fetch(base + 32, lane);
+  }
+  // Page id of tile `t`; tiles are asked for in increasing order.
+  __device__ __forceinline__ int get(int t, int lane) {
+    if (t - base >= 32) {
+      base += 32;
+      cur = nxt;
+      nxt = fetch(base + 32, lane);
+    }
+    return __shfl_sync(0xffffffffu, cur, t - base);
+  }
+};
+
+}  // namespace hkb

@@ -1,0 +1,319 @@
+// The decode walk on tensor cores, for GQA groups of 8 to 16: one CTA per
+// (sequence, kv head, kv split), the group's query heads as the N=8 columns of
+// mma.sync.m16n8k16 tiles (NT = 1 for a group of 8, 2 for 9..16).
+//
+// The contraction is written transposed, as hk-dsl's walk is (python/hk/ops/paged.py:77-83,
+// 590-638): S^T[kv, q] = K[kv, :] . Q[q, :] puts a 16-token tile on M and the heads on N,
+// and O^T[d, q] += V^T[d, kv] . P^T[kv, q] puts head_dim on M. A 16-token KV tile is then
+// exactly one A operand of the first product and the K dimension of the second, and a
+// group of 8 wastes no tensor-core lanes.
+//
+// The memory side is the CUDA-core walk's: every warp streams its own contiguous share
+// of the split's tiles through its own cp.async ring; the CTA's WARPS online-softmax
+// streams are folded once at the end. fp8 tiles are widened to bf16 in a per-warp
+// shared-memory tile first (exact: e4m3 fits bf16), so both dtypes share the mma code.
+#pragma once
+
+#include "hkb_decode.cuh"
+
+namespace hkb {
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
+  return y;
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int D, bool FP8, int NT, int WARPS, int NST>
+struct WalkMMA {
+  static constexpr int ES = FP8 ? 1 : 2;
+  static constexpr int ROWB = D * ES;     // bytes of a row as it sits in the cache
+  static constexpr int ROWB16 = D * 2;    // bytes of a row as the mma reads it
+  using Loader = TileLoader<ROWB>;
+  static constexpr int STAGE_BYTES = 2 * Loader::TILE_BYTES;
+  static constexpr int TILE16_BYTES = TILE_TOKENS * ROWB16;
+  static constexpr int WIDEN_BYTES = FP8 ? 2 * TILE16_BYTES : 0;  // per warp
+  static constexpr int KD = D / 16;       // 16-wide chunks of head_dim
+  static constexpr int HEADS = NT * 8;
+  static constexpr int PIPE_BYTES = WARPS * (NST * STAGE_BYTES + WIDEN_BYTES);
+  static constexpr int FOLD_BYTES = WARPS * HEADS * (D + 2) * 4;
+  static constexpr int SMEM_BYTES = PIPE_BYTES > FOLD_BYTES ? PIPE_BYTES : FOLD_BYTES;
+
+  // fp8 tile (rows of D bytes) -> bf16 tile (rows of 2D bytes), both swizzled.
+  __device__ static __forceinline__ void widen(uint32_t src, uint32_t dst, int lane) {
+    constexpr int CPR = ROWB / 16;
+#pragma unroll
+    for (int it = 0; it < TILE_TOKENS * CPR / 32; ++it) {
+      const int x = it * 32 + lane;
+      const int r = x / CPR, c = x % CPR;
+      const uint4 v = lds128(src + tile_off<ROWB>(r, c));
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      uint32_t o[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 a = e4m3x2_to_float2((uint16_t)(w[i] & 0xffffu));
+        const float2 b = e4m3x2_to_float2((uint16_t)(w[i] >> 16));
+        o[2 * i] = pack_bf16x2(a.x, a.y);
+        o[2 * i + 1] = pack_bf16x2(b.x, b.y);
+      }
+      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(dst + tile_off<ROWB16>(r, 2 * c)), "r"(o[0]),
+                   "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(dst + tile_off<ROWB16>(r, 2 * c + 1)), "r"(o[4]),
+                   "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+    }
+  }
+
+  template <bool LAST>
+  __device__ static __forceinline__ void tile(uint32_t ktile, uint32_t vtile, int tok0, int seq_len, int lane,
+                                              float qs, const uint32_t (&qb)[NT][KD][2], float (&m)[NT][2],
+                                              float (&l)[NT][2], float (&o)[NT][KD][4]) {
+    float sc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sc[nt][i] = 0.f;
+    // S^T = K Q^T: A = the K tile (tokens x 16 dims), B = Q^T
+    {
+      const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+      for (int kc = 0; kc < KD; ++kc) {
+        uint32_t a[4];
+        ldmatrix_x4(a, ktile + tile_off<ROWB16>(r, kc * 2 + (lane >> 4)));
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) mma_bf16(sc[nt], a, qb[nt][kc]);
+      }
+    }
+    const int tA = tok0 + (lane >> 2), tB = tA + 8;  // the two tokens this lane holds scores of
+    uint32_t pb[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sc[nt][i] *= qs;
+      if (LAST) {
+        if (tA >= seq_len) { sc[nt][0] = -INFINITY; sc[nt][1] = -INFINITY; }
+        if (tB >= seq_len) { sc[nt][2] = -INFINITY; sc[nt][3] = -INFINITY; }
+      }
+      // column (head) maxima over the tile's 16 tokens: 2 local rows, then the 8 row groups
+      float mx[2] = {fmaxf(sc[nt][0], sc[nt][2]), fmaxf(sc[nt][1], sc[nt][3])};
+#pragma unroll
+      for (int x = 4; x < 32; x <<= 1) {
+        mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], x));
+        mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], x));
+      }
+      float mu[2];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const float m_new = fmaxf(m[nt][c], mx[c]);
+        mu[c] = (m_new == -INFINITY) ? 0.f : m_new;
+        if (m_new != m[nt][c]) {
+          const float alpha = fast_exp2(m[nt][c] - mu[c]);
+          l[nt][c] *= alpha;
+#pragma unroll
+          for (int dt = 0; dt < KD; ++dt) { o[nt][dt][c] *= alpha; o[nt][dt][c + 2] *= alpha; }
+          m[nt][c] = m_new;
+        }
+      }
+      const float p0 = fast_exp2(sc[nt][0] - mu[0]), p1 = fast_exp2(sc[nt][1] - mu[1]);
+      const float p2 = fast_exp2(sc[nt][2] - mu[0]), p3 = fast_exp2(sc[nt][3] - mu[1]);
+      l[nt][0] += p0 + p2;
+      l[nt][1] += p1 + p3;
+      // [token, head] fragments -> [head, token] = the B operand of the second product
+      pb[nt][0] = movmatrix_trans(pack_bf16x2(p0, p1));
+      pb[nt][1] = movmatrix_trans(pack_bf16x2(p2, p3));
+    }
+    // O^T += V^T P^T: A = V^T (16 dims x tokens), read transposed from the row-major V tile
+    {
+      const int r = (lane & 7) + (lane >> 4) * 8;
+#pragma unroll
+      for (int dt = 0; dt < KD; ++dt) {
+        uint32_t a[4];
+        ldmatrix_x4_trans(a, vtile + tile_off<ROWB16>(r, dt * 2 + ((lane >> 3) & 1)));
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) mma_bf16(o[nt][dt], a, pb[nt]);
+      }
+    }
+  }
+
+  // Zero the V rows of a tail tile that lie past seq_len: P is 0 there, but 0 * NaN is NaN.
+  __device__ static __forceinline__ void scrub_tail(uint32_t vtile, int tok0, int seq_len, int lane) {
+    constexpr int CPR = ROWB16 / 16;
+    for (int x = lane; x < TILE_TOKENS * CPR; x += 32) {
+      const int r = x / CPR, c = x % CPR;
+      if (tok0 + r >= seq_len)
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(vtile + tile_off<ROWB16>(r, c)), "r"(0u) : "memory");
+    }
+  }
+
+  __device__ static __forceinline__ void run(const DecodeArgs& a, uint8_t* smem) {
+    const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    const int nh = a.group;  // <= HEADS
+    const int hq0 = kvh * a.group;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    int row = seq;
+    if (a.q_start) {
+      row = __ldg(a.q_start + seq);
+      if (__ldg(a.q_start + seq + 1) <= row) return;
+    }
+    const int seq_len = max(__ldg(a.seq_lens + seq), 0);
+    const int n_tiles = (seq_len + TILE_TOKENS - 1) / TILE_TOKENS;
+    int lo, hi;
+    split_range(n_tiles, a.num_splits, split, lo, hi);
+    const bool partial = a.num_splits > 1;
+    float* po = partial ? a.part_out + ((int64_t)(seq * a.num_splits + split) * a.num_q_heads + hq0) * D : nullptr;
+    float* pl = partial ? a.part_lse + (int64_t)(seq * a.num_splits + split) * a.num_q_heads + hq0 : nullptr;
+
+    if (lo >= hi) {
+      if (partial) {
+        if (threadIdx.x < nh) pl[threadIdx.x] = -INFINITY;
+      } else {
+        for (int x = threadIdx.x; x < nh * D; x += WARPS * 32)
+          a.out[(int64_t)row * a.out_stride_tok + (int64_t)(hq0 + x / D) * a.out_stride_head + x % D] =
+              __float2bfloat16(0.f);
+      }
+      return;
+    }
+    const int per_w = (hi - lo + WARPS - 1) / WARPS;
+    const int t_lo = min(hi, lo + warp * per_w);
+    const int t_hi = min(hi, t_lo + per_w);
+    const int n = t_hi - t_lo;
+
+    float qs = a.scale * LOG2E;
+    float vs = 1.f;
+    if (FP8) { qs *= __ldg(a.k_scale); vs = __ldg(a.v_scale); }
+
+    // Q^T fragments: b0 = Q[head lane/4][16 kc + 2 (lane%4) + {0,1}], b1 = the same 8 dims on
+    uint32_t qb[NT][KD][2];
+    float m[NT][2], l[NT][2], o[NT][KD][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int h = nt * 8 + (lane >> 2);
+      const uint32_t* qp = reinterpret_cast<const uint32_t*>(
+          a.q + (int64_t)row * a.q_stride_tok + (int64_t)(hq0 + h) * a.q_stride_head);
+#pragma unroll
+      for (int kc = 0; kc < KD; ++kc) {
+        qb[nt][kc][0] = h < nh ? __ldg(qp + kc * 8 + (lane & 3)) : 0u;
+        qb[nt][kc][1] = h < nh ? __ldg(qp + kc * 8 + 4 + (lane & 3)) : 0u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[nt][kc][i] = 0.f;
+      }
+      m[nt][0] = m[nt][1] = -INFINITY;
+      l[nt][0] = l[nt][1] = 0.f;
+    }
+
+    Loader ld;
+    ld.kbase = a.k + (int64_t)kvh * a.k_stride_head;
+    ld.vbase = a.v + (int64_t)kvh * a.v_stride_head;
+    ld.ksb = a.k_stride_block; ld.kst = a.k_stride_token;
+    ld.vsb = a.v_stride_block; ld.vst = a.v_stride_token;
+    ld.tiles_per_page = a.tiles_per_page; ld.num_blocks = a.num_blocks;
+    PageIds ids;
+    ids.row = a.block_table + (int64_t)seq * a.table_stride;
+    ids.max_pages = a.max_pages; ids.tiles_per_page = a.tiles_per_page; ids.t_hi = t_hi;
+    ids.init(t_lo, lane);
+
+    const uint32_t ring = smem_u32(smem) + warp * (NST * STAGE_BYTES + WIDEN_BYTES);
+    const uint32_t wide = ring + NST * STAGE_BYTES;
+#pragma unroll
+    for (int k = 0; k < NST - 1; ++k) {
+      if (k < n) ld.issue(ring + k * STAGE_BYTES, t_lo + k, ids.get(t_lo + k, lane), lane);
+      cp_async_commit();
+    }
+    for (int k = 0; k < n; ++k) {
+      cp_async_wait<NST - 2>();
+      __syncwarp();
+      const int kn = k + NST - 1;
+      if (kn < n) ld.issue(ring + (kn % NST) * STAGE_BYTES, t_lo + kn, ids.get(t_lo + kn, lane), lane);
+      cp_async_commit();
+      const uint32_t stage = ring + (k % NST) * STAGE_BYTES;
+      uint32_t ktile = stage, vtile = stage + Loader::TILE_BYTES;
+      if (FP8) {
+        widen(stage, wide, lane);
+        widen(stage + Loader::TILE_BYTES, wide + TILE16_BYTES, lane);
+        ktile = wide; vtile = wide + TILE16_BYTES;
+        __syncwarp();
+      }
+      const int t = t_lo + k;
+      if (t == n_tiles - 1) {
+        scrub_tail(vtile, t * TILE_TOKENS, seq_len, lane);
+        __syncwarp();
+        tile<true>(ktile, vtile, t * TILE_TOKENS, seq_len, lane, qs, qb, m, l, o);
+      } else {
+        tile<false>(ktile, vtile, t * TILE_TOKENS, seq_len, lane, qs, qb, m, l, o);
+      }
+    }
+    cp_async_wait<0>();
+    // each lane summed only its own two token rows: complete l over the 8 row groups
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int x = 4; x < 32; x <<= 1) l[nt][c] += __shfl_xor_sync(0xffffffffu, l[nt][c], x);
+    __syncthreads();
+
+    float* fo = reinterpret_cast<float*>(smem);   // [WARPS][HEADS][D]
+    float* fml = fo + WARPS * HEADS * D;          // [WARPS][HEADS][2]
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int h = nt * 8 + 2 * (lane & 3) + c;
+#pragma unroll
+        for (int dt = 0; dt < KD; ++dt) {
+          fo[(warp * HEADS + h) * D + dt * 16 + (lane >> 2)] = o[nt][dt][c];
+          fo[(warp * HEADS + h) * D + dt * 16 + 8 + (lane >> 2)] = o[nt][dt][c + 2];
+        }
+        if ((lane >> 2) == 0) { fml[(warp * HEADS + h) * 2] = m[nt][c]; fml[(warp * HEADS + h) * 2 + 1] = l[nt][c]; }
+      }
+    __syncthreads();
+    for (int x = threadIdx.x; x < nh * D; x += WARPS * 32) {
+      const int h = x / D, d = x % D;
+      float mm = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, fml[(w * HEADS + h) * 2]);
+      float num = 0.f, den = 0.f;
+      if (mm != -INFINITY) {
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+          const float wt = fast_exp2(fml[(w * HEADS + h) * 2] - mm);
+          num = fmaf(wt, fo[(w * HEADS + h) * D + d], num);
+          den = fmaf(wt, fml[(w * HEADS + h) * 2 + 1], den);
+        }
+      }
+      const float val = den > 0.f ? num / den * vs : 0.f;
+      if (partial) {
+        po[h * D + d] = val;
+        if (d == 0) pl[h] = den > 0.f ? (mm + log2f(den)) * LN2 : -INFINITY;
+      } else {
+        a.out[(int64_t)row * a.out_stride_tok + (int64_t)(hq0 + h) * a.out_stride_head + d] = __float2bfloat16(val);
+      }
+    }
+  }
+};
+
+template <int D, bool FP8, int NT, int WARPS, int NST>
+__global__ void __launch_bounds__(WARPS * 32) walk_mma_kernel(const DecodeArgs a) {
+  extern __shared__ __align__(128) uint8_t hkb_smem[];
+  WalkMMA<D, FP8, NT, WARPS, NST>::run(a, hkb_smem);
+}
+
+}  // namespace hkb

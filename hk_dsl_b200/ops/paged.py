@@ -1,0 +1,406 @@
+"""Paged KV cache write and paged GQA decode attention: the host side.
+
+Mirrors the decode half of hk-dsl's `hk.ops.paged` (python/hk/ops/paged.py): the launch
+contract (`check_decode`, :746-802), the split planner (`plan_splits`, :877-914), the
+split scratch (`fused_scratch`, :733-743), the two-launch driver (`decode`, :811-828) and
+the merge (`merge_splits`, :283-317) -- with the kernels behind them hand-written CUDA for
+sm_100a reached through the C ABI (include/hkb.h) instead of generated HIP.
+
+Two call forms:
+
+* the engine-flat form the vLLM-style routes use,
+  `reshape_and_cache(key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype,
+  k_scale, v_scale)` and `paged_attention_decode(out, query, key_cache, value_cache,
+  block_tables, seq_lens, scale, kv_cache_dtype, k_scale, v_scale, ...)`, whose caches are
+  `(num_blocks, block_size, num_kv_heads, head_dim)` views with any strides (hk's
+  head-major storage is passed as `.transpose(1, 2)`, as the reference's backend passes it
+  to vLLM's cache write, python/hk/integration/vllm_backend.py:594-599);
+* hk's own form, `decode(q, k_cache, v_cache, block_table, seq_lens, out, scratch, splits)`
+  on `(requests, kv_heads, group, head_dim)` q/out and `(blocks, kv_heads, KV_BLOCK, head_dim)`
+  caches.
+
+Everything launches on torch's current stream, reads nothing back, allocates nothing after
+the scratch exists, and so can be captured into a CUDA graph. There is no fallback: a call
+the kernels do not take raises.
+"""
+
+from __future__ import annotations
+
+import math
+import os
+from typing import Optional, Tuple
+
+import torch
+
+from ..runtime import lib as _lib
+
+#: The cache's page size the backend declares; the kernels read any multiple of 16.
+KV_BLOCK = 16
+#: Most query rows (the GQA group) a kv head may have.
+Q_TILE = 16
+HEAD_DIMS = (64, 128)
+MAX_SPLITS = _lib.MAX_SPLITS
+
+_FP8_NAMES = ("fp8", "fp8_e4m3")
+_FP8_DTYPES = tuple(d for d in (getattr(torch, "float8_e4m3fn", None), torch.uint8) if d is not None)
+
+
+def kv_dtype_code(kv_cache_dtype: str, cache: torch.Tensor, q_dtype=torch.bfloat16) -> int:
+    """hkb's KV element code for vLLM's `kv_cache_dtype` string and the cache tensor given."""
+    name = (kv_cache_dtype or "auto").lower()
+    if name.startswith("auto") or name in ("bfloat16", "bf16"):
+        if cache.dtype != torch.bfloat16:
+            raise TypeError(f"hk.ops.paged: kv_cache_dtype {kv_cache_dtype!r} keeps the cache in bfloat16, "
+                            f"the cache is {cache.dtype}")
+        return _lib.KV_BF16
+    if name in _FP8_NAMES:
+        if cache.dtype not in _FP8_DTYPES:
+            raise TypeError(f"hk.ops.paged: kv_cache_dtype {kv_cache_dtype!r} needs a float8_e4m3fn (or uint8) "
+                            f"cache, the cache is {cache.dtype}")
+        return _lib.KV_FP8_E4M3
+    raise NotImplementedError(f"hk.ops.paged: kv_cache_dtype {kv_cache_dtype!r}: only auto (bf16) and "
+                              f"fp8 / fp8_e4m3 caches are implemented")
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _cache_t(c: torch.Tensor) -> _lib.CacheT:
+    """A `(blocks, block_size, kv_heads, head_dim)` view as hkb_cache_t."""
+    return _lib.CacheT(c.data_ptr(), c.stride(0), c.stride(1), c.stride(2), c.shape[0])
+
+
+def _need_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("hk.ops.paged: tensors must be on a CUDA device; there is no CPU path")
+
+
+def _scale_ptr(s: Optional[torch.Tensor], fp8: bool, name: str) -> Optional[int]:
+    if s is None:
+        if fp8:
+            raise ValueError(f"hk.ops.paged: an fp8 cache needs {name} (a float32 tensor of one element)")
+        return None
+    if s.dtype != torch.float32 or s.numel() != 1:
+        raise TypeError(f"hk.ops.paged: {name} is {tuple(s.shape)} {s.dtype}; per-tensor float32 scale needed")
+    return s.data_ptr()
+
+
+# --------------------------------------------------------------------------------------
+# engine-flat form
+# --------------------------------------------------------------------------------------
+
+def reshape_and_cache(key: torch.Tensor, value: torch.Tensor, key_cache: torch.Tensor,
+                      value_cache: torch.Tensor, slot_mapping: torch.Tensor, kv_cache_dtype: str = "auto",
+                      k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None) -> None:
+    """Scatter new K/V rows into the paged caches by slot; slot < 0 is skipped.
+
+    vLLM's `reshape_and_cache_flash` signature and argument order
+    (tests/hk/engines/test_vllm_contract.py:271-277). `key`/`value` are
+    `(tokens, kv_heads, head_dim)` bf16; the caches `(blocks, block_size, kv_heads, head_dim)`
+    views of any strides, bf16 or fp8-e4m3; `slot_mapping` int64 or int32."""
+    _need_cuda(key, value, key_cache, value_cache, slot_mapping)
+    if key.dim() != 3 or value.shape != key.shape or key.dtype != torch.bfloat16 or value.dtype != key.dtype:
+        raise ValueError(f"hk.ops.paged: key {tuple(key.shape)} {key.dtype} / value {tuple(value.shape)} "
+                         f"{value.dtype}; the cache write reads (tokens, kv_heads, head_dim) bfloat16")
+    t, hkv, d = key.shape
+    for name, c in (("key_cache", key_cache), ("value_cache", value_cache)):
+        if c.dim() != 4 or c.shape[2] != hkv or c.shape[3] != d or c.stride(3) != 1:
+            raise ValueError(f"hk.ops.paged: {name} is {tuple(c.shape)} strides {c.stride()}; the cache write "
+                             f"needs (blocks, block_size, {hkv}, {d}) with head_dim contiguous")
+    if key.stride(2) != 1 or value.stride(2) != 1:
+        raise ValueError("hk.ops.paged: key/value head_dim must be contiguous")
+    if slot_mapping.dim() != 1 or slot_mapping.dtype not in (torch.int64, torch.int32) \
+            or not slot_mapping.is_contiguous():
+        raise TypeError(f"hk.ops.paged: slot_mapping is {tuple(slot_mapping.shape)} {slot_mapping.dtype}; "
+                        f"contiguous int64 or int32 (tokens,) needed")
+    n = min(t, slot_mapping.shape[0])
+    code = kv_dtype_code(kv_cache_dtype, key_cache)
+    if value_cache.dtype != key_cache.dtype or value_cache.shape[1] != key_cache.shape[1]:
+        raise ValueError("hk.ops.paged: key_cache and value_cache differ in dtype or block_size")
+    fp8 = code == _lib.KV_FP8_E4M3
+    rc = _lib.load().hkb_reshape_and_cache(
+        key.data_ptr(), value.data_ptr(), key.stride(0), key.stride(1), value.stride(0), value.stride(1),
+        _cache_t(key_cache), _cache_t(value_cache), slot_mapping.data_ptr(),
+        1 if slot_mapping.dtype == torch.int64 else 0, n, hkv, d, key_cache.shape[1], code,
+        _scale_ptr(k_scale, fp8, "k_scale"), _scale_ptr(v_scale, fp8, "v_scale"), _stream(key))
+    _lib.check("hkb_reshape_and_cache", rc)
+
+
+def split_scratch(num_seqs: int, num_q_heads: int, head_dim: int, num_splits: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(part_out, part_lse) for a split decode: fp32 normalised partials
+    `(num_seqs * num_splits, num_q_heads, head_dim)` and their natural-log lse
+    `(num_seqs * num_splits, num_q_heads)`."""
+    rows = num_seqs * num_splits
+    return (torch.empty(rows, num_q_heads, head_dim, device=device, dtype=torch.float32),
+            torch.empty(rows, num_q_heads, device=device, dtype=torch.float32))
+
+
+def paged_attention_decode(out: torch.Tensor, query: torch.Tensor, key_cache: torch.Tensor,
+                           value_cache: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor,
+                           scale: float, kv_cache_dtype: str = "auto",
+                           k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None, *,
+                           num_splits: Optional[int] = None,
+                           scratch: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                           query_start_loc: Optional[torch.Tensor] = None,
+                           max_seq_len: Optional[int] = None) -> torch.Tensor:
+    """Decode attention of one query token a sequence over a block-paged KV cache.
+
+    `query`/`out`: `(tokens, q_heads, head_dim)` bf16 (head_dim contiguous); caches
+    `(blocks, block_size, kv_heads, head_dim)` views, bf16 or fp8-e4m3 with per-tensor
+    `k_scale`/`v_scale`; `block_tables` `(seqs, max_pages)` int32; `seq_lens` `(seqs,)` int32.
+    `num_splits` None plans it from the batch and the table's width (host values only);
+    with more than one split the walk writes partials into `scratch` (allocated here if
+    not given -- pass it to stay allocation-free) and the merge kernel folds them."""
+    _need_cuda(out, query, key_cache, value_cache, block_tables, seq_lens)
+    if query.dim() != 3 or query.dtype != torch.bfloat16 or query.stride(2) != 1:
+        raise ValueError(f"hk.ops.paged: query is {tuple(query.shape)} {query.dtype}; the decode reads "
+                         f"(tokens, q_heads, head_dim) bfloat16 with head_dim contiguous")
+    if out.shape != query.shape or out.dtype != query.dtype or out.stride(2) != 1:
+        raise ValueError(f"hk.ops.paged: out is {tuple(out.shape)} {out.dtype}; it must match query "
+                         f"{tuple(query.shape)} {query.dtype}")
+    _, hq, d = query.shape
+    if key_cache.dim() != 4 or value_cache.shape != key_cache.shape or key_cache.stride(3) != 1 \
+            or value_cache.stride(3) != 1 or key_cache.shape[3] != d or value_cache.dtype != key_cache.dtype:
+        raise ValueError(f"hk.ops.paged: key_cache {tuple(key_cache.shape)} / value_cache "
+                         f"{tuple(value_cache.shape)}; the decode reads two (blocks, block_size, kv_heads, {d}) "
+                         f"views of one dtype")
+    _, bs, hkv, _ = key_cache.shape
+    if block_tables.dim() != 2 or block_tables.dtype != torch.int32 or block_tables.stride(1) != 1:
+        raise TypeError(f"hk.ops.paged: block_tables is {tuple(block_tables.shape)} {block_tables.dtype}; "
+                        f"(seqs, max_pages) int32 needed")
+    if seq_lens.dim() != 1 or seq_lens.dtype != torch.int32 or not seq_lens.is_contiguous():
+        raise TypeError(f"hk.ops.paged: seq_lens is {tuple(seq_lens.shape)} {seq_lens.dtype}; "
+                        f"contiguous (seqs,) int32 needed")
+    n = seq_lens.shape[0]
+    if block_tables.shape[0] < n:
+        raise ValueError(f"hk.ops.paged: block_tables has {block_tables.shape[0]} rows for {n} sequences")
+    qsl = None
+    if query_start_loc is not None:
+        if query_start_loc.dtype != torch.int32 or query_start_loc.numel() < n + 1 \
+                or not query_start_loc.is_contiguous():
+            raise TypeError("hk.ops.paged: query_start_loc must be contiguous int32 of seqs + 1 entries")
+        qsl = query_start_loc.data_ptr()
+    elif query.shape[0] < n:
+        raise ValueError(f"hk.ops.paged: {query.shape[0]} query rows for {n} sequences")
+    code = kv_dtype_code(kv_cache_dtype, key_cache)
+    fp8 = code == _lib.KV_FP8_E4M3
+    if num_splits is None:
+        tiles = block_tables.shape[1] * (bs // 16) if max_seq_len is None else -(-max_seq_len // 16)
+        num_splits = plan_splits(n, hkv, tiles, device=query.device)
+    po = pl = None
+    if num_splits > 1:
+        if scratch is None:
+            scratch = split_scratch(n, hq, d, num_splits, query.device)
+        po, pl = scratch
+        if po.dtype != torch.float32 or pl.dtype != torch.float32 or po.numel() < n * num_splits * hq * d \
+                or pl.numel() < n * num_splits * hq or not po.is_contiguous() or not pl.is_contiguous():
+            raise ValueError(f"hk.ops.paged: scratch too small or not contiguous fp32 for {n} sequences x "
+                             f"{num_splits} splits x {hq} heads x {d} (split_scratch)")
+    lib = _lib.load()
+    st = _stream(query)
+    rc = lib.hkb_paged_decode(
+        out.data_ptr(), out.stride(0), out.stride(1), query.data_ptr(), query.stride(0), query.stride(1),
+        _cache_t(key_cache), _cache_t(value_cache), block_tables.data_ptr(), block_tables.stride(0),
+        block_tables.shape[1], seq_lens.data_ptr(), qsl, n, hq, hkv, d, bs, float(scale), code,
+        _scale_ptr(k_scale, fp8, "k_scale"), _scale_ptr(v_scale, fp8, "v_scale"), num_splits,
+        po.data_ptr() if po is not None else None, pl.data_ptr() if pl is not None else None, st)
+    _lib.check("hkb_paged_decode", rc)
+    if num_splits > 1:
+        rc = lib.hkb_merge(out.data_ptr(), out.stride(0), out.stride(1), 0, None,
+                           po.data_ptr(), hq * d, num_splits * hq * d, pl.data_ptr(), hq, num_splits * hq,
+                           num_splits, n, hq, d, seq_lens.data_ptr(), qsl, st)
+        _lib.check("hkb_merge", rc)
+    return out
+
+
+def merge_partials(out: torch.Tensor, part_out: torch.Tensor, part_lse: torch.Tensor,
+                   out_lse: Optional[torch.Tensor] = None, seq_lens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Fold `(parts, seqs, q_heads, head_dim)` fp32 normalised partials with their
+    `(parts, seqs, q_heads)` natural-log lse into `out` `(seqs, q_heads, head_dim)` (bf16, or
+    fp32 when `out_lse` `(seqs, q_heads)` is given so a second merge can follow). The same
+    kernel folds one GPU's KV splits and the all-gathered partials of several GPUs."""
+    _need_cuda(out, part_out, part_lse)
+    p, n, hq, d = part_out.shape
+    if part_out.dtype != torch.float32 or part_lse.dtype != torch.float32 or tuple(part_lse.shape) != (p, n, hq) \
+            or not part_out.is_contiguous() or not part_lse.is_contiguous():
+        raise ValueError("hk.ops.paged: merge reads contiguous fp32 (parts, seqs, heads, head_dim) and (parts, seqs, heads)")
+    f32 = out.dtype == torch.float32
+    if tuple(out.shape) != (n, hq, d) or out.dtype not in (torch.bfloat16, torch.float32) or out.stride(2) != 1:
+        raise ValueError(f"hk.ops.paged: merge writes (seqs, heads, head_dim) bf16 or fp32, out is {tuple(out.shape)} {out.dtype}")
+    if out_lse is not None and (out_lse.dtype != torch.float32 or tuple(out_lse.shape) != (n, hq)
+                                or not out_lse.is_contiguous()):
+        raise ValueError("hk.ops.paged: out_lse must be contiguous fp32 (seqs, heads)")
+    rc = _lib.load().hkb_merge(out.data_ptr(), out.stride(0), out.stride(1), 1 if f32 else 0,
+                               out_lse.data_ptr() if out_lse is not None else None,
+                               part_out.data_ptr(), n * hq * d, hq * d, part_lse.data_ptr(), n * hq, hq,
+                               p, n, hq, d, seq_lens.data_ptr() if seq_lens is not None else None, None,
+                               _stream(out))
+    _lib.check("hkb_merge", rc)
+    return out
+
+
+# --------------------------------------------------------------------------------------
+# hk's own form: contract, plan, scratch, driver
+# --------------------------------------------------------------------------------------
+
+def check_decode(q, k_cache, v_cache, block_table, seq_lens, out, *, rows: str = "group",
+                 head_dim: Optional[int] = None, scratch=None, splits: int = 1) -> None:
+    """Refuse, before anything is launched, a decode whose tensors do not have the shapes the
+    kernels read; ValueError names the tensor, the shape it has and the one it needs.
+
+    The contract of python/hk/ops/paged.py:746-802: `q` and `out` are
+    (requests, kv_heads, rows, head_dim) bf16 with 1..Q_TILE rows (the GQA group); the caches
+    (blocks, kv_heads, page, head_dim) with page a multiple of 16, bf16 or fp8-e4m3;
+    `block_table` (requests', pages) and `seq_lens` (requests',) int32 with requests' >=
+    requests; `scratch` the split partials (`fused_scratch`). Contents are not read: that
+    would be a device sync. Works on CPU tensors too (it only looks at metadata)."""
+
+    def no(name, t, want):
+        raise ValueError(f"hk.ops.paged: {name} is {tuple(t.shape)} {t.dtype}; the decode reads {want}")
+
+    if q.dim() != 4:
+        no("q", q, "(requests, kv_heads, rows, head_dim)")
+    reqs, heads, n_rows, d = q.shape
+    if head_dim is not None and d != head_dim:
+        no("q", q, f"head_dim {head_dim} (this kernel's)")
+    if d not in HEAD_DIMS:
+        no("q", q, f"head_dim in {HEAD_DIMS}")
+    if rows == "tile" and n_rows != Q_TILE:
+        no("q", q, f"(requests, kv_heads, {Q_TILE}, head_dim): a whole {Q_TILE}-row tile")
+    if not 1 <= n_rows <= Q_TILE:
+        no("q", q, f"1 to {Q_TILE} query rows (the GQA group) a kv head")
+    if q.dtype != torch.bfloat16:
+        no("q", q, "bfloat16")
+    if out.shape != q.shape or out.dtype != q.dtype:
+        no("out", out, f"q's shape and dtype, {tuple(q.shape)} {q.dtype}")
+    kinds = (torch.bfloat16,) + _FP8_DTYPES
+    for name, t in (("k_cache", k_cache), ("v_cache", v_cache)):
+        if (t.dim() != 4 or t.shape[1] != heads or t.shape[3] != d or t.shape[2] % 16 or t.shape[2] == 0
+                or t.dtype not in kinds):
+            no(name, t, f"(blocks, {heads}, page, {d}) bfloat16 or float8_e4m3fn: q's kv heads, a page of a "
+               f"multiple of 16 tokens, q's head_dim")
+    if v_cache.shape != k_cache.shape or v_cache.dtype != k_cache.dtype:
+        no("v_cache", v_cache, f"k_cache's shape and dtype, {tuple(k_cache.shape)} {k_cache.dtype}")
+    if block_table.dim() != 2 or block_table.shape[0] < reqs or block_table.dtype != torch.int32:
+        no("block_table", block_table, f"(requests >= {reqs}, pages) int32")
+    if seq_lens.dim() != 1 or seq_lens.shape[0] < reqs or seq_lens.dtype != torch.int32:
+        no("seq_lens", seq_lens, f"(requests >= {reqs},) int32")
+    if splits > 1:
+        if scratch is None:
+            raise ValueError(f"hk.ops.paged: {splits} splits need scratch (fused_scratch)")
+        o_part, lse = scratch
+        if (o_part.dim() != 4 or o_part.shape[0] < reqs * splits or o_part.dtype != torch.float32
+                or tuple(o_part.shape[1:]) != (heads, n_rows, d)):
+            no("scratch o_part", o_part, f"(>= {reqs * splits}, {heads}, {n_rows}, {d}) float32: a row a "
+               f"(request, split), q's group rows (fused_scratch)")
+        if (lse.dim() != 3 or lse.shape[0] < reqs * splits or lse.dtype != torch.float32
+                or tuple(lse.shape[1:]) != (heads, n_rows)):
+            no("scratch lse_part", lse, f"(>= {reqs * splits}, {heads}, {n_rows}) float32 (fused_scratch)")
+
+
+def fused_scratch(rows: int, n_kv_heads: int, head_dim: int, device, group: int = 4):
+    """(o_part, lse_part) for `rows` = requests x splits: each split's normalised fp32 partial
+    for the `group` query rows, and its natural-log lse (python/hk/ops/paged.py:733-743 keeps
+    (m, l) pairs; one lse carries the same information)."""
+    return (torch.empty(rows, n_kv_heads, group, head_dim, device=device, dtype=torch.float32),
+            torch.empty(rows, n_kv_heads, group, device=device, dtype=torch.float32))
+
+
+_SM_COUNT: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """SMs of `device` (148 on a B200), or 148 where no GPU is present."""
+    if not torch.cuda.is_available():
+        return 148
+    idx = torch.device(device).index if device is not None else None
+    if idx is None:
+        idx = torch.cuda.current_device()
+    n = _SM_COUNT.get(idx)
+    if n is None:
+        n = _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return n
+
+
+def plan_splits(n_reqs: int, n_kv_heads: int, n_pages: int, device=None) -> int:
+    """How many ways to cut the KV axis, given how empty the machine is.
+
+    `n_pages` counts 16-token tiles of the longest sequence the plan must serve -- a host
+    value (the table's width or max_model_len), never a step's lengths, so a captured graph's
+    plan holds for every replay. `HK_SPLITS` = auto | off | 0 | 1 | N overrides as in
+    python/hk/ops/paged.py:891-914; the result is a power of two as
+    python/hk/integration/vllm_backend.py:137-151 rounds it."""
+    forced = os.environ.get("HK_SPLITS", "auto").strip().lower() or "auto"
+    if forced in ("off", "0", "1"):
+        return 1
+    if forced in ("auto", "plan"):
+        return plan_splits_for(n_reqs, n_kv_heads, n_pages, sm_count(device))
+    want = max(1, min(int(forced), max(1, n_pages), MAX_SPLITS))
+    return 1 << int(math.floor(math.log2(want)))
+
+
+def plan_splits_for(n_reqs: int, n_kv_heads: int, n_pages: int, sms: int) -> int:
+    """The planner's rule in Python, equal to hkb_plan_splits (tests hold them together):
+    ceil(target / (requests x kv heads)) with target = 8 CTAs an SM, at least 8 tiles a
+    split, at most MAX_SPLITS, rounded down to a power of two."""
+    sms = sms if sms > 0 else 148
+    have = max(1, n_reqs) * max(1, n_kv_heads)
+    want = -(-(sms * 8) // have)
+    cap = min(MAX_SPLITS, -(-n_pages // 8) if n_pages > 0 else 1)
+    want = max(1, min(want, cap))
+    return 1 << (want.bit_length() - 1)
+
+
+#: Shapes check_decode has passed (python/hk/ops/paged.py:805-825).
+_PASSED: set = set()
+_PASSED_CAP = 4096
+
+
+def decode(q, k_cache, v_cache, block_table, seq_lens, out, scratch, splits: int, *,
+           scale: Optional[float] = None, k_scale=None, v_scale=None) -> None:
+    """The split decode's launches on hk's tensor forms: q/out (requests, kv_heads, group,
+    head_dim), caches (blocks, kv_heads, page, head_dim). Checked against the contract once a
+    shape (`check_decode`), then the walk and, with more than one split, the merge."""
+    key = (q.shape, q.dtype, k_cache.shape, k_cache.dtype, v_cache.shape, block_table.shape, block_table.dtype,
+           seq_lens.shape, seq_lens.dtype, out.shape, out.dtype, splits,
+           scratch[0].shape if splits > 1 and scratch is not None else None,
+           scratch[1].shape if splits > 1 and scratch is not None else None)
+    if key not in _PASSED:
+        check_decode(q, k_cache, v_cache, block_table, seq_lens, out, scratch=scratch, splits=splits)
+        if q.stride(3) != 1 or q.stride(1) != q.shape[2] * q.stride(2) or \
+                out.stride(3) != 1 or out.stride(1) != out.shape[2] * out.stride(2):
+            raise ValueError("hk.ops.paged: q/out heads must be evenly strided (kv head stride = group x row stride)")
+        if len(_PASSED) < _PASSED_CAP:
+            _PASSED.add(key)
+    reqs, hkv, g, d = q.shape
+    hq = hkv * g
+    fp8 = k_cache.dtype != torch.bfloat16
+    q3 = q.as_strided((reqs, hq, d), (q.stride(0), q.stride(2), 1))
+    o3 = out.as_strided((reqs, hq, d), (out.stride(0), out.stride(2), 1))
+    sc = None
+    if splits > 1:
+        sc = (scratch[0].view(-1, hq, d), scratch[1].view(-1, hq))
+    paged_attention_decode(o3, q3, k_cache.transpose(1, 2), v_cache.transpose(1, 2), block_table[:reqs] if
+                           block_table.shape[0] != reqs else block_table, seq_lens[:reqs] if
+                           seq_lens.shape[0] != reqs else seq_lens, d ** -0.5 if scale is None else scale,
+                           "fp8" if fp8 else "auto", k_scale, v_scale, num_splits=splits, scratch=sc)
+
+
+def merge_splits(o_part: torch.Tensor, lse_part: torch.Tensor, splits: int, out: torch.Tensor) -> torch.Tensor:
+    """Combine `splits` normalised partials `(requests x splits, kv_heads, group, head_dim)`
+    and their lse `(requests x splits, kv_heads, group)` into `out` on the device: the kernel
+    form of python/hk/ops/paged.py:283-317 (which folds unnormalised partials in torch; this
+    build keeps ONE convention end to end -- normalised partial + natural-log lse)."""
+    rs, hkv, g, d = o_part.shape
+    reqs = rs // splits
+    hq = hkv * g
+    po = o_part.view(reqs, splits, hq, d)
+    pl = lse_part.view(reqs, splits, hq)
+    o3 = out.view(reqs, hq, d)
+    rc = _lib.load().hkb_merge(o3.data_ptr(), o3.stride(0), o3.stride(1), 1 if out.dtype == torch.float32 else 0,
+                               None, po.data_ptr(), hq * d, splits * hq * d, pl.data_ptr(), hq, splits * hq,
+                               splits, reqs, hq, d, None, None, _stream(out))
+    _lib.check("hkb_merge", rc)
+    return out

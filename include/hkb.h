@@ -1,0 +1,194 @@
+/*
+ * hkb -- C ABI of the B200 (sm_100a) paged-KV hot path: the KV-cache write
+ * (reshape_and_cache) and paged GQA decode attention over block tables, with
+ * split-KV partials and an LSE merge.
+ *
+ * This is the boundary a host binds to (ctypes, cffi, cgo, JNI ...). It takes
+ * plain pointers and sizes only: no C++ types, no torch types, no exceptions.
+ *
+ * Conventions that hold for every entry point
+ *   - every pointer is a BORROWED DEVICE pointer of the current CUDA device,
+ *     valid until the stream reaches the launch; the library allocates and
+ *     frees nothing (one exception, named where it is declared);
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ *     stream); launches are asynchronous and never synchronise with the host,
+ *     so every call can be captured into a CUDA graph;
+ *   - the return value is an hkb_status: 0 on success, a negative code for a
+ *     refused argument (nothing was launched), HKB_ERR_CUDA for a CUDA launch
+ *     error. Nothing aborts and nothing throws;
+ *   - re-entrant: the only state is a per-device read-only attribute cache.
+ *   - strides are in ELEMENTS of the tensor's own type; head_dim is contiguous.
+ *
+ * What each entry point stands in for in hk-dsl (paths are the reference's):
+ * see the comment above each declaration.
+ */
+#ifndef HKB_H_
+#define HKB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HKB_VERSION 100 /* major*100 + minor */
+
+/* KV element types (kv_dtype). Queries and outputs are always bf16. */
+#define HKB_KV_BF16 0
+#define HKB_KV_FP8_E4M3 1
+
+typedef enum {
+  HKB_OK = 0,
+  HKB_ERR_NULL = -1,        /* a required pointer is NULL */
+  HKB_ERR_HEAD_DIM = -2,    /* head_dim not one of 64, 128 */
+  HKB_ERR_BLOCK_SIZE = -3,  /* block_size not a positive multiple of 16 */
+  HKB_ERR_GROUP = -4,       /* q heads not a multiple of kv heads, or group > 16 */
+  HKB_ERR_DTYPE = -5,       /* kv_dtype not HKB_KV_* */
+  HKB_ERR_STRIDE = -6,      /* a stride breaks 16-byte alignment of a row */
+  HKB_ERR_ALIGN = -7,       /* a base pointer is not 16-byte aligned */
+  HKB_ERR_SPLITS = -8,      /* num_splits < 1, > HKB_MAX_SPLITS, or scratch missing */
+  HKB_ERR_SIZE = -9,        /* a count is negative or a grid limit is exceeded */
+  HKB_ERR_SCALE = -10,      /* fp8 cache without k_scale / v_scale */
+  HKB_ERR_UNSUPPORTED = -11,/* a combination this build has no kernel for */
+  HKB_ERR_CUDA = -100       /* CUDA reported an error at launch (see hkb_last_cuda_error) */
+} hkb_status;
+
+#define HKB_MAX_SPLITS 256
+#define HKB_MAX_GROUP 16
+
+/*
+ * One paged cache tensor (K or V) by base pointer and strides, so the same
+ * kernels read hk's head-major pages (blocks, kv_heads, block, head_dim), vLLM's
+ * (blocks, block, kv_heads, head_dim) views, and K|V side by side in one tensor
+ * (python/hk/integration/vllm_backend.py:603-611, vllm_prefill.py:599-628).
+ */
+typedef struct {
+  void* ptr;
+  int64_t stride_block; /* elements between consecutive blocks */
+  int64_t stride_token; /* elements between consecutive tokens of a block */
+  int64_t stride_head;  /* elements between consecutive kv heads */
+  int64_t num_blocks;   /* blocks in the pool; page ids are clamped to it */
+} hkb_cache_t;
+
+/*
+ * The KV-cache write. For every token t with slot = slot_mapping[t] >= 0 (and
+ * below num_blocks*block_size): cache[slot / block_size, slot % block_size, h, :]
+ * = key[t, h, :] (value likewise); a negative slot -- a CUDA graph's padding
+ * token -- is skipped. bf16 caches take the bits unchanged; fp8-e4m3 caches take
+ * RNE(float(x) / scale) saturated to +-448. Duplicate live slots in one call race.
+ *
+ * Replaces: vllm._custom_ops.reshape_and_cache_flash as called from
+ * python/hk/integration/vllm_backend.py:582-599 (argument order pinned by
+ * tests/hk/engines/test_vllm_contract.py:271-277); same semantics as the torch
+ * scatter of tests/hk/gpu/test_vllm_backend_decode.py:44-49 and the DSL scatter
+ * of examples/09_kv_scatter.py:20-25.
+ *
+ * key/value: [num_tokens, num_kv_heads, head_dim] bf16 with the given token and
+ * head strides. slot_mapping: int64 (slot_is_i64 != 0) or int32. k_scale/v_scale:
+ * device pointers to one float each (required for fp8, ignored for bf16).
+ */
+int hkb_reshape_and_cache(const void* key, const void* value,
+                          int64_t key_stride_tok, int64_t key_stride_head,
+                          int64_t val_stride_tok, int64_t val_stride_head,
+                          hkb_cache_t k_cache, hkb_cache_t v_cache,
+                          const void* slot_mapping, int slot_is_i64,
+                          int num_tokens, int num_kv_heads, int head_dim, int block_size,
+                          int kv_dtype, const float* k_scale, const float* v_scale,
+                          void* stream);
+
+/*
+ * The decode walk: one CTA per (sequence, kv head, kv split). Sequence i reads
+ * tokens [0, seq_lens[i]) through block_table[i, :], query head h reads kv head
+ * h / (num_q_heads / num_kv_heads).
+ *
+ *   num_splits == 1: writes out[i, h, :] = softmax(q k^T * scale) v as bf16.
+ *   num_splits  > 1: split s of sequence i covers a contiguous range of 16-token
+ *     tiles and writes its NORMALISED partial to part_out[(i*num_splits+s), h, :]
+ *     (fp32) and part_lse[(i*num_splits+s), h] = natural-log sum-exp of its scaled
+ *     scores (-inf for a split with no tokens); hkb_merge folds them.
+ *
+ * seq_lens[i] <= 0 (a padded request) reads no KV and answers zeros. If q_start
+ * is not NULL it is cu_seqlens_q (num_seqs+1 int32): sequence i's query row is
+ * q_start[i], and a sequence with q_start[i+1] <= q_start[i] writes nothing.
+ * fp8 caches are dequantised in the load: k_scale multiplies the scores and
+ * v_scale the output.
+ *
+ * Replaces: paged_decode_fused_kernel / paged_decode_split_kernel
+ * (python/hk/ops/paged.py:498-667, 171-280), paged_decode.walk_kernel
+ * (python/hk/ops/paged_decode.py:61-440) and paged_cdna.decode_kernel
+ * (python/hk/ops/paged_cdna.py:113-393), as launched from
+ * python/hk/integration/vllm_backend.py:222-232 and vllm_prefill.py:1042-1065.
+ *
+ * q/out: [rows, num_q_heads, head_dim] bf16. block_table: int32, table_stride
+ * elements per row, max_pages valid columns. scale: softmax scale.
+ */
+int hkb_paged_decode(void* out, int64_t out_stride_tok, int64_t out_stride_head,
+                     const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                     hkb_cache_t k_cache, hkb_cache_t v_cache,
+                     const int32_t* block_table, int64_t table_stride, int max_pages,
+                     const int32_t* seq_lens, const int32_t* q_start,
+                     int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                     int block_size, float scale, int kv_dtype,
+                     const float* k_scale, const float* v_scale,
+                     int num_splits, float* part_out, float* part_lse,
+                     void* stream);
+
+/*
+ * The LSE merge: out[i, h, :] = sum_p w_p * part_out[p, i, h, :] / sum_p w_p with
+ * w_p = exp(part_lse[p, i, h] - max_p part_lse). A part whose lse is -inf is
+ * never read (its memory may hold anything); if every part is -inf the answer is
+ * zero. Also folds the partials of several GPUs after an all-gather: a part is
+ * then one rank's (out, lse). If out_lse is not NULL the merged natural-log lse
+ * is written to out_lse[i, h] and out is written as fp32 (out_is_f32 != 0) so a
+ * rank's local merge can feed a second, cross-GPU merge.
+ *
+ * part_out element (p, i, h, d) is at p*part_stride_p + i*part_stride_seq +
+ * h*head_dim + d; part_lse (p, i, h) at p*lse_stride_p + i*lse_stride_seq + h.
+ * seq_lens may be NULL; otherwise sequences with seq_lens[i] <= 0 answer zeros.
+ * q_start as in hkb_paged_decode.
+ *
+ * Replaces: paged_merge_kernel / _merge_splits (python/hk/ops/paged.py:394-495),
+ * the torch merge_splits (paged.py:283-317), paged_decode.merge_kernel_def
+ * (python/hk/ops/paged_decode.py:443-537), paged_cdna.merge_kernel
+ * (python/hk/ops/paged_cdna.py:439-560).
+ */
+int hkb_merge(void* out, int64_t out_stride_tok, int64_t out_stride_head, int out_is_f32,
+              float* out_lse,
+              const float* part_out, int64_t part_stride_p, int64_t part_stride_seq,
+              const float* part_lse, int64_t lse_stride_p, int64_t lse_stride_seq,
+              int num_parts, int num_seqs, int num_q_heads, int head_dim,
+              const int32_t* seq_lens, const int32_t* q_start, void* stream);
+
+/*
+ * Split planner: how many ways to cut the KV axis so that num_seqs*num_kv_heads
+ * CTAs fill sm_count SMs; a power of two, at most max_tiles (16-token tiles of
+ * the longest sequence the engine allows) and HKB_MAX_SPLITS. A function of host
+ * values only, so a captured graph's plan is right for every replay.
+ * Replaces: plan_splits (python/hk/ops/paged.py:877-914) and decode_splits
+ * (python/hk/integration/vllm_backend.py:137-151).
+ */
+int hkb_plan_splits(int num_seqs, int num_kv_heads, int max_tiles, int sm_count);
+
+/* Bytes of (part_out, part_lse) scratch for a split decode, part_out first;
+ * part_lse starts at hkb_scratch_lse_offset. Replaces fused_scratch
+ * (python/hk/ops/paged.py:733-743). */
+size_t hkb_scratch_bytes(int num_seqs, int num_q_heads, int head_dim, int num_splits);
+size_t hkb_scratch_lse_offset(int num_seqs, int num_q_heads, int head_dim, int num_splits);
+
+/* SM count of CUDA device `device` (-1 = current), cached; <= 0 on error. */
+int hkb_sm_count(int device);
+
+/* A sentence for a status code; never NULL. */
+const char* hkb_strerror(int code);
+
+/* The last CUDA error code seen by this thread inside the library (cudaError_t). */
+int hkb_last_cuda_error(void);
+
+/* HKB_VERSION of the built library. */
+int hkb_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HKB_H_ */
