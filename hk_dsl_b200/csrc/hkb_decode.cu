@@ -73,9 +73,10 @@ __global__ void merge_kernel(const MergeArgs a) {
 // ---------------------------------------------------------------------------------
 // Launch helpers
 // ---------------------------------------------------------------------------------
-template <typename K>
-static int launch_walk(K kernel, int smem_bytes, int threads, dim3 grid, const DecodeArgs& a, cudaStream_t st) {
-  // Opt in to more than 48 KB of dynamic shared memory once per device for this kernel.
+template <void (*kernel)(const DecodeArgs)>
+static int launch_walk(int smem_bytes, int threads, dim3 grid, const DecodeArgs& a, cudaStream_t st) {
+  // Opt in to more than 48 KB of dynamic shared memory once per device for this kernel
+  // (one flag array per kernel: the kernel is a template argument).
   static bool armed[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -107,8 +108,8 @@ static int dispatch_cc(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
   dim3 grid(a.num_splits, a.num_kv_heads * chunks, num_seqs);
 #define HKB_CC(GH_)                                                                               \
   case GH_:                                                                                       \
-    return launch_walk(walk_cc_kernel<D, FP8, GH_, WARPS, NST>, WalkCC<D, FP8, GH_, WARPS, NST>::SMEM_BYTES, \
-                       WARPS * 32, grid, a, st);
+    return launch_walk<walk_cc_kernel<D, FP8, GH_, WARPS, NST>>(WalkCC<D, FP8, GH_, WARPS, NST>::SMEM_BYTES, \
+                                                                 WARPS * 32, grid, a, st);
   switch (gh) {
     HKB_CC(1) HKB_CC(2) HKB_CC(3) HKB_CC(4)
   }
@@ -123,10 +124,10 @@ static int dispatch_mma(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
   constexpr int NST = FP8 ? 4 : 3;
   dim3 grid(a.num_splits, a.num_kv_heads, num_seqs);
   if (a.group <= 8)
-    return launch_walk(walk_mma_kernel<D, FP8, 1, WARPS, NST>, WalkMMA<D, FP8, 1, WARPS, NST>::SMEM_BYTES,
-                       WARPS * 32, grid, a, st);
-  return launch_walk(walk_mma_kernel<D, FP8, 2, WARPS, NST>, WalkMMA<D, FP8, 2, WARPS, NST>::SMEM_BYTES,
-                     WARPS * 32, grid, a, st);
+    return launch_walk<walk_mma_kernel<D, FP8, 1, WARPS, NST>>(WalkMMA<D, FP8, 1, WARPS, NST>::SMEM_BYTES,
+                                                               WARPS * 32, grid, a, st);
+  return launch_walk<walk_mma_kernel<D, FP8, 2, WARPS, NST>>(WalkMMA<D, FP8, 2, WARPS, NST>::SMEM_BYTES,
+                                                             WARPS * 32, grid, a, st);
 }
 
 }  // namespace hkb

@@ -40,42 +40,43 @@ struct WalkCC {
   // head_dim index of element e of piece p for lane-in-group j
   __device__ static __forceinline__ int dim_of(int j, int p, int e) { return (j + 8 * p) * EPP + e; }
 
-  __device__ static __forceinline__ void unpack_piece(const uint4& x, float* f) {
+  // One 16-byte piece -> EPP floats as EPP/2 packed pairs (element 2i in the low half).
+  __device__ static __forceinline__ void unpack_piece(const uint4& x, uint64_t* f2) {
     const uint32_t w[4] = {x.x, x.y, x.z, x.w};
     if (!FP8) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { f[2 * i] = bf16lo(w[i]); f[2 * i + 1] = bf16hi(w[i]); }
+      for (int i = 0; i < 4; ++i) f2[i] = pack2(bf16lo(w[i]), bf16hi(w[i]));
     } else {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float2 a = e4m3x2_to_float2((uint16_t)(w[i] & 0xffffu));
         const float2 b = e4m3x2_to_float2((uint16_t)(w[i] >> 16));
-        f[4 * i] = a.x; f[4 * i + 1] = a.y; f[4 * i + 2] = b.x; f[4 * i + 3] = b.y;
+        f2[2 * i] = pack2(a.x, a.y);
+        f2[2 * i + 1] = pack2(b.x, b.y);
       }
     }
   }
 
   template <bool LAST>
   __device__ static __forceinline__ void tile(uint32_t stage, int tok0, int seq_len, int g, int j,
-                                              const float (&qf)[GH][DPL], float (&m)[GH], float (&l)[GH],
-                                              float (&o)[GH][DPL]) {
+                                              const uint64_t (&q2)[GH][DPL / 2], float (&m)[GH], float (&l)[GH],
+                                              uint64_t (&o2)[GH][DPL / 2]) {
     float s[4][GH];
-    // scores of this lane's 4 tokens over its DPL dims
+    // scores of this lane's 4 tokens over its DPL dims: packed FMAs over (even, odd) dims
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int r = i * 4 + g;
-      float kf[DPL];
+      uint64_t k2[DPL / 2];
 #pragma unroll
-      for (int p = 0; p < NP; ++p) unpack_piece(lds128(stage + tile_off<ROWB>(r, j + 8 * p)), kf + p * EPP);
+      for (int p = 0; p < NP; ++p) unpack_piece(lds128(stage + tile_off<ROWB>(r, j + 8 * p)), k2 + p * (EPP / 2));
 #pragma unroll
       for (int h = 0; h < GH; ++h) {
-        float acc0 = 0.f, acc1 = 0.f;
+        uint64_t acc = 0ull;  // (+0.f, +0.f)
 #pragma unroll
-        for (int e = 0; e < DPL; e += 2) {
-          acc0 = fmaf(kf[e], qf[h][e], acc0);
-          acc1 = fmaf(kf[e + 1], qf[h][e + 1], acc1);
-        }
-        s[i][h] = acc0 + acc1;
+        for (int e = 0; e < DPL / 2; ++e) acc = fma2(k2[e], q2[h][e], acc);
+        float a0, a1;
+        unpack2(acc, a0, a1);
+        s[i][h] = a0 + a1;
       }
     }
     // complete the dot products over the 8 lanes of the group
@@ -103,8 +104,9 @@ struct WalkCC {
       if (m_new != m[h]) {
         const float alpha = fast_exp2(m[h] - m_use);
         l[h] *= alpha;
+        const uint64_t a2 = pack2(alpha, alpha);
 #pragma unroll
-        for (int e = 0; e < DPL; ++e) o[h][e] *= alpha;
+        for (int e = 0; e < DPL / 2; ++e) o2[h][e] = mul2(o2[h][e], a2);
         m[h] = m_new;
       }
       float sum = 0.f;
@@ -117,14 +119,16 @@ struct WalkCC {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int r = i * 4 + g;
-      float vf[DPL];
+      uint64_t v2[DPL / 2];
 #pragma unroll
-      for (int p = 0; p < NP; ++p) unpack_piece(lds128(vst + tile_off<ROWB>(r, j + 8 * p)), vf + p * EPP);
+      for (int p = 0; p < NP; ++p) unpack_piece(lds128(vst + tile_off<ROWB>(r, j + 8 * p)), v2 + p * (EPP / 2));
       if (LAST && !live[i]) continue;  // rows past the end may hold anything, NaN included
 #pragma unroll
-      for (int h = 0; h < GH; ++h)
+      for (int h = 0; h < GH; ++h) {
+        const uint64_t p2 = pack2(s[i][h], s[i][h]);
 #pragma unroll
-        for (int e = 0; e < DPL; ++e) o[h][e] = fmaf(s[i][h], vf[e], o[h][e]);
+        for (int e = 0; e < DPL / 2; ++e) o2[h][e] = fma2(p2, v2[e], o2[h][e]);
+      }
     }
   }
 
@@ -172,7 +176,8 @@ struct WalkCC {
     float vs = 1.f;
     if (FP8) { qs *= __ldg(a.k_scale); vs = __ldg(a.v_scale); }
 
-    float qf[GH][DPL], o[GH][DPL], m[GH], l[GH];
+    uint64_t q2[GH][DPL / 2], o2[GH][DPL / 2];
+    float m[GH], l[GH];
 #pragma unroll
     for (int h = 0; h < GH; ++h) {
       m[h] = -INFINITY; l[h] = 0.f;
@@ -185,13 +190,10 @@ struct WalkCC {
           if (h < nh) x = __ldg(reinterpret_cast<const uint4*>(qp + dim_of(j, p, e)));
           const uint32_t w[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            qf[h][p * EPP + e + 2 * i] = bf16lo(w[i]) * qs;
-            qf[h][p * EPP + e + 2 * i + 1] = bf16hi(w[i]) * qs;
-          }
+          for (int i = 0; i < 4; ++i) q2[h][(p * EPP + e) / 2 + i] = pack2(bf16lo(w[i]) * qs, bf16hi(w[i]) * qs);
         }
 #pragma unroll
-      for (int e = 0; e < DPL; ++e) o[h][e] = 0.f;
+      for (int e = 0; e < DPL / 2; ++e) o2[h][e] = 0ull;
     }
 
     Loader ld;
@@ -219,8 +221,8 @@ struct WalkCC {
       cp_async_commit();
       const uint32_t stage = ring + (k % NST) * STAGE_BYTES;
       const int t = t_lo + k;
-      if (t == n_tiles - 1) tile<true>(stage, t * TILE_TOKENS, seq_len, g, j, qf, m, l, o);
-      else tile<false>(stage, t * TILE_TOKENS, seq_len, g, j, qf, m, l, o);
+      if (t == n_tiles - 1) tile<true>(stage, t * TILE_TOKENS, seq_len, g, j, q2, m, l, o2);
+      else tile<false>(stage, t * TILE_TOKENS, seq_len, g, j, q2, m, l, o2);
     }
     cp_async_wait<0>();
     __syncthreads();  // every warp is done with its ring: the fold reuses the memory
@@ -234,7 +236,11 @@ struct WalkCC {
 #pragma unroll
       for (int p = 0; p < NP; ++p)
 #pragma unroll
-        for (int e = 0; e < EPP; ++e) fo[(stream * GH + h) * D + dim_of(j, p, e)] = o[h][p * EPP + e];
+        for (int e = 0; e < EPP; e += 2) {
+          float x0, x1;
+          unpack2(o2[h][(p * EPP + e) / 2], x0, x1);
+          *reinterpret_cast<float2*>(&fo[(stream * GH + h) * D + dim_of(j, p, e)]) = make_float2(x0, x1);
+        }
       if (j == 0) { fml[(stream * GH + h) * 2] = m[h]; fml[(stream * GH + h) * 2 + 1] = l[h]; }
     }
     __syncthreads();

@@ -144,7 +144,7 @@ def paged_attention_decode(out: torch.Tensor, query: torch.Tensor, key_cache: to
                            num_splits: Optional[int] = None,
                            scratch: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
                            query_start_loc: Optional[torch.Tensor] = None,
-                           max_seq_len: Optional[int] = None) -> torch.Tensor:
+                           max_seq_len: Optional[int] = None, merge: bool = True) -> torch.Tensor:
     """Decode attention of one query token a sequence over a block-paged KV cache.
 
     `query`/`out`: `(tokens, q_heads, head_dim)` bf16 (head_dim contiguous); caches
@@ -152,7 +152,8 @@ def paged_attention_decode(out: torch.Tensor, query: torch.Tensor, key_cache: to
     `k_scale`/`v_scale`; `block_tables` `(seqs, max_pages)` int32; `seq_lens` `(seqs,)` int32.
     `num_splits` None plans it from the batch and the table's width (host values only);
     with more than one split the walk writes partials into `scratch` (allocated here if
-    not given -- pass it to stay allocation-free) and the merge kernel folds them."""
+    not given -- pass it to stay allocation-free) and the merge kernel folds them
+    (`merge=False` stops after the walk and leaves the partials in `scratch`)."""
     _need_cuda(out, query, key_cache, value_cache, block_tables, seq_lens)
     if query.dim() != 3 or query.dtype != torch.bfloat16 or query.stride(2) != 1:
         raise ValueError(f"hk.ops.paged: query is {tuple(query.shape)} {query.dtype}; the decode reads "
@@ -207,7 +208,7 @@ def paged_attention_decode(out: torch.Tensor, query: torch.Tensor, key_cache: to
         _scale_ptr(k_scale, fp8, "k_scale"), _scale_ptr(v_scale, fp8, "v_scale"), num_splits,
         po.data_ptr() if po is not None else None, pl.data_ptr() if pl is not None else None, st)
     _lib.check("hkb_paged_decode", rc)
-    if num_splits > 1:
+    if num_splits > 1 and merge:
         rc = lib.hkb_merge(out.data_ptr(), out.stride(0), out.stride(1), 0, None,
                            po.data_ptr(), hq * d, num_splits * hq * d, pl.data_ptr(), hq, num_splits * hq,
                            num_splits, n, hq, d, seq_lens.data_ptr(), qsl, st)

@@ -1,0 +1,129 @@
+"""The paged decode across the GPUs of one box: who owns what, and the one exchange step.
+
+hk-dsl itself has no multi-GPU plan for this path -- tensor parallelism is the engine's, and
+a rank sees only its own heads (docs/performance/scorecard.md:14-20 of the reference) -- and
+its only long-context device is the KV split inside one GPU (python/hk/ops/paged.py:171-194).
+This module carries that split one level up:
+
+* kv heads divide the world size  -> each rank owns a kv-head group and its query heads:
+  independent work, no collective (`shard_heads`);
+* otherwise                        -> whole sequences are dealt to ranks, longest first into the
+  least-loaded rank, so every rank reads about the same KV bytes; no collective (`pack_sequences`);
+* one long sequence                -> the KV axis is cut into contiguous token ranges, one a rank;
+  every rank walks its range into a partial `(out fp32, lse)`, the partials are all-gathered
+  with NCCL (they land in this rank's OWN memory: no peer loads, no multicast) and the same
+  LSE-merge kernel that folds one GPU's splits folds the ranks' (`SplitKVDecoder`).
+
+One process per GPU; `torch.distributed` (NCCL) is the plumbing.
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from ..runtime import lib as _lib
+from . import paged
+
+
+def shard_heads(num_kv_heads: int, world: int, rank: int) -> Tuple[int, int]:
+    """[lo, hi) of the kv heads rank `rank` owns; kv heads must divide evenly."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} of world {world}")
+    if num_kv_heads % world:
+        raise ValueError(f"{num_kv_heads} kv heads do not divide over {world} ranks: shard by sequence")
+    per = num_kv_heads // world
+    return rank * per, (rank + 1) * per
+
+
+def pack_sequences(lens: Sequence[int], world: int) -> List[List[int]]:
+    """Deal sequences to `world` ranks, longest first into the least-loaded rank (by tokens =
+    KV bytes). Returns each rank's sequence indices, ascending. Deterministic."""
+    bins: List[List[int]] = [[] for _ in range(world)]
+    load = [0] * world
+    for i in sorted(range(len(lens)), key=lambda i: (-lens[i], i)):
+        r = min(range(world), key=lambda r: (load[r], r))
+        bins[r].append(i)
+        load[r] += lens[i]
+    return [sorted(b) for b in bins]
+
+
+def kv_range(seq_len: int, world: int, rank: int, block_size: int = paged.KV_BLOCK) -> Tuple[int, int]:
+    """[lo, hi) of a sequence's tokens rank `rank` holds under a KV split: contiguous, whole
+    pages a rank, the ranges of all ranks tiling [0, seq_len)."""
+    per = -(-seq_len // world)
+    per = -(-per // block_size) * block_size
+    return min(seq_len, rank * per), min(seq_len, (rank + 1) * per)
+
+
+def record_floats(num_seqs: int, num_q_heads: int, head_dim: int) -> int:
+    """Floats of one rank's partial record -- out `(seqs, heads, d)` then lse `(seqs, heads)` --
+    padded to 4 so every rank's record starts 16-byte aligned in the gathered buffer."""
+    n = num_seqs * num_q_heads * (head_dim + 1)
+    return (n + 3) // 4 * 4
+
+
+class SplitKVDecoder:
+    """Decode of sequences whose KV is cut along the token axis across the ranks of `group`.
+
+    Every rank calls `decode` with its own cache shard, block table and LOCAL lengths (the
+    tokens of each sequence it holds; 0 is fine) and the same queries. Buffers are allocated
+    once here, so a step allocates nothing: walk (+ local merge) -> `all_gather_into_tensor`
+    on the current stream -> cross-rank merge. Every rank ends with the full answer."""
+
+    def __init__(self, num_seqs: int, num_q_heads: int, num_kv_heads: int, head_dim: int, device,
+                 local_splits: int, group=None):
+        import torch.distributed as dist
+
+        self.dist = dist
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.n, self.hq, self.hkv, self.d = num_seqs, num_q_heads, num_kv_heads, head_dim
+        self.local_splits = max(2, int(local_splits))       # the walk must write (out, lse) partials
+        self.rec = record_floats(num_seqs, num_q_heads, head_dim)
+        self.scratch = paged.split_scratch(num_seqs, num_q_heads, head_dim, self.local_splits, device)
+        self.mine = torch.zeros(self.rec, device=device, dtype=torch.float32)
+        self.all = torch.zeros(self.world * self.rec, device=device, dtype=torch.float32)
+        n_out = num_seqs * num_q_heads * head_dim
+        self.my_out = self.mine[:n_out].view(num_seqs, num_q_heads, head_dim)
+        self.my_lse = self.mine[n_out:n_out + num_seqs * num_q_heads].view(num_seqs, num_q_heads)
+        self.unused_out = torch.zeros(num_seqs, num_q_heads, head_dim, device=device, dtype=torch.bfloat16)
+
+    def local_partial(self, query, key_cache, value_cache, block_tables, local_lens, scale,
+                      kv_cache_dtype="auto", k_scale=None, v_scale=None) -> None:
+        """This rank's normalised partial and its lse into `self.mine` (walk + local merge)."""
+        s = self.local_splits
+        # with more than one split and merge=False the walk writes partials only; `out` is untouched
+        paged.paged_attention_decode(self.unused_out, query, key_cache, value_cache, block_tables, local_lens,
+                                     scale, kv_cache_dtype, k_scale, v_scale, num_splits=s, scratch=self.scratch,
+                                     merge=False)
+        po, pl = self.scratch
+        n, hq, d = self.n, self.hq, self.d
+        rc = _lib.load().hkb_merge(self.my_out.data_ptr(), hq * d, d, 1, self.my_lse.data_ptr(),
+                                   po.data_ptr(), hq * d, s * hq * d, pl.data_ptr(), hq, s * hq,
+                                   s, n, hq, d, None, None, paged._stream(query))
+        _lib.check("hkb_merge", rc)
+
+    def gather(self) -> None:
+        if self.world == 1:
+            self.all.copy_(self.mine)
+        else:
+            self.dist.all_gather_into_tensor(self.all, self.mine, group=self.group)
+
+    def merge(self, out: torch.Tensor) -> torch.Tensor:
+        """Fold the gathered records of all ranks into `out` `(seqs, heads, d)` bf16."""
+        n, hq, d = self.n, self.hq, self.d
+        base = self.all.data_ptr()
+        rc = _lib.load().hkb_merge(out.data_ptr(), out.stride(0), out.stride(1), 0, None,
+                                   base, self.rec, hq * d, base + 4 * n * hq * d, self.rec, hq,
+                                   self.world, n, hq, d, None, None, paged._stream(out))
+        _lib.check("hkb_merge", rc)
+        return out
+
+    def decode(self, out, query, key_cache, value_cache, block_tables, local_lens, scale,
+               kv_cache_dtype="auto", k_scale=None, v_scale=None) -> torch.Tensor:
+        self.local_partial(query, key_cache, value_cache, block_tables, local_lens, scale,
+                           kv_cache_dtype, k_scale, v_scale)
+        self.gather()
+        return self.merge(out)

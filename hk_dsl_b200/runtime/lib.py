@@ -66,7 +66,7 @@ def load(path: Optional[os.PathLike] = None) -> ctypes.CDLL:
     global _LIB
     if _LIB is not None and path is None:
         return _LIB
-    p = Path(path) if path is not None else LIB_PATH
+    p = Path(path) if path is not None else Path(os.environ.get("HKB_LIB") or LIB_PATH)
     if not p.exists():
         raise ImportError(
             f"{p} is not built. Build it with `python -m hk_dsl_b200.csrc.build` (nvcc, sm_100a); "

@@ -31,6 +31,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from .ops import paged
+from .ops.paged_dist import kv_range, pack_sequences, shard_heads
 
 
 @dataclass(frozen=True)
@@ -102,30 +103,15 @@ class Shard:
     tokens: Tuple[int, int] = (0, 0)         # kvsplit: [lo, hi) of every sequence's tokens
 
 
-def pack_sequences(lens: List[int], world: int) -> List[List[int]]:
-    """Longest first into the least-loaded rank: near-equal KV bytes a rank."""
-    bins: List[List[int]] = [[] for _ in range(world)]
-    load = [0] * world
-    for i in sorted(range(len(lens)), key=lambda i: (-lens[i], i)):
-        r = min(range(world), key=lambda r: (load[r], r))
-        bins[r].append(i)
-        load[r] += lens[i]
-    return [sorted(b) for b in bins]
-
-
 def shard_of(spec: Spec, lens: List[int], world: int, rank: int) -> Shard:
     every = list(range(len(lens)))
     if world == 1:
         return Shard("single", 0, 1, (0, spec.kv_heads), every, (0, 0))
     if spec.multi_gpu == "kvsplit":
-        n = lens[0]
-        per = -(-n // world)
-        per = -(-per // spec.block_size) * spec.block_size     # whole pages a rank
-        lo, hi = min(n, rank * per), min(n, (rank + 1) * per)
-        return Shard("kvsplit", rank, world, (0, spec.kv_heads), every, (lo, hi))
+        return Shard("kvsplit", rank, world, (0, spec.kv_heads), every,
+                     kv_range(lens[0], world, rank, spec.block_size))
     if spec.multi_gpu == "heads" and spec.kv_heads % world == 0:
-        per = spec.kv_heads // world
-        return Shard("heads", rank, world, (rank * per, (rank + 1) * per), every, (0, 0))
+        return Shard("heads", rank, world, shard_heads(spec.kv_heads, world, rank), every, (0, 0))
     return Shard("seqs", rank, world, (0, spec.kv_heads), pack_sequences(lens, world)[rank], (0, 0))
 
 
