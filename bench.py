@@ -182,6 +182,8 @@ def reference_arm(args):
 
     spec = W.CONFIGS[args.config]
     lens = W.seq_lens_of(spec)
+    if args.batch:
+        lens = lens[:args.batch]
     cores = torch.get_num_threads()
     total_budget_s = 150.0
     probe = _cpu_sample(spec, lens, 4096)
@@ -215,7 +217,7 @@ def reference_arm(args):
 
 
 def config_of(spec, lens, world, how):
-    return {"workload": f"{spec.name}: {spec.what}", "batch": spec.batch, "q_heads": spec.q_heads,
+    return {"workload": f"{spec.name}: {spec.what}", "batch": len(lens), "q_heads": spec.q_heads,
             "kv_heads": spec.kv_heads, "head_dim": spec.head_dim, "block_size": spec.block_size,
             "kv_cache_dtype": "bf16" if not spec.fp8 else "fp8_e4m3", "seq_len_min": min(lens),
             "seq_len_max": max(lens), "total_tokens": sum(lens), "kv_bytes_per_step": spec.kv_bytes(lens),
@@ -234,6 +236,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--splits", type=int, default=0, help="0 = the planner's choice")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="keep only the first N sequences of the config (small cases for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -257,11 +261,13 @@ def main():
 
     spec = W.CONFIGS[args.config]
     all_lens = W.seq_lens_of(spec)
+    if args.batch:
+        all_lens = all_lens[:args.batch]
     kv_total = spec.kv_bytes(all_lens)
     # enough distinct caches that one rotation reads >= 1 GiB on this rank
     local_kv = kv_total / world
     layers = max(1, min(16, -(-(1 << 30) // int(max(local_kv, 1)))))
-    st = W.build_step(spec, dev, world=world, rank=rank, layers=layers)
+    st = W.build_step(spec, dev, world=world, rank=rank, layers=layers, lens=all_lens)
     n = len(st.lens)
     d = spec.head_dim
     max_tiles = st.block_table.shape[1] * (spec.block_size // 16)
@@ -430,7 +436,7 @@ def main():
                                  "kvsplit": "KV axis split across GPUs + all-gather(out, lse) + merge"}[st.shard.kind]),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": launches_per_step * K, "clocks": clocks,
-            "seqs_per_s": spec.batch / (ms_step * 1e-3), "tokens_per_s": spec.batch / (ms_step * 1e-3),
+            "seqs_per_s": len(all_lens) / (ms_step * 1e-3), "tokens_per_s": len(all_lens) / (ms_step * 1e-3),
             "frac_of_aggregate_hbm_measured": value / (peak * world),
             "frac_of_aggregate_hbm_nominal": value / (NOMINAL_HBM_GBS * world),
             "splits": splits, "layers_rotated": layers, "cuda_graph": captured, "parity_sample": parity,

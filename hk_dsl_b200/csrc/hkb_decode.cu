@@ -8,8 +8,7 @@ extern thread_local int hkb_tls_cuda_error;
 namespace hkb {
 
 // ---------------------------------------------------------------------------------
-// LSE merge. grid = (q heads, sequences), D/4 threads: a thread owns 4 output dims and
-// reads every live part's float4. Latency-bound at decode sizes (a few microseconds).
+// LSE merge. grid = (q heads, sequences). Latency-bound at decode sizes (a few microseconds).
 // Weights follow the normalised-partial convention (python/hk/ops/paged.py:394-458):
 // w_p = exp(lse_p - max lse); the numerator takes w_p * out_p, the denominator w_p.
 // ---------------------------------------------------------------------------------
@@ -27,9 +26,20 @@ struct MergeArgs {
   const int* q_start;
 };
 
-__global__ void merge_kernel(const MergeArgs a) {
+// 256 threads = PG part groups x (D/4) dim threads: group g folds parts g, g+PG, ... so that
+// with the usual 2..16 parts every part's loads are in flight at once, then the groups are
+// summed through shared memory.
+constexpr int MERGE_THREADS = 256;
+
+__global__ void __launch_bounds__(MERGE_THREADS) merge_kernel(const MergeArgs a) {
+  __shared__ float s_red[MERGE_THREADS / 32];
+  __shared__ float4 s_acc[MERGE_THREADS];
+  __shared__ float s_den[MERGE_THREADS];
   const int h = blockIdx.x, seq = blockIdx.y;
-  const int d = threadIdx.x * 4;
+  const int dt = a.head_dim / 4;            // dim threads a group
+  const int pg = MERGE_THREADS / dt;        // part groups
+  const int g = threadIdx.x / dt, td = threadIdx.x % dt;
+  const int d = td * 4;
   int row = seq;
   if (a.q_start) {
     row = __ldg(a.q_start + seq);
@@ -37,14 +47,23 @@ __global__ void merge_kernel(const MergeArgs a) {
   }
   const bool empty = a.seq_lens && __ldg(a.seq_lens + seq) <= 0;
   const float* lse = a.part_lse + (int64_t)seq * a.lse_stride_seq + h;
+  // max lse over the parts: a block-wide reduction
   float mx = -INFINITY;
   if (!empty)
-    for (int p = 0; p < a.num_parts; ++p) mx = fmaxf(mx, __ldg(lse + (int64_t)p * a.lse_stride_p));
+    for (int p = threadIdx.x; p < a.num_parts; p += MERGE_THREADS) mx = fmaxf(mx, __ldg(lse + (int64_t)p * a.lse_stride_p));
+#pragma unroll
+  for (int x = 16; x > 0; x >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, x));
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = s_red[0];
+#pragma unroll
+  for (int w = 1; w < MERGE_THREADS / 32; ++w) mx = fmaxf(mx, s_red[w]);
+
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   float den = 0.f;
-  if (mx != -INFINITY) {
+  if (mx != -INFINITY && g < pg) {
     const float* po = a.part_out + (int64_t)seq * a.part_stride_seq + (int64_t)h * a.head_dim + d;
-    for (int p = 0; p < a.num_parts; ++p) {
+    for (int p = g; p < a.num_parts; p += pg) {
       const float lp = __ldg(lse + (int64_t)p * a.lse_stride_p);
       if (lp == -INFINITY) continue;  // an empty part's memory is never read
       const float w = __expf(lp - mx);
@@ -53,6 +72,15 @@ __global__ void merge_kernel(const MergeArgs a) {
       acc.z = fmaf(w, x.z, acc.z); acc.w = fmaf(w, x.w, acc.w);
       den += w;
     }
+  }
+  s_acc[threadIdx.x] = acc;
+  s_den[threadIdx.x] = den;
+  __syncthreads();
+  if (g != 0) return;
+  for (int o = 1; o < pg; ++o) {   // fixed order: the same bits every call
+    const float4 x = s_acc[o * dt + td];
+    acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+    den += s_den[o * dt + td];
   }
   const float inv = den > 0.f ? 1.f / den : 0.f;
   acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
@@ -66,7 +94,7 @@ __global__ void merge_kernel(const MergeArgs a) {
     pk.y = *reinterpret_cast<uint32_t*>(&hi);
     *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.out) + off) = pk;
   }
-  if (a.out_lse && threadIdx.x == 0)
+  if (a.out_lse && td == 0)
     a.out_lse[(int64_t)row * a.num_q_heads + h] = den > 0.f ? mx + __logf(den) : -INFINITY;
 }
 
@@ -202,7 +230,7 @@ extern "C" int hkb_merge(void* out, int64_t out_stride_tok, int64_t out_stride_h
   if (num_seqs < 0 || num_q_heads <= 0 || num_parts < 1) return HKB_ERR_SIZE;
   if (num_seqs == 0) return HKB_OK;
   if (!out || !part_out || !part_lse) return HKB_ERR_NULL;
-  if (head_dim <= 0 || head_dim % 4 || head_dim > 1024) return HKB_ERR_HEAD_DIM;
+  if (head_dim <= 0 || head_dim % 4 || head_dim > 1024 || (MERGE_THREADS * 4) % head_dim) return HKB_ERR_HEAD_DIM;
   if (num_seqs > 65535) return HKB_ERR_SIZE;
   if ((part_stride_p | part_stride_seq) % 4 || (out_stride_tok | out_stride_head) % 4) return HKB_ERR_STRIDE;
   if ((uintptr_t)part_out % 16 || (uintptr_t)out % (out_is_f32 ? 16 : 8)) return HKB_ERR_ALIGN;
@@ -213,7 +241,7 @@ extern "C" int hkb_merge(void* out, int64_t out_stride_tok, int64_t out_stride_h
   a.part_lse = part_lse; a.lse_stride_p = lse_stride_p; a.lse_stride_seq = lse_stride_seq;
   a.num_parts = num_parts; a.num_q_heads = num_q_heads; a.head_dim = head_dim;
   a.seq_lens = seq_lens; a.q_start = q_start;
-  merge_kernel<<<dim3(num_q_heads, num_seqs), head_dim / 4, 0, (cudaStream_t)stream>>>(a);
+  merge_kernel<<<dim3(num_q_heads, num_seqs), MERGE_THREADS, 0, (cudaStream_t)stream>>>(a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
   return HKB_OK;

@@ -1,0 +1,108 @@
+"""The kernels as `torch.ops.hk.*`: opaque custom ops with out-parameters that return `()`.
+
+hk-dsl exposes every compiled kernel as `torch.ops.hk.<name>` whose schema is the kernel's
+tensors in declaration order, written tensors marked `(a!)`, returning nothing
+(python/hk/codegen/scaffold.py:264-275, python/hk/runtime/torch_ext.py:102-174,
+python/hk/runtime/codeobj.py:582-629), and calls them directly in eager code. There every
+(head_dim, splits) pair is its own compiled kernel and so its own op name; here the same
+names are registered on demand onto ONE runtime-parameterised C entry point:
+
+    hk::reshape_and_cache(key, value, key_cache!, value_cache!, slot_mapping, kv_cache_dtype, k_scale, v_scale)
+    hk::paged_attention_decode(out!, query, key_cache, value_cache, block_tables, seq_lens, scale,
+                               kv_cache_dtype, k_scale, v_scale, num_splits, part_out!, part_lse!)
+    hk::paged_decode_fused_d{D}_s{S}(q, k_cache, v_cache, block_table, seq_lens, out!, o_part!, ml_part!)
+    hk::paged_merge_d{D}_s{S}(seq_lens, out!, o_part, ml_part)
+
+The split scratch (`o_part`, `ml_part`) is this build's: fp32 normalised partials and their
+natural-log lse (`hk_dsl_b200.ops.paged.fused_scratch`), caller-owned and allocated once.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Dict
+
+import torch
+
+from ..integration import engine
+from ..ops import paged
+
+NS = "hk"
+_OPS: Dict[str, engine.Op] = {}
+
+
+def _nothing(*args, **kwargs):
+    return None
+
+
+def _define(name: str, schema: str, impl: Callable) -> engine.Op:
+    op = _OPS.get(name)
+    if op is None:
+        op = engine.Op(f"{NS}::{name}", f"{name}{schema}", _nothing, ("launch",))
+        op.define(impl, dispatch="CUDA")
+        _OPS[name] = op
+    return op
+
+
+def _reshape_and_cache(key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype, k_scale, v_scale):
+    paged.reshape_and_cache(key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype, k_scale, v_scale)
+
+
+def _paged_attention_decode(out, query, key_cache, value_cache, block_tables, seq_lens, scale, kv_cache_dtype,
+                            k_scale, v_scale, num_splits, part_out, part_lse):
+    paged.paged_attention_decode(out, query, key_cache, value_cache, block_tables, seq_lens, scale,
+                                 kv_cache_dtype, k_scale, v_scale, num_splits=num_splits,
+                                 scratch=(part_out, part_lse) if num_splits > 1 else None)
+
+
+def reshape_and_cache_op() -> engine.Op:
+    return _define(
+        "reshape_and_cache",
+        "(Tensor key, Tensor value, Tensor(a!) key_cache, Tensor(b!) value_cache, Tensor slot_mapping, "
+        "str kv_cache_dtype, Tensor k_scale, Tensor v_scale) -> ()", _reshape_and_cache)
+
+
+def paged_attention_decode_op() -> engine.Op:
+    return _define(
+        "paged_attention_decode",
+        "(Tensor(a!) out, Tensor query, Tensor key_cache, Tensor value_cache, Tensor block_tables, "
+        "Tensor seq_lens, float scale, str kv_cache_dtype, Tensor k_scale, Tensor v_scale, int num_splits, "
+        "Tensor(b!) part_out, Tensor(c!) part_lse) -> ()", _paged_attention_decode)
+
+
+def fused_walk_op(head_dim: int, splits: int) -> engine.Op:
+    """`hk::paged_decode_fused_d{D}_s{S}` (python/hk/ops/paged.py:544-547, 706-708): the walk on
+    engine views; with one split it writes the answer, with more the partials."""
+    if head_dim not in paged.HEAD_DIMS:
+        raise ValueError(f"hk.ops.paged: no walk for head_dim {head_dim} (have {paged.HEAD_DIMS})")
+
+    def impl(q, k_cache, v_cache, block_table, seq_lens, out, o_part, ml_part):
+        reqs, hkv, g, d = q.shape
+        hq = hkv * g
+        q3 = q.as_strided((reqs, hq, d), (q.stride(0), q.stride(2), 1))
+        o3 = out.as_strided((reqs, hq, d), (out.stride(0), out.stride(2), 1))
+        fp8 = k_cache.dtype != torch.bfloat16
+        paged.paged_attention_decode(
+            o3, q3, k_cache.transpose(1, 2), v_cache.transpose(1, 2), block_table, seq_lens[:reqs], d ** -0.5,
+            "fp8" if fp8 else "auto", None, None, num_splits=splits,
+            scratch=(o_part.view(-1, hq, d), ml_part.view(-1, hq)) if splits > 1 else None, merge=False)
+
+    return _define(f"paged_decode_fused_d{head_dim}_s{splits}",
+                   "(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_table, Tensor seq_lens, "
+                   "Tensor(a!) out, Tensor(b!) o_part, Tensor(c!) ml_part) -> ()", impl)
+
+
+def merge_op(head_dim: int, splits: int) -> engine.Op:
+    """`hk::paged_merge_d{D}_s{S}` (python/hk/ops/paged.py:482-483, 727-729)."""
+
+    def impl(seq_lens, out, o_part, ml_part):
+        reqs = out.shape[0]
+        paged.merge_splits(o_part[: reqs * splits], ml_part[: reqs * splits], splits, out)
+
+    return _define(f"paged_merge_d{head_dim}_s{splits}",
+                   "(Tensor seq_lens, Tensor(a!) out, Tensor o_part, Tensor ml_part) -> ()", impl)
+
+
+def launcher(kind: str, head_dim: int, splits: int) -> engine.Op:
+    """The decode launches by kind, as python/hk/integration/vllm_backend.py:154-163 asks for
+    them: "walk" or "merge"."""
+    return fused_walk_op(head_dim, splits) if kind == "walk" else merge_op(head_dim, splits)

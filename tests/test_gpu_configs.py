@@ -1,0 +1,168 @@
+"""The five measured configurations: parity against the float64 oracle where the oracle
+finishes in seconds (c1 in full; c2-c5 on a slice of their sequences with their real shapes
+and dtypes), and at FULL size through properties that need no oracle: a cache of V == 1
+answers exactly 1, split and unsplit walks agree, a kv-head shard equals the same heads of the
+whole, a KV split over emulated ranks folds back to the single-GPU answer, the cache write is
+an exact round trip, and a step leaves every other slot of the cache untouched."""
+
+import pytest
+import torch
+
+from hk_dsl_b200 import workloads as W
+from oracle import paged_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _paged():
+    from hk_dsl_b200.ops import paged
+    return paged
+
+
+def _decode(st, splits=None, l=0, out=None):
+    out = torch.empty_like(st.out) if out is None else out
+    _paged().paged_attention_decode(out, st.query, st.k_caches[l], st.v_caches[l], st.block_table, st.seq_lens,
+                                    st.scale, st.spec.kv_cache_dtype, st.k_scale, st.v_scale, num_splits=splits)
+    return out
+
+
+def _oracle(st, rows=None):
+    n = len(st.lens)
+    rows = range(n) if rows is None else rows
+    want = torch.zeros(n, st.q_heads, st.spec.head_dim)
+    bs = st.spec.block_size
+    for i in rows:
+        s = st.lens[i]
+        pages = st.block_table[i, : -(-s // bs)].long()
+        kc, vc = st.k_caches[0][pages].cpu(), st.v_caches[0][pages].cpu()
+        table = torch.arange(kc.shape[0], dtype=torch.int32)[None]
+        want[i] = orc.paged_decode_ref(st.query[i:i + 1].cpu(), kc, vc, table, torch.tensor([s], dtype=torch.int32),
+                                       st.scale, st.k_scale.cpu() if st.k_scale is not None else None,
+                                       st.v_scale.cpu() if st.v_scale is not None else None)[0]
+    return want
+
+
+def test_c1_in_full_cache_write_and_decode():
+    spec = W.CONFIGS["c1"]
+    st = W.build_step(spec, "cuda")
+    kc, vc = st.k_caches[0], st.v_caches[0]
+    want_k, want_v = kc.cpu().clone(), vc.cpu().clone()
+    _paged().reshape_and_cache(st.key, st.value, kc, vc, st.slot_mapping, "auto")
+    orc.reshape_and_cache_ref(st.key.cpu(), st.value.cpu(), want_k, want_v, st.slot_mapping.cpu())
+    assert torch.equal(kc.cpu(), want_k) and torch.equal(vc.cpu(), want_v)
+    want = orc.paged_decode_ref(st.query.cpu(), want_k, want_v, st.block_table.cpu(), st.seq_lens.cpu(), st.scale)
+    for splits in (None, 1, 2, 8):
+        got = _decode(st, splits)
+        orc.check(got, want)
+        orc.check_baseline(got, want)
+
+
+@pytest.mark.parametrize("name,take", [("c2", 3), ("c3", 4), ("c4", 6), ("c5", 1)])
+def test_config_slices_against_the_oracle(name, take):
+    """The first `take` sequences of the config (c5: one sequence cut to 16384 tokens), with the
+    config's head counts, dtype and scales."""
+    spec = W.CONFIGS[name]
+    lens = W.seq_lens_of(spec)[:take]
+    if name == "c5":
+        lens = [16384 + 5]
+    st = W.build_step(spec, "cuda", lens=lens)
+    _paged().reshape_and_cache(st.key, st.value, st.k_caches[0], st.v_caches[0], st.slot_mapping,
+                               spec.kv_cache_dtype, st.k_scale, st.v_scale)
+    want = _oracle(st)
+    for splits in (None, 1, 4):
+        got = _decode(st, splits)
+        orc.check(got, want)
+        orc.check_baseline(got, want)
+
+
+@pytest.mark.parametrize("name", ["c2", "c3", "c4", "c5"])
+def test_full_size_properties(name):
+    spec = W.CONFIGS[name]
+    st = W.build_step(spec, "cuda")
+    paged = _paged()
+    n = len(st.lens)
+    kc, vc = st.k_caches[0], st.v_caches[0]
+
+    # (1) the step's cache write: exact round trip of the new rows, nothing else touched
+    before_k = kc.clone()
+    paged.reshape_and_cache(st.key, st.value, kc, vc, st.slot_mapping, spec.kv_cache_dtype, st.k_scale, st.v_scale)
+    slots = st.slot_mapping
+    blk, off = slots // spec.block_size, slots % spec.block_size
+    if spec.fp8:
+        want_rows = orc.quantize_fp8(st.key.cpu(), st.k_scale.cpu()).view(torch.uint8)
+        got_rows = kc[blk, off].view(torch.uint8).cpu()
+    else:
+        want_rows, got_rows = st.key.cpu(), kc[blk, off].cpu()
+    assert torch.equal(got_rows, want_rows)
+    changed = (kc.view(torch.uint8) != before_k.view(torch.uint8)).any(dim=-1).any(dim=-1)      # (blocks, block)
+    mask = torch.zeros_like(changed)
+    mask[blk, off] = True
+    assert not (changed & ~mask).any()
+
+    # (2) split and unsplit walks agree, and the planner's choice with them
+    a = _decode(st, 1).float()
+    planned = _decode(st, None).float()
+    b = _decode(st, 8).float()
+    assert torch.isfinite(a).all()
+    assert (a - b).abs().max().item() < 2e-2 and (a - planned).abs().max().item() < 2e-2
+    assert (a - b).abs().mean().item() < 2e-3
+
+    # (3) spot check of the two shortest sequences against the oracle at full batch
+    order = sorted(range(n), key=lambda i: st.lens[i])[:2] if name != "c5" else []
+    if order:
+        want = _oracle(st, order)
+        orc.check(planned[order], want[order])
+
+    # (4) a kv-head shard computes exactly the bits of those heads in the whole
+    if spec.kv_heads >= 2:
+        hkv, g = spec.kv_heads, spec.q_heads // spec.kv_heads
+        lo, hi = hkv // 2, hkv
+        out_sh = torch.empty(n, (hi - lo) * g, spec.head_dim, device="cuda", dtype=torch.bfloat16)
+        paged.paged_attention_decode(out_sh, st.query[:, lo * g:hi * g], kc[:, :, lo:hi], vc[:, :, lo:hi],
+                                     st.block_table, st.seq_lens, st.scale, spec.kv_cache_dtype, st.k_scale,
+                                     st.v_scale, num_splits=1)
+        whole = _decode(st, 1)
+        assert torch.equal(out_sh.view(torch.int16), whole[:, lo * g:hi * g].contiguous().view(torch.int16))
+
+    # (5) V == 1 answers exactly 1 (bf16 caches)
+    if not spec.fp8:
+        ones = torch.ones_like(vc)
+        out = torch.empty_like(st.out)
+        for s in (1, None):
+            paged.paged_attention_decode(out, st.query, kc, ones, st.block_table, st.seq_lens, st.scale,
+                                         num_splits=s)
+            assert (out.float() == 1.0).all()
+
+
+def test_c5_kv_split_over_emulated_ranks_folds_to_the_single_gpu_answer():
+    """Four 'ranks' run one after another on one GPU, each on its own token range with its own
+    local lengths and table slice; their (out, lse) records are laid out as the all-gather lays
+    them and folded by the merge kernel."""
+    from hk_dsl_b200.ops import paged_dist
+
+    paged = _paged()
+    spec = W.CONFIGS["c5"]
+    st = W.build_step(spec, "cuda", lens=[32768 + 40, 20000])
+    whole = _decode(st, None).float()
+    world = 4
+    n, hq, d = st.query.shape
+    decs = [paged_dist.SplitKVDecoder(n, hq, st.kv_heads, d, "cuda", local_splits=4) for _ in range(world)]
+    bs = spec.block_size
+    for r, dec in enumerate(decs):
+        ranges = [paged_dist.kv_range(s, world, r, bs) for s in st.lens]
+        local = torch.tensor([hi - lo for lo, hi in ranges], dtype=torch.int32, device="cuda")
+        table = torch.zeros_like(st.block_table)
+        for i, (lo, hi) in enumerate(ranges):
+            p0, p1 = lo // bs, -(-hi // bs)
+            table[i, : p1 - p0] = st.block_table[i, p0:p1]
+        dec.local_partial(st.query, st.k_caches[0], st.v_caches[0], table, local, st.scale)
+    last = decs[0]
+    last.world = world
+    last.all = torch.cat([dec.mine for dec in decs])
+    out = torch.empty_like(st.out)
+    last.merge(out)
+    torch.cuda.synchronize()
+    assert (out.float() - whole).abs().max().item() < 2e-2
+    assert (out.float() - whole).abs().mean().item() < 2e-3
+    want = _oracle(st, [1])
+    orc.check(out[1:2], want[1:2])

@@ -1,0 +1,89 @@
+"""The split planner (python/hk/ops/paged.py:877-914, tests/hk/ir/test_paged_decode_plan.py of
+the reference: powers of two, few distinct plans, HK_SPLITS override) and the C-ABI library:
+it loads, exports every symbol include/hkb.h declares, and refuses bad arguments without a GPU."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+from hk_dsl_b200.ops import paged
+from hk_dsl_b200.runtime import lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_every_declared_symbol_is_exported():
+    text = open(os.path.join(ROOT, "include", "hkb.h")).read()
+    declared = set(re.findall(r"\b(hkb_[a-z_]+)\s*\(", text))
+    declared -= {"hkb_status"}
+    assert declared == set(lib.SIGNATURES), (declared ^ set(lib.SIGNATURES))
+    loaded = lib.load()
+    for name in declared:
+        assert getattr(loaded, name) is not None
+    assert loaded.hkb_version() == 100
+
+
+def test_status_text_and_refusals_need_no_gpu():
+    l = lib.load()
+    assert lib.strerror(0) == "ok" and "unknown" in lib.strerror(-77)
+    for code in (-1, -2, -3, -4, -5, -6, -7, -8, -9, -10, -11, -100):
+        assert lib.strerror(code) and "unknown" not in lib.strerror(code)
+    c = lib.CacheT(16, 2048, 128, 32768, 4)
+    # argument checks come before any CUDA call: head_dim 96, block_size 20, group 3/2, NULL pointers
+    assert l.hkb_paged_decode(16, 1, 1, 16, 1, 1, c, c, 16, 8, 8, 16, None, 1, 4, 2, 96, 16, 0.1, 0, None, None, 1, None, None, None) == -2
+    assert l.hkb_paged_decode(16, 1, 1, 16, 1, 1, c, c, 16, 8, 8, 16, None, 1, 4, 2, 128, 20, 0.1, 0, None, None, 1, None, None, None) == -3
+    assert l.hkb_paged_decode(16, 1, 1, 16, 1, 1, c, c, 16, 8, 8, 16, None, 1, 3, 2, 128, 16, 0.1, 0, None, None, 1, None, None, None) == -4
+    assert l.hkb_paged_decode(None, 1, 1, 16, 1, 1, c, c, 16, 8, 8, 16, None, 1, 4, 2, 128, 16, 0.1, 0, None, None, 1, None, None, None) == -1
+    assert l.hkb_paged_decode(16, 1, 1, 16, 1, 1, c, c, 16, 8, 8, 16, None, 1, 4, 2, 128, 16, 0.1, 1, None, None, 1, None, None, None) == -10
+    assert l.hkb_paged_decode(16, 1, 1, 16, 1, 1, c, c, 16, 8, 8, 16, None, 1, 4, 2, 128, 16, 0.1, 0, None, None, 4, None, None, None) == -8
+    assert l.hkb_paged_decode(16, 1, 1, 16, 1, 1, c, c, 16, 8, 8, 16, None, 0, 4, 2, 128, 16, 0.1, 0, None, None, 1, None, None, None) == 0
+    assert l.hkb_reshape_and_cache(16, 16, 256, 128, 256, 128, c, c, 16, 1, 0, 2, 128, 16, 0, None, None, None) == 0
+    assert l.hkb_reshape_and_cache(16, 16, 256, 128, 256, 128, c, c, None, 1, 4, 2, 128, 16, 0, None, None, None) == -1
+    assert l.hkb_reshape_and_cache(16, 16, 256, 128, 256, 128, c, c, 16, 1, 4, 2, 128, 16, 7, None, None, None) == -5
+    assert l.hkb_merge(16, 128, 128, 0, None, None, 4, 4, 16, 1, 1, 2, 1, 4, 128, None, None, None) == -1
+    with pytest.raises(lib.HkbError, match="head_dim"):
+        lib.check("hkb_paged_decode", -2)
+
+
+def test_scratch_sizes():
+    l = lib.load()
+    off = l.hkb_scratch_lse_offset(64, 32, 128, 4)
+    assert off == 64 * 4 * 32 * 128 * 4 and off % 256 == 0
+    assert l.hkb_scratch_bytes(64, 32, 128, 4) >= off + 64 * 4 * 32 * 4
+    assert l.hkb_scratch_bytes(0, 32, 128, 4) == 0
+
+
+def test_plans_are_powers_of_two_and_few(monkeypatch):
+    monkeypatch.delenv("HK_SPLITS", raising=False)
+    plans = [paged.plan_splits_for(n, 8, 2560, 148) for n in range(1, 257)]
+    assert all(p & (p - 1) == 0 and 1 <= p <= paged.MAX_SPLITS for p in plans)
+    assert len(set(plans)) <= 9
+    assert plans == sorted(plans, reverse=True)                 # fewer requests, more splits
+    assert paged.plan_splits_for(512, 8, 2560, 148) == 1
+    # never more splits than 8-tile chunks of the longest sequence
+    assert paged.plan_splits_for(1, 1, 16, 148) <= 2
+    assert paged.plan_splits_for(1, 1, 1, 148) == 1
+
+
+def test_c_planner_equals_python_planner():
+    l = lib.load()
+    for n in (1, 2, 3, 4, 8, 16, 24, 32, 64, 100, 128, 256):
+        for hkv in (1, 2, 4, 8):
+            for tiles in (1, 7, 64, 512, 8192):
+                assert l.hkb_plan_splits(n, hkv, tiles, 148) == paged.plan_splits_for(n, hkv, tiles, 148), (n, hkv, tiles)
+
+
+def test_hk_splits_override(monkeypatch):
+    for v in ("off", "0", "1"):
+        monkeypatch.setenv("HK_SPLITS", v)
+        assert paged.plan_splits(1, 8, 2560) == 1
+    monkeypatch.setenv("HK_SPLITS", "8")
+    assert paged.plan_splits(64, 8, 2560) == 8
+    monkeypatch.setenv("HK_SPLITS", "12")
+    assert paged.plan_splits(64, 8, 2560) == 8                   # a power of two
+    monkeypatch.setenv("HK_SPLITS", "64")
+    assert paged.plan_splits(64, 8, 4) == 4                      # never more than the pages
+    monkeypatch.setenv("HK_SPLITS", "auto")
+    assert paged.plan_splits(64, 8, 2560) == paged.plan_splits_for(64, 8, 2560, paged.sm_count())
