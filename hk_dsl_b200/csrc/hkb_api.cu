@@ -34,24 +34,30 @@ extern "C" int hkb_sm_count(int device) {
   return f.sm_count;
 }
 
-// Enough CTAs for two four-warp CTAs an SM, four waves deep so that sequences of
-// unequal length even out; a power of two (each count is one plan a captured graph keeps).
-// hk-dsl aims at 256 one-warp workgroups on a 96-CU card (python/hk/ops/paged.py:838-864);
-// the shape of the rule -- ceil(target / (requests * kv heads)), capped by the pages and a
-// maximum -- is the same, the target is B200's.
+// How many partial slots a sequence gets (`num_splits`). The split decode deals the tiles of
+// all sequences of a kv head in equal shares to the W warps that serve the head (two four-warp
+// CTAs an SM, divided among the heads); a share may not be shorter than longest / (parts - 1),
+// so that no sequence needs more than `parts` slots. With n sequences whose longest is up to
+// 8x the mean, parts = 1 + 8 W / n keeps that bound from limiting the shares. Capped by the
+// pieces the longest allowed sequence can have (8 tiles a piece at least) and HKB_MAX_SPLITS,
+// rounded up to a power of two: a function of host values only, so a captured graph's plan is
+// right for every replay. hk-dsl's rule has the same shape -- ceil(target / (requests * kv
+// heads)), capped by pages and a maximum (python/hk/ops/paged.py:838-914) -- with AMD's target.
 extern "C" int hkb_plan_splits(int num_seqs, int num_kv_heads, int max_tiles, int sm_count) {
   if (sm_count <= 0) sm_count = 148;
-  const long long have = (long long)(num_seqs > 0 ? num_seqs : 1) * (num_kv_heads > 0 ? num_kv_heads : 1);
-  const long long target = (long long)sm_count * 2 * 4;
-  long long want = (target + have - 1) / have;
-  // at least 8 tiles (128 tokens) a split: below that a split costs more than it hides
-  long long cap = max_tiles > 0 ? (max_tiles + 7) / 8 : 1;
-  if (cap > HKB_MAX_SPLITS) cap = HKB_MAX_SPLITS;
+  const long long n = num_seqs > 0 ? num_seqs : 1;
+  const long long heads = num_kv_heads > 0 ? num_kv_heads : 1;
+  long long per = ((long long)sm_count * 2) / heads;
+  if (per < 1) per = 1;
+  const long long w = per * 4;
+  long long want = 1 + (8 * w + n - 1) / n;
+  const long long cap = max_tiles > 0 ? (max_tiles + 7) / 8 + 1 : 2;
   if (want > cap) want = cap;
-  if (want < 1) want = 1;
-  int p = 1;
-  while ((long long)p * 2 <= want) p *= 2;  // round down to a power of two
-  return p;
+  if (want < 2) want = 2;
+  long long p = 2;
+  while (p < want) p *= 2;
+  if (p > HKB_MAX_SPLITS) p = HKB_MAX_SPLITS;
+  return (int)p;
 }
 
 extern "C" size_t hkb_scratch_lse_offset(int num_seqs, int num_q_heads, int head_dim, int num_splits) {

@@ -2,6 +2,9 @@
 // the dispatch from (head_dim, kv dtype, GQA group) to a walk instantiation.
 #include "hkb_walk_cc.cuh"
 #include "hkb_walk_mma.cuh"
+#include "hkb_walk_stream.cuh"
+
+#include <cstdlib>
 
 extern thread_local int hkb_tls_cuda_error;
 
@@ -120,11 +123,75 @@ static int launch_walk(int smem_bytes, int threads, dim3 grid, const DecodeArgs&
   return HKB_OK;
 }
 
-// CUDA-core walk: GH query heads a pass, ceil(group / GH) passes a kv head.
+template <void (*kernel)(const DecodeArgs, int)>
+static int launch_stream(int smem_bytes, int threads, dim3 grid, const DecodeArgs& a, int num_seqs, cudaStream_t st) {
+  static bool armed[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess && dev >= 0 && dev < 64 && !armed[dev]) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e == cudaSuccess) armed[dev] = true;
+  }
+  if (e == cudaSuccess) {
+    kernel<<<grid, threads, smem_bytes, st>>>(a, num_seqs);
+    e = cudaGetLastError();
+  }
+  if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
+  return HKB_OK;
+}
+
+// More than one part and a prefix table that fits shared memory: the persistent balanced
+// stream. One part, or HKB_FIXED_SPLITS=1 in the environment (for A/B measurements): the
+// fixed-split grid, one CTA a (sequence, kv head, split).
+static bool use_stream(const DecodeArgs& a, int num_seqs) {
+  static const bool fixed = [] { const char* v = std::getenv("HKB_FIXED_SPLITS"); return v && v[0] == '1'; }();
+  return a.num_splits > 1 && num_seqs <= STREAM_MAX_SEQS && !fixed;
+}
+
+static dim3 stream_grid(int planes) {
+  int sms = hkb_sm_count(-1);
+  if (sms <= 0) sms = 148;
+  int per = (sms * 2) / planes;
+  if (per < 1) per = 1;
+  return dim3(per, planes, 1);
+}
+
+// CUDA-core walk. Fixed splits: GH query heads a CTA pass, ceil(group / GH) passes a kv head.
+// Stream: rings of two warps holding two heads each (one warp for groups of 1 and 2).
 template <int D, bool FP8>
 static int dispatch_cc(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
-  constexpr int WARPS = 4;
   constexpr int NST = FP8 ? 4 : 3;
+  if (use_stream(a, num_seqs)) {
+    constexpr int RINGS = 4;
+    if (a.group == 1) {
+      using P = StreamCC<D, FP8, 1, 1, NST>;
+      return launch_stream<walk_stream_kernel<P, RINGS>>(WalkStream<P, RINGS>::SMEM_BYTES, WalkStream<P, RINGS>::THREADS,
+                                                         stream_grid(a.num_kv_heads * P::passes(a.group)), a, num_seqs, st);
+    }
+    if (a.group == 2) {
+      using P = StreamCC<D, FP8, 2, 1, NST>;
+      return launch_stream<walk_stream_kernel<P, RINGS>>(WalkStream<P, RINGS>::SMEM_BYTES, WalkStream<P, RINGS>::THREADS,
+                                                         stream_grid(a.num_kv_heads * P::passes(a.group)), a, num_seqs, st);
+    }
+    // Rings of two warps with two heads each measured slower than one warp with four heads
+    // (4.6 against 5.4 TB/s on the Llama-3-8B shape): twice the warps do not pay for unpacking
+    // every K/V element twice. HKB_CC_RING=pair selects them for A/B measurements.
+    static const bool pair = [] { const char* v = std::getenv("HKB_CC_RING"); return v && v[0] == 'p'; }();
+    if (pair) {
+      using P = StreamCC<D, FP8, 2, 2, NST>;
+      return launch_stream<walk_stream_kernel<P, RINGS>>(WalkStream<P, RINGS>::SMEM_BYTES, WalkStream<P, RINGS>::THREADS,
+                                                         stream_grid(a.num_kv_heads * P::passes(a.group)), a, num_seqs, st);
+    }
+    if (a.group == 3) {
+      using P = StreamCC<D, FP8, 3, 1, NST>;
+      return launch_stream<walk_stream_kernel<P, RINGS>>(WalkStream<P, RINGS>::SMEM_BYTES, WalkStream<P, RINGS>::THREADS,
+                                                         stream_grid(a.num_kv_heads * P::passes(a.group)), a, num_seqs, st);
+    }
+    using P = StreamCC<D, FP8, 4, 1, NST>;
+    return launch_stream<walk_stream_kernel<P, RINGS>>(WalkStream<P, RINGS>::SMEM_BYTES, WalkStream<P, RINGS>::THREADS,
+                                                       stream_grid(a.num_kv_heads * P::passes(a.group)), a, num_seqs, st);
+  }
+  constexpr int WARPS = 4;
   int gh;
   switch (a.group) {
     case 1: gh = 1; break;
@@ -151,6 +218,14 @@ static int dispatch_mma(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
   constexpr int WARPS = 4;
   constexpr int NST = FP8 ? 4 : 3;
   dim3 grid(a.num_splits, a.num_kv_heads, num_seqs);
+  if (use_stream(a, num_seqs)) {
+    grid = stream_grid(a.num_kv_heads);
+    if (a.group <= 8)
+      return launch_stream<walk_stream_kernel<WalkMMA<D, FP8, 1, WARPS, NST>, WARPS>>(
+          WalkStream<WalkMMA<D, FP8, 1, WARPS, NST>, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
+    return launch_stream<walk_stream_kernel<WalkMMA<D, FP8, 2, WARPS, NST>, WARPS>>(
+        WalkStream<WalkMMA<D, FP8, 2, WARPS, NST>, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
+  }
   if (a.group <= 8)
     return launch_walk<walk_mma_kernel<D, FP8, 1, WARPS, NST>>(WalkMMA<D, FP8, 1, WARPS, NST>::SMEM_BYTES,
                                                                WARPS * 32, grid, a, st);
@@ -208,7 +283,9 @@ extern "C" int hkb_paged_decode(void* out, int64_t out_stride_tok, int64_t out_s
   a.seq_lens = seq_lens; a.q_start = q_start;
   a.num_q_heads = num_q_heads; a.num_kv_heads = num_kv_heads; a.group = group;
   a.tiles_per_page = block_size / TILE_TOKENS;
-  a.scale = scale; a.k_scale = k_scale; a.v_scale = v_scale;
+  a.scale = scale;
+  a.k_scale = fp8 ? k_scale : nullptr;   // scales apply to fp8 caches only
+  a.v_scale = fp8 ? v_scale : nullptr;
   a.num_splits = num_splits; a.part_out = part_out; a.part_lse = part_lse;
   cudaStream_t st = (cudaStream_t)stream;
 

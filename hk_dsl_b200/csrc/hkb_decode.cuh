@@ -47,29 +47,65 @@ template <int ROWB>
 struct TileLoader {
   static constexpr int CPR = ROWB / 16;              // 16-byte chunks per row
   static constexpr int TILE_BYTES = TILE_TOKENS * ROWB;
-  static constexpr int ITERS = TILE_TOKENS * CPR / 32;
+  static constexpr int ITERS = TILE_TOKENS * CPR / 32;   // copies a lane issues a tile
+  static constexpr int RPI = 32 / CPR;               // rows the warp covers an iteration
+  static constexpr int NPAT = 8 / RPI;               // distinct swizzle patterns over the iterations
   const uint8_t* kbase;  // + kv head offset
   const uint8_t* vbase;
   int64_t ksb, kst, vsb, vst;
   int tiles_per_page, num_blocks;
+  // per-lane constants (set by `prepare`): where this lane's chunk sits in a row group
+  uint32_t dst[NPAT];    // shared-memory offset of iteration q (mod NPAT), without it * 512
+  int lane_k, lane_v;    // global offset of the lane's chunk in iteration 0
+  bool k_flat, v_flat;   // the 16 rows of a tile are contiguous in global memory
+
+  __device__ __forceinline__ void prepare(int lane) {
+    const int rl = lane / CPR, c = lane % CPR;
+#pragma unroll
+    for (int q = 0; q < NPAT; ++q) dst[q] = rl * ROWB + ((c ^ ((RPI * q + rl) & 7)) << 4);
+    lane_k = rl * (int)kst + c * 16;
+    lane_v = rl * (int)vst + c * 16;
+    k_flat = kst == ROWB;
+    v_flat = vst == ROWB;
+  }
+
+  __device__ __forceinline__ void copy_tile(uint32_t smem_tile, const uint8_t* p, int64_t st, int lane_off,
+                                            bool flat) const {
+    p += lane_off;
+    if (flat) {   // iteration it is 512 bytes on: immediates
+#pragma unroll
+      for (int it = 0; it < ITERS; ++it) cp_async16(smem_tile + dst[it % NPAT] + it * (RPI * ROWB), p + it * 512);
+    } else {
+      const int64_t step = RPI * st;
+#pragma unroll
+      for (int it = 0; it < ITERS; ++it) cp_async16(smem_tile + dst[it % NPAT] + it * (RPI * ROWB), p + it * step);
+    }
+  }
+
+  __device__ __forceinline__ void tile_ptrs(int tile, int page_id, const uint8_t*& kp, const uint8_t*& vp) const {
+    const int id = min(max(page_id, 0), num_blocks - 1);
+    kp = kbase + (int64_t)id * ksb;
+    vp = vbase + (int64_t)id * vsb;
+    if (tiles_per_page != 1) {   // a page of several 16-token tiles
+      const int sub = tile % tiles_per_page;
+      kp += (int64_t)(sub * TILE_TOKENS) * kst;
+      vp += (int64_t)(sub * TILE_TOKENS) * vst;
+    }
+  }
+
+  // The K tile alone (which = 0) or the V tile alone (which = 1): for rings two warps fill.
+  __device__ __forceinline__ void issue_one(uint32_t smem_stage, int tile, int page_id, int lane, int which) const {
+    const uint8_t *kp, *vp;
+    tile_ptrs(tile, page_id, kp, vp);
+    if (which) copy_tile(smem_stage + TILE_BYTES, vp, vst, lane_v, v_flat);
+    else copy_tile(smem_stage, kp, kst, lane_k, k_flat);
+  }
 
   __device__ __forceinline__ void issue(uint32_t smem_stage, int tile, int page_id, int lane) const {
-    const int sub = tile % tiles_per_page;
-    const int id = min(max(page_id, 0), num_blocks - 1);
-    const uint8_t* kp = kbase + (int64_t)id * ksb + (int64_t)(sub * TILE_TOKENS) * kst;
-    const uint8_t* vp = vbase + (int64_t)id * vsb + (int64_t)(sub * TILE_TOKENS) * vst;
-#pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-      const int x = it * 32 + lane;
-      const int r = x / CPR, c = x % CPR;
-      cp_async16(smem_stage + tile_off<ROWB>(r, c), kp + (int64_t)r * kst + c * 16);
-    }
-#pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-      const int x = it * 32 + lane;
-      const int r = x / CPR, c = x % CPR;
-      cp_async16(smem_stage + TILE_BYTES + tile_off<ROWB>(r, c), vp + (int64_t)r * vst + c * 16);
-    }
+    const uint8_t *kp, *vp;
+    tile_ptrs(tile, page_id, kp, vp);
+    copy_tile(smem_stage, kp, kst, lane_k, k_flat);
+    copy_tile(smem_stage + TILE_BYTES, vp, vst, lane_v, v_flat);
   }
 };
 

@@ -61,32 +61,53 @@ struct WalkCC {
   __device__ static __forceinline__ void tile(uint32_t stage, int tok0, int seq_len, int g, int j,
                                               const uint64_t (&q2)[GH][DPL / 2], float (&m)[GH], float (&l)[GH],
                                               uint64_t (&o2)[GH][DPL / 2]) {
-    float s[4][GH];
-    // scores of this lane's 4 tokens over its DPL dims: packed FMAs over (even, odd) dims
+    // This lane's 16-byte pieces: row r = 4 i + g, chunk (j ^ (r & 7)) + 8 p. r & 7 is 4 (i & 1) + g,
+    // so two lane-constant bases (even / odd i) plus compile-time offsets address all of them.
+    const uint32_t xe = stage + g * ROWB + ((j ^ g) << 4);
+    const uint32_t xo = stage + g * ROWB + ((j ^ (4 + g)) << 4);
+    // scores of this lane's 4 tokens over its DPL dims: packed FMAs over (even, odd) dims;
+    // kept as pairs over tokens (2 i2, 2 i2 + 1) for the packed adds below
+    uint64_t s2[2][GH];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int r = i * 4 + g;
-      uint64_t k2[DPL / 2];
+    for (int i2 = 0; i2 < 2; ++i2) {
+      float sa[2][GH];
 #pragma unroll
-      for (int p = 0; p < NP; ++p) unpack_piece(lds128(stage + tile_off<ROWB>(r, j + 8 * p)), k2 + p * (EPP / 2));
+      for (int ii = 0; ii < 2; ++ii) {
+        const int i = 2 * i2 + ii;
+        uint64_t k2[DPL / 2];
 #pragma unroll
-      for (int h = 0; h < GH; ++h) {
-        uint64_t acc = 0ull;  // (+0.f, +0.f)
+        for (int p = 0; p < NP; ++p)
+          unpack_piece(lds128((ii ? xo : xe) + i * 4 * ROWB + p * 128), k2 + p * (EPP / 2));
 #pragma unroll
-        for (int e = 0; e < DPL / 2; ++e) acc = fma2(k2[e], q2[h][e], acc);
-        float a0, a1;
-        unpack2(acc, a0, a1);
-        s[i][h] = a0 + a1;
+        for (int h = 0; h < GH; ++h) {
+          uint64_t acc = 0ull;  // (+0.f, +0.f)
+#pragma unroll
+          for (int e = 0; e < DPL / 2; ++e) acc = fma2(k2[e], q2[h][e], acc);
+          float a0, a1;
+          unpack2(acc, a0, a1);
+          sa[ii][h] = a0 + a1;
+        }
       }
+#pragma unroll
+      for (int h = 0; h < GH; ++h) s2[i2][h] = pack2(sa[0][h], sa[1][h]);
     }
-    // complete the dot products over the 8 lanes of the group
+    // complete the dot products over the 8 lanes of the group (shuffle halves, add pairs)
 #pragma unroll
     for (int x = 1; x < 8; x <<= 1)
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i2 = 0; i2 < 2; ++i2)
 #pragma unroll
-        for (int h = 0; h < GH; ++h) s[i][h] += __shfl_xor_sync(0xffffffffu, s[i][h], x);
+        for (int h = 0; h < GH; ++h) {
+          float a0, a1;
+          unpack2(s2[i2][h], a0, a1);
+          s2[i2][h] = add2(s2[i2][h], pack2(__shfl_xor_sync(0xffffffffu, a0, x), __shfl_xor_sync(0xffffffffu, a1, x)));
+        }
 
+    float s[4][GH];
+#pragma unroll
+    for (int i2 = 0; i2 < 2; ++i2)
+#pragma unroll
+      for (int h = 0; h < GH; ++h) unpack2(s2[i2][h], s[2 * i2][h], s[2 * i2 + 1][h]);
     bool live[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -95,39 +116,128 @@ struct WalkCC {
 #pragma unroll
         for (int h = 0; h < GH; ++h) s[i][h] = -INFINITY;
     }
-    // online softmax of this stream, head by head
+    // online softmax of this stream: new maxima of all heads first, then ONE branch for the
+    // (rare, after the first tiles) rescale of the running sums
+    float m_use[GH];
+    bool moved = false;
 #pragma unroll
     for (int h = 0; h < GH; ++h) {
-      const float mx = fmaxf(fmaxf(s[0][h], s[1][h]), fmaxf(s[2][h], s[3][h]));
-      const float m_new = fmaxf(m[h], mx);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;  // nothing seen yet: keep exp2 finite
-      if (m_new != m[h]) {
-        const float alpha = fast_exp2(m[h] - m_use);
+      const float m_new = fmaxf(m[h], fmaxf(fmaxf(s[0][h], s[1][h]), fmaxf(s[2][h], s[3][h])));
+      moved |= m_new != m[h];
+      m_use[h] = m_new;
+    }
+    if (moved) {
+#pragma unroll
+      for (int h = 0; h < GH; ++h) {
+        const float safe = (m_use[h] == -INFINITY) ? 0.f : m_use[h];   // nothing seen yet: keep exp2 finite
+        const float alpha = fast_exp2(m[h] - safe);                    // 1 for a head whose maximum stayed
         l[h] *= alpha;
         const uint64_t a2 = pack2(alpha, alpha);
 #pragma unroll
         for (int e = 0; e < DPL / 2; ++e) o2[h][e] = mul2(o2[h][e], a2);
-        m[h] = m_new;
+        m[h] = m_use[h];
       }
+    }
+#pragma unroll
+    for (int h = 0; h < GH; ++h) {
+      const float safe = (m_use[h] == -INFINITY) ? 0.f : m_use[h];
       float sum = 0.f;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { s[i][h] = fast_exp2(s[i][h] - m_use); sum += s[i][h]; }
+      for (int i = 0; i < 4; ++i) { s[i][h] = fast_exp2(s[i][h] - safe); sum += s[i][h]; }
       l[h] += sum;
     }
     // O += P V
-    const uint32_t vst = stage + Loader::TILE_BYTES;
+    const uint32_t ve = xe + Loader::TILE_BYTES, vo = xo + Loader::TILE_BYTES;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int r = i * 4 + g;
       uint64_t v2[DPL / 2];
 #pragma unroll
-      for (int p = 0; p < NP; ++p) unpack_piece(lds128(vst + tile_off<ROWB>(r, j + 8 * p)), v2 + p * (EPP / 2));
+      for (int p = 0; p < NP; ++p)
+        unpack_piece(lds128(((i & 1) ? vo : ve) + i * 4 * ROWB + p * 128), v2 + p * (EPP / 2));
       if (LAST && !live[i]) continue;  // rows past the end may hold anything, NaN included
 #pragma unroll
       for (int h = 0; h < GH; ++h) {
         const uint64_t p2 = pack2(s[i][h], s[i][h]);
 #pragma unroll
         for (int e = 0; e < DPL / 2; ++e) o2[h][e] = fma2(p2, v2[e], o2[h][e]);
+      }
+    }
+  }
+
+  // ---- the same compute as a per-warp stream (hkb_walk_stream.cuh drives it) ----------
+  static constexpr int HEADS = GH;                       // query heads a warp
+  static constexpr int WPR = 1;                          // warps a ring
+  static constexpr int RING_SMEM = NST * STAGE_BYTES;    // one ring
+  static constexpr int STAGES = NST;
+  static constexpr int HEAD_DIM = D;
+  __host__ __device__ static constexpr int passes(int group) { return (group + GH - 1) / GH; }
+
+  struct State {
+    uint64_t q2[GH][DPL / 2], o2[GH][DPL / 2];
+    float m[GH], l[GH];
+  };
+
+  // Load the query rows of `nh` heads from hq0 on (scaled by qs) and clear the running state.
+  __device__ static __forceinline__ void begin(State& st, const DecodeArgs& a, int row, int hq0, int nh, int lane,
+                                               float qs) {
+    const int j = lane & 7;
+#pragma unroll
+    for (int h = 0; h < GH; ++h) {
+      st.m[h] = -INFINITY; st.l[h] = 0.f;
+      const __nv_bfloat16* qp = a.q + (int64_t)row * a.q_stride_tok + (int64_t)(hq0 + h) * a.q_stride_head;
+#pragma unroll
+      for (int p = 0; p < NP; ++p)
+#pragma unroll
+        for (int e = 0; e < EPP; e += 8) {
+          uint4 x = make_uint4(0, 0, 0, 0);
+          if (h < nh) x = __ldg(reinterpret_cast<const uint4*>(qp + dim_of(j, p, e)));
+          const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) st.q2[h][(p * EPP + e) / 2 + i] = pack2(bf16lo(w[i]) * qs, bf16hi(w[i]) * qs);
+        }
+#pragma unroll
+      for (int e = 0; e < DPL / 2; ++e) st.o2[h][e] = 0ull;
+    }
+  }
+
+  __device__ static __forceinline__ void step(State& st, uint32_t warp_smem, int stage_idx, int tok0, int seq_len,
+                                              bool last, int lane, float /*qs*/) {
+    const uint32_t stage = warp_smem + stage_idx * STAGE_BYTES;
+    if (last) tile<true>(stage, tok0, seq_len, lane >> 3, lane & 7, st.q2, st.m, st.l, st.o2);
+    else tile<false>(stage, tok0, seq_len, lane >> 3, lane & 7, st.q2, st.m, st.l, st.o2);
+  }
+
+  // Fold the warp's four 8-lane streams with shuffles and write the normalised partial of
+  // `nh` heads to po[h * D + d] and its natural-log lse to pl[h].
+  __device__ static __forceinline__ void end(const State& st, int lane, int nh, float vs, float* po, float* pl) {
+    const int g = lane >> 3, j = lane & 7;
+#pragma unroll
+    for (int h = 0; h < GH; ++h) {
+      float mm = fmaxf(st.m[h], __shfl_xor_sync(0xffffffffu, st.m[h], 8));
+      mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 16));
+      const float w = (st.m[h] == -INFINITY) ? 0.f : fast_exp2(st.m[h] - mm);
+      float lt = st.l[h] * w;
+      lt += __shfl_xor_sync(0xffffffffu, lt, 8);
+      lt += __shfl_xor_sync(0xffffffffu, lt, 16);
+      const float inv = lt > 0.f ? vs / lt : 0.f;
+      float o[DPL];
+#pragma unroll
+      for (int e = 0; e < DPL / 2; ++e) {
+        float x0, x1;
+        unpack2(st.o2[h][e], x0, x1);
+        x0 *= w; x1 *= w;
+        x0 += __shfl_xor_sync(0xffffffffu, x0, 8); x1 += __shfl_xor_sync(0xffffffffu, x1, 8);
+        x0 += __shfl_xor_sync(0xffffffffu, x0, 16); x1 += __shfl_xor_sync(0xffffffffu, x1, 16);
+        o[2 * e] = x0 * inv; o[2 * e + 1] = x1 * inv;
+      }
+      if (g == 0 && h < nh) {
+#pragma unroll
+        for (int p = 0; p < NP; ++p)
+#pragma unroll
+          for (int e = 0; e < EPP; e += 4)
+            *reinterpret_cast<float4*>(po + h * D + dim_of(j, p, e)) =
+                make_float4(o[p * EPP + e], o[p * EPP + e + 1], o[p * EPP + e + 2], o[p * EPP + e + 3]);
+        if (j == 0) pl[h] = lt > 0.f ? (mm + log2f(lt)) * LN2 : -INFINITY;
       }
     }
   }
@@ -202,6 +312,7 @@ struct WalkCC {
     ld.ksb = a.k_stride_block; ld.kst = a.k_stride_token;
     ld.vsb = a.v_stride_block; ld.vst = a.v_stride_token;
     ld.tiles_per_page = a.tiles_per_page; ld.num_blocks = a.num_blocks;
+    ld.prepare(lane);
     PageIds ids;
     ids.row = a.block_table + (int64_t)seq * a.table_stride;
     ids.max_pages = a.max_pages; ids.tiles_per_page = a.tiles_per_page; ids.t_hi = t_hi;
@@ -267,6 +378,17 @@ struct WalkCC {
       }
     }
   }
+};
+
+// The stream's CUDA-core worker: a ring shared by WPR_ warps, each holding GW query heads of
+// the kv head (registers for 2 heads instead of 4 let twice the warps live on an SM, which is
+// what hides this path's dependent-issue latency); warp 0 of the ring fills the K tiles, warp
+// 1 the V tiles.
+template <int D, bool FP8, int GW, int WPR_, int NST>
+struct StreamCC : WalkCC<D, FP8, GW, 1, NST> {
+  static constexpr int WPR = WPR_;
+  static constexpr int PASS_HEADS = GW * WPR_;          // query heads a ring serves a pass
+  __host__ __device__ static constexpr int passes(int group) { return (group + PASS_HEADS - 1) / PASS_HEADS; }
 };
 
 template <int D, bool FP8, int GH, int WARPS, int NST>

@@ -52,7 +52,7 @@ struct WalkMMA {
   static constexpr int TILE16_BYTES = TILE_TOKENS * ROWB16;
   static constexpr int WIDEN_BYTES = FP8 ? 2 * TILE16_BYTES : 0;  // per warp
   static constexpr int KD = D / 16;       // 16-wide chunks of head_dim
-  static constexpr int HEADS = NT * 8;
+  static constexpr int HEADS = NT * 8;          // query heads a CTA pass holds columns for
   static constexpr int PIPE_BYTES = WARPS * (NST * STAGE_BYTES + WIDEN_BYTES);
   static constexpr int FOLD_BYTES = WARPS * HEADS * (D + 2) * 4;
   static constexpr int SMEM_BYTES = PIPE_BYTES > FOLD_BYTES ? PIPE_BYTES : FOLD_BYTES;
@@ -162,6 +162,81 @@ struct WalkMMA {
     }
   }
 
+  // ---- the same compute as a per-warp stream (hkb_walk_stream.cuh drives it) ----------
+  static constexpr int RING_SMEM = NST * STAGE_BYTES + WIDEN_BYTES;
+  static constexpr int WPR = 1;                 // warps a ring
+  static constexpr int PASS_HEADS = HEADS;      // query heads a ring serves a pass
+  static constexpr int STAGES = NST;
+  static constexpr int HEAD_DIM = D;
+  __host__ __device__ static constexpr int passes(int) { return 1; }
+
+  struct State {
+    uint32_t qb[NT][KD][2];
+    float m[NT][2], l[NT][2], o[NT][KD][4];
+  };
+
+  __device__ static __forceinline__ void begin(State& st, const DecodeArgs& a, int row, int hq0, int nh, int lane,
+                                               float /*qs*/) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int h = nt * 8 + (lane >> 2);
+      const uint32_t* qp = reinterpret_cast<const uint32_t*>(
+          a.q + (int64_t)row * a.q_stride_tok + (int64_t)(hq0 + h) * a.q_stride_head);
+#pragma unroll
+      for (int kc = 0; kc < KD; ++kc) {
+        st.qb[nt][kc][0] = h < nh ? __ldg(qp + kc * 8 + (lane & 3)) : 0u;
+        st.qb[nt][kc][1] = h < nh ? __ldg(qp + kc * 8 + 4 + (lane & 3)) : 0u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) st.o[nt][kc][i] = 0.f;
+      }
+      st.m[nt][0] = st.m[nt][1] = -INFINITY;
+      st.l[nt][0] = st.l[nt][1] = 0.f;
+    }
+  }
+
+  __device__ static __forceinline__ void step(State& st, uint32_t warp_smem, int stage_idx, int tok0, int seq_len,
+                                              bool last, int lane, float qs) {
+    const uint32_t stage = warp_smem + stage_idx * STAGE_BYTES;
+    uint32_t ktile = stage, vtile = stage + Loader::TILE_BYTES;
+    if (FP8) {
+      const uint32_t wide = warp_smem + NST * STAGE_BYTES;
+      widen(stage, wide, lane);
+      widen(stage + Loader::TILE_BYTES, wide + TILE16_BYTES, lane);
+      ktile = wide; vtile = wide + TILE16_BYTES;
+      __syncwarp();
+    }
+    if (last) {
+      scrub_tail(vtile, tok0, seq_len, lane);
+      __syncwarp();
+      tile<true>(ktile, vtile, tok0, seq_len, lane, qs, st.qb, st.m, st.l, st.o);
+    } else {
+      tile<false>(ktile, vtile, tok0, seq_len, lane, qs, st.qb, st.m, st.l, st.o);
+    }
+  }
+
+  // The warp is one online-softmax stream: complete l over the 8 row groups and write the
+  // normalised partial of `nh` heads to po[h * D + d] and its natural-log lse to pl[h].
+  __device__ static __forceinline__ void end(const State& st, int lane, int nh, float vs, float* po, float* pl) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float lt = st.l[nt][c];
+#pragma unroll
+        for (int x = 4; x < 32; x <<= 1) lt += __shfl_xor_sync(0xffffffffu, lt, x);
+        const int h = nt * 8 + 2 * (lane & 3) + c;
+        const float inv = lt > 0.f ? vs / lt : 0.f;
+        if (h < nh) {
+#pragma unroll
+          for (int dt = 0; dt < KD; ++dt) {
+            po[h * D + dt * 16 + (lane >> 2)] = st.o[nt][dt][c] * inv;
+            po[h * D + dt * 16 + 8 + (lane >> 2)] = st.o[nt][dt][c + 2] * inv;
+          }
+          if ((lane >> 2) == 0) pl[h] = lt > 0.f ? (st.m[nt][c] + log2f(lt)) * LN2 : -INFINITY;
+        }
+      }
+  }
+
   __device__ static __forceinline__ void run(const DecodeArgs& a, uint8_t* smem) {
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
     const int nh = a.group;  // <= HEADS
@@ -225,6 +300,7 @@ struct WalkMMA {
     ld.ksb = a.k_stride_block; ld.kst = a.k_stride_token;
     ld.vsb = a.v_stride_block; ld.vst = a.v_stride_token;
     ld.tiles_per_page = a.tiles_per_page; ld.num_blocks = a.num_blocks;
+    ld.prepare(lane);
     PageIds ids;
     ids.row = a.block_table + (int64_t)seq * a.table_stride;
     ids.max_pages = a.max_pages; ids.tiles_per_page = a.tiles_per_page; ids.t_hi = t_hi;

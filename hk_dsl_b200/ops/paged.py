@@ -26,7 +26,6 @@ the kernels do not take raises.
 
 from __future__ import annotations
 
-import math
 import os
 from typing import Optional, Tuple
 
@@ -339,19 +338,23 @@ def plan_splits(n_reqs: int, n_kv_heads: int, n_pages: int, device=None) -> int:
     if forced in ("auto", "plan"):
         return plan_splits_for(n_reqs, n_kv_heads, n_pages, sm_count(device))
     want = max(1, min(int(forced), max(1, n_pages), MAX_SPLITS))
-    return 1 << int(math.floor(math.log2(want)))
+    return 1 << (want.bit_length() - 1)
 
 
 def plan_splits_for(n_reqs: int, n_kv_heads: int, n_pages: int, sms: int) -> int:
-    """The planner's rule in Python, equal to hkb_plan_splits (tests hold them together):
-    ceil(target / (requests x kv heads)) with target = 8 CTAs an SM, at least 8 tiles a
-    split, at most MAX_SPLITS, rounded down to a power of two."""
+    """The planner's rule in Python, equal to hkb_plan_splits (tests hold them together): the
+    partial slots a sequence gets. The tiles of all sequences of a kv head are dealt in equal
+    shares to the W warps serving that head (two four-warp CTAs an SM, divided among the heads);
+    1 + 8 W / n slots keep a sequence up to 8x the mean from limiting the shares; capped by the
+    pieces the longest allowed sequence can have (8 tiles a piece) and MAX_SPLITS; a power of two."""
     sms = sms if sms > 0 else 148
-    have = max(1, n_reqs) * max(1, n_kv_heads)
-    want = -(-(sms * 8) // have)
-    cap = min(MAX_SPLITS, -(-n_pages // 8) if n_pages > 0 else 1)
-    want = max(1, min(want, cap))
-    return 1 << (want.bit_length() - 1)
+    n = max(1, n_reqs)
+    w = max(1, (sms * 2) // max(1, n_kv_heads)) * 4
+    want = 1 + -(-(8 * w) // n)
+    cap = -(-n_pages // 8) + 1 if n_pages > 0 else 2
+    want = max(2, min(want, cap))
+    p = 1 << (want - 1).bit_length()
+    return min(p, MAX_SPLITS)
 
 
 #: Shapes check_decode has passed (python/hk/ops/paged.py:805-825).

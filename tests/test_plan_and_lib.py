@@ -61,10 +61,11 @@ def test_plans_are_powers_of_two_and_few(monkeypatch):
     assert all(p & (p - 1) == 0 and 1 <= p <= paged.MAX_SPLITS for p in plans)
     assert len(set(plans)) <= 9
     assert plans == sorted(plans, reverse=True)                 # fewer requests, more splits
-    assert paged.plan_splits_for(512, 8, 2560, 148) == 1
-    # never more splits than 8-tile chunks of the longest sequence
-    assert paged.plan_splits_for(1, 1, 16, 148) <= 2
-    assert paged.plan_splits_for(1, 1, 1, 148) == 1
+    assert paged.plan_splits_for(512, 8, 2560, 148) == 4
+    assert paged.plan_splits_for(64, 8, 2560, 148) == 32 and paged.plan_splits_for(2, 8, 8192, 148) == 256
+    # never (many) more slots than 8-tile pieces of the longest sequence allowed
+    assert paged.plan_splits_for(1, 1, 16, 148) <= 4
+    assert paged.plan_splits_for(1, 1, 1, 148) == 2
 
 
 def test_c_planner_equals_python_planner():
