@@ -187,7 +187,13 @@ static int dispatch_cc(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
       return launch_stream<walk_stream_kernel<P, RINGS>>(WalkStream<P, RINGS>::SMEM_BYTES, WalkStream<P, RINGS>::THREADS,
                                                          stream_grid(a.num_kv_heads * P::passes(a.group)), a, num_seqs, st);
     }
-    using P = StreamCC<D, FP8, 4, 1, NST>;
+    static const bool butterfly = [] { const char* v = std::getenv("HKB_CC_RING"); return v && v[0] == 'b'; }();
+    if (butterfly) {   // the butterfly-reduction form of the same worker, kept for A/B measurements
+      using P = StreamCC<D, FP8, 4, 1, NST>;
+      return launch_stream<walk_stream_kernel<P, RINGS>>(WalkStream<P, RINGS>::SMEM_BYTES, WalkStream<P, RINGS>::THREADS,
+                                                         stream_grid(a.num_kv_heads * P::passes(a.group)), a, num_seqs, st);
+    }
+    using P = StreamCC4<D, FP8, NST>;
     return launch_stream<walk_stream_kernel<P, RINGS>>(WalkStream<P, RINGS>::SMEM_BYTES, WalkStream<P, RINGS>::THREADS,
                                                        stream_grid(a.num_kv_heads * P::passes(a.group)), a, num_seqs, st);
   }

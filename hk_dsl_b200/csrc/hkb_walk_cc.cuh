@@ -36,6 +36,7 @@ struct WalkCC {
   static constexpr int FOLD_BYTES = STREAMS * GH * (D + 2) * 4;
   static constexpr int SMEM_BYTES = PIPE_BYTES > FOLD_BYTES ? PIPE_BYTES : FOLD_BYTES;
   static_assert(NP >= 1, "a row must be at least 128 bytes");
+  static constexpr float RESCALE_LOG2 = 8.f;   // how far a tile's maximum may exceed the reference
 
   // head_dim index of element e of piece p for lane-in-group j
   __device__ static __forceinline__ int dim_of(int j, int p, int e) { return (j + 8 * p) * EPP + e; }
@@ -116,31 +117,34 @@ struct WalkCC {
 #pragma unroll
         for (int h = 0; h < GH; ++h) s[i][h] = -INFINITY;
     }
-    // online softmax of this stream: new maxima of all heads first, then ONE branch for the
-    // (rare, after the first tiles) rescale of the running sums
-    float m_use[GH];
+    // online softmax of this stream with a LAZY reference: m[h] is the reference the running
+    // sums are scaled to, not the exact running maximum. It moves (and the sums are rescaled,
+    // all heads in ONE branch) only when a tile's maximum exceeds it by more than 2^RESCALE_LOG2,
+    // so after a stream's first tiles the branch is almost never taken; until then
+    // probabilities are at most 2^RESCALE_LOG2, far inside fp32. out = O / l is unchanged.
     bool moved = false;
+    float mx[GH];
 #pragma unroll
     for (int h = 0; h < GH; ++h) {
-      const float m_new = fmaxf(m[h], fmaxf(fmaxf(s[0][h], s[1][h]), fmaxf(s[2][h], s[3][h])));
-      moved |= m_new != m[h];
-      m_use[h] = m_new;
+      mx[h] = fmaxf(fmaxf(s[0][h], s[1][h]), fmaxf(s[2][h], s[3][h]));
+      moved |= mx[h] > m[h] + RESCALE_LOG2;
     }
     if (moved) {
 #pragma unroll
       for (int h = 0; h < GH; ++h) {
-        const float safe = (m_use[h] == -INFINITY) ? 0.f : m_use[h];   // nothing seen yet: keep exp2 finite
-        const float alpha = fast_exp2(m[h] - safe);                    // 1 for a head whose maximum stayed
+        const float m_new = fmaxf(m[h], mx[h]);
+        const float safe = (m_new == -INFINITY) ? 0.f : m_new;   // nothing seen yet: keep exp2 finite
+        const float alpha = fast_exp2(m[h] - safe);              // 1 for a head whose reference stays
         l[h] *= alpha;
         const uint64_t a2 = pack2(alpha, alpha);
 #pragma unroll
         for (int e = 0; e < DPL / 2; ++e) o2[h][e] = mul2(o2[h][e], a2);
-        m[h] = m_use[h];
+        m[h] = m_new;
       }
     }
 #pragma unroll
     for (int h = 0; h < GH; ++h) {
-      const float safe = (m_use[h] == -INFINITY) ? 0.f : m_use[h];
+      const float safe = (m[h] == -INFINITY) ? 0.f : m[h];
       float sum = 0.f;
 #pragma unroll
       for (int i = 0; i < 4; ++i) { s[i][h] = fast_exp2(s[i][h] - safe); sum += s[i][h]; }
@@ -324,13 +328,16 @@ struct WalkCC {
       if (k < n) ld.issue(ring + k * STAGE_BYTES, t_lo + k, ids.get(t_lo + k, lane), lane);
       cp_async_commit();
     }
+    int sc = 0, sl = NST - 1;   // ring stages of the compute and of the loader
     for (int k = 0; k < n; ++k) {
       cp_async_wait<NST - 2>();
       __syncwarp();
       const int kn = k + NST - 1;
-      if (kn < n) ld.issue(ring + (kn % NST) * STAGE_BYTES, t_lo + kn, ids.get(t_lo + kn, lane), lane);
+      if (kn < n) ld.issue(ring + sl * STAGE_BYTES, t_lo + kn, ids.get(t_lo + kn, lane), lane);
       cp_async_commit();
-      const uint32_t stage = ring + (k % NST) * STAGE_BYTES;
+      const uint32_t stage = ring + sc * STAGE_BYTES;
+      sc = sc + 1 == NST ? 0 : sc + 1;
+      sl = sl + 1 == NST ? 0 : sl + 1;
       const int t = t_lo + k;
       if (t == n_tiles - 1) tile<true>(stage, t * TILE_TOKENS, seq_len, g, j, q2, m, l, o2);
       else tile<false>(stage, t * TILE_TOKENS, seq_len, g, j, q2, m, l, o2);
@@ -389,6 +396,189 @@ struct StreamCC : WalkCC<D, FP8, GW, 1, NST> {
   static constexpr int WPR = WPR_;
   static constexpr int PASS_HEADS = GW * WPR_;          // query heads a ring serves a pass
   __host__ __device__ static constexpr int passes(int group) { return (group + PASS_HEADS - 1) / PASS_HEADS; }
+};
+
+// The stream's worker for four query heads a kv head (the GQA-4 shapes): WalkCC's tile with the
+// dot products completed by a TRANSPOSED reduction instead of a butterfly.
+//
+// A butterfly leaves all 16 (token, head) scores of a step in all 8 lanes of a group: 48
+// shuffles, and every lane repeats the same softmax arithmetic. Here each exchange halves what
+// a lane keeps -- 8, 4, 2 values over the xor-4, xor-2, xor-1 partners: 14 shuffles -- so a lane
+// ends with the two scores of ONE token for ONE pair of heads, does the softmax for those two,
+// and the 16 probabilities the P V product needs come back with 14 shuffles. To make "keep one
+// half, send the other" a compile-time register choice, a lane's register order is permuted
+// by its own lane bits: token register i holds token i ^ (j >> 1) of the step, head register hh
+// holds head hh ^ (2 (j & 1)). The reference maximum m and the partial sum l are kept per lane
+// for its own head pair (2 (j & 1), 2 (j & 1) + 1) and its own token slot.
+template <int D, bool FP8, int NST>
+struct StreamCC4 : WalkCC<D, FP8, 4, 1, NST> {
+  using B = WalkCC<D, FP8, 4, 1, NST>;
+  static constexpr int WPR = 1;
+  static constexpr int PASS_HEADS = 4;
+  static constexpr int DPL = B::DPL, NP = B::NP, EPP = B::EPP, ROWB = B::ROWB;
+  __host__ __device__ static constexpr int passes(int group) { return (group + 3) / 4; }
+
+  struct State {
+    uint64_t q2[4][DPL / 2], o2[4][DPL / 2];
+    float m[2], l[2];
+    uint32_t rowoff[4];   // shared-memory offset of token register i's first piece inside a tile
+  };
+
+  __device__ static __forceinline__ void begin(State& st, const DecodeArgs& a, int row, int hq0, int nh, int lane,
+                                               float qs) {
+    const int g = lane >> 3, j = lane & 7;
+#pragma unroll
+    for (int hh = 0; hh < 4; ++hh) {
+      const int ha = hh ^ (2 * (j & 1));
+      const __nv_bfloat16* qp = a.q + (int64_t)row * a.q_stride_tok + (int64_t)(hq0 + ha) * a.q_stride_head;
+#pragma unroll
+      for (int p = 0; p < NP; ++p)
+#pragma unroll
+        for (int e = 0; e < EPP; e += 8) {
+          uint4 x = make_uint4(0, 0, 0, 0);
+          if (ha < nh) x = __ldg(reinterpret_cast<const uint4*>(qp + B::dim_of(j, p, e)));
+          const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) st.q2[hh][(p * EPP + e) / 2 + i] = pack2(bf16lo(w[i]) * qs, bf16hi(w[i]) * qs);
+        }
+#pragma unroll
+      for (int e = 0; e < DPL / 2; ++e) st.o2[hh][e] = 0ull;
+    }
+    st.m[0] = st.m[1] = -INFINITY;
+    st.l[0] = st.l[1] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) st.rowoff[i] = tile_off<ROWB>(4 * (i ^ (j >> 1)) + g, j);
+  }
+
+  template <bool LAST>
+  __device__ static __forceinline__ void tile4(State& st, uint32_t stage, int tok0, int seq_len, int lane) {
+    const int g = lane >> 3, j = lane & 7;
+    float s[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint64_t k2[DPL / 2];
+#pragma unroll
+      for (int p = 0; p < NP; ++p) B::unpack_piece(lds128(stage + st.rowoff[i] + p * 128), k2 + p * (EPP / 2));
+#pragma unroll
+      for (int hh = 0; hh < 4; ++hh) {
+        uint64_t acc = 0ull;
+#pragma unroll
+        for (int e = 0; e < DPL / 2; ++e) acc = fma2(k2[e], st.q2[hh][e], acc);
+        float a0, a1;
+        unpack2(acc, a0, a1);
+        s[i][hh] = a0 + a1;
+      }
+    }
+    // transposed reduction over the 8 lanes: keep the low half of the registers, send the high half
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int hh = 0; hh < 4; ++hh) s[i][hh] += __shfl_xor_sync(0xffffffffu, s[i + 2][hh], 4);
+#pragma unroll
+    for (int hh = 0; hh < 4; ++hh) s[0][hh] += __shfl_xor_sync(0xffffffffu, s[1][hh], 2);
+    float sa = s[0][0] + __shfl_xor_sync(0xffffffffu, s[0][2], 1);
+    float sb = s[0][1] + __shfl_xor_sync(0xffffffffu, s[0][3], 1);
+    // sa, sb: token (j >> 1) of the step, heads 2 (j & 1) and 2 (j & 1) + 1
+    if (LAST && tok0 + 4 * (j >> 1) + g >= seq_len) { sa = -INFINITY; sb = -INFINITY; }
+    float ma = fmaxf(sa, __shfl_xor_sync(0xffffffffu, sa, 2));
+    float mb = fmaxf(sb, __shfl_xor_sync(0xffffffffu, sb, 2));
+    ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, 4));
+    mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 4));
+    // lazy reference (see WalkCC::tile): one warp-uniform branch for the rare rescale
+    const bool moved = ma > st.m[0] + B::RESCALE_LOG2 || mb > st.m[1] + B::RESCALE_LOG2;
+    if (__any_sync(0xffffffffu, moved)) {
+      const float na = fmaxf(st.m[0], ma), nb = fmaxf(st.m[1], mb);
+      const float al_a = fast_exp2(st.m[0] - ((na == -INFINITY) ? 0.f : na));
+      const float al_b = fast_exp2(st.m[1] - ((nb == -INFINITY) ? 0.f : nb));
+      st.l[0] *= al_a; st.l[1] *= al_b;
+      st.m[0] = na; st.m[1] = nb;
+      const float al[4] = {al_a, al_b, __shfl_xor_sync(0xffffffffu, al_a, 1), __shfl_xor_sync(0xffffffffu, al_b, 1)};
+#pragma unroll
+      for (int hh = 0; hh < 4; ++hh) {
+        const uint64_t a2 = pack2(al[hh], al[hh]);
+#pragma unroll
+        for (int e = 0; e < DPL / 2; ++e) st.o2[hh][e] = mul2(st.o2[hh][e], a2);
+      }
+    }
+    const float pa = fast_exp2(sa - ((st.m[0] == -INFINITY) ? 0.f : st.m[0]));
+    const float pb = fast_exp2(sb - ((st.m[1] == -INFINITY) ? 0.f : st.m[1]));
+    st.l[0] += pa;
+    st.l[1] += pb;
+    // O += P V: the probabilities of this lane's token registers come from the lanes that own them
+    const uint32_t vst = stage + B::Loader::TILE_BYTES;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint64_t v2[DPL / 2];
+#pragma unroll
+      for (int p = 0; p < NP; ++p) B::unpack_piece(lds128(vst + st.rowoff[i] + p * 128), v2 + p * (EPP / 2));
+      float pr[4];
+#pragma unroll
+      for (int hh = 0; hh < 4; ++hh)
+        pr[hh] = (i == 0 && hh < 2) ? ((hh & 1) ? pb : pa)
+                                    : __shfl_xor_sync(0xffffffffu, (hh & 1) ? pb : pa, (i << 1) | (hh >> 1));
+      if (LAST && tok0 + 4 * (i ^ (j >> 1)) + g >= seq_len) continue;   // rows past the end may hold NaN
+#pragma unroll
+      for (int hh = 0; hh < 4; ++hh) {
+        const uint64_t p2 = pack2(pr[hh], pr[hh]);
+#pragma unroll
+        for (int e = 0; e < DPL / 2; ++e) st.o2[hh][e] = fma2(p2, v2[e], st.o2[hh][e]);
+      }
+    }
+  }
+
+  __device__ static __forceinline__ void step(State& st, uint32_t warp_smem, int stage_idx, int tok0, int seq_len,
+                                              bool last, int lane, float /*qs*/) {
+    const uint32_t stage = warp_smem + stage_idx * B::STAGE_BYTES;
+    if (last) tile4<true>(st, stage, tok0, seq_len, lane);
+    else tile4<false>(st, stage, tok0, seq_len, lane);
+  }
+
+  // Fold the 4 token slots of a group and the warp's 4 groups, write the normalised partial.
+  __device__ static __forceinline__ void end(const State& st, int lane, int nh, float vs, float* po, float* pl) {
+    const int g = lane >> 3, j = lane & 7;
+    float w[2], lt[2], mm[2];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      mm[c] = fmaxf(st.m[c], __shfl_xor_sync(0xffffffffu, st.m[c], 8));
+      mm[c] = fmaxf(mm[c], __shfl_xor_sync(0xffffffffu, mm[c], 16));
+      w[c] = (st.m[c] == -INFINITY) ? 0.f : fast_exp2(st.m[c] - mm[c]);
+      lt[c] = st.l[c] * w[c];
+#pragma unroll
+      for (int x = 2; x < 32; x <<= 1) lt[c] += __shfl_xor_sync(0xffffffffu, lt[c], x);   // token slots, then groups
+    }
+    const float wh[4] = {w[0], w[1], __shfl_xor_sync(0xffffffffu, w[0], 1), __shfl_xor_sync(0xffffffffu, w[1], 1)};
+    const float lh[4] = {lt[0], lt[1], __shfl_xor_sync(0xffffffffu, lt[0], 1), __shfl_xor_sync(0xffffffffu, lt[1], 1)};
+#pragma unroll
+    for (int hh = 0; hh < 4; ++hh) {
+      const int ha = hh ^ (2 * (j & 1));
+      const float inv = lh[hh] > 0.f ? vs / lh[hh] : 0.f;
+      float o[DPL];
+#pragma unroll
+      for (int e = 0; e < DPL / 2; ++e) {
+        float x0, x1;
+        unpack2(st.o2[hh][e], x0, x1);
+        x0 *= wh[hh]; x1 *= wh[hh];
+        x0 += __shfl_xor_sync(0xffffffffu, x0, 8); x1 += __shfl_xor_sync(0xffffffffu, x1, 8);
+        x0 += __shfl_xor_sync(0xffffffffu, x0, 16); x1 += __shfl_xor_sync(0xffffffffu, x1, 16);
+        o[2 * e] = x0 * inv; o[2 * e + 1] = x1 * inv;
+      }
+      if (g == 0 && ha < nh) {
+#pragma unroll
+        for (int p = 0; p < NP; ++p)
+#pragma unroll
+          for (int e = 0; e < EPP; e += 4)
+            *reinterpret_cast<float4*>(po + ha * D + B::dim_of(j, p, e)) =
+                make_float4(o[p * EPP + e], o[p * EPP + e + 1], o[p * EPP + e + 2], o[p * EPP + e + 3]);
+      }
+    }
+    if (g == 0 && (j >> 1) == 0) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int ha = 2 * (j & 1) + c;
+        if (ha < nh) pl[ha] = lt[c] > 0.f ? (mm[c] + log2f(lt[c])) * LN2 : -INFINITY;
+      }
+    }
+  }
 };
 
 template <int D, bool FP8, int GH, int WARPS, int NST>

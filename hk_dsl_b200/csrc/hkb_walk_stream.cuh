@@ -136,7 +136,7 @@ struct WalkStream {
     // loader cursor (each warp of the ring keeps its own and issues its share of every tile)
     int seq_l = lo, gl = g_lo;
     bool fresh = true;
-    auto issue = [&](int k) {
+    auto issue = [&](int stage_idx) {
       while (gl >= base[seq_l + 1]) { ++seq_l; fresh = true; }
       const int t = gl - base[seq_l];
       if (fresh) {
@@ -145,7 +145,7 @@ struct WalkStream {
         ids.init(t, lane);
         fresh = false;
       }
-      const uint32_t stage = ring + (k % P::STAGES) * P::STAGE_BYTES;
+      const uint32_t stage = ring + stage_idx * P::STAGE_BYTES;
       if (WPR == 1) ld.issue(stage, t, ids.get(t, lane), lane);
       else ld.issue_one(stage, t, ids.get(t, lane), lane, sub);
       ++gl;
@@ -160,10 +160,11 @@ struct WalkStream {
     // compute cursor
     typename P::State st;
     int seq_c = -1, seq_end = g_lo, seq_len = 0, n_tiles = 0, seq_base = 0;
+    int sc = 0, sl = P::STAGES - 1;   // ring stages of the compute and of the loader
     for (int k = 0; k < n; ++k) {
       cp_async_wait<P::STAGES - 2>();
       ring_sync<WPR>(ring_id);
-      if (k + P::STAGES - 1 < n) issue(k + P::STAGES - 1);
+      if (k + P::STAGES - 1 < n) issue(sl);
       cp_async_commit();
       const int g = g_lo + k;
       if (g >= seq_end) {
@@ -182,7 +183,9 @@ struct WalkStream {
         if (nh > 0) P::begin(st, a, row, hq0, nh, lane, qs);
       }
       const int t = g - seq_base;
-      if (nh > 0) P::step(st, ring, k % P::STAGES, t * TILE_TOKENS, seq_len, t == n_tiles - 1, lane, qs);
+      if (nh > 0) P::step(st, ring, sc, t * TILE_TOKENS, seq_len, t == n_tiles - 1, lane, qs);
+      sc = sc + 1 == P::STAGES ? 0 : sc + 1;
+      sl = sl + 1 == P::STAGES ? 0 : sl + 1;
     }
     cp_async_wait<0>();
     if (nh > 0) {
