@@ -86,6 +86,9 @@ extern "C" const char* hkb_strerror(int code) {
     case HKB_ERR_SIZE: return "a count is negative or past a launch limit";
     case HKB_ERR_SCALE: return "an fp8 cache needs k_scale and v_scale";
     case HKB_ERR_UNSUPPORTED: return "no kernel for this combination of head_dim, dtype and group";
+    case HKB_ERR_STATIC_SCRATCH:
+      return "the split partials need more than the library's built-in scratch (HKB_STATIC_SCRATCH_BYTES): use fewer "
+             "splits or the caller-scratch entry points";
     case HKB_ERR_CUDA: return "CUDA reported an error at launch (hkb_last_cuda_error)";
     default: return "unknown hkb status";
   }

@@ -5,6 +5,7 @@
 #include "hkb_walk_stream.cuh"
 
 #include <cstdlib>
+#include <mutex>
 
 extern thread_local int hkb_tls_cuda_error;
 
@@ -328,4 +329,77 @@ extern "C" int hkb_merge(void* out, int64_t out_stride_tok, int64_t out_stride_h
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
   return HKB_OK;
+}
+
+// ---------------------------------------------------------------------------------
+// The split decode on scratch built into the library, for callers that cannot allocate.
+// ---------------------------------------------------------------------------------
+// A fixed file-scope device array holds the split partials. The name below is only a
+// host-side handle for the symbol: host code must not pass it to a kernel; the device
+// address comes from cudaGetSymbolAddress, looked up once per device with that device current.
+static __device__ __align__(256) unsigned char hkb_static_scratch[HKB_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+std::mutex g_static_mu;
+void* g_static_ptr[64] = {};
+
+// Device address of the built-in scratch on the current device; nullptr (and the CUDA error
+// recorded) if the lookup fails. No allocation happens here: the array is part of the module.
+void* static_scratch_address() {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    hkb_tls_cuda_error = (int)(e != cudaSuccess ? e : cudaErrorInvalidDevice);
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, hkb_static_scratch);
+    if (e != cudaSuccess || !p) {
+      hkb_tls_cuda_error = (int)e;
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    g_static_ptr[dev] = p;
+  }
+  return g_static_ptr[dev];
+}
+
+}  // namespace
+
+extern "C" int hkb_paged_decode_static(void* out, int64_t out_stride_tok, int64_t out_stride_head,
+                                       const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                                       hkb_cache_t kc, hkb_cache_t vc,
+                                       const int32_t* block_table, int64_t table_stride, int max_pages,
+                                       const int32_t* seq_lens, const int32_t* q_start,
+                                       int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                                       int block_size, float scale, int kv_dtype,
+                                       const float* k_scale, const float* v_scale,
+                                       int num_splits, void* stream) {
+  if (num_splits <= 1)   // one split writes the answer itself: no partials, nothing to hold
+    return hkb_paged_decode(out, out_stride_tok, out_stride_head, q, q_stride_tok, q_stride_head, kc, vc, block_table,
+                            table_stride, max_pages, seq_lens, q_start, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                            block_size, scale, kv_dtype, k_scale, v_scale, num_splits, nullptr, nullptr, stream);
+  if (num_seqs < 0 || num_q_heads <= 0 || head_dim <= 0) return HKB_ERR_SIZE;
+  if (num_seqs == 0) return HKB_OK;
+  if (num_splits > HKB_MAX_SPLITS) return HKB_ERR_SPLITS;
+  const size_t need = hkb_scratch_bytes(num_seqs, num_q_heads, head_dim, num_splits);
+  if (need == 0 || need > (size_t)HKB_STATIC_SCRATCH_BYTES) return HKB_ERR_STATIC_SCRATCH;
+  unsigned char* base = static_cast<unsigned char*>(static_scratch_address());
+  if (!base) return HKB_ERR_CUDA;
+  float* part_out = reinterpret_cast<float*>(base);
+  float* part_lse = reinterpret_cast<float*>(base + hkb_scratch_lse_offset(num_seqs, num_q_heads, head_dim, num_splits));
+  // The walk rewrites the lse of every (sequence, slot, head) before the merge reads any of
+  // them -- a value, or -inf for a slot without tokens -- so what the last call left behind
+  // in the array is never read and nothing needs clearing first.
+  int rc = hkb_paged_decode(out, out_stride_tok, out_stride_head, q, q_stride_tok, q_stride_head, kc, vc, block_table,
+                            table_stride, max_pages, seq_lens, q_start, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                            block_size, scale, kv_dtype, k_scale, v_scale, num_splits, part_out, part_lse, stream);
+  if (rc != HKB_OK) return rc;
+  return hkb_merge(out, out_stride_tok, out_stride_head, 0, nullptr, part_out, (int64_t)num_q_heads * head_dim,
+                   (int64_t)num_splits * num_q_heads * head_dim, part_lse, num_q_heads,
+                   (int64_t)num_splits * num_q_heads, num_splits, num_seqs, num_q_heads, head_dim, seq_lens, q_start,
+                   stream);
 }

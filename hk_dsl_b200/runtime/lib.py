@@ -20,6 +20,8 @@ KV_BF16 = 0
 KV_FP8_E4M3 = 1
 MAX_SPLITS = 256
 MAX_GROUP = 16
+STATIC_SCRATCH_BYTES = 8 << 20
+ERR_STATIC_SCRATCH = -12
 ERR_CUDA = -100
 
 
@@ -47,6 +49,9 @@ SIGNATURES = {
                                  c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                  c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                  c_void_p]),
+    "hkb_paged_decode_static": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, CacheT, CacheT,
+                                        c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                        c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "hkb_merge": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p,
                           c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "hkb_plan_splits": (c_int, [c_int, c_int, c_int, c_int]),

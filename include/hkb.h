@@ -9,10 +9,11 @@
  * Conventions that hold for every entry point
  *   - every pointer is a BORROWED DEVICE pointer of the current CUDA device,
  *     valid until the stream reaches the launch; the library allocates and
- *     frees nothing (one exception, named where it is declared);
+ *     frees nothing;
  *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
- *     stream); launches are asynchronous and never synchronise with the host,
- *     so every call can be captured into a CUDA graph;
+ *     stream); launches are asynchronous and never synchronise with the host;
+ *     hkb_reshape_and_cache, hkb_paged_decode and hkb_merge can be captured into
+ *     a CUDA graph;
  *   - the return value is an hkb_status: 0 on success, a negative code for a
  *     refused argument (nothing was launched), HKB_ERR_CUDA for a CUDA launch
  *     error. Nothing aborts and nothing throws;
@@ -51,6 +52,7 @@ typedef enum {
   HKB_ERR_SIZE = -9,        /* a count is negative or a grid limit is exceeded */
   HKB_ERR_SCALE = -10,      /* fp8 cache without k_scale / v_scale */
   HKB_ERR_UNSUPPORTED = -11,/* a combination this build has no kernel for */
+  HKB_ERR_STATIC_SCRATCH = -12, /* the split partials would not fit the library's built-in scratch */
   HKB_ERR_CUDA = -100       /* CUDA reported an error at launch (see hkb_last_cuda_error) */
 } hkb_status;
 
@@ -159,6 +161,49 @@ int hkb_merge(void* out, int64_t out_stride_tok, int64_t out_stride_head, int ou
               const float* part_lse, int64_t lse_stride_p, int64_t lse_stride_seq,
               int num_parts, int num_seqs, int num_q_heads, int head_dim,
               const int32_t* seq_lens, const int32_t* q_start, void* stream);
+
+/*
+ * Bytes of the scratch array built into the library for hkb_paged_decode_static (below).
+ */
+#define HKB_STATIC_SCRATCH_BYTES (8u << 20)
+
+/*
+ * The split decode for callers that have no device memory to give and no way to get any:
+ * the same walk + merge as hkb_paged_decode followed by hkb_merge, but the split partials
+ * live in a fixed array inside the library instead of caller-owned scratch, and the call
+ * itself allocates and frees nothing (no cudaMalloc, no cudaFree, no allocating library
+ * routine). It has no counterpart in the reference, whose routes always own their scratch.
+ *
+ * Who needs it: a binding that only ever holds the pointers its engine handed it -- a cgo /
+ * JNI / N-API caller with no allocator bridge -- and a serving loop that runs after the engine
+ * has given the whole GPU to its KV-cache pool, where a late cudaMalloc fails or stalls.
+ *
+ * Arguments are those of hkb_paged_decode without part_out / part_lse; `out` receives the
+ * final bf16 answer. num_splits == 1 needs no partials and is passed straight through.
+ *
+ * Limits and rules:
+ *   - the partials need hkb_scratch_bytes(num_seqs, num_q_heads, head_dim, num_splits) bytes;
+ *     more than HKB_STATIC_SCRATCH_BYTES is refused with HKB_ERR_STATIC_SCRATCH and nothing
+ *     is launched -- use fewer splits or the caller-scratch entry points;
+ *   - the array costs HKB_STATIC_SCRATCH_BYTES of device memory on every GPU that loads the
+ *     library, from load until the process exits;
+ *   - the FIRST call on each device looks the array's device address up (with that device
+ *     current); make that first call before any stream capture begins;
+ *   - every call on a device shares the one array and finds the previous call's partials in
+ *     it. Nothing in it has to start at zero: each call first rewrites the lse of every slot
+ *     it may read (a value, or -inf for "unused") and never reads a slot marked unused. Two
+ *     calls that overlap on the GPU (different streams, or threads on one device) race on the
+ *     array: serialise them.
+ */
+int hkb_paged_decode_static(void* out, int64_t out_stride_tok, int64_t out_stride_head,
+                            const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                            hkb_cache_t k_cache, hkb_cache_t v_cache,
+                            const int32_t* block_table, int64_t table_stride, int max_pages,
+                            const int32_t* seq_lens, const int32_t* q_start,
+                            int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                            int block_size, float scale, int kv_dtype,
+                            const float* k_scale, const float* v_scale,
+                            int num_splits, void* stream);
 
 /*
  * Split planner: how many ways to cut the KV axis so that num_seqs*num_kv_heads
