@@ -30,20 +30,17 @@ struct MergeArgs {
   const int* q_start;
 };
 
-// 256 threads = PG part groups x (D/4) dim threads: group g folds parts g, g+PG, ... so that
-// with the usual 2..16 parts every part's loads are in flight at once, then the groups are
-// summed through shared memory.
-constexpr int MERGE_THREADS = 256;
+// One warp a (sequence, q head), 8 heads a CTA. A lane first loads the lse of one part (32 parts
+// a round), the warp votes which parts are live, and only those are read: with the stream's
+// slot layout most of a sequence's `num_parts` slots are marked -inf, so a merge reads two or
+// three partials however many slots there are. Each lane owns head_dim / 32 output columns.
+constexpr int MERGE_WARPS = 8;
 
-__global__ void __launch_bounds__(MERGE_THREADS) merge_kernel(const MergeArgs a) {
-  __shared__ float s_red[MERGE_THREADS / 32];
-  __shared__ float4 s_acc[MERGE_THREADS];
-  __shared__ float s_den[MERGE_THREADS];
-  const int h = blockIdx.x, seq = blockIdx.y;
-  const int dt = a.head_dim / 4;            // dim threads a group
-  const int pg = MERGE_THREADS / dt;        // part groups
-  const int g = threadIdx.x / dt, td = threadIdx.x % dt;
-  const int d = td * 4;
+template <int VEC>   // floats a lane: head_dim / 32
+__global__ void __launch_bounds__(MERGE_WARPS * 32) merge_kernel(const MergeArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.x * MERGE_WARPS + warp, seq = blockIdx.y;
+  if (h >= a.num_q_heads) return;
   int row = seq;
   if (a.q_start) {
     row = __ldg(a.q_start + seq);
@@ -51,54 +48,58 @@ __global__ void __launch_bounds__(MERGE_THREADS) merge_kernel(const MergeArgs a)
   }
   const bool empty = a.seq_lens && __ldg(a.seq_lens + seq) <= 0;
   const float* lse = a.part_lse + (int64_t)seq * a.lse_stride_seq + h;
-  // max lse over the parts: a block-wide reduction
+  const float* po = a.part_out + (int64_t)seq * a.part_stride_seq + (int64_t)h * a.head_dim + lane * VEC;
+
+  // pass 1: the maximum lse over the parts
   float mx = -INFINITY;
   if (!empty)
-    for (int p = threadIdx.x; p < a.num_parts; p += MERGE_THREADS) mx = fmaxf(mx, __ldg(lse + (int64_t)p * a.lse_stride_p));
+    for (int p = lane; p < a.num_parts; p += 32) mx = fmaxf(mx, __ldg(lse + (int64_t)p * a.lse_stride_p));
 #pragma unroll
   for (int x = 16; x > 0; x >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, x));
-  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = mx;
-  __syncthreads();
-  mx = s_red[0];
-#pragma unroll
-  for (int w = 1; w < MERGE_THREADS / 32; ++w) mx = fmaxf(mx, s_red[w]);
 
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float acc[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) acc[v] = 0.f;
   float den = 0.f;
-  if (mx != -INFINITY && g < pg) {
-    const float* po = a.part_out + (int64_t)seq * a.part_stride_seq + (int64_t)h * a.head_dim + d;
-    for (int p = g; p < a.num_parts; p += pg) {
-      const float lp = __ldg(lse + (int64_t)p * a.lse_stride_p);
-      if (lp == -INFINITY) continue;  // an empty part's memory is never read
-      const float w = __expf(lp - mx);
-      const float4 x = __ldg(reinterpret_cast<const float4*>(po + (int64_t)p * a.part_stride_p));
-      acc.x = fmaf(w, x.x, acc.x); acc.y = fmaf(w, x.y, acc.y);
-      acc.z = fmaf(w, x.z, acc.z); acc.w = fmaf(w, x.w, acc.w);
-      den += w;
+  if (mx != -INFINITY) {
+    for (int p0 = 0; p0 < a.num_parts; p0 += 32) {
+      const int p = p0 + lane;
+      const float lp = p < a.num_parts ? __ldg(lse + (int64_t)p * a.lse_stride_p) : -INFINITY;
+      const float w = lp == -INFINITY ? 0.f : __expf(lp - mx);
+      unsigned live = __ballot_sync(0xffffffffu, lp != -INFINITY);   // an empty part's memory is never read
+      while (live) {   // ascending part order: the same bits every call
+        const int src = __ffs(live) - 1;
+        live &= live - 1;
+        const float ws = __shfl_sync(0xffffffffu, w, src);
+        const float* x = po + (int64_t)(p0 + src) * a.part_stride_p;
+        if (VEC == 4) {
+          const float4 t = __ldg(reinterpret_cast<const float4*>(x));
+          acc[0] = fmaf(ws, t.x, acc[0]); acc[1] = fmaf(ws, t.y, acc[1]);
+          acc[2] = fmaf(ws, t.z, acc[2]); acc[3] = fmaf(ws, t.w, acc[3]);
+        } else {
+#pragma unroll
+          for (int v = 0; v < VEC; v += 2) {
+            const float2 t = __ldg(reinterpret_cast<const float2*>(x + v));
+            acc[v] = fmaf(ws, t.x, acc[v]); acc[v + 1] = fmaf(ws, t.y, acc[v + 1]);
+          }
+        }
+        den += ws;
+      }
     }
   }
-  s_acc[threadIdx.x] = acc;
-  s_den[threadIdx.x] = den;
-  __syncthreads();
-  if (g != 0) return;
-  for (int o = 1; o < pg; ++o) {   // fixed order: the same bits every call
-    const float4 x = s_acc[o * dt + td];
-    acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
-    den += s_den[o * dt + td];
-  }
   const float inv = den > 0.f ? 1.f / den : 0.f;
-  acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
-  const int64_t off = (int64_t)row * a.out_stride_tok + (int64_t)h * a.out_stride_head + d;
+  const int64_t off = (int64_t)row * a.out_stride_tok + (int64_t)h * a.out_stride_head + lane * VEC;
   if (a.out_is_f32) {
-    *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + off) = acc;
+    float* o = reinterpret_cast<float*>(a.out) + off;
+#pragma unroll
+    for (int v = 0; v < VEC; v += 2) *reinterpret_cast<float2*>(o + v) = make_float2(acc[v] * inv, acc[v + 1] * inv);
   } else {
-    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
-    uint2 pk;
-    pk.x = *reinterpret_cast<uint32_t*>(&lo);
-    pk.y = *reinterpret_cast<uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.out) + off) = pk;
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out) + off;
+#pragma unroll
+    for (int v = 0; v < VEC; v += 2)
+      *reinterpret_cast<__nv_bfloat162*>(o + v) = __floats2bfloat162_rn(acc[v] * inv, acc[v + 1] * inv);
   }
-  if (a.out_lse && td == 0)
+  if (a.out_lse && lane == 0)
     a.out_lse[(int64_t)row * a.num_q_heads + h] = den > 0.f ? mx + __logf(den) : -INFINITY;
 }
 
@@ -314,7 +315,7 @@ extern "C" int hkb_merge(void* out, int64_t out_stride_tok, int64_t out_stride_h
   if (num_seqs < 0 || num_q_heads <= 0 || num_parts < 1) return HKB_ERR_SIZE;
   if (num_seqs == 0) return HKB_OK;
   if (!out || !part_out || !part_lse) return HKB_ERR_NULL;
-  if (head_dim <= 0 || head_dim % 4 || head_dim > 1024 || (MERGE_THREADS * 4) % head_dim) return HKB_ERR_HEAD_DIM;
+  if (head_dim != 64 && head_dim != 128 && head_dim != 256) return HKB_ERR_HEAD_DIM;
   if (num_seqs > 65535) return HKB_ERR_SIZE;
   if ((part_stride_p | part_stride_seq) % 4 || (out_stride_tok | out_stride_head) % 4) return HKB_ERR_STRIDE;
   if ((uintptr_t)part_out % 16 || (uintptr_t)out % (out_is_f32 ? 16 : 8)) return HKB_ERR_ALIGN;
@@ -325,7 +326,10 @@ extern "C" int hkb_merge(void* out, int64_t out_stride_tok, int64_t out_stride_h
   a.part_lse = part_lse; a.lse_stride_p = lse_stride_p; a.lse_stride_seq = lse_stride_seq;
   a.num_parts = num_parts; a.num_q_heads = num_q_heads; a.head_dim = head_dim;
   a.seq_lens = seq_lens; a.q_start = q_start;
-  merge_kernel<<<dim3(num_q_heads, num_seqs), MERGE_THREADS, 0, (cudaStream_t)stream>>>(a);
+  const dim3 grid((num_q_heads + MERGE_WARPS - 1) / MERGE_WARPS, num_seqs);
+  if (head_dim == 128) merge_kernel<4><<<grid, MERGE_WARPS * 32, 0, (cudaStream_t)stream>>>(a);
+  else if (head_dim == 64) merge_kernel<2><<<grid, MERGE_WARPS * 32, 0, (cudaStream_t)stream>>>(a);
+  else merge_kernel<8><<<grid, MERGE_WARPS * 32, 0, (cudaStream_t)stream>>>(a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
   return HKB_OK;
