@@ -232,3 +232,23 @@ def test_backend_prefill_batches_raise_and_checks_metadata():
         impl._check(torch.zeros(2, 2, dtype=torch.int32), torch.tensor([10, 100], dtype=torch.int32))
     out = torch.ones(3, 8)
     assert impl.forward(None, None, None, None, kv, None, output=out) is out and (out == 0).all()   # profiling run
+
+
+def test_register_with_an_installed_vllm_resolves_to_our_backend():
+    """With vLLM importable, `register()` puts the backend under the chosen enum member and the
+    classes it builds have vLLM's bases and this build's cache shape."""
+    pytest.importorskip("vllm")
+    try:
+        from vllm.v1.attention.backends.registry import AttentionBackendEnum
+    except Exception as e:  # noqa: BLE001 -- another vLLM layout: the plugin would report the route off
+        pytest.skip(f"this vLLM has no v1 backend registry: {e}")
+    msg = vllm_backend.register()
+    assert "registered over CUSTOM" in msg
+    backend = vllm_backend.HKAttentionBackend
+    assert AttentionBackendEnum.CUSTOM.get_path().endswith("vllm_backend.HKAttentionBackend")
+    assert backend.get_name() == "CUSTOM" and backend.get_impl_cls() is vllm_backend.HKAttentionImpl
+    assert backend.get_kv_cache_shape(10, 16, 8, 128) == (2, 10, 8, 16, 128)
+    assert issubclass(vllm_backend.HKAttentionImpl, vllm_backend.HKAttentionImplCore)
+    with pytest.raises(RuntimeError, match="no AttentionBackendEnum"):
+        vllm_backend.register("NOT_A_BACKEND")
+    vllm_backend.register()     # idempotent, and restores the slot name
