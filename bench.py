@@ -238,8 +238,12 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--batch", type=int, default=0,
                     help="keep only the first N sequences of the config (small cases for profiler captures)")
+    ap.add_argument("--table", action="store_true",
+                    help="decode latency (walk + merge, us a layer) over the reference's requests x context grid")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.table:
+        return latency_table()
     if args.impl == "reference":
         return reference_arm(args)
 
@@ -468,6 +472,68 @@ def main():
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    return 0
+
+
+#: us a layer of hk-dsl's own decode on an MI355X (8 TB/s HBM3e), Qwen3-8B's attention shape, from
+#: docs/history/39-cdna-paged.md:163-177 of the reference: (requests, context) -> hk's column.
+REFERENCE_MI355X_US = {(1, 512): 9.2, (1, 1024): 9.1, (1, 4096): 13.5, (1, 8192): 16.1, (4, 1024): 9.9,
+                       (4, 8192): 28.2, (16, 1024): 17.3, (16, 8192): 88.7, (32, 1024): 25.4, (32, 8192): 171.4,
+                       (64, 4096): 167.3, (128, 1024): 84.0, (128, 8192): 659.2}
+
+
+def latency_table():
+    """The reference's kernel-level benchmark of this path (tools/hk-bench/paged_cdna.py decode):
+    32 q / 8 kv heads, head_dim 128, bf16, uniform contexts; walk + merge timed as a CUDA graph
+    whose calls rotate through enough caches to read past L2 (>= 256 MB a cycle), median of 7."""
+    import torch
+
+    from hk_dsl_b200 import workloads as W
+    from hk_dsl_b200.ops import paged
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    rows = []
+    for (reqs, ctx), ref_us in REFERENCE_MI355X_US.items():
+        spec = W.Spec(f"t{reqs}x{ctx}", reqs, 32, 8, dist="fixed", lo=ctx, hi=ctx)
+        kv = spec.kv_bytes([ctx] * reqs)
+        layers = max(2, min(128, -(-(256 << 20) // kv)))
+        st = W.build_step(spec, dev, layers=layers, seed=1)
+        splits = paged.plan_splits(reqs, 8, st.block_table.shape[1], device=dev)
+        scratch = paged.split_scratch(reqs, 32, 128, splits, dev)
+
+        def call(l):
+            paged.paged_attention_decode(st.out, st.query, st.k_caches[l], st.v_caches[l], st.block_table,
+                                         st.seq_lens, st.scale, num_splits=splits, scratch=scratch)
+
+        for l in range(layers):
+            call(l)
+        torch.cuda.synchronize()
+        reps = max(1, 64 // layers)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                for l in range(layers):
+                    call(l)
+        g.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(7):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3 / (reps * layers))
+        us = statistics.median(times)
+        rows.append({"requests": reqs, "context": ctx, "us_per_layer": round(us, 2), "kv_gbs": round(kv / us / 1e3, 1),
+                     "parts": splits, "caches_rotated": layers, "reference_hk_mi355x_us": ref_us,
+                     "reference_over_ours": round(ref_us / us, 2)})
+        del st, scratch, g
+        torch.cuda.empty_cache()
+    print(json.dumps({"table": "decode walk + merge, us a layer, 32q/8kv heads, D128, bf16, block 16, cold KV, "
+                               "CUDA-graph replay, median of 7", "gpu": torch.cuda.get_device_name(dev), "rows": rows}),
+          flush=True)
     return 0
 
 

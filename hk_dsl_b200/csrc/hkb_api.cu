@@ -39,7 +39,7 @@ extern "C" int hkb_sm_count(int device) {
 // CTAs an SM, divided among the heads); a share may not be shorter than longest / (parts - 1),
 // so that no sequence needs more than `parts` slots. With n sequences whose longest is up to
 // 8x the mean, parts = 1 + 8 W / n keeps that bound from limiting the shares. Capped by the
-// pieces the longest allowed sequence can have (8 tiles a piece at least) and HKB_MAX_SPLITS,
+// pieces the longest allowed sequence can usefully have (2 tiles a piece) and HKB_MAX_SPLITS,
 // rounded up to a power of two: a function of host values only, so a captured graph's plan is
 // right for every replay. hk-dsl's rule has the same shape -- ceil(target / (requests * kv
 // heads)), capped by pages and a maximum (python/hk/ops/paged.py:838-914) -- with AMD's target.
@@ -51,7 +51,7 @@ extern "C" int hkb_plan_splits(int num_seqs, int num_kv_heads, int max_tiles, in
   if (per < 1) per = 1;
   const long long w = per * 4;
   long long want = 1 + (8 * w + n - 1) / n;
-  const long long cap = max_tiles > 0 ? (max_tiles + 7) / 8 + 1 : 2;
+  const long long cap = max_tiles > 0 ? (max_tiles + 1) / 2 + 1 : 2;
   if (want > cap) want = cap;
   if (want < 2) want = 2;
   long long p = 2;

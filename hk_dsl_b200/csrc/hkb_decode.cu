@@ -67,25 +67,117 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_kernel(const MergeArgs
       const float lp = p < a.num_parts ? __ldg(lse + (int64_t)p * a.lse_stride_p) : -INFINITY;
       const float w = lp == -INFINITY ? 0.f : __expf(lp - mx);
       unsigned live = __ballot_sync(0xffffffffu, lp != -INFINITY);   // an empty part's memory is never read
-      while (live) {   // ascending part order: the same bits every call
-        const int src = __ffs(live) - 1;
-        live &= live - 1;
-        const float ws = __shfl_sync(0xffffffffu, w, src);
-        const float* x = po + (int64_t)(p0 + src) * a.part_stride_p;
-        if (VEC == 4) {
-          const float4 t = __ldg(reinterpret_cast<const float4*>(x));
-          acc[0] = fmaf(ws, t.x, acc[0]); acc[1] = fmaf(ws, t.y, acc[1]);
-          acc[2] = fmaf(ws, t.z, acc[2]); acc[3] = fmaf(ws, t.w, acc[3]);
-        } else {
+      while (live) {   // ascending part order, four parts a round so that their loads overlap
+        int src[4];
+        float ws[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          src[u] = live ? __ffs(live) - 1 : 0;
+          ws[u] = live ? __shfl_sync(0xffffffffu, w, src[u]) : 0.f;
+          live &= live - 1;   // 0 stays 0
+        }
+        float x[4][VEC];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (ws[u] == 0.f) {   // no part (or a live part whose weight underflowed): nothing to read
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) x[u][v] = 0.f;
+            continue;
+          }
+          const float* xp = po + (int64_t)(p0 + src[u]) * a.part_stride_p;
 #pragma unroll
           for (int v = 0; v < VEC; v += 2) {
-            const float2 t = __ldg(reinterpret_cast<const float2*>(x + v));
-            acc[v] = fmaf(ws, t.x, acc[v]); acc[v + 1] = fmaf(ws, t.y, acc[v + 1]);
+            const float2 t = __ldg(reinterpret_cast<const float2*>(xp + v));
+            x[u][v] = t.x; x[u][v + 1] = t.y;
           }
         }
-        den += ws;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) acc[v] = fmaf(ws[u], x[u][v], acc[v]);
+          den += ws[u];
+        }
       }
     }
+  }
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  const int64_t off = (int64_t)row * a.out_stride_tok + (int64_t)h * a.out_stride_head + lane * VEC;
+  if (a.out_is_f32) {
+    float* o = reinterpret_cast<float*>(a.out) + off;
+#pragma unroll
+    for (int v = 0; v < VEC; v += 2) *reinterpret_cast<float2*>(o + v) = make_float2(acc[v] * inv, acc[v + 1] * inv);
+  } else {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out) + off;
+#pragma unroll
+    for (int v = 0; v < VEC; v += 2)
+      *reinterpret_cast<__nv_bfloat162*>(o + v) = __floats2bfloat162_rn(acc[v] * inv, acc[v + 1] * inv);
+  }
+  if (a.out_lse && lane == 0)
+    a.out_lse[(int64_t)row * a.num_q_heads + h] = den > 0.f ? mx + __logf(den) : -INFINITY;
+}
+
+// The same fold for many live parts a (sequence, head) -- a long sequence cut into a hundred
+// pieces: one CTA a (sequence, q head), its 8 warps take the parts round-robin (two in flight a
+// warp) and the warps' sums are added through shared memory in a fixed order.
+template <int VEC>
+__global__ void __launch_bounds__(MERGE_WARPS * 32) merge_wide_kernel(const MergeArgs a) {
+  __shared__ float s_mx[MERGE_WARPS];
+  __shared__ float s_acc[MERGE_WARPS][32 * VEC + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.x, seq = blockIdx.y;
+  int row = seq;
+  if (a.q_start) {
+    row = __ldg(a.q_start + seq);
+    if (__ldg(a.q_start + seq + 1) <= row) return;
+  }
+  const bool empty = a.seq_lens && __ldg(a.seq_lens + seq) <= 0;
+  const float* lse = a.part_lse + (int64_t)seq * a.lse_stride_seq + h;
+  const float* po = a.part_out + (int64_t)seq * a.part_stride_seq + (int64_t)h * a.head_dim + lane * VEC;
+  float mx = -INFINITY;
+  if (!empty)
+    for (int p = threadIdx.x; p < a.num_parts; p += MERGE_WARPS * 32) mx = fmaxf(mx, __ldg(lse + (int64_t)p * a.lse_stride_p));
+#pragma unroll
+  for (int x = 16; x > 0; x >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, x));
+  if (lane == 0) s_mx[warp] = mx;
+  __syncthreads();
+  mx = s_mx[0];
+#pragma unroll
+  for (int w = 1; w < MERGE_WARPS; ++w) mx = fmaxf(mx, s_mx[w]);
+
+  float acc[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) acc[v] = 0.f;
+  float den = 0.f;
+  if (mx != -INFINITY) {
+    for (int p = warp; p < a.num_parts; p += 2 * MERGE_WARPS) {
+      const int p2 = p + MERGE_WARPS;
+      const float l0 = __ldg(lse + (int64_t)p * a.lse_stride_p);
+      const float l1 = p2 < a.num_parts ? __ldg(lse + (int64_t)p2 * a.lse_stride_p) : -INFINITY;
+      const float w0 = l0 == -INFINITY ? 0.f : __expf(l0 - mx);   // an empty part's memory is never read
+      const float w1 = l1 == -INFINITY ? 0.f : __expf(l1 - mx);
+      float x0[VEC], x1[VEC];
+#pragma unroll
+      for (int v = 0; v < VEC; v += 2) {
+        float2 t0 = make_float2(0.f, 0.f), t1 = make_float2(0.f, 0.f);
+        if (w0 != 0.f) t0 = __ldg(reinterpret_cast<const float2*>(po + (int64_t)p * a.part_stride_p + v));
+        if (w1 != 0.f) t1 = __ldg(reinterpret_cast<const float2*>(po + (int64_t)p2 * a.part_stride_p + v));
+        x0[v] = t0.x; x0[v + 1] = t0.y; x1[v] = t1.x; x1[v + 1] = t1.y;
+      }
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) acc[v] = fmaf(w1, x1[v], fmaf(w0, x0[v], acc[v]));
+      den += w0 + w1;
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) s_acc[warp][lane * VEC + v] = acc[v];
+  if (lane == 0) s_acc[warp][32 * VEC] = den;
+  __syncthreads();
+  if (warp != 0) return;
+  den = s_acc[0][32 * VEC];
+  for (int w = 1; w < MERGE_WARPS; ++w) {   // fixed order: the same bits every call
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) acc[v] += s_acc[w][lane * VEC + v];
+    den += s_acc[w][32 * VEC];
   }
   const float inv = den > 0.f ? 1.f / den : 0.f;
   const int64_t off = (int64_t)row * a.out_stride_tok + (int64_t)h * a.out_stride_head + lane * VEC;
@@ -326,10 +418,19 @@ extern "C" int hkb_merge(void* out, int64_t out_stride_tok, int64_t out_stride_h
   a.part_lse = part_lse; a.lse_stride_p = lse_stride_p; a.lse_stride_seq = lse_stride_seq;
   a.num_parts = num_parts; a.num_q_heads = num_q_heads; a.head_dim = head_dim;
   a.seq_lens = seq_lens; a.q_start = q_start;
-  const dim3 grid((num_q_heads + MERGE_WARPS - 1) / MERGE_WARPS, num_seqs);
-  if (head_dim == 128) merge_kernel<4><<<grid, MERGE_WARPS * 32, 0, (cudaStream_t)stream>>>(a);
-  else if (head_dim == 64) merge_kernel<2><<<grid, MERGE_WARPS * 32, 0, (cudaStream_t)stream>>>(a);
-  else merge_kernel<8><<<grid, MERGE_WARPS * 32, 0, (cudaStream_t)stream>>>(a);
+  // Few slots a sequence: a warp a (sequence, head). Many (a long sequence in a hundred pieces):
+  // a CTA a (sequence, head), the parts spread over its warps.
+  if (num_parts > 32) {
+    const dim3 grid(num_q_heads, num_seqs);
+    if (head_dim == 128) merge_wide_kernel<4><<<grid, MERGE_WARPS * 32, 0, (cudaStream_t)stream>>>(a);
+    else if (head_dim == 64) merge_wide_kernel<2><<<grid, MERGE_WARPS * 32, 0, (cudaStream_t)stream>>>(a);
+    else merge_wide_kernel<8><<<grid, MERGE_WARPS * 32, 0, (cudaStream_t)stream>>>(a);
+  } else {
+    const dim3 grid((num_q_heads + MERGE_WARPS - 1) / MERGE_WARPS, num_seqs);
+    if (head_dim == 128) merge_kernel<4><<<grid, MERGE_WARPS * 32, 0, (cudaStream_t)stream>>>(a);
+    else if (head_dim == 64) merge_kernel<2><<<grid, MERGE_WARPS * 32, 0, (cudaStream_t)stream>>>(a);
+    else merge_kernel<8><<<grid, MERGE_WARPS * 32, 0, (cudaStream_t)stream>>>(a);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
   return HKB_OK;

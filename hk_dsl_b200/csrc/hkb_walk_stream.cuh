@@ -14,7 +14,7 @@
 //     four query heads (half the registers a thread, twice the warps an SM) and fill the K and
 //     the V tiles respectively;
 //   * ring w of the plane's W rings owns tiles [w R, (w+1) R) of that line,
-//     R = max(ceil(total / W), ceil(longest / (parts - 1)), 8): equal shares, cut where they
+//     R = max(ceil(total / W), ceil(longest / (parts - 1)), 1): equal shares, cut where they
 //     fall -- a share may end one sequence and begin the next;
 //   * the warp's cp.async ring runs on across sequence boundaries (the loader has its own
 //     cursor, NST-1 tiles ahead of the compute), so only the first tiles of a warp wait for memory;
@@ -31,7 +31,7 @@
 
 namespace hkb {
 
-constexpr int STREAM_MIN_RANGE = 8;      // tiles: below this a share costs more than it hides
+constexpr int STREAM_MIN_RANGE = 1;      // tiles: a small batch is spread over as many rings as it has tiles (latency, not bandwidth)
 constexpr int STREAM_MAX_SEQS = 2048;    // rows of the prefix table kept in shared memory
 
 // Barrier among the WPR warps that share a ring (a named barrier a ring; __syncwarp for one).

@@ -346,12 +346,12 @@ def plan_splits_for(n_reqs: int, n_kv_heads: int, n_pages: int, sms: int) -> int
     partial slots a sequence gets. The tiles of all sequences of a kv head are dealt in equal
     shares to the W warps serving that head (two four-warp CTAs an SM, divided among the heads);
     1 + 8 W / n slots keep a sequence up to 8x the mean from limiting the shares; capped by the
-    pieces the longest allowed sequence can have (8 tiles a piece) and MAX_SPLITS; a power of two."""
+    pieces the longest allowed sequence can usefully have (2 tiles a piece) and MAX_SPLITS; a power of two."""
     sms = sms if sms > 0 else 148
     n = max(1, n_reqs)
     w = max(1, (sms * 2) // max(1, n_kv_heads)) * 4
     want = 1 + -(-(8 * w) // n)
-    cap = -(-n_pages // 8) + 1 if n_pages > 0 else 2
+    cap = -(-n_pages // 2) + 1 if n_pages > 0 else 2
     want = max(2, min(want, cap))
     p = 1 << (want - 1).bit_length()
     return min(p, MAX_SPLITS)

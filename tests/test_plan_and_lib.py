@@ -63,8 +63,8 @@ def test_plans_are_powers_of_two_and_few(monkeypatch):
     assert plans == sorted(plans, reverse=True)                 # fewer requests, more splits
     assert paged.plan_splits_for(512, 8, 2560, 148) == 4
     assert paged.plan_splits_for(64, 8, 2560, 148) == 32 and paged.plan_splits_for(2, 8, 8192, 148) == 256
-    # never (many) more slots than 8-tile pieces of the longest sequence allowed
-    assert paged.plan_splits_for(1, 1, 16, 148) <= 4
+    # never (many) more slots than 2-tile pieces of the longest sequence allowed
+    assert paged.plan_splits_for(1, 1, 16, 148) <= 16
     assert paged.plan_splits_for(1, 1, 1, 148) == 2
 
 
