@@ -71,9 +71,22 @@ def _cache_t(c: torch.Tensor) -> _lib.CacheT:
 
 
 def _need_cuda(*ts: torch.Tensor) -> None:
+    """Every tensor on ONE CUDA device, and that device current (the C ABI launches on the current
+    device; one process per GPU sets it once)."""
+    dev = None
     for t in ts:
-        if t is not None and not t.is_cuda:
+        if t is None:
+            continue
+        if not t.is_cuda:
             raise RuntimeError("hk.ops.paged: tensors must be on a CUDA device; there is no CPU path")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"hk.ops.paged: tensors on different devices ({dev} and {t.device})")
+    if dev is not None and dev.index != torch.cuda.current_device():
+        raise RuntimeError(f"hk.ops.paged: the tensors live on {dev} but the current CUDA device is "
+                           f"cuda:{torch.cuda.current_device()}; call torch.cuda.set_device({dev.index}) "
+                           f"(or use `with torch.cuda.device(...)`) before launching")
 
 
 def _scale_ptr(s: Optional[torch.Tensor], fp8: bool, name: str) -> Optional[int]:
