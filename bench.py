@@ -240,10 +240,14 @@ def main():
                     help="keep only the first N sequences of the config (small cases for profiler captures)")
     ap.add_argument("--table", action="store_true",
                     help="decode latency (walk + merge, us a layer) over the reference's requests x context grid")
+    ap.add_argument("--prefill", action="store_true",
+                    help="paged prefill (the next row of the path): TFLOP/s over a few prompt shapes")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.table:
         return latency_table()
+    if args.prefill:
+        return prefill_table()
     if args.impl == "reference":
         return reference_arm(args)
 
@@ -534,6 +538,66 @@ def latency_table():
     print(json.dumps({"table": "decode walk + merge, us a layer, 32q/8kv heads, D128, bf16, block 16, cold KV, "
                                "CUDA-graph replay, median of 7", "gpu": torch.cuda.get_device_name(dev), "rows": rows}),
           flush=True)
+    return 0
+
+
+def prefill_table():
+    """Paged prefill on 32 q / 8 kv heads, head_dim 128, bf16: causal flops = 4 * q_heads * head_dim *
+    sum over query rows of the keys they see; timed with CUDA events, median of 7; against the
+    measured bf16 tensor peak (this kernel is the mma.sync form of the contraction)."""
+    import torch
+
+    from hk_dsl_b200.ops import paged
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    hq, hkv, d, bs = 32, 8, 128, 16
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak = float(json.load(f)["bf16_tflops"])
+    except Exception:  # noqa: BLE001
+        peak = 1590.0
+    rows = []
+    g = torch.Generator(device=dev).manual_seed(3)
+    for reqs in ([(0, 2048)], [(0, 8192)], [(0, 2048)] * 8, [(6144, 2048)] * 4, [(0, 512)] * 32):
+        seq = [c + n for c, n in reqs]
+        pages = [-(-s // bs) for s in seq]
+        nb = sum(pages) + 3
+        k = torch.randn(nb, hkv, bs, d, device=dev, generator=g).to(torch.bfloat16)
+        v = torch.randn(nb, hkv, bs, d, device=dev, generator=g).to(torch.bfloat16)
+        table = torch.zeros(len(reqs), max(pages), dtype=torch.int32)
+        perm = torch.randperm(nb)
+        at = 0
+        for i, p in enumerate(pages):
+            table[i, :p] = perm[at:at + p].to(torch.int32)
+            at += p
+        starts = [0]
+        for _, n in reqs:
+            starts.append(starts[-1] + n)
+        q = torch.randn(starts[-1], hq, d, device=dev, generator=g).to(torch.bfloat16)
+        out = torch.empty_like(q)
+        work = paged.work_list([(r, n) for r, (_, n) in enumerate(reqs)], paged.prefill_tile_rows(hq, hkv), dev,
+                               seq_lens=seq)
+        args = (out, q, k.transpose(1, 2), v.transpose(1, 2), table.to(dev), torch.tensor(seq, dtype=torch.int32, device=dev),
+                torch.tensor(starts, dtype=torch.int32, device=dev), work, d ** -0.5)
+        for _ in range(3):
+            paged.paged_prefill(*args)
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(7):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            paged.paged_prefill(*args)
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+        ms = statistics.median(times)
+        keys_seen = sum(n * c + n * (n + 1) // 2 for c, n in reqs)
+        flops = 4.0 * hq * d * keys_seen
+        rows.append({"requests": len(reqs), "context": reqs[0][0], "q_len": reqs[0][1], "ms": round(ms, 3),
+                     "tflops": round(flops / ms / 1e9, 1), "frac_of_measured_bf16_peak": round(flops / ms / 1e9 / peak, 3)})
+    print(json.dumps({"table": "paged prefill, 32q/8kv heads, D128, bf16, block 16; mma.sync form", "peak_tflops": peak,
+                      "rows": rows}), flush=True)
     return 0
 
 

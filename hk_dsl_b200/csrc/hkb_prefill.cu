@@ -1,0 +1,333 @@
+// Paged prefill: causal attention of a request's new tokens (a chunk, or a whole prompt)
+// over its paged KV cache -- the cached prefix plus the chunk itself, already written.
+//
+// What it computes is hk-dsl's paged prefill (python/hk/ops/paged_prefill.py:1-27, 59-620):
+// `ctx` tokens of the sequence are in the cache from before, the `q_len` new ones attend to
+// all ctx + q_len causally, query row i sitting at position ctx + i; a query tile belongs to
+// one request and its rows end where the request's do; the grid is a work list built on the
+// host, one entry a (request, query tile), so a ragged batch launches once.
+//
+// Schedule (sm_100a, legacy tensor path): one CTA a (work item, kv head [x head chunk]) of 8
+// warps; a warp owns a 16-row query tile of ONE query head (its Q fragments stay in registers)
+// and the warps of a CTA are the GP heads of the GQA group times 8 / GP consecutive 16-token
+// tiles, so one staged K/V block serves the whole group. K/V blocks of 64 tokens (4 pages of
+// 16) come through the page table into a 2-stage cp.async ring, XOR-swizzled for ldmatrix;
+// S = Q K^T and O += P V are mma.sync.m16n8k16 bf16 with P reused from the S accumulators;
+// online softmax in exp2 with a lazy reference. This is a dense contraction whose roofline
+// is the tensor pipe; mma.sync is the baseline form of it, not the tcgen05 form.
+#include "hkb_walk_mma.cuh"
+
+extern thread_local int hkb_tls_cuda_error;
+
+namespace hkb {
+
+struct PrefillArgs {
+  __nv_bfloat16* out;
+  int64_t out_stride_tok, out_stride_head;
+  const __nv_bfloat16* q;
+  int64_t q_stride_tok, q_stride_head;
+  const uint8_t* k;
+  const uint8_t* v;
+  int64_t k_stride_block, k_stride_token, k_stride_head;   // bytes
+  int64_t v_stride_block, v_stride_token, v_stride_head;
+  int num_blocks;
+  const int* block_table;
+  int64_t table_stride;
+  int max_pages;
+  const int* seq_lens;
+  const int* q_start;
+  const int* work;   // (request, first query row of the tile inside the request) pairs
+  int num_q_heads, num_kv_heads, group, tiles_per_page;
+  float scale;
+};
+
+template <int D, int GP>
+struct Prefill {
+  static constexpr int WARPS = 8;
+  static constexpr int TOK_TILES = WARPS / GP;        // 16-token query tiles a CTA
+  static constexpr int BT = 16 * TOK_TILES;           // query tokens a CTA
+  static constexpr int KV_TILES = 4;                  // 16-token KV tiles a stage
+  static constexpr int KVB = 16 * KV_TILES;
+  static constexpr int NST = 2;
+  static constexpr int ROWB = D * 2;
+  static constexpr int KD = D / 16;
+  using Loader = TileLoader<ROWB>;
+  static constexpr int TILE_BYTES = Loader::TILE_BYTES;
+  static constexpr int STAGE_BYTES = KV_TILES * 2 * TILE_BYTES;
+  static constexpr int SMEM_BYTES = NST * STAGE_BYTES;
+  static constexpr float RESCALE_LOG2 = 8.f;
+
+  // One warp fills one (tile, K|V) of a stage; rows at or past `kv_limit` are zero-filled
+  // instead of read, so nothing past the keys this CTA may attend to enters shared memory.
+  __device__ static __forceinline__ void fill(const PrefillArgs& a, const Loader& ld, uint32_t stage, int kv0,
+                                              int kv_limit, const int* table_row, int warp, int lane) {
+    const int t = warp >> 1, which = warp & 1;
+    const int tok0 = kv0 + 16 * t;
+    const uint32_t dst = stage + (t * 2 + which) * TILE_BYTES;
+    const int valid = min(16, kv_limit - tok0);      // rows of this tile that hold attendable keys
+    if (valid <= 0) {
+      for (int x = lane; x < 16 * Loader::CPR; x += 32)
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(dst + x * 16), "r"(0u) : "memory");
+      return;
+    }
+    const int tile = tok0 / TILE_TOKENS;
+    const int page = min(tile / a.tiles_per_page, a.max_pages - 1);
+    const int id = min(max(__ldg(table_row + page), 0), a.num_blocks - 1);
+    const int sub = tile % a.tiles_per_page;
+    const int64_t sb = which ? ld.vsb : ld.ksb, st = which ? ld.vst : ld.kst;
+    const uint8_t* p = (which ? ld.vbase : ld.kbase) + (int64_t)id * sb + (int64_t)(sub * TILE_TOKENS) * st;
+#pragma unroll
+    for (int it = 0; it < Loader::ITERS; ++it) {
+      const int x = it * 32 + lane;
+      const int r = x / Loader::CPR, c = x % Loader::CPR;
+      const uint32_t d = dst + tile_off<ROWB>(r, c);
+      if (r < valid) cp_async16(d, p + (int64_t)r * st + c * 16);
+      else asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(d), "r"(0u) : "memory");
+    }
+  }
+
+  __device__ static __forceinline__ void run(const PrefillArgs& a, uint8_t* smem) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int passes = a.group / GP;
+    const int kvh = blockIdx.y / passes;
+    const int hq = kvh * a.group + (blockIdx.y % passes) * GP + (warp % GP);   // this warp's query head
+    const int req = __ldg(a.work + 2 * blockIdx.x), row0 = __ldg(a.work + 2 * blockIdx.x + 1);
+    const int q0 = __ldg(a.q_start + req), q1 = __ldg(a.q_start + req + 1);
+    const int q_len = q1 - q0;
+    const int seq_len = __ldg(a.seq_lens + req);
+    const int ctx = seq_len - q_len;
+    if (q_len <= 0 || row0 >= q_len || ctx < 0) return;
+    const int rows_cta = min(BT, q_len - row0);                 // query rows of this request the CTA covers
+    const int kv_limit = min(seq_len, ctx + row0 + rows_cta);   // keys any of them may attend to
+    const int n_blocks = (kv_limit + KVB - 1) / KVB;
+
+    // this warp's 16 rows: tokens row0 + 16 * (warp / GP) + {lane/4, lane/4 + 8}
+    const int wrow0 = row0 + 16 * (warp / GP);
+    const int rA = wrow0 + (lane >> 2), rB = rA + 8;            // rows inside the request
+    const bool vA = rA < q_len, vB = rB < q_len;
+    const int posA = ctx + rA, posB = ctx + rB;                 // their positions in the sequence
+    uint32_t qa[KD][4];
+    {
+      const uint32_t* qA = reinterpret_cast<const uint32_t*>(a.q + (int64_t)(q0 + rA) * a.q_stride_tok + (int64_t)hq * a.q_stride_head);
+      const uint32_t* qB = reinterpret_cast<const uint32_t*>(a.q + (int64_t)(q0 + rB) * a.q_stride_tok + (int64_t)hq * a.q_stride_head);
+#pragma unroll
+      for (int kc = 0; kc < KD; ++kc) {
+        qa[kc][0] = vA ? __ldg(qA + kc * 8 + (lane & 3)) : 0u;
+        qa[kc][1] = vB ? __ldg(qB + kc * 8 + (lane & 3)) : 0u;
+        qa[kc][2] = vA ? __ldg(qA + kc * 8 + 4 + (lane & 3)) : 0u;
+        qa[kc][3] = vB ? __ldg(qB + kc * 8 + 4 + (lane & 3)) : 0u;
+      }
+    }
+    float o[2 * KD][4];
+#pragma unroll
+    for (int nt = 0; nt < 2 * KD; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[nt][i] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const float qs = a.scale * LOG2E;
+    const bool warp_live = wrow0 < q_len;                       // a warp whose 16 rows are all past the request idles
+
+    Loader ld;
+    ld.kbase = a.k + (int64_t)kvh * a.k_stride_head;
+    ld.vbase = a.v + (int64_t)kvh * a.v_stride_head;
+    ld.ksb = a.k_stride_block; ld.kst = a.k_stride_token;
+    ld.vsb = a.v_stride_block; ld.vst = a.v_stride_token;
+    ld.tiles_per_page = a.tiles_per_page; ld.num_blocks = a.num_blocks;
+    const int* table_row = a.block_table + (int64_t)req * a.table_stride;
+    const uint32_t ring = smem_u32(smem);
+
+    fill(a, ld, ring, 0, kv_limit, table_row, warp, lane);
+    cp_async_commit();
+    for (int b = 0; b < n_blocks; ++b) {
+      cp_async_wait<0>();
+      __syncthreads();   // block b has landed for every warp; block b-1's stage is free again
+      if (b + 1 < n_blocks) fill(a, ld, ring + ((b + 1) & 1) * STAGE_BYTES, (b + 1) * KVB, kv_limit, table_row, warp, lane);
+      cp_async_commit();
+      const uint32_t stage = ring + (b & 1) * STAGE_BYTES;
+      const int kv0 = b * KVB;
+      if (!warp_live) continue;
+      // keys past every row of this warp need no work at all
+      const int warp_limit = min(kv_limit, ctx + min(wrow0 + 16, q_len));
+#pragma unroll
+      for (int t = 0; t < KV_TILES; ++t) {
+        const int t0 = kv0 + 16 * t;
+        if (t0 >= warp_limit) break;
+        const uint32_t ktile = stage + (t * 2) * TILE_BYTES, vtile = ktile + TILE_BYTES;
+        float s[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
+        {   // S = Q K^T: B = K rows (keys x 16 dims), two 8-key column tiles
+          const int r = ((lane >> 4) & 1) * 8 + (lane & 7);
+#pragma unroll
+          for (int kc = 0; kc < KD; ++kc) {
+            uint32_t kb[4];
+            ldmatrix_x4(kb, ktile + tile_off<ROWB>(r, kc * 2 + ((lane >> 3) & 1)));
+            const uint32_t b0[2] = {kb[0], kb[1]}, b1[2] = {kb[2], kb[3]};
+            mma_bf16(s[0], qa[kc], b0);
+            mma_bf16(s[1], qa[kc], b1);
+          }
+        }
+        // scale, causal mask (key j is seen by the row at position p iff j <= p), row maxima
+        const bool diag = t0 + 15 > ctx + wrow0;   // the tile reaches past the first row's position
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const int j = t0 + nt * 8 + 2 * (lane & 3);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) s[nt][i] *= qs;
+          if (diag) {
+            if (j > posA) s[nt][0] = -INFINITY;
+            if (j + 1 > posA) s[nt][1] = -INFINITY;
+            if (j > posB) s[nt][2] = -INFINITY;
+            if (j + 1 > posB) s[nt][3] = -INFINITY;
+          }
+          mx[0] = fmaxf(mx[0], fmaxf(s[nt][0], s[nt][1]));
+          mx[1] = fmaxf(mx[1], fmaxf(s[nt][2], s[nt][3]));
+        }
+#pragma unroll
+        for (int x = 1; x < 4; x <<= 1) {
+          mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], x));
+          mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], x));
+        }
+        // lazy reference: rescale only when a tile's maximum exceeds it by 2^RESCALE_LOG2
+        if (__any_sync(0xffffffffu, mx[0] > m[0] + RESCALE_LOG2 || mx[1] > m[1] + RESCALE_LOG2)) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const float m_new = fmaxf(m[c], mx[c]);
+            const float alpha = fast_exp2(m[c] - ((m_new == -INFINITY) ? 0.f : m_new));
+            l[c] *= alpha;
+#pragma unroll
+            for (int nt = 0; nt < 2 * KD; ++nt) { o[nt][2 * c] *= alpha; o[nt][2 * c + 1] *= alpha; }
+            m[c] = m_new;
+          }
+        }
+        const float sa = (m[0] == -INFINITY) ? 0.f : m[0], sb = (m[1] == -INFINITY) ? 0.f : m[1];
+        uint32_t pa[4];
+        {
+          const float p00 = fast_exp2(s[0][0] - sa), p01 = fast_exp2(s[0][1] - sa);
+          const float p02 = fast_exp2(s[0][2] - sb), p03 = fast_exp2(s[0][3] - sb);
+          const float p10 = fast_exp2(s[1][0] - sa), p11 = fast_exp2(s[1][1] - sa);
+          const float p12 = fast_exp2(s[1][2] - sb), p13 = fast_exp2(s[1][3] - sb);
+          l[0] += p00 + p01 + p10 + p11;
+          l[1] += p02 + p03 + p12 + p13;
+          pa[0] = pack_bf16x2(p00, p01);   // (row A, keys 0-7 pair)
+          pa[1] = pack_bf16x2(p02, p03);   // (row B, keys 0-7 pair)
+          pa[2] = pack_bf16x2(p10, p11);   // (row A, keys 8-15 pair)
+          pa[3] = pack_bf16x2(p12, p13);   // (row B, keys 8-15 pair)
+        }
+        {   // O += P V: B = V^T read transposed from the row-major V tile, two 8-dim column tiles a load
+          const int r = ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+          for (int dt = 0; dt < KD; ++dt) {
+            uint32_t vb[4];
+            ldmatrix_x4_trans(vb, vtile + tile_off<ROWB>(r, dt * 2 + (lane >> 4)));
+            const uint32_t b0[2] = {vb[0], vb[1]}, b1[2] = {vb[2], vb[3]};
+            mma_bf16(o[2 * dt], pa, b0);
+            mma_bf16(o[2 * dt + 1], pa, b1);
+          }
+        }
+      }
+    }
+    cp_async_wait<0>();
+    if (!warp_live) return;
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+      for (int x = 1; x < 4; x <<= 1) l[c] += __shfl_xor_sync(0xffffffffu, l[c], x);
+    const float iA = l[0] > 0.f ? 1.f / l[0] : 0.f, iB = l[1] > 0.f ? 1.f / l[1] : 0.f;
+    __nv_bfloat16* oA = a.out + (int64_t)(q0 + rA) * a.out_stride_tok + (int64_t)hq * a.out_stride_head;
+    __nv_bfloat16* oB = a.out + (int64_t)(q0 + rB) * a.out_stride_tok + (int64_t)hq * a.out_stride_head;
+#pragma unroll
+    for (int nt = 0; nt < 2 * KD; ++nt) {
+      const int d = nt * 8 + 2 * (lane & 3);
+      if (vA) *reinterpret_cast<uint32_t*>(oA + d) = pack_bf16x2(o[nt][0] * iA, o[nt][1] * iA);
+      if (vB) *reinterpret_cast<uint32_t*>(oB + d) = pack_bf16x2(o[nt][2] * iB, o[nt][3] * iB);
+    }
+  }
+};
+
+template <int D, int GP>
+__global__ void __launch_bounds__(256) prefill_kernel(const PrefillArgs a) {
+  extern __shared__ __align__(128) uint8_t hkb_smem[];
+  Prefill<D, GP>::run(a, hkb_smem);
+}
+
+template <int D, int GP>
+static int launch_prefill(const PrefillArgs& a, int num_work, cudaStream_t st) {
+  static bool armed[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  constexpr int smem = Prefill<D, GP>::SMEM_BYTES;
+  if (e == cudaSuccess && dev >= 0 && dev < 64 && !armed[dev]) {
+    e = cudaFuncSetAttribute(prefill_kernel<D, GP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) armed[dev] = true;
+  }
+  if (e == cudaSuccess) {
+    dim3 grid(num_work, a.num_kv_heads * (a.group / GP));
+    prefill_kernel<D, GP><<<grid, 256, smem, st>>>(a);
+    e = cudaGetLastError();
+  }
+  if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
+  return HKB_OK;
+}
+
+template <int D>
+static int dispatch_prefill(const PrefillArgs& a, int num_work, cudaStream_t st) {
+  // heads of the GQA group a CTA serves: the largest of 8, 4, 2, 1 that divides the group
+  if (a.group % 8 == 0) return launch_prefill<D, 8>(a, num_work, st);
+  if (a.group % 4 == 0) return launch_prefill<D, 4>(a, num_work, st);
+  if (a.group % 2 == 0) return launch_prefill<D, 2>(a, num_work, st);
+  return launch_prefill<D, 1>(a, num_work, st);
+}
+
+}  // namespace hkb
+
+extern "C" int hkb_prefill_tile_rows(int num_q_heads, int num_kv_heads) {
+  if (num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads) return 0;
+  const int g = num_q_heads / num_kv_heads;
+  const int gp = g % 8 == 0 ? 8 : g % 4 == 0 ? 4 : g % 2 == 0 ? 2 : 1;
+  return 16 * (8 / gp);
+}
+
+extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_stride_head,
+                                 const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                                 hkb_cache_t kc, hkb_cache_t vc,
+                                 const int32_t* block_table, int64_t table_stride, int max_pages,
+                                 const int32_t* seq_lens, const int32_t* q_start,
+                                 const int32_t* work, int num_work,
+                                 int num_q_heads, int num_kv_heads, int head_dim, int block_size,
+                                 float scale, int kv_dtype, void* stream) {
+  using namespace hkb;
+  if (num_work < 0 || num_q_heads <= 0 || num_kv_heads <= 0) return HKB_ERR_SIZE;
+  if (num_work == 0) return HKB_OK;
+  if (!out || !q || !kc.ptr || !vc.ptr || !block_table || !seq_lens || !q_start || !work) return HKB_ERR_NULL;
+  if (head_dim != 64 && head_dim != 128) return HKB_ERR_HEAD_DIM;
+  if (block_size <= 0 || block_size % TILE_TOKENS) return HKB_ERR_BLOCK_SIZE;
+  if (num_q_heads % num_kv_heads || num_q_heads / num_kv_heads > HKB_MAX_GROUP) return HKB_ERR_GROUP;
+  if (kv_dtype != HKB_KV_BF16) return kv_dtype == HKB_KV_FP8_E4M3 ? HKB_ERR_UNSUPPORTED : HKB_ERR_DTYPE;
+  if (max_pages < 1 || kc.num_blocks < 1 || vc.num_blocks < 1) return HKB_ERR_SIZE;
+  const int group = num_q_heads / num_kv_heads;
+  if ((int64_t)num_kv_heads * group > 65535) return HKB_ERR_SIZE;
+  const int64_t kv_strides = kc.stride_block | kc.stride_token | kc.stride_head | vc.stride_block | vc.stride_token | vc.stride_head;
+  if ((kv_strides * 2) % 16) return HKB_ERR_STRIDE;
+  if ((q_stride_tok | q_stride_head | out_stride_tok | out_stride_head) % 2) return HKB_ERR_STRIDE;
+  if (((uintptr_t)kc.ptr | (uintptr_t)vc.ptr) % 16 || ((uintptr_t)q | (uintptr_t)out) % 4) return HKB_ERR_ALIGN;
+
+  PrefillArgs a;
+  a.out = (__nv_bfloat16*)out; a.out_stride_tok = out_stride_tok; a.out_stride_head = out_stride_head;
+  a.q = (const __nv_bfloat16*)q; a.q_stride_tok = q_stride_tok; a.q_stride_head = q_stride_head;
+  a.k = (const uint8_t*)kc.ptr; a.v = (const uint8_t*)vc.ptr;
+  a.k_stride_block = kc.stride_block * 2; a.k_stride_token = kc.stride_token * 2; a.k_stride_head = kc.stride_head * 2;
+  a.v_stride_block = vc.stride_block * 2; a.v_stride_token = vc.stride_token * 2; a.v_stride_head = vc.stride_head * 2;
+  const int64_t nb = kc.num_blocks < vc.num_blocks ? kc.num_blocks : vc.num_blocks;
+  a.num_blocks = nb > 0x7fffffff ? 0x7fffffff : (int)nb;
+  a.block_table = block_table; a.table_stride = table_stride; a.max_pages = max_pages;
+  a.seq_lens = seq_lens; a.q_start = q_start; a.work = work;
+  a.num_q_heads = num_q_heads; a.num_kv_heads = num_kv_heads; a.group = group;
+  a.tiles_per_page = block_size / TILE_TOKENS;
+  a.scale = scale;
+  cudaStream_t st = (cudaStream_t)stream;
+  return head_dim == 128 ? dispatch_prefill<128>(a, num_work, st) : dispatch_prefill<64>(a, num_work, st);
+}

@@ -15,7 +15,8 @@ kernels behind it:
 * what it does not implement raises with a sentence (:538-556): ALiBi, sliding windows,
   sinks, softcap, fused output quantisation, head sizes without a kernel. Unlike the
   reference it accepts an fp8-e4m3 KV cache with per-tensor k_scale / v_scale.
-* a batch with prefill in it is not built yet in this build: it raises.
+* a batch with prefill in it runs ONE paged-prefill launch over a host-built work list, decodes
+  included (:637-698); it is never captured (its grid follows host-read query lengths).
 
 `HKAttentionImplCore` has no vLLM import, so it is constructed and driven in tests with
 plain tensors; `register()` wraps it in vLLM's classes when vLLM is importable.
@@ -180,9 +181,32 @@ class HKAttentionImplCore:
                 f"{NAME} is being captured on a batch with prefill in it. It claims "
                 f"UNIFORM_SINGLE_TOKEN_DECODE: a prefill step reads its query lengths on the host, which a "
                 f"replay would not repeat.")
-        raise NotImplementedError(
-            f"{NAME}: a batch with prefill in it (max_query_len {attn_metadata.max_query_len}); the paged "
-            f"prefill kernel is not part of this build yet -- run prefill on the engine's backend")
+        # A step with prefill in it: every new token's K/V is in the cache by now, so ONE paged
+        # prefill launch over a host-built work list serves the whole batch -- chunks, cached
+        # prefixes and the one-token decodes riding along (a lone token is a one-row tile).
+        self._prefill(query, output, k_cache, v_cache, attn_metadata, n)
+        PATCH.count("prefill")
+        return output
+
+    def _prefill(self, query, output, k_cache, v_cache, attn_metadata, n):
+        """The batch's rows as (tokens, heads, head_dim); the work list comes from the metadata
+        builder (`hk_prefill_work`, built on the host where the query lengths already are) or, for
+        a caller without one, from query_start_loc read back here (never under capture)."""
+        if self.kv_cache_dtype != "auto":
+            raise NotImplementedError(f"{NAME}: prefill over an fp8 KV cache is not built; decode is")
+        hq, d = self.num_heads, self.head_size
+        work = getattr(attn_metadata, "hk_prefill_work", None)
+        qsl = attn_metadata.query_start_loc
+        reqs = qsl.shape[0] - 1
+        if not self._checked:
+            self._check(attn_metadata.block_table[:reqs], attn_metadata.seq_lens[:reqs])
+        if work is None:
+            starts = qsl.tolist()
+            work = paged.work_list([(r, starts[r + 1] - starts[r]) for r in range(reqs)],
+                                   paged.prefill_tile_rows(hq, self.num_kv_heads), query.device)
+        paged.paged_prefill(output[:n].view(n, hq, d), query[:n].view(n, hq, d), k_cache.transpose(1, 2),
+                            v_cache.transpose(1, 2), attn_metadata.block_table, attn_metadata.seq_lens, qsl, work,
+                            self.scale)
 
     def _decode_all(self, query, output, k_cache, v_cache, attn_metadata, n, layer=None):
         """Every request has exactly one token: the walk and its merge, reading the query and
@@ -276,7 +300,27 @@ def _build():
             # what vLLM's Triton backend's builder already assembles
             from vllm.v1.attention.backends.triton_attn import TritonAttentionMetadataBuilder  # noqa: PLC0415
 
-            return TritonAttentionMetadataBuilder
+            rows = paged.prefill_tile_rows
+
+            class HKAttentionMetadataBuilder(TritonAttentionMetadataBuilder):
+                """vLLM's builder plus the prefill work list, made on the host where vLLM already
+                has the query lengths (python/hk/integration/vllm_backend.py:447-471 of the
+                reference does the same in its builder)."""
+
+                def build(self, common_prefix_len, common_attn_metadata, fast_build=False):
+                    md = super().build(common_prefix_len, common_attn_metadata, fast_build)
+                    md.hk_prefill_work = None
+                    if getattr(common_attn_metadata, "max_query_len", 1) > 1:
+                        qs = common_attn_metadata.query_start_loc_cpu.tolist()
+                        spec = getattr(self, "kv_cache_spec", None)
+                        hkv = getattr(spec, "num_kv_heads", None)
+                        hq = getattr(self, "num_heads_q", None)
+                        if hkv and hq:
+                            md.hk_prefill_work = paged.work_list(
+                                [(r, qs[r + 1] - qs[r]) for r in range(len(qs) - 1)], rows(hq, hkv), self.device)
+                    return md
+
+            return HKAttentionMetadataBuilder
 
         @staticmethod
         def get_supported_kernel_block_sizes():

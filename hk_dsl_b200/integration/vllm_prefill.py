@@ -1,6 +1,6 @@
 """In-place attention route: stand-ins with vLLM's own signatures that send a decode-only call
-to this build's paged decode on the engine's own cache, and everything else back to the
-engine's kernel, counted.
+to this build's paged decode and a call with prefill in it to the paged prefill, both on the
+engine's own cache, and everything else back to the engine's kernel, counted.
 
 The decode half of hk-dsl's route (python/hk/integration/vllm_prefill.py:937-1095 for
 `unified_attention`, :1287-1376 for `chunked_prefill_paged_decode`):
@@ -35,7 +35,7 @@ from ..ops import paged
 from . import engine, switches
 from ._common import rebind
 
-PATCH = engine.Patch("vllm_prefill", ("decode", "fallback"), graph="safe")
+PATCH = engine.Patch("vllm_prefill", ("prefill", "decode", "fallback"), graph="safe")
 
 ARCHES = (switches.SM100,)
 
@@ -185,6 +185,42 @@ def _decode(q, out, k, v, block_table, seq_lens, q_start, scale, k_descale, v_de
     return True
 
 
+def u_why_not(a: dict) -> str:
+    """Why this unified_attention call WITH prefill in it is not taken, or "". The same checks as
+    a decode-only call, minus decode-only, plus: never under capture (the grid follows query
+    lengths read on the host), bf16 caches only."""
+    if switches.arch() not in ARCHES:
+        return f"arch {switches.arch()}"
+    if engine.capturing():
+        return "being captured (a mixed batch's grid follows its query lengths)"
+    for name, ok in _U_OFF.items():
+        if name in a and not ok(a[name]):
+            return f"{name} set"
+    if not a.get("causal", True):
+        return "not causal"
+    unknown = _unknown_set(a, _U_SIG, _U_READ | _U_OFF.keys())
+    if unknown:
+        return f"{unknown} set (an argument hk does not know)"
+    if a["k"].dtype != torch.bfloat16:
+        return f"cache dtype {a['k'].dtype} (prefill reads bf16 caches)"
+    return _common_why_not(a["q"], a["out"], a["k"], a["v"], a["block_table"], a["seqused_k"],
+                           a.get("cu_seqlens_q"), None, None)
+
+
+def _prefill(a: dict) -> bool:
+    """The paged prefill on a batch with prefill in it (decodes included as one-row tiles)."""
+    q, out, k = a["q"], a["out"], a["k"]
+    hq, d = q.shape[1], q.shape[2]
+    starts = a["cu_seqlens_q"].tolist()           # a host read: mixed batches are never captured
+    reqs = len(starts) - 1
+    work = paged.work_list([(r, starts[r + 1] - starts[r]) for r in range(reqs)],
+                           paged.prefill_tile_rows(hq, int(k.shape[2])), q.device)
+    sc = a.get("softmax_scale")
+    paged.paged_prefill(out, q, k, a["v"], a["block_table"], a["seqused_k"], a["cu_seqlens_q"], work,
+                        d ** -0.5 if sc is None else float(sc))
+    return True
+
+
 def _fallback(orig, args, kwargs, why: str):
     PATCH.count("fallback")
     if orig is None:
@@ -194,9 +230,16 @@ def _fallback(orig, args, kwargs, why: str):
 
 
 def unified_attention(*args, **kwargs):
-    """vLLM's unified_attention (its signature, set on apply): a decode-only call goes to the
-    paged decode, anything else to the original."""
+    """vLLM's unified_attention (its signature, set on apply): a call with prefill in it goes to
+    the paged prefill (python/hk/integration/vllm_prefill.py:1096-1163 of the reference), a
+    decode-only call to the paged decode, anything the kernels do not take to the original."""
     a = kwargs if not args else _U_SIG.bind(*args, **kwargs).arguments
+    if int(a.get("max_seqlen_q", 1)) > 1:
+        why = u_why_not(a)
+        if not why and _prefill(a):
+            PATCH.count("prefill")
+            return None
+        return _fallback(_ORIG_U, args, kwargs, why)
     why = "decode route off (HK_VLLM_DECODE=0)"
     if DECODE:
         why = d_why_not(a)

@@ -228,6 +228,69 @@ def paged_attention_decode(out: torch.Tensor, query: torch.Tensor, key_cache: to
     return out
 
 
+# --------------------------------------------------------------------------------------
+# prefill (the rows of a batch that are not single-token decodes)
+# --------------------------------------------------------------------------------------
+
+def prefill_tile_rows(num_q_heads: int, num_kv_heads: int) -> int:
+    """Query rows one work item of the prefill kernel covers: 16 x 8 / GP, GP the largest of
+    8, 4, 2, 1 dividing the GQA group (hkb_prefill_tile_rows)."""
+    g = num_q_heads // num_kv_heads
+    gp = 8 if g % 8 == 0 else 4 if g % 4 == 0 else 2 if g % 2 == 0 else 1
+    return 16 * (8 // gp)
+
+
+def work_list(reqs, tile_rows: int, device, seq_lens=None) -> torch.Tensor:
+    """The prefill's grid, built on the host where the query lengths already are: `reqs` is
+    [(request, q_len)]; one (request, first row) pair a `tile_rows`-row query tile, the tiles that
+    see the most keys first (`seq_lens`, host ints, if given) so the long ones do not trail.
+    The counterpart of hk-dsl's `work_list` (python/hk/ops/paged_prefill.py:879-968)."""
+    items = []
+    for r, n in reqs:
+        for row0 in range(0, int(n), tile_rows):
+            end = min(int(n), row0 + tile_rows)
+            keys = (int(seq_lens[r]) - int(n) + end) if seq_lens is not None else end
+            items.append((-keys, r, row0))
+    items.sort()
+    flat = [x for _, r, row0 in items for x in (r, row0)]
+    return torch.tensor(flat, dtype=torch.int32).view(-1, 2).to(device, non_blocking=True)
+
+
+def paged_prefill(out: torch.Tensor, query: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
+                  block_tables: torch.Tensor, seq_lens: torch.Tensor, query_start_loc: torch.Tensor,
+                  work: torch.Tensor, scale: float, kv_cache_dtype: str = "auto") -> torch.Tensor:
+    """Causal attention of every request's new tokens over its paged cache (prefix + new tokens,
+    already written). `query`/`out` `(tokens, q_heads, head_dim)` bf16; caches
+    `(blocks, block_size, kv_heads, head_dim)` bf16 views; `seq_lens` the tokens in the cache a
+    request (int32), `query_start_loc` cu_seqlens_q (int32, requests + 1); `work` from `work_list`.
+    Requests that are not in `work` keep their output rows untouched."""
+    _need_cuda(out, query, key_cache, value_cache, block_tables, seq_lens, query_start_loc, work)
+    if query.dim() != 3 or query.dtype != torch.bfloat16 or query.stride(2) != 1 or out.shape != query.shape \
+            or out.dtype != query.dtype or out.stride(2) != 1:
+        raise ValueError(f"hk.ops.paged: prefill reads/writes (tokens, q_heads, head_dim) bfloat16; query "
+                         f"{tuple(query.shape)} {query.dtype}, out {tuple(out.shape)} {out.dtype}")
+    _, hq, d = query.shape
+    if key_cache.dim() != 4 or value_cache.shape != key_cache.shape or key_cache.shape[3] != d \
+            or key_cache.stride(3) != 1 or value_cache.stride(3) != 1:
+        raise ValueError(f"hk.ops.paged: key_cache {tuple(key_cache.shape)} / value_cache {tuple(value_cache.shape)}: "
+                         f"two (blocks, block_size, kv_heads, {d}) views needed")
+    for name, t in (("block_tables", block_tables), ("seq_lens", seq_lens), ("query_start_loc", query_start_loc),
+                    ("work", work)):
+        if t.dtype != torch.int32 or t.stride(-1) != 1:
+            raise TypeError(f"hk.ops.paged: {name} is {t.dtype} {tuple(t.shape)}; contiguous int32 needed")
+    if work.dim() != 2 or work.shape[1] != 2 or not work.is_contiguous():
+        raise ValueError("hk.ops.paged: work must be (items, 2) int32 (work_list)")
+    code = kv_dtype_code(kv_cache_dtype, key_cache)
+    _, bs, hkv, _ = key_cache.shape
+    rc = _lib.load().hkb_paged_prefill(
+        out.data_ptr(), out.stride(0), out.stride(1), query.data_ptr(), query.stride(0), query.stride(1),
+        _cache_t(key_cache), _cache_t(value_cache), block_tables.data_ptr(), block_tables.stride(0),
+        block_tables.shape[1], seq_lens.data_ptr(), query_start_loc.data_ptr(), work.data_ptr(), work.shape[0],
+        hq, hkv, d, bs, float(scale), code, _stream(query))
+    _lib.check("hkb_paged_prefill", rc)
+    return out
+
+
 def merge_partials(out: torch.Tensor, part_out: torch.Tensor, part_lse: torch.Tensor,
                    out_lse: Optional[torch.Tensor] = None, seq_lens: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Fold `(parts, seqs, q_heads, head_dim)` fp32 normalised partials with their

@@ -12,6 +12,7 @@ names are registered on demand onto ONE runtime-parameterised C entry point:
                                kv_cache_dtype, k_scale, v_scale, num_splits, part_out!, part_lse!)
     hk::paged_decode_fused_d{D}_s{S}(q, k_cache, v_cache, block_table, seq_lens, out!, o_part!, ml_part!)
     hk::paged_merge_d{D}_s{S}(seq_lens, out!, o_part, ml_part)
+    hk::paged_prefill_d{D}_g{G}(q, k_cache, v_cache, block_table, seq_lens, q_start, tiles, out!)
 
 The split scratch (`o_part`, `ml_part`) is this build's: fp32 normalised partials and their
 natural-log lse (`hk_dsl_b200.ops.paged.fused_scratch`), caller-owned and allocated once.
@@ -100,6 +101,23 @@ def merge_op(head_dim: int, splits: int) -> engine.Op:
 
     return _define(f"paged_merge_d{head_dim}_s{splits}",
                    "(Tensor seq_lens, Tensor(a!) out, Tensor o_part, Tensor ml_part) -> ()", impl)
+
+
+def prefill_op(head_dim: int, group: int) -> engine.Op:
+    """`hk::paged_prefill_d{D}_g{G}(q, k_cache, v_cache, block_table, seq_lens, q_start, tiles, out!)`:
+    the reference's prefill launch and argument order (tests/hk/gpu/test_paged_prefill.py:80-82;
+    python/hk/ops/paged_prefill.py kernel_for) on 2-D (tokens, heads * head_dim) q / out rows and
+    hk's (blocks, kv_heads, page, head_dim) caches; `tiles` from `hk_dsl_b200.ops.paged.work_list`."""
+
+    def impl(q, k_cache, v_cache, block_table, seq_lens, q_start, tiles, out):
+        n = q.shape[0]
+        hq = k_cache.shape[1] * group
+        paged.paged_prefill(out.view(n, hq, head_dim), q.view(n, hq, head_dim), k_cache.transpose(1, 2),
+                            v_cache.transpose(1, 2), block_table, seq_lens, q_start, tiles, head_dim ** -0.5)
+
+    return _define(f"paged_prefill_d{head_dim}_g{group}",
+                   "(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_table, Tensor seq_lens, Tensor q_start, "
+                   "Tensor tiles, Tensor(a!) out) -> ()", impl)
 
 
 def launcher(kind: str, head_dim: int, splits: int) -> engine.Op:

@@ -163,6 +163,33 @@ int hkb_merge(void* out, int64_t out_stride_tok, int64_t out_stride_head, int ou
               const int32_t* seq_lens, const int32_t* q_start, void* stream);
 
 /*
+ * Paged prefill: causal attention of each request's new tokens over its paged KV cache
+ * (cached prefix + the new tokens, already written by hkb_reshape_and_cache). Request r has
+ * q_start[r+1] - q_start[r] query rows and seq_lens[r] tokens in the cache; its query row i
+ * sits at position seq_lens[r] - q_len + i and sees keys 0..that position.
+ *
+ * `work` is a device array of num_work (request, first row) int32 pairs, one a query tile of
+ * hkb_prefill_tile_rows(num_q_heads, num_kv_heads) rows (the host builds it: query lengths
+ * are host values in a prefill step; put long tiles first). Rows of requests that are not in
+ * the work list are not written. bf16 caches only (HKB_ERR_UNSUPPORTED for fp8).
+ *
+ * Replaces: paged_prefill_kernel and its work list (python/hk/ops/paged_prefill.py:59-620,
+ * 879-968) as launched from python/hk/integration/vllm_backend.py:667-698.
+ */
+int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_stride_head,
+                      const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                      hkb_cache_t k_cache, hkb_cache_t v_cache,
+                      const int32_t* block_table, int64_t table_stride, int max_pages,
+                      const int32_t* seq_lens, const int32_t* q_start,
+                      const int32_t* work, int num_work,
+                      int num_q_heads, int num_kv_heads, int head_dim, int block_size,
+                      float scale, int kv_dtype, void* stream);
+
+/* Query rows one work item of hkb_paged_prefill covers (16..128, by GQA group); 0 if the
+ * head counts are not a valid GQA shape. */
+int hkb_prefill_tile_rows(int num_q_heads, int num_kv_heads);
+
+/*
  * Bytes of the scratch array built into the library for hkb_paged_decode_static (below).
  */
 #define HKB_STATIC_SCRATCH_BYTES (8u << 20)

@@ -15,6 +15,8 @@ function:
 * `paged_decode_ref`       -- `_reference` of tests/hk/gpu/test_paged_decode.py:89-101 and
   tests/hk/gpu/test_vllm_backend_decode.py:74-86 (gather `table[i, :ceil(s/page)]`, cat pages,
   `[:s]`, q head hh reads kv head hh // group; a request of length 0 answers zeros).
+* `paged_prefill_ref`      -- `_reference` of tests/hk/gpu/test_paged_prefill.py:54-70 (causal, cached
+  prefix: query row j of a request at position ctx + j keeps keys <= its position).
 * `paged_decode_ref_fp32`  -- the vectorised fp32 form of tools/hk-bench/paged_cdna.py:132-140
   (the fairer speed baseline).
 * `merge_splits_unnormalised` -- python/hk/ops/paged.py:283-317 verbatim in meaning
@@ -150,6 +152,31 @@ def paged_decode_ref_fp32(q, key_cache, value_cache, block_tables, seq_lens, sca
         qq = q[i].float().view(hkv, g, d)
         sc = torch.einsum("hgd,nhd->hgn", qq, kk) * scale
         out[i] = torch.einsum("hgn,nhd->hgd", torch.softmax(sc, -1), vv).reshape(h, d)
+    return out
+
+
+def paged_prefill_ref(q, key_cache, value_cache, block_tables, seq_lens, query_start_loc, scale=None):
+    """Causal prefill over a paged cache in float64, float32 out: the `_reference` of
+    tests/hk/gpu/test_paged_prefill.py:54-70 -- request i's q_len new tokens are the last q_len of
+    its seq_lens[i] cached tokens; query row j sits at position ctx + j and keeps keys <= it."""
+    n_tok, h, d = q.shape
+    page, hkv = key_cache.shape[1], key_cache.shape[2]
+    group = h // hkv
+    scale = d ** -0.5 if scale is None else scale
+    out = torch.zeros(n_tok, h, d, dtype=torch.float32)
+    qsl, lens = query_start_loc.tolist(), seq_lens.tolist()
+    for i in range(len(lens)):
+        q0, q1, s = qsl[i], qsl[i + 1], lens[i]
+        n, ctx = q1 - q0, s - (q1 - q0)
+        if n <= 0:
+            continue
+        pages = block_tables[i, : -(-s // page)].long()
+        kk_all = key_cache[pages].reshape(-1, hkv, d)[:s]
+        vv_all = value_cache[pages].reshape(-1, hkv, d)[:s]
+        pos = ctx + torch.arange(n)
+        keep = torch.arange(s)[None, :] <= pos[:, None]
+        for hh in range(h):
+            out[q0:q1, hh] = softmax_v64(q[q0:q1, hh], kk_all[:, hh // group], vv_all[:, hh // group], scale, keep)
     return out
 
 

@@ -62,9 +62,27 @@ def attn_golden():
             kk = torch.cat([k[p, hh // group] for p in pg])[:s]
             vv = torch.cat([v[p, hh // group] for p in pg])[:s]
             out[i, hh] = ref.softmax_v64(q[i, hh][None], kk, vv, d ** -0.5)[0]
+    # causal prefill with a cached prefix, as tests/hk/gpu/test_paged_prefill.py:54-70 builds it:
+    # request i's last q_len tokens are the queries, row j at position ctx + j keeps keys <= it
+    q_lens = [1, 5, 40, 16]
+    starts = [0]
+    for n in q_lens:
+        starts.append(starts[-1] + n)
+    qp = torch.randn(starts[-1], hkv * group, d, generator=g).to(torch.bfloat16)
+    outp = torch.zeros(starts[-1], hkv * group, d, dtype=torch.float32)
+    for i, s in enumerate(lens):
+        n, q0 = q_lens[i], starts[i]
+        ctx = s - n
+        pg = table[i, : -(-s // page)].tolist()
+        keep = torch.arange(s)[None, :] <= (ctx + torch.arange(n))[:, None]
+        for hh in range(hkv * group):
+            kk = torch.cat([k[p, hh // group] for p in pg])[:s]
+            vv = torch.cat([v[p, hh // group] for p in pg])[:s]
+            outp[q0:q0 + n, hh] = ref.softmax_v64(qp[q0:q0 + n, hh], kk, vv, d ** -0.5, keep)
     noisy = (out + 3e-3 * torch.randn(out.shape, generator=g)).to(torch.bfloat16)
     torch.save({"q": q, "k": k, "v": v, "table": table, "lens": torch.tensor(lens, dtype=torch.int32),
-                "out": out, "noisy": noisy, "rel": ref.rel(noisy, out), "ulps": ref.ulps(noisy, out),
+                "out": out, "noisy": noisy, "prefill_q": qp, "prefill_q_start": torch.tensor(starts, dtype=torch.int32),
+                "prefill_out": outp, "rel": ref.rel(noisy, out), "ulps": ref.ulps(noisy, out),
                 "ULPS": ref.ULPS, "TOL": ref.TOL}, os.path.join(HERE, "attn_golden.pt"))
 
 

@@ -1,0 +1,138 @@
+"""Paged prefill against the float64 oracle, through the C ABI. Cases are those of the reference's
+tests/hk/gpu/test_paged_prefill.py:86-125: no prefix with a short second tile, a cached prefix with
+a chunk shorter than a tile, a tile that runs into the next request, a ragged batch with a
+one-token request, requests outside the work list untouched, every GQA group, head_dim 64 -- plus
+NaN past the ends, vLLM's NHD layout, pages of 32, and a long prompt."""
+
+import pytest
+import torch
+
+from oracle import paged_oracle as orc
+
+pytestmark = pytest.mark.gpu
+PAGE = 16
+
+
+def _case(reqs, head_dim=128, h_kv=2, group=4, seed=0, page=PAGE, nan_past=False, layout="hnd"):
+    """reqs: [(ctx, q_len)]. Every request's whole sequence is in the cache; its last q_len tokens
+    are the queries (tests/hk/gpu/test_paged_prefill.py:30-51)."""
+    g = torch.Generator().manual_seed(seed)
+    r = len(reqs)
+    seq = [c + n for c, n in reqs]
+    max_pages = max(1, max(-(-s // page) for s in seq))
+    nb = r * max_pages + 5
+    k = torch.randn(nb, h_kv, page, head_dim, generator=g).to(torch.bfloat16)
+    v = torch.randn(nb, h_kv, page, head_dim, generator=g).to(torch.bfloat16)
+    table = torch.randperm(nb, generator=g)[: r * max_pages].reshape(r, max_pages).to(torch.int32).contiguous()
+    if nan_past:
+        live = torch.zeros(nb, page, dtype=torch.bool)
+        for i, s in enumerate(seq):
+            for j in range(-(-s // page)):
+                live[int(table[i, j]), : min(page, s - j * page)] = True
+        dead = ~live[:, None, :, None]
+        k, v = k.masked_fill(dead, float("nan")), v.masked_fill(dead, float("nan"))
+    n_tok = sum(n for _, n in reqs)
+    q = torch.randn(n_tok, h_kv * group, head_dim, generator=g).to(torch.bfloat16)
+    starts = [0]
+    for _, n in reqs:
+        starts.append(starts[-1] + n)
+    if layout == "nhd":
+        k, v = k.transpose(1, 2).contiguous().transpose(1, 2), v.transpose(1, 2).contiguous().transpose(1, 2)
+    return q, k, v, table, torch.tensor(seq, dtype=torch.int32), torch.tensor(starts, dtype=torch.int32)
+
+
+def _run(reqs, prefill=None, **kw):
+    from hk_dsl_b200.ops import paged
+
+    q, k, v, table, lens, q_start = _case(reqs, **kw)
+    clean = _case(reqs, **dict(kw, nan_past=False)) if kw.get("nan_past") else (q, k, v, table, lens, q_start)
+    n_tok, h, d = q.shape
+    out = torch.full(q.shape, 7.0, device="cuda", dtype=torch.bfloat16)
+    which = range(len(reqs)) if prefill is None else prefill
+    rows = paged.prefill_tile_rows(h, k.shape[1])
+    work = paged.work_list([(r, reqs[r][1]) for r in which], rows, "cuda", seq_lens=lens.tolist())
+    paged.paged_prefill(out, q.cuda(), k.cuda().transpose(1, 2), v.cuda().transpose(1, 2), table.cuda(), lens.cuda(),
+                        q_start.cuda(), work, d ** -0.5)
+    torch.cuda.synchronize()
+    want = orc.paged_prefill_ref(clean[0], clean[1].transpose(1, 2), clean[2].transpose(1, 2), table, lens, q_start)
+    return out, want, q_start
+
+
+def test_no_prefix_two_tiles_the_second_short():
+    got, want, _ = _run([(0, 300)])
+    orc.check(got, want)
+
+
+def test_a_cached_prefix_and_a_chunk_shorter_than_a_tile():
+    got, want, _ = _run([(1000, 77)])
+    orc.check(got, want)
+
+
+def test_a_tile_that_runs_into_the_next_request():
+    got, want, _ = _run([(64, 100), (300, 50), (0, 200)])
+    orc.check(got, want)
+
+
+def test_ragged_batch_with_a_one_token_request():
+    got, want, _ = _run([(0, 192), (500, 5), (40, 600), (33, 1)])
+    orc.check(got, want)
+    orc.check_baseline(got, want)
+
+
+def test_rows_of_requests_not_in_the_work_list_are_untouched():
+    reqs = [(0, 40), (128, 70), (10, 30)]
+    got, want, q_start = _run(reqs, prefill=[1])
+    a, b = int(q_start[1]), int(q_start[2])
+    orc.check(got[a:b], want[a:b])
+    assert (got[:a] == 7.0).all() and (got[b:] == 7.0).all()
+
+
+@pytest.mark.parametrize("group", [1, 2, 3, 4, 6, 8, 16])
+def test_every_gqa_group(group):
+    got, want, _ = _run([(37, 150), (0, 17), (260, 1)], group=group, seed=group)
+    orc.check(got, want)
+
+
+def test_head_dim_64():
+    got, want, _ = _run([(100, 90), (0, 33)], head_dim=64, group=4, seed=3)
+    orc.check(got, want)
+
+
+def test_nan_past_the_ends_never_reaches_the_answer():
+    got, want, _ = _run([(0, 300), (1000, 77), (5, 1), (16, 16)], nan_past=True, seed=5)
+    assert torch.isfinite(got.float()).all()
+    orc.check(got, want)
+
+
+@pytest.mark.parametrize("page", [32, 48])
+def test_pages_of_a_multiple_of_16(page):
+    got, want, _ = _run([(100, 90), (0, 130)], page=page, seed=page)
+    orc.check(got, want)
+
+
+def test_vllm_nhd_layout():
+    got, want, _ = _run([(64, 100), (0, 200)], layout="nhd", h_kv=4, seed=6)
+    orc.check(got, want)
+
+
+def test_a_long_prompt_and_a_long_prefix():
+    got, want, _ = _run([(0, 2100), (4000, 300)], h_kv=1, group=4, seed=7)
+    orc.check(got, want)
+
+
+def test_refusals():
+    from hk_dsl_b200.ops import paged
+    from hk_dsl_b200.runtime.lib import HkbError
+
+    q, k, v, table, lens, q_start = _case([(0, 40)])
+    kw = dict(block_tables=table.cuda(), seq_lens=lens.cuda(), query_start_loc=q_start.cuda(),
+              work=paged.work_list([(0, 40)], 32, "cuda"), scale=0.1)
+    out = torch.empty_like(q).cuda()
+    with pytest.raises(TypeError):
+        paged.paged_prefill(out, q.cuda(), k.cuda().transpose(1, 2), v.cuda().transpose(1, 2),
+                            **dict(kw, seq_lens=lens.long().cuda()))
+    with pytest.raises(ValueError):
+        paged.paged_prefill(out, q.cuda().float(), k.cuda().transpose(1, 2), v.cuda().transpose(1, 2), **kw)
+    k8 = k.cuda().to(torch.float8_e4m3fn).transpose(1, 2)
+    with pytest.raises(HkbError, match="no kernel"):
+        paged.paged_prefill(out, q.cuda(), k8, k8, kv_cache_dtype="fp8", **kw)

@@ -71,7 +71,7 @@ def test_unified_attention_stand_in_as_vllm_calls_it(route, order, group):
                             lens_t.cuda(), max(lens), 128 ** -0.5, True, (-1, -1), table.cuda(), 0.0, None, None,
                             None)
     orc.check(out, want)
-    assert route.PATCH.stats == {"decode": 1, "fallback": 0}
+    assert route.PATCH.stats == {"prefill": 0, "decode": 1, "fallback": 0}
 
 
 def test_the_stand_in_under_graph_capture_and_padding(route):
@@ -280,3 +280,94 @@ def test_guard_bands_around_everything_written(group, splits):
         assert (raw[:4096] == CAN).all() and (raw[-4096:] == CAN).all()
     want = orc.paged_decode_ref(q.cpu(), kc.cpu().transpose(1, 2), vc.cpu().transpose(1, 2), table, lens_t)
     orc.check(out, want)
+
+
+def _mixed_case(reqs, hkv=8, group=4, d=128, page=16, seed=0):
+    """reqs: [(ctx, q_len)]; the whole sequence of each is in the cache, the last q_len tokens query."""
+    g = torch.Generator().manual_seed(seed)
+    seq = [c + n for c, n in reqs]
+    pages = [max(1, -(-s // page)) for s in seq]
+    nb = sum(pages) + 3
+    k = torch.randn(nb, hkv, page, d, generator=g).to(torch.bfloat16)
+    v = torch.randn(nb, hkv, page, d, generator=g).to(torch.bfloat16)
+    perm = torch.randperm(nb, generator=g)
+    table = torch.zeros(len(reqs), max(pages), dtype=torch.int32)
+    at = 0
+    for i, n in enumerate(pages):
+        table[i, :n] = perm[at:at + n].to(torch.int32)
+        at += n
+    n_tok = sum(n for _, n in reqs)
+    q = torch.randn(n_tok, hkv * group, d, generator=g).to(torch.bfloat16)
+    starts = [0]
+    for _, n in reqs:
+        starts.append(starts[-1] + n)
+    return q, k, v, table, torch.tensor(seq, dtype=torch.int32), torch.tensor(starts, dtype=torch.int32)
+
+
+def test_backend_forward_on_a_batch_with_prefill_in_it():
+    """Decodes first, then a chunk with a cached prefix and a fresh prompt: the step's K/V rows are
+    written by slot, then one prefill launch serves every request (a decode is a one-row tile)."""
+    from hk_dsl_b200.integration import vllm_backend
+
+    hq, hkv, d, page = 32, 8, 128, 16
+    reqs = [(700, 1), (33, 1), (1000, 77), (0, 300)]
+    q, k, v, table, lens, q_start = _mixed_case(reqs, hkv=hkv, seed=41)
+    n = q.shape[0]
+    g = torch.Generator().manual_seed(43)
+    key = torch.randn(n, hkv, d, generator=g).to(torch.bfloat16)
+    value = torch.randn(n, hkv, d, generator=g).to(torch.bfloat16)
+    slots = []
+    for i, (ctx, ql) in enumerate(reqs):
+        pos = torch.arange(ctx, ctx + ql)
+        slots.append(table[i, pos // page].long() * page + pos % page)
+    slots = torch.cat(slots)
+    want_k, want_v = k.transpose(1, 2).contiguous(), v.transpose(1, 2).contiguous()
+    orc.reshape_and_cache_ref(key, value, want_k, want_v, slots)
+    want = orc.paged_prefill_ref(q, want_k, want_v, table, lens, q_start)
+
+    kv = torch.stack([k, v]).cuda()
+    impl = vllm_backend.HKAttentionImplCore(hq, d, d ** -0.5, hkv, None, None, "auto")
+    md = vllm_backend.metadata(n, slots.cuda(), table.cuda(), lens.cuda(), max_query_len=300,
+                               query_start_loc=q_start.cuda())
+    out = torch.full((n, hq * d), 7.0, device="cuda", dtype=torch.bfloat16)
+    vllm_backend.PATCH.reset()
+    impl.forward(None, q.cuda().view(n, hq * d), key.cuda(), value.cuda(), kv, md, output=out)
+    torch.cuda.synchronize()
+    orc.check(out.view(n, hq, d), want)
+    assert vllm_backend.PATCH.stats == {"decode": 0, "prefill": 1}
+    # a prefill step is never captured: it reads query lengths on the host
+    from hk_dsl_b200.integration import engine
+    qd = q.cuda().view(n, hq * d)
+    with pytest.raises(engine.GraphCaptureError, match="prefill"):
+        with torch.cuda.graph(torch.cuda.CUDAGraph()):
+            impl.forward(None, qd, None, None, kv, md, output=out)
+    torch.cuda.synchronize()
+
+
+def test_unified_attention_stand_in_takes_a_batch_with_prefill(route):
+    reqs = [(64, 100), (300, 1), (0, 200)]
+    q, k, v, table, lens, q_start = _mixed_case(reqs, hkv=2, group=8, seed=44)
+    want = orc.paged_prefill_ref(q, k.transpose(1, 2), v.transpose(1, 2), table, lens, q_start)
+    out = torch.full(q.shape, 7.0, device="cuda", dtype=torch.bfloat16)
+    route.unified_attention(q.cuda(), k.cuda().transpose(1, 2), v.cuda().transpose(1, 2), out, q_start.cuda(), 200,
+                            lens.cuda(), 300, 128 ** -0.5, True, (-1, -1), table.cuda(), 0.0, None, None, None)
+    torch.cuda.synchronize()
+    orc.check(out, want)
+    assert route.PATCH.stats == {"prefill": 1, "decode": 0, "fallback": 0}
+
+
+def test_prefill_torch_op():
+    from hk_dsl_b200.ops import paged
+    from hk_dsl_b200.runtime import torch_ext
+
+    reqs = [(100, 90), (0, 33)]
+    q, k, v, table, lens, q_start = _mixed_case(reqs, hkv=2, group=4, seed=45)
+    want = orc.paged_prefill_ref(q, k.transpose(1, 2), v.transpose(1, 2), table, lens, q_start)
+    n, hq, d = q.shape
+    op = torch_ext.prefill_op(d, 4)
+    assert op.name == "hk::paged_prefill_d128_g4"
+    tiles = paged.work_list([(0, 90), (1, 33)], paged.prefill_tile_rows(hq, 2), "cuda")
+    out = torch.empty(n, hq * d, device="cuda", dtype=torch.bfloat16)
+    torch.ops.hk.paged_prefill_d128_g4(q.cuda().view(n, hq * d), k.cuda(), v.cuda(), table.cuda(), lens.cuda(),
+                                       q_start.cuda(), tiles, out)
+    orc.check(out.view(n, hq, d), want)

@@ -21,6 +21,13 @@ def test_decode_oracle_equals_the_references_float64_softmax():
     assert (fp32 - g["out"]).abs().max().item() < 1e-5
 
 
+def test_prefill_oracle_equals_the_references_masked_softmax():
+    g = torch.load(os.path.join(GOLD, "attn_golden.pt"))
+    got = orc.paged_prefill_ref(g["prefill_q"], g["k"].transpose(1, 2), g["v"].transpose(1, 2), g["table"], g["lens"],
+                                g["prefill_q_start"])
+    assert (got - g["prefill_out"]).abs().max().item() < 1e-6
+
+
 def test_tolerance_functions_equal_the_references():
     g = torch.load(os.path.join(GOLD, "attn_golden.pt"))
     assert orc.ULPS == g["ULPS"] and orc.TOL == g["TOL"]

@@ -90,7 +90,7 @@ def test_untaken_calls_fall_back_to_the_engine_and_are_counted(on_b200):
     assert vllm_prefill.unified_attention(**a) == "engine"
     assert vllm_prefill.unified_attention(*a.values()) == "engine"            # positional, as vLLM calls it
     assert _stub_unified.calls == 2
-    assert vllm_prefill.PATCH.stats == {"decode": 0, "fallback": 2}
+    assert vllm_prefill.PATCH.stats == {"prefill": 0, "decode": 0, "fallback": 2}
 
 
 def test_switch_off_sends_everything_back(on_b200, monkeypatch):
@@ -111,6 +111,34 @@ def test_a_taken_call_never_reaches_the_engine_and_has_no_cpu_path(on_b200):
     with pytest.raises(RuntimeError, match="no CPU path"):
         vllm_prefill.unified_attention(**_args())
     assert _stub_unified.calls == 0
+
+
+def test_prefill_calls_are_judged_by_their_own_predicate(on_b200):
+    a = _args(max_seqlen_q=7)
+    assert vllm_prefill.u_why_not(a) == ""
+    assert "softcap set" in vllm_prefill.u_why_not(_args(max_seqlen_q=7, softcap=30.0))
+    assert "not causal" in vllm_prefill.u_why_not(_args(max_seqlen_q=7, causal=False))
+    fp8 = _args(max_seqlen_q=7, dtype=torch.float8_e4m3fn, k_descale=torch.ones(1), v_descale=torch.ones(1))
+    assert "prefill reads bf16 caches" in vllm_prefill.u_why_not(fp8)
+    assert vllm_prefill.unified_attention(**_args(max_seqlen_q=7, softcap=30.0)) == "engine"
+    assert vllm_prefill.PATCH.stats == {"prefill": 0, "decode": 0, "fallback": 1}
+    with pytest.raises(RuntimeError, match="no CPU path"):      # taken: the launch refuses CPU tensors
+        vllm_prefill.unified_attention(**a)
+
+
+def test_work_list_orders_long_tiles_first():
+    from hk_dsl_b200.ops import paged
+
+    assert paged.prefill_tile_rows(32, 8) == 32 and paged.prefill_tile_rows(8, 8) == 128
+    assert paged.prefill_tile_rows(64, 8) == 16 and paged.prefill_tile_rows(6, 2) == 128
+    w = paged.work_list([(0, 40), (2, 70)], 32, "cpu").tolist()
+    assert sorted(w) == [[0, 0], [0, 32], [2, 0], [2, 32], [2, 64]]
+    w = paged.work_list([(0, 40), (1, 33)], 32, "cpu", seq_lens=[40, 1033]).tolist()
+    assert w[0] == [1, 32] and w[1] == [1, 0]                       # the tiles that see the most keys lead
+    lib_rows = __import__("hk_dsl_b200.runtime.lib", fromlist=["load"]).load().hkb_prefill_tile_rows
+    for hq, hkv in ((32, 8), (8, 8), (64, 8), (6, 2), (24, 8), (16, 1)):
+        assert lib_rows(hq, hkv) == paged.prefill_tile_rows(hq, hkv)
+    assert lib_rows(7, 2) == 0
 
 
 def test_decode_switch_parsing():
@@ -221,9 +249,13 @@ def test_backend_prefill_batches_raise_and_checks_metadata():
     md = vllm_backend.metadata(4, torch.zeros(4, dtype=torch.int64), torch.zeros(2, 8, dtype=torch.int32),
                                torch.ones(2, dtype=torch.int32), max_query_len=3)
     kv = torch.zeros(2, 4, 8, 16, 128, dtype=torch.bfloat16)
-    with pytest.raises(NotImplementedError, match="prefill"):
+    md.query_start_loc = torch.tensor([0, 3, 4], dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="no CPU path"):          # a prefill batch is taken; CPU tensors are not
         impl.forward(None, torch.zeros(4, 32 * 128, dtype=torch.bfloat16), None, None, kv, md,
                      output=torch.zeros(4, 32 * 128, dtype=torch.bfloat16))
+    with pytest.raises(NotImplementedError, match="fp8"):
+        _impl(kv_cache_dtype="fp8").forward(None, torch.zeros(4, 32 * 128, dtype=torch.bfloat16), None, None, kv, md,
+                                            output=torch.zeros(4, 32 * 128, dtype=torch.bfloat16))
     with pytest.raises(NotImplementedError, match="output quant"):
         impl.forward(None, None, None, None, kv, md, output=None, output_scale=torch.ones(1))
     with pytest.raises(TypeError, match="int32"):
