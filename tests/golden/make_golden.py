@@ -1,9 +1,9 @@
 """Generate the golden fixtures that pin the oracle to the reference's own code.
 
-Run in the build container, where the reference checkout is mounted (its path is the first
-argument, default /root/reference); the fixtures travel, the reference does not:
+Run where a checkout of the reference (hk-dsl) is available; its path is the first argument or
+the HK_DSL_REFERENCE environment variable. The fixtures travel, the reference does not:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/hk-dsl
 
 What is executed from the reference, unmodified:
   * tests/hk/gpu/_attn_ref.py, loaded by path: `softmax_v64`, `rel`, `ulps` (the float64
@@ -27,7 +27,9 @@ import sys
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("HK_DSL_REFERENCE", "")
+if not REF or not os.path.isdir(REF):
+    sys.exit("usage: python tests/golden/make_golden.py /path/to/hk-dsl")
 
 
 def load_by_path(name, path):
