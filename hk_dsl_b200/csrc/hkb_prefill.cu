@@ -11,7 +11,8 @@
 // warps; a warp owns a 16-row query tile of ONE query head (its Q fragments stay in registers)
 // and the warps of a CTA are the GP heads of the GQA group times 8 / GP consecutive 16-token
 // tiles, so one staged K/V block serves the whole group. K/V blocks of 64 tokens (4 pages of
-// 16) come through the page table into a 2-stage cp.async ring, XOR-swizzled for ldmatrix;
+// 16) come through the page table into a 2-stage cp.async ring, XOR-swizzled for ldmatrix (fp8
+// tiles land in a raw ring and the warp that fetched a tile widens it to bf16, exactly);
 // S = Q K^T and O += P V are mma.sync.m16n8k16 bf16 with P reused from the S accumulators;
 // online softmax in exp2 with a lazy reference. This is a dense contraction whose roofline
 // is the tensor pipe; mma.sync is the baseline form of it, not the tcgen05 form.
@@ -39,9 +40,11 @@ struct PrefillArgs {
   const int* work;   // (request, first query row of the tile inside the request) pairs
   int num_q_heads, num_kv_heads, group, tiles_per_page;
   float scale;
+  const float* k_scale;   // fp8 caches: per-tensor dequantisation scales (device pointers), else NULL
+  const float* v_scale;
 };
 
-template <int D, int GP>
+template <int D, int GP, bool FP8>
 struct Prefill {
   static constexpr int WARPS = 8;
   static constexpr int TOK_TILES = WARPS / GP;        // 16-token query tiles a CTA
@@ -49,12 +52,15 @@ struct Prefill {
   static constexpr int KV_TILES = 4;                  // 16-token KV tiles a stage
   static constexpr int KVB = 16 * KV_TILES;
   static constexpr int NST = 2;
-  static constexpr int ROWB = D * 2;
+  static constexpr int ROWB = D * 2;                 // a row as the mma reads it (bf16)
+  static constexpr int ROWC = FP8 ? D : D * 2;        // a row as it sits in the cache
   static constexpr int KD = D / 16;
-  using Loader = TileLoader<ROWB>;
-  static constexpr int TILE_BYTES = Loader::TILE_BYTES;
+  using Loader = TileLoader<ROWC>;
+  static constexpr int TILE_BYTES = TILE_TOKENS * ROWB;
+  static constexpr int RAW_TILE_BYTES = Loader::TILE_BYTES;
   static constexpr int STAGE_BYTES = KV_TILES * 2 * TILE_BYTES;
-  static constexpr int SMEM_BYTES = NST * STAGE_BYTES;
+  static constexpr int RAW_STAGE_BYTES = FP8 ? KV_TILES * 2 * RAW_TILE_BYTES : 0;   // fp8 tiles land here first
+  static constexpr int SMEM_BYTES = NST * (STAGE_BYTES + RAW_STAGE_BYTES);
   static constexpr float RESCALE_LOG2 = 8.f;
 
   // One warp fills one (tile, K|V) of a stage; rows at or past `kv_limit` are zero-filled
@@ -63,7 +69,7 @@ struct Prefill {
                                               int kv_limit, const int* table_row, int warp, int lane) {
     const int t = warp >> 1, which = warp & 1;
     const int tok0 = kv0 + 16 * t;
-    const uint32_t dst = stage + (t * 2 + which) * TILE_BYTES;
+    const uint32_t dst = stage + (t * 2 + which) * (FP8 ? RAW_TILE_BYTES : TILE_BYTES);
     const int valid = min(16, kv_limit - tok0);      // rows of this tile that hold attendable keys
     if (valid <= 0) {
       for (int x = lane; x < 16 * Loader::CPR; x += 32)
@@ -80,7 +86,7 @@ struct Prefill {
     for (int it = 0; it < Loader::ITERS; ++it) {
       const int x = it * 32 + lane;
       const int r = x / Loader::CPR, c = x % Loader::CPR;
-      const uint32_t d = dst + tile_off<ROWB>(r, c);
+      const uint32_t d = dst + tile_off<ROWC>(r, c);
       if (r < valid) cp_async16(d, p + (int64_t)r * st + c * 16);
       else asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(d), "r"(0u) : "memory");
     }
@@ -124,7 +130,9 @@ struct Prefill {
 #pragma unroll
       for (int i = 0; i < 4; ++i) o[nt][i] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    const float qs = a.scale * LOG2E;
+    float qs = a.scale * LOG2E;
+    float vs = 1.f;
+    if (FP8) { qs *= __ldg(a.k_scale); vs = __ldg(a.v_scale); }
     const bool warp_live = wrow0 < q_len;                       // a warp whose 16 rows are all past the request idles
 
     Loader ld;
@@ -135,13 +143,24 @@ struct Prefill {
     ld.tiles_per_page = a.tiles_per_page; ld.num_blocks = a.num_blocks;
     const int* table_row = a.block_table + (int64_t)req * a.table_stride;
     const uint32_t ring = smem_u32(smem);
+    const uint32_t raw = ring + NST * STAGE_BYTES;   // fp8 only: where the copies land before they are widened
+    const uint32_t land = FP8 ? raw : ring;
+    constexpr int LAND_BYTES = FP8 ? RAW_STAGE_BYTES : STAGE_BYTES;
 
-    fill(a, ld, ring, 0, kv_limit, table_row, warp, lane);
+    fill(a, ld, land, 0, kv_limit, table_row, warp, lane);
     cp_async_commit();
     for (int b = 0; b < n_blocks; ++b) {
       cp_async_wait<0>();
+      if (FP8) {
+        // the warp that fetched a tile widens it to bf16 (exact) into block b's stage. Every warp
+        // is past its work on block b-2, the stage's previous tenant (the barrier of iteration b-1).
+        __syncwarp();
+        const int tw = warp >> 1, which = warp & 1;
+        WalkMMA<D, true, 1, 4, 4>::widen(raw + (b & 1) * RAW_STAGE_BYTES + (tw * 2 + which) * RAW_TILE_BYTES,
+                                         ring + (b & 1) * STAGE_BYTES + (tw * 2 + which) * TILE_BYTES, lane);
+      }
       __syncthreads();   // block b has landed for every warp; block b-1's stage is free again
-      if (b + 1 < n_blocks) fill(a, ld, ring + ((b + 1) & 1) * STAGE_BYTES, (b + 1) * KVB, kv_limit, table_row, warp, lane);
+      if (b + 1 < n_blocks) fill(a, ld, land + ((b + 1) & 1) * LAND_BYTES, (b + 1) * KVB, kv_limit, table_row, warp, lane);
       cp_async_commit();
       const uint32_t stage = ring + (b & 1) * STAGE_BYTES;
       const int kv0 = b * KVB;
@@ -236,7 +255,7 @@ struct Prefill {
     for (int c = 0; c < 2; ++c)
 #pragma unroll
       for (int x = 1; x < 4; x <<= 1) l[c] += __shfl_xor_sync(0xffffffffu, l[c], x);
-    const float iA = l[0] > 0.f ? 1.f / l[0] : 0.f, iB = l[1] > 0.f ? 1.f / l[1] : 0.f;
+    const float iA = l[0] > 0.f ? vs / l[0] : 0.f, iB = l[1] > 0.f ? vs / l[1] : 0.f;
     __nv_bfloat16* oA = a.out + (int64_t)(q0 + rA) * a.out_stride_tok + (int64_t)hq * a.out_stride_head;
     __nv_bfloat16* oB = a.out + (int64_t)(q0 + rB) * a.out_stride_tok + (int64_t)hq * a.out_stride_head;
 #pragma unroll
@@ -248,38 +267,38 @@ struct Prefill {
   }
 };
 
-template <int D, int GP>
+template <int D, int GP, bool FP8>
 __global__ void __launch_bounds__(256) prefill_kernel(const PrefillArgs a) {
   extern __shared__ __align__(128) uint8_t hkb_smem[];
-  Prefill<D, GP>::run(a, hkb_smem);
+  Prefill<D, GP, FP8>::run(a, hkb_smem);
 }
 
-template <int D, int GP>
+template <int D, int GP, bool FP8>
 static int launch_prefill(const PrefillArgs& a, int num_work, cudaStream_t st) {
   static bool armed[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
-  constexpr int smem = Prefill<D, GP>::SMEM_BYTES;
+  constexpr int smem = Prefill<D, GP, FP8>::SMEM_BYTES;
   if (e == cudaSuccess && dev >= 0 && dev < 64 && !armed[dev]) {
-    e = cudaFuncSetAttribute(prefill_kernel<D, GP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    e = cudaFuncSetAttribute(prefill_kernel<D, GP, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e == cudaSuccess) armed[dev] = true;
   }
   if (e == cudaSuccess) {
     dim3 grid(num_work, a.num_kv_heads * (a.group / GP));
-    prefill_kernel<D, GP><<<grid, 256, smem, st>>>(a);
+    prefill_kernel<D, GP, FP8><<<grid, 256, smem, st>>>(a);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
   return HKB_OK;
 }
 
-template <int D>
+template <int D, bool FP8>
 static int dispatch_prefill(const PrefillArgs& a, int num_work, cudaStream_t st) {
   // heads of the GQA group a CTA serves: the largest of 8, 4, 2, 1 that divides the group
-  if (a.group % 8 == 0) return launch_prefill<D, 8>(a, num_work, st);
-  if (a.group % 4 == 0) return launch_prefill<D, 4>(a, num_work, st);
-  if (a.group % 2 == 0) return launch_prefill<D, 2>(a, num_work, st);
-  return launch_prefill<D, 1>(a, num_work, st);
+  if (a.group % 8 == 0) return launch_prefill<D, 8, FP8>(a, num_work, st);
+  if (a.group % 4 == 0) return launch_prefill<D, 4, FP8>(a, num_work, st);
+  if (a.group % 2 == 0) return launch_prefill<D, 2, FP8>(a, num_work, st);
+  return launch_prefill<D, 1, FP8>(a, num_work, st);
 }
 
 }  // namespace hkb
@@ -298,7 +317,8 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
                                  const int32_t* seq_lens, const int32_t* q_start,
                                  const int32_t* work, int num_work,
                                  int num_q_heads, int num_kv_heads, int head_dim, int block_size,
-                                 float scale, int kv_dtype, void* stream) {
+                                 float scale, int kv_dtype, const float* k_scale, const float* v_scale,
+                                 void* stream) {
   using namespace hkb;
   if (num_work < 0 || num_q_heads <= 0 || num_kv_heads <= 0) return HKB_ERR_SIZE;
   if (num_work == 0) return HKB_OK;
@@ -306,12 +326,16 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
   if (head_dim != 64 && head_dim != 128) return HKB_ERR_HEAD_DIM;
   if (block_size <= 0 || block_size % TILE_TOKENS) return HKB_ERR_BLOCK_SIZE;
   if (num_q_heads % num_kv_heads || num_q_heads / num_kv_heads > HKB_MAX_GROUP) return HKB_ERR_GROUP;
-  if (kv_dtype != HKB_KV_BF16) return kv_dtype == HKB_KV_FP8_E4M3 ? HKB_ERR_UNSUPPORTED : HKB_ERR_DTYPE;
+  if (kv_dtype != HKB_KV_BF16 && kv_dtype != HKB_KV_FP8_E4M3) return HKB_ERR_DTYPE;
+  const bool fp8 = kv_dtype == HKB_KV_FP8_E4M3;
+  if (fp8 && (!k_scale || !v_scale)) return HKB_ERR_SCALE;
+  if (fp8 && head_dim != 128) return HKB_ERR_UNSUPPORTED;
+  const int es = fp8 ? 1 : 2;
   if (max_pages < 1 || kc.num_blocks < 1 || vc.num_blocks < 1) return HKB_ERR_SIZE;
   const int group = num_q_heads / num_kv_heads;
   if ((int64_t)num_kv_heads * group > 65535) return HKB_ERR_SIZE;
   const int64_t kv_strides = kc.stride_block | kc.stride_token | kc.stride_head | vc.stride_block | vc.stride_token | vc.stride_head;
-  if ((kv_strides * 2) % 16) return HKB_ERR_STRIDE;
+  if ((kv_strides * es) % 16) return HKB_ERR_STRIDE;
   if ((q_stride_tok | q_stride_head | out_stride_tok | out_stride_head) % 2) return HKB_ERR_STRIDE;
   if (((uintptr_t)kc.ptr | (uintptr_t)vc.ptr) % 16 || ((uintptr_t)q | (uintptr_t)out) % 4) return HKB_ERR_ALIGN;
 
@@ -319,8 +343,8 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
   a.out = (__nv_bfloat16*)out; a.out_stride_tok = out_stride_tok; a.out_stride_head = out_stride_head;
   a.q = (const __nv_bfloat16*)q; a.q_stride_tok = q_stride_tok; a.q_stride_head = q_stride_head;
   a.k = (const uint8_t*)kc.ptr; a.v = (const uint8_t*)vc.ptr;
-  a.k_stride_block = kc.stride_block * 2; a.k_stride_token = kc.stride_token * 2; a.k_stride_head = kc.stride_head * 2;
-  a.v_stride_block = vc.stride_block * 2; a.v_stride_token = vc.stride_token * 2; a.v_stride_head = vc.stride_head * 2;
+  a.k_stride_block = kc.stride_block * es; a.k_stride_token = kc.stride_token * es; a.k_stride_head = kc.stride_head * es;
+  a.v_stride_block = vc.stride_block * es; a.v_stride_token = vc.stride_token * es; a.v_stride_head = vc.stride_head * es;
   const int64_t nb = kc.num_blocks < vc.num_blocks ? kc.num_blocks : vc.num_blocks;
   a.num_blocks = nb > 0x7fffffff ? 0x7fffffff : (int)nb;
   a.block_table = block_table; a.table_stride = table_stride; a.max_pages = max_pages;
@@ -328,6 +352,9 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
   a.num_q_heads = num_q_heads; a.num_kv_heads = num_kv_heads; a.group = group;
   a.tiles_per_page = block_size / TILE_TOKENS;
   a.scale = scale;
+  a.k_scale = fp8 ? k_scale : nullptr;
+  a.v_scale = fp8 ? v_scale : nullptr;
   cudaStream_t st = (cudaStream_t)stream;
-  return head_dim == 128 ? dispatch_prefill<128>(a, num_work, st) : dispatch_prefill<64>(a, num_work, st);
+  if (fp8) return dispatch_prefill<128, true>(a, num_work, st);
+  return head_dim == 128 ? dispatch_prefill<128, false>(a, num_work, st) : dispatch_prefill<64, false>(a, num_work, st);
 }

@@ -184,16 +184,14 @@ class HKAttentionImplCore:
         # A step with prefill in it: every new token's K/V is in the cache by now, so ONE paged
         # prefill launch over a host-built work list serves the whole batch -- chunks, cached
         # prefixes and the one-token decodes riding along (a lone token is a one-row tile).
-        self._prefill(query, output, k_cache, v_cache, attn_metadata, n)
+        self._prefill(query, output, k_cache, v_cache, attn_metadata, n, layer)
         PATCH.count("prefill")
         return output
 
-    def _prefill(self, query, output, k_cache, v_cache, attn_metadata, n):
+    def _prefill(self, query, output, k_cache, v_cache, attn_metadata, n, layer=None):
         """The batch's rows as (tokens, heads, head_dim); the work list comes from the metadata
         builder (`hk_prefill_work`, built on the host where the query lengths already are) or, for
         a caller without one, from query_start_loc read back here (never under capture)."""
-        if self.kv_cache_dtype != "auto":
-            raise NotImplementedError(f"{NAME}: prefill over an fp8 KV cache is not built; decode is")
         hq, d = self.num_heads, self.head_size
         work = getattr(attn_metadata, "hk_prefill_work", None)
         qsl = attn_metadata.query_start_loc
@@ -206,7 +204,7 @@ class HKAttentionImplCore:
                                    paged.prefill_tile_rows(hq, self.num_kv_heads), query.device)
         paged.paged_prefill(output[:n].view(n, hq, d), query[:n].view(n, hq, d), k_cache.transpose(1, 2),
                             v_cache.transpose(1, 2), attn_metadata.block_table, attn_metadata.seq_lens, qsl, work,
-                            self.scale)
+                            self.scale, self.kv_cache_dtype, *_kv_scales(layer, query.device))
 
     def _decode_all(self, query, output, k_cache, v_cache, attn_metadata, n, layer=None):
         """Every request has exactly one token: the walk and its merge, reading the query and
@@ -285,6 +283,7 @@ def _build():
     class HKAttentionBackend(AttentionBackend):
         accept_output_buffer: bool = True
         supported_dtypes: ClassVar[list] = [torch.bfloat16]
+        supported_kv_cache_dtypes: ClassVar[list] = ["auto", "bfloat16", "fp8", "fp8_e4m3"]
 
         @staticmethod
         def get_name() -> str:

@@ -188,7 +188,7 @@ def _decode(q, out, k, v, block_table, seq_lens, q_start, scale, k_descale, v_de
 def u_why_not(a: dict) -> str:
     """Why this unified_attention call WITH prefill in it is not taken, or "". The same checks as
     a decode-only call, minus decode-only, plus: never under capture (the grid follows query
-    lengths read on the host), bf16 caches only."""
+    lengths read on the host)."""
     if switches.arch() not in ARCHES:
         return f"arch {switches.arch()}"
     if engine.capturing():
@@ -201,10 +201,8 @@ def u_why_not(a: dict) -> str:
     unknown = _unknown_set(a, _U_SIG, _U_READ | _U_OFF.keys())
     if unknown:
         return f"{unknown} set (an argument hk does not know)"
-    if a["k"].dtype != torch.bfloat16:
-        return f"cache dtype {a['k'].dtype} (prefill reads bf16 caches)"
     return _common_why_not(a["q"], a["out"], a["k"], a["v"], a["block_table"], a["seqused_k"],
-                           a.get("cu_seqlens_q"), None, None)
+                           a.get("cu_seqlens_q"), a.get("k_descale"), a.get("v_descale"))
 
 
 def _prefill(a: dict) -> bool:
@@ -216,8 +214,10 @@ def _prefill(a: dict) -> bool:
     work = paged.work_list([(r, starts[r + 1] - starts[r]) for r in range(reqs)],
                            paged.prefill_tile_rows(hq, int(k.shape[2])), q.device)
     sc = a.get("softmax_scale")
+    fp8 = k.dtype != torch.bfloat16
     paged.paged_prefill(out, q, k, a["v"], a["block_table"], a["seqused_k"], a["cu_seqlens_q"], work,
-                        d ** -0.5 if sc is None else float(sc))
+                        d ** -0.5 if sc is None else float(sc), "fp8" if fp8 else "auto",
+                        a.get("k_descale") if fp8 else None, a.get("v_descale") if fp8 else None)
     return True
 
 

@@ -258,10 +258,11 @@ def work_list(reqs, tile_rows: int, device, seq_lens=None) -> torch.Tensor:
 
 def paged_prefill(out: torch.Tensor, query: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
                   block_tables: torch.Tensor, seq_lens: torch.Tensor, query_start_loc: torch.Tensor,
-                  work: torch.Tensor, scale: float, kv_cache_dtype: str = "auto") -> torch.Tensor:
+                  work: torch.Tensor, scale: float, kv_cache_dtype: str = "auto",
+                  k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of every request's new tokens over its paged cache (prefix + new tokens,
     already written). `query`/`out` `(tokens, q_heads, head_dim)` bf16; caches
-    `(blocks, block_size, kv_heads, head_dim)` bf16 views; `seq_lens` the tokens in the cache a
+    `(blocks, block_size, kv_heads, head_dim)` views, bf16 or fp8-e4m3 with per-tensor scales; `seq_lens` the tokens in the cache a
     request (int32), `query_start_loc` cu_seqlens_q (int32, requests + 1); `work` from `work_list`.
     Requests that are not in `work` keep their output rows untouched."""
     _need_cuda(out, query, key_cache, value_cache, block_tables, seq_lens, query_start_loc, work)
@@ -281,12 +282,14 @@ def paged_prefill(out: torch.Tensor, query: torch.Tensor, key_cache: torch.Tenso
     if work.dim() != 2 or work.shape[1] != 2 or not work.is_contiguous():
         raise ValueError("hk.ops.paged: work must be (items, 2) int32 (work_list)")
     code = kv_dtype_code(kv_cache_dtype, key_cache)
+    fp8 = code == _lib.KV_FP8_E4M3
     _, bs, hkv, _ = key_cache.shape
     rc = _lib.load().hkb_paged_prefill(
         out.data_ptr(), out.stride(0), out.stride(1), query.data_ptr(), query.stride(0), query.stride(1),
         _cache_t(key_cache), _cache_t(value_cache), block_tables.data_ptr(), block_tables.stride(0),
         block_tables.shape[1], seq_lens.data_ptr(), query_start_loc.data_ptr(), work.data_ptr(), work.shape[0],
-        hq, hkv, d, bs, float(scale), code, _stream(query))
+        hq, hkv, d, bs, float(scale), code, _scale_ptr(k_scale, fp8, "k_scale"), _scale_ptr(v_scale, fp8, "v_scale"),
+        _stream(query))
     _lib.check("hkb_paged_prefill", rc)
     return out
 

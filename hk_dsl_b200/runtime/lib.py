@@ -54,7 +54,7 @@ SIGNATURES = {
                                         c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "hkb_paged_prefill": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, CacheT, CacheT,
                                   c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                  c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
+                                  c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p]),
     "hkb_prefill_tile_rows": (c_int, [c_int, c_int]),
     "hkb_merge": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p,
                           c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),

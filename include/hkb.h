@@ -171,7 +171,8 @@ int hkb_merge(void* out, int64_t out_stride_tok, int64_t out_stride_head, int ou
  * `work` is a device array of num_work (request, first row) int32 pairs, one a query tile of
  * hkb_prefill_tile_rows(num_q_heads, num_kv_heads) rows (the host builds it: query lengths
  * are host values in a prefill step; put long tiles first). Rows of requests that are not in
- * the work list are not written. bf16 caches only (HKB_ERR_UNSUPPORTED for fp8).
+ * the work list are not written. bf16 caches, or fp8-e4m3 with per-tensor k_scale / v_scale
+ * (device pointers to one float each; head_dim 128).
  *
  * Replaces: paged_prefill_kernel and its work list (python/hk/ops/paged_prefill.py:59-620,
  * 879-968) as launched from python/hk/integration/vllm_backend.py:667-698.
@@ -183,7 +184,8 @@ int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_stride_head
                       const int32_t* seq_lens, const int32_t* q_start,
                       const int32_t* work, int num_work,
                       int num_q_heads, int num_kv_heads, int head_dim, int block_size,
-                      float scale, int kv_dtype, void* stream);
+                      float scale, int kv_dtype, const float* k_scale, const float* v_scale,
+                      void* stream);
 
 /* Query rows one work item of hkb_paged_prefill covers (16..128, by GQA group); 0 if the
  * head counts are not a valid GQA shape. */

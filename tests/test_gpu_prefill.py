@@ -134,5 +134,30 @@ def test_refusals():
     with pytest.raises(ValueError):
         paged.paged_prefill(out, q.cuda().float(), k.cuda().transpose(1, 2), v.cuda().transpose(1, 2), **kw)
     k8 = k.cuda().to(torch.float8_e4m3fn).transpose(1, 2)
-    with pytest.raises(HkbError, match="no kernel"):
+    with pytest.raises(ValueError, match="k_scale"):          # an fp8 cache needs its scales
         paged.paged_prefill(out, q.cuda(), k8, k8, kv_cache_dtype="fp8", **kw)
+    q64, k64, _, _, _, _ = _case([(0, 40)], head_dim=64)
+    k64 = k64.cuda().to(torch.float8_e4m3fn).transpose(1, 2)
+    one = torch.ones(1, device="cuda")
+    with pytest.raises(HkbError, match="no kernel"):           # fp8 prefill is built for head_dim 128
+        paged.paged_prefill(torch.empty_like(q64).cuda(), q64.cuda(), k64, k64, kv_cache_dtype="fp8", k_scale=one,
+                            v_scale=one, **kw)
+
+
+@pytest.mark.parametrize("group", [1, 4, 8])
+def test_fp8_cache_against_the_dequantised_oracle(group):
+    from hk_dsl_b200.ops import paged
+
+    reqs = [(0, 300), (1000, 77), (33, 1), (64, 100)]
+    q, k, v, table, lens, q_start = _case(reqs, group=group, seed=20 + group)
+    ks, vs = torch.tensor([0.0125]), torch.tensor([0.011])
+    k8, v8 = orc.quantize_fp8(k, ks), orc.quantize_fp8(v, vs)
+    want = orc.paged_prefill_ref(q, orc.dequantize_fp8(k8, ks).transpose(1, 2), orc.dequantize_fp8(v8, vs).transpose(1, 2),
+                                 table, lens, q_start)
+    out = torch.full(q.shape, 7.0, device="cuda", dtype=torch.bfloat16)
+    work = paged.work_list([(r, n) for r, (_, n) in enumerate(reqs)], paged.prefill_tile_rows(q.shape[1], 2), "cuda")
+    paged.paged_prefill(out, q.cuda(), k8.cuda().transpose(1, 2), v8.cuda().transpose(1, 2), table.cuda(), lens.cuda(),
+                        q_start.cuda(), work, 128 ** -0.5, "fp8", ks.cuda(), vs.cuda())
+    torch.cuda.synchronize()
+    orc.check(out, want)
+    orc.check_baseline(out, want)

@@ -119,7 +119,8 @@ def test_prefill_calls_are_judged_by_their_own_predicate(on_b200):
     assert "softcap set" in vllm_prefill.u_why_not(_args(max_seqlen_q=7, softcap=30.0))
     assert "not causal" in vllm_prefill.u_why_not(_args(max_seqlen_q=7, causal=False))
     fp8 = _args(max_seqlen_q=7, dtype=torch.float8_e4m3fn, k_descale=torch.ones(1), v_descale=torch.ones(1))
-    assert "prefill reads bf16 caches" in vllm_prefill.u_why_not(fp8)
+    assert vllm_prefill.u_why_not(fp8) == ""
+    assert "fp8 cache without" in vllm_prefill.u_why_not(_args(max_seqlen_q=7, dtype=torch.float8_e4m3fn))
     assert vllm_prefill.unified_attention(**_args(max_seqlen_q=7, softcap=30.0)) == "engine"
     assert vllm_prefill.PATCH.stats == {"prefill": 0, "decode": 0, "fallback": 1}
     with pytest.raises(RuntimeError, match="no CPU path"):      # taken: the launch refuses CPU tensors
@@ -253,9 +254,7 @@ def test_backend_prefill_batches_raise_and_checks_metadata():
     with pytest.raises(RuntimeError, match="no CPU path"):          # a prefill batch is taken; CPU tensors are not
         impl.forward(None, torch.zeros(4, 32 * 128, dtype=torch.bfloat16), None, None, kv, md,
                      output=torch.zeros(4, 32 * 128, dtype=torch.bfloat16))
-    with pytest.raises(NotImplementedError, match="fp8"):
-        _impl(kv_cache_dtype="fp8").forward(None, torch.zeros(4, 32 * 128, dtype=torch.bfloat16), None, None, kv, md,
-                                            output=torch.zeros(4, 32 * 128, dtype=torch.bfloat16))
+
     with pytest.raises(NotImplementedError, match="output quant"):
         impl.forward(None, None, None, None, kv, md, output=None, output_scale=torch.ones(1))
     with pytest.raises(TypeError, match="int32"):
