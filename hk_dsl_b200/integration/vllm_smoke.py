@@ -1,6 +1,6 @@
 """End-to-end smoke of the attention backend inside a real vLLM engine, without weights.
 
-    python -m hk_dsl_b200.integration.vllm_smoke [--graphs] [--kv fp8]
+    python -m hk_dsl_b200.integration.vllm_smoke [--graphs] [--kv fp8] [--route]
 
 Builds a two-layer Llama-shaped model with random ("dummy") weights from a config written to
 a temporary directory, runs the same token prompts greedily through vLLM twice in one process
@@ -9,6 +9,9 @@ plugin's own code path (`HK_VLLM_BACKEND=1`, `_vllm_plugin.register()`) -- and c
 log-probabilities the two engines assign to the tokens they generate. It exercises, inside the
 engine: the metadata builder (work list for prefill steps), the cache write, paged prefill,
 paged decode and, with --graphs, decode steps captured by vLLM into CUDA graphs.
+
+With --route the second engine keeps vLLM's own TRITON_ATTN backend and the test covers the
+in-place route instead (`HK_VLLM_PREFILL=1`: vLLM's unified_attention rebound to the stand-in).
 
 The engine core runs in this process (VLLM_ENABLE_V1_MULTIPROCESSING=0) so that the backend
 registered here is the one it resolves; in a served deployment the `vllm.general_plugins`
@@ -66,24 +69,28 @@ def main(argv=None) -> int:
     ap.add_argument("--graphs", action="store_true", help="let vLLM capture decode steps into CUDA graphs")
     ap.add_argument("--kv", default="auto", help="kv_cache_dtype: auto | fp8")
     ap.add_argument("--max-tokens", type=int, default=24)
+    ap.add_argument("--route", action="store_true",
+                    help="test the in-place route instead: vLLM keeps its TRITON_ATTN backend and cache, and its "
+                         "unified_attention calls are rebound to this build's stand-in (HK_VLLM_PREFILL=1)")
     args = ap.parse_args(argv)
     os.environ.setdefault("VLLM_ENABLE_V1_MULTIPROCESSING", "0")
-    os.environ["HK_VLLM_BACKEND"] = "1"
-    os.environ["HK_VLLM_PREFILL"] = "0"
+    os.environ["HK_VLLM_BACKEND"] = "0" if args.route else "1"
+    os.environ["HK_VLLM_PREFILL"] = "1" if args.route else "0"
 
     import torch
 
-    from . import _vllm_plugin, vllm_backend
+    from . import _vllm_plugin, vllm_backend, vllm_prefill
 
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(3, 2000, (n,), generator=g).tolist() for n in (5, 37, 300, 1, 1025, 64)]
     with tempfile.TemporaryDirectory() as d:
         tiny_config(d)
-        base = run(d, None, prompts, args.max_tokens, args.graphs, args.kv)
+        base = run(d, "TRITON_ATTN" if args.route else None, prompts, args.max_tokens, args.graphs, args.kv)
         _vllm_plugin.register()
-        vllm_backend.PATCH.reset()
-        ours = run(d, vllm_backend.SLOT, prompts, args.max_tokens, args.graphs, args.kv)
-    stats = dict(vllm_backend.PATCH.stats), dict(vllm_backend.PATCH.captured)
+        patch = vllm_prefill.PATCH if args.route else vllm_backend.PATCH
+        patch.reset()
+        ours = run(d, "TRITON_ATTN" if args.route else vllm_backend.SLOT, prompts, args.max_tokens, args.graphs, args.kv)
+    stats = dict(patch.stats), dict(patch.captured)
     worst, same = 0.0, 0
     for (tb, lb), (to, lo) in zip(base, ours):
         n = 0
@@ -95,7 +102,8 @@ def main(argv=None) -> int:
     total = sum(len(t) for t, _ in base)
     print(json.dumps({"prompts": len(prompts), "tokens_generated": total, "tokens_identical_prefix": same,
                       "worst_logprob_gap_on_shared_prefix": round(worst, 4), "eager_calls": stats[0],
-                      "captured_calls": stats[1], "graphs": args.graphs, "kv_cache_dtype": args.kv}))
+                      "captured_calls": stats[1], "graphs": args.graphs, "kv_cache_dtype": args.kv,
+                      "surface": "in-place route (vLLM's TRITON_ATTN backend and cache)" if args.route else "backend"}))
     ok = stats[0].get("decode", 0) + stats[1].get("decode", 0) > 0 and stats[0].get("prefill", 0) > 0 and worst < 0.1
     return 0 if ok else 1
 
