@@ -290,7 +290,11 @@ def main():
         dec = paged_dist.SplitKVDecoder(n, st.q_heads, st.kv_heads, d, dev, splits)
         splits = dec.local_splits
     scratch = paged.split_scratch(n, st.q_heads, d, splits, dev) if splits > 1 else None
-    launches_per_step = 1 + 1 + (1 if splits > 1 else 0) + (1 if kvsplit else 0)   # ours; NCCL's not counted
+    # ours; NCCL's not counted. One GPU's step is paged.decode_step: the walk writes the new rows
+    # itself (2 launches with the merge); a KV-split step keeps the write apart (write, walk,
+    # local merge, merge of the gathered partials)
+    joined = not kvsplit and splits > 1 and n <= 2048
+    launches_per_step = (2 if joined else 1 + 1 + (1 if splits > 1 else 0)) + (1 if kvsplit else 0)
 
     def write(l, key=st.key, value=st.value, slots=st.slot_mapping):
         paged.reshape_and_cache(key, value, st.k_caches[l], st.v_caches[l], slots, spec.kv_cache_dtype,
@@ -307,12 +311,14 @@ def main():
 
     def step(i, **kw):
         l = i % layers
-        write(l)
         if kvsplit:
+            write(l)
             dec.decode(st.out, st.query, st.k_caches[l], st.v_caches[l], st.block_table, st.seq_lens, st.scale,
                        spec.kv_cache_dtype, st.k_scale, st.v_scale)
         else:
-            walk(l, merge=True)
+            paged.decode_step(st.out, st.query, st.key, st.value, st.k_caches[l], st.v_caches[l], st.slot_mapping,
+                              st.block_table, st.seq_lens, st.scale, spec.kv_cache_dtype, st.k_scale, st.v_scale,
+                              num_splits=splits, scratch=scratch)
 
     def barrier():
         if world > 1:
@@ -421,15 +427,15 @@ def main():
     def e2e_step(i):
         l = i % layers
         stage_d.copy_(stage_h, non_blocking=True)
-        paged.reshape_and_cache(devb["key"], devb["value"], st.k_caches[l], st.v_caches[l], devb["slot_mapping"],
-                                spec.kv_cache_dtype, st.k_scale, st.v_scale)
         if kvsplit:
+            paged.reshape_and_cache(devb["key"], devb["value"], st.k_caches[l], st.v_caches[l], devb["slot_mapping"],
+                                    spec.kv_cache_dtype, st.k_scale, st.v_scale)
             dec.decode(st.out, devb["query"], st.k_caches[l], st.v_caches[l], devb["block_table"],
                        devb["seq_lens"], st.scale, spec.kv_cache_dtype, st.k_scale, st.v_scale)
         else:
-            paged.paged_attention_decode(st.out, devb["query"], st.k_caches[l], st.v_caches[l], devb["block_table"],
-                                         devb["seq_lens"], st.scale, spec.kv_cache_dtype, st.k_scale, st.v_scale,
-                                         num_splits=splits, scratch=scratch)
+            paged.decode_step(st.out, devb["query"], devb["key"], devb["value"], st.k_caches[l], st.v_caches[l],
+                              devb["slot_mapping"], devb["block_table"], devb["seq_lens"], st.scale,
+                              spec.kv_cache_dtype, st.k_scale, st.v_scale, num_splits=splits, scratch=scratch)
         out_host.copy_(st.out, non_blocking=True)
         torch.cuda.current_stream().synchronize()      # the caller reads the result before the next step
 
@@ -444,7 +450,8 @@ def main():
     e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / K
     e2e = {"value": kv_total / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
-           "api": "hk_dsl_b200.ops.paged.reshape_and_cache + paged_attention_decode"}
+           "api": "hk_dsl_b200.ops.paged.decode_step" if not kvsplit else
+           "hk_dsl_b200.ops.paged.reshape_and_cache + paged_dist.SplitKVDecoder.decode"}
 
     clocks = sampler.stop() if sampler is not None else None
 
@@ -610,9 +617,9 @@ def sample_parity(spec, st, splits, scratch):
     from oracle import paged_oracle as orc
 
     take = min(2, len(st.lens))
-    paged.paged_attention_decode(st.out, st.query, st.k_caches[0], st.v_caches[0], st.block_table, st.seq_lens,
-                                 st.scale, spec.kv_cache_dtype, st.k_scale, st.v_scale, num_splits=splits,
-                                 scratch=scratch)
+    paged.decode_step(st.out, st.query, st.key, st.value, st.k_caches[0], st.v_caches[0], st.slot_mapping,
+                      st.block_table, st.seq_lens, st.scale, spec.kv_cache_dtype, st.k_scale, st.v_scale,
+                      num_splits=splits, scratch=scratch)
     torch.cuda.synchronize()
     bs = spec.block_size
     rows = []

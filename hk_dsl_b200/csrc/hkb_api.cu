@@ -60,6 +60,14 @@ extern "C" int hkb_plan_splits(int num_seqs, int num_kv_heads, int max_tiles, in
   return (int)p;
 }
 
+// 1 + HKB_MAX_SPLITS / 16 counters (finished groups, then finished pieces of each 16-slot group) a
+// (plane, sequence); a kv head has at most two planes (a CUDA-core walk of a group of 5 to 7
+// takes its heads in two passes).
+extern "C" size_t hkb_arrivals_bytes(int num_seqs, int num_kv_heads) {
+  if (num_seqs <= 0 || num_kv_heads <= 0) return 0;
+  return (size_t)num_seqs * num_kv_heads * 2 * (1 + HKB_MAX_SPLITS / 16) * sizeof(int32_t);
+}
+
 extern "C" size_t hkb_scratch_lse_offset(int num_seqs, int num_q_heads, int head_dim, int num_splits) {
   if (num_seqs <= 0 || num_q_heads <= 0 || head_dim <= 0 || num_splits <= 0) return 0;
   size_t b = (size_t)num_seqs * num_splits * num_q_heads * head_dim * sizeof(float);

@@ -46,6 +46,22 @@ __device__ __forceinline__ float2 e4m3x2_to_float2(uint16_t x) {
   return __half22float2(h);
 }
 
+// Eight bf16 (one 16-byte chunk) -> eight e4m3 bytes of a cache with scale `den`:
+// float(x) / den in IEEE fp32 division, then round-to-nearest-even, saturating at +-448.
+__device__ __forceinline__ uint2 quantize_chunk_e4m3(const uint4& v, float den) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint32_t o[2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f;
+    f.x = __fdiv_rn(bf16lo(w[i]), den);
+    f.y = __fdiv_rn(bf16hi(w[i]), den);
+    const uint32_t p = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
+    if (i & 1) o[i >> 1] |= p << 16; else o[i >> 1] = p;
+  }
+  return make_uint2(o[0], o[1]);
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));

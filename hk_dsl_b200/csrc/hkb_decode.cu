@@ -335,16 +335,38 @@ static int dispatch_mma(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
 
 }  // namespace hkb
 
-extern "C" int hkb_paged_decode(void* out, int64_t out_stride_tok, int64_t out_stride_head,
-                                const void* q, int64_t q_stride_tok, int64_t q_stride_head,
-                                hkb_cache_t kc, hkb_cache_t vc,
-                                const int32_t* block_table, int64_t table_stride, int max_pages,
-                                const int32_t* seq_lens, const int32_t* q_start,
-                                int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
-                                int block_size, float scale, int kv_dtype,
-                                const float* k_scale, const float* v_scale,
-                                int num_splits, float* part_out, float* part_lse, void* stream) {
-  using namespace hkb;
+namespace hkb {
+
+// What the one-launch decode step adds to a walk: the step's new K/V rows and the fold counters.
+struct StepExtra {
+  const void* key = nullptr;
+  const void* value = nullptr;
+  int64_t key_stride_tok = 0, key_stride_head = 0, val_stride_tok = 0, val_stride_head = 0;
+  const void* slots = nullptr;
+  int slot_is_i64 = 0;
+  int32_t* arrivals = nullptr;
+  bool wrote = false;    // out: the walk wrote the new rows into the cache itself
+  bool folded = false;   // out: the walk folded the partials itself
+};
+
+// The stream kernel can take the whole step when its rings are single warps (every worker but
+// the paired-ring variant kept for A/B runs).
+static bool step_fusable(int num_splits, int num_seqs) {
+  static const bool fixed = [] { const char* v = std::getenv("HKB_FIXED_SPLITS"); return v && v[0] == '1'; }();
+  static const bool pair = [] { const char* v = std::getenv("HKB_CC_RING"); return v && v[0] == 'p'; }();
+  static const bool off = [] { const char* v = std::getenv("HKB_STEP_UNFUSED"); return v && v[0] == '1'; }();
+  return num_splits > 1 && num_seqs <= STREAM_MAX_SEQS && !fixed && !pair && !off;
+}
+
+static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_head,
+                       const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                       hkb_cache_t kc, hkb_cache_t vc,
+                       const int32_t* block_table, int64_t table_stride, int max_pages,
+                       const int32_t* seq_lens, const int32_t* q_start,
+                       int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                       int block_size, float scale, int kv_dtype,
+                       const float* k_scale, const float* v_scale,
+                       int num_splits, float* part_out, float* part_lse, void* stream, StepExtra* extra) {
   if (num_seqs < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || max_pages < 0) return HKB_ERR_SIZE;
   if (num_seqs == 0) return HKB_OK;
   if (num_seqs > 65535 * 16 || num_splits > 0x7fffffff) return HKB_ERR_SIZE;
@@ -387,6 +409,22 @@ extern "C" int hkb_paged_decode(void* out, int64_t out_stride_tok, int64_t out_s
   a.k_scale = fp8 ? k_scale : nullptr;   // scales apply to fp8 caches only
   a.v_scale = fp8 ? v_scale : nullptr;
   a.num_splits = num_splits; a.part_out = part_out; a.part_lse = part_lse;
+  a.arrivals = nullptr; a.new_k = nullptr; a.new_v = nullptr;
+  a.new_k_stride_tok = a.new_k_stride_head = a.new_v_stride_tok = a.new_v_stride_head = 0;
+  a.slots = nullptr; a.slot_is_i64 = 0; a.block_size = block_size;
+  if (extra && step_fusable(num_splits, num_seqs)) {
+    if (extra->arrivals) {
+      a.arrivals = extra->arrivals;
+      extra->folded = true;
+    }
+    if (extra->key) {
+      a.new_k = (const __nv_bfloat16*)extra->key; a.new_v = (const __nv_bfloat16*)extra->value;
+      a.new_k_stride_tok = extra->key_stride_tok; a.new_k_stride_head = extra->key_stride_head;
+      a.new_v_stride_tok = extra->val_stride_tok; a.new_v_stride_head = extra->val_stride_head;
+      a.slots = extra->slots; a.slot_is_i64 = extra->slot_is_i64;
+      extra->wrote = true;
+    }
+  }
   cudaStream_t st = (cudaStream_t)stream;
 
   const bool mma = group >= 8;
@@ -395,6 +433,66 @@ extern "C" int hkb_paged_decode(void* out, int64_t out_stride_tok, int64_t out_s
     return mma ? dispatch_mma<128, false>(a, num_seqs, st) : dispatch_cc<128, false>(a, num_seqs, st);
   }
   return mma ? dispatch_mma<64, false>(a, num_seqs, st) : dispatch_cc<64, false>(a, num_seqs, st);
+}
+
+}  // namespace hkb
+
+extern "C" int hkb_paged_decode(void* out, int64_t out_stride_tok, int64_t out_stride_head,
+                                const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                                hkb_cache_t kc, hkb_cache_t vc,
+                                const int32_t* block_table, int64_t table_stride, int max_pages,
+                                const int32_t* seq_lens, const int32_t* q_start,
+                                int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                                int block_size, float scale, int kv_dtype,
+                                const float* k_scale, const float* v_scale,
+                                int num_splits, float* part_out, float* part_lse, void* stream) {
+  return hkb::decode_impl(out, out_stride_tok, out_stride_head, q, q_stride_tok, q_stride_head, kc, vc, block_table,
+                          table_stride, max_pages, seq_lens, q_start, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                          block_size, scale, kv_dtype, k_scale, v_scale, num_splits, part_out, part_lse, stream, nullptr);
+}
+
+extern "C" int hkb_decode_step(void* out, int64_t out_stride_tok, int64_t out_stride_head,
+                               const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                               const void* key, const void* value,
+                               int64_t key_stride_tok, int64_t key_stride_head,
+                               int64_t val_stride_tok, int64_t val_stride_head,
+                               const void* slot_mapping, int slot_is_i64,
+                               hkb_cache_t kc, hkb_cache_t vc,
+                               const int32_t* block_table, int64_t table_stride, int max_pages,
+                               const int32_t* seq_lens, const int32_t* q_start,
+                               int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                               int block_size, float scale, int kv_dtype,
+                               const float* k_scale, const float* v_scale,
+                               int num_splits, float* part_out, float* part_lse, int32_t* arrivals, void* stream) {
+  using namespace hkb;
+  if (num_seqs < 0) return HKB_ERR_SIZE;
+  if (num_seqs == 0) return HKB_OK;
+  if ((key == nullptr) != (value == nullptr)) return HKB_ERR_NULL;
+  if (key && !slot_mapping) return HKB_ERR_NULL;
+  if (key) {
+    // the new rows are read as 16-byte chunks, whichever launch writes them
+    if ((key_stride_tok | key_stride_head | val_stride_tok | val_stride_head) % 8) return HKB_ERR_STRIDE;
+    if (((uintptr_t)key | (uintptr_t)value) % 16) return HKB_ERR_ALIGN;
+  }
+  StepExtra x;
+  x.key = key; x.value = value;
+  x.key_stride_tok = key_stride_tok; x.key_stride_head = key_stride_head;
+  x.val_stride_tok = val_stride_tok; x.val_stride_head = val_stride_head;
+  x.slots = slot_mapping; x.slot_is_i64 = slot_is_i64; x.arrivals = arrivals;
+  if (key && !step_fusable(num_splits, num_seqs)) {   // the separate cache write: one row a sequence
+    const int rc = hkb_reshape_and_cache(key, value, key_stride_tok, key_stride_head, val_stride_tok, val_stride_head, kc,
+                                         vc, slot_mapping, slot_is_i64, num_seqs, num_kv_heads, head_dim, block_size,
+                                         kv_dtype, k_scale, v_scale, stream);
+    if (rc != HKB_OK) return rc;
+  }
+  int rc = decode_impl(out, out_stride_tok, out_stride_head, q, q_stride_tok, q_stride_head, kc, vc, block_table,
+                       table_stride, max_pages, seq_lens, q_start, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                       block_size, scale, kv_dtype, k_scale, v_scale, num_splits, part_out, part_lse, stream, &x);
+  if (rc != HKB_OK || x.folded || num_splits <= 1) return rc;
+  return hkb_merge(out, out_stride_tok, out_stride_head, 0, nullptr, part_out, (int64_t)num_q_heads * head_dim,
+                   (int64_t)num_splits * num_q_heads * head_dim, part_lse, num_q_heads,
+                   (int64_t)num_splits * num_q_heads, num_splits, num_seqs, num_q_heads, head_dim, seq_lens, q_start,
+                   stream);
 }
 
 extern "C" int hkb_merge(void* out, int64_t out_stride_tok, int64_t out_stride_head, int out_is_f32,

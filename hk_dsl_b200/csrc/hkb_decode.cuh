@@ -29,6 +29,14 @@ struct DecodeArgs {
   int num_splits;
   float* part_out;
   float* part_lse;
+  // The decode step in one launch (stream kernel only; null = off):
+  int* arrivals;                 // fold-on-arrival counters, ARRIVAL_INTS a (plane, sequence), zero between launches
+  const __nv_bfloat16* new_k;    // the step's new token of every sequence, written into the cache by the ring
+  const __nv_bfloat16* new_v;    // that walks the sequence's last tile, before it fetches that tile
+  int64_t new_k_stride_tok, new_k_stride_head, new_v_stride_tok, new_v_stride_head;   // elements
+  const void* slots;
+  int slot_is_i64;
+  int block_size;
 };
 
 // The range of 16-token tiles split `split` of a sequence with `n_tiles` tiles walks:

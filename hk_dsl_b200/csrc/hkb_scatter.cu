@@ -56,18 +56,7 @@ __global__ void __launch_bounds__(256) scatter_kernel(const ScatterArgs a, int t
     if (!FP8) {
       *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.dst[which]) + d) = v;
     } else {
-      // float(x) / scale in IEEE fp32 division, then RNE to e4m3 saturating at +-448.
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-      uint32_t o[2];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float2 f;
-        f.x = __fdiv_rn(bf16lo(w[i]), inv_scale_den);
-        f.y = __fdiv_rn(bf16hi(w[i]), inv_scale_den);
-        const uint32_t p = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
-        if (i & 1) o[i >> 1] |= p << 16; else o[i >> 1] = p;
-      }
-      *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(a.dst[which]) + d) = make_uint2(o[0], o[1]);
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(a.dst[which]) + d) = quantize_chunk_e4m3(v, inv_scale_den);
     }
   }
 }

@@ -23,11 +23,19 @@
 //     p < parts. Slots no warp will write are marked lse = -inf by the plane's first CTA.
 //     The LSE-merge kernel then folds a sequence's slots as it folds fixed splits.
 //
+// The whole decode step in this one launch (DecodeArgs::arrivals / new_k set; rings of one
+// warp): the ring that owns a sequence's last tile first writes the step's new K/V row of
+// that sequence into the cache -- its own later fetch of the tile then reads it back, no
+// other ring of the plane touches that tile -- and the ring that finishes a sequence's last
+// outstanding piece folds the partials (hkb_fold.cuh). This is hk-dsl's "cache write + walk +
+// merge as <= 2 launches" (docs/history/17-the-decode-step-captured-whole.md:181-188), as one.
+//
 // `num_splits` of the C ABI is `parts` here: still a host-known power of two, still the row
 // count of the caller's scratch, so plans and CUDA graphs behave as with fixed splits.
 #pragma once
 
 #include "hkb_decode.cuh"
+#include "hkb_fold.cuh"
 
 namespace hkb {
 
@@ -90,15 +98,33 @@ struct WalkStream {
     int range = max((total + plane_rings - 1) / plane_rings, STREAM_MIN_RANGE);
     range = max(range, (longest + parts - 2) / max(parts - 1, 1));
 
-    // slots that no ring of this plane will write: marked by all the plane's CTAs, a slice each
-    // (every warp marks the heads it owns)
-    for (int x = blockIdx.x * (RINGS * 32) + ring_id * 32 + lane; x < num_seqs * parts; x += gridDim.x * RINGS * 32) {
-      const int i = x / parts, p = x % parts;
-      const int nt = base[i + 1] - base[i];
-      const int np = nt > 0 ? (base[i] + nt - 1) / range - base[i] / range + 1 : 0;
-      if (p >= np) {
-        float* pl = a.part_lse + (int64_t)(i * parts + p) * a.num_q_heads + hq0;
-        for (int h = 0; h < nh; ++h) pl[h] = -INFINITY;
+    const bool fold = WPR == 1 && a.arrivals != nullptr;
+    if (!fold) {
+      // slots that no ring of this plane will write: marked by all the plane's CTAs, a slice each
+      // (every warp marks the heads it owns)
+      for (int x = blockIdx.x * (RINGS * 32) + ring_id * 32 + lane; x < num_seqs * parts; x += gridDim.x * RINGS * 32) {
+        const int i = x / parts, p = x % parts;
+        const int nt = base[i + 1] - base[i];
+        const int np = nt > 0 ? (base[i] + nt - 1) / range - base[i] / range + 1 : 0;
+        if (p >= np) {
+          float* pl = a.part_lse + (int64_t)(i * parts + p) * a.num_q_heads + hq0;
+          for (int h = 0; h < nh; ++h) pl[h] = -INFINITY;
+        }
+      }
+    } else {
+      // folding in this launch: no marks are read, but a sequence without tokens has no ring to
+      // write its output row -- zeros, as the merge kernel gives it
+      for (int i = blockIdx.x * (RINGS * 32) + ring_id * 32 + lane; i < num_seqs; i += gridDim.x * RINGS * 32) {
+        if (base[i + 1] != base[i]) continue;
+        int row = i;
+        if (a.q_start) {
+          row = __ldg(a.q_start + i);
+          if (__ldg(a.q_start + i + 1) <= row) continue;   // no query row either
+        }
+        for (int h = 0; h < nh; ++h) {
+          __nv_bfloat16* o = a.out + (int64_t)row * a.out_stride_tok + (int64_t)(hq0 + h) * a.out_stride_head;
+          for (int d = 0; d < P::HEAD_DIM; d += 2) *reinterpret_cast<__nv_bfloat162*>(o + d) = __floats2bfloat162_rn(0.f, 0.f);
+        }
       }
     }
 
@@ -145,6 +171,29 @@ struct WalkStream {
         ids.init(t, lane);
         fresh = false;
       }
+      if (WPR == 1 && a.new_k && t == base[seq_l + 1] - base[seq_l] - 1) {
+        // the sequence's last tile: the step's new token goes into the cache first (this kv head's
+        // K row and V row, one 16-byte chunk a lane), then the tile is fetched with it inside
+        const int row = a.q_start ? __ldg(a.q_start + seq_l) : seq_l;
+        const int64_t slot = a.slot_is_i64 ? (int64_t)__ldg(reinterpret_cast<const long long*>(a.slots) + row)
+                                           : (int64_t)__ldg(reinterpret_cast<const int*>(a.slots) + row);
+        if (slot >= 0 && slot < (int64_t)a.num_blocks * a.block_size) {
+          constexpr int CH = P::HEAD_DIM / 8;
+          const int64_t blk = slot / a.block_size, off = slot - blk * a.block_size;
+          for (int c = lane; c < 2 * CH; c += 32) {
+            const bool is_v = c >= CH;
+            const int cc = is_v ? c - CH : c;
+            const __nv_bfloat16* src = is_v ? a.new_v + (int64_t)row * a.new_v_stride_tok + (int64_t)kvh * a.new_v_stride_head
+                                            : a.new_k + (int64_t)row * a.new_k_stride_tok + (int64_t)kvh * a.new_k_stride_head;
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + cc * 8));
+            uint8_t* dst = const_cast<uint8_t*>(is_v ? ld.vbase + blk * ld.vsb + off * ld.vst : ld.kbase + blk * ld.ksb + off * ld.kst);
+            if (P::ES == 2) *reinterpret_cast<uint4*>(dst + cc * 16) = v;
+            else *reinterpret_cast<uint2*>(dst + cc * 8) = quantize_chunk_e4m3(v, __ldg(is_v ? a.v_scale : a.k_scale));
+          }
+        }
+        __threadfence_block();
+        __syncwarp();
+      }
       const uint32_t stage = ring + stage_idx * P::STAGE_BYTES;
       if (WPR == 1) ld.issue(stage, t, ids.get(t, lane), lane);
       else ld.issue_one(stage, t, ids.get(t, lane), lane, sub);
@@ -161,6 +210,22 @@ struct WalkStream {
     typename P::State st;
     int seq_c = -1, seq_end = g_lo, seq_len = 0, n_tiles = 0, seq_base = 0;
     int sc = 0, sl = P::STAGES - 1;   // ring stages of the compute and of the loader
+    int owe_seq[2] = {-1, -1}, owe_p[2] = {0, 0}, owe_np[2] = {0, 0};   // folds to run after the last tile
+    auto close_piece = [&]() {
+      const int p = min(w - seq_base / range, parts - 1);   // < parts by the choice of `range`
+      P::end(st, lane, nh, vs, a.part_out + ((int64_t)(seq_c * parts + p) * a.num_q_heads + hq0) * P::HEAD_DIM,
+             a.part_lse + (int64_t)(seq_c * parts + p) * a.num_q_heads + hq0);
+      if (fold) {
+        const int np = (seq_end - 1) / range - seq_base / range + 1;   // pieces of this sequence
+        if (np == 1) {
+          Fold<P::HEAD_DIM, P::HEADS>::single(a, seq_c, hq0, nh, lane);
+        } else if (Fold<P::HEAD_DIM, P::HEADS>::count_in(
+                       a.arrivals + ((int64_t)blockIdx.y * num_seqs + seq_c) * ARRIVAL_INTS, p, np, lane)) {
+          if (owe_seq[0] < 0) { owe_seq[0] = seq_c; owe_p[0] = p; owe_np[0] = np; }
+          else { owe_seq[1] = seq_c; owe_p[1] = p; owe_np[1] = np; }
+        }
+      }
+    };
     for (int k = 0; k < n; ++k) {
       cp_async_wait<P::STAGES - 2>();
       ring_sync<WPR>(ring_id);
@@ -168,11 +233,7 @@ struct WalkStream {
       cp_async_commit();
       const int g = g_lo + k;
       if (g >= seq_end) {
-        if (seq_c >= 0 && nh > 0) {   // close the piece of the sequence just finished
-          const int p = min(w - seq_base / range, parts - 1);   // < parts by the choice of `range`
-          P::end(st, lane, nh, vs, a.part_out + ((int64_t)(seq_c * parts + p) * a.num_q_heads + hq0) * P::HEAD_DIM,
-                 a.part_lse + (int64_t)(seq_c * parts + p) * a.num_q_heads + hq0);
-        }
+        if (seq_c >= 0 && nh > 0) close_piece();   // the piece of the sequence just finished
         seq_c = seq_c < 0 ? lo : seq_c + 1;
         while (g >= base[seq_c + 1]) ++seq_c;
         seq_base = base[seq_c];
@@ -188,10 +249,15 @@ struct WalkStream {
       sl = sl + 1 == P::STAGES ? 0 : sl + 1;
     }
     cp_async_wait<0>();
-    if (nh > 0) {
-      const int p = min(w - seq_base / range, parts - 1);
-      P::end(st, lane, nh, vs, a.part_out + ((int64_t)(seq_c * parts + p) * a.num_q_heads + hq0) * P::HEAD_DIM,
-             a.part_lse + (int64_t)(seq_c * parts + p) * a.num_q_heads + hq0);
+    if (nh > 0) close_piece();
+    if (fold) {
+#pragma unroll 1
+      for (int k = 0; k < 2; ++k) {
+        const int s = k ? owe_seq[1] : owe_seq[0];
+        if (s < 0) break;
+        Fold<P::HEAD_DIM, P::HEADS>::finish(a, a.arrivals + ((int64_t)blockIdx.y * num_seqs + s) * ARRIVAL_INTS, s,
+                                            k ? owe_p[1] : owe_p[0], k ? owe_np[1] : owe_np[0], hq0, nh, lane);
+      }
     }
   }
 };

@@ -94,6 +94,11 @@ def decode_splits(n: int, n_kv_heads: int, pages_cap: int, device=None) -> int:
     return paged.plan_splits(n, n_kv_heads, pages_cap, device=device)
 
 
+def joined_step() -> bool:
+    """HK_VLLM_JOINED_STEP=0 keeps the cache write of a decode step a launch of its own."""
+    return os.environ.get("HK_VLLM_JOINED_STEP", "1") not in ("0", "false", "off", "no")
+
+
 class HKAttentionImplCore:
     """vLLM's AttentionImpl constructor and forward, on plain tensors."""
 
@@ -171,10 +176,17 @@ class HKAttentionImplCore:
             raise NotImplementedError(f"{NAME} has no fused output quant")
         n = attn_metadata.num_actual_tokens
         k_cache, v_cache = self._kv(kv_cache)
+        decode_only = attn_metadata.max_query_len == 1      # a host int: no device read
+        new = None
         if key is not None and value is not None:
-            self._update_cache(layer, key[:n], value[:n], k_cache, v_cache, attn_metadata.slot_mapping[:n])
-        if attn_metadata.max_query_len == 1:      # a host int: no device read
-            self._decode_all(query, output, k_cache, v_cache, attn_metadata, n, layer)
+            if decode_only and joined_step():
+                # one token a request: the walk writes each request's new row itself, just before it
+                # reads the tile the row lands in (two launches a layer instead of three)
+                new = (key[:n], value[:n], attn_metadata.slot_mapping[:n])
+            else:
+                self._update_cache(layer, key[:n], value[:n], k_cache, v_cache, attn_metadata.slot_mapping[:n])
+        if decode_only:
+            self._decode_all(query, output, k_cache, v_cache, attn_metadata, n, layer, new)
             return output
         if engine.capturing():
             raise engine.GraphCaptureError(
@@ -206,9 +218,10 @@ class HKAttentionImplCore:
                             v_cache.transpose(1, 2), attn_metadata.block_table, attn_metadata.seq_lens, qsl, work,
                             self.scale, self.kv_cache_dtype, *_kv_scales(layer, query.device))
 
-    def _decode_all(self, query, output, k_cache, v_cache, attn_metadata, n, layer=None):
+    def _decode_all(self, query, output, k_cache, v_cache, attn_metadata, n, layer=None, new=None):
         """Every request has exactly one token: the walk and its merge, reading the query and
-        writing the answer where the engine keeps them."""
+        writing the answer where the engine keeps them. `new`: (key, value, slot_mapping) of the
+        step when the cache write rides in the walk."""
         hq, d = self.num_heads, self.head_size
         q = query[:n].view(n, hq, d)
         out = output[:n].view(n, hq, d)
@@ -222,8 +235,12 @@ class HKAttentionImplCore:
             po, pl = _scratch(query.device, hq, d, self._scratch_rows(query.device))
             scratch = (po, pl)
         ks, vs = _kv_scales(layer, query.device)
-        paged.paged_attention_decode(out, q, k_cache.transpose(1, 2), v_cache.transpose(1, 2), table, lens,
-                                     self.scale, self.kv_cache_dtype, ks, vs, num_splits=splits, scratch=scratch)
+        if new is not None:
+            paged.decode_step(out, q, new[0], new[1], k_cache.transpose(1, 2), v_cache.transpose(1, 2), new[2], table,
+                              lens, self.scale, self.kv_cache_dtype, ks, vs, num_splits=splits, scratch=scratch)
+        else:
+            paged.paged_attention_decode(out, q, k_cache.transpose(1, 2), v_cache.transpose(1, 2), table, lens,
+                                         self.scale, self.kv_cache_dtype, ks, vs, num_splits=splits, scratch=scratch)
         PATCH.count("decode")
 
     def _check(self, table, lens):

@@ -149,23 +149,8 @@ def split_scratch(num_seqs: int, num_q_heads: int, head_dim: int, num_splits: in
             torch.empty(rows, num_q_heads, device=device, dtype=torch.float32))
 
 
-def paged_attention_decode(out: torch.Tensor, query: torch.Tensor, key_cache: torch.Tensor,
-                           value_cache: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor,
-                           scale: float, kv_cache_dtype: str = "auto",
-                           k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None, *,
-                           num_splits: Optional[int] = None,
-                           scratch: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
-                           query_start_loc: Optional[torch.Tensor] = None,
-                           max_seq_len: Optional[int] = None, merge: bool = True) -> torch.Tensor:
-    """Decode attention of one query token a sequence over a block-paged KV cache.
-
-    `query`/`out`: `(tokens, q_heads, head_dim)` bf16 (head_dim contiguous); caches
-    `(blocks, block_size, kv_heads, head_dim)` views, bf16 or fp8-e4m3 with per-tensor
-    `k_scale`/`v_scale`; `block_tables` `(seqs, max_pages)` int32; `seq_lens` `(seqs,)` int32.
-    `num_splits` None plans it from the batch and the table's width (host values only);
-    with more than one split the walk writes partials into `scratch` (allocated here if
-    not given -- pass it to stay allocation-free) and the merge kernel folds them
-    (`merge=False` stops after the walk and leaves the partials in `scratch`)."""
+def _decode_call(out, query, key_cache, value_cache, block_tables, seq_lens, query_start_loc):
+    """Validate the tensors of a decode call; returns (seqs, q_heads, head_dim, block_size, kv_heads, q_start ptr)."""
     _need_cuda(out, query, key_cache, value_cache, block_tables, seq_lens)
     if query.dim() != 3 or query.dtype != torch.bfloat16 or query.stride(2) != 1:
         raise ValueError(f"hk.ops.paged: query is {tuple(query.shape)} {query.dtype}; the decode reads "
@@ -197,20 +182,46 @@ def paged_attention_decode(out: torch.Tensor, query: torch.Tensor, key_cache: to
         qsl = query_start_loc.data_ptr()
     elif query.shape[0] < n:
         raise ValueError(f"hk.ops.paged: {query.shape[0]} query rows for {n} sequences")
+    return n, hq, d, bs, hkv, qsl
+
+
+def _scratch_ptrs(scratch, n, hq, d, num_splits, device):
+    if num_splits <= 1:
+        return None, None, scratch
+    if scratch is None:
+        scratch = split_scratch(n, hq, d, num_splits, device)
+    po, pl = scratch[0], scratch[1]
+    if po.dtype != torch.float32 or pl.dtype != torch.float32 or po.numel() < n * num_splits * hq * d \
+            or pl.numel() < n * num_splits * hq or not po.is_contiguous() or not pl.is_contiguous():
+        raise ValueError(f"hk.ops.paged: scratch too small or not contiguous fp32 for {n} sequences x "
+                         f"{num_splits} splits x {hq} heads x {d} (split_scratch)")
+    return po, pl, scratch
+
+
+def paged_attention_decode(out: torch.Tensor, query: torch.Tensor, key_cache: torch.Tensor,
+                           value_cache: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor,
+                           scale: float, kv_cache_dtype: str = "auto",
+                           k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None, *,
+                           num_splits: Optional[int] = None,
+                           scratch: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                           query_start_loc: Optional[torch.Tensor] = None,
+                           max_seq_len: Optional[int] = None, merge: bool = True) -> torch.Tensor:
+    """Decode attention of one query token a sequence over a block-paged KV cache.
+
+    `query`/`out`: `(tokens, q_heads, head_dim)` bf16 (head_dim contiguous); caches
+    `(blocks, block_size, kv_heads, head_dim)` views, bf16 or fp8-e4m3 with per-tensor
+    `k_scale`/`v_scale`; `block_tables` `(seqs, max_pages)` int32; `seq_lens` `(seqs,)` int32.
+    `num_splits` None plans it from the batch and the table's width (host values only);
+    with more than one split the walk writes partials into `scratch` (allocated here if
+    not given -- pass it to stay allocation-free) and the merge kernel folds them
+    (`merge=False` stops after the walk and leaves the partials in `scratch`)."""
+    n, hq, d, bs, hkv, qsl = _decode_call(out, query, key_cache, value_cache, block_tables, seq_lens, query_start_loc)
     code = kv_dtype_code(kv_cache_dtype, key_cache)
     fp8 = code == _lib.KV_FP8_E4M3
     if num_splits is None:
         tiles = block_tables.shape[1] * (bs // 16) if max_seq_len is None else -(-max_seq_len // 16)
         num_splits = plan_splits(n, hkv, tiles, device=query.device)
-    po = pl = None
-    if num_splits > 1:
-        if scratch is None:
-            scratch = split_scratch(n, hq, d, num_splits, query.device)
-        po, pl = scratch
-        if po.dtype != torch.float32 or pl.dtype != torch.float32 or po.numel() < n * num_splits * hq * d \
-                or pl.numel() < n * num_splits * hq or not po.is_contiguous() or not pl.is_contiguous():
-            raise ValueError(f"hk.ops.paged: scratch too small or not contiguous fp32 for {n} sequences x "
-                             f"{num_splits} splits x {hq} heads x {d} (split_scratch)")
+    po, pl, scratch = _scratch_ptrs(scratch, n, hq, d, num_splits, query.device)
     lib = _lib.load()
     st = _stream(query)
     rc = lib.hkb_paged_decode(
@@ -225,6 +236,78 @@ def paged_attention_decode(out: torch.Tensor, query: torch.Tensor, key_cache: to
                            po.data_ptr(), hq * d, num_splits * hq * d, pl.data_ptr(), hq, num_splits * hq,
                            num_splits, n, hq, d, seq_lens.data_ptr(), qsl, st)
         _lib.check("hkb_merge", rc)
+    return out
+
+
+def step_arrivals(num_seqs: int, num_kv_heads: int, device) -> torch.Tensor:
+    """The arrival counters `decode_step` needs: zeroed once here, left zero by every step.
+    One array a stream -- two steps in flight at once must not share it."""
+    return torch.zeros(_lib.load().hkb_arrivals_bytes(num_seqs, num_kv_heads) // 4, device=device, dtype=torch.int32)
+
+
+def decode_step(out: torch.Tensor, query: torch.Tensor, key: Optional[torch.Tensor], value: Optional[torch.Tensor],
+                key_cache: torch.Tensor, value_cache: torch.Tensor, slot_mapping: Optional[torch.Tensor],
+                block_tables: torch.Tensor, seq_lens: torch.Tensor, scale: float, kv_cache_dtype: str = "auto",
+                k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None, *,
+                num_splits: Optional[int] = None, scratch: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                arrivals: Optional[torch.Tensor] = None, query_start_loc: Optional[torch.Tensor] = None,
+                max_seq_len: Optional[int] = None) -> torch.Tensor:
+    """One decode step of a layer: `reshape_and_cache(key, value, ...)` then
+    `paged_attention_decode(out, query, ...)`, in two launches instead of three -- or in one.
+
+    The backend's decode step is a cache write and two launches
+    (python/hk/integration/vllm_backend.py:582-599, 700-729); here the ring of the walk that owns
+    a sequence's last tile writes the new row first, then the merge kernel runs. `key`/`value`:
+    `(seqs, kv_heads, head_dim)` bf16, one new token a sequence, `slot_mapping[i]` = the slot of
+    position `seq_lens[i] - 1` of sequence i (negative: skipped); both None when the cache is
+    already written. With `arrivals` (`step_arrivals`) the walk also folds the partials -- the ring
+    that finishes a sequence's last piece does it -- and the step is one launch; measured, that
+    pays only for small evenly cut batches, so it is opt-in. `scratch` is allocated here if not
+    given. Shapes the stream kernel does not take (one split, more than 2048 sequences) run the
+    separate launches."""
+    n, hq, d, bs, hkv, qsl = _decode_call(out, query, key_cache, value_cache, block_tables, seq_lens, query_start_loc)
+    if (key is None) != (value is None):
+        raise ValueError("hk.ops.paged: decode_step takes key and value together")
+    kp = vp = sp = None
+    kst = (0, 0, 0, 0)
+    slot64 = 0
+    if key is not None:
+        _need_cuda(key, value, slot_mapping)
+        if key.dim() != 3 or value.shape != key.shape or key.dtype != torch.bfloat16 or value.dtype != key.dtype \
+                or key.shape[1] != hkv or key.shape[2] != d or key.stride(2) != 1 or value.stride(2) != 1:
+            raise ValueError(f"hk.ops.paged: key {tuple(key.shape)} {key.dtype} / value {tuple(value.shape)} "
+                             f"{value.dtype}; the step writes (seqs, {hkv}, {d}) bfloat16 rows")
+        if slot_mapping.dim() != 1 or slot_mapping.dtype not in (torch.int64, torch.int32) \
+                or not slot_mapping.is_contiguous():
+            raise TypeError(f"hk.ops.paged: slot_mapping is {tuple(slot_mapping.shape)} {slot_mapping.dtype}; "
+                            f"contiguous int64 or int32 needed")
+        rows = query.shape[0] if query_start_loc is not None else n
+        if key.shape[0] < rows or slot_mapping.shape[0] < rows:
+            raise ValueError(f"hk.ops.paged: {key.shape[0]} new rows / {slot_mapping.shape[0]} slots for {rows} query rows")
+        kp, vp, sp = key.data_ptr(), value.data_ptr(), slot_mapping.data_ptr()
+        kst = (key.stride(0), key.stride(1), value.stride(0), value.stride(1))
+        slot64 = 1 if slot_mapping.dtype == torch.int64 else 0
+    code = kv_dtype_code(kv_cache_dtype, key_cache)
+    fp8 = code == _lib.KV_FP8_E4M3
+    if num_splits is None:
+        tiles = block_tables.shape[1] * (bs // 16) if max_seq_len is None else -(-max_seq_len // 16)
+        num_splits = plan_splits(n, hkv, tiles, device=query.device)
+    po, pl, scratch = _scratch_ptrs(scratch, n, hq, d, num_splits, query.device)
+    lib = _lib.load()
+    if num_splits > 1 and arrivals is not None:
+        if arrivals.dtype != torch.int32 or not arrivals.is_contiguous() \
+                or arrivals.numel() * 4 < lib.hkb_arrivals_bytes(n, hkv):
+            raise ValueError(f"hk.ops.paged: arrivals too small or not contiguous int32 for {n} sequences x {hkv} "
+                             f"kv heads (step_arrivals)")
+        _need_cuda(arrivals)
+    rc = lib.hkb_decode_step(
+        out.data_ptr(), out.stride(0), out.stride(1), query.data_ptr(), query.stride(0), query.stride(1),
+        kp, vp, *kst, sp, slot64, _cache_t(key_cache), _cache_t(value_cache), block_tables.data_ptr(),
+        block_tables.stride(0), block_tables.shape[1], seq_lens.data_ptr(), qsl, n, hq, hkv, d, bs, float(scale), code,
+        _scale_ptr(k_scale, fp8, "k_scale"), _scale_ptr(v_scale, fp8, "v_scale"), num_splits,
+        po.data_ptr() if po is not None else None, pl.data_ptr() if pl is not None else None,
+        arrivals.data_ptr() if arrivals is not None and num_splits > 1 else None, _stream(query))
+    _lib.check("hkb_decode_step", rc)
     return out
 
 

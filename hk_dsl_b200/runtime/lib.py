@@ -52,6 +52,12 @@ SIGNATURES = {
     "hkb_paged_decode_static": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, CacheT, CacheT,
                                         c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                         c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "hkb_decode_step": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64,
+                                c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int,
+                                CacheT, CacheT, c_void_p, c_int64, c_int, c_void_p, c_void_p,
+                                c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
+                                c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "hkb_arrivals_bytes": (c_size_t, [c_int, c_int]),
     "hkb_paged_prefill": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, CacheT, CacheT,
                                   c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                   c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p]),

@@ -10,6 +10,8 @@ names are registered on demand onto ONE runtime-parameterised C entry point:
     hk::reshape_and_cache(key, value, key_cache!, value_cache!, slot_mapping, kv_cache_dtype, k_scale, v_scale)
     hk::paged_attention_decode(out!, query, key_cache, value_cache, block_tables, seq_lens, scale,
                                kv_cache_dtype, k_scale, v_scale, num_splits, part_out!, part_lse!)
+    hk::paged_decode_step(out!, query, key, value, key_cache!, value_cache!, slot_mapping, block_tables, seq_lens,
+                          scale, kv_cache_dtype, k_scale, v_scale, num_splits, part_out!, part_lse!)
     hk::paged_decode_fused_d{D}_s{S}(q, k_cache, v_cache, block_table, seq_lens, out!, o_part!, ml_part!)
     hk::paged_merge_d{D}_s{S}(seq_lens, out!, o_part, ml_part)
     hk::paged_prefill_d{D}_g{G}(q, k_cache, v_cache, block_table, seq_lens, q_start, tiles, out!)
@@ -53,6 +55,23 @@ def _paged_attention_decode(out, query, key_cache, value_cache, block_tables, se
     paged.paged_attention_decode(out, query, key_cache, value_cache, block_tables, seq_lens, scale,
                                  kv_cache_dtype, k_scale, v_scale, num_splits=num_splits,
                                  scratch=(part_out, part_lse) if num_splits > 1 else None)
+
+
+def _paged_decode_step(out, query, key, value, key_cache, value_cache, slot_mapping, block_tables, seq_lens, scale,
+                       kv_cache_dtype, k_scale, v_scale, num_splits, part_out, part_lse):
+    paged.decode_step(out, query, key, value, key_cache, value_cache, slot_mapping, block_tables, seq_lens, scale,
+                      kv_cache_dtype, k_scale, v_scale, num_splits=num_splits,
+                      scratch=(part_out, part_lse) if num_splits > 1 else None)
+
+
+def paged_decode_step_op() -> engine.Op:
+    """The cache write of a decode step and its attention as one op: the walk writes the new rows
+    (two launches where `reshape_and_cache` + `paged_attention_decode` are three)."""
+    return _define(
+        "paged_decode_step",
+        "(Tensor(a!) out, Tensor query, Tensor key, Tensor value, Tensor(b!) key_cache, Tensor(c!) value_cache, "
+        "Tensor slot_mapping, Tensor block_tables, Tensor seq_lens, float scale, str kv_cache_dtype, Tensor k_scale, "
+        "Tensor v_scale, int num_splits, Tensor(d!) part_out, Tensor(e!) part_lse) -> ()", _paged_decode_step)
 
 
 def reshape_and_cache_op() -> engine.Op:

@@ -187,6 +187,53 @@ int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_stride_head
                       float scale, int kv_dtype, const float* k_scale, const float* v_scale,
                       void* stream);
 
+/*
+ * One decode step -- the cache write of the step's new token of every sequence, the walk
+ * and the merge -- in fewer launches than hkb_reshape_and_cache + hkb_paged_decode +
+ * hkb_merge: two (the walk writes the new rows itself; then the merge kernel), or one when
+ * `arrivals` is given (the walk also folds the partials). Where the shape does not allow it
+ * (one split, more than 2048 sequences) the three separate launches run. `out` holds the
+ * final bf16 answer either way, and the cache holds the new rows.
+ *
+ * key / value: the new rows, bf16, one row a sequence (row of sequence i = q_start[i], or i
+ * when q_start is NULL -- the row of its query; with q_start, row i must belong to sequence
+ * i, as in a decode-only batch), strides in elements; slot_mapping[row] is where the row
+ * goes, and must address position seq_lens[i] - 1 of sequence i (what a decode step's slot
+ * mapping is) or be negative (skipped). key == value == NULL: the cache is already written.
+ *
+ * The ring of the walk that owns a sequence's last tile writes the new row into the cache
+ * before it fetches that tile; no other ring of that kv head reads the tile.
+ *
+ * arrivals (optional): hkb_arrivals_bytes(num_seqs, num_kv_heads) bytes of int32 counters,
+ * ZERO before the first call; every call leaves them zero. One array a stream: two steps in
+ * flight at once must not share it (nor the scratch). With it the ring that finishes the last
+ * outstanding piece of a sequence folds its partials -- no ring waits for another -- as a
+ * two-level tree of 16-way folds, so results may differ from hkb_merge's in the last fp32
+ * bits when a sequence has more than 16 pieces (identical otherwise). One warp folds where
+ * the merge kernel uses a grid: measured on B200 this form is slower than the merge launch
+ * it saves except for small, evenly cut batches, which is why it is opt-in.
+ *
+ * Replaces: the backend's decode step, _update_cache + two launches
+ * (python/hk/integration/vllm_backend.py:582-599, 700-729); joining them is what
+ * docs/history/17-the-decode-step-captured-whole.md:181-188 leaves as future work.
+ */
+int hkb_decode_step(void* out, int64_t out_stride_tok, int64_t out_stride_head,
+                    const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                    const void* key, const void* value,
+                    int64_t key_stride_tok, int64_t key_stride_head,
+                    int64_t val_stride_tok, int64_t val_stride_head,
+                    const void* slot_mapping, int slot_is_i64,
+                    hkb_cache_t k_cache, hkb_cache_t v_cache,
+                    const int32_t* block_table, int64_t table_stride, int max_pages,
+                    const int32_t* seq_lens, const int32_t* q_start,
+                    int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                    int block_size, float scale, int kv_dtype,
+                    const float* k_scale, const float* v_scale,
+                    int num_splits, float* part_out, float* part_lse, int32_t* arrivals, void* stream);
+
+/* Bytes of the arrival counters hkb_decode_step takes. */
+size_t hkb_arrivals_bytes(int num_seqs, int num_kv_heads);
+
 /* Query rows one work item of hkb_paged_prefill covers (16..128, by GQA group); 0 if the
  * head counts are not a valid GQA shape. */
 int hkb_prefill_tile_rows(int num_q_heads, int num_kv_heads);
