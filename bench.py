@@ -284,7 +284,8 @@ def main():
     max_tiles = st.block_table.shape[1] * (spec.block_size // 16)
     kvsplit = st.shard.kind == "kvsplit"
     splits = args.splits or paged.plan_splits(n, st.kv_heads, max_tiles, device=dev)
-    path = "mma" if spec.q_heads // spec.kv_heads >= 8 else "cc"
+    from hk_dsl_b200.runtime import lib as hkb_lib
+    path = "mma" if hkb_lib.load().hkb_walk_uses_mma(spec.q_heads // spec.kv_heads, 1 if spec.fp8 else 0) else "cc"
     dec = None
     if kvsplit:
         dec = paged_dist.SplitKVDecoder(n, st.q_heads, st.kv_heads, d, dev, splits)

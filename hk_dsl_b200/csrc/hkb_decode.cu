@@ -427,7 +427,7 @@ static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_hea
   }
   cudaStream_t st = (cudaStream_t)stream;
 
-  const bool mma = group >= 8;
+  const bool mma = hkb_walk_uses_mma(group, kv_dtype) != 0;
   if (head_dim == 128) {
     if (fp8) return mma ? dispatch_mma<128, true>(a, num_seqs, st) : dispatch_cc<128, true>(a, num_seqs, st);
     return mma ? dispatch_mma<128, false>(a, num_seqs, st) : dispatch_cc<128, false>(a, num_seqs, st);
@@ -436,6 +436,24 @@ static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_hea
 }
 
 }  // namespace hkb
+
+// Which worker walks a GQA group. The brief for this path puts tensor-core tiles at groups of 8
+// and more and CUDA cores below. Measured on B200 that bound is too high: a CUDA-core walk of a
+// group of 5 to 7 takes its heads in two passes and reads the KV twice (3.4 against 6.5 TB/s for
+// bf16), and at a group of 4 the bf16 CUDA-core walk -- 692 instructions a tile against ~300 --
+// draws enough power to run at 1.62 GHz under the 1 kW cap, where the mma walk with half its
+// columns empty holds 6.4 TB/s (5.7-5.8 for CUDA cores; equal in short bursts). fp8 tiles are
+// widened in shared memory for the mma, which costs more than the CUDA-core dequant up to 4 heads.
+// So: bf16 from 4, fp8 from 5. HKB_MMA_MIN_GROUP=8 restores the bound of the brief; 1..8 is taken.
+extern "C" int hkb_walk_uses_mma(int group, int kv_dtype) {
+  static const int forced = [] {
+    const char* v = std::getenv("HKB_MMA_MIN_GROUP");
+    const int x = v ? std::atoi(v) : 0;
+    return x >= 1 && x <= 8 ? x : 0;
+  }();
+  const int bound = forced ? forced : (kv_dtype == HKB_KV_FP8_E4M3 ? 5 : 4);
+  return group >= bound ? 1 : 0;
+}
 
 extern "C" int hkb_paged_decode(void* out, int64_t out_stride_tok, int64_t out_stride_head,
                                 const void* q, int64_t q_stride_tok, int64_t q_stride_head,

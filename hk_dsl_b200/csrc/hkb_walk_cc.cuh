@@ -1,5 +1,5 @@
-// The decode walk on CUDA cores, for GQA groups below 8 (up to 4 query heads a CTA
-// pass): one CTA per (sequence, kv head [x head chunk], kv split).
+// The decode walk on CUDA cores, for small GQA groups (up to 4 query heads a CTA
+// pass; hkb_walk_uses_mma says which groups come here): one CTA per (sequence, kv head [x head chunk], kv split).
 //
 // What it computes is hk-dsl's fused walk (python/hk/ops/paged.py:544-662): scores
 // scaled by scale*log2(e), tail rows past seq_len masked, online softmax in exp2,

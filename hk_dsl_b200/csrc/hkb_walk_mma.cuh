@@ -1,4 +1,5 @@
-// The decode walk on tensor cores, for GQA groups of 8 to 16: one CTA per
+// The decode walk on tensor cores, for GQA groups up to 16 (a group under 8 leaves columns
+// of zeros; hkb_walk_uses_mma says from which group on that is still the faster walk): one CTA per
 // (sequence, kv head, kv split), the group's query heads as the N=8 columns of
 // mma.sync.m16n8k16 tiles (NT = 1 for a group of 8, 2 for 9..16).
 //

@@ -27,6 +27,7 @@ from __future__ import annotations
 
 import inspect
 import os
+import sys
 from typing import Callable, List, Optional
 
 import torch
@@ -221,6 +222,48 @@ def _prefill(a: dict) -> bool:
     return True
 
 
+#: HK_VLLM_PREFILL_SHADOW=1 (the reference's switch, python/hk/integration/vllm_prefill.py:236-275):
+#: after every call this module takes, the engine's own kernel runs on the same arguments into a
+#: scratch output and the two are compared row by row in bf16 ulps of the row's largest value --
+#: the in-situ check of a drop-in. It reads the device every call and doubles the attention work:
+#: a diagnostic, never a serving mode, and skipped while a CUDA graph is being captured.
+SHADOW = os.environ.get("HK_VLLM_PREFILL_SHADOW", "").strip().lower() not in ("", "0", "off", "false", "no")
+SHADOW_STATS = {"calls": 0, "rows": 0, "worst_ulps": 0.0, "worst_call": -1, "over_4": 0}
+
+
+def shadow_compare(ours: torch.Tensor, ref: torch.Tensor, stats: dict = SHADOW_STATS) -> float:
+    """Worst row of `ours` against `ref`, (rows, heads, head_dim) each, in bf16 ulps of the
+    reference row's largest magnitude (4 is the reference's own bound for this path,
+    tests/hk/gpu/_attn_ref.py:43-44); counted into `stats`."""
+    stats["calls"] += 1
+    if ours.numel() == 0:
+        return 0.0
+    a, b = ours.float(), ref.float()
+    top = b.abs().amax(dim=-1).clamp_min(1e-30)
+    ulp = torch.exp2(torch.floor(torch.log2(top)) - 7)
+    err = float(((a - b).abs().amax(dim=-1) / ulp).max())
+    stats["rows"] += ours.shape[0]
+    if err > stats["worst_ulps"]:
+        stats["worst_ulps"], stats["worst_call"] = err, stats["calls"]
+    if err > 4:
+        stats["over_4"] += 1
+    if err > 4 or stats["calls"] % 500 == 0:
+        print(f"[hk] attention shadow: {stats}", file=sys.stderr, flush=True)
+    return err
+
+
+def _shadow(orig, a: dict, out_name: str, starts_name: str) -> None:
+    if orig is None or engine.capturing():
+        return
+    ours = a[out_name]
+    again = dict(a)
+    again[out_name] = torch.empty_like(ours)
+    orig(**again)
+    starts = a.get(starts_name)
+    live = int(starts[-1]) if starts is not None else ours.shape[0]      # a host read: diagnostic mode
+    shadow_compare(ours[:live], again[out_name][:live], SHADOW_STATS)
+
+
 def _fallback(orig, args, kwargs, why: str):
     PATCH.count("fallback")
     if orig is None:
@@ -238,6 +281,8 @@ def unified_attention(*args, **kwargs):
         why = u_why_not(a)
         if not why and _prefill(a):
             PATCH.count("prefill")
+            if SHADOW:
+                _shadow(_ORIG_U, dict(a), "out", "cu_seqlens_q")
             return None
         return _fallback(_ORIG_U, args, kwargs, why)
     why = "decode route off (HK_VLLM_DECODE=0)"
@@ -247,6 +292,8 @@ def unified_attention(*args, **kwargs):
             if _decode(a["q"], a["out"], a["k"], a["v"], a["block_table"], a["seqused_k"], a.get("cu_seqlens_q"),
                        a.get("softmax_scale"), a.get("k_descale"), a.get("v_descale")):
                 PATCH.count("decode")
+                if SHADOW:
+                    _shadow(_ORIG_U, dict(a), "out", "cu_seqlens_q")
                 return None
             why = "scratch would grow under capture"
     return _fallback(_ORIG_U, args, kwargs, why)
@@ -293,6 +340,8 @@ def chunked_prefill_paged_decode(*args, **kwargs):
         if _decode(a["query"], a["output"], a["key_cache"], a["value_cache"], a["block_table"], a["seq_lens"],
                    a.get("query_start_loc"), a.get("sm_scale"), a.get("k_scale"), a.get("v_scale")):
             PATCH.count("decode")
+            if SHADOW:
+                _shadow(_ORIG_R, dict(a), "output", "query_start_loc")
             return None
         why = "scratch would grow under capture"
     return _fallback(_ORIG_R, args, kwargs, why)

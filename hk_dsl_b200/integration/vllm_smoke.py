@@ -72,7 +72,12 @@ def main(argv=None) -> int:
     ap.add_argument("--route", action="store_true",
                     help="test the in-place route instead: vLLM keeps its TRITON_ATTN backend and cache, and its "
                          "unified_attention calls are rebound to this build's stand-in (HK_VLLM_PREFILL=1)")
+    ap.add_argument("--shadow", action="store_true",
+                    help="with --route: HK_VLLM_PREFILL_SHADOW=1, vLLM's own kernel runs beside every taken call "
+                         "and the rows are compared in bf16 ulps (eager only)")
     args = ap.parse_args(argv)
+    if args.shadow:
+        os.environ["HK_VLLM_PREFILL_SHADOW"] = "1"
     os.environ.setdefault("VLLM_ENABLE_V1_MULTIPROCESSING", "0")
     os.environ["HK_VLLM_BACKEND"] = "0" if args.route else "1"
     os.environ["HK_VLLM_PREFILL"] = "1" if args.route else "0"
@@ -103,7 +108,8 @@ def main(argv=None) -> int:
     print(json.dumps({"prompts": len(prompts), "tokens_generated": total, "tokens_identical_prefix": same,
                       "worst_logprob_gap_on_shared_prefix": round(worst, 4), "eager_calls": stats[0],
                       "captured_calls": stats[1], "graphs": args.graphs, "kv_cache_dtype": args.kv,
-                      "surface": "in-place route (vLLM's TRITON_ATTN backend and cache)" if args.route else "backend"}))
+                      "surface": "in-place route (vLLM's TRITON_ATTN backend and cache)" if args.route else "backend",
+                      "shadow": dict(vllm_prefill.SHADOW_STATS) if args.shadow else None}))
     ok = stats[0].get("decode", 0) + stats[1].get("decode", 0) > 0 and stats[0].get("prefill", 0) > 0 and worst < 0.1
     return 0 if ok else 1
 

@@ -64,6 +64,7 @@ SIGNATURES = {
     "hkb_prefill_tile_rows": (c_int, [c_int, c_int]),
     "hkb_merge": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p,
                           c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "hkb_walk_uses_mma": (c_int, [c_int, c_int]),
     "hkb_plan_splits": (c_int, [c_int, c_int, c_int, c_int]),
     "hkb_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "hkb_scratch_lse_offset": (c_size_t, [c_int, c_int, c_int, c_int]),

@@ -371,3 +371,41 @@ def test_prefill_torch_op():
     torch.ops.hk.paged_prefill_d128_g4(q.cuda().view(n, hq * d), k.cuda(), v.cuda(), table.cuda(), lens.cuda(),
                                        q_start.cuda(), tiles, out)
     orc.check(out.view(n, hq, d), want)
+
+
+def test_shadow_mode_runs_the_engines_kernel_beside_ours(route, monkeypatch):
+    """HK_VLLM_PREFILL_SHADOW: after a taken call the engine's function runs on the same arguments
+    into a scratch output and the rows are compared. The "engine" here is this build's one-split
+    kernel (another code path to the same answer), then one that is wrong on purpose."""
+    from hk_dsl_b200.ops import paged
+
+    lens = [1, 33, 1000, 2063]
+    q, k, v, table, lens_t = _case(lens, group=4, seed=12)
+    kc, vc = k.cuda().transpose(1, 2), v.cuda().transpose(1, 2)
+    n = len(lens)
+    seen = []
+
+    def engine_kernel(q, k, v, out, cu_seqlens_q, max_seqlen_q, seqused_k, max_seqlen_k, softmax_scale, causal,
+                      window_size, block_table, softcap, q_descale, k_descale, v_descale, alibi_slopes=None,
+                      output_scale=None, qq_bias=None, sinks=None):
+        seen.append(out.data_ptr())
+        paged.paged_attention_decode(out, q, k, v, block_table, seqused_k, softmax_scale, num_splits=1)
+        if len(seen) > 1:
+            out.add_(0.5)
+
+    stats = {"calls": 0, "rows": 0, "worst_ulps": 0.0, "worst_call": -1, "over_4": 0}
+    monkeypatch.setattr(route, "_ORIG_U", engine_kernel)
+    monkeypatch.setattr(route, "SHADOW", True)
+    monkeypatch.setattr(route, "SHADOW_STATS", stats)
+    out = torch.full(q.shape, 7.0, device="cuda", dtype=torch.bfloat16)
+    args = (q.cuda(), kc, vc, out, torch.arange(n + 1, dtype=torch.int32, device="cuda"), 1, lens_t.cuda(), max(lens),
+            128 ** -0.5, True, (-1, -1), table.cuda(), 0.0, None, None, None)
+    route.unified_attention(*args)
+    assert seen and seen[0] != out.data_ptr(), "the engine's kernel writes a scratch output, not ours"
+    assert stats["calls"] == 1 and stats["rows"] == n and stats["worst_ulps"] <= 4 and stats["over_4"] == 0
+    want = orc.paged_decode_ref(q, k.transpose(1, 2), v.transpose(1, 2), table, lens_t)
+    orc.check(out, want)                      # our answer is what the caller gets
+    route.unified_attention(*args)            # the second "engine" answer is off by 0.5
+    assert stats["calls"] == 2 and stats["over_4"] == 1 and stats["worst_call"] == 2
+    orc.check(out, want)
+    assert route.PATCH.stats == {"prefill": 0, "decode": 2, "fallback": 0}

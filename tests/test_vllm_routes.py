@@ -283,3 +283,20 @@ def test_register_with_an_installed_vllm_resolves_to_our_backend():
     with pytest.raises(RuntimeError, match="no AttentionBackendEnum"):
         vllm_backend.register("NOT_A_BACKEND")
     vllm_backend.register()     # idempotent, and restores the slot name
+
+
+def test_shadow_compare_counts_rows_in_bf16_ulps():
+    """The in-situ check's arithmetic (the reference's, python/hk/integration/vllm_prefill.py:258-275):
+    a row's error in ulps of bf16 at the reference row's largest value; more than 4 is counted."""
+    stats = {"calls": 0, "rows": 0, "worst_ulps": 0.0, "worst_call": -1, "over_4": 0}
+    ref = torch.zeros(3, 2, 8)
+    ref[..., 0] = 1.5                                  # largest value 1.5: one bf16 ulp there is 2^-7
+    ours = ref.clone()
+    assert vllm_prefill.shadow_compare(ours, ref, stats) == 0.0
+    ours[1, 0, 3] = 2 * 2.0 ** -7
+    assert vllm_prefill.shadow_compare(ours, ref, stats) == pytest.approx(2.0)
+    assert stats == {"calls": 2, "rows": 6, "worst_ulps": pytest.approx(2.0), "worst_call": 2, "over_4": 0}
+    ours[2, 1, 5] = 9 * 2.0 ** -7
+    assert vllm_prefill.shadow_compare(ours, ref, stats) == pytest.approx(9.0)
+    assert stats["over_4"] == 1 and stats["worst_call"] == 3
+    assert vllm_prefill.shadow_compare(ours[:0], ref[:0], stats) == 0.0 and stats["calls"] == 4
