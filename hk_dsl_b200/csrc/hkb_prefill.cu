@@ -7,10 +7,12 @@
 // one request and its rows end where the request's do; the grid is a work list built on the
 // host, one entry a (request, query tile), so a ragged batch launches once.
 //
-// Schedule (sm_100a, legacy tensor path): one CTA a (work item, kv head [x head chunk]) of 8
-// warps; a warp owns a 16-row query tile of ONE query head (its Q fragments stay in registers)
-// and the warps of a CTA are the GP heads of the GQA group times 8 / GP consecutive 16-token
-// tiles, so one staged K/V block serves the whole group. K/V blocks of 64 tokens (4 pages of
+// Schedule (sm_100a, legacy tensor path): one CTA a (work item, kv head [x head chunk]) of 4
+// warps, two CTAs an SM; a warp owns two units, a unit being a 16-row query tile of ONE query
+// head, so every K and V fragment it reads from shared memory feeds two mma tiles; the 8 units
+// of a CTA are the GP heads of the GQA group times 8 / GP consecutive 16-token tiles, so one
+// staged K/V block serves the whole group. Query rows sit in shared memory and are re-read as A
+// fragments each block (the registers go to the two 16 x head_dim accumulators). K/V blocks of 64 tokens (4 pages of
 // 16) come through the page table into a 2-stage cp.async ring, XOR-swizzled for ldmatrix (fp8
 // tiles land in a raw ring and the warp that fetched a tile widens it to bf16, exactly);
 // S = Q K^T and O += P V are mma.sync.m16n8k16 bf16 with P reused from the S accumulators;
@@ -46,10 +48,12 @@ struct PrefillArgs {
 
 template <int D, int GP, bool FP8>
 struct Prefill {
-  static constexpr int WARPS = 8;
-  static constexpr int TOK_TILES = WARPS / GP;        // 16-token query tiles a CTA
+  static constexpr int WARPS = 4;
+  static constexpr int UNITS = 8;                     // (16-row query tile, query head) pairs a CTA: two a warp
+  static constexpr int UPW = UNITS / WARPS;
+  static constexpr int TOK_TILES = UNITS / GP;        // 16-token query tiles a CTA
   static constexpr int BT = 16 * TOK_TILES;           // query tokens a CTA
-  static constexpr int KV_TILES = 4;                  // 16-token KV tiles a stage
+  static constexpr int KV_TILES = 4;                  // 16-token KV tiles a stage: one a warp to fill
   static constexpr int KVB = 16 * KV_TILES;
   static constexpr int NST = 2;
   static constexpr int ROWB = D * 2;                 // a row as the mma reads it (bf16)
@@ -58,37 +62,39 @@ struct Prefill {
   using Loader = TileLoader<ROWC>;
   static constexpr int TILE_BYTES = TILE_TOKENS * ROWB;
   static constexpr int RAW_TILE_BYTES = Loader::TILE_BYTES;
+  static constexpr int Q_BYTES = UNITS * TILE_BYTES;  // the CTA's query rows, read back as A fragments every block
   static constexpr int STAGE_BYTES = KV_TILES * 2 * TILE_BYTES;
   static constexpr int RAW_STAGE_BYTES = FP8 ? KV_TILES * 2 * RAW_TILE_BYTES : 0;   // fp8 tiles land here first
-  static constexpr int SMEM_BYTES = NST * (STAGE_BYTES + RAW_STAGE_BYTES);
+  static constexpr int SMEM_BYTES = Q_BYTES + NST * (STAGE_BYTES + RAW_STAGE_BYTES);
   static constexpr float RESCALE_LOG2 = 8.f;
 
-  // One warp fills one (tile, K|V) of a stage; rows at or past `kv_limit` are zero-filled
-  // instead of read, so nothing past the keys this CTA may attend to enters shared memory.
+  // A warp fills the K and the V tile of its 16 tokens of a stage; rows at or past `kv_limit` are
+  // zero-filled instead of read, so nothing past the keys this CTA may attend to enters shared memory.
   __device__ static __forceinline__ void fill(const PrefillArgs& a, const Loader& ld, uint32_t stage, int kv0,
                                               int kv_limit, const int* table_row, int warp, int lane) {
-    const int t = warp >> 1, which = warp & 1;
+    const int t = warp;
     const int tok0 = kv0 + 16 * t;
-    const uint32_t dst = stage + (t * 2 + which) * (FP8 ? RAW_TILE_BYTES : TILE_BYTES);
     const int valid = min(16, kv_limit - tok0);      // rows of this tile that hold attendable keys
-    if (valid <= 0) {
-      for (int x = lane; x < 16 * Loader::CPR; x += 32)
-        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(dst + x * 16), "r"(0u) : "memory");
-      return;
+    int id = 0, sub = 0;
+    if (valid > 0) {
+      const int tile = tok0 / TILE_TOKENS;
+      const int page = min(tile / a.tiles_per_page, a.max_pages - 1);
+      id = min(max(__ldg(table_row + page), 0), a.num_blocks - 1);
+      sub = tile % a.tiles_per_page;
     }
-    const int tile = tok0 / TILE_TOKENS;
-    const int page = min(tile / a.tiles_per_page, a.max_pages - 1);
-    const int id = min(max(__ldg(table_row + page), 0), a.num_blocks - 1);
-    const int sub = tile % a.tiles_per_page;
-    const int64_t sb = which ? ld.vsb : ld.ksb, st = which ? ld.vst : ld.kst;
-    const uint8_t* p = (which ? ld.vbase : ld.kbase) + (int64_t)id * sb + (int64_t)(sub * TILE_TOKENS) * st;
 #pragma unroll
-    for (int it = 0; it < Loader::ITERS; ++it) {
-      const int x = it * 32 + lane;
-      const int r = x / Loader::CPR, c = x % Loader::CPR;
-      const uint32_t d = dst + tile_off<ROWC>(r, c);
-      if (r < valid) cp_async16(d, p + (int64_t)r * st + c * 16);
-      else asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(d), "r"(0u) : "memory");
+    for (int which = 0; which < 2; ++which) {
+      const uint32_t dst = stage + (t * 2 + which) * (FP8 ? RAW_TILE_BYTES : TILE_BYTES);
+      const int64_t sb = which ? ld.vsb : ld.ksb, st = which ? ld.vst : ld.kst;
+      const uint8_t* p = (which ? ld.vbase : ld.kbase) + (int64_t)id * sb + (int64_t)(sub * TILE_TOKENS) * st;
+#pragma unroll
+      for (int it = 0; it < Loader::ITERS; ++it) {
+        const int x = it * 32 + lane;
+        const int r = x / Loader::CPR, c = x % Loader::CPR;
+        const uint32_t d = dst + tile_off<ROWC>(r, c);
+        if (r < valid) cp_async16(d, p + (int64_t)r * st + c * 16);
+        else asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(d), "r"(0u) : "memory");
+      }
     }
   }
 
@@ -96,7 +102,7 @@ struct Prefill {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int passes = a.group / GP;
     const int kvh = blockIdx.y / passes;
-    const int hq = kvh * a.group + (blockIdx.y % passes) * GP + (warp % GP);   // this warp's query head
+    const int hbase = kvh * a.group + (blockIdx.y % passes) * GP;
     const int req = __ldg(a.work + 2 * blockIdx.x), row0 = __ldg(a.work + 2 * blockIdx.x + 1);
     const int q0 = __ldg(a.q_start + req), q1 = __ldg(a.q_start + req + 1);
     const int q_len = q1 - q0;
@@ -107,33 +113,61 @@ struct Prefill {
     const int kv_limit = min(seq_len, ctx + row0 + rows_cta);   // keys any of them may attend to
     const int n_blocks = (kv_limit + KVB - 1) / KVB;
 
-    // this warp's 16 rows: tokens row0 + 16 * (warp / GP) + {lane/4, lane/4 + 8}
-    const int wrow0 = row0 + 16 * (warp / GP);
-    const int rA = wrow0 + (lane >> 2), rB = rA + 8;            // rows inside the request
-    const bool vA = rA < q_len, vB = rB < q_len;
-    const int posA = ctx + rA, posB = ctx + rB;                 // their positions in the sequence
-    uint32_t qa[KD][4];
-    {
-      const uint32_t* qA = reinterpret_cast<const uint32_t*>(a.q + (int64_t)(q0 + rA) * a.q_stride_tok + (int64_t)hq * a.q_stride_head);
-      const uint32_t* qB = reinterpret_cast<const uint32_t*>(a.q + (int64_t)(q0 + rB) * a.q_stride_tok + (int64_t)hq * a.q_stride_head);
+    // The warp's two units: unit u is query head u % GP of the CTA's heads and 16-token tile u / GP.
+    // Thread rows inside a unit: tokens wrow0 + {lane/4, lane/4 + 8}.
+    int hq[UPW], wrow0[UPW], posA[UPW], posB[UPW], limit[UPW];
+    bool live[UPW];
 #pragma unroll
-      for (int kc = 0; kc < KD; ++kc) {
-        qa[kc][0] = vA ? __ldg(qA + kc * 8 + (lane & 3)) : 0u;
-        qa[kc][1] = vB ? __ldg(qB + kc * 8 + (lane & 3)) : 0u;
-        qa[kc][2] = vA ? __ldg(qA + kc * 8 + 4 + (lane & 3)) : 0u;
-        qa[kc][3] = vB ? __ldg(qB + kc * 8 + 4 + (lane & 3)) : 0u;
+    for (int i = 0; i < UPW; ++i) {
+      const int u = warp * UPW + i;
+      hq[i] = hbase + u % GP;
+      wrow0[i] = row0 + 16 * (u / GP);
+      posA[i] = ctx + wrow0[i] + (lane >> 2);
+      posB[i] = posA[i] + 8;
+      live[i] = wrow0[i] < q_len;                               // a unit whose 16 rows are all past the request idles
+      limit[i] = min(kv_limit, ctx + min(wrow0[i] + 16, q_len));   // keys past every row of the unit need no work
+    }
+
+    const uint32_t qsm = smem_u32(smem);
+    const uint32_t ring = qsm + Q_BYTES;
+    const uint32_t raw = ring + NST * STAGE_BYTES;   // fp8 only: where the copies land before they are widened
+    const uint32_t land = FP8 ? raw : ring;
+    constexpr int LAND_BYTES = FP8 ? RAW_STAGE_BYTES : STAGE_BYTES;
+
+    // Stage the warp's query rows (rows past the request: zeros) in the swizzled layout ldmatrix reads.
+    const bool q16 = ((reinterpret_cast<uintptr_t>(a.q) | (uintptr_t)(a.q_stride_tok * 2) | (uintptr_t)(a.q_stride_head * 2)) & 15) == 0;
+#pragma unroll
+    for (int i = 0; i < UPW; ++i) {
+      const uint32_t qt = qsm + (warp * UPW + i) * TILE_BYTES;
+      for (int x = lane; x < 16 * (ROWB / 16); x += 32) {
+        const int r = x / (ROWB / 16), c = x % (ROWB / 16);
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (wrow0[i] + r < q_len) {
+          const __nv_bfloat16* src = a.q + (int64_t)(q0 + wrow0[i] + r) * a.q_stride_tok + (int64_t)hq[i] * a.q_stride_head + c * 8;
+          if (q16) v = __ldg(reinterpret_cast<const uint4*>(src));
+          else {
+            const uint32_t* s32 = reinterpret_cast<const uint32_t*>(src);
+            v = make_uint4(__ldg(s32), __ldg(s32 + 1), __ldg(s32 + 2), __ldg(s32 + 3));
+          }
+        }
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(qt + tile_off<ROWB>(r, c)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
       }
     }
-    float o[2 * KD][4];
+
+    float o[UPW][2 * KD][4];
+    float m[UPW][2], l[UPW][2];
 #pragma unroll
-    for (int nt = 0; nt < 2 * KD; ++nt)
+    for (int i = 0; i < UPW; ++i) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) o[nt][i] = 0.f;
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+      for (int nt = 0; nt < 2 * KD; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[i][nt][e] = 0.f;
+      m[i][0] = m[i][1] = -INFINITY;
+      l[i][0] = l[i][1] = 0.f;
+    }
     float qs = a.scale * LOG2E;
     float vs = 1.f;
     if (FP8) { qs *= __ldg(a.k_scale); vs = __ldg(a.v_scale); }
-    const bool warp_live = wrow0 < q_len;                       // a warp whose 16 rows are all past the request idles
 
     Loader ld;
     ld.kbase = a.k + (int64_t)kvh * a.k_stride_head;
@@ -142,10 +176,16 @@ struct Prefill {
     ld.vsb = a.v_stride_block; ld.vst = a.v_stride_token;
     ld.tiles_per_page = a.tiles_per_page; ld.num_blocks = a.num_blocks;
     const int* table_row = a.block_table + (int64_t)req * a.table_stride;
-    const uint32_t ring = smem_u32(smem);
-    const uint32_t raw = ring + NST * STAGE_BYTES;   // fp8 only: where the copies land before they are widened
-    const uint32_t land = FP8 ? raw : ring;
-    constexpr int LAND_BYTES = FP8 ? RAW_STAGE_BYTES : STAGE_BYTES;
+
+    // where this lane's ldmatrix rows sit inside a 16-token tile, one value a 16-dim chunk:
+    // A (query rows, row-major), B for S (key rows), B for O (value rows, read transposed)
+    uint32_t qoff[KD], koff[KD], voff[KD];
+#pragma unroll
+    for (int kc = 0; kc < KD; ++kc) {
+      qoff[kc] = tile_off<ROWB>(lane & 15, kc * 2 + (lane >> 4));
+      koff[kc] = tile_off<ROWB>(((lane >> 4) & 1) * 8 + (lane & 7), kc * 2 + ((lane >> 3) & 1));
+      voff[kc] = tile_off<ROWB>(((lane >> 3) & 1) * 8 + (lane & 7), kc * 2 + (lane >> 4));
+    }
 
     fill(a, ld, land, 0, kv_limit, table_row, warp, lane);
     cp_async_commit();
@@ -155,120 +195,144 @@ struct Prefill {
         // the warp that fetched a tile widens it to bf16 (exact) into block b's stage. Every warp
         // is past its work on block b-2, the stage's previous tenant (the barrier of iteration b-1).
         __syncwarp();
-        const int tw = warp >> 1, which = warp & 1;
-        WalkMMA<D, true, 1, 4, 4>::widen(raw + (b & 1) * RAW_STAGE_BYTES + (tw * 2 + which) * RAW_TILE_BYTES,
-                                         ring + (b & 1) * STAGE_BYTES + (tw * 2 + which) * TILE_BYTES, lane);
+#pragma unroll
+        for (int which = 0; which < 2; ++which)
+          WalkMMA<D, true, 1, 4, 4>::widen(raw + (b & 1) * RAW_STAGE_BYTES + (warp * 2 + which) * RAW_TILE_BYTES,
+                                           ring + (b & 1) * STAGE_BYTES + (warp * 2 + which) * TILE_BYTES, lane);
       }
-      __syncthreads();   // block b has landed for every warp; block b-1's stage is free again
+      __syncthreads();   // block b has landed for every warp (and, the first time, the query rows); block b-1's stage is free
       if (b + 1 < n_blocks) fill(a, ld, land + ((b + 1) & 1) * LAND_BYTES, (b + 1) * KVB, kv_limit, table_row, warp, lane);
       cp_async_commit();
       const uint32_t stage = ring + (b & 1) * STAGE_BYTES;
       const int kv0 = b * KVB;
-      if (!warp_live) continue;
-      // keys past every row of this warp need no work at all
-      const int warp_limit = min(kv_limit, ctx + min(wrow0 + 16, q_len));
+      bool on[UPW];
+      bool any = false;
 #pragma unroll
-      for (int t = 0; t < KV_TILES; ++t) {
-        const int t0 = kv0 + 16 * t;
-        if (t0 >= warp_limit) break;
-        const uint32_t ktile = stage + (t * 2) * TILE_BYTES, vtile = ktile + TILE_BYTES;
-        float s[2][4];
+      for (int i = 0; i < UPW; ++i) { on[i] = live[i] && kv0 < limit[i]; any |= on[i]; }
+      if (!any) continue;
+
+      // S = Q K^T for the block's 64 keys and both units: every K fragment feeds two query tiles,
+      // 16 independent accumulator tiles. Keys past kv_limit are zero rows in the stage; keys past
+      // a row's own position are masked below.
+      float sc[UPW][2 * KV_TILES][4];
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+      for (int i = 0; i < UPW; ++i)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
-        {   // S = Q K^T: B = K rows (keys x 16 dims), two 8-key column tiles
-          const int r = ((lane >> 4) & 1) * 8 + (lane & 7);
+        for (int nt = 0; nt < 2 * KV_TILES; ++nt)
 #pragma unroll
-          for (int kc = 0; kc < KD; ++kc) {
-            uint32_t kb[4];
-            ldmatrix_x4(kb, ktile + tile_off<ROWB>(r, kc * 2 + ((lane >> 3) & 1)));
-            const uint32_t b0[2] = {kb[0], kb[1]}, b1[2] = {kb[2], kb[3]};
-            mma_bf16(s[0], qa[kc], b0);
-            mma_bf16(s[1], qa[kc], b1);
+          for (int e = 0; e < 4; ++e) sc[i][nt][e] = 0.f;
+#pragma unroll
+      for (int kc = 0; kc < KD; ++kc) {
+        uint32_t qa[UPW][4];
+#pragma unroll
+        for (int i = 0; i < UPW; ++i) ldmatrix_x4(qa[i], qsm + (warp * UPW + i) * TILE_BYTES + qoff[kc]);
+#pragma unroll
+        for (int t = 0; t < KV_TILES; ++t) {
+          uint32_t kb[4];
+          ldmatrix_x4(kb, stage + (t * 2) * TILE_BYTES + koff[kc]);
+          const uint32_t b0[2] = {kb[0], kb[1]}, b1[2] = {kb[2], kb[3]};
+#pragma unroll
+          for (int i = 0; i < UPW; ++i) {
+            mma_bf16(sc[i][2 * t], qa[i], b0);
+            mma_bf16(sc[i][2 * t + 1], qa[i], b1);
           }
         }
-        // scale, causal mask (key j is seen by the row at position p iff j <= p), row maxima
-        const bool diag = t0 + 15 > ctx + wrow0;   // the tile reaches past the first row's position
+      }
+      uint32_t pa[UPW][KV_TILES][4];
+#pragma unroll
+      for (int i = 0; i < UPW; ++i) {
+        // causal mask (key j is seen by the row at position p iff j <= p), row maxima. Scores stay
+        // unscaled: the exponent below is exp2(s * qs - m) in one fma, m kept in scaled units.
+        if (!on[i] || kv0 + KVB - 1 > ctx + wrow0[i]) {   // an idle unit, or a block that reaches past the unit's first row
+#pragma unroll
+          for (int nt = 0; nt < 2 * KV_TILES; ++nt) {
+            const int j = kv0 + nt * 8 + 2 * (lane & 3);
+            if (!on[i] || j > posA[i]) sc[i][nt][0] = -INFINITY;
+            if (!on[i] || j + 1 > posA[i]) sc[i][nt][1] = -INFINITY;
+            if (!on[i] || j > posB[i]) sc[i][nt][2] = -INFINITY;
+            if (!on[i] || j + 1 > posB[i]) sc[i][nt][3] = -INFINITY;
+          }
+        }
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-          const int j = t0 + nt * 8 + 2 * (lane & 3);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) s[nt][i] *= qs;
-          if (diag) {
-            if (j > posA) s[nt][0] = -INFINITY;
-            if (j + 1 > posA) s[nt][1] = -INFINITY;
-            if (j > posB) s[nt][2] = -INFINITY;
-            if (j + 1 > posB) s[nt][3] = -INFINITY;
-          }
-          mx[0] = fmaxf(mx[0], fmaxf(s[nt][0], s[nt][1]));
-          mx[1] = fmaxf(mx[1], fmaxf(s[nt][2], s[nt][3]));
+        for (int nt = 0; nt < 2 * KV_TILES; ++nt) {
+          mx[0] = fmaxf(mx[0], fmaxf(sc[i][nt][0], sc[i][nt][1]));
+          mx[1] = fmaxf(mx[1], fmaxf(sc[i][nt][2], sc[i][nt][3]));
         }
 #pragma unroll
         for (int x = 1; x < 4; x <<= 1) {
           mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], x));
           mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], x));
         }
-        // lazy reference: rescale only when a tile's maximum exceeds it by 2^RESCALE_LOG2
-        if (__any_sync(0xffffffffu, mx[0] > m[0] + RESCALE_LOG2 || mx[1] > m[1] + RESCALE_LOG2)) {
+        mx[0] *= qs; mx[1] *= qs;            // qs > 0: the maximum of the scaled scores
+        // lazy reference: rescale only when a block's maximum exceeds it by 2^RESCALE_LOG2
+        if (__any_sync(0xffffffffu, mx[0] > m[i][0] + RESCALE_LOG2 || mx[1] > m[i][1] + RESCALE_LOG2)) {
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
-            const float m_new = fmaxf(m[c], mx[c]);
-            const float alpha = fast_exp2(m[c] - ((m_new == -INFINITY) ? 0.f : m_new));
-            l[c] *= alpha;
+            const float m_new = fmaxf(m[i][c], mx[c]);
+            const float alpha = fast_exp2(m[i][c] - ((m_new == -INFINITY) ? 0.f : m_new));
+            l[i][c] *= alpha;
 #pragma unroll
-            for (int nt = 0; nt < 2 * KD; ++nt) { o[nt][2 * c] *= alpha; o[nt][2 * c + 1] *= alpha; }
-            m[c] = m_new;
+            for (int nt = 0; nt < 2 * KD; ++nt) { o[i][nt][2 * c] *= alpha; o[i][nt][2 * c + 1] *= alpha; }
+            m[i][c] = m_new;
           }
         }
-        const float sa = (m[0] == -INFINITY) ? 0.f : m[0], sb = (m[1] == -INFINITY) ? 0.f : m[1];
-        uint32_t pa[4];
-        {
-          const float p00 = fast_exp2(s[0][0] - sa), p01 = fast_exp2(s[0][1] - sa);
-          const float p02 = fast_exp2(s[0][2] - sb), p03 = fast_exp2(s[0][3] - sb);
-          const float p10 = fast_exp2(s[1][0] - sa), p11 = fast_exp2(s[1][1] - sa);
-          const float p12 = fast_exp2(s[1][2] - sb), p13 = fast_exp2(s[1][3] - sb);
-          l[0] += p00 + p01 + p10 + p11;
-          l[1] += p02 + p03 + p12 + p13;
-          pa[0] = pack_bf16x2(p00, p01);   // (row A, keys 0-7 pair)
-          pa[1] = pack_bf16x2(p02, p03);   // (row B, keys 0-7 pair)
-          pa[2] = pack_bf16x2(p10, p11);   // (row A, keys 8-15 pair)
-          pa[3] = pack_bf16x2(p12, p13);   // (row B, keys 8-15 pair)
-        }
-        {   // O += P V: B = V^T read transposed from the row-major V tile, two 8-dim column tiles a load
-          const int r = ((lane >> 3) & 1) * 8 + (lane & 7);
+        const float sa = (m[i][0] == -INFINITY) ? 0.f : -m[i][0], sb = (m[i][1] == -INFINITY) ? 0.f : -m[i][1];
 #pragma unroll
-          for (int dt = 0; dt < KD; ++dt) {
-            uint32_t vb[4];
-            ldmatrix_x4_trans(vb, vtile + tile_off<ROWB>(r, dt * 2 + (lane >> 4)));
-            const uint32_t b0[2] = {vb[0], vb[1]}, b1[2] = {vb[2], vb[3]};
-            mma_bf16(o[2 * dt], pa, b0);
-            mma_bf16(o[2 * dt + 1], pa, b1);
+        for (int t = 0; t < KV_TILES; ++t) {
+          const float p00 = fast_exp2(fmaf(sc[i][2 * t][0], qs, sa)), p01 = fast_exp2(fmaf(sc[i][2 * t][1], qs, sa));
+          const float p02 = fast_exp2(fmaf(sc[i][2 * t][2], qs, sb)), p03 = fast_exp2(fmaf(sc[i][2 * t][3], qs, sb));
+          const float p10 = fast_exp2(fmaf(sc[i][2 * t + 1][0], qs, sa)), p11 = fast_exp2(fmaf(sc[i][2 * t + 1][1], qs, sa));
+          const float p12 = fast_exp2(fmaf(sc[i][2 * t + 1][2], qs, sb)), p13 = fast_exp2(fmaf(sc[i][2 * t + 1][3], qs, sb));
+          l[i][0] += (p00 + p01) + (p10 + p11);
+          l[i][1] += (p02 + p03) + (p12 + p13);
+          pa[i][t][0] = pack_bf16x2(p00, p01);   // (row A, keys 0-7 pair)
+          pa[i][t][1] = pack_bf16x2(p02, p03);   // (row B, keys 0-7 pair)
+          pa[i][t][2] = pack_bf16x2(p10, p11);   // (row A, keys 8-15 pair)
+          pa[i][t][3] = pack_bf16x2(p12, p13);   // (row B, keys 8-15 pair)
+        }
+      }
+      // O += P V: B = V^T read transposed from the row-major V tiles; every V fragment feeds both units
+#pragma unroll
+      for (int t = 0; t < KV_TILES; ++t) {
+#pragma unroll
+        for (int dt = 0; dt < KD; ++dt) {
+          uint32_t vb[4];
+          ldmatrix_x4_trans(vb, stage + (t * 2 + 1) * TILE_BYTES + voff[dt]);
+          const uint32_t b0[2] = {vb[0], vb[1]}, b1[2] = {vb[2], vb[3]};
+#pragma unroll
+          for (int i = 0; i < UPW; ++i) {
+            mma_bf16(o[i][2 * dt], pa[i][t], b0);
+            mma_bf16(o[i][2 * dt + 1], pa[i][t], b1);
           }
         }
       }
     }
     cp_async_wait<0>();
-    if (!warp_live) return;
 #pragma unroll
-    for (int c = 0; c < 2; ++c)
+    for (int i = 0; i < UPW; ++i) {
+      if (!live[i]) continue;
 #pragma unroll
-      for (int x = 1; x < 4; x <<= 1) l[c] += __shfl_xor_sync(0xffffffffu, l[c], x);
-    const float iA = l[0] > 0.f ? vs / l[0] : 0.f, iB = l[1] > 0.f ? vs / l[1] : 0.f;
-    __nv_bfloat16* oA = a.out + (int64_t)(q0 + rA) * a.out_stride_tok + (int64_t)hq * a.out_stride_head;
-    __nv_bfloat16* oB = a.out + (int64_t)(q0 + rB) * a.out_stride_tok + (int64_t)hq * a.out_stride_head;
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
-    for (int nt = 0; nt < 2 * KD; ++nt) {
-      const int d = nt * 8 + 2 * (lane & 3);
-      if (vA) *reinterpret_cast<uint32_t*>(oA + d) = pack_bf16x2(o[nt][0] * iA, o[nt][1] * iA);
-      if (vB) *reinterpret_cast<uint32_t*>(oB + d) = pack_bf16x2(o[nt][2] * iB, o[nt][3] * iB);
+        for (int x = 1; x < 4; x <<= 1) l[i][c] += __shfl_xor_sync(0xffffffffu, l[i][c], x);
+      const int rA = wrow0[i] + (lane >> 2), rB = rA + 8;
+      const bool vA = rA < q_len, vB = rB < q_len;
+      const float iA = l[i][0] > 0.f ? vs / l[i][0] : 0.f, iB = l[i][1] > 0.f ? vs / l[i][1] : 0.f;
+      __nv_bfloat16* oA = a.out + (int64_t)(q0 + rA) * a.out_stride_tok + (int64_t)hq[i] * a.out_stride_head;
+      __nv_bfloat16* oB = a.out + (int64_t)(q0 + rB) * a.out_stride_tok + (int64_t)hq[i] * a.out_stride_head;
+#pragma unroll
+      for (int nt = 0; nt < 2 * KD; ++nt) {
+        const int d = nt * 8 + 2 * (lane & 3);
+        if (vA) *reinterpret_cast<uint32_t*>(oA + d) = pack_bf16x2(o[i][nt][0] * iA, o[i][nt][1] * iA);
+        if (vB) *reinterpret_cast<uint32_t*>(oB + d) = pack_bf16x2(o[i][nt][2] * iB, o[i][nt][3] * iB);
+      }
     }
   }
 };
 
 template <int D, int GP, bool FP8>
-__global__ void __launch_bounds__(256) prefill_kernel(const PrefillArgs a) {
+__global__ void __launch_bounds__(128, 2) prefill_kernel(const PrefillArgs a) {
   extern __shared__ __align__(128) uint8_t hkb_smem[];
   Prefill<D, GP, FP8>::run(a, hkb_smem);
 }
@@ -285,7 +349,7 @@ static int launch_prefill(const PrefillArgs& a, int num_work, cudaStream_t st) {
   }
   if (e == cudaSuccess) {
     dim3 grid(num_work, a.num_kv_heads * (a.group / GP));
-    prefill_kernel<D, GP, FP8><<<grid, 256, smem, st>>>(a);
+    prefill_kernel<D, GP, FP8><<<grid, Prefill<D, GP, FP8>::WARPS * 32, smem, st>>>(a);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
