@@ -320,6 +320,16 @@ static int dispatch_mma(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
   dim3 grid(a.num_splits, a.num_kv_heads, num_seqs);
   if (use_stream(a, num_seqs)) {
     grid = stream_grid(a.num_kv_heads);
+    if constexpr (FP8) {   // the fp8 stream builds its mma fragments straight from the fp8 tile
+      static const bool widen = [] { const char* v = std::getenv("HKB_FP8_WIDEN"); return v && v[0] == '1'; }();
+      if (!widen) {
+        if (a.group <= 8)
+          return launch_stream<walk_stream_kernel<WalkMMAF8<D, 1, NST>, WARPS>>(
+              WalkStream<WalkMMAF8<D, 1, NST>, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
+        return launch_stream<walk_stream_kernel<WalkMMAF8<D, 2, NST>, WARPS>>(
+            WalkStream<WalkMMAF8<D, 2, NST>, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
+      }
+    }
     if (a.group <= 8)
       return launch_stream<walk_stream_kernel<WalkMMA<D, FP8, 1, WARPS, NST>, WARPS>>(
           WalkStream<WalkMMA<D, FP8, 1, WARPS, NST>, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);

@@ -387,6 +387,226 @@ struct WalkMMA {
   }
 };
 
+// ---------------------------------------------------------------------------------
+// The stream worker for fp8-e4m3 caches: the dequant fused into the fragment loads.
+// ---------------------------------------------------------------------------------
+// WalkMMA above widens an fp8 tile to a bf16 tile in shared memory before the mma reads it:
+// a second pass over every byte. Here the mma fragments are built straight from the fp8 tile:
+// cvt.rn.f16x2.e4m3x2 turns two adjacent bytes into one f16x2 register exactly, and
+// mma.sync.m16n8k16 runs in f16 (q converted bf16 -> f16, exact in f16's range; P rounded to
+// f16, three more mantissa bits than bf16). Two permutations make the bytes fall into place:
+//   * K (A operand of S^T = K Q^T, tokens x dims): a lane reads 8 consecutive bytes of rows g
+//     and g+8 (one 64-bit load each) and uses byte pairs (0,1),(2,3) as the k columns
+//     (2t,2t+1),(2t+8,2t+9) of one 16-dim chunk and (4,5),(6,7) as those of the next. The
+//     contraction runs over dims, so any order will do as long as Q's fragments use the same:
+//     chunk pair s, lane t holds dims 32s + 8t .. + 7 -- one 16-byte load of the query row.
+//   * V (A operand of O^T += V^T P^T, dims x tokens): a lane reads 4 consecutive bytes (dims
+//     32jj + 4g .. + 3) of token rows 2t, 2t+1, 2t+8, 2t+9; a byte permute pairs the tokens of
+//     one dim. Rows g / g+8 of output tile 2jj + cc are then dims 32jj + 4g + 2cc / + 1: the
+//     output's dim order is permuted, which `end` undoes when it writes the partial.
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_bytes) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(h2) : "h"((uint16_t)two_bytes));
+  return h2;
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+  return v;
+}
+
+template <int D, int NT, int NST>
+struct WalkMMAF8 {
+  static_assert(D % 32 == 0, "dims are taken 32 at a time");
+  static constexpr int ES = 1;
+  static constexpr int ROWB = D;
+  using Loader = TileLoader<ROWB>;
+  static constexpr int STAGE_BYTES = 2 * Loader::TILE_BYTES;
+  static constexpr int KD = D / 16;
+  static constexpr int SPANS = D / 32;
+  static constexpr int HEADS = NT * 8;
+  static constexpr int RING_SMEM = NST * STAGE_BYTES;
+  static constexpr int WPR = 1;
+  static constexpr int PASS_HEADS = HEADS;
+  static constexpr int STAGES = NST;
+  static constexpr int HEAD_DIM = D;
+  static constexpr float F16_MAX = 65504.f;
+  __host__ __device__ static constexpr int passes(int) { return 1; }
+
+  struct State {
+    uint32_t qb[NT][KD][2];
+    float m[NT][2], l[NT][2], o[NT][KD][4];
+    uint32_t koff[SPANS], voff[SPANS][2];   // this lane's byte offsets inside a K tile / a V tile
+  };
+
+  __device__ static __forceinline__ void begin(State& st, const DecodeArgs& a, int row, int hq0, int nh, int lane,
+                                               float /*qs*/) {
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int s = 0; s < SPANS; ++s) {
+      st.koff[s] = tile_off<ROWB>(g, 2 * s + (t >> 1)) + (t & 1) * 8;
+      st.voff[s][0] = tile_off<ROWB>(2 * t, 2 * s + (g >> 2)) + (g & 3) * 4;
+      st.voff[s][1] = tile_off<ROWB>(2 * t + 1, 2 * s + (g >> 2)) + (g & 3) * 4;
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int h = nt * 8 + g;
+      const uint4* qp = reinterpret_cast<const uint4*>(a.q + (int64_t)row * a.q_stride_tok + (int64_t)(hq0 + h) * a.q_stride_head);
+#pragma unroll
+      for (int s = 0; s < SPANS; ++s) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (h < nh) v = __ldg(qp + s * 4 + t);            // dims 32s + 8t .. + 7
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t f[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          f[i] = pack_f16x2(fminf(fmaxf(bf16lo(w[i]), -F16_MAX), F16_MAX), fminf(fmaxf(bf16hi(w[i]), -F16_MAX), F16_MAX));
+        st.qb[nt][2 * s][0] = f[0]; st.qb[nt][2 * s][1] = f[1];
+        st.qb[nt][2 * s + 1][0] = f[2]; st.qb[nt][2 * s + 1][1] = f[3];
+      }
+#pragma unroll
+      for (int kc = 0; kc < KD; ++kc)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) st.o[nt][kc][i] = 0.f;
+      st.m[nt][0] = st.m[nt][1] = -INFINITY;
+      st.l[nt][0] = st.l[nt][1] = 0.f;
+    }
+  }
+
+  template <bool LAST>
+  __device__ static __forceinline__ void tile(State& st, uint32_t ktile, uint32_t vtile, int tok0, int seq_len, int lane,
+                                              float qs) {
+    float sc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sc[nt][i] = 0.f;
+#pragma unroll
+    for (int s = 0; s < SPANS; ++s) {
+      const uint2 lo = lds64(ktile + st.koff[s]);                    // row g
+      const uint2 hi = lds64(ktile + st.koff[s] + 8 * ROWB);         // row g + 8: the same swizzle
+      const uint32_t a0[4] = {e4m3x2_to_f16x2(lo.x), e4m3x2_to_f16x2(hi.x), e4m3x2_to_f16x2(lo.x >> 16), e4m3x2_to_f16x2(hi.x >> 16)};
+      const uint32_t a1[4] = {e4m3x2_to_f16x2(lo.y), e4m3x2_to_f16x2(hi.y), e4m3x2_to_f16x2(lo.y >> 16), e4m3x2_to_f16x2(hi.y >> 16)};
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        mma_f16(sc[nt], a0, st.qb[nt][2 * s]);
+        mma_f16(sc[nt], a1, st.qb[nt][2 * s + 1]);
+      }
+    }
+    const int tA = tok0 + (lane >> 2), tB = tA + 8;  // the two tokens this lane holds scores of
+    uint32_t pb[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sc[nt][i] *= qs;
+      if (LAST) {
+        if (tA >= seq_len) { sc[nt][0] = -INFINITY; sc[nt][1] = -INFINITY; }
+        if (tB >= seq_len) { sc[nt][2] = -INFINITY; sc[nt][3] = -INFINITY; }
+      }
+      float mx[2] = {fmaxf(sc[nt][0], sc[nt][2]), fmaxf(sc[nt][1], sc[nt][3])};
+#pragma unroll
+      for (int x = 4; x < 32; x <<= 1) {
+        mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], x));
+        mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], x));
+      }
+      float mu[2];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const float m_new = fmaxf(st.m[nt][c], mx[c]);
+        mu[c] = (m_new == -INFINITY) ? 0.f : m_new;
+        if (m_new != st.m[nt][c]) {
+          const float alpha = fast_exp2(st.m[nt][c] - mu[c]);
+          st.l[nt][c] *= alpha;
+#pragma unroll
+          for (int dt = 0; dt < KD; ++dt) { st.o[nt][dt][c] *= alpha; st.o[nt][dt][c + 2] *= alpha; }
+          st.m[nt][c] = m_new;
+        }
+      }
+      const float p0 = fast_exp2(sc[nt][0] - mu[0]), p1 = fast_exp2(sc[nt][1] - mu[1]);
+      const float p2 = fast_exp2(sc[nt][2] - mu[0]), p3 = fast_exp2(sc[nt][3] - mu[1]);
+      st.l[nt][0] += p0 + p2;
+      st.l[nt][1] += p1 + p3;
+      // [token, head] fragments -> [head, token] = the B operand of the second product
+      pb[nt][0] = movmatrix_trans(pack_f16x2(p0, p1));
+      pb[nt][1] = movmatrix_trans(pack_f16x2(p2, p3));
+    }
+#pragma unroll
+    for (int jj = 0; jj < SPANS; ++jj) {
+      const uint32_t w0 = lds32(vtile + st.voff[jj][0]), w1 = lds32(vtile + st.voff[jj][1]);                      // tokens 2t, 2t+1
+      const uint32_t w2 = lds32(vtile + st.voff[jj][0] + 8 * ROWB), w3 = lds32(vtile + st.voff[jj][1] + 8 * ROWB);  // 2t+8, 2t+9
+      const uint32_t x01 = __byte_perm(w0, w1, 0x5140), y01 = __byte_perm(w0, w1, 0x7362);   // (dim, token pair) byte pairs
+      const uint32_t x23 = __byte_perm(w2, w3, 0x5140), y23 = __byte_perm(w2, w3, 0x7362);
+      const uint32_t a0[4] = {e4m3x2_to_f16x2(x01), e4m3x2_to_f16x2(x01 >> 16), e4m3x2_to_f16x2(x23), e4m3x2_to_f16x2(x23 >> 16)};
+      const uint32_t a1[4] = {e4m3x2_to_f16x2(y01), e4m3x2_to_f16x2(y01 >> 16), e4m3x2_to_f16x2(y23), e4m3x2_to_f16x2(y23 >> 16)};
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        mma_f16(st.o[nt][2 * jj], a0, pb[nt]);
+        mma_f16(st.o[nt][2 * jj + 1], a1, pb[nt]);
+      }
+    }
+  }
+
+  // Zero the V rows of a tail tile that lie past seq_len (0x00 is +0 in e4m3): P is 0 there, but 0 * NaN is NaN.
+  __device__ static __forceinline__ void scrub_tail(uint32_t vtile, int tok0, int seq_len, int lane) {
+    constexpr int CPR = ROWB / 16;
+    for (int x = lane; x < TILE_TOKENS * CPR; x += 32) {
+      const int r = x / CPR, c = x % CPR;
+      if (tok0 + r >= seq_len)
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(vtile + tile_off<ROWB>(r, c)), "r"(0u) : "memory");
+    }
+  }
+
+  __device__ static __forceinline__ void step(State& st, uint32_t warp_smem, int stage_idx, int tok0, int seq_len,
+                                              bool last, int lane, float qs) {
+    const uint32_t ktile = warp_smem + stage_idx * STAGE_BYTES, vtile = ktile + Loader::TILE_BYTES;
+    if (last) {
+      scrub_tail(vtile, tok0, seq_len, lane);
+      __syncwarp();
+      tile<true>(st, ktile, vtile, tok0, seq_len, lane, qs);
+    } else {
+      tile<false>(st, ktile, vtile, tok0, seq_len, lane, qs);
+    }
+  }
+
+  // As WalkMMA::end, with the output's dim order undone: rows g / g+8 of output tile dt hold
+  // dims 32 (dt / 2) + 4 g + 2 (dt % 2) and the next one.
+  __device__ static __forceinline__ void end(const State& st, int lane, int nh, float vs, float* po, float* pl) {
+    const int g = lane >> 2;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float lt = st.l[nt][c];
+#pragma unroll
+        for (int x = 4; x < 32; x <<= 1) lt += __shfl_xor_sync(0xffffffffu, lt, x);
+        const int h = nt * 8 + 2 * (lane & 3) + c;
+        const float inv = lt > 0.f ? vs / lt : 0.f;
+        if (h < nh) {
+#pragma unroll
+          for (int dt = 0; dt < KD; ++dt)
+            *reinterpret_cast<float2*>(po + h * D + 32 * (dt >> 1) + 4 * g + 2 * (dt & 1)) =
+                make_float2(st.o[nt][dt][c] * inv, st.o[nt][dt][c + 2] * inv);
+          if (g == 0) pl[h] = lt > 0.f ? (st.m[nt][c] + log2f(lt)) * LN2 : -INFINITY;
+        }
+      }
+  }
+};
+
 template <int D, bool FP8, int NT, int WARPS, int NST>
 __global__ void __launch_bounds__(WARPS * 32) walk_mma_kernel(const DecodeArgs a) {
   extern __shared__ __align__(128) uint8_t hkb_smem[];
