@@ -491,11 +491,12 @@ struct WalkMMAF8 {
   template <bool LAST>
   __device__ static __forceinline__ void tile(State& st, uint32_t ktile, uint32_t vtile, int tok0, int seq_len, int lane,
                                               float qs) {
-    float sc[NT][4];
+    // two accumulators a column tile (even and odd chunks), so the chain of dependent mma is half as long
+    float sc[NT][4], sd[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) sc[nt][i] = 0.f;
+      for (int i = 0; i < 4; ++i) sc[nt][i] = sd[nt][i] = 0.f;
 #pragma unroll
     for (int s = 0; s < SPANS; ++s) {
       const uint2 lo = lds64(ktile + st.koff[s]);                    // row g
@@ -505,9 +506,13 @@ struct WalkMMAF8 {
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         mma_f16(sc[nt], a0, st.qb[nt][2 * s]);
-        mma_f16(sc[nt], a1, st.qb[nt][2 * s + 1]);
+        mma_f16(sd[nt], a1, st.qb[nt][2 * s + 1]);
       }
     }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sc[nt][i] += sd[nt][i];
     const int tA = tok0 + (lane >> 2), tB = tA + 8;  // the two tokens this lane holds scores of
     uint32_t pb[NT][2];
 #pragma unroll

@@ -298,7 +298,7 @@ size_t hkb_scratch_bytes(int num_seqs, int num_q_heads, int head_dim, int num_sp
 size_t hkb_scratch_lse_offset(int num_seqs, int num_q_heads, int head_dim, int num_splits);
 
 /* 1 if the walk of a GQA group of `group` query heads a kv head runs on tensor-core (mma) tiles,
- * 0 if on CUDA cores: bf16 caches from a group of 4, fp8-e4m3 from 5 (measured on B200; the
+ * 0 if on CUDA cores: bf16 caches from a group of 4, fp8-e4m3 always (measured on B200; the
  * environment's HKB_MMA_MIN_GROUP = 1..8 overrides both). The reference picks its own contraction
  * form per architecture the same way (python/hk/ops/paged.py:498-547). */
 int hkb_walk_uses_mma(int group, int kv_dtype);
