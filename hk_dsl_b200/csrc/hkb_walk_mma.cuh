@@ -54,6 +54,7 @@ struct WalkMMA {
   static constexpr int WIDEN_BYTES = FP8 ? 2 * TILE16_BYTES : 0;  // per warp
   static constexpr int KD = D / 16;       // 16-wide chunks of head_dim
   static constexpr int HEADS = NT * 8;          // query heads a CTA pass holds columns for
+  static constexpr float RESCALE_LOG2 = 8.f;    // how far a tile's maximum may exceed the softmax reference
   static constexpr int PIPE_BYTES = WARPS * (NST * STAGE_BYTES + WIDEN_BYTES);
   static constexpr int FOLD_BYTES = WARPS * HEADS * (D + 2) * 4;
   static constexpr int SMEM_BYTES = PIPE_BYTES > FOLD_BYTES ? PIPE_BYTES : FOLD_BYTES;
@@ -106,8 +107,7 @@ struct WalkMMA {
     uint32_t pb[NT][2];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) sc[nt][i] *= qs;
+      // scores stay unscaled: the exponent is exp2(s * qs - m) in one fma, m kept in scaled units
       if (LAST) {
         if (tA >= seq_len) { sc[nt][0] = -INFINITY; sc[nt][1] = -INFINITY; }
         if (tB >= seq_len) { sc[nt][2] = -INFINITY; sc[nt][3] = -INFINITY; }
@@ -119,21 +119,23 @@ struct WalkMMA {
         mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], x));
         mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], x));
       }
-      float mu[2];
+      mx[0] *= qs; mx[1] *= qs;   // qs > 0
+      // lazy reference: the running maximum moves (and the accumulators are rescaled) only when a
+      // tile's maximum exceeds it by 2^RESCALE_LOG2 -- one warp-uniform branch, rarely taken
+      if (__any_sync(0xffffffffu, mx[0] > m[nt][0] + RESCALE_LOG2 || mx[1] > m[nt][1] + RESCALE_LOG2)) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const float m_new = fmaxf(m[nt][c], mx[c]);
-        mu[c] = (m_new == -INFINITY) ? 0.f : m_new;
-        if (m_new != m[nt][c]) {
-          const float alpha = fast_exp2(m[nt][c] - mu[c]);
+        for (int c = 0; c < 2; ++c) {
+          const float m_new = fmaxf(m[nt][c], mx[c]);
+          const float alpha = fast_exp2(m[nt][c] - ((m_new == -INFINITY) ? 0.f : m_new));
           l[nt][c] *= alpha;
 #pragma unroll
           for (int dt = 0; dt < KD; ++dt) { o[nt][dt][c] *= alpha; o[nt][dt][c + 2] *= alpha; }
           m[nt][c] = m_new;
         }
       }
-      const float p0 = fast_exp2(sc[nt][0] - mu[0]), p1 = fast_exp2(sc[nt][1] - mu[1]);
-      const float p2 = fast_exp2(sc[nt][2] - mu[0]), p3 = fast_exp2(sc[nt][3] - mu[1]);
+      const float mu0 = (m[nt][0] == -INFINITY) ? 0.f : -m[nt][0], mu1 = (m[nt][1] == -INFINITY) ? 0.f : -m[nt][1];
+      const float p0 = fast_exp2(fmaf(sc[nt][0], qs, mu0)), p1 = fast_exp2(fmaf(sc[nt][1], qs, mu1));
+      const float p2 = fast_exp2(fmaf(sc[nt][2], qs, mu0)), p3 = fast_exp2(fmaf(sc[nt][3], qs, mu1));
       l[nt][0] += p0 + p2;
       l[nt][1] += p1 + p3;
       // [token, head] fragments -> [head, token] = the B operand of the second product
@@ -446,6 +448,7 @@ struct WalkMMAF8 {
   static constexpr int STAGES = NST;
   static constexpr int HEAD_DIM = D;
   static constexpr float F16_MAX = 65504.f;
+  static constexpr float RESCALE_LOG2 = 8.f;   // how far a tile's maximum may exceed the reference (P <= 2^8 fits f16)
   __host__ __device__ static constexpr int passes(int) { return 1; }
 
   struct State {
@@ -517,8 +520,7 @@ struct WalkMMAF8 {
     uint32_t pb[NT][2];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) sc[nt][i] *= qs;
+      // scores stay unscaled: the exponent is exp2(s * qs - m) in one fma, m kept in scaled units
       if (LAST) {
         if (tA >= seq_len) { sc[nt][0] = -INFINITY; sc[nt][1] = -INFINITY; }
         if (tB >= seq_len) { sc[nt][2] = -INFINITY; sc[nt][3] = -INFINITY; }
@@ -529,21 +531,23 @@ struct WalkMMAF8 {
         mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], x));
         mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], x));
       }
-      float mu[2];
+      mx[0] *= qs; mx[1] *= qs;   // qs > 0
+      // lazy reference: the running maximum moves (and the accumulators are rescaled) only when a
+      // tile's maximum exceeds it by 2^RESCALE_LOG2 -- one warp-uniform branch, rarely taken
+      if (__any_sync(0xffffffffu, mx[0] > st.m[nt][0] + RESCALE_LOG2 || mx[1] > st.m[nt][1] + RESCALE_LOG2)) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const float m_new = fmaxf(st.m[nt][c], mx[c]);
-        mu[c] = (m_new == -INFINITY) ? 0.f : m_new;
-        if (m_new != st.m[nt][c]) {
-          const float alpha = fast_exp2(st.m[nt][c] - mu[c]);
+        for (int c = 0; c < 2; ++c) {
+          const float m_new = fmaxf(st.m[nt][c], mx[c]);
+          const float alpha = fast_exp2(st.m[nt][c] - ((m_new == -INFINITY) ? 0.f : m_new));
           st.l[nt][c] *= alpha;
 #pragma unroll
           for (int dt = 0; dt < KD; ++dt) { st.o[nt][dt][c] *= alpha; st.o[nt][dt][c + 2] *= alpha; }
           st.m[nt][c] = m_new;
         }
       }
-      const float p0 = fast_exp2(sc[nt][0] - mu[0]), p1 = fast_exp2(sc[nt][1] - mu[1]);
-      const float p2 = fast_exp2(sc[nt][2] - mu[0]), p3 = fast_exp2(sc[nt][3] - mu[1]);
+      const float mu0 = (st.m[nt][0] == -INFINITY) ? 0.f : -st.m[nt][0], mu1 = (st.m[nt][1] == -INFINITY) ? 0.f : -st.m[nt][1];
+      const float p0 = fast_exp2(fmaf(sc[nt][0], qs, mu0)), p1 = fast_exp2(fmaf(sc[nt][1], qs, mu1));
+      const float p2 = fast_exp2(fmaf(sc[nt][2], qs, mu0)), p3 = fast_exp2(fmaf(sc[nt][3], qs, mu1));
       st.l[nt][0] += p0 + p2;
       st.l[nt][1] += p1 + p3;
       // [token, head] fragments -> [head, token] = the B operand of the second product

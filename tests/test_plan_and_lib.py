@@ -88,3 +88,15 @@ def test_hk_splits_override(monkeypatch):
     assert paged.plan_splits(64, 8, 4) == 4                      # never more than the pages
     monkeypatch.setenv("HK_SPLITS", "auto")
     assert paged.plan_splits(64, 8, 2560) == paged.plan_splits_for(64, 8, 2560, paged.sm_count())
+
+
+def test_worker_choice_and_step_sizes_are_host_facts():
+    """Which worker walks a GQA group, and the arrival-counter size of the one-launch step: host-only
+    entry points, callable without a GPU. Defaults (no HKB_MMA_MIN_GROUP in the environment):
+    bf16 caches go to the tensor-core worker from a group of 4, fp8 caches always."""
+    h = lib.load()
+    if not os.environ.get("HKB_MMA_MIN_GROUP"):
+        assert [h.hkb_walk_uses_mma(g, lib.KV_BF16) for g in (1, 2, 3, 4, 6, 8, 16)] == [0, 0, 0, 1, 1, 1, 1]
+        assert [h.hkb_walk_uses_mma(g, lib.KV_FP8_E4M3) for g in (1, 2, 4, 8)] == [1, 1, 1, 1]
+    assert h.hkb_arrivals_bytes(64, 8) == 64 * 8 * 2 * 17 * 4
+    assert h.hkb_arrivals_bytes(0, 8) == 0 and h.hkb_arrivals_bytes(4, 0) == 0
