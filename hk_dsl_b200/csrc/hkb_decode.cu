@@ -242,10 +242,10 @@ static bool use_stream(const DecodeArgs& a, int num_seqs) {
   return a.num_splits > 1 && num_seqs <= STREAM_MAX_SEQS && !fixed;
 }
 
-static dim3 stream_grid(int planes) {
+static dim3 stream_grid(int planes, int ctas_per_sm = 2) {
   int sms = hkb_sm_count(-1);
   if (sms <= 0) sms = 148;
-  int per = (sms * 2) / planes;
+  int per = (sms * ctas_per_sm) / planes;
   if (per < 1) per = 1;
   return dim3(per, planes, 1);
 }
@@ -323,11 +323,23 @@ static int dispatch_mma(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
     if constexpr (FP8) {   // the fp8 stream builds its mma fragments straight from the fp8 tile
       static const bool widen = [] { const char* v = std::getenv("HKB_FP8_WIDEN"); return v && v[0] == '1'; }();
       if (!widen) {
-        if (a.group <= 8)
-          return launch_stream<walk_stream_kernel<WalkMMAF8<D, 1, NST>, WARPS>>(
-              WalkStream<WalkMMAF8<D, 1, NST>, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
-        return launch_stream<walk_stream_kernel<WalkMMAF8<D, 2, NST>, WARPS>>(
-            WalkStream<WalkMMAF8<D, 2, NST>, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
+        // Three CTAs an SM (168 registers a thread, 12 warps) for a group of up to 8: the walk of an
+        // fp8 tile is a chain of dependent shared-memory loads, converts, mma and shuffles, and with
+        // half the bytes a tile it needs more warps in flight than the bf16 walk to keep HBM busy
+        // (6.2 against 4.9 TB/s at two CTAs; four CTAs at 128 registers spill and fall to 4.3).
+        // HKB_F8_CTAS=2 selects the two-CTA build for A/B measurements.
+        static const int f8 = [] { const char* v = std::getenv("HKB_F8_CTAS"); return v ? std::atoi(v) : 3; }();
+        if (a.group <= 8) {
+          if (f8 != 2) {
+            using P = WalkMMAF8<D, 1, 4, 3>;
+            return launch_stream<walk_stream_kernel<P, WARPS>>(WalkStream<P, WARPS>::SMEM_BYTES, WARPS * 32,
+                                                               stream_grid(a.num_kv_heads, 3), a, num_seqs, st);
+          }
+          using P = WalkMMAF8<D, 1, NST, 2>;
+          return launch_stream<walk_stream_kernel<P, WARPS>>(WalkStream<P, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
+        }
+        using P2 = WalkMMAF8<D, 2, NST, 2>;
+        return launch_stream<walk_stream_kernel<P2, WARPS>>(WalkStream<P2, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
       }
     }
     if (a.group <= 8)

@@ -170,6 +170,7 @@ struct WalkCC {
 
   // ---- the same compute as a per-warp stream (hkb_walk_stream.cuh drives it) ----------
   static constexpr int HEADS = GH;                       // query heads a warp
+  static constexpr int MIN_CTAS = 2;                     // CTAs an SM the stream kernel is compiled and launched for
   static constexpr int WPR = 1;                          // warps a ring
   static constexpr int RING_SMEM = NST * STAGE_BYTES;    // one ring
   static constexpr int STAGES = NST;

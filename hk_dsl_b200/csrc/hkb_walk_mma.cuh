@@ -171,6 +171,7 @@ struct WalkMMA {
   static constexpr int PASS_HEADS = HEADS;      // query heads a ring serves a pass
   static constexpr int STAGES = NST;
   static constexpr int HEAD_DIM = D;
+  static constexpr int MIN_CTAS = 2;
   __host__ __device__ static constexpr int passes(int) { return 1; }
 
   struct State {
@@ -432,8 +433,9 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   return v;
 }
 
-template <int D, int NT, int NST>
+template <int D, int NT, int NST, int CTAS>
 struct WalkMMAF8 {
+  static constexpr int MIN_CTAS = CTAS;   // CTAs an SM the kernel is compiled and launched for
   static_assert(D % 32 == 0, "dims are taken 32 at a time");
   static constexpr int ES = 1;
   static constexpr int ROWB = D;

@@ -263,7 +263,7 @@ struct WalkStream {
 };
 
 template <class P, int RINGS>
-__global__ void __launch_bounds__(RINGS * P::WPR * 32, 2) walk_stream_kernel(const DecodeArgs a, int num_seqs) {
+__global__ void __launch_bounds__(RINGS * P::WPR * 32, P::MIN_CTAS) walk_stream_kernel(const DecodeArgs a, int num_seqs) {
   extern __shared__ __align__(128) uint8_t hkb_smem[];
   WalkStream<P, RINGS>::run(a, hkb_smem, num_seqs);
 }
