@@ -101,4 +101,14 @@ __device__ __forceinline__ uint32_t tile_off(int r, int c) {
   return static_cast<uint32_t>(r * ROW_BYTES + ((c ^ (r & 7)) << 4));
 }
 
+// The same tile in the layout the fp8 fragment loads want: rows of 128 bytes whose 32-byte
+// units are XOR-ed with f(r) = (r & 3) ^ ((r >> 2) & 1). A lane of those loads reads 8 or 4
+// bytes of a row and 8 lanes cover 32 bytes, so a warp-wide request touches rows {0..3} or {4..7}
+// (K: 64-bit loads, two phases) or {0,2,4,6} / {1,3,5,7} (V: 32-bit loads): f is one-to-one on
+// each of those sets, which the 16-byte swizzle above is not, so no two rows share a bank.
+__device__ __forceinline__ uint32_t tile_off_u32(int r, int c) {
+  const int f = (r & 3) ^ ((r >> 2) & 1);
+  return r * 128 + (((((c >> 1) ^ f) << 1) | (c & 1)) << 4);
+}
+
 }  // namespace hkb
