@@ -316,9 +316,20 @@ static int dispatch_cc(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
 template <int D, bool FP8>
 static int dispatch_mma(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
   constexpr int WARPS = 4;
-  constexpr int NST = FP8 ? 4 : 3;
+  // a 16-token K+V tile of head_dim 256 is 16 KB: two stages a ring, six rings in the one CTA an SM has room for
+  constexpr int NST = FP8 ? 4 : (D == 256 ? 2 : 3);
   dim3 grid(a.num_splits, a.num_kv_heads, num_seqs);
   if (use_stream(a, num_seqs)) {
+    if constexpr (D == 256) {
+      constexpr int RINGS = 6;
+      grid = stream_grid(a.num_kv_heads, 1);
+      if (a.group <= 8) {
+        using P = WalkMMA<D, FP8, 1, WARPS, NST>;
+        return launch_stream<walk_stream_kernel<P, RINGS>>(WalkStream<P, RINGS>::SMEM_BYTES, RINGS * 32, grid, a, num_seqs, st);
+      }
+      using P2 = WalkMMA<D, FP8, 2, WARPS, NST>;
+      return launch_stream<walk_stream_kernel<P2, RINGS>>(WalkStream<P2, RINGS>::SMEM_BYTES, RINGS * 32, grid, a, num_seqs, st);
+    } else {
     grid = stream_grid(a.num_kv_heads);
     if constexpr (FP8) {   // the fp8 stream builds its mma fragments straight from the fp8 tile
       static const bool widen = [] { const char* v = std::getenv("HKB_FP8_WIDEN"); return v && v[0] == '1'; }();
@@ -347,6 +358,7 @@ static int dispatch_mma(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
           WalkStream<WalkMMA<D, FP8, 1, WARPS, NST>, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
     return launch_stream<walk_stream_kernel<WalkMMA<D, FP8, 2, WARPS, NST>, WARPS>>(
         WalkStream<WalkMMA<D, FP8, 2, WARPS, NST>, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
+    }
   }
   if (a.group <= 8)
     return launch_walk<walk_mma_kernel<D, FP8, 1, WARPS, NST>>(WalkMMA<D, FP8, 1, WARPS, NST>::SMEM_BYTES,
@@ -393,7 +405,7 @@ static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_hea
   if (num_seqs == 0) return HKB_OK;
   if (num_seqs > 65535 * 16 || num_splits > 0x7fffffff) return HKB_ERR_SIZE;
   if (!out || !q || !kc.ptr || !vc.ptr || !block_table || !seq_lens) return HKB_ERR_NULL;
-  if (head_dim != 64 && head_dim != 128) return HKB_ERR_HEAD_DIM;
+  if (head_dim != 64 && head_dim != 128 && head_dim != 256) return HKB_ERR_HEAD_DIM;
   if (block_size <= 0 || block_size % TILE_TOKENS) return HKB_ERR_BLOCK_SIZE;
   if (num_q_heads % num_kv_heads) return HKB_ERR_GROUP;
   const int group = num_q_heads / num_kv_heads;
@@ -454,6 +466,7 @@ static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_hea
     if (fp8) return mma ? dispatch_mma<128, true>(a, num_seqs, st) : dispatch_cc<128, true>(a, num_seqs, st);
     return mma ? dispatch_mma<128, false>(a, num_seqs, st) : dispatch_cc<128, false>(a, num_seqs, st);
   }
+  if (head_dim == 256) return dispatch_mma<256, false>(a, num_seqs, st);   // 512-byte rows: tensor-core tiles at every group
   return mma ? dispatch_mma<64, false>(a, num_seqs, st) : dispatch_cc<64, false>(a, num_seqs, st);
 }
 

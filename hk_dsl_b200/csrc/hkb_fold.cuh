@@ -36,7 +36,7 @@ struct Fold {
   static constexpr int FPL = D / LPH;               // output floats a lane
   static constexpr int VW = FPL >= 4 ? 4 : 2;       // floats a load
   static constexpr int LR = (FOLD_ROWS + LPH - 1) / LPH;   // lse values a lane holds
-  static constexpr int RB = FPL >= 32 ? 4 : 8;      // rows requested at a time (128 registers: the walk's own are free by then)
+  static constexpr int RB = FPL >= 64 ? 2 : FPL >= 32 ? 4 : 8;      // rows requested at a time (128 registers: the walk's own are free by then)
 
   // Folds `count` <= FOLD_ROWS partials of sequence `seq` -- slots s0, s0 + step, ... -- for the
   // warp's nh heads from hq0. final_: the result goes to the output row as bf16; otherwise

@@ -37,7 +37,8 @@ from ..runtime import lib as _lib
 KV_BLOCK = 16
 #: Most query rows (the GQA group) a kv head may have.
 Q_TILE = 16
-HEAD_DIMS = (64, 128)
+HEAD_DIMS = (64, 128)            # head sizes every kernel takes (decode, prefill): what the engine surfaces offer
+DECODE_HEAD_DIMS = (64, 128, 256)  # the decode walk and merge also take 256 (bf16 caches)
 MAX_SPLITS = _lib.MAX_SPLITS
 
 _FP8_NAMES = ("fp8", "fp8_e4m3")
@@ -427,8 +428,8 @@ def check_decode(q, k_cache, v_cache, block_table, seq_lens, out, *, rows: str =
     reqs, heads, n_rows, d = q.shape
     if head_dim is not None and d != head_dim:
         no("q", q, f"head_dim {head_dim} (this kernel's)")
-    if d not in HEAD_DIMS:
-        no("q", q, f"head_dim in {HEAD_DIMS}")
+    if d not in DECODE_HEAD_DIMS:
+        no("q", q, f"head_dim in {DECODE_HEAD_DIMS}")
     if rows == "tile" and n_rows != Q_TILE:
         no("q", q, f"(requests, kv_heads, {Q_TILE}, head_dim): a whole {Q_TILE}-row tile")
     if not 1 <= n_rows <= Q_TILE:

@@ -92,8 +92,8 @@ def paged_attention_decode_op() -> engine.Op:
 def fused_walk_op(head_dim: int, splits: int) -> engine.Op:
     """`hk::paged_decode_fused_d{D}_s{S}` (python/hk/ops/paged.py:544-547, 706-708): the walk on
     engine views; with one split it writes the answer, with more the partials."""
-    if head_dim not in paged.HEAD_DIMS:
-        raise ValueError(f"hk.ops.paged: no walk for head_dim {head_dim} (have {paged.HEAD_DIMS})")
+    if head_dim not in paged.DECODE_HEAD_DIMS:
+        raise ValueError(f"hk.ops.paged: no walk for head_dim {head_dim} (have {paged.DECODE_HEAD_DIMS})")
 
     def impl(q, k_cache, v_cache, block_table, seq_lens, out, o_part, ml_part):
         reqs, hkv, g, d = q.shape

@@ -328,3 +328,48 @@ def test_hk_form_decode_and_merge(splits):
     scratch = paged.fused_scratch(n * splits, 8, d, "cuda", group=4)
     paged.decode(q4, g["k"], g["v"], g["table"], g["lens"], out.view(n, 8, 4, d), scratch, splits)
     _check(out, _reference(c))
+
+
+# ---------------------------------------------------------------- head_dim 256 (decode only)
+
+@pytest.mark.parametrize("splits", [1, 4, 32])
+@pytest.mark.parametrize("group,h_kv", [(2, 4), (8, 1), (16, 1)])
+def test_head_dim_256(splits, group, h_kv):
+    """512-byte rows (the reference lists D=256 among the shapes beside its D=128 route,
+    python/hk/ops/paged_decode.py:17-20): the tensor-core worker at every group, one split and the stream."""
+    c = _case(LENS, head_dim=256, h_kv=h_kv, group=group, seed=7 + splits)
+    _check(_run(c, splits=splits), _reference(c))
+
+
+def test_head_dim_256_step_writes_the_cache():
+    paged = _paged()
+    c = _case([5, 700, 33, 2048], head_dim=256, h_kv=2, group=4, seed=3)
+    g = _cuda(c)
+    n, hkv, d = 4, 2, 256
+    gen = torch.Generator().manual_seed(11)
+    key = torch.randn(n, hkv, d, generator=gen).to(torch.bfloat16)
+    value = torch.randn(n, hkv, d, generator=gen).to(torch.bfloat16)
+    slots = torch.tensor([int(c["table"][i, (s - 1) // 16]) * 16 + (s - 1) % 16 for i, s in enumerate([5, 700, 33, 2048])])
+    k_want, v_want = c["k"].clone(), c["v"].clone()
+    k_want[slots // 16, :, slots % 16] = key
+    v_want[slots // 16, :, slots % 16] = value
+    out = torch.empty_like(g["q"])
+    paged.decode_step(out, g["q"], key.cuda(), value.cuda(), g["k"].transpose(1, 2), g["v"].transpose(1, 2), slots.cuda(),
+                      g["table"], g["lens"], d ** -0.5, num_splits=8)
+    assert torch.equal(g["k"].cpu(), k_want) and torch.equal(g["v"].cpu(), v_want)
+    want = orc.paged_decode_ref(c["q"], k_want.transpose(1, 2), v_want.transpose(1, 2), c["table"], c["lens"])
+    _check(out.cpu(), want)
+
+
+# ---------------------------------------------------------------- hybrid page sizes
+
+@pytest.mark.parametrize("page", [544, 784, 2064])
+@pytest.mark.parametrize("group,h_kv,fp8", [(4, 2, False), (8, 1, False), (4, 2, True)])
+def test_hybrid_page_sizes_with_nan_past_the_end(page, group, h_kv, fp8):
+    """Pages of 544 / 784 / 2064 tokens -- the sizes vLLM gives a hybrid model's attention layers,
+    with NaN in the unused tail of the last page (python/hk/ops/paged_decode.py:17-20, 93-94):
+    34 / 49 / 129 16-token tiles a page, lengths that end inside, at and just past a page."""
+    lens = [1, page - 1, page, page + 1, 2 * page + 17]
+    c = _case(lens, h_kv=h_kv, group=group, page=page, seed=page, nan_tail=not fp8, fp8=fp8, spare=1)
+    _check(_run(c, splits=4), _reference(c))
+    _check(_run(c, splits=1), _reference(c))
