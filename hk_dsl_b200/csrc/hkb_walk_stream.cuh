@@ -99,38 +99,45 @@ struct WalkStream {
     range = max(range, (longest + parts - 2) / max(parts - 1, 1));
 
     const bool fold = WPR == 1 && a.arrivals != nullptr;
-    if (!fold) {
-      // slots that no ring of this plane will write: marked by all the plane's CTAs, a slice each
-      // (every warp marks the heads it owns)
-      for (int x = blockIdx.x * (RINGS * 32) + ring_id * 32 + lane; x < num_seqs * parts; x += gridDim.x * RINGS * 32) {
-        const int i = x / parts, p = x % parts;
-        const int nt = base[i + 1] - base[i];
-        const int np = nt > 0 ? (base[i] + nt - 1) / range - base[i] / range + 1 : 0;
-        if (p >= np) {
-          float* pl = a.part_lse + (int64_t)(i * parts + p) * a.num_q_heads + hq0;
-          for (int h = 0; h < nh; ++h) pl[h] = -INFINITY;
+    // Housekeeping every ring owes the plane, run once its first tiles are on their way (an idle ring
+    // runs it before it leaves): it only writes, so it costs the stream no latency.
+    auto housekeeping = [&]() {
+      if (!fold) {
+        // slots that no ring of this plane will write: marked by all the plane's CTAs, a slice each
+        // (every warp marks the heads it owns)
+        for (int x = blockIdx.x * (RINGS * 32) + ring_id * 32 + lane; x < num_seqs * parts; x += gridDim.x * RINGS * 32) {
+          const int i = x / parts, p = x % parts;
+          const int nt = base[i + 1] - base[i];
+          const int np = nt > 0 ? (base[i] + nt - 1) / range - base[i] / range + 1 : 0;
+          if (p >= np) {
+            float* pl = a.part_lse + (int64_t)(i * parts + p) * a.num_q_heads + hq0;
+            for (int h = 0; h < nh; ++h) pl[h] = -INFINITY;
+          }
+        }
+      } else {
+        // folding in this launch: no marks are read, but a sequence without tokens has no ring to
+        // write its output row -- zeros, as the merge kernel gives it
+        for (int i = blockIdx.x * (RINGS * 32) + ring_id * 32 + lane; i < num_seqs; i += gridDim.x * RINGS * 32) {
+          if (base[i + 1] != base[i]) continue;
+          int row = i;
+          if (a.q_start) {
+            row = __ldg(a.q_start + i);
+            if (__ldg(a.q_start + i + 1) <= row) continue;   // no query row either
+          }
+          for (int h = 0; h < nh; ++h) {
+            __nv_bfloat16* o = a.out + (int64_t)row * a.out_stride_tok + (int64_t)(hq0 + h) * a.out_stride_head;
+            for (int d = 0; d < P::HEAD_DIM; d += 2) *reinterpret_cast<__nv_bfloat162*>(o + d) = __floats2bfloat162_rn(0.f, 0.f);
+          }
         }
       }
-    } else {
-      // folding in this launch: no marks are read, but a sequence without tokens has no ring to
-      // write its output row -- zeros, as the merge kernel gives it
-      for (int i = blockIdx.x * (RINGS * 32) + ring_id * 32 + lane; i < num_seqs; i += gridDim.x * RINGS * 32) {
-        if (base[i + 1] != base[i]) continue;
-        int row = i;
-        if (a.q_start) {
-          row = __ldg(a.q_start + i);
-          if (__ldg(a.q_start + i + 1) <= row) continue;   // no query row either
-        }
-        for (int h = 0; h < nh; ++h) {
-          __nv_bfloat16* o = a.out + (int64_t)row * a.out_stride_tok + (int64_t)(hq0 + h) * a.out_stride_head;
-          for (int d = 0; d < P::HEAD_DIM; d += 2) *reinterpret_cast<__nv_bfloat162*>(o + d) = __floats2bfloat162_rn(0.f, 0.f);
-        }
-      }
-    }
+    };
 
     const int w = blockIdx.x * RINGS + ring_id;
     const int64_t g_lo64 = (int64_t)w * range;
-    if (g_lo64 >= total) return;                          // both warps of a ring leave together
+    if (g_lo64 >= total) {                                // both warps of a ring leave together
+      housekeeping();
+      return;
+    }
     const int g_lo = (int)g_lo64;
     const int g_hi = min(total, g_lo + range);
     const int n = g_hi - g_lo;
@@ -207,8 +214,13 @@ struct WalkStream {
     }
 
     // compute cursor
+    // The ring's first sequence is entered here, before the first tile is waited for, so that the
+    // loads of its query rows fly together with the tiles just requested.
     typename P::State st;
-    int seq_c = -1, seq_end = g_lo, seq_len = 0, n_tiles = 0, seq_base = 0;
+    int seq_c = lo, seq_base = base[lo], seq_end = base[lo + 1];
+    int n_tiles = seq_end - seq_base, seq_len = max(__ldg(a.seq_lens + lo), 0);
+    if (nh > 0) P::begin(st, a, a.q_start ? __ldg(a.q_start + lo) : lo, hq0, nh, lane, qs);
+    housekeeping();
     int sc = 0, sl = P::STAGES - 1;   // ring stages of the compute and of the loader
     int owe_seq[2] = {-1, -1}, owe_p[2] = {0, 0}, owe_np[2] = {0, 0};   // folds to run after the last tile
     auto close_piece = [&]() {
@@ -233,8 +245,8 @@ struct WalkStream {
       cp_async_commit();
       const int g = g_lo + k;
       if (g >= seq_end) {
-        if (seq_c >= 0 && nh > 0) close_piece();   // the piece of the sequence just finished
-        seq_c = seq_c < 0 ? lo : seq_c + 1;
+        if (nh > 0) close_piece();   // the piece of the sequence just finished
+        ++seq_c;
         while (g >= base[seq_c + 1]) ++seq_c;
         seq_base = base[seq_c];
         seq_end = base[seq_c + 1];
