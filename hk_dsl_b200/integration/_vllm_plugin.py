@@ -4,8 +4,10 @@ vLLM V1 runs the model in a spawned EngineCore process, so a patch applied in th
 never reaches it; a `vllm.general_plugins` entry point runs in every process
 (python/hk/integration/_vllm_plugin.py:3-14, 145-216 of the reference). `register()` never
 raises: a plugin that throws takes the engine's startup with it, and a route that did not
-apply is a slower server, not a broken one. A route whose `apply` raises stays off with its
-own warning line and the others proceed.
+apply is a slower server, not a broken one. Before a route is applied its engine contract is
+checked (`contract.py`: the names and parameters it binds to still exist); a route whose
+contract is broken, or whose `apply` raises, stays off with its own warning line and the
+other proceeds.
 
     [project.entry-points."vllm.general_plugins"]
     hk = "hk_dsl_b200.integration._vllm_plugin:register"
@@ -56,19 +58,13 @@ def register() -> None:
         why = switches.decide("vllm_prefill").why
         print(f"[hk] vLLM: no route on ({why}), stock (pid {pid})", flush=True)
         return
-    notes, applied, off = [], [], []
-    for name, fn in APPLY.items():
-        if name not in routes:
-            continue
-        try:
-            report, revert = fn()
-        except Exception as e:  # noqa: BLE001 -- this route is off; the others proceed
-            off.append(name)
-            print(f"[hk] WARNING: vLLM route {name} is off: its apply raised {type(e).__name__}: {e}", flush=True)
-            continue
-        applied.append(name)
-        REVERT[name] = revert
-        notes.append(report)
+    # each route's engine contract first (introspection only); a route whose contract is broken, or
+    # whose apply raises, stays off with its own warning line and the other proceeds
+    from . import contract
+
+    notes, done, off = contract.apply_routes(routes, APPLY)
+    REVERT.update(done)
+    applied = list(done)
     if not applied:
         print(f"[hk] vLLM: no route applied ({len(off)} off, see the warnings), stock (pid {pid})", flush=True)
         return

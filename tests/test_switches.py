@@ -77,5 +77,6 @@ def test_plugin_never_raises_and_says_what_it_did(capsys, monkeypatch):
     monkeypatch.setenv("HK_VLLM_PREFILL", "0")
     monkeypatch.setitem(_vllm_plugin.APPLY, "vllm_backend", lambda: (_ for _ in ()).throw(RuntimeError("boom")))
     _vllm_plugin.register()
-    out = capsys.readouterr().out
-    assert "WARNING" in out and "boom" in out and "no route applied" in out
+    got = capsys.readouterr()
+    assert "WARNING" in got.err and "boom" in got.err and "route vllm_backend OFF" in got.err     # the warning line: stderr
+    assert "no route applied" in got.out
