@@ -258,3 +258,22 @@ def test_as_a_torch_op():
     assert r is None
     assert torch.equal(_bits(k), _bits(g["k_want"])) and torch.equal(_bits(v), _bits(g["v_want"]))
     _check(o.cpu(), _want(c))
+
+
+@pytest.mark.parametrize("n", [2048, 2100])
+def test_batches_at_and_past_the_streams_sequence_limit(n):
+    """2048 sequences is the most the persistent stream keeps a prefix table for; one more batch
+    size up, the same calls run on the fixed-split grid and the step on its three separate launches.
+    Same answers, same cache, either side of the limit."""
+    g0 = torch.Generator().manual_seed(n)
+    lens = torch.randint(1, 48, (n,), generator=g0).tolist()
+    c = _step_case(lens, seed=n % 97, h_kv=2, group=4)
+    g = _cuda(c)
+    o1, k1, v1 = _separate(g, c, 2)
+    o2, k2, v2 = _joined(g, c, 2, fold=False)
+    o3, k3, v3 = _joined(g, c, 2, fold=True)
+    for k, v in ((k1, v1), (k2, v2), (k3, v3)):
+        assert torch.equal(_bits(k), _bits(g["k_want"])) and torch.equal(_bits(v), _bits(g["v_want"]))
+    want = _want(c)
+    for o in (o1, o2, o3):
+        _check(o.cpu(), want)
