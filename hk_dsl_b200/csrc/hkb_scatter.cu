@@ -24,39 +24,48 @@ struct ScatterArgs {
   int num_tokens, num_kv_heads, head_dim, block_size;
 };
 
-// grid = (ceil(tokens / TOK_PER_CTA), 2 [K, V]); each thread walks (token, head, chunk)
-// items of its CTA's tokens, a chunk being 8 bf16 elements of the source row.
+// grid = (ceil(tokens / TOK_PER_CTA), 2 [K, V]); a warp takes a token at a time -- its slot is
+// read and split into (block, offset) once -- and its lanes the token's 16-byte chunks (8 bf16
+// elements of a (head, chunk) each), so the per-chunk work is one load, one store and a shift.
 template <bool FP8>
 __global__ void __launch_bounds__(256) scatter_kernel(const ScatterArgs a, int tok_per_cta) {
   const int which = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int chunks_per_head = a.head_dim >> 3;
   const int chunks_per_tok = a.num_kv_heads * chunks_per_head;
+  const int shift = (chunks_per_head & (chunks_per_head - 1)) == 0 ? __ffs(chunks_per_head) - 1 : -1;
   const int t0 = blockIdx.x * tok_per_cta;
   const int t1 = min(a.num_tokens, t0 + tok_per_cta);
-  const int items = (t1 - t0) * chunks_per_tok;
   float inv_scale_den = 1.0f;
   if (FP8) inv_scale_den = __ldg(a.scale[which]);
 
-  for (int it = threadIdx.x; it < items; it += blockDim.x) {
-    const int t = t0 + it / chunks_per_tok;
-    const int rem = it % chunks_per_tok;
-    const int h = rem / chunks_per_head;
-    const int c = rem % chunks_per_head;
+  // a token with fewer than 32 chunks (one kv head of 128 on a GPU of a head-sharded job): the warp
+  // takes 32 / chunks of them at once, so that no lane idles
+  const int tpw = chunks_per_tok < 32 && 32 % chunks_per_tok == 0 ? 32 / chunks_per_tok : 1;
+  const int sub = tpw > 1 ? lane / chunks_per_tok : 0;
+  const int x0 = tpw > 1 ? lane - sub * chunks_per_tok : lane;
+  const int xstep = tpw > 1 ? chunks_per_tok : 32;
+  for (int tw = t0 + warp * tpw; tw < t1; tw += 8 * tpw) {
+    const int t = tw + sub;
+    if (t >= t1) continue;
     int64_t slot;
     if (a.slot_is_i64) slot = __ldg(reinterpret_cast<const long long*>(a.slots) + t);
     else slot = __ldg(reinterpret_cast<const int*>(a.slots) + t);
     if (slot < 0 || slot >= a.num_slots[which]) continue;  // padding token, or out of the pool
     const int64_t blk = slot / a.block_size;
     const int64_t off = slot - blk * a.block_size;
-    const __nv_bfloat16* s =
-        a.src[which] + (int64_t)t * a.src_stride_tok[which] + (int64_t)h * a.src_stride_head[which] + c * 8;
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(s));
-    const int64_t d = blk * a.dst_stride_block[which] + off * a.dst_stride_token[which] +
-                      (int64_t)h * a.dst_stride_head[which] + c * 8;
-    if (!FP8) {
-      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.dst[which]) + d) = v;
-    } else {
-      *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(a.dst[which]) + d) = quantize_chunk_e4m3(v, inv_scale_den);
+    const __nv_bfloat16* src = a.src[which] + (int64_t)t * a.src_stride_tok[which];
+    const int64_t dst = blk * a.dst_stride_block[which] + off * a.dst_stride_token[which];
+    for (int x = x0; x < chunks_per_tok; x += xstep) {
+      const int h = shift >= 0 ? x >> shift : x / chunks_per_head;
+      const int c = x - h * chunks_per_head;
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + (int64_t)h * a.src_stride_head[which] + c * 8));
+      const int64_t d = dst + (int64_t)h * a.dst_stride_head[which] + c * 8;
+      if (!FP8) {
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.dst[which]) + d) = v;
+      } else {
+        *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(a.dst[which]) + d) = quantize_chunk_e4m3(v, inv_scale_den);
+      }
     }
   }
 }
