@@ -177,15 +177,13 @@ struct Prefill {
     ld.tiles_per_page = a.tiles_per_page; ld.num_blocks = a.num_blocks;
     const int* table_row = a.block_table + (int64_t)req * a.table_stride;
 
-    // where this lane's ldmatrix rows sit inside a 16-token tile, one value a 16-dim chunk:
-    // A (query rows, row-major), B for S (key rows), B for O (value rows, read transposed)
-    uint32_t qoff[KD], koff[KD], voff[KD];
-#pragma unroll
-    for (int kc = 0; kc < KD; ++kc) {
-      qoff[kc] = tile_off<ROWB>(lane & 15, kc * 2 + (lane >> 4));
-      koff[kc] = tile_off<ROWB>(((lane >> 4) & 1) * 8 + (lane & 7), kc * 2 + ((lane >> 3) & 1));
-      voff[kc] = tile_off<ROWB>(((lane >> 3) & 1) * 8 + (lane & 7), kc * 2 + (lane >> 4));
-    }
+    // Where this lane's ldmatrix rows sit inside a 16-token tile: A (query rows, row-major), B for S
+    // (key rows), B for O (value rows, read transposed). The offset of 16-dim chunk kc is the chunk-0
+    // offset XOR (kc << 5): the swizzle XORs the 16-byte chunk index with the row, and 2 kc only
+    // touches bits the lane's own part of the index leaves alone -- one register a kind, not KD.
+    const uint32_t qoff0 = tile_off<ROWB>(lane & 15, lane >> 4);
+    const uint32_t koff0 = tile_off<ROWB>(((lane >> 4) & 1) * 8 + (lane & 7), (lane >> 3) & 1);
+    const uint32_t voff0 = tile_off<ROWB>(((lane >> 3) & 1) * 8 + (lane & 7), lane >> 4);
 
     fill(a, ld, land, 0, kv_limit, table_row, warp, lane);
     cp_async_commit();
@@ -225,11 +223,11 @@ struct Prefill {
       for (int kc = 0; kc < KD; ++kc) {
         uint32_t qa[UPW][4];
 #pragma unroll
-        for (int i = 0; i < UPW; ++i) ldmatrix_x4(qa[i], qsm + (warp * UPW + i) * TILE_BYTES + qoff[kc]);
+        for (int i = 0; i < UPW; ++i) ldmatrix_x4(qa[i], qsm + (warp * UPW + i) * TILE_BYTES + (qoff0 ^ (kc << 5)));
 #pragma unroll
         for (int t = 0; t < KV_TILES; ++t) {
           uint32_t kb[4];
-          ldmatrix_x4(kb, stage + (t * 2) * TILE_BYTES + koff[kc]);
+          ldmatrix_x4(kb, stage + (t * 2) * TILE_BYTES + (koff0 ^ (kc << 5)));
           const uint32_t b0[2] = {kb[0], kb[1]}, b1[2] = {kb[2], kb[3]};
 #pragma unroll
           for (int i = 0; i < UPW; ++i) {
@@ -298,7 +296,7 @@ struct Prefill {
 #pragma unroll
         for (int dt = 0; dt < KD; ++dt) {
           uint32_t vb[4];
-          ldmatrix_x4_trans(vb, stage + (t * 2 + 1) * TILE_BYTES + voff[dt]);
+          ldmatrix_x4_trans(vb, stage + (t * 2 + 1) * TILE_BYTES + (voff0 ^ (dt << 5)));
           const uint32_t b0[2] = {vb[0], vb[1]}, b1[2] = {vb[2], vb[3]};
 #pragma unroll
           for (int i = 0; i < UPW; ++i) {
