@@ -277,3 +277,29 @@ def test_batches_at_and_past_the_streams_sequence_limit(n):
     want = _want(c)
     for o in (o1, o2, o3):
         _check(o.cpu(), want)
+
+
+@pytest.mark.parametrize("name", ["c2", "c3", "c4"])
+def test_full_size_configs_step_equals_separate_launches(name):
+    """At the measured configurations' full sizes (no oracle needed): the two-launch step leaves the
+    same cache and the same answer, bit for bit, as cache write + walk + merge launched separately."""
+    from hk_dsl_b200 import workloads as W
+
+    paged = _paged()
+    spec = W.CONFIGS[name]
+    st = W.build_step(spec, "cuda")
+    k0, v0 = st.k_caches[0], st.v_caches[0]
+    # the step's slots hold something else before it runs
+    key = torch.randn(st.key.shape, device="cuda").to(torch.bfloat16)
+    value = torch.randn(st.value.shape, device="cuda").to(torch.bfloat16)
+    ka, va = k0.clone(), v0.clone()
+    paged.reshape_and_cache(key, value, ka, va, st.slot_mapping, spec.kv_cache_dtype, st.k_scale, st.v_scale)
+    o1 = torch.empty_like(st.out)
+    paged.paged_attention_decode(o1, st.query, ka, va, st.block_table, st.seq_lens, st.scale, spec.kv_cache_dtype,
+                                 st.k_scale, st.v_scale)
+    o2 = torch.empty_like(st.out)
+    paged.decode_step(o2, st.query, key, value, k0, v0, st.slot_mapping, st.block_table, st.seq_lens, st.scale,
+                      spec.kv_cache_dtype, st.k_scale, st.v_scale)
+    torch.cuda.synchronize()
+    assert torch.equal(_bits(k0), _bits(ka)) and torch.equal(_bits(v0), _bits(va))
+    assert torch.equal(o1.view(torch.int16), o2.view(torch.int16))
