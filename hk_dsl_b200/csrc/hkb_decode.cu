@@ -19,7 +19,7 @@ namespace hkb {
 struct MergeArgs {
   void* out;
   int64_t out_stride_tok, out_stride_head;
-  int out_is_f32;
+  int out_is_f32;   // 0: bf16, 1: fp32, 2: fp16
   float* out_lse;
   const float* part_out;
   int64_t part_stride_p, part_stride_seq;
@@ -102,10 +102,14 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_kernel(const MergeArgs
   }
   const float inv = den > 0.f ? 1.f / den : 0.f;
   const int64_t off = (int64_t)row * a.out_stride_tok + (int64_t)h * a.out_stride_head + lane * VEC;
-  if (a.out_is_f32) {
+  if (a.out_is_f32 == 1) {
     float* o = reinterpret_cast<float*>(a.out) + off;
 #pragma unroll
     for (int v = 0; v < VEC; v += 2) *reinterpret_cast<float2*>(o + v) = make_float2(acc[v] * inv, acc[v + 1] * inv);
+  } else if (a.out_is_f32 == 2) {   // fp16 activations
+    __half* o = reinterpret_cast<__half*>(a.out) + off;
+#pragma unroll
+    for (int v = 0; v < VEC; v += 2) *reinterpret_cast<__half2*>(o + v) = __floats2half2_rn(acc[v] * inv, acc[v + 1] * inv);
   } else {
     __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out) + off;
 #pragma unroll
@@ -181,10 +185,14 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_wide_kernel(const Merg
   }
   const float inv = den > 0.f ? 1.f / den : 0.f;
   const int64_t off = (int64_t)row * a.out_stride_tok + (int64_t)h * a.out_stride_head + lane * VEC;
-  if (a.out_is_f32) {
+  if (a.out_is_f32 == 1) {
     float* o = reinterpret_cast<float*>(a.out) + off;
 #pragma unroll
     for (int v = 0; v < VEC; v += 2) *reinterpret_cast<float2*>(o + v) = make_float2(acc[v] * inv, acc[v + 1] * inv);
+  } else if (a.out_is_f32 == 2) {   // fp16 activations
+    __half* o = reinterpret_cast<__half*>(a.out) + off;
+#pragma unroll
+    for (int v = 0; v < VEC; v += 2) *reinterpret_cast<__half2*>(o + v) = __floats2half2_rn(acc[v] * inv, acc[v + 1] * inv);
   } else {
     __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out) + off;
 #pragma unroll
@@ -313,7 +321,7 @@ static int dispatch_cc(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
 }
 
 // Tensor-core walk for groups of 8 to 16: NT 8-head column tiles a CTA.
-template <int D, bool FP8>
+template <int D, bool FP8, bool F16 = false>
 static int dispatch_mma(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
   constexpr int WARPS = 4;
   // a 16-token K+V tile of head_dim 256 is 16 KB: two stages a ring, six rings in the one CTA an SM has room for
@@ -324,10 +332,10 @@ static int dispatch_mma(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
       constexpr int RINGS = 6;
       grid = stream_grid(a.num_kv_heads, 1);
       if (a.group <= 8) {
-        using P = WalkMMA<D, FP8, 1, WARPS, NST>;
+        using P = WalkMMA<D, FP8, 1, WARPS, NST, F16>;
         return launch_stream<walk_stream_kernel<P, RINGS>>(WalkStream<P, RINGS>::SMEM_BYTES, RINGS * 32, grid, a, num_seqs, st);
       }
-      using P2 = WalkMMA<D, FP8, 2, WARPS, NST>;
+      using P2 = WalkMMA<D, FP8, 2, WARPS, NST, F16>;
       return launch_stream<walk_stream_kernel<P2, RINGS>>(WalkStream<P2, RINGS>::SMEM_BYTES, RINGS * 32, grid, a, num_seqs, st);
     } else {
     grid = stream_grid(a.num_kv_heads);
@@ -354,16 +362,16 @@ static int dispatch_mma(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
       }
     }
     if (a.group <= 8)
-      return launch_stream<walk_stream_kernel<WalkMMA<D, FP8, 1, WARPS, NST>, WARPS>>(
-          WalkStream<WalkMMA<D, FP8, 1, WARPS, NST>, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
-    return launch_stream<walk_stream_kernel<WalkMMA<D, FP8, 2, WARPS, NST>, WARPS>>(
-        WalkStream<WalkMMA<D, FP8, 2, WARPS, NST>, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
+      return launch_stream<walk_stream_kernel<WalkMMA<D, FP8, 1, WARPS, NST, F16>, WARPS>>(
+          WalkStream<WalkMMA<D, FP8, 1, WARPS, NST, F16>, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
+    return launch_stream<walk_stream_kernel<WalkMMA<D, FP8, 2, WARPS, NST, F16>, WARPS>>(
+        WalkStream<WalkMMA<D, FP8, 2, WARPS, NST, F16>, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
     }
   }
   if (a.group <= 8)
-    return launch_walk<walk_mma_kernel<D, FP8, 1, WARPS, NST>>(WalkMMA<D, FP8, 1, WARPS, NST>::SMEM_BYTES,
+    return launch_walk<walk_mma_kernel<D, FP8, 1, WARPS, NST, F16>>(WalkMMA<D, FP8, 1, WARPS, NST, F16>::SMEM_BYTES,
                                                                WARPS * 32, grid, a, st);
-  return launch_walk<walk_mma_kernel<D, FP8, 2, WARPS, NST>>(WalkMMA<D, FP8, 2, WARPS, NST>::SMEM_BYTES,
+  return launch_walk<walk_mma_kernel<D, FP8, 2, WARPS, NST, F16>>(WalkMMA<D, FP8, 2, WARPS, NST, F16>::SMEM_BYTES,
                                                              WARPS * 32, grid, a, st);
 }
 
@@ -410,8 +418,8 @@ static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_hea
   if (num_q_heads % num_kv_heads) return HKB_ERR_GROUP;
   const int group = num_q_heads / num_kv_heads;
   if (group > HKB_MAX_GROUP) return HKB_ERR_GROUP;
-  if (kv_dtype != HKB_KV_BF16 && kv_dtype != HKB_KV_FP8_E4M3) return HKB_ERR_DTYPE;
-  const bool fp8 = kv_dtype == HKB_KV_FP8_E4M3;
+  if (kv_dtype != HKB_KV_BF16 && kv_dtype != HKB_KV_FP8_E4M3 && kv_dtype != HKB_KV_F16) return HKB_ERR_DTYPE;
+  const bool fp8 = kv_dtype == HKB_KV_FP8_E4M3, f16 = kv_dtype == HKB_KV_F16;
   if (fp8 && (!k_scale || !v_scale)) return HKB_ERR_SCALE;
   if (fp8 && head_dim != 128) return HKB_ERR_UNSUPPORTED;
   if (num_splits < 1 || num_splits > HKB_MAX_SPLITS) return HKB_ERR_SPLITS;
@@ -447,7 +455,7 @@ static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_hea
   a.new_k_stride_tok = a.new_k_stride_head = a.new_v_stride_tok = a.new_v_stride_head = 0;
   a.slots = nullptr; a.slot_is_i64 = 0; a.block_size = block_size;
   if (extra && step_fusable(num_splits, num_seqs)) {
-    if (extra->arrivals) {
+    if (extra->arrivals && !f16) {   // the fold on arrival writes bf16; fp16 steps keep the merge launch
       a.arrivals = extra->arrivals;
       extra->folded = true;
     }
@@ -461,6 +469,11 @@ static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_hea
   }
   cudaStream_t st = (cudaStream_t)stream;
 
+  if (f16) {   // fp16: the tensor-core worker at every group (the CUDA-core workers unpack bf16)
+    if (head_dim == 128) return dispatch_mma<128, false, true>(a, num_seqs, st);
+    if (head_dim == 256) return dispatch_mma<256, false, true>(a, num_seqs, st);
+    return dispatch_mma<64, false, true>(a, num_seqs, st);
+  }
   const bool mma = hkb_walk_uses_mma(group, kv_dtype) != 0;
   if (head_dim == 128) {
     if (fp8) return mma ? dispatch_mma<128, true>(a, num_seqs, st) : dispatch_cc<128, true>(a, num_seqs, st);
@@ -487,6 +500,7 @@ extern "C" int hkb_walk_uses_mma(int group, int kv_dtype) {
     const int x = v ? std::atoi(v) : 0;
     return x >= 1 && x <= 8 ? x : 0;
   }();
+  if (kv_dtype == HKB_KV_F16) return 1;
   const int bound = forced ? forced : (kv_dtype == HKB_KV_FP8_E4M3 ? 1 : 4);
   return group >= bound ? 1 : 0;
 }
@@ -543,7 +557,7 @@ extern "C" int hkb_decode_step(void* out, int64_t out_stride_tok, int64_t out_st
                        table_stride, max_pages, seq_lens, q_start, num_seqs, num_q_heads, num_kv_heads, head_dim,
                        block_size, scale, kv_dtype, k_scale, v_scale, num_splits, part_out, part_lse, stream, &x);
   if (rc != HKB_OK || x.folded || num_splits <= 1) return rc;
-  return hkb_merge(out, out_stride_tok, out_stride_head, 0, nullptr, part_out, (int64_t)num_q_heads * head_dim,
+  return hkb_merge(out, out_stride_tok, out_stride_head, kv_dtype == HKB_KV_F16 ? 2 : 0, nullptr, part_out, (int64_t)num_q_heads * head_dim,
                    (int64_t)num_splits * num_q_heads * head_dim, part_lse, num_q_heads,
                    (int64_t)num_splits * num_q_heads, num_splits, num_seqs, num_q_heads, head_dim, seq_lens, q_start,
                    stream);
@@ -562,7 +576,7 @@ extern "C" int hkb_merge(void* out, int64_t out_stride_tok, int64_t out_stride_h
   if (head_dim != 64 && head_dim != 128 && head_dim != 256) return HKB_ERR_HEAD_DIM;
   if (num_seqs > 65535) return HKB_ERR_SIZE;
   if ((part_stride_p | part_stride_seq) % 4 || (out_stride_tok | out_stride_head) % 4) return HKB_ERR_STRIDE;
-  if ((uintptr_t)part_out % 16 || (uintptr_t)out % (out_is_f32 ? 16 : 8)) return HKB_ERR_ALIGN;
+  if ((uintptr_t)part_out % 16 || (uintptr_t)out % (out_is_f32 == 1 ? 16 : 8)) return HKB_ERR_ALIGN;
   MergeArgs a;
   a.out = out; a.out_stride_tok = out_stride_tok; a.out_stride_head = out_stride_head;
   a.out_is_f32 = out_is_f32; a.out_lse = out_lse;
@@ -655,7 +669,7 @@ extern "C" int hkb_paged_decode_static(void* out, int64_t out_stride_tok, int64_
                             table_stride, max_pages, seq_lens, q_start, num_seqs, num_q_heads, num_kv_heads, head_dim,
                             block_size, scale, kv_dtype, k_scale, v_scale, num_splits, part_out, part_lse, stream);
   if (rc != HKB_OK) return rc;
-  return hkb_merge(out, out_stride_tok, out_stride_head, 0, nullptr, part_out, (int64_t)num_q_heads * head_dim,
+  return hkb_merge(out, out_stride_tok, out_stride_head, kv_dtype == HKB_KV_F16 ? 2 : 0, nullptr, part_out, (int64_t)num_q_heads * head_dim,
                    (int64_t)num_splits * num_q_heads * head_dim, part_lse, num_q_heads,
                    (int64_t)num_splits * num_q_heads, num_splits, num_seqs, num_q_heads, head_dim, seq_lens, q_start,
                    stream);

@@ -46,8 +46,9 @@ struct PrefillArgs {
   const float* v_scale;
 };
 
-template <int D, int GP, bool FP8>
+template <int D, int GP, bool FP8, bool F16 = false>
 struct Prefill {
+  static_assert(!(FP8 && F16), "an fp8 cache goes with bf16 activations");
   static constexpr int WARPS = 4;
   static constexpr int UNITS = 8;                     // (16-row query tile, query head) pairs a CTA: two a warp
   static constexpr int UPW = UNITS / WARPS;
@@ -231,8 +232,8 @@ struct Prefill {
           const uint32_t b0[2] = {kb[0], kb[1]}, b1[2] = {kb[2], kb[3]};
 #pragma unroll
           for (int i = 0; i < UPW; ++i) {
-            mma_bf16(sc[i][2 * t], qa[i], b0);
-            mma_bf16(sc[i][2 * t + 1], qa[i], b1);
+            mma16<F16>(sc[i][2 * t], qa[i], b0);
+            mma16<F16>(sc[i][2 * t + 1], qa[i], b1);
           }
         }
       }
@@ -284,10 +285,10 @@ struct Prefill {
           const float p12 = fast_exp2(fmaf(sc[i][2 * t + 1][2], qs, sb)), p13 = fast_exp2(fmaf(sc[i][2 * t + 1][3], qs, sb));
           l[i][0] += (p00 + p01) + (p10 + p11);
           l[i][1] += (p02 + p03) + (p12 + p13);
-          pa[i][t][0] = pack_bf16x2(p00, p01);   // (row A, keys 0-7 pair)
-          pa[i][t][1] = pack_bf16x2(p02, p03);   // (row B, keys 0-7 pair)
-          pa[i][t][2] = pack_bf16x2(p10, p11);   // (row A, keys 8-15 pair)
-          pa[i][t][3] = pack_bf16x2(p12, p13);   // (row B, keys 8-15 pair)
+          pa[i][t][0] = pack16x2<F16>(p00, p01);   // (row A, keys 0-7 pair)
+          pa[i][t][1] = pack16x2<F16>(p02, p03);   // (row B, keys 0-7 pair)
+          pa[i][t][2] = pack16x2<F16>(p10, p11);   // (row A, keys 8-15 pair)
+          pa[i][t][3] = pack16x2<F16>(p12, p13);   // (row B, keys 8-15 pair)
         }
       }
       // O += P V: B = V^T read transposed from the row-major V tiles; every V fragment feeds both units
@@ -300,8 +301,8 @@ struct Prefill {
           const uint32_t b0[2] = {vb[0], vb[1]}, b1[2] = {vb[2], vb[3]};
 #pragma unroll
           for (int i = 0; i < UPW; ++i) {
-            mma_bf16(o[i][2 * dt], pa[i][t], b0);
-            mma_bf16(o[i][2 * dt + 1], pa[i][t], b1);
+            mma16<F16>(o[i][2 * dt], pa[i][t], b0);
+            mma16<F16>(o[i][2 * dt + 1], pa[i][t], b1);
           }
         }
       }
@@ -322,45 +323,45 @@ struct Prefill {
 #pragma unroll
       for (int nt = 0; nt < 2 * KD; ++nt) {
         const int d = nt * 8 + 2 * (lane & 3);
-        if (vA) *reinterpret_cast<uint32_t*>(oA + d) = pack_bf16x2(o[i][nt][0] * iA, o[i][nt][1] * iA);
-        if (vB) *reinterpret_cast<uint32_t*>(oB + d) = pack_bf16x2(o[i][nt][2] * iB, o[i][nt][3] * iB);
+        if (vA) *reinterpret_cast<uint32_t*>(oA + d) = pack16x2<F16>(o[i][nt][0] * iA, o[i][nt][1] * iA);
+        if (vB) *reinterpret_cast<uint32_t*>(oB + d) = pack16x2<F16>(o[i][nt][2] * iB, o[i][nt][3] * iB);
       }
     }
   }
 };
 
-template <int D, int GP, bool FP8>
+template <int D, int GP, bool FP8, bool F16>
 __global__ void __launch_bounds__(128, 2) prefill_kernel(const PrefillArgs a) {
   extern __shared__ __align__(128) uint8_t hkb_smem[];
-  Prefill<D, GP, FP8>::run(a, hkb_smem);
+  Prefill<D, GP, FP8, F16>::run(a, hkb_smem);
 }
 
-template <int D, int GP, bool FP8>
+template <int D, int GP, bool FP8, bool F16>
 static int launch_prefill(const PrefillArgs& a, int num_work, cudaStream_t st) {
   static bool armed[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
-  constexpr int smem = Prefill<D, GP, FP8>::SMEM_BYTES;
+  constexpr int smem = Prefill<D, GP, FP8, F16>::SMEM_BYTES;
   if (e == cudaSuccess && dev >= 0 && dev < 64 && !armed[dev]) {
-    e = cudaFuncSetAttribute(prefill_kernel<D, GP, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    e = cudaFuncSetAttribute(prefill_kernel<D, GP, FP8, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e == cudaSuccess) armed[dev] = true;
   }
   if (e == cudaSuccess) {
     dim3 grid(num_work, a.num_kv_heads * (a.group / GP));
-    prefill_kernel<D, GP, FP8><<<grid, Prefill<D, GP, FP8>::WARPS * 32, smem, st>>>(a);
+    prefill_kernel<D, GP, FP8, F16><<<grid, Prefill<D, GP, FP8, F16>::WARPS * 32, smem, st>>>(a);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
   return HKB_OK;
 }
 
-template <int D, bool FP8>
+template <int D, bool FP8, bool F16 = false>
 static int dispatch_prefill(const PrefillArgs& a, int num_work, cudaStream_t st) {
   // heads of the GQA group a CTA serves: the largest of 8, 4, 2, 1 that divides the group
-  if (a.group % 8 == 0) return launch_prefill<D, 8, FP8>(a, num_work, st);
-  if (a.group % 4 == 0) return launch_prefill<D, 4, FP8>(a, num_work, st);
-  if (a.group % 2 == 0) return launch_prefill<D, 2, FP8>(a, num_work, st);
-  return launch_prefill<D, 1, FP8>(a, num_work, st);
+  if (a.group % 8 == 0) return launch_prefill<D, 8, FP8, F16>(a, num_work, st);
+  if (a.group % 4 == 0) return launch_prefill<D, 4, FP8, F16>(a, num_work, st);
+  if (a.group % 2 == 0) return launch_prefill<D, 2, FP8, F16>(a, num_work, st);
+  return launch_prefill<D, 1, FP8, F16>(a, num_work, st);
 }
 
 }  // namespace hkb
@@ -388,7 +389,7 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
   if (head_dim != 64 && head_dim != 128) return HKB_ERR_HEAD_DIM;
   if (block_size <= 0 || block_size % TILE_TOKENS) return HKB_ERR_BLOCK_SIZE;
   if (num_q_heads % num_kv_heads || num_q_heads / num_kv_heads > HKB_MAX_GROUP) return HKB_ERR_GROUP;
-  if (kv_dtype != HKB_KV_BF16 && kv_dtype != HKB_KV_FP8_E4M3) return HKB_ERR_DTYPE;
+  if (kv_dtype != HKB_KV_BF16 && kv_dtype != HKB_KV_FP8_E4M3 && kv_dtype != HKB_KV_F16) return HKB_ERR_DTYPE;
   const bool fp8 = kv_dtype == HKB_KV_FP8_E4M3;
   if (fp8 && (!k_scale || !v_scale)) return HKB_ERR_SCALE;
   if (fp8 && head_dim != 128) return HKB_ERR_UNSUPPORTED;
@@ -418,5 +419,7 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
   a.v_scale = fp8 ? v_scale : nullptr;
   cudaStream_t st = (cudaStream_t)stream;
   if (fp8) return dispatch_prefill<128, true>(a, num_work, st);
+  if (kv_dtype == HKB_KV_F16)
+    return head_dim == 128 ? dispatch_prefill<128, false, true>(a, num_work, st) : dispatch_prefill<64, false, true>(a, num_work, st);
   return head_dim == 128 ? dispatch_prefill<128, false>(a, num_work, st) : dispatch_prefill<64, false>(a, num_work, st);
 }

@@ -88,7 +88,8 @@ extern "C" int hkb_reshape_and_cache(const void* key, const void* value,
   if (!key || !value || !kc.ptr || !vc.ptr || !slot_mapping) return HKB_ERR_NULL;
   if (head_dim <= 0 || head_dim % 8 != 0 || head_dim > 1024) return HKB_ERR_HEAD_DIM;
   if (block_size <= 0) return HKB_ERR_BLOCK_SIZE;
-  if (kv_dtype != HKB_KV_BF16 && kv_dtype != HKB_KV_FP8_E4M3) return HKB_ERR_DTYPE;
+  // fp16 rows are copied like bf16 rows: 16-bit elements, no conversion
+  if (kv_dtype != HKB_KV_BF16 && kv_dtype != HKB_KV_FP8_E4M3 && kv_dtype != HKB_KV_F16) return HKB_ERR_DTYPE;
   const bool fp8 = kv_dtype == HKB_KV_FP8_E4M3;
   if (fp8 && (!k_scale || !v_scale)) return HKB_ERR_SCALE;
   // 16-byte source chunks; destination chunks are 16 bytes (bf16) or 8 bytes (fp8).

@@ -43,8 +43,32 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int D, bool FP8, int NT, int WARPS, int NST>
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+// The 16-bit type of the activations and of a 16-bit cache: bf16, or fp16 (F16) for a model served
+// in float16. Same fragments, same loads; the mma instruction, the packing of P and the output differ.
+template <bool F16>
+__device__ __forceinline__ void mma16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  if (F16) mma_f16(c, a, b); else mma_bf16(c, a, b);
+}
+template <bool F16>
+__device__ __forceinline__ uint32_t pack16x2(float lo, float hi) { return F16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi); }
+template <bool F16>
+__device__ __forceinline__ void store16(__nv_bfloat16* p, float x) {
+  if (F16) *reinterpret_cast<__half*>(p) = __float2half_rn(x); else *p = __float2bfloat16(x);
+}
+
+template <int D, bool FP8, int NT, int WARPS, int NST, bool F16 = false>
 struct WalkMMA {
+  static_assert(!(FP8 && F16), "an fp8 cache goes with bf16 activations");
   static constexpr int ES = FP8 ? 1 : 2;
   static constexpr int ROWB = D * ES;     // bytes of a row as it sits in the cache
   static constexpr int ROWB16 = D * 2;    // bytes of a row as the mma reads it
@@ -100,7 +124,7 @@ struct WalkMMA {
         uint32_t a[4];
         ldmatrix_x4(a, ktile + tile_off<ROWB16>(r, kc * 2 + (lane >> 4)));
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) mma_bf16(sc[nt], a, qb[nt][kc]);
+        for (int nt = 0; nt < NT; ++nt) mma16<F16>(sc[nt], a, qb[nt][kc]);
       }
     }
     const int tA = tok0 + (lane >> 2), tB = tA + 8;  // the two tokens this lane holds scores of
@@ -139,8 +163,8 @@ struct WalkMMA {
       l[nt][0] += p0 + p2;
       l[nt][1] += p1 + p3;
       // [token, head] fragments -> [head, token] = the B operand of the second product
-      pb[nt][0] = movmatrix_trans(pack_bf16x2(p0, p1));
-      pb[nt][1] = movmatrix_trans(pack_bf16x2(p2, p3));
+      pb[nt][0] = movmatrix_trans(pack16x2<F16>(p0, p1));
+      pb[nt][1] = movmatrix_trans(pack16x2<F16>(p2, p3));
     }
     // O^T += V^T P^T: A = V^T (16 dims x tokens), read transposed from the row-major V tile
     {
@@ -150,7 +174,7 @@ struct WalkMMA {
         uint32_t a[4];
         ldmatrix_x4_trans(a, vtile + tile_off<ROWB16>(r, dt * 2 + ((lane >> 3) & 1)));
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) mma_bf16(o[nt][dt], a, pb[nt]);
+        for (int nt = 0; nt < NT; ++nt) mma16<F16>(o[nt][dt], a, pb[nt]);
       }
     }
   }
@@ -265,8 +289,7 @@ struct WalkMMA {
         if (threadIdx.x < nh) pl[threadIdx.x] = -INFINITY;
       } else {
         for (int x = threadIdx.x; x < nh * D; x += WARPS * 32)
-          a.out[(int64_t)row * a.out_stride_tok + (int64_t)(hq0 + x / D) * a.out_stride_head + x % D] =
-              __float2bfloat16(0.f);
+          store16<F16>(a.out + (int64_t)row * a.out_stride_tok + (int64_t)(hq0 + x / D) * a.out_stride_head + x % D, 0.f);
       }
       return;
     }
@@ -384,7 +407,7 @@ struct WalkMMA {
         po[h * D + d] = val;
         if (d == 0) pl[h] = den > 0.f ? (mm + log2f(den)) * LN2 : -INFINITY;
       } else {
-        a.out[(int64_t)row * a.out_stride_tok + (int64_t)(hq0 + h) * a.out_stride_head + d] = __float2bfloat16(val);
+        store16<F16>(a.out + (int64_t)row * a.out_stride_tok + (int64_t)(hq0 + h) * a.out_stride_head + d, val);
       }
     }
   }
@@ -407,20 +430,10 @@ struct WalkMMA {
 //     32jj + 4g .. + 3) of token rows 2t, 2t+1, 2t+8, 2t+9; a byte permute pairs the tokens of
 //     one dim. Rows g / g+8 of output tile 2jj + cc are then dims 32jj + 4g + 2cc / + 1: the
 //     output's dim order is permuted, which `end` undoes when it writes the partial.
-__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-}
 __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_bytes) {
   uint32_t h2;
   asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(h2) : "h"((uint16_t)two_bytes));
   return h2;
-}
-__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
-  const __half2 v = __floats2half2_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t*>(&v);
 }
 __device__ __forceinline__ uint2 lds64(uint32_t addr) {
   uint2 v;
@@ -618,10 +631,10 @@ struct WalkMMAF8 {
   }
 };
 
-template <int D, bool FP8, int NT, int WARPS, int NST>
+template <int D, bool FP8, int NT, int WARPS, int NST, bool F16 = false>
 __global__ void __launch_bounds__(WARPS * 32) walk_mma_kernel(const DecodeArgs a) {
   extern __shared__ __align__(128) uint8_t hkb_smem[];
-  WalkMMA<D, FP8, NT, WARPS, NST>::run(a, hkb_smem);
+  WalkMMA<D, FP8, NT, WARPS, NST, F16>::run(a, hkb_smem);
 }
 
 }  // namespace hkb

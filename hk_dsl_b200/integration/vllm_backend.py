@@ -115,9 +115,10 @@ class HKAttentionImplCore:
         if logits_soft_cap:
             raise NotImplementedError(f"{NAME} has no logits_soft_cap")
         name = (kv_cache_dtype or "auto").lower()
-        if not (name.startswith("auto") or name in ("fp8", "fp8_e4m3", "bfloat16")):
+        if not (name.startswith("auto") or name in ("fp8", "fp8_e4m3", "bfloat16", "float16", "half")):
             raise NotImplementedError(
-                f"{NAME} keeps the cache in bfloat16 or fp8-e4m3 (per-tensor scales), not {kv_cache_dtype}")
+                f"{NAME} keeps the cache in the model's 16-bit dtype (bfloat16 or float16) or in fp8-e4m3 "
+                f"(per-tensor scales, bfloat16 models), not {kv_cache_dtype}")
         if kv_sharing_target_layer_name is not None:
             raise NotImplementedError(f"{NAME} has no cross-layer KV sharing")
         if num_heads % num_kv_heads or num_heads // num_kv_heads > paged.Q_TILE:
@@ -299,8 +300,8 @@ def _build():
 
     class HKAttentionBackend(AttentionBackend):
         accept_output_buffer: bool = True
-        supported_dtypes: ClassVar[list] = [torch.bfloat16]
-        supported_kv_cache_dtypes: ClassVar[list] = ["auto", "bfloat16", "fp8", "fp8_e4m3"]
+        supported_dtypes: ClassVar[list] = [torch.bfloat16, torch.float16]
+        supported_kv_cache_dtypes: ClassVar[list] = ["auto", "bfloat16", "float16", "fp8", "fp8_e4m3"]
 
         @staticmethod
         def get_name() -> str:

@@ -109,11 +109,13 @@ def layout_why_not(k, v) -> str:
 
 
 def _dtype_why_not(q, out, k, k_descale, v_descale) -> str:
-    if q.dtype != torch.bfloat16 or out.dtype != q.dtype:
-        return f"dtype {q.dtype} (bfloat16 queries only)"
-    if k.dtype == torch.bfloat16:
+    if q.dtype not in paged.ACT_DTYPES or out.dtype != q.dtype:
+        return f"dtype {q.dtype} (bfloat16 or float16 queries only)"
+    if k.dtype == q.dtype:
         return ""
     if k.dtype in paged._FP8_DTYPES:
+        if q.dtype != torch.bfloat16:
+            return f"fp8 cache with {q.dtype} queries (bfloat16 only)"
         for s in (k_descale, v_descale):
             if not isinstance(s, torch.Tensor) or s.numel() != 1 or s.dtype != torch.float32:
                 return "fp8 cache without per-tensor float32 k/v descale"
@@ -179,7 +181,7 @@ def _decode(q, out, k, v, block_table, seq_lens, q_start, scale, k_descale, v_de
     scratch = _scratch(q.device, reqs * splits, hq, d) if splits > 1 else None
     if splits > 1 and scratch is None:
         return False
-    fp8 = k.dtype != torch.bfloat16
+    fp8 = k.dtype not in paged.ACT_DTYPES
     paged.paged_attention_decode(out, q, k, v, block_table, seq_lens, d ** -0.5 if scale is None else float(scale),
                                  "fp8" if fp8 else "auto", k_descale if fp8 else None, v_descale if fp8 else None,
                                  num_splits=splits, scratch=scratch, query_start_loc=q_start)
@@ -215,7 +217,7 @@ def _prefill(a: dict) -> bool:
     work = paged.work_list([(r, starts[r + 1] - starts[r]) for r in range(reqs)],
                            paged.prefill_tile_rows(hq, int(k.shape[2])), q.device)
     sc = a.get("softmax_scale")
-    fp8 = k.dtype != torch.bfloat16
+    fp8 = k.dtype not in paged.ACT_DTYPES
     paged.paged_prefill(out, q, k, a["v"], a["block_table"], a["seqused_k"], a["cu_seqlens_q"], work,
                         d ** -0.5 if sc is None else float(sc), "fp8" if fp8 else "auto",
                         a.get("k_descale") if fp8 else None, a.get("v_descale") if fp8 else None)

@@ -1,6 +1,6 @@
 """End-to-end smoke of the attention backend inside a real vLLM engine, without weights.
 
-    python -m hk_dsl_b200.integration.vllm_smoke [--graphs] [--kv fp8] [--route]
+    python -m hk_dsl_b200.integration.vllm_smoke [--graphs] [--kv fp8] [--dtype float16] [--route [--shadow]]
 
 Builds a two-layer Llama-shaped model with random ("dummy") weights from a config written to
 a temporary directory, runs the same token prompts greedily through vLLM twice in one process
@@ -39,10 +39,10 @@ def tiny_config(path: str, heads: int = 8, kv_heads: int = 2) -> None:
         json.dump(cfg, f)
 
 
-def run(model_dir: str, backend, prompts, max_tokens: int, graphs: bool, kv: str):
+def run(model_dir: str, backend, prompts, max_tokens: int, graphs: bool, kv: str, dtype: str = "bfloat16"):
     from vllm import LLM, SamplingParams
 
-    kw = dict(model=model_dir, load_format="dummy", skip_tokenizer_init=True, dtype="bfloat16", max_model_len=4096,
+    kw = dict(model=model_dir, load_format="dummy", skip_tokenizer_init=True, dtype=dtype, max_model_len=4096,
               gpu_memory_utilization=0.25, enforce_eager=not graphs, seed=0, block_size=16, kv_cache_dtype=kv,
               enable_prefix_caching=False)
     if backend:
@@ -69,6 +69,7 @@ def main(argv=None) -> int:
     ap.add_argument("--graphs", action="store_true", help="let vLLM capture decode steps into CUDA graphs")
     ap.add_argument("--kv", default="auto", help="kv_cache_dtype: auto | fp8")
     ap.add_argument("--max-tokens", type=int, default=24)
+    ap.add_argument("--dtype", default="bfloat16", help="the model's dtype: bfloat16 | float16")
     ap.add_argument("--route", action="store_true",
                     help="test the in-place route instead: vLLM keeps its TRITON_ATTN backend and cache, and its "
                          "unified_attention calls are rebound to this build's stand-in (HK_VLLM_PREFILL=1)")
@@ -90,11 +91,11 @@ def main(argv=None) -> int:
     prompts = [torch.randint(3, 2000, (n,), generator=g).tolist() for n in (5, 37, 300, 1, 1025, 64)]
     with tempfile.TemporaryDirectory() as d:
         tiny_config(d)
-        base = run(d, "TRITON_ATTN" if args.route else None, prompts, args.max_tokens, args.graphs, args.kv)
+        base = run(d, "TRITON_ATTN" if args.route else None, prompts, args.max_tokens, args.graphs, args.kv, args.dtype)
         _vllm_plugin.register()
         patch = vllm_prefill.PATCH if args.route else vllm_backend.PATCH
         patch.reset()
-        ours = run(d, "TRITON_ATTN" if args.route else vllm_backend.SLOT, prompts, args.max_tokens, args.graphs, args.kv)
+        ours = run(d, "TRITON_ATTN" if args.route else vllm_backend.SLOT, prompts, args.max_tokens, args.graphs, args.kv, args.dtype)
     stats = dict(patch.stats), dict(patch.captured)
     worst, same = 0.0, 0
     for (tb, lb), (to, lo) in zip(base, ours):
@@ -107,7 +108,7 @@ def main(argv=None) -> int:
     total = sum(len(t) for t, _ in base)
     print(json.dumps({"prompts": len(prompts), "tokens_generated": total, "tokens_identical_prefix": same,
                       "worst_logprob_gap_on_shared_prefix": round(worst, 4), "eager_calls": stats[0],
-                      "captured_calls": stats[1], "graphs": args.graphs, "kv_cache_dtype": args.kv,
+                      "captured_calls": stats[1], "graphs": args.graphs, "kv_cache_dtype": args.kv, "dtype": args.dtype,
                       "surface": "in-place route (vLLM's TRITON_ATTN backend and cache)" if args.route else "backend",
                       "shadow": dict(vllm_prefill.SHADOW_STATS) if args.shadow else None}))
     ok = stats[0].get("decode", 0) + stats[1].get("decode", 0) > 0 and stats[0].get("prefill", 0) > 0 and worst < 0.1

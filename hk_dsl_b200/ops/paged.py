@@ -42,18 +42,25 @@ DECODE_HEAD_DIMS = (64, 128, 256)  # the decode walk and merge also take 256 (bf
 MAX_SPLITS = _lib.MAX_SPLITS
 
 _FP8_NAMES = ("fp8", "fp8_e4m3")
+ACT_DTYPES = (torch.bfloat16, torch.float16)   # activations: query, new K/V rows, output
 _FP8_DTYPES = tuple(d for d in (getattr(torch, "float8_e4m3fn", None), torch.uint8) if d is not None)
 
 
 def kv_dtype_code(kv_cache_dtype: str, cache: torch.Tensor, q_dtype=torch.bfloat16) -> int:
     """hkb's KV element code for vLLM's `kv_cache_dtype` string and the cache tensor given."""
     name = (kv_cache_dtype or "auto").lower()
-    if name.startswith("auto") or name in ("bfloat16", "bf16"):
-        if cache.dtype != torch.bfloat16:
-            raise TypeError(f"hk.ops.paged: kv_cache_dtype {kv_cache_dtype!r} keeps the cache in bfloat16, "
-                            f"the cache is {cache.dtype}")
-        return _lib.KV_BF16
+    if name.startswith("auto") or name in ("bfloat16", "bf16", "float16", "half", "fp16"):
+        # "auto" keeps the cache in the model's dtype: bf16, or fp16 for a model served in float16
+        # (then the query, the new rows and the output are fp16 too)
+        want = torch.float16 if name in ("float16", "half", "fp16") else \
+            torch.bfloat16 if name in ("bfloat16", "bf16") else q_dtype
+        if cache.dtype != want or want not in ACT_DTYPES:
+            raise TypeError(f"hk.ops.paged: kv_cache_dtype {kv_cache_dtype!r} keeps the cache in {want}, "
+                            f"the cache is {cache.dtype} (bfloat16 and float16 are implemented)")
+        return _lib.KV_F16 if want == torch.float16 else _lib.KV_BF16
     if name in _FP8_NAMES:
+        if q_dtype != torch.bfloat16:
+            raise TypeError(f"hk.ops.paged: an fp8 cache goes with bfloat16 activations, the query is {q_dtype}")
         if cache.dtype not in _FP8_DTYPES:
             raise TypeError(f"hk.ops.paged: kv_cache_dtype {kv_cache_dtype!r} needs a float8_e4m3fn (or uint8) "
                             f"cache, the cache is {cache.dtype}")
@@ -114,9 +121,9 @@ def reshape_and_cache(key: torch.Tensor, value: torch.Tensor, key_cache: torch.T
     `(tokens, kv_heads, head_dim)` bf16; the caches `(blocks, block_size, kv_heads, head_dim)`
     views of any strides, bf16 or fp8-e4m3; `slot_mapping` int64 or int32."""
     _need_cuda(key, value, key_cache, value_cache, slot_mapping)
-    if key.dim() != 3 or value.shape != key.shape or key.dtype != torch.bfloat16 or value.dtype != key.dtype:
+    if key.dim() != 3 or value.shape != key.shape or key.dtype not in ACT_DTYPES or value.dtype != key.dtype:
         raise ValueError(f"hk.ops.paged: key {tuple(key.shape)} {key.dtype} / value {tuple(value.shape)} "
-                         f"{value.dtype}; the cache write reads (tokens, kv_heads, head_dim) bfloat16")
+                         f"{value.dtype}; the cache write reads (tokens, kv_heads, head_dim) bfloat16 or float16")
     t, hkv, d = key.shape
     for name, c in (("key_cache", key_cache), ("value_cache", value_cache)):
         if c.dim() != 4 or c.shape[2] != hkv or c.shape[3] != d or c.stride(3) != 1:
@@ -129,7 +136,7 @@ def reshape_and_cache(key: torch.Tensor, value: torch.Tensor, key_cache: torch.T
         raise TypeError(f"hk.ops.paged: slot_mapping is {tuple(slot_mapping.shape)} {slot_mapping.dtype}; "
                         f"contiguous int64 or int32 (tokens,) needed")
     n = min(t, slot_mapping.shape[0])
-    code = kv_dtype_code(kv_cache_dtype, key_cache)
+    code = kv_dtype_code(kv_cache_dtype, key_cache, key.dtype)
     if value_cache.dtype != key_cache.dtype or value_cache.shape[1] != key_cache.shape[1]:
         raise ValueError("hk.ops.paged: key_cache and value_cache differ in dtype or block_size")
     fp8 = code == _lib.KV_FP8_E4M3
@@ -153,9 +160,9 @@ def split_scratch(num_seqs: int, num_q_heads: int, head_dim: int, num_splits: in
 def _decode_call(out, query, key_cache, value_cache, block_tables, seq_lens, query_start_loc):
     """Validate the tensors of a decode call; returns (seqs, q_heads, head_dim, block_size, kv_heads, q_start ptr)."""
     _need_cuda(out, query, key_cache, value_cache, block_tables, seq_lens)
-    if query.dim() != 3 or query.dtype != torch.bfloat16 or query.stride(2) != 1:
+    if query.dim() != 3 or query.dtype not in ACT_DTYPES or query.stride(2) != 1:
         raise ValueError(f"hk.ops.paged: query is {tuple(query.shape)} {query.dtype}; the decode reads "
-                         f"(tokens, q_heads, head_dim) bfloat16 with head_dim contiguous")
+                         f"(tokens, q_heads, head_dim) bfloat16 or float16 with head_dim contiguous")
     if out.shape != query.shape or out.dtype != query.dtype or out.stride(2) != 1:
         raise ValueError(f"hk.ops.paged: out is {tuple(out.shape)} {out.dtype}; it must match query "
                          f"{tuple(query.shape)} {query.dtype}")
@@ -217,7 +224,7 @@ def paged_attention_decode(out: torch.Tensor, query: torch.Tensor, key_cache: to
     not given -- pass it to stay allocation-free) and the merge kernel folds them
     (`merge=False` stops after the walk and leaves the partials in `scratch`)."""
     n, hq, d, bs, hkv, qsl = _decode_call(out, query, key_cache, value_cache, block_tables, seq_lens, query_start_loc)
-    code = kv_dtype_code(kv_cache_dtype, key_cache)
+    code = kv_dtype_code(kv_cache_dtype, key_cache, query.dtype)
     fp8 = code == _lib.KV_FP8_E4M3
     if num_splits is None:
         tiles = block_tables.shape[1] * (bs // 16) if max_seq_len is None else -(-max_seq_len // 16)
@@ -233,7 +240,7 @@ def paged_attention_decode(out: torch.Tensor, query: torch.Tensor, key_cache: to
         po.data_ptr() if po is not None else None, pl.data_ptr() if pl is not None else None, st)
     _lib.check("hkb_paged_decode", rc)
     if num_splits > 1 and merge:
-        rc = lib.hkb_merge(out.data_ptr(), out.stride(0), out.stride(1), 0, None,
+        rc = lib.hkb_merge(out.data_ptr(), out.stride(0), out.stride(1), 2 if out.dtype == torch.float16 else 0, None,
                            po.data_ptr(), hq * d, num_splits * hq * d, pl.data_ptr(), hq, num_splits * hq,
                            num_splits, n, hq, d, seq_lens.data_ptr(), qsl, st)
         _lib.check("hkb_merge", rc)
@@ -274,10 +281,10 @@ def decode_step(out: torch.Tensor, query: torch.Tensor, key: Optional[torch.Tens
     slot64 = 0
     if key is not None:
         _need_cuda(key, value, slot_mapping)
-        if key.dim() != 3 or value.shape != key.shape or key.dtype != torch.bfloat16 or value.dtype != key.dtype \
+        if key.dim() != 3 or value.shape != key.shape or key.dtype != query.dtype or value.dtype != key.dtype \
                 or key.shape[1] != hkv or key.shape[2] != d or key.stride(2) != 1 or value.stride(2) != 1:
             raise ValueError(f"hk.ops.paged: key {tuple(key.shape)} {key.dtype} / value {tuple(value.shape)} "
-                             f"{value.dtype}; the step writes (seqs, {hkv}, {d}) bfloat16 rows")
+                             f"{value.dtype}; the step writes (seqs, {hkv}, {d}) rows of the query's dtype ({query.dtype})")
         if slot_mapping.dim() != 1 or slot_mapping.dtype not in (torch.int64, torch.int32) \
                 or not slot_mapping.is_contiguous():
             raise TypeError(f"hk.ops.paged: slot_mapping is {tuple(slot_mapping.shape)} {slot_mapping.dtype}; "
@@ -288,7 +295,7 @@ def decode_step(out: torch.Tensor, query: torch.Tensor, key: Optional[torch.Tens
         kp, vp, sp = key.data_ptr(), value.data_ptr(), slot_mapping.data_ptr()
         kst = (key.stride(0), key.stride(1), value.stride(0), value.stride(1))
         slot64 = 1 if slot_mapping.dtype == torch.int64 else 0
-    code = kv_dtype_code(kv_cache_dtype, key_cache)
+    code = kv_dtype_code(kv_cache_dtype, key_cache, query.dtype)
     fp8 = code == _lib.KV_FP8_E4M3
     if num_splits is None:
         tiles = block_tables.shape[1] * (bs // 16) if max_seq_len is None else -(-max_seq_len // 16)
@@ -350,9 +357,9 @@ def paged_prefill(out: torch.Tensor, query: torch.Tensor, key_cache: torch.Tenso
     request (int32), `query_start_loc` cu_seqlens_q (int32, requests + 1); `work` from `work_list`.
     Requests that are not in `work` keep their output rows untouched."""
     _need_cuda(out, query, key_cache, value_cache, block_tables, seq_lens, query_start_loc, work)
-    if query.dim() != 3 or query.dtype != torch.bfloat16 or query.stride(2) != 1 or out.shape != query.shape \
+    if query.dim() != 3 or query.dtype not in ACT_DTYPES or query.stride(2) != 1 or out.shape != query.shape \
             or out.dtype != query.dtype or out.stride(2) != 1:
-        raise ValueError(f"hk.ops.paged: prefill reads/writes (tokens, q_heads, head_dim) bfloat16; query "
+        raise ValueError(f"hk.ops.paged: prefill reads/writes (tokens, q_heads, head_dim) bfloat16 or float16; query "
                          f"{tuple(query.shape)} {query.dtype}, out {tuple(out.shape)} {out.dtype}")
     _, hq, d = query.shape
     if key_cache.dim() != 4 or value_cache.shape != key_cache.shape or key_cache.shape[3] != d \
@@ -365,7 +372,7 @@ def paged_prefill(out: torch.Tensor, query: torch.Tensor, key_cache: torch.Tenso
             raise TypeError(f"hk.ops.paged: {name} is {t.dtype} {tuple(t.shape)}; contiguous int32 needed")
     if work.dim() != 2 or work.shape[1] != 2 or not work.is_contiguous():
         raise ValueError("hk.ops.paged: work must be (items, 2) int32 (work_list)")
-    code = kv_dtype_code(kv_cache_dtype, key_cache)
+    code = kv_dtype_code(kv_cache_dtype, key_cache, query.dtype)
     fp8 = code == _lib.KV_FP8_E4M3
     _, bs, hkv, _ = key_cache.shape
     rc = _lib.load().hkb_paged_prefill(
@@ -389,13 +396,13 @@ def merge_partials(out: torch.Tensor, part_out: torch.Tensor, part_lse: torch.Te
     if part_out.dtype != torch.float32 or part_lse.dtype != torch.float32 or tuple(part_lse.shape) != (p, n, hq) \
             or not part_out.is_contiguous() or not part_lse.is_contiguous():
         raise ValueError("hk.ops.paged: merge reads contiguous fp32 (parts, seqs, heads, head_dim) and (parts, seqs, heads)")
-    f32 = out.dtype == torch.float32
-    if tuple(out.shape) != (n, hq, d) or out.dtype not in (torch.bfloat16, torch.float32) or out.stride(2) != 1:
-        raise ValueError(f"hk.ops.paged: merge writes (seqs, heads, head_dim) bf16 or fp32, out is {tuple(out.shape)} {out.dtype}")
+    kind = {torch.bfloat16: 0, torch.float32: 1, torch.float16: 2}.get(out.dtype)
+    if tuple(out.shape) != (n, hq, d) or kind is None or out.stride(2) != 1:
+        raise ValueError(f"hk.ops.paged: merge writes (seqs, heads, head_dim) bf16, fp16 or fp32, out is {tuple(out.shape)} {out.dtype}")
     if out_lse is not None and (out_lse.dtype != torch.float32 or tuple(out_lse.shape) != (n, hq)
                                 or not out_lse.is_contiguous()):
         raise ValueError("hk.ops.paged: out_lse must be contiguous fp32 (seqs, heads)")
-    rc = _lib.load().hkb_merge(out.data_ptr(), out.stride(0), out.stride(1), 1 if f32 else 0,
+    rc = _lib.load().hkb_merge(out.data_ptr(), out.stride(0), out.stride(1), kind,
                                out_lse.data_ptr() if out_lse is not None else None,
                                part_out.data_ptr(), n * hq * d, hq * d, part_lse.data_ptr(), n * hq, hq,
                                p, n, hq, d, seq_lens.data_ptr() if seq_lens is not None else None, None,
@@ -434,15 +441,15 @@ def check_decode(q, k_cache, v_cache, block_table, seq_lens, out, *, rows: str =
         no("q", q, f"(requests, kv_heads, {Q_TILE}, head_dim): a whole {Q_TILE}-row tile")
     if not 1 <= n_rows <= Q_TILE:
         no("q", q, f"1 to {Q_TILE} query rows (the GQA group) a kv head")
-    if q.dtype != torch.bfloat16:
-        no("q", q, "bfloat16")
+    if q.dtype not in ACT_DTYPES:
+        no("q", q, "bfloat16 or float16")
     if out.shape != q.shape or out.dtype != q.dtype:
         no("out", out, f"q's shape and dtype, {tuple(q.shape)} {q.dtype}")
-    kinds = (torch.bfloat16,) + _FP8_DTYPES
+    kinds = (q.dtype,) + (_FP8_DTYPES if q.dtype == torch.bfloat16 else ())
     for name, t in (("k_cache", k_cache), ("v_cache", v_cache)):
         if (t.dim() != 4 or t.shape[1] != heads or t.shape[3] != d or t.shape[2] % 16 or t.shape[2] == 0
                 or t.dtype not in kinds):
-            no(name, t, f"(blocks, {heads}, page, {d}) bfloat16 or float8_e4m3fn: q's kv heads, a page of a "
+            no(name, t, f"(blocks, {heads}, page, {d}) of q's dtype (or float8_e4m3fn with a bfloat16 q): q's kv heads, a page of a "
                f"multiple of 16 tokens, q's head_dim")
     if v_cache.shape != k_cache.shape or v_cache.dtype != k_cache.dtype:
         no("v_cache", v_cache, f"k_cache's shape and dtype, {tuple(k_cache.shape)} {k_cache.dtype}")
@@ -543,7 +550,7 @@ def decode(q, k_cache, v_cache, block_table, seq_lens, out, scratch, splits: int
             _PASSED.add(key)
     reqs, hkv, g, d = q.shape
     hq = hkv * g
-    fp8 = k_cache.dtype != torch.bfloat16
+    fp8 = k_cache.dtype not in ACT_DTYPES
     q3 = q.as_strided((reqs, hq, d), (q.stride(0), q.stride(2), 1))
     o3 = out.as_strided((reqs, hq, d), (out.stride(0), out.stride(2), 1))
     sc = None
@@ -566,7 +573,8 @@ def merge_splits(o_part: torch.Tensor, lse_part: torch.Tensor, splits: int, out:
     po = o_part.view(reqs, splits, hq, d)
     pl = lse_part.view(reqs, splits, hq)
     o3 = out.view(reqs, hq, d)
-    rc = _lib.load().hkb_merge(o3.data_ptr(), o3.stride(0), o3.stride(1), 1 if out.dtype == torch.float32 else 0,
+    rc = _lib.load().hkb_merge(o3.data_ptr(), o3.stride(0), o3.stride(1),
+                               {torch.float32: 1, torch.float16: 2}.get(out.dtype, 0),
                                None, po.data_ptr(), hq * d, splits * hq * d, pl.data_ptr(), hq, splits * hq,
                                splits, reqs, hq, d, None, None, _stream(out))
     _lib.check("hkb_merge", rc)

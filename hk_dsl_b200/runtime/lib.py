@@ -18,6 +18,7 @@ LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / "libhkb.so"
 
 KV_BF16 = 0
 KV_FP8_E4M3 = 1
+KV_F16 = 2          # float16 throughout: cache, new rows, query and output
 MAX_SPLITS = 256
 MAX_GROUP = 16
 STATIC_SCRATCH_BYTES = 8 << 20

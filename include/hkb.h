@@ -38,6 +38,9 @@ extern "C" {
 /* KV element types (kv_dtype). Queries and outputs are always bf16. */
 #define HKB_KV_BF16 0
 #define HKB_KV_FP8_E4M3 1
+/* float16 throughout: the cache, the new K/V rows, the query and the output are all fp16 (a model
+ * served in float16; the reference's `_f16` kernel variants, python/hk/ops/paged.py:706-729). */
+#define HKB_KV_F16 2
 
 typedef enum {
   HKB_OK = 0,
@@ -142,8 +145,8 @@ int hkb_paged_decode(void* out, int64_t out_stride_tok, int64_t out_stride_head,
  * never read (its memory may hold anything); if every part is -inf the answer is
  * zero. Also folds the partials of several GPUs after an all-gather: a part is
  * then one rank's (out, lse). If out_lse is not NULL the merged natural-log lse
- * is written to out_lse[i, h] and out is written as fp32 (out_is_f32 != 0) so a
- * rank's local merge can feed a second, cross-GPU merge.
+ * is written to out_lse[i, h]. out_is_f32 says what `out` holds: 0 bf16, 1 fp32 (so a
+ * rank's local merge can feed a second, cross-GPU merge), 2 fp16.
  *
  * part_out element (p, i, h, d) is at p*part_stride_p + i*part_stride_seq +
  * h*head_dim + d; part_lse (p, i, h) at p*lse_stride_p + i*lse_stride_seq + h.
