@@ -49,7 +49,8 @@ struct PrefillArgs {
 template <int D, int GP, bool FP8, bool F16 = false>
 struct Prefill {
   static_assert(!(FP8 && F16), "an fp8 cache goes with bf16 activations");
-  static constexpr int WARPS = 4;
+  // head_dim 256: a unit's 16 x 256 accumulator is 128 registers, so a warp owns one unit and a CTA has 8 warps
+  static constexpr int WARPS = D == 256 ? 8 : 4;
   static constexpr int UNITS = 8;                     // (16-row query tile, query head) pairs a CTA: two a warp
   static constexpr int UPW = UNITS / WARPS;
   static constexpr int TOK_TILES = UNITS / GP;        // 16-token query tiles a CTA
@@ -73,7 +74,7 @@ struct Prefill {
   // zero-filled instead of read, so nothing past the keys this CTA may attend to enters shared memory.
   __device__ static __forceinline__ void fill(const PrefillArgs& a, const Loader& ld, uint32_t stage, int kv0,
                                               int kv_limit, const int* table_row, int warp, int lane) {
-    const int t = warp;
+    const int t = WARPS == 4 ? warp : warp >> 1;     // 4 warps: K and V of tile `warp`; 8 warps: one of the two
     const int tok0 = kv0 + 16 * t;
     const int valid = min(16, kv_limit - tok0);      // rows of this tile that hold attendable keys
     int id = 0, sub = 0;
@@ -85,6 +86,7 @@ struct Prefill {
     }
 #pragma unroll
     for (int which = 0; which < 2; ++which) {
+      if (WARPS == 8 && which != (warp & 1)) continue;
       const uint32_t dst = stage + (t * 2 + which) * (FP8 ? RAW_TILE_BYTES : TILE_BYTES);
       const int64_t sb = which ? ld.vsb : ld.ksb, st = which ? ld.vst : ld.kst;
       const uint8_t* p = (which ? ld.vbase : ld.kbase) + (int64_t)id * sb + (int64_t)(sub * TILE_TOKENS) * st;
@@ -331,7 +333,7 @@ struct Prefill {
 };
 
 template <int D, int GP, bool FP8, bool F16>
-__global__ void __launch_bounds__(128, 2) prefill_kernel(const PrefillArgs a) {
+__global__ void __launch_bounds__(D == 256 ? 256 : 128, D == 256 ? 1 : 2) prefill_kernel(const PrefillArgs a) {
   extern __shared__ __align__(128) uint8_t hkb_smem[];
   Prefill<D, GP, FP8, F16>::run(a, hkb_smem);
 }
@@ -386,7 +388,7 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
   if (num_work < 0 || num_q_heads <= 0 || num_kv_heads <= 0) return HKB_ERR_SIZE;
   if (num_work == 0) return HKB_OK;
   if (!out || !q || !kc.ptr || !vc.ptr || !block_table || !seq_lens || !q_start || !work) return HKB_ERR_NULL;
-  if (head_dim != 64 && head_dim != 128) return HKB_ERR_HEAD_DIM;
+  if (head_dim != 64 && head_dim != 128 && head_dim != 256) return HKB_ERR_HEAD_DIM;
   if (block_size <= 0 || block_size % TILE_TOKENS) return HKB_ERR_BLOCK_SIZE;
   if (num_q_heads % num_kv_heads || num_q_heads / num_kv_heads > HKB_MAX_GROUP) return HKB_ERR_GROUP;
   if (kv_dtype != HKB_KV_BF16 && kv_dtype != HKB_KV_FP8_E4M3 && kv_dtype != HKB_KV_F16) return HKB_ERR_DTYPE;
@@ -419,7 +421,10 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
   a.v_scale = fp8 ? v_scale : nullptr;
   cudaStream_t st = (cudaStream_t)stream;
   if (fp8) return dispatch_prefill<128, true>(a, num_work, st);
-  if (kv_dtype == HKB_KV_F16)
+  if (kv_dtype == HKB_KV_F16) {
+    if (head_dim == 256) return dispatch_prefill<256, false, true>(a, num_work, st);
     return head_dim == 128 ? dispatch_prefill<128, false, true>(a, num_work, st) : dispatch_prefill<64, false, true>(a, num_work, st);
+  }
+  if (head_dim == 256) return dispatch_prefill<256, false>(a, num_work, st);
   return head_dim == 128 ? dispatch_prefill<128, false>(a, num_work, st) : dispatch_prefill<64, false>(a, num_work, st);
 }

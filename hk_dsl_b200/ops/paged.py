@@ -37,8 +37,8 @@ from ..runtime import lib as _lib
 KV_BLOCK = 16
 #: Most query rows (the GQA group) a kv head may have.
 Q_TILE = 16
-HEAD_DIMS = (64, 128)            # head sizes every kernel takes (decode, prefill): what the engine surfaces offer
-DECODE_HEAD_DIMS = (64, 128, 256)  # the decode walk and merge also take 256 (bf16 caches)
+HEAD_DIMS = (64, 128, 256)       # head sizes the kernels take (fp8 caches: 128 only)
+DECODE_HEAD_DIMS = HEAD_DIMS
 MAX_SPLITS = _lib.MAX_SPLITS
 
 _FP8_NAMES = ("fp8", "fp8_e4m3")

@@ -45,7 +45,7 @@ extern "C" {
 typedef enum {
   HKB_OK = 0,
   HKB_ERR_NULL = -1,        /* a required pointer is NULL */
-  HKB_ERR_HEAD_DIM = -2,    /* head_dim not one of 64, 128 (decode and merge: also 256, bf16 caches) */
+  HKB_ERR_HEAD_DIM = -2,    /* head_dim not one of 64, 128, 256 */
   HKB_ERR_BLOCK_SIZE = -3,  /* block_size not a positive multiple of 16 */
   HKB_ERR_GROUP = -4,       /* q heads not a multiple of kv heads, or group > 16 */
   HKB_ERR_DTYPE = -5,       /* kv_dtype not HKB_KV_* */

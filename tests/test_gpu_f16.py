@@ -110,3 +110,35 @@ def test_float16_refusals():
     with pytest.raises(ValueError, match="match query"):
         paged.paged_attention_decode(out.to(torch.bfloat16), c["q"], c["k"].transpose(1, 2), c["v"].transpose(1, 2),
                                      c["table"], c["lens"], 0.1)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("group,h_kv", [(2, 2), (8, 1), (1, 2)])
+def test_prefill_at_head_dim_256(dtype, group, h_kv):
+    """512-byte rows in the prefill kernel: one (query tile, head) unit a warp, eight warps a CTA."""
+    paged = _paged()
+    d, page = 256, 16
+    reqs = [(0, 70), (100, 33), (513, 1), (0, 257)]
+    gen = torch.Generator().manual_seed(group)
+    seq = [c + n for c, n in reqs]
+    pages = [-(-s // page) for s in seq]
+    nb = sum(pages) + 3
+    k = torch.randn(nb, h_kv, page, d, generator=gen).to(dtype)
+    v = torch.randn(nb, h_kv, page, d, generator=gen).to(dtype)
+    perm = torch.randperm(nb, generator=gen)
+    table = torch.zeros(len(reqs), max(pages), dtype=torch.int32)
+    at = 0
+    for i, p in enumerate(pages):
+        table[i, :p] = perm[at:at + p].to(torch.int32)
+        at += p
+    starts = [0]
+    for _, n in reqs:
+        starts.append(starts[-1] + n)
+    q = torch.randn(starts[-1], h_kv * group, d, generator=gen).to(dtype)
+    lens_t, qsl = torch.tensor(seq, dtype=torch.int32), torch.tensor(starts, dtype=torch.int32)
+    out = torch.empty_like(q, device="cuda")
+    work = paged.work_list([(r, n) for r, (_, n) in enumerate(reqs)], paged.prefill_tile_rows(h_kv * group, h_kv), "cuda")
+    paged.paged_prefill(out, q.cuda(), k.cuda().transpose(1, 2), v.cuda().transpose(1, 2), table.cuda(), lens_t.cuda(),
+                        qsl.cuda(), work, d ** -0.5)
+    want = orc.paged_prefill_ref(q, k.transpose(1, 2), v.transpose(1, 2), table, lens_t, qsl)
+    _check(out.float().cpu(), want)
