@@ -50,12 +50,13 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_kernel(const MergeArgs
   const float* lse = a.part_lse + (int64_t)seq * a.lse_stride_seq + h;
   const float* po = a.part_out + (int64_t)seq * a.part_stride_seq + (int64_t)h * a.head_dim + lane * VEC;
 
-  // pass 1: the maximum lse over the parts
+  // pass 1: the maximum lse over the parts. The lse values are requested whether or not the
+  // sequence is empty, so that they fly together with seq_lens instead of after it.
   float mx = -INFINITY;
-  if (!empty)
-    for (int p = lane; p < a.num_parts; p += 32) mx = fmaxf(mx, __ldg(lse + (int64_t)p * a.lse_stride_p));
+  for (int p = lane; p < a.num_parts; p += 32) mx = fmaxf(mx, __ldg(lse + (int64_t)p * a.lse_stride_p));
 #pragma unroll
   for (int x = 16; x > 0; x >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, x));
+  if (empty) mx = -INFINITY;
 
   float acc[VEC];
 #pragma unroll
@@ -138,8 +139,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_wide_kernel(const Merg
   const float* lse = a.part_lse + (int64_t)seq * a.lse_stride_seq + h;
   const float* po = a.part_out + (int64_t)seq * a.part_stride_seq + (int64_t)h * a.head_dim + lane * VEC;
   float mx = -INFINITY;
-  if (!empty)
-    for (int p = threadIdx.x; p < a.num_parts; p += MERGE_WARPS * 32) mx = fmaxf(mx, __ldg(lse + (int64_t)p * a.lse_stride_p));
+  for (int p = threadIdx.x; p < a.num_parts; p += MERGE_WARPS * 32) mx = fmaxf(mx, __ldg(lse + (int64_t)p * a.lse_stride_p));
 #pragma unroll
   for (int x = 16; x > 0; x >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, x));
   if (lane == 0) s_mx[warp] = mx;
@@ -147,6 +147,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_wide_kernel(const Merg
   mx = s_mx[0];
 #pragma unroll
   for (int w = 1; w < MERGE_WARPS; ++w) mx = fmaxf(mx, s_mx[w]);
+  if (empty) mx = -INFINITY;
 
   float acc[VEC];
 #pragma unroll
