@@ -144,3 +144,34 @@ def test_refusals_before_any_launch():
         paged.reshape_and_cache(key, value, kc, kc.clone(), slots, "fp8_e5m2")
     with pytest.raises(RuntimeError):
         paged.reshape_and_cache(key.cpu(), value.cpu(), kc.cpu(), kc.cpu(), slots.cpu())   # no CPU path
+
+
+@pytest.mark.parametrize("kv", ["auto", "fp8"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_against_vllms_own_cache_write_bit_for_bit(kv, dtype):
+    """The arithmetic of the cache write lives in vLLM, not in hk-dsl (its backend calls
+    `vllm._custom_ops.reshape_and_cache_flash`, python/hk/integration/vllm_backend.py:594-599): where a
+    vLLM is installed beside this build, the two ops must leave the same bytes -- 16-bit caches and,
+    which nothing in the reference pins, the fp8-e4m3 cache with per-tensor scales."""
+    pytest.importorskip("vllm")
+    try:
+        from vllm import _custom_ops as vops
+        vops.reshape_and_cache_flash  # noqa: B018
+        import vllm._C  # noqa: F401  (the compiled ops)
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"vLLM's compiled cache ops are not usable here: {type(e).__name__}")
+    if kv == "fp8" and dtype != torch.bfloat16:
+        pytest.skip("an fp8 cache goes with bfloat16 activations in this build")
+    paged = _paged()
+    key, value, slots = _inputs(n=513, nb=80, seed=11)
+    key, value = (key * 3).to(dtype), (value * 3).to(dtype)
+    nb, hkv, d = 80, 8, 128
+    cache_dtype = torch.uint8 if kv == "fp8" else dtype
+    ks, vs = torch.tensor([0.0173], device="cuda"), torch.tensor([0.0221], device="cuda")
+    ours = torch.zeros(2, nb, PAGE, hkv, d, device="cuda", dtype=cache_dtype)
+    theirs = torch.zeros_like(ours)
+    paged.reshape_and_cache(key, value, ours[0], ours[1], slots, kv, ks, vs)
+    vops.reshape_and_cache_flash(key, value, theirs[0], theirs[1], slots, kv, ks, vs)
+    torch.cuda.synchronize()
+    assert torch.equal(ours.view(torch.uint8), theirs.view(torch.uint8))
+    assert int((ours.view(torch.uint8) != 0).sum()) > 0
