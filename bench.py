@@ -4,18 +4,21 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--config c2] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-A step is one pass of the hot path over one batch: the cache write of every sequence's new
-token (`reshape_and_cache`), the decode walk and the LSE merge. The metric is the KV bytes
+A step is one pass of the hot path over one batch -- the cache write of every sequence's new
+token, the decode walk and the LSE merge -- through `paged.decode_step` (two launches: the walk
+writes the new rows itself). The metric is the KV bytes
 the decode must read (sum(seq_len) x kv_heads x head_dim x (K + V), tokens counted exactly)
 divided by time: KV GB/s, whole job over all ranks. One JSON line is printed by rank 0.
 
   value     device-timed: inputs resident in HBM, K steps replayed as one CUDA graph that
             rotates over enough distinct caches that a cycle reads >= 1 GiB (cold KV; the
             cache is far larger than L2 in any case), CUDA events, max over ranks.
-  roofline  the walk kernel alone, timed live with CUDA events around each launch.
+  roofline  the walk kernel alone: a graph of K walk launches between two CUDA events on the
+            launching stream, replayed for about a second.
   e2e       the same step through the public Python API with HOST (pinned) inputs:
             host->device copies of q, k, v, slot_mapping, block_table, seq_lens and the
-            device->host read of the output are inside the timed region, every step.
+            device->host read of the output are inside the timed region, every step (the step
+            replayed as a CUDA graph; the eager figure is reported beside it).
             The KV cache is the path's persistent state and stays on the device.
   cpu_baseline  the oracle's torch port of the path timed on this box's host cores on a
             bounded sample (rank 0, N=1), also used to check the GPU output of that sample.
@@ -545,6 +548,47 @@ REFERENCE_MI355X_US = {(1, 512): 9.2, (1, 1024): 9.1, (1, 4096): 13.5, (1, 8192)
                        (64, 4096): 167.3, (128, 1024): 84.0, (128, 8192): 659.2}
 
 
+def _flash_attn_decode_us(st, layers, reps):
+    """vLLM's FlashAttention paged decode on token-major copies of the same caches, same graph-replay timing."""
+    import torch
+    from vllm.vllm_flash_attn import flash_attn_varlen_func as fa
+
+    try:
+        kcs = [c.contiguous() for c in st.k_caches[:layers]]
+        vcs = [c.contiguous() for c in st.v_caches[:layers]]
+        n = st.query.shape[0]
+        cu = torch.arange(n + 1, dtype=torch.int32, device=st.query.device)
+        out = torch.empty_like(st.query)
+        ctx = int(max(st.lens))
+
+        def call(l):
+            fa(st.query, kcs[l], vcs[l], max_seqlen_q=1, cu_seqlens_q=cu, max_seqlen_k=ctx, seqused_k=st.seq_lens,
+               block_table=st.block_table, causal=True, softmax_scale=st.scale, out=out)
+
+        for l in range(layers):
+            call(l)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                for l in range(layers):
+                    call(l)
+        g.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(7):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3 / (reps * layers))
+        return statistics.median(times)
+    except Exception:  # noqa: BLE001 -- another vLLM, another signature: no column
+        torch.cuda.synchronize()
+        return None
+
+
 def latency_table():
     """The reference's kernel-level benchmark of this path (tools/hk-bench/paged_cdna.py decode):
     32 q / 8 kv heads, head_dim 128, bf16, uniform contexts; walk + merge timed as a CUDA graph
@@ -557,6 +601,11 @@ def latency_table():
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     rows = []
+    try:        # the FlashAttention paged decode vLLM ships, where a vLLM is installed: the same shapes on the same GPU
+        from vllm.vllm_flash_attn import flash_attn_varlen_func  # noqa: F401
+        fa_column = True
+    except Exception:  # noqa: BLE001
+        fa_column = False
     for (reqs, ctx), ref_us in REFERENCE_MI355X_US.items():
         spec = W.Spec(f"t{reqs}x{ctx}", reqs, 32, 8, dist="fixed", lo=ctx, hi=ctx)
         kv = spec.kv_bytes([ctx] * reqs)
@@ -589,9 +638,14 @@ def latency_table():
             torch.cuda.synchronize()
             times.append(a.elapsed_time(b) * 1e3 / (reps * layers))
         us = statistics.median(times)
-        rows.append({"requests": reqs, "context": ctx, "us_per_layer": round(us, 2), "kv_gbs": round(kv / us / 1e3, 1),
-                     "parts": splits, "caches_rotated": layers, "reference_hk_mi355x_us": ref_us,
-                     "reference_over_ours": round(ref_us / us, 2)})
+        row = {"requests": reqs, "context": ctx, "us_per_layer": round(us, 2), "kv_gbs": round(kv / us / 1e3, 1),
+               "parts": splits, "caches_rotated": layers, "reference_hk_mi355x_us": ref_us,
+               "reference_over_ours": round(ref_us / us, 2)}
+        fa_us = _flash_attn_decode_us(st, layers, reps) if fa_column else None
+        if fa_us is not None:      # a library kernel on the same GPU, timed the same way: a baseline, not a path of this build
+            row["vllm_flash_attn_us"] = round(fa_us, 2)
+            row["vllm_flash_attn_over_ours"] = round(fa_us / us, 2)
+        rows.append(row)
         del st, scratch, g
         torch.cuda.empty_cache()
     print(json.dumps({"table": "decode walk + merge, us a layer, 32q/8kv heads, D128, bf16, block 16, cold KV, "
