@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define HKB_VERSION 100 /* major*100 + minor */
+#define HKB_VERSION 110 /* major*100 + minor */
 
 /* KV element types (kv_dtype). Queries and outputs are always bf16. */
 #define HKB_KV_BF16 0
