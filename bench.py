@@ -672,7 +672,9 @@ def prefill_table():
         peak = 1590.0
     rows = []
     g = torch.Generator(device=dev).manual_seed(3)
-    for reqs in ([(0, 2048)], [(0, 8192)], [(0, 2048)] * 8, [(6144, 2048)] * 4, [(0, 512)] * 32):
+    cases = [(r, "bf16") for r in ([(0, 2048)], [(0, 8192)], [(0, 2048)] * 8, [(6144, 2048)] * 4, [(0, 512)] * 32)]
+    cases += [([(0, 2048)] * 8, "fp16"), ([(0, 2048)] * 8, "fp8")]      # the other cache dtypes, one shape each
+    for reqs, kind in cases:
         seq = [c + n for c, n in reqs]
         pages = [-(-s // bs) for s in seq]
         nb = sum(pages) + 3
@@ -688,11 +690,19 @@ def prefill_table():
         for _, n in reqs:
             starts.append(starts[-1] + n)
         q = torch.randn(starts[-1], hq, d, device=dev, generator=g).to(torch.bfloat16)
+        extra = ()
+        if kind == "fp16":
+            q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
+        elif kind == "fp8":
+            one = torch.full((1,), 6.0 / 448.0, device=dev)
+            k = (k.float() / one).clamp(-448, 448).to(torch.float8_e4m3fn)
+            v = (v.float() / one).clamp(-448, 448).to(torch.float8_e4m3fn)
+            extra = ("fp8", one, one)
         out = torch.empty_like(q)
         work = paged.work_list([(r, n) for r, (_, n) in enumerate(reqs)], paged.prefill_tile_rows(hq, hkv), dev,
                                seq_lens=seq)
         args = (out, q, k.transpose(1, 2), v.transpose(1, 2), table.to(dev), torch.tensor(seq, dtype=torch.int32, device=dev),
-                torch.tensor(starts, dtype=torch.int32, device=dev), work, d ** -0.5)
+                torch.tensor(starts, dtype=torch.int32, device=dev), work, d ** -0.5) + extra
         for _ in range(3):
             paged.paged_prefill(*args)
         torch.cuda.synchronize()
@@ -707,9 +717,9 @@ def prefill_table():
         ms = statistics.median(times)
         keys_seen = sum(n * c + n * (n + 1) // 2 for c, n in reqs)
         flops = 4.0 * hq * d * keys_seen
-        rows.append({"requests": len(reqs), "context": reqs[0][0], "q_len": reqs[0][1], "ms": round(ms, 3),
+        rows.append({"requests": len(reqs), "context": reqs[0][0], "q_len": reqs[0][1], "cache": kind, "ms": round(ms, 3),
                      "tflops": round(flops / ms / 1e9, 1), "frac_of_measured_bf16_peak": round(flops / ms / 1e9 / peak, 3)})
-    print(json.dumps({"table": "paged prefill, 32q/8kv heads, D128, bf16, block 16; mma.sync form", "peak_tflops": peak,
+    print(json.dumps({"table": "paged prefill, 32q/8kv heads, D128, block 16; mma.sync form", "peak_tflops": peak,
                       "rows": rows}), flush=True)
     return 0
 
