@@ -486,15 +486,15 @@ static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_hea
 
 }  // namespace hkb
 
-// Which worker walks a GQA group. The brief for this path puts tensor-core tiles at groups of 8
-// and more and CUDA cores below. Measured on B200 that bound is too high: a CUDA-core walk of a
+// Which worker walks a GQA group. The usual rule puts tensor-core tiles at groups of 8 and more
+// (a full 8-column mma tile) and CUDA cores below. Measured on B200 that bound is too high: a CUDA-core walk of a
 // group of 5 to 7 takes its heads in two passes and reads the KV twice (3.4 against 6.5 TB/s for
 // bf16), and at a group of 4 the bf16 CUDA-core walk -- 692 instructions a tile against ~300 --
 // draws enough power to run at 1.62 GHz under the 1 kW cap, where the mma walk with half its
 // columns empty holds 6.4 TB/s (5.7-5.8 for CUDA cores; equal in short bursts). For fp8 caches
 // the mma walk builds its fragments straight from the fp8 tile (WalkMMAF8) and reads 4.9-5.0 TB/s
 // at every group, against 4.9 / 4.0 / 3.1 TB/s for CUDA cores at groups of 1 / 2 / 4.
-// So: bf16 from 4, fp8 always. HKB_MMA_MIN_GROUP=8 restores the bound of the brief; 1..8 is taken.
+// So: bf16 from 4, fp8 always. HKB_MMA_MIN_GROUP=8 restores the bound of 8; 1..8 is taken.
 extern "C" int hkb_walk_uses_mma(int group, int kv_dtype) {
   static const int forced = [] {
     const char* v = std::getenv("HKB_MMA_MIN_GROUP");

@@ -24,7 +24,7 @@ function:
 * `merge_lse_ref`          -- the same fold in this build's single convention: normalised
   partials + natural-log lse.
 * `rel`, `ulps`, `check`   -- tests/hk/gpu/_attn_ref.py:80-107 (4 bf16 ulps a row, 2^-6 relative),
-  and `check_baseline` the max-abs 2e-2 / mean-abs 2e-3 bound of this build's brief.
+  and `check_baseline` the max-abs 2e-2 / mean-abs 2e-3 bound this build states for itself.
 
 Pinning: `tests/golden/make_golden.py` runs the reference's `_attn_ref.py` (loaded by path)
 and the reference's `merge_splits` (its source text executed stand-alone) in the build

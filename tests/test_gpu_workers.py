@@ -19,7 +19,7 @@ PICK = "lens_by_splits or gqa_shapes or fp8_cache or head_dim_64 or nan_past or 
 
 
 @pytest.mark.parametrize("env", [
-    {"HKB_MMA_MIN_GROUP": "8"},                               # CUDA cores below a group of 8, bf16 and fp8: the brief's bound
+    {"HKB_MMA_MIN_GROUP": "8"},                               # CUDA cores below a group of 8, bf16 and fp8
     {"HKB_MMA_MIN_GROUP": "1"},                               # tensor-core tiles at every group
     {"HKB_MMA_MIN_GROUP": "1", "HKB_FP8_WIDEN": "1"},          # fp8 tiles widened to bf16 in shared memory first
     {"HKB_F8_CTAS": "2"},                                     # the fp8 worker's two-CTA build
