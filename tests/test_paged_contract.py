@@ -73,3 +73,16 @@ def test_no_cpu_path():
         paged.reshape_and_cache(torch.zeros(2, 2, 128, dtype=torch.bfloat16), torch.zeros(2, 2, 128, dtype=torch.bfloat16),
                                 torch.zeros(4, 16, 2, 128, dtype=torch.bfloat16), torch.zeros(4, 16, 2, 128, dtype=torch.bfloat16),
                                 torch.zeros(2, dtype=torch.int64))
+
+
+def test_the_joined_step_and_the_prefill_have_no_cpu_path_either():
+    q = torch.zeros(2, 8, 128, dtype=torch.bfloat16)
+    kv = torch.zeros(2, 2, 128, dtype=torch.bfloat16)
+    cache = torch.zeros(4, 16, 2, 128, dtype=torch.bfloat16)
+    table = torch.zeros(2, 2, dtype=torch.int32)
+    lens = torch.ones(2, dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        paged.decode_step(torch.empty_like(q), q, kv, kv, cache, cache, torch.zeros(2, dtype=torch.int64), table, lens, 0.1)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        paged.paged_prefill(torch.empty_like(q), q, cache, cache, table, lens, torch.tensor([0, 1, 2], dtype=torch.int32),
+                            torch.zeros(2, 2, dtype=torch.int32), 0.1)
