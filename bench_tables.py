@@ -1,0 +1,217 @@
+#!/usr/bin/env python
+"""Measurement tables beside bench.py: sweeps a reader of the profiles can re-run. Nothing
+here is part of the bench line.
+
+    python bench_tables.py --latency     decode latency (walk + merge, us a layer) over the reference's
+                                         requests x context grid, next to hk-dsl's own published column
+    python bench_tables.py --prefill     paged prefill TFLOP/s over a few prompt shapes, against the
+                                         measured bf16 tensor peak
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+#: us a layer of hk-dsl's own decode on an MI355X (8 TB/s HBM3e), Qwen3-8B's attention shape, from
+#: docs/history/39-cdna-paged.md:163-177 of the reference: (requests, context) -> hk's column.
+REFERENCE_MI355X_US = {(1, 512): 9.2, (1, 1024): 9.1, (1, 4096): 13.5, (1, 8192): 16.1, (4, 1024): 9.9,
+                       (4, 8192): 28.2, (16, 1024): 17.3, (16, 8192): 88.7, (32, 1024): 25.4, (32, 8192): 171.4,
+                       (64, 4096): 167.3, (128, 1024): 84.0, (128, 8192): 659.2}
+
+
+def _flash_attn_decode_us(st, layers, reps):
+    """vLLM's FlashAttention paged decode on token-major copies of the same caches, same graph-replay timing."""
+    import torch
+    from vllm.vllm_flash_attn import flash_attn_varlen_func as fa
+
+    try:
+        kcs = [c.contiguous() for c in st.k_caches[:layers]]
+        vcs = [c.contiguous() for c in st.v_caches[:layers]]
+        n = st.query.shape[0]
+        cu = torch.arange(n + 1, dtype=torch.int32, device=st.query.device)
+        out = torch.empty_like(st.query)
+        ctx = int(max(st.lens))
+
+        def call(l):
+            fa(st.query, kcs[l], vcs[l], max_seqlen_q=1, cu_seqlens_q=cu, max_seqlen_k=ctx, seqused_k=st.seq_lens,
+               block_table=st.block_table, causal=True, softmax_scale=st.scale, out=out)
+
+        for l in range(layers):
+            call(l)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                for l in range(layers):
+                    call(l)
+        g.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(7):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3 / (reps * layers))
+        return statistics.median(times)
+    except Exception:  # noqa: BLE001 -- another vLLM, another signature: no column
+        torch.cuda.synchronize()
+        return None
+
+
+def latency_table():
+    """The reference's kernel-level benchmark of this path (tools/hk-bench/paged_cdna.py decode):
+    32 q / 8 kv heads, head_dim 128, bf16, uniform contexts; walk + merge timed as a CUDA graph
+    whose calls rotate through enough caches to read past L2 (>= 256 MB a cycle), median of 7."""
+    import torch
+
+    from hk_dsl_b200 import workloads as W
+    from hk_dsl_b200.ops import paged
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    rows = []
+    try:        # the FlashAttention paged decode vLLM ships, where a vLLM is installed: the same shapes on the same GPU
+        from vllm.vllm_flash_attn import flash_attn_varlen_func  # noqa: F401
+        fa_column = True
+    except Exception:  # noqa: BLE001
+        fa_column = False
+    for (reqs, ctx), ref_us in REFERENCE_MI355X_US.items():
+        spec = W.Spec(f"t{reqs}x{ctx}", reqs, 32, 8, dist="fixed", lo=ctx, hi=ctx)
+        kv = spec.kv_bytes([ctx] * reqs)
+        layers = max(2, min(128, -(-(256 << 20) // kv)))
+        st = W.build_step(spec, dev, layers=layers, seed=1)
+        splits = paged.plan_splits(reqs, 8, st.block_table.shape[1], device=dev)
+        scratch = paged.split_scratch(reqs, 32, 128, splits, dev)
+
+        def call(l):
+            paged.paged_attention_decode(st.out, st.query, st.k_caches[l], st.v_caches[l], st.block_table,
+                                         st.seq_lens, st.scale, num_splits=splits, scratch=scratch)
+
+        for l in range(layers):
+            call(l)
+        torch.cuda.synchronize()
+        reps = max(1, 64 // layers)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                for l in range(layers):
+                    call(l)
+        g.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(7):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3 / (reps * layers))
+        us = statistics.median(times)
+        row = {"requests": reqs, "context": ctx, "us_per_layer": round(us, 2), "kv_gbs": round(kv / us / 1e3, 1),
+               "parts": splits, "caches_rotated": layers, "reference_hk_mi355x_us": ref_us,
+               "reference_over_ours": round(ref_us / us, 2)}
+        fa_us = _flash_attn_decode_us(st, layers, reps) if fa_column else None
+        if fa_us is not None:      # a library kernel on the same GPU, timed the same way: a baseline, not a path of this build
+            row["vllm_flash_attn_us"] = round(fa_us, 2)
+            row["vllm_flash_attn_over_ours"] = round(fa_us / us, 2)
+        rows.append(row)
+        del st, scratch, g
+        torch.cuda.empty_cache()
+    print(json.dumps({"table": "decode walk + merge, us a layer, 32q/8kv heads, D128, bf16, block 16, cold KV, "
+                               "CUDA-graph replay, median of 7", "gpu": torch.cuda.get_device_name(dev), "rows": rows}),
+          flush=True)
+    return 0
+
+
+def prefill_table():
+    """Paged prefill on 32 q / 8 kv heads, head_dim 128, bf16: causal flops = 4 * q_heads * head_dim *
+    sum over query rows of the keys they see; timed with CUDA events, median of 7; against the
+    measured bf16 tensor peak (this kernel is the mma.sync form of the contraction)."""
+    import torch
+
+    from hk_dsl_b200.ops import paged
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    hq, hkv, d, bs = 32, 8, 128, 16
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak = float(json.load(f)["bf16_tflops"])
+    except Exception:  # noqa: BLE001
+        peak = 1590.0
+    rows = []
+    g = torch.Generator(device=dev).manual_seed(3)
+    cases = [(r, "bf16") for r in ([(0, 2048)], [(0, 8192)], [(0, 2048)] * 8, [(6144, 2048)] * 4, [(0, 512)] * 32)]
+    cases += [([(0, 2048)] * 8, "fp16"), ([(0, 2048)] * 8, "fp8")]      # the other cache dtypes, one shape each
+    for reqs, kind in cases:
+        seq = [c + n for c, n in reqs]
+        pages = [-(-s // bs) for s in seq]
+        nb = sum(pages) + 3
+        k = torch.randn(nb, hkv, bs, d, device=dev, generator=g).to(torch.bfloat16)
+        v = torch.randn(nb, hkv, bs, d, device=dev, generator=g).to(torch.bfloat16)
+        table = torch.zeros(len(reqs), max(pages), dtype=torch.int32)
+        perm = torch.randperm(nb)
+        at = 0
+        for i, p in enumerate(pages):
+            table[i, :p] = perm[at:at + p].to(torch.int32)
+            at += p
+        starts = [0]
+        for _, n in reqs:
+            starts.append(starts[-1] + n)
+        q = torch.randn(starts[-1], hq, d, device=dev, generator=g).to(torch.bfloat16)
+        extra = ()
+        if kind == "fp16":
+            q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
+        elif kind == "fp8":
+            one = torch.full((1,), 6.0 / 448.0, device=dev)
+            k = (k.float() / one).clamp(-448, 448).to(torch.float8_e4m3fn)
+            v = (v.float() / one).clamp(-448, 448).to(torch.float8_e4m3fn)
+            extra = ("fp8", one, one)
+        out = torch.empty_like(q)
+        work = paged.work_list([(r, n) for r, (_, n) in enumerate(reqs)], paged.prefill_tile_rows(hq, hkv), dev,
+                               seq_lens=seq)
+        args = (out, q, k.transpose(1, 2), v.transpose(1, 2), table.to(dev), torch.tensor(seq, dtype=torch.int32, device=dev),
+                torch.tensor(starts, dtype=torch.int32, device=dev), work, d ** -0.5) + extra
+        for _ in range(3):
+            paged.paged_prefill(*args)
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(7):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            paged.paged_prefill(*args)
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+        ms = statistics.median(times)
+        keys_seen = sum(n * c + n * (n + 1) // 2 for c, n in reqs)
+        flops = 4.0 * hq * d * keys_seen
+        rows.append({"requests": len(reqs), "context": reqs[0][0], "q_len": reqs[0][1], "cache": kind, "ms": round(ms, 3),
+                     "tflops": round(flops / ms / 1e9, 1), "frac_of_measured_bf16_peak": round(flops / ms / 1e9 / peak, 3)})
+    print(json.dumps({"table": "paged prefill, 32q/8kv heads, D128, block 16; mma.sync form", "peak_tflops": peak,
+                      "rows": rows}), flush=True)
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--latency", action="store_true")
+    ap.add_argument("--prefill", action="store_true")
+    args = ap.parse_args()
+    if args.prefill:
+        return prefill_table()
+    return latency_table()
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -84,10 +84,10 @@ extern "C" const char* hkb_strerror(int code) {
   switch (code) {
     case HKB_OK: return "ok";
     case HKB_ERR_NULL: return "a required pointer is NULL";
-    case HKB_ERR_HEAD_DIM: return "head_dim is not one this build has a kernel for (64, 128)";
+    case HKB_ERR_HEAD_DIM: return "head_dim is not one this build has a kernel for (64, 128, 256)";
     case HKB_ERR_BLOCK_SIZE: return "block_size is not a positive multiple of 16";
     case HKB_ERR_GROUP: return "query heads are not a multiple of kv heads, or more than 16 a kv head";
-    case HKB_ERR_DTYPE: return "kv_dtype is neither bf16 (0) nor fp8-e4m3 (1)";
+    case HKB_ERR_DTYPE: return "kv_dtype is not bf16 (0), fp8-e4m3 (1) or fp16 throughout (2)";
     case HKB_ERR_STRIDE: return "a stride breaks the 16-byte alignment of a row";
     case HKB_ERR_ALIGN: return "a base pointer is not aligned as the kernels read it";
     case HKB_ERR_SPLITS: return "num_splits out of range, or split scratch missing";

@@ -243,12 +243,18 @@ static int launch_stream(int smem_bytes, int threads, dim3 grid, const DecodeArg
   return HKB_OK;
 }
 
+// An on/off switch of the environment, read at every call (a getenv is a fraction of a
+// microsecond), so a process can flip it between calls.
+static bool env_on(const char* name) {
+  const char* v = std::getenv(name);
+  return v && v[0] == '1';
+}
+
 // More than one part and a prefix table that fits shared memory: the persistent balanced
-// stream. One part, or HKB_FIXED_SPLITS=1 in the environment (for A/B measurements): the
-// fixed-split grid, one CTA a (sequence, kv head, split).
+// stream. One part, or HKB_FIXED_SPLITS=1 in the environment (the reference's grid, kept as
+// the comparison arm): the fixed-split grid, one CTA a (sequence, kv head, split).
 static bool use_stream(const DecodeArgs& a, int num_seqs) {
-  static const bool fixed = [] { const char* v = std::getenv("HKB_FIXED_SPLITS"); return v && v[0] == '1'; }();
-  return a.num_splits > 1 && num_seqs <= STREAM_MAX_SEQS && !fixed;
+  return a.num_splits > 1 && num_seqs <= STREAM_MAX_SEQS && !env_on("HKB_FIXED_SPLITS");
 }
 
 static dim3 stream_grid(int planes, int ctas_per_sm = 2) {
@@ -260,7 +266,7 @@ static dim3 stream_grid(int planes, int ctas_per_sm = 2) {
 }
 
 // CUDA-core walk. Fixed splits: GH query heads a CTA pass, ceil(group / GH) passes a kv head.
-// Stream: rings of two warps holding two heads each (one warp for groups of 1 and 2).
+// Stream: one warp a ring, holding up to four heads.
 template <int D, bool FP8>
 static int dispatch_cc(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
   constexpr int NST = FP8 ? 4 : 3;
@@ -276,26 +282,14 @@ static int dispatch_cc(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
       return launch_stream<walk_stream_kernel<P, RINGS>>(WalkStream<P, RINGS>::SMEM_BYTES, WalkStream<P, RINGS>::THREADS,
                                                          stream_grid(a.num_kv_heads * P::passes(a.group)), a, num_seqs, st);
     }
-    // Rings of two warps with two heads each measured slower than one warp with four heads
-    // (4.6 against 5.4 TB/s on the Llama-3-8B shape): twice the warps do not pay for unpacking
-    // every K/V element twice. HKB_CC_RING=pair selects them for A/B measurements.
-    static const bool pair = [] { const char* v = std::getenv("HKB_CC_RING"); return v && v[0] == 'p'; }();
-    if (pair) {
-      using P = StreamCC<D, FP8, 2, 2, NST>;
-      return launch_stream<walk_stream_kernel<P, RINGS>>(WalkStream<P, RINGS>::SMEM_BYTES, WalkStream<P, RINGS>::THREADS,
-                                                         stream_grid(a.num_kv_heads * P::passes(a.group)), a, num_seqs, st);
-    }
     if (a.group == 3) {
       using P = StreamCC<D, FP8, 3, 1, NST>;
       return launch_stream<walk_stream_kernel<P, RINGS>>(WalkStream<P, RINGS>::SMEM_BYTES, WalkStream<P, RINGS>::THREADS,
                                                          stream_grid(a.num_kv_heads * P::passes(a.group)), a, num_seqs, st);
     }
-    static const bool butterfly = [] { const char* v = std::getenv("HKB_CC_RING"); return v && v[0] == 'b'; }();
-    if (butterfly) {   // the butterfly-reduction form of the same worker, kept for A/B measurements
-      using P = StreamCC<D, FP8, 4, 1, NST>;
-      return launch_stream<walk_stream_kernel<P, RINGS>>(WalkStream<P, RINGS>::SMEM_BYTES, WalkStream<P, RINGS>::THREADS,
-                                                         stream_grid(a.num_kv_heads * P::passes(a.group)), a, num_seqs, st);
-    }
+    // a group of 4 or more: one warp a ring holding four heads (rings of two warps with two heads
+    // each measured slower, 4.6 against 5.4 TB/s on the Llama-3-8B shape: every K/V element is
+    // unpacked twice)
     using P = StreamCC4<D, FP8, NST>;
     return launch_stream<walk_stream_kernel<P, RINGS>>(WalkStream<P, RINGS>::SMEM_BYTES, WalkStream<P, RINGS>::THREADS,
                                                        stream_grid(a.num_kv_heads * P::passes(a.group)), a, num_seqs, st);
@@ -339,34 +333,28 @@ static int dispatch_mma(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
       using P2 = WalkMMA<D, FP8, 2, WARPS, NST, F16>;
       return launch_stream<walk_stream_kernel<P2, RINGS>>(WalkStream<P2, RINGS>::SMEM_BYTES, RINGS * 32, grid, a, num_seqs, st);
     } else {
-    grid = stream_grid(a.num_kv_heads);
-    if constexpr (FP8) {   // the fp8 stream builds its mma fragments straight from the fp8 tile
-      static const bool widen = [] { const char* v = std::getenv("HKB_FP8_WIDEN"); return v && v[0] == '1'; }();
-      if (!widen) {
-        // Three CTAs an SM (168 registers a thread, 12 warps) for a group of up to 8: the walk of an
-        // fp8 tile is a chain of dependent shared-memory loads, converts, mma and shuffles, and with
-        // half the bytes a tile it needs more warps in flight than the bf16 walk to keep HBM busy
-        // (6.2 against 4.9 TB/s at two CTAs; four CTAs at 128 registers spill and fall to 4.3).
-        // HKB_F8_CTAS=2 selects the two-CTA build for A/B measurements.
-        static const int f8 = [] { const char* v = std::getenv("HKB_F8_CTAS"); return v ? std::atoi(v) : 3; }();
+      grid = stream_grid(a.num_kv_heads);
+      if constexpr (FP8) {
+        // The fp8 stream builds its mma fragments straight from the fp8 tile (WalkMMAF8). Three CTAs an
+        // SM (168 registers a thread, 12 warps) for a group of up to 8: the walk of an fp8 tile is a
+        // chain of dependent shared-memory loads, converts, mma and shuffles, and with half the bytes
+        // a tile it needs more warps in flight than the bf16 walk to keep HBM busy (6.2 against 4.9
+        // TB/s at two CTAs; four CTAs at 128 registers spill and fall to 4.3; widening tiles to bf16
+        // in shared memory first reads 2.8).
         if (a.group <= 8) {
-          if (f8 != 2) {
-            using P = WalkMMAF8<D, 1, 4, 3>;
-            return launch_stream<walk_stream_kernel<P, WARPS>>(WalkStream<P, WARPS>::SMEM_BYTES, WARPS * 32,
-                                                               stream_grid(a.num_kv_heads, 3), a, num_seqs, st);
-          }
-          using P = WalkMMAF8<D, 1, NST, 2>;
-          return launch_stream<walk_stream_kernel<P, WARPS>>(WalkStream<P, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
+          using P = WalkMMAF8<D, 1, 4, 3>;
+          return launch_stream<walk_stream_kernel<P, WARPS>>(WalkStream<P, WARPS>::SMEM_BYTES, WARPS * 32,
+                                                             stream_grid(a.num_kv_heads, 3), a, num_seqs, st);
         }
         using P2 = WalkMMAF8<D, 2, NST, 2>;
         return launch_stream<walk_stream_kernel<P2, WARPS>>(WalkStream<P2, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
+      } else {
+        if (a.group <= 8)
+          return launch_stream<walk_stream_kernel<WalkMMA<D, FP8, 1, WARPS, NST, F16>, WARPS>>(
+              WalkStream<WalkMMA<D, FP8, 1, WARPS, NST, F16>, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
+        return launch_stream<walk_stream_kernel<WalkMMA<D, FP8, 2, WARPS, NST, F16>, WARPS>>(
+            WalkStream<WalkMMA<D, FP8, 2, WARPS, NST, F16>, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
       }
-    }
-    if (a.group <= 8)
-      return launch_stream<walk_stream_kernel<WalkMMA<D, FP8, 1, WARPS, NST, F16>, WARPS>>(
-          WalkStream<WalkMMA<D, FP8, 1, WARPS, NST, F16>, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
-    return launch_stream<walk_stream_kernel<WalkMMA<D, FP8, 2, WARPS, NST, F16>, WARPS>>(
-        WalkStream<WalkMMA<D, FP8, 2, WARPS, NST, F16>, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
     }
   }
   if (a.group <= 8)
@@ -392,24 +380,18 @@ struct StepExtra {
   bool folded = false;   // out: the walk folded the partials itself
 };
 
-// The stream kernel can take the whole step when its rings are single warps (every worker but
-// the paired-ring variant kept for A/B runs).
+// The stream kernel takes the whole step (every ring is a single warp). HKB_STEP_UNFUSED=1 keeps
+// the three separate launches, the arm the joined step is compared with.
 static bool step_fusable(int num_splits, int num_seqs) {
-  static const bool fixed = [] { const char* v = std::getenv("HKB_FIXED_SPLITS"); return v && v[0] == '1'; }();
-  static const bool pair = [] { const char* v = std::getenv("HKB_CC_RING"); return v && v[0] == 'p'; }();
-  static const bool off = [] { const char* v = std::getenv("HKB_STEP_UNFUSED"); return v && v[0] == '1'; }();
-  return num_splits > 1 && num_seqs <= STREAM_MAX_SEQS && !fixed && !pair && !off;
+  return num_splits > 1 && num_seqs <= STREAM_MAX_SEQS && !env_on("HKB_FIXED_SPLITS") && !env_on("HKB_STEP_UNFUSED");
 }
 
-static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_head,
-                       const void* q, int64_t q_stride_tok, int64_t q_stride_head,
-                       hkb_cache_t kc, hkb_cache_t vc,
-                       const int32_t* block_table, int64_t table_stride, int max_pages,
-                       const int32_t* seq_lens, const int32_t* q_start,
-                       int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
-                       int block_size, float scale, int kv_dtype,
-                       const float* k_scale, const float* v_scale,
-                       int num_splits, float* part_out, float* part_lse, void* stream, StepExtra* extra) {
+// Everything a decode call can be refused for, checked before anything is launched.
+static int decode_check(const void* out, const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                        const hkb_cache_t& kc, const hkb_cache_t& vc, const int32_t* block_table, int max_pages,
+                        const int32_t* seq_lens, int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                        int block_size, int kv_dtype, const float* k_scale, const float* v_scale,
+                        int num_splits, const float* part_out, const float* part_lse) {
   if (num_seqs < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || max_pages < 0) return HKB_ERR_SIZE;
   if (num_seqs == 0) return HKB_OK;
   if (num_seqs > 65535 * 16 || num_splits > 0x7fffffff) return HKB_ERR_SIZE;
@@ -417,10 +399,9 @@ static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_hea
   if (head_dim != 64 && head_dim != 128 && head_dim != 256) return HKB_ERR_HEAD_DIM;
   if (block_size <= 0 || block_size % TILE_TOKENS) return HKB_ERR_BLOCK_SIZE;
   if (num_q_heads % num_kv_heads) return HKB_ERR_GROUP;
-  const int group = num_q_heads / num_kv_heads;
-  if (group > HKB_MAX_GROUP) return HKB_ERR_GROUP;
+  if (num_q_heads / num_kv_heads > HKB_MAX_GROUP) return HKB_ERR_GROUP;
   if (kv_dtype != HKB_KV_BF16 && kv_dtype != HKB_KV_FP8_E4M3 && kv_dtype != HKB_KV_F16) return HKB_ERR_DTYPE;
-  const bool fp8 = kv_dtype == HKB_KV_FP8_E4M3, f16 = kv_dtype == HKB_KV_F16;
+  const bool fp8 = kv_dtype == HKB_KV_FP8_E4M3;
   if (fp8 && (!k_scale || !v_scale)) return HKB_ERR_SCALE;
   if (fp8 && head_dim != 128) return HKB_ERR_UNSUPPORTED;
   if (num_splits < 1 || num_splits > HKB_MAX_SPLITS) return HKB_ERR_SPLITS;
@@ -435,6 +416,39 @@ static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_hea
   if ((q_stride_tok | q_stride_head) % 8) return HKB_ERR_STRIDE;
   if (((uintptr_t)kc.ptr | (uintptr_t)vc.ptr | (uintptr_t)q) % 16) return HKB_ERR_ALIGN;
   if ((uintptr_t)out % 2 || (part_out && (uintptr_t)part_out % 16)) return HKB_ERR_ALIGN;
+  return HKB_OK;
+}
+
+// What hkb_merge refuses, for a caller that wants to know before it launches the walk.
+static int merge_check(const void* out, int64_t out_stride_tok, int64_t out_stride_head, int out_kind,
+                       const float* part_out, int64_t part_stride_p, int64_t part_stride_seq, const float* part_lse,
+                       int num_parts, int num_seqs, int num_q_heads, int head_dim) {
+  if (num_seqs < 0 || num_q_heads <= 0 || num_parts < 1) return HKB_ERR_SIZE;
+  if (num_seqs == 0) return HKB_OK;
+  if (!out || !part_out || !part_lse) return HKB_ERR_NULL;
+  if (head_dim != 64 && head_dim != 128 && head_dim != 256) return HKB_ERR_HEAD_DIM;
+  if (num_seqs > 65535) return HKB_ERR_SIZE;
+  if ((part_stride_p | part_stride_seq) % 4 || (out_stride_tok | out_stride_head) % 4) return HKB_ERR_STRIDE;
+  if ((uintptr_t)part_out % 16 || (uintptr_t)out % (out_kind == 1 ? 16 : 8)) return HKB_ERR_ALIGN;
+  return HKB_OK;
+}
+
+static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_head,
+                       const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                       hkb_cache_t kc, hkb_cache_t vc,
+                       const int32_t* block_table, int64_t table_stride, int max_pages,
+                       const int32_t* seq_lens, const int32_t* q_start,
+                       int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                       int block_size, float scale, int kv_dtype,
+                       const float* k_scale, const float* v_scale,
+                       int num_splits, float* part_out, float* part_lse, void* stream, StepExtra* extra) {
+  const int rc = decode_check(out, q, q_stride_tok, q_stride_head, kc, vc, block_table, max_pages, seq_lens, num_seqs,
+                              num_q_heads, num_kv_heads, head_dim, block_size, kv_dtype, k_scale, v_scale, num_splits,
+                              part_out, part_lse);
+  if (rc != HKB_OK || num_seqs == 0) return rc;
+  const int group = num_q_heads / num_kv_heads;
+  const bool fp8 = kv_dtype == HKB_KV_FP8_E4M3, f16 = kv_dtype == HKB_KV_F16;
+  const int es = fp8 ? 1 : 2;
 
   DecodeArgs a;
   a.out = (__nv_bfloat16*)out; a.out_stride_tok = out_stride_tok; a.out_stride_head = out_stride_head;
@@ -496,11 +510,9 @@ static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_hea
 // at every group, against 4.9 / 4.0 / 3.1 TB/s for CUDA cores at groups of 1 / 2 / 4.
 // So: bf16 from 4, fp8 always. HKB_MMA_MIN_GROUP=8 restores the bound of 8; 1..8 is taken.
 extern "C" int hkb_walk_uses_mma(int group, int kv_dtype) {
-  static const int forced = [] {
-    const char* v = std::getenv("HKB_MMA_MIN_GROUP");
-    const int x = v ? std::atoi(v) : 0;
-    return x >= 1 && x <= 8 ? x : 0;
-  }();
+  const char* v = std::getenv("HKB_MMA_MIN_GROUP");
+  const int x = v ? std::atoi(v) : 0;
+  const int forced = x >= 1 && x <= 8 ? x : 0;
   if (kv_dtype == HKB_KV_F16) return 1;
   const int bound = forced ? forced : (kv_dtype == HKB_KV_FP8_E4M3 ? 1 : 4);
   return group >= bound ? 1 : 0;
@@ -520,6 +532,77 @@ extern "C" int hkb_paged_decode(void* out, int64_t out_stride_tok, int64_t out_s
                           block_size, scale, kv_dtype, k_scale, v_scale, num_splits, part_out, part_lse, stream, nullptr);
 }
 
+namespace hkb {
+
+// One decode step: cache write, walk, merge. `out_kind` 0 / 2: the bf16 / fp16 answer in `out`;
+// 1: the step's normalised fp32 answer in `out` and its natural-log lse in `out_lse` -- one rank's
+// record of a KV axis cut across GPUs. Every refusal happens before the first launch.
+static int step_impl(void* out, int64_t out_stride_tok, int64_t out_stride_head, int out_kind, float* out_lse,
+                     const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                     const void* key, const void* value,
+                     int64_t key_stride_tok, int64_t key_stride_head,
+                     int64_t val_stride_tok, int64_t val_stride_head,
+                     const void* slot_mapping, int slot_is_i64,
+                     hkb_cache_t kc, hkb_cache_t vc,
+                     const int32_t* block_table, int64_t table_stride, int max_pages,
+                     const int32_t* seq_lens, const int32_t* q_start,
+                     int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                     int block_size, float scale, int kv_dtype,
+                     const float* k_scale, const float* v_scale,
+                     int num_splits, float* part_out, float* part_lse, int32_t* arrivals, void* stream) {
+  if (num_seqs < 0) return HKB_ERR_SIZE;
+  if (num_seqs == 0) return HKB_OK;
+  if ((key == nullptr) != (value == nullptr)) return HKB_ERR_NULL;
+  if (key && !slot_mapping) return HKB_ERR_NULL;
+  if (key) {
+    // the new rows are read as 16-byte chunks, whichever launch writes them
+    if ((key_stride_tok | key_stride_head | val_stride_tok | val_stride_head) % 8) return HKB_ERR_STRIDE;
+    if (((uintptr_t)key | (uintptr_t)value) % 16) return HKB_ERR_ALIGN;
+  }
+  // the walk's and the merge's refusals, before the cache write (or anything else) is launched
+  int rc = decode_check(out, q, q_stride_tok, q_stride_head, kc, vc, block_table, max_pages, seq_lens, num_seqs,
+                        num_q_heads, num_kv_heads, head_dim, block_size, kv_dtype, k_scale, v_scale, num_splits,
+                        part_out, part_lse);
+  if (rc != HKB_OK) return rc;
+  if (out_kind == 1 && (num_splits < 2 || !out_lse)) return HKB_ERR_SPLITS;   // a record is written by the merge
+  const bool fusable = step_fusable(num_splits, num_seqs);
+  const bool fold = arrivals && fusable && kv_dtype != HKB_KV_F16 && out_kind == 0;
+  if (num_splits > 1 && !fold) {
+    rc = merge_check(out, out_stride_tok, out_stride_head, out_kind, part_out, (int64_t)num_q_heads * head_dim,
+                     (int64_t)num_splits * num_q_heads * head_dim, part_lse, num_splits, num_seqs, num_q_heads, head_dim);
+    if (rc != HKB_OK) return rc;
+  }
+  // the fold on arrival and the walk's zero rows store two 16-bit elements at a time
+  if (fold && ((uintptr_t)out % 4 || (out_stride_tok | out_stride_head) % 2)) return HKB_ERR_STRIDE;
+  if (key && !fusable) {
+    const int64_t dmask = kc.stride_block | kc.stride_token | kc.stride_head | vc.stride_block | vc.stride_token | vc.stride_head;
+    if (dmask % 8) return HKB_ERR_STRIDE;   // the separate cache write's own bound
+  }
+
+  StepExtra x;
+  x.key = key; x.value = value;
+  x.key_stride_tok = key_stride_tok; x.key_stride_head = key_stride_head;
+  x.val_stride_tok = val_stride_tok; x.val_stride_head = val_stride_head;
+  x.slots = slot_mapping; x.slot_is_i64 = slot_is_i64; x.arrivals = fold ? arrivals : nullptr;
+  if (key && !fusable) {   // the separate cache write: one row a sequence
+    rc = hkb_reshape_and_cache(key, value, key_stride_tok, key_stride_head, val_stride_tok, val_stride_head, kc,
+                               vc, slot_mapping, slot_is_i64, num_seqs, num_kv_heads, head_dim, block_size,
+                               kv_dtype, k_scale, v_scale, stream);
+    if (rc != HKB_OK) return rc;
+  }
+  rc = decode_impl(out, out_stride_tok, out_stride_head, q, q_stride_tok, q_stride_head, kc, vc, block_table,
+                   table_stride, max_pages, seq_lens, q_start, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                   block_size, scale, kv_dtype, k_scale, v_scale, num_splits, part_out, part_lse, stream, &x);
+  if (rc != HKB_OK || x.folded || num_splits <= 1) return rc;
+  const int kind = out_kind == 1 ? 1 : (kv_dtype == HKB_KV_F16 ? 2 : 0);
+  return hkb_merge(out, out_stride_tok, out_stride_head, kind, out_kind == 1 ? out_lse : nullptr, part_out,
+                   (int64_t)num_q_heads * head_dim, (int64_t)num_splits * num_q_heads * head_dim, part_lse, num_q_heads,
+                   (int64_t)num_splits * num_q_heads, num_splits, num_seqs, num_q_heads, head_dim, seq_lens, q_start,
+                   stream);
+}
+
+}  // namespace hkb
+
 extern "C" int hkb_decode_step(void* out, int64_t out_stride_tok, int64_t out_stride_head,
                                const void* q, int64_t q_stride_tok, int64_t q_stride_head,
                                const void* key, const void* value,
@@ -533,35 +616,31 @@ extern "C" int hkb_decode_step(void* out, int64_t out_stride_tok, int64_t out_st
                                int block_size, float scale, int kv_dtype,
                                const float* k_scale, const float* v_scale,
                                int num_splits, float* part_out, float* part_lse, int32_t* arrivals, void* stream) {
-  using namespace hkb;
-  if (num_seqs < 0) return HKB_ERR_SIZE;
-  if (num_seqs == 0) return HKB_OK;
-  if ((key == nullptr) != (value == nullptr)) return HKB_ERR_NULL;
-  if (key && !slot_mapping) return HKB_ERR_NULL;
-  if (key) {
-    // the new rows are read as 16-byte chunks, whichever launch writes them
-    if ((key_stride_tok | key_stride_head | val_stride_tok | val_stride_head) % 8) return HKB_ERR_STRIDE;
-    if (((uintptr_t)key | (uintptr_t)value) % 16) return HKB_ERR_ALIGN;
-  }
-  StepExtra x;
-  x.key = key; x.value = value;
-  x.key_stride_tok = key_stride_tok; x.key_stride_head = key_stride_head;
-  x.val_stride_tok = val_stride_tok; x.val_stride_head = val_stride_head;
-  x.slots = slot_mapping; x.slot_is_i64 = slot_is_i64; x.arrivals = arrivals;
-  if (key && !step_fusable(num_splits, num_seqs)) {   // the separate cache write: one row a sequence
-    const int rc = hkb_reshape_and_cache(key, value, key_stride_tok, key_stride_head, val_stride_tok, val_stride_head, kc,
-                                         vc, slot_mapping, slot_is_i64, num_seqs, num_kv_heads, head_dim, block_size,
-                                         kv_dtype, k_scale, v_scale, stream);
-    if (rc != HKB_OK) return rc;
-  }
-  int rc = decode_impl(out, out_stride_tok, out_stride_head, q, q_stride_tok, q_stride_head, kc, vc, block_table,
-                       table_stride, max_pages, seq_lens, q_start, num_seqs, num_q_heads, num_kv_heads, head_dim,
-                       block_size, scale, kv_dtype, k_scale, v_scale, num_splits, part_out, part_lse, stream, &x);
-  if (rc != HKB_OK || x.folded || num_splits <= 1) return rc;
-  return hkb_merge(out, out_stride_tok, out_stride_head, kv_dtype == HKB_KV_F16 ? 2 : 0, nullptr, part_out, (int64_t)num_q_heads * head_dim,
-                   (int64_t)num_splits * num_q_heads * head_dim, part_lse, num_q_heads,
-                   (int64_t)num_splits * num_q_heads, num_splits, num_seqs, num_q_heads, head_dim, seq_lens, q_start,
-                   stream);
+  return hkb::step_impl(out, out_stride_tok, out_stride_head, 0, nullptr, q, q_stride_tok, q_stride_head, key, value,
+                        key_stride_tok, key_stride_head, val_stride_tok, val_stride_head, slot_mapping, slot_is_i64, kc,
+                        vc, block_table, table_stride, max_pages, seq_lens, q_start, num_seqs, num_q_heads, num_kv_heads,
+                        head_dim, block_size, scale, kv_dtype, k_scale, v_scale, num_splits, part_out, part_lse, arrivals,
+                        stream);
+}
+
+extern "C" int hkb_decode_step_record(float* rec_out, float* rec_lse,
+                                      const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                                      const void* key, const void* value,
+                                      int64_t key_stride_tok, int64_t key_stride_head,
+                                      int64_t val_stride_tok, int64_t val_stride_head,
+                                      const void* slot_mapping, int slot_is_i64,
+                                      hkb_cache_t kc, hkb_cache_t vc,
+                                      const int32_t* block_table, int64_t table_stride, int max_pages,
+                                      const int32_t* seq_lens, const int32_t* q_start,
+                                      int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                                      int block_size, float scale, int kv_dtype,
+                                      const float* k_scale, const float* v_scale,
+                                      int num_splits, float* part_out, float* part_lse, void* stream) {
+  return hkb::step_impl(rec_out, (int64_t)num_q_heads * head_dim, head_dim, 1, rec_lse, q, q_stride_tok, q_stride_head,
+                        key, value, key_stride_tok, key_stride_head, val_stride_tok, val_stride_head, slot_mapping,
+                        slot_is_i64, kc, vc, block_table, table_stride, max_pages, seq_lens, q_start, num_seqs,
+                        num_q_heads, num_kv_heads, head_dim, block_size, scale, kv_dtype, k_scale, v_scale, num_splits,
+                        part_out, part_lse, nullptr, stream);
 }
 
 extern "C" int hkb_merge(void* out, int64_t out_stride_tok, int64_t out_stride_head, int out_is_f32,
@@ -571,13 +650,9 @@ extern "C" int hkb_merge(void* out, int64_t out_stride_tok, int64_t out_stride_h
                          int num_parts, int num_seqs, int num_q_heads, int head_dim,
                          const int32_t* seq_lens, const int32_t* q_start, void* stream) {
   using namespace hkb;
-  if (num_seqs < 0 || num_q_heads <= 0 || num_parts < 1) return HKB_ERR_SIZE;
-  if (num_seqs == 0) return HKB_OK;
-  if (!out || !part_out || !part_lse) return HKB_ERR_NULL;
-  if (head_dim != 64 && head_dim != 128 && head_dim != 256) return HKB_ERR_HEAD_DIM;
-  if (num_seqs > 65535) return HKB_ERR_SIZE;
-  if ((part_stride_p | part_stride_seq) % 4 || (out_stride_tok | out_stride_head) % 4) return HKB_ERR_STRIDE;
-  if ((uintptr_t)part_out % 16 || (uintptr_t)out % (out_is_f32 == 1 ? 16 : 8)) return HKB_ERR_ALIGN;
+  const int rc = merge_check(out, out_stride_tok, out_stride_head, out_is_f32, part_out, part_stride_p, part_stride_seq,
+                             part_lse, num_parts, num_seqs, num_q_heads, head_dim);
+  if (rc != HKB_OK || num_seqs == 0) return rc;
   MergeArgs a;
   a.out = out; a.out_stride_tok = out_stride_tok; a.out_stride_head = out_stride_head;
   a.out_is_f32 = out_is_f32; a.out_lse = out_lse;

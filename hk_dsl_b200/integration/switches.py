@@ -71,8 +71,9 @@ ROUTES: Dict[str, Route] = {r.name: r for r in (
 )}
 
 
-def _get(env: Mapping[str, str], name: str) -> str:
-    return env.get(name, "").strip() if name else ""
+def _setting(env: Mapping[str, str], var: str) -> str:
+    """A variable's value with blanks trimmed; unset, empty and "no such variable" are all ""."""
+    return str(env.get(var, "")).strip() if var else ""
 
 
 def is_off(v: str) -> bool:
@@ -81,54 +82,81 @@ def is_off(v: str) -> bool:
 
 def disabled(env: Optional[Mapping[str, str]] = None) -> bool:
     """Whether HK_DISABLE turns everything off."""
-    v = _get(os.environ if env is None else env, DISABLE)
-    return bool(v) and not is_off(v)
+    setting = _setting(os.environ if env is None else env, DISABLE)
+    return setting != "" and not is_off(setting)
 
 
-_ARCH: List[Optional[str]] = []
+_ARCH_SEEN: Dict[str, Optional[str]] = {}
 
 
 def arch() -> Optional[str]:
     """`sm_<major><minor>` of the current GPU (`sm_100` on a B200), `HK_ARCH` if set, or None
-    without a GPU: a default never assumes one."""
-    forced = os.environ.get("HK_ARCH", "").strip()
-    if forced:
-        return forced
-    if not _ARCH:
-        found = None
+    without a GPU: a default never assumes one. The GPU is asked once a process."""
+    override = os.environ.get("HK_ARCH", "").strip()
+    if override:
+        return override
+    if "gpu" not in _ARCH_SEEN:
+        name = None
         try:
             import torch  # noqa: PLC0415
 
             if torch.cuda.is_available():
-                major, minor = torch.cuda.get_device_capability()
-                found = f"sm_{major}{minor}"
+                name = "sm_%d%d" % torch.cuda.get_device_capability()
         except Exception:  # noqa: BLE001 -- no torch, no driver: nothing is validated here
-            found = None
-        _ARCH.append(found)
-    return _ARCH[0]
+            name = None
+        _ARCH_SEEN["gpu"] = name
+    return _ARCH_SEEN["gpu"]
+
+
+# ---- the rules, in order of precedence. Each looks at one thing and either settles the
+# ---- question (a Decision) or passes (None); `decide` returns the first answer.
+
+def _rule_kill_switch(route: Route, env: Mapping[str, str], gpu) -> Optional[Decision]:
+    if disabled(env):
+        return Decision(False, f"{DISABLE}={_setting(env, DISABLE)}")
+    return None
+
+
+def _rule_engine_switch(route: Route, env: Mapping[str, str], gpu) -> Optional[Decision]:
+    var = ENGINES.get(route.engine, "")
+    setting = _setting(env, var)
+    if setting and is_off(setting):
+        return Decision(False, f"{var}={setting}")
+    return None
+
+
+def _rule_route_switch(route: Route, env: Mapping[str, str], gpu) -> Optional[Decision]:
+    setting = _setting(env, route.env)
+    if not setting:
+        return None
+    said = f"{route.env}={setting}"
+    if is_off(setting):
+        return Decision(False, said)
+    # on; a value that is not a plain on word rides along (a backend slot name, say)
+    return Decision(True, said, setting if setting.lower() not in ON else "")
+
+
+def _rule_default(route: Route, env: Mapping[str, str], gpu) -> Optional[Decision]:
+    if not route.default:
+        return Decision(False, "default off")
+    found = arch() if gpu == "detect" else gpu
+    if found in route.arches:
+        return Decision(True, f"default on ({found})")
+    return Decision(False, f"default off on {found or 'no GPU'} (validated on {', '.join(route.arches)})")
+
+
+RULES = (_rule_kill_switch, _rule_engine_switch, _rule_route_switch, _rule_default)
 
 
 def decide(name: str, env: Optional[Mapping[str, str]] = None, gpu: Optional[str] = "detect") -> Decision:
     """On or off for one route, and which rule decided."""
+    route = ROUTES[name]
     env = os.environ if env is None else env
-    r = ROUTES[name]
-    if disabled(env):
-        return Decision(False, f"{DISABLE}={_get(env, DISABLE)}")
-    master = ENGINES.get(r.engine, "")
-    mv = _get(env, master)
-    if mv and is_off(mv):
-        return Decision(False, f"{master}={mv}")
-    v = _get(env, r.env)
-    if v:
-        if is_off(v):
-            return Decision(False, f"{r.env}={v}")
-        return Decision(True, f"{r.env}={v}", "" if v.lower() in ON else v)
-    if not r.default:
-        return Decision(False, "default off")
-    here = arch() if gpu == "detect" else gpu
-    if here in r.arches:
-        return Decision(True, f"default on ({here})")
-    return Decision(False, f"default off on {here or 'no GPU'} (validated on {', '.join(r.arches)})")
+    for rule in RULES:
+        verdict = rule(route, env, gpu)
+        if verdict is not None:
+            return verdict
+    raise AssertionError("the default rule always decides")
 
 
 def enabled(name: str, env: Optional[Mapping[str, str]] = None) -> bool:
@@ -141,22 +169,22 @@ def value(name: str, env: Optional[Mapping[str, str]] = None) -> str:
 
 
 def routes(engine: str) -> List[Route]:
-    return [r for r in ROUTES.values() if r.engine == engine]
+    return [route for route in ROUTES.values() if route.engine == engine]
 
 
 def on(engine: str, env: Optional[Mapping[str, str]] = None) -> Dict[str, Decision]:
     """Every route of `engine` that is on: name -> its decision."""
-    found = {}
-    for r in routes(engine):
-        d = decide(r.name, env)
-        if d.on:
-            found[r.name] = d
-    return found
+    verdicts = {route.name: decide(route.name, env) for route in routes(engine)}
+    return {name: verdict for name, verdict in verdicts.items() if verdict.on}
 
 
 def table(env: Optional[Mapping[str, str]] = None) -> str:
     """Every route, on or off and why: what `--status` prints."""
-    rows = [(r.name, r.env, "on" if d.on else "off", d.why) for r in ROUTES.values()
-            for d in (decide(r.name, env),)]
-    w = [max(len(x[i]) for x in rows) for i in range(3)]
-    return "\n".join(f"{a:{w[0]}}  {b:{w[1]}}  {c:{w[2]}}  {e}" for a, b, c, e in rows)
+    verdicts = {name: decide(name, env) for name in ROUTES}
+    name_w = max(map(len, ROUTES))
+    env_w = max(len(route.env) for route in ROUTES.values())
+    lines = []
+    for name, verdict in verdicts.items():
+        state = "on" if verdict.on else "off"
+        lines.append(f"{name.ljust(name_w)}  {ROUTES[name].env.ljust(env_w)}  {state.ljust(3)}  {verdict.why}")
+    return "\n".join(lines)

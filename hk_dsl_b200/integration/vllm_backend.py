@@ -231,7 +231,7 @@ class HKAttentionImplCore:
         table = attn_metadata.block_table[:n]
         lens = attn_metadata.seq_lens[:n]
         if not self._checked and not engine.capturing():
-            self._check(table, lens)
+            self._check(table, lens, k_cache.shape[2])       # head-major cache: (blocks, kv_heads, page, d)
         splits = self._plan(n, query.device)
         scratch = None
         if splits > 1:
@@ -246,9 +246,12 @@ class HKAttentionImplCore:
                                          self.scale, self.kv_cache_dtype, ks, vs, num_splits=splits, scratch=scratch)
         PATCH.count("decode")
 
-    def _check(self, table, lens):
+    def _check(self, table, lens, block_size: int = paged.KV_BLOCK):
         """Once per layer object, never under capture: it reads the device. The kernel reads
-        these two as int32 and indexes memory with the result."""
+        these two as int32 and indexes memory with the result. `block_size` is the page size of
+        the cache in hand (16, 32, 64 or a hybrid model's larger page): a table column is one such
+        page. The reference counts with its constant because it refuses any page but 16
+        (python/hk/integration/vllm_backend.py:490, 731-753)."""
         self._checked = True
         for name, t in (("block_table", table), ("seq_lens", lens)):
             if t.dtype != torch.int32 or t.stride(-1) != 1:
@@ -257,8 +260,9 @@ class HKAttentionImplCore:
         if lens.numel():
             mx = int(lens.max())
             cols = table.shape[-1]
-            if -(-mx // paged.KV_BLOCK) > cols:
-                raise ValueError(f"{NAME}: seq_len {mx} needs {-(-mx // paged.KV_BLOCK)} pages but block_table "
+            need = -(-mx // max(1, int(block_size)))
+            if need > cols:
+                raise ValueError(f"{NAME}: seq_len {mx} needs {need} pages of {block_size} tokens but block_table "
                                  f"has {cols} columns.")
 
 

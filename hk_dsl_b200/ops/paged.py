@@ -274,27 +274,7 @@ def decode_step(out: torch.Tensor, query: torch.Tensor, key: Optional[torch.Tens
     given. Shapes the stream kernel does not take (one split, more than 2048 sequences) run the
     separate launches."""
     n, hq, d, bs, hkv, qsl = _decode_call(out, query, key_cache, value_cache, block_tables, seq_lens, query_start_loc)
-    if (key is None) != (value is None):
-        raise ValueError("hk.ops.paged: decode_step takes key and value together")
-    kp = vp = sp = None
-    kst = (0, 0, 0, 0)
-    slot64 = 0
-    if key is not None:
-        _need_cuda(key, value, slot_mapping)
-        if key.dim() != 3 or value.shape != key.shape or key.dtype != query.dtype or value.dtype != key.dtype \
-                or key.shape[1] != hkv or key.shape[2] != d or key.stride(2) != 1 or value.stride(2) != 1:
-            raise ValueError(f"hk.ops.paged: key {tuple(key.shape)} {key.dtype} / value {tuple(value.shape)} "
-                             f"{value.dtype}; the step writes (seqs, {hkv}, {d}) rows of the query's dtype ({query.dtype})")
-        if slot_mapping.dim() != 1 or slot_mapping.dtype not in (torch.int64, torch.int32) \
-                or not slot_mapping.is_contiguous():
-            raise TypeError(f"hk.ops.paged: slot_mapping is {tuple(slot_mapping.shape)} {slot_mapping.dtype}; "
-                            f"contiguous int64 or int32 needed")
-        rows = query.shape[0] if query_start_loc is not None else n
-        if key.shape[0] < rows or slot_mapping.shape[0] < rows:
-            raise ValueError(f"hk.ops.paged: {key.shape[0]} new rows / {slot_mapping.shape[0]} slots for {rows} query rows")
-        kp, vp, sp = key.data_ptr(), value.data_ptr(), slot_mapping.data_ptr()
-        kst = (key.stride(0), key.stride(1), value.stride(0), value.stride(1))
-        slot64 = 1 if slot_mapping.dtype == torch.int64 else 0
+    new = _new_rows(query, key, value, slot_mapping, n, hkv, d, query_start_loc)
     code = kv_dtype_code(kv_cache_dtype, key_cache, query.dtype)
     fp8 = code == _lib.KV_FP8_E4M3
     if num_splits is None:
@@ -310,13 +290,71 @@ def decode_step(out: torch.Tensor, query: torch.Tensor, key: Optional[torch.Tens
         _need_cuda(arrivals)
     rc = lib.hkb_decode_step(
         out.data_ptr(), out.stride(0), out.stride(1), query.data_ptr(), query.stride(0), query.stride(1),
-        kp, vp, *kst, sp, slot64, _cache_t(key_cache), _cache_t(value_cache), block_tables.data_ptr(),
+        *new, _cache_t(key_cache), _cache_t(value_cache), block_tables.data_ptr(),
         block_tables.stride(0), block_tables.shape[1], seq_lens.data_ptr(), qsl, n, hq, hkv, d, bs, float(scale), code,
         _scale_ptr(k_scale, fp8, "k_scale"), _scale_ptr(v_scale, fp8, "v_scale"), num_splits,
         po.data_ptr() if po is not None else None, pl.data_ptr() if pl is not None else None,
         arrivals.data_ptr() if arrivals is not None and num_splits > 1 else None, _stream(query))
     _lib.check("hkb_decode_step", rc)
     return out
+
+
+def _new_rows(query, key, value, slot_mapping, n, hkv, d, query_start_loc):
+    """The step's new K/V rows as the C ABI takes them: (key ptr, value ptr, four strides, slot ptr, slot_is_i64)."""
+    if (key is None) != (value is None):
+        raise ValueError("hk.ops.paged: decode_step takes key and value together")
+    if key is None:
+        return (None, None, 0, 0, 0, 0, None, 0)
+    _need_cuda(key, value, slot_mapping)
+    if key.dim() != 3 or value.shape != key.shape or key.dtype != query.dtype or value.dtype != key.dtype \
+            or key.shape[1] != hkv or key.shape[2] != d or key.stride(2) != 1 or value.stride(2) != 1:
+        raise ValueError(f"hk.ops.paged: key {tuple(key.shape)} {key.dtype} / value {tuple(value.shape)} "
+                         f"{value.dtype}; the step writes (seqs, {hkv}, {d}) rows of the query's dtype ({query.dtype})")
+    if slot_mapping is None or slot_mapping.dim() != 1 or slot_mapping.dtype not in (torch.int64, torch.int32) \
+            or not slot_mapping.is_contiguous():
+        raise TypeError("hk.ops.paged: slot_mapping must be a contiguous int64 or int32 (rows,) tensor")
+    rows = query.shape[0] if query_start_loc is not None else n
+    if key.shape[0] < rows or slot_mapping.shape[0] < rows:
+        raise ValueError(f"hk.ops.paged: {key.shape[0]} new rows / {slot_mapping.shape[0]} slots for {rows} query rows")
+    return (key.data_ptr(), value.data_ptr(), key.stride(0), key.stride(1), value.stride(0), value.stride(1),
+            slot_mapping.data_ptr(), 1 if slot_mapping.dtype == torch.int64 else 0)
+
+
+def decode_step_record(rec_out: torch.Tensor, rec_lse: torch.Tensor, query: torch.Tensor,
+                       key: Optional[torch.Tensor], value: Optional[torch.Tensor], key_cache: torch.Tensor,
+                       value_cache: torch.Tensor, slot_mapping: Optional[torch.Tensor], block_tables: torch.Tensor,
+                       local_lens: torch.Tensor, scale: float, kv_cache_dtype: str = "auto",
+                       k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None, *,
+                       num_splits: int, scratch: Tuple[torch.Tensor, torch.Tensor],
+                       query_start_loc: Optional[torch.Tensor] = None) -> None:
+    """One rank's decode step of a KV axis cut across GPUs: the walk over this rank's tokens
+    (`local_lens`; it writes the new rows when `key` / `value` are given, i.e. on the rank that
+    holds the sequences' last position) and a merge of its splits into the rank's record --
+    `rec_out` `(seqs, q_heads, head_dim)` fp32 normalised and `rec_lse` `(seqs, q_heads)` fp32
+    natural-log sum-exp (-inf where the rank holds nothing of a sequence). Two launches.
+    `merge_partials` (or `SplitKVDecoder.merge`) folds the gathered records of all ranks."""
+    n = local_lens.shape[0]
+    _, hq, d = query.shape
+    if rec_out.dtype != torch.float32 or rec_lse.dtype != torch.float32 or not rec_out.is_contiguous() \
+            or not rec_lse.is_contiguous() or rec_out.numel() < n * hq * d or rec_lse.numel() < n * hq:
+        raise ValueError(f"hk.ops.paged: the record is contiguous fp32 ({n}, {hq}, {d}) and ({n}, {hq})")
+    if num_splits < 2:
+        raise ValueError("hk.ops.paged: a record is written by the merge of at least two splits")
+    _need_cuda(rec_out, rec_lse)
+    # the record stands where a decode's 16-bit out would; the query is passed in that position only to be checked
+    n, hq, d, bs, hkv, qsl = _decode_call(query, query, key_cache, value_cache, block_tables, local_lens,
+                                          query_start_loc)
+    new = _new_rows(query, key, value, slot_mapping, n, hkv, d, query_start_loc)
+    code = kv_dtype_code(kv_cache_dtype, key_cache, query.dtype)
+    fp8 = code == _lib.KV_FP8_E4M3
+    po, pl, _ = _scratch_ptrs(scratch, n, hq, d, num_splits, query.device)
+    rc = _lib.load().hkb_decode_step_record(
+        rec_out.data_ptr(), rec_lse.data_ptr(), query.data_ptr(), query.stride(0), query.stride(1), *new,
+        _cache_t(key_cache), _cache_t(value_cache), block_tables.data_ptr(), block_tables.stride(0),
+        block_tables.shape[1], local_lens.data_ptr(), qsl, n, hq, hkv, d, bs, float(scale), code,
+        _scale_ptr(k_scale, fp8, "k_scale"), _scale_ptr(v_scale, fp8, "v_scale"), num_splits,
+        po.data_ptr(), pl.data_ptr(), _stream(query))
+    _lib.check("hkb_decode_step_record", rc)
 
 
 # --------------------------------------------------------------------------------------
@@ -527,6 +565,20 @@ def plan_splits_for(n_reqs: int, n_kv_heads: int, n_pages: int, sms: int) -> int
     return min(p, MAX_SPLITS)
 
 
+def _row_stride(t: torch.Tensor) -> int:
+    """Stride between consecutive query heads of an evenly strided (requests, kv_heads, group, d) tensor."""
+    return t.stride(2) if t.shape[2] > 1 else t.stride(1)
+
+
+def even_heads(t: torch.Tensor, name: str) -> None:
+    """A (requests, kv_heads, group, head_dim) tensor can be read as (requests, q_heads, head_dim)
+    only if head_dim is contiguous and a kv head's stride is group x the row stride; anything
+    else (a transposed view, say) would be read at the wrong elements, so it is refused."""
+    if t.dim() != 4 or t.stride(3) != 1 or (t.shape[2] > 1 and t.shape[1] > 1 and t.stride(1) != t.shape[2] * t.stride(2)):
+        raise ValueError(f"hk.ops.paged: {name} has strides {tuple(t.stride())} for shape {tuple(t.shape)}; head_dim must be "
+                         f"contiguous and the heads evenly strided (kv head stride = group x row stride)")
+
+
 #: Shapes check_decode has passed (python/hk/ops/paged.py:805-825).
 _PASSED: set = set()
 _PASSED_CAP = 4096
@@ -543,16 +595,15 @@ def decode(q, k_cache, v_cache, block_table, seq_lens, out, scratch, splits: int
            scratch[1].shape if splits > 1 and scratch is not None else None)
     if key not in _PASSED:
         check_decode(q, k_cache, v_cache, block_table, seq_lens, out, scratch=scratch, splits=splits)
-        if q.stride(3) != 1 or q.stride(1) != q.shape[2] * q.stride(2) or \
-                out.stride(3) != 1 or out.stride(1) != out.shape[2] * out.stride(2):
-            raise ValueError("hk.ops.paged: q/out heads must be evenly strided (kv head stride = group x row stride)")
         if len(_PASSED) < _PASSED_CAP:
             _PASSED.add(key)
+    even_heads(q, "q")          # strides are not part of the shape key: checked on every call
+    even_heads(out, "out")
     reqs, hkv, g, d = q.shape
     hq = hkv * g
     fp8 = k_cache.dtype not in ACT_DTYPES
-    q3 = q.as_strided((reqs, hq, d), (q.stride(0), q.stride(2), 1))
-    o3 = out.as_strided((reqs, hq, d), (out.stride(0), out.stride(2), 1))
+    q3 = q.as_strided((reqs, hq, d), (q.stride(0), _row_stride(q), 1))
+    o3 = out.as_strided((reqs, hq, d), (out.stride(0), _row_stride(out), 1))
     sc = None
     if splits > 1:
         sc = (scratch[0].view(-1, hq, d), scratch[1].view(-1, hq))

@@ -69,7 +69,8 @@ class SplitKVDecoder:
 
     Every rank calls `decode` with its own cache shard, block table and LOCAL lengths (the
     tokens of each sequence it holds; 0 is fine) and the same queries. Buffers are allocated
-    once here, so a step allocates nothing: walk (+ local merge) -> `all_gather_into_tensor`
+    once here, so a step allocates nothing: walk (writing the step's new rows where this rank
+    holds them) -> merge of the local splits into this rank's record -> `all_gather_into_tensor`
     on the current stream -> cross-rank merge. Every rank ends with the full answer."""
 
     def __init__(self, num_seqs: int, num_q_heads: int, num_kv_heads: int, head_dim: int, device,
@@ -88,21 +89,36 @@ class SplitKVDecoder:
         n_out = num_seqs * num_q_heads * head_dim
         self.my_out = self.mine[:n_out].view(num_seqs, num_q_heads, head_dim)
         self.my_lse = self.mine[n_out:n_out + num_seqs * num_q_heads].view(num_seqs, num_q_heads)
-        self.unused_out = torch.zeros(num_seqs, num_q_heads, head_dim, device=device, dtype=torch.bfloat16)
+        self._no_out = None
 
     def local_partial(self, query, key_cache, value_cache, block_tables, local_lens, scale,
-                      kv_cache_dtype="auto", k_scale=None, v_scale=None) -> None:
-        """This rank's normalised partial and its lse into `self.mine` (walk + local merge)."""
-        s = self.local_splits
+                      kv_cache_dtype="auto", k_scale=None, v_scale=None, *, key=None, value=None,
+                      slot_mapping=None) -> None:
+        """This rank's record (normalised partial + lse) into `self.mine`: the walk over its tokens
+        and the merge of its splits, two launches. The rank that holds the sequences' last position
+        passes the step's new rows (`key`, `value`, `slot_mapping`): its walk writes them."""
+        paged.decode_step_record(self.my_out, self.my_lse, query, key, value, key_cache, value_cache, slot_mapping,
+                                 block_tables, local_lens, scale, kv_cache_dtype, k_scale, v_scale,
+                                 num_splits=self.local_splits, scratch=self.scratch)
+
+    # the two launches of `local_partial` on their own, for timing them apart and for tests
+    def walk(self, query, key_cache, value_cache, block_tables, local_lens, scale,
+             kv_cache_dtype="auto", k_scale=None, v_scale=None) -> None:
+        """The walk alone: this rank's split partials into `self.scratch` (no cache write, no merge)."""
+        if self._no_out is None or self._no_out.dtype != query.dtype:
+            self._no_out = torch.zeros(self.n, self.hq, self.d, device=query.device, dtype=query.dtype)
         # with more than one split and merge=False the walk writes partials only; `out` is untouched
-        paged.paged_attention_decode(self.unused_out, query, key_cache, value_cache, block_tables, local_lens,
-                                     scale, kv_cache_dtype, k_scale, v_scale, num_splits=s, scratch=self.scratch,
-                                     merge=False)
+        paged.paged_attention_decode(self._no_out, query, key_cache, value_cache, block_tables, local_lens, scale,
+                                     kv_cache_dtype, k_scale, v_scale, num_splits=self.local_splits,
+                                     scratch=self.scratch, merge=False)
+
+    def local_merge(self) -> None:
+        """The merge of this rank's splits into its record (`self.mine`)."""
         po, pl = self.scratch
-        n, hq, d = self.n, self.hq, self.d
+        n, hq, d, s = self.n, self.hq, self.d, self.local_splits
         rc = _lib.load().hkb_merge(self.my_out.data_ptr(), hq * d, d, 1, self.my_lse.data_ptr(),
                                    po.data_ptr(), hq * d, s * hq * d, pl.data_ptr(), hq, s * hq,
-                                   s, n, hq, d, None, None, paged._stream(query))
+                                   s, n, hq, d, None, None, paged._stream(po))
         _lib.check("hkb_merge", rc)
 
     def gather(self) -> None:
@@ -122,8 +138,10 @@ class SplitKVDecoder:
         return out
 
     def decode(self, out, query, key_cache, value_cache, block_tables, local_lens, scale,
-               kv_cache_dtype="auto", k_scale=None, v_scale=None) -> torch.Tensor:
+               kv_cache_dtype="auto", k_scale=None, v_scale=None, *, key=None, value=None,
+               slot_mapping=None) -> torch.Tensor:
+        """The whole step: two launches, one all-gather, one launch."""
         self.local_partial(query, key_cache, value_cache, block_tables, local_lens, scale,
-                           kv_cache_dtype, k_scale, v_scale)
+                           kv_cache_dtype, k_scale, v_scale, key=key, value=value, slot_mapping=slot_mapping)
         self.gather()
         return self.merge(out)

@@ -58,6 +58,11 @@ SIGNATURES = {
                                 CacheT, CacheT, c_void_p, c_int64, c_int, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
                                 c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "hkb_decode_step_record": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                       c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int,
+                                       CacheT, CacheT, c_void_p, c_int64, c_int, c_void_p, c_void_p,
+                                       c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
+                                       c_int, c_void_p, c_void_p, c_void_p]),
     "hkb_arrivals_bytes": (c_size_t, [c_int, c_int]),
     "hkb_paged_prefill": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, CacheT, CacheT,
                                   c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int,
@@ -69,6 +74,7 @@ SIGNATURES = {
     "hkb_plan_splits": (c_int, [c_int, c_int, c_int, c_int]),
     "hkb_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "hkb_scratch_lse_offset": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "hkb_hbm_read_probe": (c_int, [c_void_p, c_size_t, c_int, c_int, c_void_p, c_void_p]),
     "hkb_sm_count": (c_int, [c_int]),
     "hkb_strerror": (c_char_p, [c_int]),
     "hkb_last_cuda_error": (c_int, []),

@@ -96,14 +96,19 @@ def fused_walk_op(head_dim: int, splits: int) -> engine.Op:
         raise ValueError(f"hk.ops.paged: no walk for head_dim {head_dim} (have {paged.DECODE_HEAD_DIMS})")
 
     def impl(q, k_cache, v_cache, block_table, seq_lens, out, o_part, ml_part):
+        paged.even_heads(q, "q")
+        paged.even_heads(out, "out")
         reqs, hkv, g, d = q.shape
         hq = hkv * g
-        q3 = q.as_strided((reqs, hq, d), (q.stride(0), q.stride(2), 1))
-        o3 = out.as_strided((reqs, hq, d), (out.stride(0), out.stride(2), 1))
-        fp8 = k_cache.dtype != torch.bfloat16
+        q3 = q.as_strided((reqs, hq, d), (q.stride(0), paged._row_stride(q), 1))
+        o3 = out.as_strided((reqs, hq, d), (out.stride(0), paged._row_stride(out), 1))
+        if k_cache.dtype not in paged.ACT_DTYPES:
+            # the reference's schema has no room for scales: an fp8 cache goes through the flat op
+            raise TypeError(f"hk::paged_decode_fused_d{head_dim}_s{splits} reads bfloat16 or float16 caches; an "
+                            f"fp8 cache ({k_cache.dtype}) needs k_scale / v_scale: use hk::paged_attention_decode")
         paged.paged_attention_decode(
             o3, q3, k_cache.transpose(1, 2), v_cache.transpose(1, 2), block_table, seq_lens[:reqs], d ** -0.5,
-            "fp8" if fp8 else "auto", None, None, num_splits=splits,
+            "auto", None, None, num_splits=splits,
             scratch=(o_part.view(-1, hq, d), ml_part.view(-1, hq)) if splits > 1 else None, merge=False)
 
     return _define(f"paged_decode_fused_d{head_dim}_s{splits}",
@@ -131,7 +136,12 @@ def prefill_op(head_dim: int, group: int) -> engine.Op:
     def impl(q, k_cache, v_cache, block_table, seq_lens, q_start, tiles, out):
         n = q.shape[0]
         hq = k_cache.shape[1] * group
-        paged.paged_prefill(out.view(n, hq, head_dim), q.view(n, hq, head_dim), k_cache.transpose(1, 2),
+        for name, t in (("q", q), ("out", out)):
+            if t.dim() != 2 or t.shape[1] != hq * head_dim or t.stride(1) != 1:
+                raise ValueError(f"hk::paged_prefill_d{head_dim}_g{group}: {name} is {tuple(t.shape)} strides "
+                                 f"{tuple(t.stride())}; (tokens, {hq * head_dim}) rows with contiguous columns needed")
+        paged.paged_prefill(out.as_strided((n, hq, head_dim), (out.stride(0), head_dim, 1)),
+                            q.as_strided((n, hq, head_dim), (q.stride(0), head_dim, 1)), k_cache.transpose(1, 2),
                             v_cache.transpose(1, 2), block_table, seq_lens, q_start, tiles, head_dim ** -0.5)
 
     return _define(f"paged_prefill_d{head_dim}_g{group}",

@@ -17,7 +17,9 @@
  *   - the return value is an hkb_status: 0 on success, a negative code for a
  *     refused argument (nothing was launched), HKB_ERR_CUDA for a CUDA launch
  *     error. Nothing aborts and nothing throws;
- *   - re-entrant: the only state is a per-device read-only attribute cache.
+ *   - re-entrant: the only state is a per-device read-only attribute cache -- except where an
+ *     entry point says otherwise (hkb_paged_decode_static shares one built-in array a device;
+ *     hkb_decode_step with `arrivals` keeps counters in the caller's array).
  *   - strides are in ELEMENTS of the tensor's own type; head_dim is contiguous.
  *
  * What each entry point stands in for in hk-dsl (paths are the reference's):
@@ -33,9 +35,9 @@
 extern "C" {
 #endif
 
-#define HKB_VERSION 110 /* major*100 + minor */
+#define HKB_VERSION 120 /* major*100 + minor */
 
-/* KV element types (kv_dtype). Queries and outputs are always bf16. */
+/* KV element types (kv_dtype). Queries, new K/V rows and outputs are bf16, except with HKB_KV_F16. */
 #define HKB_KV_BF16 0
 #define HKB_KV_FP8_E4M3 1
 /* float16 throughout: the cache, the new K/V rows, the query and the output are all fp16 (a model
@@ -196,7 +198,8 @@ int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_stride_head
  * hkb_merge: two (the walk writes the new rows itself; then the merge kernel), or one when
  * `arrivals` is given (the walk also folds the partials). Where the shape does not allow it
  * (one split, more than 2048 sequences) the three separate launches run. `out` holds the
- * final bf16 answer either way, and the cache holds the new rows.
+ * final bf16 answer either way, and the cache holds the new rows. Every refusal -- the cache
+ * write's, the walk's and the merge's -- is returned before the first launch.
  *
  * key / value: the new rows, bf16, one row a sequence (row of sequence i = q_start[i], or i
  * when q_start is NULL -- the row of its query; with q_start, row i must belong to sequence
@@ -233,6 +236,33 @@ int hkb_decode_step(void* out, int64_t out_stride_tok, int64_t out_stride_head,
                     int block_size, float scale, int kv_dtype,
                     const float* k_scale, const float* v_scale,
                     int num_splits, float* part_out, float* part_lse, int32_t* arrivals, void* stream);
+
+/*
+ * The same step for ONE RANK of a KV axis cut across GPUs: the walk over this rank's tokens
+ * (writing the step's new rows if key / value are given -- the rank that holds the sequence's
+ * last position passes them, the others pass NULL) and a merge of its splits that leaves the
+ * rank's RECORD instead of the final answer: rec_out[i, h, :] the normalised fp32 partial
+ * (contiguous, num_seqs x num_q_heads x head_dim) and rec_lse[i, h] its natural-log sum-exp
+ * (-inf where the rank holds no token of sequence i). Records of all ranks, gathered, are folded
+ * by hkb_merge with one part a rank. Two launches; num_splits >= 2 (the record is written by the
+ * merge). Everything else as hkb_decode_step.
+ *
+ * Replaces nothing in the reference, which cuts the KV axis inside one GPU only
+ * (python/hk/ops/paged.py:171-194); it is that cut carried one level up.
+ */
+int hkb_decode_step_record(float* rec_out, float* rec_lse,
+                           const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                           const void* key, const void* value,
+                           int64_t key_stride_tok, int64_t key_stride_head,
+                           int64_t val_stride_tok, int64_t val_stride_head,
+                           const void* slot_mapping, int slot_is_i64,
+                           hkb_cache_t k_cache, hkb_cache_t v_cache,
+                           const int32_t* block_table, int64_t table_stride, int max_pages,
+                           const int32_t* seq_lens, const int32_t* q_start,
+                           int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                           int block_size, float scale, int kv_dtype,
+                           const float* k_scale, const float* v_scale,
+                           int num_splits, float* part_out, float* part_lse, void* stream);
 
 /* Bytes of the arrival counters hkb_decode_step takes. */
 size_t hkb_arrivals_bytes(int num_seqs, int num_kv_heads);
@@ -305,6 +335,17 @@ size_t hkb_scratch_lse_offset(int num_seqs, int num_q_heads, int head_dim, int n
  * environment's HKB_MMA_MIN_GROUP = 1..8 overrides both). The reference picks its own contraction
  * form per architecture the same way (python/hk/ops/paged.py:498-547). */
 int hkb_walk_uses_mma(int group, int kv_dtype);
+
+/*
+ * A read-only streaming probe: one launch reads `bytes` of `buf` once with 16-byte loads (a
+ * persistent grid of ctas_per_sm x SMs CTAs of 256 threads, loads_in_flight = 1, 2, 4, 8 or 16
+ * independent loads a thread) and writes nothing (`sink`, 4 device bytes, is only there to keep
+ * the loads alive). The caller times it, rotates buffers larger than L2 and sweeps the two
+ * parameters; the best figure is the read ceiling the decode walk is held to beside the copy peak.
+ * Replaces: tools/hk-bench/hbm_probe.hip:1-134.
+ */
+int hkb_hbm_read_probe(const void* buf, size_t bytes, int ctas_per_sm, int loads_in_flight, void* sink,
+                       void* stream);
 
 /* SM count of CUDA device `device` (-1 = current), cached; <= 0 on error. */
 int hkb_sm_count(int device);

@@ -1,6 +1,8 @@
-"""End-to-end smoke of the attention backend inside a real vLLM engine, without weights.
+"""End-to-end smoke of the attention backend inside a real vLLM engine, without weights. An
+opt-in engine test (it needs a GPU and an installed vLLM, and takes minutes): pytest does not
+collect it; run it by hand.
 
-    python -m hk_dsl_b200.integration.vllm_smoke [--graphs] [--kv fp8] [--dtype float16] [--route [--shadow]]
+    python tests/engine_smoke.py [--graphs] [--kv fp8] [--dtype float16] [--route [--shadow]]
 
 Builds a two-layer Llama-shaped model with random ("dummy") weights from a config written to
 a temporary directory, runs the same token prompts greedily through vLLM twice in one process
@@ -25,6 +27,8 @@ import json
 import os
 import sys
 import tempfile
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
 def tiny_config(path: str, heads: int = 8, kv_heads: int = 2) -> None:
@@ -85,7 +89,7 @@ def main(argv=None) -> int:
 
     import torch
 
-    from . import _vllm_plugin, vllm_backend, vllm_prefill
+    from hk_dsl_b200.integration import _vllm_plugin, vllm_backend, vllm_prefill
 
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(3, 2000, (n,), generator=g).tolist() for n in (5, 37, 300, 1, 1025, 64)]

@@ -86,3 +86,42 @@ def test_the_joined_step_and_the_prefill_have_no_cpu_path_either():
     with pytest.raises(RuntimeError, match="no CPU path"):
         paged.paged_prefill(torch.empty_like(q), q, cache, cache, table, lens, torch.tensor([0, 1, 2], dtype=torch.int32),
                             torch.zeros(2, 2, dtype=torch.int32), 0.1)
+
+
+def test_strides_are_checked_on_every_call_not_once_a_shape():
+    """The shape memo holds shapes and dtypes, not strides: a view of an already-passed shape whose
+    heads are not evenly strided (here: transposed rows) must still be refused, on every call."""
+    a = _ok()
+    paged._PASSED.clear()
+    q = a["q"]
+    key = (q.shape, q.dtype, a["k_cache"].shape, a["k_cache"].dtype, a["v_cache"].shape, a["block_table"].shape,
+           a["block_table"].dtype, a["seq_lens"].shape, a["seq_lens"].dtype, a["out"].shape, a["out"].dtype, 1, None, None)
+    paged._PASSED.add(key)                       # as if a well-formed call of this shape had passed before
+    reqs, hkv, g, d = q.shape
+    bad = torch.zeros(reqs, hkv, d, g, dtype=q.dtype).transpose(2, 3)        # same shape, head_dim not contiguous
+    assert bad.shape == q.shape
+    with pytest.raises(ValueError, match="evenly strided"):
+        paged.decode(bad, a["k_cache"], a["v_cache"], a["block_table"], a["seq_lens"], a["out"], None, 1)
+    uneven = torch.zeros(reqs, hkv, g + 1, d, dtype=q.dtype)[:, :, :g]       # kv-head stride != group x row stride
+    with pytest.raises(ValueError, match="evenly strided"):
+        paged.decode(a["q"], a["k_cache"], a["v_cache"], a["block_table"], a["seq_lens"], uneven, None, 1)
+    paged.even_heads(a["q"], "q")
+
+
+def test_backend_check_counts_pages_of_the_caches_own_block_size():
+    """A table column is one page of the cache in hand: 32, 64 or a hybrid model's 544 tokens, not
+    always 16."""
+    from hk_dsl_b200.integration.vllm_backend import HKAttentionImplCore
+
+    core = HKAttentionImplCore.__new__(HKAttentionImplCore)
+    for block_size, max_len in ((16, 4096), (32, 4096), (64, 4096), (544, 8192)):
+        cols = -(-max_len // block_size)
+        table = torch.zeros(2, cols, dtype=torch.int32)
+        lens = torch.tensor([max_len - 3, 17], dtype=torch.int32)       # a sequence near max_model_len
+        core._checked = False
+        core._check(table, lens, block_size)
+        assert core._checked
+        with pytest.raises(ValueError, match=f"pages of {block_size} tokens"):
+            core._check(table[:, : cols - 1], torch.tensor([max_len, 1], dtype=torch.int32), block_size)
+    with pytest.raises(TypeError, match="int32"):
+        core._check(torch.zeros(2, 4, dtype=torch.int64), torch.ones(2, dtype=torch.int32), 16)

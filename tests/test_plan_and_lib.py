@@ -22,7 +22,7 @@ def test_every_declared_symbol_is_exported():
     loaded = lib.load()
     for name in declared:
         assert getattr(loaded, name) is not None
-    assert loaded.hkb_version() == 110
+    assert loaded.hkb_version() == 120
 
 
 def test_status_text_and_refusals_need_no_gpu():
@@ -45,6 +45,41 @@ def test_status_text_and_refusals_need_no_gpu():
     assert l.hkb_merge(16, 128, 128, 0, None, None, 4, 4, 16, 1, 1, 2, 1, 4, 128, None, None, None) == -1
     with pytest.raises(lib.HkbError, match="head_dim"):
         lib.check("hkb_paged_decode", -2)
+
+
+def test_decode_step_refuses_everything_before_its_first_launch():
+    """hkb_decode_step runs up to three launches; whatever any of them would refuse -- the merge's
+    alignment and stride rules included -- comes back before the first one, so a negative status
+    always means that nothing ran. No GPU is needed: every case below is refused on the host."""
+    l = lib.load()
+    c = lib.CacheT(16, 2048, 128, 32768, 4)
+
+    def step(out=16, out_st=(512, 128), key=16, kst=(256, 128), splits=4, po=16, pl=16, arrivals=None, nseq=1,
+             fn=l.hkb_decode_step):
+        return fn(out, out_st[0], out_st[1], 16, 512, 128, key, key, kst[0], kst[1], kst[0], kst[1], 16 if key else None,
+                  1, c, c, 16, 8, 8, 16, None, nseq, 4, 2, 128, 16, 0.1, 0, None, None, splits, po, pl, arrivals, None)
+
+    assert step(nseq=0) == 0
+    assert step(out=18) == -7                      # the merge stores 8-byte pairs: out must be 8-byte aligned
+    assert step(out_st=(510, 128)) == -6           # and its strides multiples of 4 elements
+    assert step(out_st=(512, 126)) == -6
+    assert step(po=None) == -8                     # splits without scratch
+    assert step(kst=(257, 128)) == -6              # new rows are read as 16-byte chunks
+    assert step(key=20) == -7
+    # the record-writing form: a record needs the merge, hence at least two splits
+    rec = l.hkb_decode_step_record
+    args = (16, 16, 16, 512, 128, None, None, 0, 0, 0, 0, None, 0, c, c, 16, 8, 8, 16, None, 1, 4, 2, 128, 16, 0.1, 0,
+            None, None)
+    assert rec(*args, 1, 16, 16, None) == -8
+    assert rec(*args[:20], 0, *args[21:], 4, 16, 16, None) == 0        # no sequences: nothing to do
+    assert rec(None, 16, *args[2:], 4, 16, 16, None) == -1
+
+
+def test_probe_refuses_bad_arguments_without_a_gpu():
+    l = lib.load()
+    assert l.hkb_hbm_read_probe(None, 1 << 20, 2, 4, 16, None) == -1
+    assert l.hkb_hbm_read_probe(16, 1 << 20, 0, 4, 16, None) == -9
+    assert l.hkb_hbm_read_probe(24, 1 << 20, 2, 4, 16, None) == -7
 
 
 def test_scratch_sizes():

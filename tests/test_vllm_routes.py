@@ -259,7 +259,7 @@ def test_backend_prefill_batches_raise_and_checks_metadata():
         impl.forward(None, None, None, None, kv, md, output=None, output_scale=torch.ones(1))
     with pytest.raises(TypeError, match="int32"):
         impl._check(torch.zeros(2, 8, dtype=torch.int64), torch.ones(2, dtype=torch.int32))
-    with pytest.raises(ValueError, match="pages but block_table"):
+    with pytest.raises(ValueError, match="pages of 16 tokens but block_table"):
         impl._check(torch.zeros(2, 2, dtype=torch.int32), torch.tensor([10, 100], dtype=torch.int32))
     out = torch.ones(3, 8)
     assert impl.forward(None, None, None, None, kv, None, output=out) is out and (out == 0).all()   # profiling run
