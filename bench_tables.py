@@ -198,7 +198,7 @@ def prefill_table():
         flops = 4.0 * hq * d * keys_seen
         rows.append({"requests": len(reqs), "context": reqs[0][0], "q_len": reqs[0][1], "cache": kind, "ms": round(ms, 3),
                      "tflops": round(flops / ms / 1e9, 1), "frac_of_measured_bf16_peak": round(flops / ms / 1e9 / peak, 3)})
-    print(json.dumps({"table": "paged prefill, 32q/8kv heads, D128, block 16; mma.sync form", "peak_tflops": peak,
+    print(json.dumps({"table": "paged prefill, 32q/8kv heads, D128, block 16", "kernel": "mma.sync" if os.environ.get("HKB_PREFILL_MMA_SYNC") == "1" else "tcgen05 + TMEM for 16-bit caches, mma.sync for fp8", "peak_tflops": peak,
                       "rows": rows}), flush=True)
     return 0
 

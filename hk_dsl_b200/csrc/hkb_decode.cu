@@ -378,7 +378,25 @@ struct StepExtra {
   int32_t* arrivals = nullptr;
   bool wrote = false;    // out: the walk wrote the new rows into the cache itself
   bool folded = false;   // out: the walk folded the partials itself
+  int ablate = 0;        // ABL_* mask: an attribution run (hkb_paged_decode_ablate)
 };
+
+// The stream walk with stages left out. Built for the headline shape only -- head_dim 128, a bf16
+// cache, a GQA group of 4 to 8 on the tensor-core worker, more than one split -- and for the masks
+// an attribution table needs: each stage alone, both copies, all the math.
+static int dispatch_ablated(const DecodeArgs& a, int num_seqs, int ablate, cudaStream_t st) {
+  using P = WalkMMA<128, false, 1, 4, 3, false>;
+  const dim3 grid = stream_grid(a.num_kv_heads);
+#define HKB_ABL(MASK)                                                                                               \
+  case MASK:                                                                                                        \
+    return launch_stream<walk_stream_ablated_kernel<P, 4, MASK>>(WalkStream<P, 4>::SMEM_BYTES, 4 * 32, grid, a, num_seqs, st);
+  switch (ablate) {
+    HKB_ABL(ABL_PAGE) HKB_ABL(ABL_KLOAD) HKB_ABL(ABL_VLOAD) HKB_ABL(ABL_QK) HKB_ABL(ABL_SOFTMAX) HKB_ABL(ABL_PV)
+    HKB_ABL(ABL_KLOAD | ABL_VLOAD) HKB_ABL(ABL_QK | ABL_SOFTMAX | ABL_PV)
+  }
+#undef HKB_ABL
+  return HKB_ERR_UNSUPPORTED;
+}
 
 // The stream kernel takes the whole step (every ring is a single warp). HKB_STEP_UNFUSED=1 keeps
 // the three separate launches, the arm the joined step is compared with.
@@ -484,6 +502,11 @@ static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_hea
   }
   cudaStream_t st = (cudaStream_t)stream;
 
+  if (extra && extra->ablate) {
+    if (head_dim != 128 || fp8 || f16 || group < 4 || group > 8 || !use_stream(a, num_seqs) || !hkb_walk_uses_mma(group, kv_dtype))
+      return HKB_ERR_UNSUPPORTED;
+    return dispatch_ablated(a, num_seqs, extra->ablate, st);
+  }
   if (f16) {   // fp16: the tensor-core worker at every group (the CUDA-core workers unpack bf16)
     if (head_dim == 128) return dispatch_mma<128, false, true>(a, num_seqs, st);
     if (head_dim == 256) return dispatch_mma<256, false, true>(a, num_seqs, st);
@@ -602,6 +625,26 @@ static int step_impl(void* out, int64_t out_stride_tok, int64_t out_stride_head,
 }
 
 }  // namespace hkb
+
+extern "C" int hkb_paged_decode_ablate(void* out, int64_t out_stride_tok, int64_t out_stride_head,
+                                       const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                                       hkb_cache_t kc, hkb_cache_t vc,
+                                       const int32_t* block_table, int64_t table_stride, int max_pages,
+                                       const int32_t* seq_lens, const int32_t* q_start,
+                                       int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                                       int block_size, float scale, int kv_dtype,
+                                       const float* k_scale, const float* v_scale,
+                                       int num_splits, float* part_out, float* part_lse, int ablate, void* stream) {
+  if (ablate == 0)
+    return hkb_paged_decode(out, out_stride_tok, out_stride_head, q, q_stride_tok, q_stride_head, kc, vc, block_table,
+                            table_stride, max_pages, seq_lens, q_start, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                            block_size, scale, kv_dtype, k_scale, v_scale, num_splits, part_out, part_lse, stream);
+  hkb::StepExtra x;
+  x.ablate = ablate;
+  return hkb::decode_impl(out, out_stride_tok, out_stride_head, q, q_stride_tok, q_stride_head, kc, vc, block_table,
+                          table_stride, max_pages, seq_lens, q_start, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                          block_size, scale, kv_dtype, k_scale, v_scale, num_splits, part_out, part_lse, stream, &x);
+}
 
 extern "C" int hkb_decode_step(void* out, int64_t out_stride_tok, int64_t out_stride_head,
                                const void* q, int64_t q_stride_tok, int64_t q_stride_head,

@@ -6,6 +6,16 @@
 
 namespace hkb {
 
+// Stages of the walk a measurement build can leave out, to see what each costs (the mask of
+// hkb_paged_decode_ablate; the reference's ablate=("page","kload","vload","qk","softmax","pv"),
+// python/hk/ops/paged.py:524-533). A walk with any of them set computes nothing meaningful.
+constexpr int ABL_PAGE = 1;      // page ids are not read from the block table (tile t reads block t mod pool)
+constexpr int ABL_KLOAD = 2;     // K tiles are not copied
+constexpr int ABL_VLOAD = 4;     // V tiles are not copied
+constexpr int ABL_QK = 8;        // no S = K Q^T products
+constexpr int ABL_SOFTMAX = 16;  // no maximum / exponential / sum
+constexpr int ABL_PV = 32;       // no O += V^T P^T products
+
 struct DecodeArgs {
   __nv_bfloat16* out;
   int64_t out_stride_tok, out_stride_head;

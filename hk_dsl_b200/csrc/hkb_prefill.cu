@@ -19,6 +19,9 @@
 // online softmax in exp2 with a lazy reference. This is a dense contraction whose roofline
 // is the tensor pipe; mma.sync is the baseline form of it, not the tcgen05 form.
 #include "hkb_walk_mma.cuh"
+#include "hkb_prefill_tc.cuh"
+
+#include <cstdlib>
 
 extern thread_local int hkb_tls_cuda_error;
 
@@ -106,7 +109,9 @@ struct Prefill {
     const int passes = a.group / GP;
     const int kvh = blockIdx.y / passes;
     const int hbase = kvh * a.group + (blockIdx.y % passes) * GP;
-    const int req = __ldg(a.work + 2 * blockIdx.x), row0 = __ldg(a.work + 2 * blockIdx.x + 1);
+    // a work item covers 2 * BT query rows (what the tensor-memory kernel takes in one CTA): two CTAs here
+    const int item = blockIdx.x >> 1;
+    const int req = __ldg(a.work + 2 * item), row0 = __ldg(a.work + 2 * item + 1) + (blockIdx.x & 1) * BT;
     const int q0 = __ldg(a.q_start + req), q1 = __ldg(a.q_start + req + 1);
     const int q_len = q1 - q0;
     const int seq_len = __ldg(a.seq_lens + req);
@@ -349,7 +354,7 @@ static int launch_prefill(const PrefillArgs& a, int num_work, cudaStream_t st) {
     if (e == cudaSuccess) armed[dev] = true;
   }
   if (e == cudaSuccess) {
-    dim3 grid(num_work, a.num_kv_heads * (a.group / GP));
+    dim3 grid(2 * num_work, a.num_kv_heads * (a.group / GP));
     prefill_kernel<D, GP, FP8, F16><<<grid, Prefill<D, GP, FP8, F16>::WARPS * 32, smem, st>>>(a);
     e = cudaGetLastError();
   }
@@ -366,13 +371,57 @@ static int dispatch_prefill(const PrefillArgs& a, int num_work, cudaStream_t st)
   return launch_prefill<D, 1, FP8, F16>(a, num_work, st);
 }
 
+// ---- the tensor-memory form (head_dim 128, 16-bit caches) ----
+template <int GP, bool F16>
+static int launch_prefill_tc(const tc::Args& a, int num_work, cudaStream_t st) {
+  static bool armed[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess && dev >= 0 && dev < 64 && !armed[dev]) {
+    e = cudaFuncSetAttribute(tc::prefill_tc_kernel<GP, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+    if (e == cudaSuccess) armed[dev] = true;
+  }
+  if (e == cudaSuccess) {
+    dim3 grid(num_work, a.num_kv_heads * (a.group / GP));
+    tc::prefill_tc_kernel<GP, F16><<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(a);
+    e = cudaGetLastError();
+  }
+  if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
+  return HKB_OK;
+}
+
+template <bool F16>
+static int dispatch_prefill_tc(const tc::Args& a, int num_work, cudaStream_t st) {
+  if (a.group % 8 == 0) return launch_prefill_tc<8, F16>(a, num_work, st);
+  if (a.group % 4 == 0) return launch_prefill_tc<4, F16>(a, num_work, st);
+  if (a.group % 2 == 0) return launch_prefill_tc<2, F16>(a, num_work, st);
+  return launch_prefill_tc<1, F16>(a, num_work, st);
+}
+
 }  // namespace hkb
 
+// 256 query rows (tokens x the heads of the GQA group a CTA serves) a work item, whichever kernel runs.
 extern "C" int hkb_prefill_tile_rows(int num_q_heads, int num_kv_heads) {
   if (num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads) return 0;
   const int g = num_q_heads / num_kv_heads;
   const int gp = g % 8 == 0 ? 8 : g % 4 == 0 ? 4 : g % 2 == 0 ? 2 : 1;
-  return 16 * (8 / gp);
+  return 256 / gp;
+}
+
+extern "C" int hkb_prefill_uses_tcgen05(int head_dim, int kv_dtype) {
+  const char* v = std::getenv("HKB_PREFILL_MMA_SYNC");
+  if (v && v[0] == '1') return 0;
+  return head_dim == 128 && (kv_dtype == HKB_KV_BF16 || kv_dtype == HKB_KV_F16) ? 1 : 0;
+}
+
+extern "C" int hkb_prefill_tc_error(int clear) {
+  int code = 0;
+  if (cudaMemcpyFromSymbol(&code, hkb::tc::g_error, sizeof(int)) != cudaSuccess) { (void)cudaGetLastError(); return -1; }
+  if (clear && code) {
+    const int zero = 0;
+    if (cudaMemcpyToSymbol(hkb::tc::g_error, &zero, sizeof(int)) != cudaSuccess) (void)cudaGetLastError();
+  }
+  return code;
 }
 
 extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_stride_head,
@@ -420,6 +469,21 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
   a.k_scale = fp8 ? k_scale : nullptr;
   a.v_scale = fp8 ? v_scale : nullptr;
   cudaStream_t st = (cudaStream_t)stream;
+  // head_dim 128 on a 16-bit cache: the tcgen05 / TMEM kernel, when every query row can be read in
+  // 16-byte chunks (it stages them with vector loads); the mma.sync kernel otherwise
+  if (hkb_prefill_uses_tcgen05(head_dim, kv_dtype) && (uintptr_t)q % 16 == 0 && (q_stride_tok | q_stride_head) % 8 == 0) {
+    tc::Args t;
+    t.out = a.out; t.out_stride_tok = a.out_stride_tok; t.out_stride_head = a.out_stride_head;
+    t.q = a.q; t.q_stride_tok = a.q_stride_tok; t.q_stride_head = a.q_stride_head;
+    t.k = a.k; t.v = a.v;
+    t.k_stride_block = a.k_stride_block; t.k_stride_token = a.k_stride_token; t.k_stride_head = a.k_stride_head;
+    t.v_stride_block = a.v_stride_block; t.v_stride_token = a.v_stride_token; t.v_stride_head = a.v_stride_head;
+    t.num_blocks = a.num_blocks; t.block_table = a.block_table; t.table_stride = a.table_stride; t.max_pages = a.max_pages;
+    t.seq_lens = a.seq_lens; t.q_start = a.q_start; t.work = a.work;
+    t.num_q_heads = a.num_q_heads; t.num_kv_heads = a.num_kv_heads; t.group = a.group; t.tiles_per_page = a.tiles_per_page;
+    t.scale = a.scale;
+    return kv_dtype == HKB_KV_F16 ? dispatch_prefill_tc<true>(t, num_work, st) : dispatch_prefill_tc<false>(t, num_work, st);
+  }
   if (fp8) return dispatch_prefill<128, true>(a, num_work, st);
   if (kv_dtype == HKB_KV_F16) {
     if (head_dim == 256) return dispatch_prefill<256, false, true>(a, num_work, st);

@@ -1,0 +1,460 @@
+// Paged prefill on the fifth-generation tensor cores: tcgen05.mma with accumulators in tensor
+// memory (TMEM). head_dim 128, bf16 or fp16 caches.
+//
+// What it computes is hk-dsl's paged prefill (python/hk/ops/paged_prefill.py:59-620): causal
+// attention of a request's new tokens over its paged cache, the grid a host-built work list of
+// (request, query tile) items (paged_prefill.py:879-968).
+//
+// One CTA an SM works on one item: 2 query tiles of 128 rows each -- a tile is T = 128 / GP
+// consecutive tokens of GP query heads of one kv head, so both tiles and all their heads share
+// every K/V block the CTA stages -- and walks the keys in blocks of 64:
+//
+//   producers (2 warps)  gather the block's 16-token pages through the block table into a ring of
+//                        16 KB shared-memory slots with cp.async, rows of 128 bytes XOR-swizzled
+//                        the way the tensor core reads them (K blocks and V blocks alternate in
+//                        the ring), make them visible to the async proxy and arrive on the slot's
+//                        mbarrier;
+//   MMA warp (1 thread)  S = Q K^T for both tiles (8 tcgen05.mma of 128 x 64 x 16, Q and K from
+//                        shared memory) into two alternating 64-column TMEM buffers a tile, and
+//                        O += P V (4 tcgen05.mma of 128 x 128 x 16, P from TMEM, V from shared
+//                        memory read MN-major) into the tile's 128 accumulator columns; completion
+//                        is signalled by tcgen05.commit onto mbarriers;
+//   softmax (2 x 4 warps) a thread owns one query row: it reads its 64 scores from TMEM
+//                        (tcgen05.ld), masks the diagonal block, keeps the running maximum lazily
+//                        (the accumulator is rescaled only when a block's maximum exceeds the
+//                        reference by 2^8), writes P as packed 16-bit pairs over the scores it has
+//                        just read (tcgen05.st) and arrives; no shuffles: a row is a TMEM lane.
+//
+// While the softmax warps of one tile work on block j, the tensor core computes block j+1's scores
+// and the other tile's products. Every wait is bounded: a barrier that does not flip within about a
+// second sets an error word (hkb_prefill_tc_error) and the CTA winds down -- its copies drained,
+// its TMEM freed -- instead of spinning.
+#pragma once
+
+#include "hkb_common.cuh"
+
+namespace hkb {
+namespace tc {
+
+constexpr int KVB = 64;                       // keys a block
+constexpr int ROWS = 128;                     // rows of a query tile = TMEM lanes
+constexpr int D = 128;                        // head_dim
+constexpr int HALF_BYTES_Q = ROWS * 128;      // 64 dims of 128 rows, 128-byte rows
+constexpr int Q_BYTES = 2 * HALF_BYTES_Q;     // one query tile: 32 KB
+constexpr int HALF_BYTES_KV = KVB * 128;      // 64 dims of 64 tokens
+constexpr int SLOT_BYTES = 2 * HALF_BYTES_KV; // a K or a V block: 16 KB
+constexpr int NSLOT = 8;                      // ring slots: K blocks in the even ones, V blocks in the odd ones
+constexpr int LAG = 3;                        // copy groups a producer warp keeps in flight
+constexpr int SOFTMAX_WARPS = 8, MMA_WARP = 8, K_WARP = 9, V_WARP = 10, WARPS = 11;
+constexpr int THREADS = WARPS * 32;
+constexpr int TMEM_COLS = 512;
+// TMEM columns: O of tile 0 and 1, then two score buffers a tile (P is written over the scores)
+__host__ __device__ constexpr int o_col(int tile) { return tile * 128; }
+__host__ __device__ constexpr int s_col(int tile, int buf) { return 256 + tile * 128 + buf * 64; }
+
+struct Bars {                                  // mbarriers, 8 bytes each
+  uint64_t full[NSLOT], empty[NSLOT];
+  uint64_t s_full[2][2], p_full[2][2], o_done[2];
+  uint32_t tmem_base;
+  int abort;
+};
+constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + 2 * Q_BYTES + NSLOT * SLOT_BYTES + 1024 /*Bars*/;
+static_assert(sizeof(Bars) <= 1024, "barrier block");
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory of one SM");
+
+__device__ int g_error;   // first failure code of any CTA since it was last cleared (0: none)
+
+// ---- PTX wrappers -------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.shared::cta.b64 st, [%0];\n}\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Wait for the phase of `parity` to complete; gives up (and raises the CTA's abort flag) after
+// about 2^31 clocks, or as soon as another thread of the CTA has given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort, int code) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try(bar, parity)) return true;
+    if (*abort) return false;
+    if (clock64() - t0 > (1ll << 31)) {
+      *abort = code;
+      atomicCAS(&g_error, 0, code);
+      return false;
+    }
+  }
+}
+// The same for a whole warp: every lane polls, and all lanes take the same way out (the TMEM loads
+// and stores that follow are warp-collective).
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort, int code) {
+  const bool ok = mbar_wait(bar, parity, abort, code);
+  return __all_sync(0xffffffffu, ok);
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void umma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void umma_ts(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+               ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+      ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+        "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a tile whose rows are 128 bytes, 8-row groups 1024 bytes
+// apart, 16-byte chunks XOR-swizzled by the row (the 128-byte swizzle): start address, leading
+// and stride byte offsets in 16-byte units, descriptor version 1 (sm_100), layout type 2.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lead_bytes) {
+  return (uint64_t)((addr & 0x3ffffu) >> 4) | ((uint64_t)((lead_bytes >> 4) & 0x3fffu) << 16) |
+         ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor of kind::f16: fp32 accumulate, A and B both bf16 (1) or f16 (0), A K-major,
+// B K-major or MN-major, N / 8 and M / 16.
+__host__ __device__ constexpr uint32_t instr_desc(bool f16, bool b_mn_major, int n) {
+  return (1u << 4) | ((f16 ? 0u : 1u) << 7) | ((f16 ? 0u : 1u) << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+}
+
+struct Args {
+  __nv_bfloat16* out;
+  int64_t out_stride_tok, out_stride_head;
+  const __nv_bfloat16* q;
+  int64_t q_stride_tok, q_stride_head;
+  const uint8_t* k;
+  const uint8_t* v;
+  int64_t k_stride_block, k_stride_token, k_stride_head;   // bytes
+  int64_t v_stride_block, v_stride_token, v_stride_head;
+  int num_blocks;
+  const int* block_table;
+  int64_t table_stride;
+  int max_pages;
+  const int* seq_lens;
+  const int* q_start;
+  const int* work;
+  int num_q_heads, num_kv_heads, group, tiles_per_page;
+  float scale;
+};
+
+// A producer warp's copy of one 64-token block (K or V) into a ring slot: 64 rows x 16 chunks of
+// 16 bytes, 32 copies a lane. Rows at or past `kv_limit` are zero-filled, never read.
+__device__ __forceinline__ void fill_slot(const Args& a, uint32_t slot, const uint8_t* base, int64_t sb, int64_t st,
+                                          const int* table_row, int kv0, int kv_limit, int lane) {
+  // the block's four 16-token tiles: page id and offset of each, one lane a tile
+  int my_id = 0, my_sub = 0;
+  if (lane < 4) {
+    const int tile = kv0 / TILE_TOKENS + lane;
+    if (tile * TILE_TOKENS < kv_limit) {
+      const int page = min(tile / a.tiles_per_page, a.max_pages - 1);
+      my_id = min(max(__ldg(table_row + page), 0), a.num_blocks - 1);
+      my_sub = tile % a.tiles_per_page;
+    }
+  }
+  const int c = lane & 15, half = c >> 3, cc = c & 7;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int id = __shfl_sync(0xffffffffu, my_id, t), sub = __shfl_sync(0xffffffffu, my_sub, t);
+    const uint8_t* p = base + (int64_t)id * sb + (int64_t)(sub * TILE_TOKENS) * st + c * 16;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int r = t * 16 + it * 2 + (lane >> 4);                    // row of the block
+      const uint32_t dst = slot + half * HALF_BYTES_KV + r * 128 + ((cc ^ (r & 7)) << 4);
+      if (kv0 + r < kv_limit) cp_async16(dst, p + (int64_t)(it * 2 + (lane >> 4)) * st);
+      else asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(dst), "r"(0u) : "memory");
+    }
+  }
+}
+
+template <int GP, bool F16>
+__global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a) {
+  extern __shared__ uint8_t raw_smem[];
+  constexpr int T = ROWS / GP;                 // tokens of one query tile
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const uint32_t base = (smem_u32(raw_smem) + 1023u) & ~1023u;
+  uint8_t* gen = raw_smem + (base - smem_u32(raw_smem));
+  const uint32_t q_smem = base;                              // two query tiles
+  const uint32_t ring = base + 2 * Q_BYTES;
+  Bars* bars = reinterpret_cast<Bars*>(gen + 2 * Q_BYTES + NSLOT * SLOT_BYTES);
+  const uint32_t bars_u = base + 2 * Q_BYTES + NSLOT * SLOT_BYTES;
+#define HKB_BAR(field) (bars_u + (uint32_t)offsetof(Bars, field))
+  volatile int* abort = &bars->abort;
+
+  // ---- the work item ----
+  const int passes = a.group / GP;
+  const int kvh = blockIdx.y / passes;
+  const int hbase = kvh * a.group + (blockIdx.y % passes) * GP;
+  const int req = __ldg(a.work + 2 * blockIdx.x), row0 = __ldg(a.work + 2 * blockIdx.x + 1);
+  const int q0 = __ldg(a.q_start + req), q_len = __ldg(a.q_start + req + 1) - q0;
+  const int seq_len = __ldg(a.seq_lens + req);
+  const int ctx = seq_len - q_len;
+  if (q_len <= 0 || row0 >= q_len || ctx < 0) return;        // uniform: before any barrier or allocation
+  // keys tile t may attend to, and its blocks (tile 1 may be empty)
+  int nblk[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int first = row0 + t * T;
+    const int lim = first < q_len ? min(seq_len, ctx + min(first + T, q_len)) : 0;
+    nblk[t] = (lim + KVB - 1) / KVB;
+  }
+  const int kv_limit = min(seq_len, ctx + min(row0 + 2 * T, q_len));
+  const int n = max(nblk[0], nblk[1]);
+
+  // ---- set-up: barriers, TMEM, the query tiles ----
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NSLOT; ++i) { mbar_init(HKB_BAR(full) + 8 * i, 32); mbar_init(HKB_BAR(empty) + 8 * i, 1); }
+    for (int i = 0; i < 4; ++i) { mbar_init(HKB_BAR(s_full) + 8 * i, 1); mbar_init(HKB_BAR(p_full) + 8 * i, ROWS); }
+    for (int i = 0; i < 2; ++i) mbar_init(HKB_BAR(o_done) + 8 * i, 1);
+    bars->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == MMA_WARP) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(HKB_BAR(tmem_base)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  // query rows: row r of tile t is head r / T, token r % T of the tile; rows past the request are zeros
+  for (int x = threadIdx.x; x < 2 * ROWS * 16; x += THREADS) {
+    const int t = x / (ROWS * 16), r = (x / 16) % ROWS, c = x % 16;
+    const int tok = row0 + t * T + r % T;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (tok < q_len)
+      v = __ldg(reinterpret_cast<const uint4*>(a.q + (int64_t)(q0 + tok) * a.q_stride_tok +
+                                               (int64_t)(hbase + r / T) * a.q_stride_head + c * 8));
+    const uint32_t dst = q_smem + t * Q_BYTES + (c >> 3) * HALF_BYTES_Q + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp < SOFTMAX_WARPS) {
+    // ================= softmax: thread = one query row of tile g =================
+    const int g = warp >> 2, row = (warp & 3) * 32 + lane;
+    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const int tok = row0 + g * T + row % T, hq = hbase + row / T;
+    const bool valid = tok < q_len;
+    const int pos = ctx + tok;                              // the last key this row sees
+    const float qs = a.scale * LOG2E;
+    float m = -INFINITY, l = 0.f;
+    const int nb = nblk[g];
+    bool ok = true;
+    for (int j = 0; j < nb && ok; ++j) {
+      const int b = j & 1;
+      ok = warp_wait(HKB_BAR(s_full) + 8 * (g * 2 + b), (j >> 1) & 1, abort, 1);
+      if (!ok) break;
+      tc_fence_after();
+      float s[KVB];
+      {
+        float lo[32], hi[32];
+        tmem_ld32(lane_addr + s_col(g, b), lo);
+        tmem_ld32(lane_addr + s_col(g, b) + 32, hi);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { s[i] = lo[i]; s[32 + i] = hi[i]; }
+      }
+      const int kv0 = j * KVB;
+      if (!valid || kv0 + KVB - 1 > pos) {                   // the diagonal block, or a row past the request
+#pragma unroll
+        for (int i = 0; i < KVB; ++i)
+          if (!valid || kv0 + i > pos) s[i] = -INFINITY;
+      }
+      float mx = s[0];
+#pragma unroll
+      for (int i = 1; i < KVB; ++i) mx = fmaxf(mx, s[i]);
+      mx *= qs;                                              // qs > 0
+      // lazy reference: it moves only when a block's maximum exceeds it by 2^8 (P <= 256 fits 16 bits)
+      const bool need = mx > m + 8.f;
+      const bool any_need = __any_sync(0xffffffffu, need);
+      float alpha = 1.f;
+      if (need) {
+        alpha = fast_exp2(m - mx);                           // m = -inf the first time: 0
+        m = mx;
+      }
+      const float off = (m == -INFINITY) ? 0.f : -m;
+      uint32_t p[32];
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float p0 = fast_exp2(fmaf(s[2 * i], qs, off)), p1 = fast_exp2(fmaf(s[2 * i + 1], qs, off));
+        sum += p0 + p1;
+        if (F16) { const __half2 h = __floats2half2_rn(p0, p1); p[i] = *reinterpret_cast<const uint32_t*>(&h); }
+        else { const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1); p[i] = *reinterpret_cast<const uint32_t*>(&h); }
+      }
+      l = l * alpha + sum;
+      if (j > 0) {
+        // the tile's previous product has landed: O may be touched, and stays untouched until P arrives
+        ok = warp_wait(HKB_BAR(o_done) + 8 * g, (j - 1) & 1, abort, 2);
+        if (!ok) break;
+        tc_fence_after();
+        if (any_need) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            float o[32];
+            uint32_t w[32];
+            tmem_ld32(lane_addr + o_col(g) + c0, o);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(o[i] * alpha);
+            tmem_st32(lane_addr + o_col(g) + c0, w);
+          }
+        }
+      }
+      tmem_st32(lane_addr + s_col(g, b), p);                  // P over the first 32 columns of the scores just read
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(HKB_BAR(p_full) + 8 * (g * 2 + b));
+    }
+    if (ok && nb > 0) {
+      ok = warp_wait(HKB_BAR(o_done) + 8 * g, (nb - 1) & 1, abort, 3);
+      if (ok) {
+        tc_fence_after();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16* orow = a.out + (int64_t)(q0 + tok) * a.out_stride_tok + (int64_t)hq * a.out_stride_head;
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          float o[32];
+          tmem_ld32(lane_addr + o_col(g) + c0, o);
+          if (valid) {
+            uint32_t w[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              if (F16) { const __half2 h = __floats2half2_rn(o[2 * i] * inv, o[2 * i + 1] * inv); w[i] = *reinterpret_cast<const uint32_t*>(&h); }
+              else { const __nv_bfloat162 h = __floats2bfloat162_rn(o[2 * i] * inv, o[2 * i + 1] * inv); w[i] = *reinterpret_cast<const uint32_t*>(&h); }
+            }
+            uint32_t* dst = reinterpret_cast<uint32_t*>(orow + c0);   // rows are 4-byte aligned at least
+#pragma unroll
+            for (int i = 0; i < 16; ++i) dst[i] = w[i];
+          }
+        }
+      }
+    }
+  } else if (warp == MMA_WARP) {
+    // ================= MMA issue: one thread; the whole warp keeps step at the barriers =================
+    constexpr uint32_t IDESC_S = instr_desc(F16, false, KVB), IDESC_PV = instr_desc(F16, true, D);
+    bool ok = true;
+    auto scores = [&](int j) {    // S_t(j) = Q_t K_j^T for the tiles that reach block j
+      const int slot = (2 * j) % NSLOT;
+      ok = warp_wait(HKB_BAR(full) + 8 * slot, ((2 * j) / NSLOT) & 1, abort, 4);
+      if (!ok) return;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t kaddr = ring + slot * SLOT_BYTES;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (j >= nblk[t]) continue;
+          const uint32_t d = tmem + s_col(t, j & 1);
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)       // 16 dims = 32 bytes a step inside the 128-byte row
+              umma_ss(d, smem_desc(q_smem + t * Q_BYTES + h * HALF_BYTES_Q + ks * 32, 16),
+                      smem_desc(kaddr + h * HALF_BYTES_KV + ks * 32, 16), IDESC_S, (h | ks) ? 1u : 0u);
+          tc_commit(HKB_BAR(s_full) + 8 * (t * 2 + (j & 1)));
+        }
+        tc_commit(HKB_BAR(empty) + 8 * slot);   // the K block is free once these products are done
+      }
+      __syncwarp();
+    };
+    scores(0);
+    for (int j = 0; j < n && ok; ++j) {
+      if (j + 1 < n) scores(j + 1);
+      if (!ok) break;
+      const int slot = (2 * j + 1) % NSLOT;
+      ok = warp_wait(HKB_BAR(full) + 8 * slot, ((2 * j + 1) / NSLOT) & 1, abort, 5);
+      if (!ok) break;
+      const uint32_t vaddr = ring + slot * SLOT_BYTES;
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (j >= nblk[t]) continue;
+        ok = warp_wait(HKB_BAR(p_full) + 8 * (t * 2 + (j & 1)), (j >> 1) & 1, abort, 6);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)         // 16 tokens a step: 8 TMEM columns of P, 16 rows of V
+            umma_ts(tmem + o_col(t), tmem + s_col(t, j & 1) + ks * 8,
+                    smem_desc(vaddr + ks * 16 * 128, HALF_BYTES_KV), IDESC_PV, (j | ks) ? 1u : 0u);
+          tc_commit(HKB_BAR(o_done) + 8 * t);
+        }
+        __syncwarp();
+      }
+      if (ok && lane == 0) tc_commit(HKB_BAR(empty) + 8 * slot);
+      __syncwarp();
+    }
+  } else {
+    // ================= producers: warp K_WARP fills the K blocks, warp V_WARP the V blocks =================
+    const int which = warp - K_WARP;   // 0: K, 1: V
+    const uint8_t* src = (which ? a.v + (int64_t)kvh * a.v_stride_head : a.k + (int64_t)kvh * a.k_stride_head);
+    const int64_t sb = which ? a.v_stride_block : a.k_stride_block, st = which ? a.v_stride_token : a.k_stride_token;
+    const int* table_row = a.block_table + (int64_t)req * a.table_stride;
+    bool ok = true;
+    auto publish = [&](int j) {        // block j's copies of this lane have landed: hand the slot over
+      fence_async_smem();
+      mbar_arrive(HKB_BAR(full) + 8 * ((2 * j + which) % NSLOT));
+    };
+    int issued = 0;
+    for (int j = 0; j < n && ok; ++j) {
+      const int use = 2 * j + which, slot = use % NSLOT, lap = use / NSLOT;
+      if (lap > 0) ok = warp_wait(HKB_BAR(empty) + 8 * slot, (lap - 1) & 1, abort, 7);
+      if (!ok) break;
+      fill_slot(a, ring + slot * SLOT_BYTES, src, sb, st, table_row, j * KVB, kv_limit, lane);
+      cp_async_commit();
+      ++issued;
+      if (j >= LAG - 1) { cp_async_wait<LAG - 1>(); publish(j - (LAG - 1)); }
+    }
+    // drain: whatever was issued lands before the CTA leaves, and is handed over if all is well
+    cp_async_wait<0>();
+    if (ok)
+      for (int j = max(0, issued - (LAG - 1)); j < issued; ++j) publish(j);
+  }
+
+  // ---- wind-down ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  }
+#undef HKB_BAR
+}
+
+}  // namespace tc
+}  // namespace hkb

@@ -107,7 +107,8 @@ struct WalkMMA {
     }
   }
 
-  template <bool LAST>
+  // ABL: stages left out for attribution runs (hkb_paged_decode_ablate), a mask of ABL_* bits; 0 = the walk.
+  template <bool LAST, int ABL = 0>
   __device__ static __forceinline__ void tile(uint32_t ktile, uint32_t vtile, int tok0, int seq_len, int lane,
                                               float qs, const uint32_t (&qb)[NT][KD][2], float (&m)[NT][2],
                                               float (&l)[NT][2], float (&o)[NT][KD][4]) {
@@ -115,9 +116,9 @@ struct WalkMMA {
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) sc[nt][i] = 0.f;
+      for (int i = 0; i < 4; ++i) sc[nt][i] = (ABL & ABL_QK) ? __uint_as_float(ktile + i) * 1e-30f : 0.f;
     // S^T = K Q^T: A = the K tile (tokens x 16 dims), B = Q^T
-    {
+    if (!(ABL & ABL_QK)) {
       const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
       for (int kc = 0; kc < KD; ++kc) {
@@ -131,6 +132,11 @@ struct WalkMMA {
     uint32_t pb[NT][2];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
+      if (ABL & ABL_SOFTMAX) {   // no maximum, no exponential, no sum: the scores go on as they are
+        pb[nt][0] = movmatrix_trans(pack16x2<F16>(sc[nt][0], sc[nt][1]));
+        pb[nt][1] = movmatrix_trans(pack16x2<F16>(sc[nt][2], sc[nt][3]));
+        continue;
+      }
       // scores stay unscaled: the exponent is exp2(s * qs - m) in one fma, m kept in scaled units
       if (LAST) {
         if (tA >= seq_len) { sc[nt][0] = -INFINITY; sc[nt][1] = -INFINITY; }
@@ -167,7 +173,7 @@ struct WalkMMA {
       pb[nt][1] = movmatrix_trans(pack16x2<F16>(p2, p3));
     }
     // O^T += V^T P^T: A = V^T (16 dims x tokens), read transposed from the row-major V tile
-    {
+    if (!(ABL & ABL_PV)) {
       const int r = (lane & 7) + (lane >> 4) * 8;
 #pragma unroll
       for (int dt = 0; dt < KD; ++dt) {
@@ -176,6 +182,9 @@ struct WalkMMA {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) mma16<F16>(o[nt][dt], a, pb[nt]);
       }
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) o[nt][0][0] += __uint_as_float(pb[nt][0] ^ pb[nt][1]) * 1e-30f;   // keeps P alive
     }
   }
 
@@ -222,6 +231,7 @@ struct WalkMMA {
     }
   }
 
+  template <int ABL = 0>
   __device__ static __forceinline__ void step(State& st, uint32_t warp_smem, int stage_idx, int tok0, int seq_len,
                                               bool last, int lane, float qs) {
     const uint32_t stage = warp_smem + stage_idx * STAGE_BYTES;
@@ -236,9 +246,9 @@ struct WalkMMA {
     if (last) {
       scrub_tail(vtile, tok0, seq_len, lane);
       __syncwarp();
-      tile<true>(ktile, vtile, tok0, seq_len, lane, qs, st.qb, st.m, st.l, st.o);
+      tile<true, ABL>(ktile, vtile, tok0, seq_len, lane, qs, st.qb, st.m, st.l, st.o);
     } else {
-      tile<false>(ktile, vtile, tok0, seq_len, lane, qs, st.qb, st.m, st.l, st.o);
+      tile<false, ABL>(ktile, vtile, tok0, seq_len, lane, qs, st.qb, st.m, st.l, st.o);
     }
   }
 

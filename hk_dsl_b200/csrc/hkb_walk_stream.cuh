@@ -56,6 +56,7 @@ struct WalkStream {
   static constexpr int BASE_BYTES = (STREAM_MAX_SEQS + 2) * 4;
   static constexpr int SMEM_BYTES = RINGS * P::RING_SMEM + BASE_BYTES;
 
+  template <int ABL = 0>
   __device__ static __forceinline__ void run(const DecodeArgs& a, uint8_t* smem, int num_seqs) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ring_id = warp / WPR, sub = warp % WPR;     // which ring, and which of its warps
@@ -175,7 +176,7 @@ struct WalkStream {
       if (fresh) {
         ids.row = a.block_table + (int64_t)seq_l * a.table_stride;
         ids.t_hi = min(base[seq_l + 1], g_hi) - base[seq_l];
-        ids.init(t, lane);
+        if (!(ABL & ABL_PAGE)) ids.init(t, lane);
         fresh = false;
       }
       if (WPR == 1 && a.new_k && t == base[seq_l + 1] - base[seq_l] - 1) {
@@ -202,7 +203,11 @@ struct WalkStream {
         __syncwarp();
       }
       const uint32_t stage = ring + stage_idx * P::STAGE_BYTES;
-      if (WPR == 1) ld.issue(stage, t, ids.get(t, lane), lane);
+      if (ABL & (ABL_PAGE | ABL_KLOAD | ABL_VLOAD)) {      // attribution builds: no table read, or one of the copies left out
+        const int id = (ABL & ABL_PAGE) ? gl % a.num_blocks : ids.get(t, lane);
+        if (!(ABL & ABL_KLOAD)) ld.issue_one(stage, t, id, lane, 0);
+        if (!(ABL & ABL_VLOAD)) ld.issue_one(stage, t, id, lane, 1);
+      } else if (WPR == 1) ld.issue(stage, t, ids.get(t, lane), lane);
       else ld.issue_one(stage, t, ids.get(t, lane), lane, sub);
       ++gl;
     };
@@ -256,7 +261,10 @@ struct WalkStream {
         if (nh > 0) P::begin(st, a, row, hq0, nh, lane, qs);
       }
       const int t = g - seq_base;
-      if (nh > 0) P::step(st, ring, sc, t * TILE_TOKENS, seq_len, t == n_tiles - 1, lane, qs);
+      if (nh > 0) {
+        if constexpr (ABL != 0) P::template step<ABL>(st, ring, sc, t * TILE_TOKENS, seq_len, t == n_tiles - 1, lane, qs);
+        else P::step(st, ring, sc, t * TILE_TOKENS, seq_len, t == n_tiles - 1, lane, qs);
+      }
       sc = sc + 1 == P::STAGES ? 0 : sc + 1;
       sl = sl + 1 == P::STAGES ? 0 : sl + 1;
     }
@@ -278,6 +286,13 @@ template <class P, int RINGS>
 __global__ void __launch_bounds__(RINGS * P::WPR * 32, P::MIN_CTAS) walk_stream_kernel(const DecodeArgs a, int num_seqs) {
   extern __shared__ __align__(128) uint8_t hkb_smem[];
   WalkStream<P, RINGS>::run(a, hkb_smem, num_seqs);
+}
+
+// The same kernel with stages left out (ABL_* mask), for attribution measurements only.
+template <class P, int RINGS, int ABL>
+__global__ void __launch_bounds__(RINGS * P::WPR * 32, P::MIN_CTAS) walk_stream_ablated_kernel(const DecodeArgs a, int num_seqs) {
+  extern __shared__ __align__(128) uint8_t hkb_smem[];
+  WalkStream<P, RINGS>::template run<ABL>(a, hkb_smem, num_seqs);
 }
 
 }  // namespace hkb

@@ -362,11 +362,11 @@ def decode_step_record(rec_out: torch.Tensor, rec_lse: torch.Tensor, query: torc
 # --------------------------------------------------------------------------------------
 
 def prefill_tile_rows(num_q_heads: int, num_kv_heads: int) -> int:
-    """Query rows one work item of the prefill kernel covers: 16 x 8 / GP, GP the largest of
+    """Query tokens one work item of the prefill kernels covers: 256 rows / GP, GP the largest of
     8, 4, 2, 1 dividing the GQA group (hkb_prefill_tile_rows)."""
     g = num_q_heads // num_kv_heads
     gp = 8 if g % 8 == 0 else 4 if g % 4 == 0 else 2 if g % 2 == 0 else 1
-    return 16 * (8 // gp)
+    return 256 // gp
 
 
 def work_list(reqs, tile_rows: int, device, seq_lens=None) -> torch.Tensor:

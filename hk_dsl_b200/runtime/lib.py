@@ -50,6 +50,10 @@ SIGNATURES = {
                                  c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                  c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                  c_void_p]),
+    "hkb_paged_decode_ablate": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, CacheT, CacheT,
+                                        c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                        c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                        c_int, c_void_p]),
     "hkb_paged_decode_static": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, CacheT, CacheT,
                                         c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                         c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p]),
@@ -68,6 +72,8 @@ SIGNATURES = {
                                   c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                   c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p]),
     "hkb_prefill_tile_rows": (c_int, [c_int, c_int]),
+    "hkb_prefill_uses_tcgen05": (c_int, [c_int, c_int]),
+    "hkb_prefill_tc_error": (c_int, [c_int]),
     "hkb_merge": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p,
                           c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "hkb_walk_uses_mma": (c_int, [c_int, c_int]),

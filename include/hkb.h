@@ -142,6 +142,28 @@ int hkb_paged_decode(void* out, int64_t out_stride_tok, int64_t out_stride_head,
                      void* stream);
 
 /*
+ * The walk of hkb_paged_decode with stages left out, for attribution measurements: time it with
+ * one stage missing and the difference to the whole walk is what the stage costs. `ablate` is a
+ * mask: 1 page-table reads, 2 the K copies, 4 the V copies, 8 the q.K products, 16 the softmax
+ * (maximum, exponential, sum), 32 the p.V products; the masks built are each bit alone, 2|4 (no
+ * copies) and 8|16|32 (no math); 0 is hkb_paged_decode itself. Only the headline shape is built
+ * (head_dim 128, bf16 cache, a GQA group of 4 to 8, num_splits > 1): anything else answers
+ * HKB_ERR_UNSUPPORTED. What it writes into part_out / part_lse is meaningless.
+ *
+ * Replaces: the `ablate=` switches of the reference's fused walk (python/hk/ops/paged.py:524-533)
+ * and the table tools/hk-bench/paged_attrib.py builds from them.
+ */
+int hkb_paged_decode_ablate(void* out, int64_t out_stride_tok, int64_t out_stride_head,
+                            const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                            hkb_cache_t k_cache, hkb_cache_t v_cache,
+                            const int32_t* block_table, int64_t table_stride, int max_pages,
+                            const int32_t* seq_lens, const int32_t* q_start,
+                            int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                            int block_size, float scale, int kv_dtype,
+                            const float* k_scale, const float* v_scale,
+                            int num_splits, float* part_out, float* part_lse, int ablate, void* stream);
+
+/*
  * The LSE merge: out[i, h, :] = sum_p w_p * part_out[p, i, h, :] / sum_p w_p with
  * w_p = exp(part_lse[p, i, h] - max_p part_lse). A part whose lse is -inf is
  * never read (its memory may hold anything); if every part is -inf the answer is
@@ -267,9 +289,21 @@ int hkb_decode_step_record(float* rec_out, float* rec_lse,
 /* Bytes of the arrival counters hkb_decode_step takes. */
 size_t hkb_arrivals_bytes(int num_seqs, int num_kv_heads);
 
-/* Query rows one work item of hkb_paged_prefill covers (16..128, by GQA group); 0 if the
- * head counts are not a valid GQA shape. */
+/* Query tokens one work item of hkb_paged_prefill covers: 256 rows divided by the heads of the
+ * GQA group a CTA serves (32 for a group of 8, 64 for 4, 128 for 2, 256 for 1); 0 if the head
+ * counts are not a valid GQA shape. */
 int hkb_prefill_tile_rows(int num_q_heads, int num_kv_heads);
+
+/* 1 if hkb_paged_prefill runs its tcgen05 / tensor-memory kernel for this head size and cache
+ * type (head_dim 128, bf16 or fp16), 0 if the mma.sync kernel (other head sizes, fp8 caches, or
+ * HKB_PREFILL_MMA_SYNC=1 in the environment, the comparison arm). Like the reference, which picks
+ * its contraction form per architecture and shape (python/hk/ops/paged_prefill.py:59-120). */
+int hkb_prefill_uses_tcgen05(int head_dim, int kv_dtype);
+
+/* The tensor-memory prefill kernel bounds every wait on a barrier; a wait that ran out leaves a
+ * code here (0: none; 1..7: which wait) instead of hanging the GPU. Reads the word back from the
+ * current device (this synchronises); `clear` != 0 resets it. -1 if the read failed. */
+int hkb_prefill_tc_error(int clear);
 
 /*
  * Bytes of the scratch array built into the library for hkb_paged_decode_static (below).

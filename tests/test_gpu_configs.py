@@ -1,6 +1,8 @@
 """The five measured configurations: parity against the float64 oracle where the oracle
 finishes in seconds (c1 in full; c2-c5 on a slice of their sequences with their real shapes
-and dtypes), and at FULL size through properties that need no oracle: a cache of V == 1
+and dtypes), EVERY sequence of the full-size c2 / c3 / c4 batches against the oracle's fp32
+evaluation, one full 131072-token c5 sequence against the float64 oracle, and at FULL size
+through properties that need no oracle: a cache of V == 1
 answers exactly 1, split and unsplit walks agree, a kv-head shard equals the same heads of the
 whole, a KV split over emulated ranks folds back to the single-GPU answer, the cache write is
 an exact round trip, and a step leaves every other slot of the cache untouched."""
@@ -166,3 +168,111 @@ def test_c5_kv_split_over_emulated_ranks_folds_to_the_single_gpu_answer():
     assert (out.float() - whole).abs().mean().item() < 2e-3
     want = _oracle(st, [1])
     orc.check(out[1:2], want[1:2])
+
+
+def _whole_batch_fp32(st):
+    """The oracle's vectorised fp32 evaluation of every sequence of the step, on the host."""
+    ks = st.k_scale.cpu() if st.k_scale is not None else None
+    vs = st.v_scale.cpu() if st.v_scale is not None else None
+    return orc.paged_decode_ref_fp32(st.query.cpu(), st.k_caches[0].cpu(), st.v_caches[0].cpu(), st.block_table.cpu(),
+                                     st.seq_lens.cpu(), st.scale, ks, vs)
+
+
+@pytest.mark.parametrize("name", ["c2", "c3", "c4"])
+def test_every_sequence_of_the_full_batch_against_the_oracle(name):
+    """The whole batch at its full size (64 / 128 / 256 sequences), the step as the bench runs it
+    (`decode_step`: the walk writes the new rows, then the merge), every output row held to the
+    oracle: max-abs 2e-2, mean-abs 2e-3 and the reference's 4-ulp row bound. The fp32 oracle's own
+    error (~1e-6) is far below a bf16 ulp, so it stands in for the float64 one at this size; the
+    shortest, median and longest sequence are also checked against float64."""
+    spec = W.CONFIGS[name]
+    st = W.build_step(spec, "cuda")
+    paged = _paged()
+    for splits in (None, 1):
+        out = torch.full_like(st.out, 7.0)
+        if splits is None:
+            paged.decode_step(out, st.query, st.key, st.value, st.k_caches[0], st.v_caches[0], st.slot_mapping,
+                              st.block_table, st.seq_lens, st.scale, spec.kv_cache_dtype, st.k_scale, st.v_scale)
+        else:
+            out = _decode(st, 1)
+        torch.cuda.synchronize()
+        if splits is None:
+            want = _whole_batch_fp32(st)       # after the step: the cache holds the new rows
+        orc.check(out, want)
+        mx, mean = orc.check_baseline(out, want)
+    n = len(st.lens)
+    order = sorted(range(n), key=lambda i: (st.lens[i], i))
+    few = sorted({order[0], order[n // 2], order[-1]})
+    want64 = _oracle(st, few)
+    orc.check(out[few], want64[few])
+    if spec.fp8:       # the config's scales are amax / 448 of what was quantised: the largest value maps to +-448
+        for cache, scale in ((st.k_caches[0], st.k_scale), (st.v_caches[0], st.v_scale)):
+            top = cache.view(torch.uint8).cpu().view(torch.float8_e4m3fn).float().abs().max().item()
+            assert top == 448.0 and 5.0 / 448 < scale.item() < 7.0 / 448
+
+
+@pytest.mark.parametrize("splits", [None, 256])
+def test_c5_a_full_131072_token_sequence_against_the_float64_oracle(splits):
+    """What c5 is about: 8192 tiles of one sequence through every slot the plan gives it (and
+    through all 256, where the wide merge folds them), compared with float64 for the query heads
+    of two kv heads (the other heads run the same code on other data)."""
+    spec = W.CONFIGS["c5"]
+    st = W.build_step(spec, "cuda", lens=[131072])
+    paged = _paged()
+    out = torch.empty_like(st.out)
+    paged.decode_step(out, st.query, st.key, st.value, st.k_caches[0], st.v_caches[0], st.slot_mapping,
+                      st.block_table, st.seq_lens, st.scale, spec.kv_cache_dtype, num_splits=splits)
+    torch.cuda.synchronize()
+    g = spec.q_heads // spec.kv_heads
+    pages = st.block_table[0, : 131072 // spec.block_size].long()
+    q = st.query.cpu()
+    for kh in (0, spec.kv_heads - 1):
+        kk = st.k_caches[0][pages][:, :, kh].reshape(-1, spec.head_dim).cpu()
+        vv = st.v_caches[0][pages][:, :, kh].reshape(-1, spec.head_dim).cpu()
+        hs = slice(kh * g, (kh + 1) * g)
+        want = orc.softmax_v64(q[0, hs], kk, vv, st.scale)
+        orc.check(out[0, hs], want)
+        orc.check_baseline(out[0, hs], want)
+
+
+def test_kv_split_step_writes_the_new_rows_on_the_rank_that_holds_them():
+    """A KV-split step as two emulated ranks run one after the other on one GPU: the rank that holds
+    the sequences' last position passes the step's new rows and its walk writes them (the same bits
+    the cache-write kernel writes); the other passes none. The folded records equal the one-GPU
+    step's answer within tolerance and the float64 oracle's within the row bound."""
+    from hk_dsl_b200.ops import paged_dist
+
+    paged = _paged()
+    spec = W.CONFIGS["c5"]
+    lens = [4096 + 33, 2048]
+    st = W.build_step(spec, "cuda", lens=lens)
+    ref = W.build_step(spec, "cuda", lens=lens)          # the same seeded tensors, for the separate launches
+    paged.reshape_and_cache(ref.key, ref.value, ref.k_caches[0], ref.v_caches[0], ref.slot_mapping, "auto")
+    whole = _decode(ref, None).float()
+    world, bs = 2, spec.block_size
+    n, hq, d = st.query.shape
+    decs = [paged_dist.SplitKVDecoder(n, hq, st.kv_heads, d, "cuda", local_splits=4) for _ in range(world)]
+    for r, dec in enumerate(decs):
+        ranges = [paged_dist.kv_range(s, world, r, bs) for s in st.lens]
+        local = torch.tensor([hi - lo for lo, hi in ranges], dtype=torch.int32, device="cuda")
+        table = torch.zeros_like(st.block_table)
+        slots = torch.full_like(st.slot_mapping, -1)
+        for i, (lo, hi) in enumerate(ranges):
+            p0, p1 = lo // bs, -(-hi // bs)
+            table[i, : p1 - p0] = st.block_table[i, p0:p1]
+            if hi == st.lens[i] and hi > lo:      # this rank holds the last position: the new row is its to write
+                slots[i] = st.slot_mapping[i]
+        new = dict(key=st.key, value=st.value, slot_mapping=slots) if (slots >= 0).any() else {}
+        dec.local_partial(st.query, st.k_caches[0], st.v_caches[0], table, local, st.scale, **new)
+    torch.cuda.synchronize()
+    assert torch.equal(st.k_caches[0].view(torch.int16), ref.k_caches[0].view(torch.int16))
+    assert torch.equal(st.v_caches[0].view(torch.int16), ref.v_caches[0].view(torch.int16))
+    last = decs[0]
+    last.world = world
+    last.all = torch.cat([dec.mine for dec in decs])
+    out = torch.empty_like(st.out)
+    last.merge(out)
+    torch.cuda.synchronize()
+    assert (out.float() - whole).abs().max().item() < 2e-2
+    want = _oracle(ref)
+    orc.check(out, want)

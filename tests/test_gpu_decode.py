@@ -373,3 +373,46 @@ def test_hybrid_page_sizes_with_nan_past_the_end(page, group, h_kv, fp8):
     c = _case(lens, h_kv=h_kv, group=group, page=page, seed=page, nan_tail=not fp8, fp8=fp8, spare=1)
     _check(_run(c, splits=4), _reference(c))
     _check(_run(c, splits=1), _reference(c))
+
+
+def test_read_probe_runs_and_reads_at_a_plausible_rate():
+    """hkb_hbm_read_probe through the C ABI: it launches, touches nothing but its sink, and a 256 MB
+    read lands between 1 and 12 TB/s on an HBM3e part (a sanity band, not a benchmark)."""
+    from hk_dsl_b200.runtime import lib as hkb
+
+    lib = hkb.load()
+    nbytes = 256 << 20
+    buf = torch.full((nbytes + 64,), 0x5a, dtype=torch.uint8, device="cuda")
+    sink = torch.zeros(4, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    best = 0.0
+    for ctas, inflight in ((2, 4), (4, 8)):
+        for _ in range(3):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            assert lib.hkb_hbm_read_probe(buf.data_ptr(), nbytes, ctas, inflight, sink.data_ptr(), st) == 0
+            b.record()
+            torch.cuda.synchronize()
+            best = max(best, nbytes / (a.elapsed_time(b) * 1e-3) / 1e9)
+    assert 1000.0 < best < 12000.0, best
+    assert (buf[nbytes:] == 0x5a).all() and (sink == 0).all()
+    assert lib.hkb_hbm_read_probe(buf.data_ptr(), nbytes, 2, 3, sink.data_ptr(), st) == -9       # loads in flight: 1, 2, 4, 8, 16
+
+
+def test_the_environment_switches_are_read_at_every_call(monkeypatch):
+    """`HKB_MMA_MIN_GROUP` moves the worker bound between two calls of one process."""
+    from hk_dsl_b200.runtime import lib as hkb
+
+    lib = hkb.load()
+    monkeypatch.delenv("HKB_MMA_MIN_GROUP", raising=False)
+    assert lib.hkb_walk_uses_mma(4, 0) == 1 and lib.hkb_walk_uses_mma(3, 0) == 0
+    monkeypatch.setenv("HKB_MMA_MIN_GROUP", "8")
+    assert lib.hkb_walk_uses_mma(4, 0) == 0 and lib.hkb_walk_uses_mma(8, 1) == 1 and lib.hkb_walk_uses_mma(4, 1) == 0
+    c = _case([700, 33, 1500], group=4, h_kv=2, seed=3)
+    want = _reference(c)
+    _check(_run(c, splits=4), want)               # the CUDA-core worker
+    monkeypatch.setenv("HKB_FIXED_SPLITS", "1")
+    _check(_run(c, splits=4), want)               # on the fixed-split grid
+    monkeypatch.delenv("HKB_FIXED_SPLITS")
+    monkeypatch.delenv("HKB_MMA_MIN_GROUP")
+    _check(_run(c, splits=4), want)               # the default worker again

@@ -161,3 +161,47 @@ def test_fp8_cache_against_the_dequantised_oracle(group):
     torch.cuda.synchronize()
     orc.check(out, want)
     orc.check_baseline(out, want)
+
+
+def test_which_kernel_runs_and_that_no_wait_ran_out(monkeypatch):
+    """head_dim 128 on a 16-bit cache runs the tcgen05 / tensor-memory kernel, everything else (and
+    HKB_PREFILL_MMA_SYNC=1) the mma.sync one; both give the oracle's answer on the same inputs and
+    each other's within two bf16 ulps of the row maximum; the tensor-memory kernel's bounded waits
+    left no error code behind -- in this test or in any that ran before it in this process."""
+    from hk_dsl_b200.runtime import lib as hkb
+
+    lib = hkb.load()
+    monkeypatch.delenv("HKB_PREFILL_MMA_SYNC", raising=False)
+    assert lib.hkb_prefill_uses_tcgen05(128, hkb.KV_BF16) == 1 and lib.hkb_prefill_uses_tcgen05(128, hkb.KV_F16) == 1
+    assert lib.hkb_prefill_uses_tcgen05(128, hkb.KV_FP8_E4M3) == 0 and lib.hkb_prefill_uses_tcgen05(64, hkb.KV_BF16) == 0
+    reqs = [(0, 700), (900, 300), (17, 1), (2048, 130)]
+    new, want, _ = _run(reqs, h_kv=2, group=4, seed=11)
+    orc.check(new, want)
+    orc.check_baseline(new, want)
+    monkeypatch.setenv("HKB_PREFILL_MMA_SYNC", "1")
+    assert lib.hkb_prefill_uses_tcgen05(128, hkb.KV_BF16) == 0
+    old, _, _ = _run(reqs, h_kv=2, group=4, seed=11)
+    orc.check(old, want)
+    assert orc.ulps(new, old.float()) < 2.0
+    monkeypatch.delenv("HKB_PREFILL_MMA_SYNC")
+    assert lib.hkb_prefill_tc_error(0) == 0
+
+
+@pytest.mark.parametrize("group,h_kv", [(1, 2), (2, 2), (4, 8), (8, 1), (16, 1), (6, 2)])
+def test_tensor_memory_kernel_tile_shapes(group, h_kv):
+    """Every way the 256 rows of a work item divide into tokens x heads (a group of 8 or 16: 32 tokens,
+    4: 64, 2 or 6: 128, 1: 256), with a cached prefix, a chunk that ends inside the first query tile and
+    one that ends inside the second."""
+    from hk_dsl_b200.runtime import lib as hkb
+
+    got, want, _ = _run([(100, 40), (0, 290), (515, 70), (64, 3)], h_kv=h_kv, group=group, seed=group)
+    orc.check(got, want)
+    assert hkb.load().hkb_prefill_tc_error(0) == 0
+
+
+def test_tensor_memory_kernel_long_prompt_and_big_pages():
+    """A 5000-token prompt (79 key blocks: the ring of slots laps ten times) and pages of 64 tokens."""
+    got, want, _ = _run([(0, 5000)], h_kv=1, group=4, seed=3)
+    orc.check(got, want)
+    got, want, _ = _run([(300, 500), (0, 129)], h_kv=2, group=4, seed=4, page=64)
+    orc.check(got, want)

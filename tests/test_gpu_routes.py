@@ -222,6 +222,26 @@ def test_torch_ops_surface():
     torch.ops.hk.paged_merge_d128_s4(ld, out4, o_part, ml_part)
     orc.check(out4.view(n, hq, d), want)
 
+    # the same names on a float16 cache (a model served in float16) ...
+    out16 = torch.empty(n, 8, 4, d, device="cuda", dtype=torch.float16)
+    walk(qd.half().view(n, 8, 4, d), kd.half(), vd.half(), td, ld, out16, o_part, ml_part)
+    merge(ld, out16, o_part, ml_part)
+    want16 = orc.paged_decode_ref(q.half(), k.half().transpose(1, 2), v.half().transpose(1, 2), table, lens_t)
+    orc.check(out16.view(n, hq, d), want16)
+    # ... an fp8 cache is refused by name (the reference's schema has no scales); the flat op takes it
+    k8 = orc.quantize_fp8(k, torch.tensor([0.02])).cuda()
+    v8 = orc.quantize_fp8(v, torch.tensor([0.02])).cuda()
+    with pytest.raises(TypeError, match="hk::paged_attention_decode"):
+        walk(qd.view(n, 8, 4, d), k8, v8, td, ld, out4, o_part, ml_part)
+    s8 = torch.full((1,), 0.02, device="cuda")
+    torch.ops.hk.paged_attention_decode(out, qd, k8.transpose(1, 2), v8.transpose(1, 2), td, ld, d ** -0.5, "fp8", s8, s8,
+                                        4, po, pl)
+    orc.check(out, orc.paged_decode_ref(q, k8.cpu().transpose(1, 2), v8.cpu().transpose(1, 2), table, lens_t, None,
+                                        s8.cpu(), s8.cpu()))
+    # a view whose heads are not evenly strided is refused, not read at the wrong elements
+    with pytest.raises(ValueError, match="evenly strided"):
+        walk(torch.zeros(n, 8, d, 4, device="cuda", dtype=torch.bfloat16).transpose(2, 3), kd, vd, td, ld, out4, o_part, ml_part)
+
     # the cache write as an op
     key = torch.randn(n, 8, d, device="cuda").to(torch.bfloat16)
     slots = torch.arange(n, device="cuda") * 16

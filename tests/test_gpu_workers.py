@@ -1,9 +1,9 @@
 """The walk's workers that are not the default ones, held to the same tests.
 
-Which worker walks a GQA group, how an fp8 tile reaches the mma, and stream or fixed-split grid
-are read from the environment once a process (`HKB_MMA_MIN_GROUP`, `HKB_FP8_WIDEN`, `HKB_F8_CTAS`,
-`HKB_FIXED_SPLITS`, `HKB_CC_RING`, `HKB_STEP_UNFUSED`), so each setting runs the decode and step
-tests in a child process of its own. The defaults are what every other GPU test runs."""
+Which worker walks a GQA group (`HKB_MMA_MIN_GROUP`), stream or fixed-split grid
+(`HKB_FIXED_SPLITS`) and joined or separate step launches (`HKB_STEP_UNFUSED`) are read from the
+environment; each setting runs the decode and step tests in a child process of its own. The
+defaults are what every other GPU test runs."""
 
 import os
 import subprocess
@@ -21,11 +21,7 @@ PICK = "lens_by_splits or gqa_shapes or fp8_cache or head_dim_64 or nan_past or 
 @pytest.mark.parametrize("env", [
     {"HKB_MMA_MIN_GROUP": "8"},                               # CUDA cores below a group of 8, bf16 and fp8
     {"HKB_MMA_MIN_GROUP": "1"},                               # tensor-core tiles at every group
-    {"HKB_MMA_MIN_GROUP": "1", "HKB_FP8_WIDEN": "1"},          # fp8 tiles widened to bf16 in shared memory first
-    {"HKB_F8_CTAS": "2"},                                     # the fp8 worker's two-CTA build
     {"HKB_FIXED_SPLITS": "1"},                                # one CTA a (sequence, kv head, split)
-    {"HKB_MMA_MIN_GROUP": "8", "HKB_CC_RING": "pair"},        # two-warp rings
-    {"HKB_MMA_MIN_GROUP": "8", "HKB_CC_RING": "b"},           # butterfly reduction
     {"HKB_STEP_UNFUSED": "1"},                                # hkb_decode_step as three launches
 ], ids=lambda e: ",".join(f"{k}={v}" for k, v in e.items()))
 def test_decode_and_step_tests_under_another_worker(env):

@@ -16,7 +16,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def test_every_declared_symbol_is_exported():
     text = open(os.path.join(ROOT, "include", "hkb.h")).read()
-    declared = set(re.findall(r"\b(hkb_[a-z_]+)\s*\(", text))
+    declared = set(re.findall(r"\b(hkb_[a-z0-9_]+)\s*\(", text))
     declared -= {"hkb_status"}
     assert declared == set(lib.SIGNATURES), (declared ^ set(lib.SIGNATURES))
     loaded = lib.load()

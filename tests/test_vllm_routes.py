@@ -130,8 +130,8 @@ def test_prefill_calls_are_judged_by_their_own_predicate(on_b200):
 def test_work_list_orders_long_tiles_first():
     from hk_dsl_b200.ops import paged
 
-    assert paged.prefill_tile_rows(32, 8) == 32 and paged.prefill_tile_rows(8, 8) == 128
-    assert paged.prefill_tile_rows(64, 8) == 16 and paged.prefill_tile_rows(6, 2) == 128
+    assert paged.prefill_tile_rows(32, 8) == 64 and paged.prefill_tile_rows(8, 8) == 256
+    assert paged.prefill_tile_rows(64, 8) == 32 and paged.prefill_tile_rows(6, 2) == 256
     w = paged.work_list([(0, 40), (2, 70)], 32, "cpu").tolist()
     assert sorted(w) == [[0, 0], [0, 32], [2, 0], [2, 32], [2, 64]]
     w = paged.work_list([(0, 40), (1, 33)], 32, "cpu", seq_lens=[40, 1033]).tolist()
