@@ -6,6 +6,8 @@ here is part of the bench line.
                                          requests x context grid, next to hk-dsl's own published column
     python bench_tables.py --prefill     paged prefill TFLOP/s over a few prompt shapes, against the
                                          measured bf16 tensor peak
+    python bench_tables.py --prefill-trace [--case 1x0+8192]
+                                         where the tensor-memory prefill kernel's cycles go, by role
 """
 
 from __future__ import annotations
@@ -133,10 +135,10 @@ def latency_table():
     return 0
 
 
-def prefill_table():
-    """Paged prefill on 32 q / 8 kv heads, head_dim 128, bf16: causal flops = 4 * q_heads * head_dim *
+def prefill_table(only: str = ""):
+    """Paged prefill on 32 q / 8 kv heads, head_dim 128: causal flops = 4 * q_heads * head_dim *
     sum over query rows of the keys they see; timed with CUDA events, median of 7; against the
-    measured bf16 tensor peak (this kernel is the mma.sync form of the contraction)."""
+    measured bf16 tensor peak. `only` = "RxCTX+QLEN" (e.g. "1x0+8192") runs that one bf16 shape."""
     import torch
 
     from hk_dsl_b200.ops import paged
@@ -153,6 +155,10 @@ def prefill_table():
     g = torch.Generator(device=dev).manual_seed(3)
     cases = [(r, "bf16") for r in ([(0, 2048)], [(0, 8192)], [(0, 2048)] * 8, [(6144, 2048)] * 4, [(0, 512)] * 32)]
     cases += [([(0, 2048)] * 8, "fp16"), ([(0, 2048)] * 8, "fp8")]      # the other cache dtypes, one shape each
+    if only:
+        reps, _, rest = only.partition("x")
+        ctx, _, qlen = rest.partition("+")
+        cases = [([(int(ctx), int(qlen))] * int(reps), "bf16")]
     for reqs, kind in cases:
         seq = [c + n for c, n in reqs]
         pages = [-(-s // bs) for s in seq]
@@ -203,13 +209,88 @@ def prefill_table():
     return 0
 
 
+def prefill_trace(case: str):
+    """Where the tensor-memory prefill kernel's cycles go on one shape (default 1x0+8192): the traced
+    build's per-CTA counters (hkb_paged_prefill_trace), summed over CTAs and divided by the key blocks
+    walked -- cycles a 64-key block for each role and phase."""
+    import torch
+
+    from hk_dsl_b200.ops import paged
+    from hk_dsl_b200.runtime import lib as hkb
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    reps, _, rest = (case or "1x0+8192").partition("x")
+    ctx, _, qlen = rest.partition("+")
+    reqs = [(int(ctx), int(qlen))] * int(reps)
+    hq, hkv, d, bs = 32, 8, 128, 16
+    g = torch.Generator(device=dev).manual_seed(3)
+    seq = [c + n for c, n in reqs]
+    pages = [-(-s // bs) for s in seq]
+    nb = sum(pages) + 3
+    k = torch.randn(nb, hkv, bs, d, device=dev, generator=g).to(torch.bfloat16)
+    v = torch.randn(nb, hkv, bs, d, device=dev, generator=g).to(torch.bfloat16)
+    table = torch.zeros(len(reqs), max(pages), dtype=torch.int32)
+    perm = torch.randperm(nb)
+    at = 0
+    for i, p_ in enumerate(pages):
+        table[i, :p_] = perm[at:at + p_].to(torch.int32)
+        at += p_
+    starts = [0]
+    for _, n in reqs:
+        starts.append(starts[-1] + n)
+    q = torch.randn(starts[-1], hq, d, device=dev, generator=g).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    tile = paged.prefill_tile_rows(hq, hkv)
+    work = paged.work_list([(r, n) for r, (_, n) in enumerate(reqs)], tile, dev, seq_lens=seq)
+    table_d, lens_d = table.to(dev), torch.tensor(seq, dtype=torch.int32, device=dev)
+    starts_d = torch.tensor(starts, dtype=torch.int32, device=dev)
+    kc, vc = k.transpose(1, 2), v.transpose(1, 2)
+    n_cta = work.shape[0] * hkv
+    trace = torch.zeros(n_cta, 32, dtype=torch.int64, device=dev)
+    lib = hkb.load()
+    cache = lambda c: hkb.CacheT(c.data_ptr(), c.stride(0), c.stride(1), c.stride(2), c.shape[0])
+    for _ in range(2):
+        rc = lib.hkb_paged_prefill_trace(out.data_ptr(), out.stride(0), out.stride(1), q.data_ptr(), q.stride(0), q.stride(1),
+                                         cache(kc), cache(vc), table_d.data_ptr(), table_d.stride(0), table_d.shape[1],
+                                         lens_d.data_ptr(), starts_d.data_ptr(), work.data_ptr(), work.shape[0], hq, hkv, d, bs,
+                                         d ** -0.5, hkb.KV_BF16, None, None, trace.data_ptr(),
+                                         torch.cuda.current_stream().cuda_stream)
+        hkb.check("hkb_paged_prefill_trace", rc)
+    torch.cuda.synchronize()
+    t = trace.cpu().double()
+    # key blocks a CTA walks: those of its second query tile (the longer one)
+    blocks = 0
+    for r, row0 in work.cpu().tolist():
+        c, n = reqs[r]
+        blocks += -(-min(c + n, c + min(row0 + tile, n)) // 64)
+    blocks *= hkv
+    names = {0: "softmax tile 0: wait for scores", 1: "softmax tile 0: TMEM load", 2: "softmax tile 0: max + exp",
+             3: "softmax tile 0: wait for previous product (+ rescale)", 4: "softmax tile 0: store P, arrive", 5: "softmax tile 0: epilogue",
+             8: "softmax tile 1: wait for scores", 9: "softmax tile 1: TMEM load", 10: "softmax tile 1: max + exp",
+             11: "softmax tile 1: wait for previous product (+ rescale)", 12: "softmax tile 1: store P, arrive", 13: "softmax tile 1: epilogue",
+             16: "mma: wait for Q", 17: "mma: wait for K", 18: "mma: issue q.K", 19: "mma: wait for V", 20: "mma: wait for P of tile 0",
+             21: "mma: issue p.V", 22: "mma: wait for P of tile 1", 24: "K producer: wait for a free slot", 25: "K producer: issue copies",
+             26: "K producer: wait for copies", 28: "V producer: wait for a free slot", 29: "V producer: issue copies",
+             30: "V producer: wait for copies", 31: "CTA total"}
+    rows = {names[i]: round(float(t[:, i].sum()) / blocks, 1) for i in sorted(names)}
+    print(json.dumps({"table": "tensor-memory prefill, cycles a 64-key block (both query tiles), by role and phase",
+                      "case": case or "1x0+8192", "ctas": n_cta, "key_blocks": blocks,
+                      "ideal_tensor_cycles_a_block": 1024, "rows": rows}, indent=1), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--latency", action="store_true")
     ap.add_argument("--prefill", action="store_true")
+    ap.add_argument("--case", default="", help="with --prefill: one shape, REQUESTSxCONTEXT+QLEN (a small case for a profiler)")
+    ap.add_argument("--prefill-trace", action="store_true", help="cycles by role and phase of the tensor-memory prefill kernel")
     args = ap.parse_args()
+    if args.prefill_trace:
+        return prefill_trace(args.case)
     if args.prefill:
-        return prefill_table()
+        return prefill_table(args.case)
     return latency_table()
 
 

@@ -372,18 +372,18 @@ static int dispatch_prefill(const PrefillArgs& a, int num_work, cudaStream_t st)
 }
 
 // ---- the tensor-memory form (head_dim 128, 16-bit caches) ----
-template <int GP, bool F16>
+template <int GP, bool F16, bool TRACE = false>
 static int launch_prefill_tc(const tc::Args& a, int num_work, cudaStream_t st) {
   static bool armed[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e == cudaSuccess && dev >= 0 && dev < 64 && !armed[dev]) {
-    e = cudaFuncSetAttribute(tc::prefill_tc_kernel<GP, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+    e = cudaFuncSetAttribute(tc::prefill_tc_kernel<GP, F16, TRACE>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
     if (e == cudaSuccess) armed[dev] = true;
   }
   if (e == cudaSuccess) {
     dim3 grid(num_work, a.num_kv_heads * (a.group / GP));
-    tc::prefill_tc_kernel<GP, F16><<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(a);
+    tc::prefill_tc_kernel<GP, F16, TRACE><<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(a);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
@@ -423,6 +423,8 @@ extern "C" int hkb_prefill_tc_error(int clear) {
   }
   return code;
 }
+
+namespace { thread_local unsigned long long* g_trace_for_next_call = nullptr; }
 
 extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_stride_head,
                                  const void* q, int64_t q_stride_tok, int64_t q_stride_head,
@@ -482,6 +484,11 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
     t.seq_lens = a.seq_lens; t.q_start = a.q_start; t.work = a.work;
     t.num_q_heads = a.num_q_heads; t.num_kv_heads = a.num_kv_heads; t.group = a.group; t.tiles_per_page = a.tiles_per_page;
     t.scale = a.scale;
+    t.trace = g_trace_for_next_call;
+    if (t.trace) {   // the traced build: the headline shape only (a bf16 cache, a GQA group of 4)
+      if (kv_dtype != HKB_KV_BF16 || group % 4 || group % 8 == 0) return HKB_ERR_UNSUPPORTED;
+      return launch_prefill_tc<4, false, true>(t, num_work, st);
+    }
     return kv_dtype == HKB_KV_F16 ? dispatch_prefill_tc<true>(t, num_work, st) : dispatch_prefill_tc<false>(t, num_work, st);
   }
   if (fp8) return dispatch_prefill<128, true>(a, num_work, st);
@@ -491,4 +498,26 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
   }
   if (head_dim == 256) return dispatch_prefill<256, false>(a, num_work, st);
   return head_dim == 128 ? dispatch_prefill<128, false>(a, num_work, st) : dispatch_prefill<64, false>(a, num_work, st);
+}
+
+// hkb_paged_prefill on the traced build of the tensor-memory kernel: every CTA (work item x kv head,
+// CTA index = kv-head index * num_work + work index) leaves 32 cycle counters in `trace` -- where
+// the softmax warps, the MMA warp and the producers spent their clocks. Measurement only.
+extern "C" int hkb_paged_prefill_trace(void* out, int64_t out_stride_tok, int64_t out_stride_head,
+                                       const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                                       hkb_cache_t kc, hkb_cache_t vc,
+                                       const int32_t* block_table, int64_t table_stride, int max_pages,
+                                       const int32_t* seq_lens, const int32_t* q_start,
+                                       const int32_t* work, int num_work,
+                                       int num_q_heads, int num_kv_heads, int head_dim, int block_size,
+                                       float scale, int kv_dtype, const float* k_scale, const float* v_scale,
+                                       unsigned long long* trace, void* stream) {
+  if (!trace) return HKB_ERR_NULL;
+  if (!hkb_prefill_uses_tcgen05(head_dim, kv_dtype)) return HKB_ERR_UNSUPPORTED;
+  g_trace_for_next_call = trace;
+  const int rc = hkb_paged_prefill(out, out_stride_tok, out_stride_head, q, q_stride_tok, q_stride_head, kc, vc, block_table,
+                                   table_stride, max_pages, seq_lens, q_start, work, num_work, num_q_heads, num_kv_heads,
+                                   head_dim, block_size, scale, kv_dtype, k_scale, v_scale, stream);
+  g_trace_for_next_call = nullptr;
+  return rc;
 }

@@ -54,7 +54,7 @@ __host__ __device__ constexpr int s_col(int tile, int buf) { return 256 + tile *
 
 struct Bars {                                  // mbarriers, 8 bytes each
   uint64_t full[NSLOT], empty[NSLOT];
-  uint64_t s_full[2][2], p_full[2][2], o_done[2];
+  uint64_t s_full[2][2], p_full[2][2], o_done[2], q_full[2];
   uint32_t tmem_base;
   int abort;
 };
@@ -65,6 +65,11 @@ static_assert(SMEM_BYTES <= 227 * 1024, "shared memory of one SM");
 __device__ int g_error;   // first failure code of any CTA since it was last cleared (0: none)
 
 // ---- PTX wrappers -------------------------------------------------------------------------
+__device__ __forceinline__ long long now() {   // the SM's cycle counter
+  long long t;
+  asm volatile("mov.u64 %0, %%clock64;\n" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
 }
@@ -81,11 +86,11 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 // about 2^31 clocks, or as soon as another thread of the CTA has given up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort, int code) {
   if (mbar_try(bar, parity)) return true;
-  const long long t0 = clock64();
+  const long long t0 = now();
   while (true) {
     if (mbar_try(bar, parity)) return true;
     if (*abort) return false;
-    if (clock64() - t0 > (1ll << 31)) {
+    if (now() - t0 > (1ll << 31)) {
       *abort = code;
       atomicCAS(&g_error, 0, code);
       return false;
@@ -128,6 +133,31 @@ __device__ __forceinline__ void tmem_ld32(uint32_t addr, float (&v)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// 64 consecutive fp32 columns of this thread's TMEM lane: two 32-column loads in flight, one wait
+__device__ __forceinline__ void tmem_ld64(uint32_t addr, float (&v)[64]) {
+  uint32_t r[64];
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[32 * h + 0]), "=r"(r[32 * h + 1]), "=r"(r[32 * h + 2]), "=r"(r[32 * h + 3]), "=r"(r[32 * h + 4]), "=r"(r[32 * h + 5]),
+          "=r"(r[32 * h + 6]), "=r"(r[32 * h + 7]), "=r"(r[32 * h + 8]), "=r"(r[32 * h + 9]), "=r"(r[32 * h + 10]), "=r"(r[32 * h + 11]),
+          "=r"(r[32 * h + 12]), "=r"(r[32 * h + 13]), "=r"(r[32 * h + 14]), "=r"(r[32 * h + 15]), "=r"(r[32 * h + 16]), "=r"(r[32 * h + 17]),
+          "=r"(r[32 * h + 18]), "=r"(r[32 * h + 19]), "=r"(r[32 * h + 20]), "=r"(r[32 * h + 21]), "=r"(r[32 * h + 22]), "=r"(r[32 * h + 23]),
+          "=r"(r[32 * h + 24]), "=r"(r[32 * h + 25]), "=r"(r[32 * h + 26]), "=r"(r[32 * h + 27]), "=r"(r[32 * h + 28]), "=r"(r[32 * h + 29]),
+          "=r"(r[32 * h + 30]), "=r"(r[32 * h + 31])
+        : "r"(addr + 32 * h) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+// max of three (one instruction on sm_100)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 __device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&r)[32]) {
   asm volatile(
@@ -173,6 +203,23 @@ struct Args {
   const int* work;
   int num_q_heads, num_kv_heads, group, tiles_per_page;
   float scale;
+  unsigned long long* trace;   // TRACE builds only: 32 cycle counters a CTA (see Lap), else unused
+};
+
+// Where a CTA's cycles go, for the traced build (hkb_paged_prefill_trace): one thread of each role
+// adds the clocks between consecutive laps to a counter. Slots: softmax of tile g at 8 g + {0 wait
+// for the scores, 1 TMEM load, 2 maximum and exponentials, 3 wait for the previous product (and the
+// rescale), 4 P store and arrive, 5 epilogue}; MMA warp 16 wait for Q, 17 wait for K, 18 issue of the
+// score products, 19 wait for V, 20 / 22 wait for P of tile 0 / 1, 21 issue of the P V products;
+// producers 24 + 4 w + {0 wait for a free slot, 1 issue of the copies, 2 wait for copies to land};
+// 31 the CTA's whole time.
+template <bool TRACE>
+struct Lap {
+  long long t;
+  __device__ __forceinline__ Lap() : t(TRACE ? now() : 0) {}
+  __device__ __forceinline__ void operator()(unsigned long long& acc) {
+    if (TRACE) { const long long n = now(); acc += (unsigned long long)(n - t); t = n; }
+  }
 };
 
 // A producer warp's copy of one 64-token block (K or V) into a ring slot: 64 rows x 16 chunks of
@@ -204,9 +251,11 @@ __device__ __forceinline__ void fill_slot(const Args& a, uint32_t slot, const ui
   }
 }
 
-template <int GP, bool F16>
+template <int GP, bool F16, bool TRACE = false>
 __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a) {
   extern __shared__ uint8_t raw_smem[];
+  unsigned long long tr[8] = {0, 0, 0, 0, 0, 0, 0, 0};      // this thread's lap counters (TRACE builds)
+  const long long t_begin = TRACE ? now() : 0;
   constexpr int T = ROWS / GP;                 // tokens of one query tile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -243,7 +292,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < NSLOT; ++i) { mbar_init(HKB_BAR(full) + 8 * i, 32); mbar_init(HKB_BAR(empty) + 8 * i, 1); }
     for (int i = 0; i < 4; ++i) { mbar_init(HKB_BAR(s_full) + 8 * i, 1); mbar_init(HKB_BAR(p_full) + 8 * i, ROWS); }
-    for (int i = 0; i < 2; ++i) mbar_init(HKB_BAR(o_done) + 8 * i, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(HKB_BAR(o_done) + 8 * i, 1); mbar_init(HKB_BAR(q_full) + 8 * i, ROWS); }
     bars->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -251,18 +300,6 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(HKB_BAR(tmem_base)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
-  // query rows: row r of tile t is head r / T, token r % T of the tile; rows past the request are zeros
-  for (int x = threadIdx.x; x < 2 * ROWS * 16; x += THREADS) {
-    const int t = x / (ROWS * 16), r = (x / 16) % ROWS, c = x % 16;
-    const int tok = row0 + t * T + r % T;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (tok < q_len)
-      v = __ldg(reinterpret_cast<const uint4*>(a.q + (int64_t)(q0 + tok) * a.q_stride_tok +
-                                               (int64_t)(hbase + r / T) * a.q_stride_head + c * 8));
-    const uint32_t dst = q_smem + t * Q_BYTES + (c >> 3) * HALF_BYTES_Q + r * 128 + (((c & 7) ^ (r & 7)) << 4);
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-  }
-  fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -271,6 +308,30 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a) {
   if (warp < SOFTMAX_WARPS) {
     // ================= softmax: thread = one query row of tile g =================
     const int g = warp >> 2, row = (warp & 3) * 32 + lane;
+    // whether output rows can be written as 16-byte vectors (else as 4-byte words)
+    const bool out16 = ((reinterpret_cast<uintptr_t>(a.out) | (uintptr_t)(a.out_stride_tok * 2) | (uintptr_t)(a.out_stride_head * 2)) & 15) == 0;
+    // This tile's query rows first (the producers are already fetching K and V): row r is head r / T,
+    // token r % T of the tile; rows past the request are zeros. 128 threads x 16 chunks a row group.
+    if (nblk[g] > 0) {
+      uint4 qv[16];
+#pragma unroll
+      for (int it = 0; it < 16; ++it) {                      // all sixteen loads in flight, then the stores
+        const int x = it * ROWS + (warp & 3) * 32 + lane, r = x >> 4, c = x & 15;
+        const int tk = row0 + g * T + r % T;
+        qv[it] = make_uint4(0u, 0u, 0u, 0u);
+        if (tk < q_len)
+          qv[it] = __ldg(reinterpret_cast<const uint4*>(a.q + (int64_t)(q0 + tk) * a.q_stride_tok +
+                                                        (int64_t)(hbase + r / T) * a.q_stride_head + c * 8));
+      }
+#pragma unroll
+      for (int it = 0; it < 16; ++it) {
+        const int x = it * ROWS + (warp & 3) * 32 + lane, r = x >> 4, c = x & 15;
+        const uint32_t dst = q_smem + g * Q_BYTES + (c >> 3) * HALF_BYTES_Q + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(dst), "r"(qv[it].x), "r"(qv[it].y), "r"(qv[it].z), "r"(qv[it].w) : "memory");
+      }
+      fence_async_smem();
+      mbar_arrive(HKB_BAR(q_full) + 8 * g);
+    }
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const int tok = row0 + g * T + row % T, hq = hbase + row / T;
     const bool valid = tok < q_len;
@@ -281,27 +342,30 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a) {
     bool ok = true;
     for (int j = 0; j < nb && ok; ++j) {
       const int b = j & 1;
+      Lap<TRACE> lap;
       ok = warp_wait(HKB_BAR(s_full) + 8 * (g * 2 + b), (j >> 1) & 1, abort, 1);
       if (!ok) break;
+      lap(tr[0]);
       tc_fence_after();
       float s[KVB];
-      {
-        float lo[32], hi[32];
-        tmem_ld32(lane_addr + s_col(g, b), lo);
-        tmem_ld32(lane_addr + s_col(g, b) + 32, hi);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) { s[i] = lo[i]; s[32 + i] = hi[i]; }
-      }
+      tmem_ld64(lane_addr + s_col(g, b), s);
+      lap(tr[1]);
       const int kv0 = j * KVB;
       if (!valid || kv0 + KVB - 1 > pos) {                   // the diagonal block, or a row past the request
 #pragma unroll
         for (int i = 0; i < KVB; ++i)
           if (!valid || kv0 + i > pos) s[i] = -INFINITY;
       }
-      float mx = s[0];
+      // the row maximum: four independent chains of three-input max
+      float mq[4];
 #pragma unroll
-      for (int i = 1; i < KVB; ++i) mx = fmaxf(mx, s[i]);
-      mx *= qs;                                              // qs > 0
+      for (int c = 0; c < 4; ++c) {
+        mq[c] = max3(s[16 * c], s[16 * c + 1], s[16 * c + 2]);
+#pragma unroll
+        for (int i = 3; i < 15; i += 2) mq[c] = max3(mq[c], s[16 * c + i], s[16 * c + i + 1]);
+        mq[c] = fmaxf(mq[c], s[16 * c + 15]);
+      }
+      const float mx = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])) * qs;    // qs > 0
       // lazy reference: it moves only when a block's maximum exceeds it by 2^8 (P <= 256 fits 16 bits)
       const bool need = mx > m + 8.f;
       const bool any_need = __any_sync(0xffffffffu, need);
@@ -311,16 +375,29 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a) {
         m = mx;
       }
       const float off = (m == -INFINITY) ? 0.f : -m;
+      // p = exp2(s * qs - m): packed fp32 pairs for the multiply-add and the sums (four chains), one
+      // MUFU a value, a packed convert a pair
+      const uint64_t qs2 = pack2(qs, qs), off2 = pack2(off, off);
       uint32_t p[32];
-      float sum = 0.f;
+      uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        const float p0 = fast_exp2(fmaf(s[2 * i], qs, off)), p1 = fast_exp2(fmaf(s[2 * i + 1], qs, off));
-        sum += p0 + p1;
-        if (F16) { const __half2 h = __floats2half2_rn(p0, p1); p[i] = *reinterpret_cast<const uint32_t*>(&h); }
-        else { const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1); p[i] = *reinterpret_cast<const uint32_t*>(&h); }
+        float x0, x1;
+        unpack2(fma2(pack2(s[2 * i], s[2 * i + 1]), qs2, off2), x0, x1);
+        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+        acc[i & 3] = add2(acc[i & 3], pack2(p0, p1));
+        if (F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(p[i]) : "f"(p1), "f"(p0));
+        else asm("cvt.rn.bf16x2.f32 %0, %1, %2;\n" : "=r"(p[i]) : "f"(p1), "f"(p0));
+      }
+      float sum;
+      {
+        float a0, a1;
+        unpack2(add2(add2(acc[0], acc[1]), add2(acc[2], acc[3])), a0, a1);
+        sum = a0 + a1;
       }
       l = l * alpha + sum;
+      if (TRACE) asm volatile("" ::"r"(p[0]), "r"(p[31]), "f"(l));   // the math is done before the lap is taken
+      lap(tr[2]);
       if (j > 0) {
         // the tile's previous product has landed: O may be touched, and stays untouched until P arrives
         ok = warp_wait(HKB_BAR(o_done) + 8 * g, (j - 1) & 1, abort, 2);
@@ -338,87 +415,135 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a) {
           }
         }
       }
+      lap(tr[3]);
       tmem_st32(lane_addr + s_col(g, b), p);                  // P over the first 32 columns of the scores just read
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(HKB_BAR(p_full) + 8 * (g * 2 + b));
+      lap(tr[4]);
     }
+    Lap<TRACE> lap_end;
     if (ok && nb > 0) {
       ok = warp_wait(HKB_BAR(o_done) + 8 * g, (nb - 1) & 1, abort, 3);
       if (ok) {
         tc_fence_after();
         const float inv = l > 0.f ? 1.f / l : 0.f;
-        __nv_bfloat16* orow = a.out + (int64_t)(q0 + tok) * a.out_stride_tok + (int64_t)hq * a.out_stride_head;
+        // The tile's query rows in shared memory are dead (every product that read them has landed):
+        // each thread parks its output row there (256 bytes, 16-byte chunks XOR-ed by the row so that the
+        // 32 rows of a warp do not collide on banks), then the warp -- which owns exactly these 32
+        // rows -- writes them out two whole rows an instruction.
+        const uint32_t stage = q_smem + g * Q_BYTES + (warp & 3) * 32 * 256;
 #pragma unroll 1
         for (int c0 = 0; c0 < D; c0 += 32) {
           float o[32];
           tmem_ld32(lane_addr + o_col(g) + c0, o);
-          if (valid) {
-            uint32_t w[16];
+          uint32_t w[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              if (F16) { const __half2 h = __floats2half2_rn(o[2 * i] * inv, o[2 * i + 1] * inv); w[i] = *reinterpret_cast<const uint32_t*>(&h); }
-              else { const __nv_bfloat162 h = __floats2bfloat162_rn(o[2 * i] * inv, o[2 * i + 1] * inv); w[i] = *reinterpret_cast<const uint32_t*>(&h); }
+          for (int i = 0; i < 16; ++i) {
+            if (F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(w[i]) : "f"(o[2 * i + 1] * inv), "f"(o[2 * i] * inv));
+            else asm("cvt.rn.bf16x2.f32 %0, %1, %2;\n" : "=r"(w[i]) : "f"(o[2 * i + 1] * inv), "f"(o[2 * i] * inv));
+          }
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const int chunk = (c0 >> 3) + q4;                 // 16-byte chunk of the row
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)),
+                         "r"(w[4 * q4]), "r"(w[4 * q4 + 1]), "r"(w[4 * q4 + 2]), "r"(w[4 * q4 + 3]) : "memory");
+          }
+        }
+        __syncwarp();
+#pragma unroll 4
+        for (int it = 0; it < 16; ++it) {
+          const int rr = it * 2 + (lane >> 4), chunk = lane & 15;      // row of the warp, chunk of the row
+          const int r_tile = (warp & 3) * 32 + rr;
+          const int tk = row0 + g * T + r_tile % T;
+          const uint4 v = lds128(stage + rr * 256 + ((chunk ^ (rr & 15)) << 4));
+          if (tk < q_len) {
+            __nv_bfloat16* dst = a.out + (int64_t)(q0 + tk) * a.out_stride_tok + (int64_t)(hbase + r_tile / T) * a.out_stride_head + chunk * 8;
+            if (out16) *reinterpret_cast<uint4*>(dst) = v;
+            else {
+              uint32_t* d32 = reinterpret_cast<uint32_t*>(dst);
+              d32[0] = v.x; d32[1] = v.y; d32[2] = v.z; d32[3] = v.w;
             }
-            uint32_t* dst = reinterpret_cast<uint32_t*>(orow + c0);   // rows are 4-byte aligned at least
-#pragma unroll
-            for (int i = 0; i < 16; ++i) dst[i] = w[i];
           }
         }
       }
     }
+    lap_end(tr[5]);
+    if (TRACE && row == 0)
+      for (int i = 0; i < 6; ++i) a.trace[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 32 + 8 * g + i] = tr[i];
   } else if (warp == MMA_WARP) {
     // ================= MMA issue: one thread; the whole warp keeps step at the barriers =================
     constexpr uint32_t IDESC_S = instr_desc(F16, false, KVB), IDESC_PV = instr_desc(F16, true, D);
     bool ok = true;
+    Lap<TRACE> lap;
+    for (int t = 0; t < 2 && ok; ++t)
+      if (nblk[t] > 0) ok = warp_wait(HKB_BAR(q_full) + 8 * t, 0, abort, 8);   // the tile's query rows are in place
+    lap(tr[0]);
     auto scores = [&](int j) {    // S_t(j) = Q_t K_j^T for the tiles that reach block j
       const int slot = (2 * j) % NSLOT;
       ok = warp_wait(HKB_BAR(full) + 8 * slot, ((2 * j) / NSLOT) & 1, abort, 4);
       if (!ok) return;
+      lap(tr[1]);
       tc_fence_after();
       if (lane == 0) {
         const uint32_t kaddr = ring + slot * SLOT_BYTES;
+        // the eight products of a tile accumulate into one TMEM tile, a dependent chain: the two tiles'
+        // chains are issued alternately so that one's latency hides behind the other's work
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          if (j >= nblk[t]) continue;
-          const uint32_t d = tmem + s_col(t, j & 1);
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
-          for (int h = 0; h < 2; ++h)
+          for (int ks = 0; ks < 4; ++ks) {       // 16 dims = 32 bytes a step inside the 128-byte row
+            const uint64_t kd = smem_desc(kaddr + h * HALF_BYTES_KV + ks * 32, 16);
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks)       // 16 dims = 32 bytes a step inside the 128-byte row
-              umma_ss(d, smem_desc(q_smem + t * Q_BYTES + h * HALF_BYTES_Q + ks * 32, 16),
-                      smem_desc(kaddr + h * HALF_BYTES_KV + ks * 32, 16), IDESC_S, (h | ks) ? 1u : 0u);
-          tc_commit(HKB_BAR(s_full) + 8 * (t * 2 + (j & 1)));
-        }
+            for (int t = 0; t < 2; ++t)
+              if (j < nblk[t])
+                umma_ss(tmem + s_col(t, j & 1), smem_desc(q_smem + t * Q_BYTES + h * HALF_BYTES_Q + ks * 32, 16), kd, IDESC_S,
+                        (h | ks) ? 1u : 0u);
+          }
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+          if (j < nblk[t]) tc_commit(HKB_BAR(s_full) + 8 * (t * 2 + (j & 1)));
         tc_commit(HKB_BAR(empty) + 8 * slot);   // the K block is free once these products are done
       }
       __syncwarp();
+      lap(tr[2]);
     };
-    scores(0);
+    if (ok) scores(0);
     for (int j = 0; j < n && ok; ++j) {
       if (j + 1 < n) scores(j + 1);
       if (!ok) break;
       const int slot = (2 * j + 1) % NSLOT;
       ok = warp_wait(HKB_BAR(full) + 8 * slot, ((2 * j + 1) / NSLOT) & 1, abort, 5);
       if (!ok) break;
+      lap(tr[3]);
       const uint32_t vaddr = ring + slot * SLOT_BYTES;
       for (int t = 0; t < 2 && ok; ++t) {
         if (j >= nblk[t]) continue;
         ok = warp_wait(HKB_BAR(p_full) + 8 * (t * 2 + (j & 1)), (j >> 1) & 1, abort, 6);
-        if (!ok) break;
-        tc_fence_after();
-        if (lane == 0) {
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)         // 16 tokens a step: 8 TMEM columns of P, 16 rows of V
-            umma_ts(tmem + o_col(t), tmem + s_col(t, j & 1) + ks * 8,
-                    smem_desc(vaddr + ks * 16 * 128, HALF_BYTES_KV), IDESC_PV, (j | ks) ? 1u : 0u);
-          tc_commit(HKB_BAR(o_done) + 8 * t);
-        }
-        __syncwarp();
+        lap(tr[t ? 6 : 4]);
       }
+      if (!ok) break;
+      tc_fence_after();
+      if (lane == 0) {
+        // both tiles' P are in place: their two chains of four products, alternately
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {         // 16 tokens a step: 8 TMEM columns of P, 16 rows of V
+          const uint64_t vd = smem_desc(vaddr + ks * 16 * 128, HALF_BYTES_KV);
+#pragma unroll
+          for (int t = 0; t < 2; ++t)
+            if (j < nblk[t]) umma_ts(tmem + o_col(t), tmem + s_col(t, j & 1) + ks * 8, vd, IDESC_PV, (j | ks) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+          if (j < nblk[t]) tc_commit(HKB_BAR(o_done) + 8 * t);
+      }
+      __syncwarp();
+      lap(tr[5]);
       if (ok && lane == 0) tc_commit(HKB_BAR(empty) + 8 * slot);
       __syncwarp();
     }
+    if (TRACE && lane == 0)
+      for (int i = 0; i < 7; ++i) a.trace[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 32 + 16 + i] = tr[i];
   } else {
     // ================= producers: warp K_WARP fills the K blocks, warp V_WARP the V blocks =================
     const int which = warp - K_WARP;   // 0: K, 1: V
@@ -433,22 +558,30 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a) {
     int issued = 0;
     for (int j = 0; j < n && ok; ++j) {
       const int use = 2 * j + which, slot = use % NSLOT, lap = use / NSLOT;
+      Lap<TRACE> tick;
       if (lap > 0) ok = warp_wait(HKB_BAR(empty) + 8 * slot, (lap - 1) & 1, abort, 7);
       if (!ok) break;
+      tick(tr[0]);
       fill_slot(a, ring + slot * SLOT_BYTES, src, sb, st, table_row, j * KVB, kv_limit, lane);
       cp_async_commit();
       ++issued;
+      tick(tr[1]);
       if (j >= LAG - 1) { cp_async_wait<LAG - 1>(); publish(j - (LAG - 1)); }
+      tick(tr[2]);
     }
     // drain: whatever was issued lands before the CTA leaves, and is handed over if all is well
     cp_async_wait<0>();
     if (ok)
       for (int j = max(0, issued - (LAG - 1)); j < issued; ++j) publish(j);
+    if (TRACE && lane == 0)
+      for (int i = 0; i < 3; ++i) a.trace[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 32 + 24 + 4 * which + i] = tr[i];
   }
 
   // ---- wind-down ----
   tc_fence_before();
   __syncthreads();
+  if (TRACE && threadIdx.x == 0)
+    a.trace[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 32 + 31] = (unsigned long long)(now() - t_begin);
   if (warp == MMA_WARP) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");

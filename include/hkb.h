@@ -300,6 +300,28 @@ int hkb_prefill_tile_rows(int num_q_heads, int num_kv_heads);
  * its contraction form per architecture and shape (python/hk/ops/paged_prefill.py:59-120). */
 int hkb_prefill_uses_tcgen05(int head_dim, int kv_dtype);
 
+/*
+ * hkb_paged_prefill on a traced build of the tensor-memory kernel (head_dim 128, a bf16 cache, a
+ * GQA group of 4, 16-byte-aligned query rows; HKB_ERR_UNSUPPORTED otherwise): besides the answer,
+ * every CTA -- index kv_head * num_work + work item -- writes 32 uint64 cycle counters to
+ * `trace` (device memory, num_work * num_kv_heads * 32 entries): softmax warps of query tile g at
+ * 8 g + {0 waiting for scores, 1 TMEM load, 2 maximum and exponentials, 3 waiting for the
+ * previous product / rescale, 4 P store and arrive, 5 epilogue}; MMA warp at 16 + {0 wait for Q,
+ * 1 wait for K, 2 issue of q.K, 3 wait for V, 4 / 6 wait for P of tile 0 / 1, 5 issue of p.V};
+ * producer w (0 K, 1 V) at 24 + 4 w + {0 wait for a free slot, 1 issue of copies, 2 wait for
+ * copies to land}; 31 the CTA's whole time. A measurement aid with no counterpart in the reference
+ * (which attributes time by ablation, python/hk/ops/paged.py:524-533).
+ */
+int hkb_paged_prefill_trace(void* out, int64_t out_stride_tok, int64_t out_stride_head,
+                            const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                            hkb_cache_t k_cache, hkb_cache_t v_cache,
+                            const int32_t* block_table, int64_t table_stride, int max_pages,
+                            const int32_t* seq_lens, const int32_t* q_start,
+                            const int32_t* work, int num_work,
+                            int num_q_heads, int num_kv_heads, int head_dim, int block_size,
+                            float scale, int kv_dtype, const float* k_scale, const float* v_scale,
+                            unsigned long long* trace, void* stream);
+
 /* The tensor-memory prefill kernel bounds every wait on a barrier; a wait that ran out leaves a
  * code here (0: none; 1..7: which wait) instead of hanging the GPU. Reads the word back from the
  * current device (this synchronises); `clear` != 0 resets it. -1 if the read failed. */
