@@ -379,8 +379,24 @@ def run_config(ctx, name: str, *, headline: bool, probe_gbs=None):
     splits = args.splits or paged.plan_splits(n, st.kv_heads, max_tiles, device=dev)
     path = "mma" if hkb_lib.load().hkb_walk_uses_mma(spec.q_heads // spec.kv_heads, 1 if spec.fp8 else 0) else "cc"
     dec = None
+    exchange = None
     if kvsplit:
-        dec = paged_dist.SplitKVDecoder(n, st.q_heads, st.kv_heads, d, dev, splits)
+        # the ranks' records go over peer memory (two kernels of this build, no collective) where the
+        # box maps it; HKB_KVSPLIT_EXCHANGE=nccl, or a box that cannot, takes the all-gather
+        exchange = os.environ.get("HKB_KVSPLIT_EXCHANGE", "peer")
+        try:
+            dec = paged_dist.SplitKVDecoder(n, st.q_heads, st.kv_heads, d, dev, splits, exchange=exchange)
+        except Exception as ex:  # noqa: BLE001
+            if exchange != "peer":
+                raise
+            exchange = f"nccl (peer memory unavailable: {type(ex).__name__}: {str(ex).splitlines()[0][:120]})"
+            dec = paged_dist.SplitKVDecoder(n, st.q_heads, st.kv_heads, d, dev, splits, exchange="nccl")
+        if world > 1:       # every rank takes the same path
+            flag = torch.tensor([1 if dec.peer is not None else 0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if dec.peer is not None and int(flag.item()) == 0:
+                exchange = "nccl (peer memory unavailable on another rank)"
+                dec = paged_dist.SplitKVDecoder(n, st.q_heads, st.kv_heads, d, dev, splits, exchange="nccl")
         splits = dec.local_splits
     scratch = paged.split_scratch(n, st.q_heads, d, splits, dev) if splits > 1 else None
     owns_new = bool((st.slot_mapping >= 0).any().item())
@@ -421,7 +437,8 @@ def run_config(ctx, name: str, *, headline: bool, probe_gbs=None):
     # the launches either side of it are captured (one graph a rotated cache for the walk + the
     # local merge, one for the merge of the gathered records) and the all-gather is launched
     # eagerly between them.
-    captured = not (kvsplit and world > 1)
+    peer = kvsplit and dec.peer is not None
+    captured = not (kvsplit and world > 1) or peer      # a step without a collective is captured whole
     capture_note = None
     graph = torch.cuda.CUDAGraph()
     if captured:
@@ -519,8 +536,12 @@ def run_config(ctx, name: str, *, headline: bool, probe_gbs=None):
                               "bytes_a_rotation_this_rank": st.kv_bytes * layers}}
     if capture_note:
         rec["cuda_graph_note"] = capture_note
+    if kvsplit:
+        rec["exchange"] = exchange if not peer else "peer memory: hkb_kvsplit_push + hkb_kvsplit_merge, no collective"
+        if peer:
+            rec["exchange_error_word"] = dec.peer.error()
     if kvsplit and world > 1:
-        rec["breakdown_us"] = kvsplit_breakdown(ctx, spec, st, dec, layers, K, owns_new)
+        rec["breakdown_us"] = (peer_breakdown if peer else kvsplit_breakdown)(ctx, spec, st, dec, layers, K, owns_new)
 
     if headline:
         rec["e2e"] = e2e_leg(ctx, spec, st, dec, layers, splits, scratch, kv_total, K, Wm, kvsplit, owns_new)
@@ -560,6 +581,35 @@ def kvsplit_breakdown(ctx, spec, st, dec, layers, K, owns_new):
     out = {}
     for j, nm in enumerate(names):
         out[nm] = ctx.max_over_ranks(statistics.fmean(ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(K)) * 1e3)
+    out["how"] = "eager launches, one CUDA event between pieces, mean of the steps, max over ranks"
+    return out
+
+
+def peer_breakdown(ctx, spec, st, dec, layers, K, owns_new):
+    """The three launches of a KV-split step over peer memory, eagerly, a CUDA event between them: the
+    walk (it writes the new rows), the push (fold of the local splits + stores into every rank), the
+    merge (its wait for the slowest rank's record included). Means over K steps, max over ranks."""
+    torch = ctx.torch
+    from hk_dsl_b200.ops import paged
+
+    names = ("walk_us", "push_us", "wait_and_merge_us")
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(K)]
+    new = dict(key=st.key, value=st.value, slot_mapping=st.slot_mapping) if owns_new else dict(key=None, value=None, slot_mapping=None)
+    ctx.barrier()
+    for i in range(K):
+        l = i % layers
+        ev[i][0].record()
+        paged.decode_step_record(None, None, st.query, new["key"], new["value"], st.k_caches[l], st.v_caches[l],
+                                 new["slot_mapping"], st.block_table, st.seq_lens, st.scale, spec.kv_cache_dtype,
+                                 st.k_scale, st.v_scale, num_splits=dec.local_splits, scratch=dec.scratch)
+        ev[i][1].record()
+        dec.peer.push(dec.scratch, dec.local_splits)
+        ev[i][2].record()
+        dec.peer.merge(st.out)
+        ev[i][3].record()
+    ctx.barrier()
+    out = {nm: ctx.max_over_ranks(statistics.fmean(ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(K)) * 1e3)
+           for j, nm in enumerate(names)}
     out["how"] = "eager launches, one CUDA event between pieces, mean of the steps, max over ranks"
     return out
 
@@ -614,7 +664,7 @@ def e2e_leg(ctx, spec, st, dec, layers, splits, scratch, kv_total, K, Wm, kvspli
 
     eager_ms = timed(e2e_step)
     e2e_ms, how = eager_ms, "eager: one host->device copy, the API call(s), one device->host copy, a stream sync a step"
-    if not (kvsplit and world > 1):
+    if not (kvsplit and world > 1) or (dec is not None and dec.peer is not None):
         # The same step as an engine runs it: captured once (a graph a rotated cache) and replayed. A
         # replay performs the host->device copy of the step's inputs from pinned memory, the launches
         # of decode_step and the device->host copy of the result; then the caller syncs and reads.

@@ -212,7 +212,7 @@ def prefill_table(only: str = ""):
 def prefill_trace(case: str):
     """Where the tensor-memory prefill kernel's cycles go on one shape (default 1x0+8192): the traced
     build's per-CTA counters (hkb_paged_prefill_trace), summed over CTAs and divided by the key blocks
-    walked -- cycles a 64-key block for each role and phase."""
+    walked -- cycles a 128-key block for each role and phase."""
     import torch
 
     from hk_dsl_b200.ops import paged
@@ -263,20 +263,20 @@ def prefill_trace(case: str):
     blocks = 0
     for r, row0 in work.cpu().tolist():
         c, n = reqs[r]
-        blocks += -(-min(c + n, c + min(row0 + tile, n)) // 64)
+        blocks += -(-min(c + n, c + min(row0 + tile, n)) // 128)
     blocks *= hkv
-    names = {0: "softmax tile 0: wait for scores", 1: "softmax tile 0: TMEM load", 2: "softmax tile 0: max + exp",
+    names = {0: "softmax tile 0: wait for scores", 1: "softmax tile 0: loads + maximum", 2: "softmax tile 0: exponentials",
              3: "softmax tile 0: wait for previous product (+ rescale)", 4: "softmax tile 0: store P, arrive", 5: "softmax tile 0: epilogue",
-             8: "softmax tile 1: wait for scores", 9: "softmax tile 1: TMEM load", 10: "softmax tile 1: max + exp",
+             8: "softmax tile 1: wait for scores", 9: "softmax tile 1: loads + maximum", 10: "softmax tile 1: exponentials",
              11: "softmax tile 1: wait for previous product (+ rescale)", 12: "softmax tile 1: store P, arrive", 13: "softmax tile 1: epilogue",
-             16: "mma: wait for Q", 17: "mma: wait for K", 18: "mma: issue q.K", 19: "mma: wait for V", 20: "mma: wait for P of tile 0",
-             21: "mma: issue p.V", 22: "mma: wait for P of tile 1", 24: "K producer: wait for a free slot", 25: "K producer: issue copies",
+             16: "mma: wait for Q", 17: "mma: wait for K", 18: "mma: issue first q.K", 19: "mma: wait for V", 20: "mma: wait for P of tile 0",
+             21: "mma: issue p.V and the next q.K", 22: "mma: wait for P of tile 1", 24: "K producer: wait for a free slot", 25: "K producer: issue copies",
              26: "K producer: wait for copies", 28: "V producer: wait for a free slot", 29: "V producer: issue copies",
              30: "V producer: wait for copies", 31: "CTA total"}
     rows = {names[i]: round(float(t[:, i].sum()) / blocks, 1) for i in sorted(names)}
-    print(json.dumps({"table": "tensor-memory prefill, cycles a 64-key block (both query tiles), by role and phase",
+    print(json.dumps({"table": "tensor-memory prefill, cycles a 128-key block (both query tiles), by role and phase",
                       "case": case or "1x0+8192", "ctas": n_cta, "key_blocks": blocks,
-                      "ideal_tensor_cycles_a_block": 1024, "rows": rows}, indent=1), flush=True)
+                      "ideal_tensor_cycles_a_block": 2048, "rows": rows}, indent=1), flush=True)
     return 0
 
 

@@ -577,6 +577,9 @@ static int step_impl(void* out, int64_t out_stride_tok, int64_t out_stride_head,
   if (num_seqs == 0) return HKB_OK;
   if ((key == nullptr) != (value == nullptr)) return HKB_ERR_NULL;
   if (key && !slot_mapping) return HKB_ERR_NULL;
+  if (out_kind == 1 && (out == nullptr) != (out_lse == nullptr)) return HKB_ERR_NULL;   // a record is both halves, or neither
+  const bool out_record_is_null = out_kind == 1 && out == nullptr;
+  if (out_record_is_null) out = const_cast<void*>(q);   // never written: a split walk without a fold touches no output row
   if (key) {
     // the new rows are read as 16-byte chunks, whichever launch writes them
     if ((key_stride_tok | key_stride_head | val_stride_tok | val_stride_head) % 8) return HKB_ERR_STRIDE;
@@ -587,10 +590,13 @@ static int step_impl(void* out, int64_t out_stride_tok, int64_t out_stride_head,
                         num_q_heads, num_kv_heads, head_dim, block_size, kv_dtype, k_scale, v_scale, num_splits,
                         part_out, part_lse);
   if (rc != HKB_OK) return rc;
-  if (out_kind == 1 && (num_splits < 2 || !out_lse)) return HKB_ERR_SPLITS;   // a record is written by the merge
+  // a record is written by the merge of at least two splits; with no record to write (out_kind 1, out NULL)
+  // the step is the walk alone and the partials stay in the scratch for the caller to fold
+  const bool walk_only = out_kind == 1 && out_record_is_null;
+  if (out_kind == 1 && (num_splits < 2 || (!walk_only && !out_lse))) return HKB_ERR_SPLITS;
   const bool fusable = step_fusable(num_splits, num_seqs);
   const bool fold = arrivals && fusable && kv_dtype != HKB_KV_F16 && out_kind == 0;
-  if (num_splits > 1 && !fold) {
+  if (num_splits > 1 && !fold && !walk_only) {
     rc = merge_check(out, out_stride_tok, out_stride_head, out_kind, part_out, (int64_t)num_q_heads * head_dim,
                      (int64_t)num_splits * num_q_heads * head_dim, part_lse, num_splits, num_seqs, num_q_heads, head_dim);
     if (rc != HKB_OK) return rc;
@@ -616,7 +622,7 @@ static int step_impl(void* out, int64_t out_stride_tok, int64_t out_stride_head,
   rc = decode_impl(out, out_stride_tok, out_stride_head, q, q_stride_tok, q_stride_head, kc, vc, block_table,
                    table_stride, max_pages, seq_lens, q_start, num_seqs, num_q_heads, num_kv_heads, head_dim,
                    block_size, scale, kv_dtype, k_scale, v_scale, num_splits, part_out, part_lse, stream, &x);
-  if (rc != HKB_OK || x.folded || num_splits <= 1) return rc;
+  if (rc != HKB_OK || x.folded || num_splits <= 1 || walk_only) return rc;
   const int kind = out_kind == 1 ? 1 : (kv_dtype == HKB_KV_F16 ? 2 : 0);
   return hkb_merge(out, out_stride_tok, out_stride_head, kind, out_kind == 1 ? out_lse : nullptr, part_out,
                    (int64_t)num_q_heads * head_dim, (int64_t)num_splits * num_q_heads * head_dim, part_lse, num_q_heads,

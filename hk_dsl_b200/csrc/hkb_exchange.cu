@@ -1,0 +1,293 @@
+// The exchange step of a KV axis cut across GPUs, without a library collective: the fold of a
+// rank's splits writes its record straight into every peer's gather buffer over NVLink (plain peer
+// stores into memory the ranks mapped into each other), and the final merge waits -- boundedly --
+// for every rank's record before it folds them.
+//
+// A step on every rank, on one stream: walk (hkb_paged_decode, partials into local scratch) ->
+// hkb_kvsplit_push (fold of the local splits; the record goes to all peers, then one flag a peer)
+// -> hkb_kvsplit_merge (wait for all ranks' flags of this step, fold the records). Against an
+// all-gather between two launches this saves the collective's launch and protocol latency: the
+// record is 66 KB at the long-context shape, far below what a ring or tree is built to move.
+//
+// Protocol. Every rank keeps a step counter `epoch` in its own memory (zero before the first
+// step; the merge kernel's last CTA increments it), so nothing on the host changes between steps
+// and a captured graph replays. Gather buffers and flags are double-buffered by the step's parity:
+// a rank that is one step ahead writes the other half. A push CTA stores its part of the record to
+// every peer, fences at system scope and counts itself done; the CTA that counts last stores
+// epoch + 1 into this rank's flag on every peer. The merge kernel's CTAs poll the flags of all
+// ranks (volatile loads, at most `spin_limit` polls a flag); if one does not arrive in time the
+// CTA sets the rank's error word, skips the fold and returns -- the context stays usable, and the
+// host reads the word. No multimem, no multicast: peer pointers only.
+//
+// hk-dsl has no counterpart: it cuts the KV axis inside one GPU (python/hk/ops/paged.py:171-194)
+// and leaves tensor parallelism to the engine.
+#include "hkb_common.cuh"
+
+extern thread_local int hkb_tls_cuda_error;
+
+namespace hkb {
+
+constexpr int XCH_WARPS = 8;
+
+struct PushArgs {
+  const float* part_out;   // (seqs, splits, heads, d) normalised partials of this rank
+  const float* part_lse;   // (seqs, splits, heads)
+  int num_splits, num_q_heads, head_dim, num_seqs;
+  int world, rank;
+  float* gather[8];        // peer r's gather buffer as mapped here
+  uint32_t* flags[8];      // peer r's flag block as mapped here
+  uint32_t* epoch;         // this rank's step counter
+  uint32_t* done;          // this rank's CTA counter (zero between launches)
+  int64_t rec_floats;      // floats of one record (out then lse, padded to 4)
+};
+
+// One CTA a (sequence, head): its eight warps take the rank's splits round-robin (lse = -inf marks
+// a split without tokens; its memory is never read), the warps' sums are added through shared
+// memory in a fixed order, and warp 0 stores the normalised fp32 row and its lse into slot `rank`
+// of the step's half of every peer's gather buffer.
+template <int VEC>
+__global__ void __launch_bounds__(XCH_WARPS * 32) kvsplit_push_kernel(const PushArgs a) {
+  __shared__ float s_mx[XCH_WARPS];
+  __shared__ float s_acc[XCH_WARPS][32 * VEC + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.x, seq = blockIdx.y;
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch);
+  const int64_t half_off = (int64_t)(epoch & 1u) * a.world * a.rec_floats + (int64_t)a.rank * a.rec_floats;
+  const float* lse = a.part_lse + (int64_t)seq * a.num_splits * a.num_q_heads + h;
+  const float* po = a.part_out + ((int64_t)seq * a.num_splits * a.num_q_heads + h) * a.head_dim + lane * VEC;
+  const int64_t lse_stride = a.num_q_heads, part_stride = (int64_t)a.num_q_heads * a.head_dim;
+  float mx = -INFINITY;
+  for (int p = threadIdx.x; p < a.num_splits; p += XCH_WARPS * 32) mx = fmaxf(mx, __ldg(lse + p * lse_stride));
+#pragma unroll
+  for (int x = 16; x > 0; x >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, x));
+  if (lane == 0) s_mx[warp] = mx;
+  __syncthreads();
+  mx = s_mx[0];
+#pragma unroll
+  for (int w = 1; w < XCH_WARPS; ++w) mx = fmaxf(mx, s_mx[w]);
+  float acc[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) acc[v] = 0.f;
+  float den = 0.f;
+  if (mx != -INFINITY) {
+    for (int p = warp; p < a.num_splits; p += 2 * XCH_WARPS) {      // two parts in flight a warp
+      const int p2 = p + XCH_WARPS;
+      const float l0 = __ldg(lse + p * lse_stride);
+      const float l1 = p2 < a.num_splits ? __ldg(lse + p2 * lse_stride) : -INFINITY;
+      const float w0 = l0 == -INFINITY ? 0.f : __expf(l0 - mx);
+      const float w1 = l1 == -INFINITY ? 0.f : __expf(l1 - mx);
+#pragma unroll
+      for (int v = 0; v < VEC; v += 2) {
+        float2 t0 = make_float2(0.f, 0.f), t1 = make_float2(0.f, 0.f);
+        if (w0 != 0.f) t0 = __ldg(reinterpret_cast<const float2*>(po + p * part_stride + v));
+        if (w1 != 0.f) t1 = __ldg(reinterpret_cast<const float2*>(po + p2 * part_stride + v));
+        acc[v] = fmaf(w1, t1.x, fmaf(w0, t0.x, acc[v]));
+        acc[v + 1] = fmaf(w1, t1.y, fmaf(w0, t0.y, acc[v + 1]));
+      }
+      den += w0 + w1;
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) s_acc[warp][lane * VEC + v] = acc[v];
+  if (lane == 0) s_acc[warp][32 * VEC] = den;
+  __syncthreads();
+  if (warp == 0) {
+    den = s_acc[0][32 * VEC];
+    for (int w = 1; w < XCH_WARPS; ++w) {   // fixed order: the same bits every call
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) acc[v] += s_acc[w][lane * VEC + v];
+      den += s_acc[w][32 * VEC];
+    }
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    const float out_lse = den > 0.f ? mx + __logf(den) : -INFINITY;
+    const int64_t row = ((int64_t)seq * a.num_q_heads + h) * a.head_dim + lane * VEC;
+    const int64_t lse_at = (int64_t)a.num_seqs * a.num_q_heads * a.head_dim + (int64_t)seq * a.num_q_heads + h;
+    for (int r = 0; r < a.world; ++r) {
+      float* g = a.gather[r] + half_off;
+#pragma unroll
+      for (int v = 0; v < VEC; v += 2) *reinterpret_cast<float2*>(g + row + v) = make_float2(acc[v] * inv, acc[v + 1] * inv);
+      if (lane == 0) g[lse_at] = out_lse;
+    }
+    // every store of this CTA is visible system-wide before it counts itself done; the last CTA raises the flags
+    __threadfence_system();
+    __syncwarp();
+    if (lane == 0) {
+      const uint32_t total = gridDim.x * gridDim.y;
+      if (atomicAdd(a.done, 1u) == total - 1) {
+        *a.done = 0u;
+        __threadfence_system();
+        for (int r = 0; r < a.world; ++r)
+          *reinterpret_cast<volatile uint32_t*>(a.flags[r] + (epoch & 1u) * 8 + a.rank) = epoch + 1u;
+        __threadfence_system();
+      }
+    }
+  }
+}
+
+struct XMergeArgs {
+  void* out;
+  int64_t out_stride_tok, out_stride_head;
+  int out_kind;            // 0 bf16, 2 fp16
+  const float* gather;     // this rank's gather buffer (own memory)
+  uint32_t* flags;         // this rank's flag block (own memory)
+  uint32_t* epoch;
+  uint32_t* done;          // CTA counter of this kernel (zero between launches)
+  int32_t* error;          // set to 1 + the rank whose record did not arrive in time
+  int world, num_q_heads, head_dim, num_seqs;
+  int64_t rec_floats;
+  int spin_limit;
+};
+
+template <int VEC>
+__global__ void __launch_bounds__(XCH_WARPS * 32) kvsplit_merge_kernel(const XMergeArgs a) {
+  __shared__ int s_ok;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.x * XCH_WARPS + warp, seq = blockIdx.y;
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch);
+  // one thread a rank polls that rank's flag of this step: bounded, and a miss is reported, not waited out
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < a.world) {
+    const volatile uint32_t* f = reinterpret_cast<const volatile uint32_t*>(a.flags + (epoch & 1u) * 8 + threadIdx.x);
+    int polls = 0;
+    while (*f != epoch + 1u) {
+      if (++polls > a.spin_limit) {
+        s_ok = 0;
+        atomicCAS(a.error, 0, 1 + (int)threadIdx.x);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  __threadfence_system();          // the records were written before the flags: order this CTA's reads after the flags
+  if (s_ok && h < a.num_q_heads) {
+    const float* base = a.gather + (int64_t)(epoch & 1u) * a.world * a.rec_floats;
+    const int64_t row = ((int64_t)seq * a.num_q_heads + h) * a.head_dim + lane * VEC;
+    const int64_t lse_at = (int64_t)a.num_seqs * a.num_q_heads * a.head_dim + (int64_t)seq * a.num_q_heads + h;
+    float lp[8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      lp[r] = r < a.world ? *reinterpret_cast<const volatile float*>(base + r * a.rec_floats + lse_at) : -INFINITY;
+      mx = fmaxf(mx, lp[r]);
+    }
+    float acc[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) acc[v] = 0.f;
+    float den = 0.f;
+    if (mx != -INFINITY) {
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (lp[r] == -INFINITY) continue;
+        const float w = __expf(lp[r] - mx);
+        const float* xp = base + r * a.rec_floats + row;
+#pragma unroll
+        for (int v = 0; v < VEC; v += 2) {
+          const float2 t = __ldcv(reinterpret_cast<const float2*>(xp + v));   // written by a peer: not through a stale cache line
+          acc[v] = fmaf(w, t.x, acc[v]);
+          acc[v + 1] = fmaf(w, t.y, acc[v + 1]);
+        }
+        den += w;
+      }
+    }
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    const int64_t off = (int64_t)seq * a.out_stride_tok + (int64_t)h * a.out_stride_head + lane * VEC;
+    if (a.out_kind == 2) {
+      __half* o = reinterpret_cast<__half*>(a.out) + off;
+#pragma unroll
+      for (int v = 0; v < VEC; v += 2) *reinterpret_cast<__half2*>(o + v) = __floats2half2_rn(acc[v] * inv, acc[v + 1] * inv);
+    } else {
+      __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out) + off;
+#pragma unroll
+      for (int v = 0; v < VEC; v += 2)
+        *reinterpret_cast<__nv_bfloat162*>(o + v) = __floats2bfloat162_rn(acc[v] * inv, acc[v + 1] * inv);
+    }
+  }
+  // the step is over on this rank when its last CTA is: the counter moves on for the next step
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t total = gridDim.x * gridDim.y;
+    if (atomicAdd(a.done, 1u) == total - 1) {
+      *a.done = 0u;
+      *reinterpret_cast<volatile uint32_t*>(a.epoch) = epoch + 1u;
+    }
+  }
+}
+
+static int64_t record_floats(int num_seqs, int num_q_heads, int head_dim) {
+  const int64_t n = (int64_t)num_seqs * num_q_heads * (head_dim + 1);
+  return (n + 3) / 4 * 4;
+}
+
+}  // namespace hkb
+
+extern "C" size_t hkb_exchange_gather_bytes(int world, int num_seqs, int num_q_heads, int head_dim) {
+  if (world < 1 || world > 8 || num_seqs <= 0 || num_q_heads <= 0 || head_dim <= 0) return 0;
+  return (size_t)(2 * world * hkb::record_floats(num_seqs, num_q_heads, head_dim)) * sizeof(float);
+}
+
+// two parity halves of eight flags, then the step counter, the two CTA counters and the error word
+extern "C" size_t hkb_exchange_state_bytes(void) { return (16 + 4) * sizeof(uint32_t); }
+
+extern "C" int hkb_kvsplit_push(hkb_exchange_t x, const float* part_out, const float* part_lse, int num_splits,
+                                int num_seqs, int num_q_heads, int head_dim, void* stream) {
+  using namespace hkb;
+  if (x.world < 1 || x.world > 8 || x.rank < 0 || x.rank >= x.world) return HKB_ERR_SIZE;
+  if (num_seqs < 0 || num_q_heads <= 0 || num_splits < 1 || num_splits > HKB_MAX_SPLITS) return HKB_ERR_SIZE;
+  if (num_seqs == 0) return HKB_OK;
+  if (num_seqs > 65535) return HKB_ERR_SIZE;
+  if (!part_out || !part_lse || !x.state[x.rank]) return HKB_ERR_NULL;
+  if (head_dim != 64 && head_dim != 128 && head_dim != 256) return HKB_ERR_HEAD_DIM;
+  if ((uintptr_t)part_out % 16) return HKB_ERR_ALIGN;
+  PushArgs a;
+  a.part_out = part_out; a.part_lse = part_lse;
+  a.num_splits = num_splits; a.num_q_heads = num_q_heads; a.head_dim = head_dim; a.num_seqs = num_seqs;
+  a.world = x.world; a.rank = x.rank;
+  for (int r = 0; r < 8; ++r) {
+    a.gather[r] = r < x.world ? static_cast<float*>(x.gather[r]) : nullptr;
+    a.flags[r] = r < x.world ? static_cast<uint32_t*>(x.state[r]) : nullptr;
+    if (r < x.world && (!a.gather[r] || !a.flags[r] || (uintptr_t)a.gather[r] % 16)) return HKB_ERR_NULL;
+  }
+  uint32_t* mine = static_cast<uint32_t*>(x.state[x.rank]);
+  a.epoch = mine + 16; a.done = mine + 17;
+  a.rec_floats = record_floats(num_seqs, num_q_heads, head_dim);
+  const dim3 grid(num_q_heads, num_seqs);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (head_dim == 128) kvsplit_push_kernel<4><<<grid, XCH_WARPS * 32, 0, st>>>(a);
+  else if (head_dim == 64) kvsplit_push_kernel<2><<<grid, XCH_WARPS * 32, 0, st>>>(a);
+  else kvsplit_push_kernel<8><<<grid, XCH_WARPS * 32, 0, st>>>(a);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
+  return HKB_OK;
+}
+
+extern "C" int hkb_kvsplit_merge(hkb_exchange_t x, void* out, int64_t out_stride_tok, int64_t out_stride_head, int out_kind,
+                                 int num_seqs, int num_q_heads, int head_dim, int spin_limit, void* stream) {
+  using namespace hkb;
+  if (x.world < 1 || x.world > 8 || x.rank < 0 || x.rank >= x.world) return HKB_ERR_SIZE;
+  if (num_seqs < 0 || num_q_heads <= 0 || spin_limit < 1) return HKB_ERR_SIZE;
+  if (num_seqs == 0) return HKB_OK;
+  if (num_seqs > 65535) return HKB_ERR_SIZE;
+  if (!out || !x.gather[x.rank] || !x.state[x.rank]) return HKB_ERR_NULL;
+  if (head_dim != 64 && head_dim != 128 && head_dim != 256) return HKB_ERR_HEAD_DIM;
+  if (out_kind != 0 && out_kind != 2) return HKB_ERR_DTYPE;
+  if ((out_stride_tok | out_stride_head) % 4) return HKB_ERR_STRIDE;
+  if ((uintptr_t)out % 8) return HKB_ERR_ALIGN;
+  XMergeArgs a;
+  a.out = out; a.out_stride_tok = out_stride_tok; a.out_stride_head = out_stride_head; a.out_kind = out_kind;
+  a.gather = static_cast<const float*>(x.gather[x.rank]);
+  uint32_t* mine = static_cast<uint32_t*>(x.state[x.rank]);
+  a.flags = mine; a.epoch = mine + 16; a.done = mine + 18; a.error = reinterpret_cast<int32_t*>(mine + 19);
+  a.world = x.world; a.num_q_heads = num_q_heads; a.head_dim = head_dim; a.num_seqs = num_seqs;
+  a.rec_floats = record_floats(num_seqs, num_q_heads, head_dim);
+  a.spin_limit = spin_limit;
+  const dim3 grid((num_q_heads + XCH_WARPS - 1) / XCH_WARPS, num_seqs);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (head_dim == 128) kvsplit_merge_kernel<4><<<grid, XCH_WARPS * 32, 0, st>>>(a);
+  else if (head_dim == 64) kvsplit_merge_kernel<2><<<grid, XCH_WARPS * 32, 0, st>>>(a);
+  else kvsplit_merge_kernel<8><<<grid, XCH_WARPS * 32, 0, st>>>(a);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
+  return HKB_OK;
+}

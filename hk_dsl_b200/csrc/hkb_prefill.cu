@@ -22,6 +22,7 @@
 #include "hkb_prefill_tc.cuh"
 
 #include <cstdlib>
+#include <cstring>
 
 extern thread_local int hkb_tls_cuda_error;
 
@@ -372,8 +373,57 @@ static int dispatch_prefill(const PrefillArgs& a, int num_work, cudaStream_t st)
 }
 
 // ---- the tensor-memory form (head_dim 128, 16-bit caches) ----
+
+// cuTensorMapEncodeTiled, fetched through the runtime so that the library links against no driver stub.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn tensor_map_encoder() {
+  static const EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      p = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// A 4-D tensor map of one paged cache (16-bit elements): head_dim innermost, then the token, kv-head
+// and block axes in order of increasing stride (whatever the layout: head-major pages, token-major
+// pages, K and V side by side). A copy is a box of 64 dims x 16 tokens of one head of one block, laid
+// down with the 128-byte swizzle. `pos` receives the coordinate index of (token, head, block). False
+// if the driver has no encoder or refuses the layout: the kernel then gathers with cp.async.
+static bool make_cache_map(CUtensorMap* m, const hkb_cache_t& c, int block_size, int num_kv_heads, int pos[3]) {
+  const EncodeTiledFn encode = tensor_map_encoder();
+  if (!encode) return false;
+  struct Axis { cuuint64_t size, stride; int role; } ax[3] = {
+      {(cuuint64_t)block_size, (cuuint64_t)c.stride_token * 2, 0},
+      {(cuuint64_t)num_kv_heads, (cuuint64_t)c.stride_head * 2, 1},
+      {(cuuint64_t)c.num_blocks, (cuuint64_t)c.stride_block * 2, 2}};
+  for (int i = 0; i < 3; ++i)
+    if (c.stride_token < 0 || c.stride_head < 0 || c.stride_block < 0 || ax[i].stride % 16 || ax[i].stride >= (1ull << 40) ||
+        ax[i].size == 0 || ax[i].size > (1ull << 32))
+      return false;
+  for (int i = 0; i < 3; ++i)          // three entries: a hand-rolled sort by stride
+    for (int j = i + 1; j < 3; ++j)
+      if (ax[j].stride < ax[i].stride) { const Axis t = ax[i]; ax[i] = ax[j]; ax[j] = t; }
+  cuuint64_t dims[4] = {128, ax[0].size, ax[1].size, ax[2].size};
+  cuuint64_t strides[3] = {ax[0].stride, ax[1].stride, ax[2].stride};
+  cuuint32_t box[4] = {64, 1, 1, 1}, elem[4] = {1, 1, 1, 1};
+  for (int i = 0; i < 3; ++i) {
+    pos[ax[i].role] = i + 1;
+    if (ax[i].role == 0) box[i + 1] = TILE_TOKENS;
+  }
+  return encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, c.ptr, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int GP, bool F16, bool TRACE = false>
-static int launch_prefill_tc(const tc::Args& a, int num_work, cudaStream_t st) {
+static int launch_prefill_tc(const tc::Args& a, const CUtensorMap& kmap, const CUtensorMap& vmap, int num_work, cudaStream_t st) {
   static bool armed[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -383,7 +433,7 @@ static int launch_prefill_tc(const tc::Args& a, int num_work, cudaStream_t st) {
   }
   if (e == cudaSuccess) {
     dim3 grid(num_work, a.num_kv_heads * (a.group / GP));
-    tc::prefill_tc_kernel<GP, F16, TRACE><<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(a);
+    tc::prefill_tc_kernel<GP, F16, TRACE><<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(a, kmap, vmap);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
@@ -391,11 +441,11 @@ static int launch_prefill_tc(const tc::Args& a, int num_work, cudaStream_t st) {
 }
 
 template <bool F16>
-static int dispatch_prefill_tc(const tc::Args& a, int num_work, cudaStream_t st) {
-  if (a.group % 8 == 0) return launch_prefill_tc<8, F16>(a, num_work, st);
-  if (a.group % 4 == 0) return launch_prefill_tc<4, F16>(a, num_work, st);
-  if (a.group % 2 == 0) return launch_prefill_tc<2, F16>(a, num_work, st);
-  return launch_prefill_tc<1, F16>(a, num_work, st);
+static int dispatch_prefill_tc(const tc::Args& a, const CUtensorMap& kmap, const CUtensorMap& vmap, int num_work, cudaStream_t st) {
+  if (a.group % 8 == 0) return launch_prefill_tc<8, F16>(a, kmap, vmap, num_work, st);
+  if (a.group % 4 == 0) return launch_prefill_tc<4, F16>(a, kmap, vmap, num_work, st);
+  if (a.group % 2 == 0) return launch_prefill_tc<2, F16>(a, kmap, vmap, num_work, st);
+  return launch_prefill_tc<1, F16>(a, kmap, vmap, num_work, st);
 }
 
 }  // namespace hkb
@@ -485,11 +535,21 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
     t.num_q_heads = a.num_q_heads; t.num_kv_heads = a.num_kv_heads; t.group = a.group; t.tiles_per_page = a.tiles_per_page;
     t.scale = a.scale;
     t.trace = g_trace_for_next_call;
+    // K and V blocks come by TMA where a tensor map describes the cache (HKB_PREFILL_NO_TMA=1: the cp.async gather, the comparison arm)
+    alignas(64) CUtensorMap kmap, vmap;
+    const char* no_tma = std::getenv("HKB_PREFILL_NO_TMA");
+    t.tma = !(no_tma && no_tma[0] == '1') && make_cache_map(&kmap, kc, block_size, num_kv_heads, t.k_pos) &&
+            make_cache_map(&vmap, vc, block_size, num_kv_heads, t.v_pos);
+    if (!t.tma) {
+      memset(&kmap, 0, sizeof(kmap)); memset(&vmap, 0, sizeof(vmap));
+      for (int i = 0; i < 3; ++i) t.k_pos[i] = t.v_pos[i] = i + 1;
+    }
     if (t.trace) {   // the traced build: the headline shape only (a bf16 cache, a GQA group of 4)
       if (kv_dtype != HKB_KV_BF16 || group % 4 || group % 8 == 0) return HKB_ERR_UNSUPPORTED;
-      return launch_prefill_tc<4, false, true>(t, num_work, st);
+      return launch_prefill_tc<4, false, true>(t, kmap, vmap, num_work, st);
     }
-    return kv_dtype == HKB_KV_F16 ? dispatch_prefill_tc<true>(t, num_work, st) : dispatch_prefill_tc<false>(t, num_work, st);
+    return kv_dtype == HKB_KV_F16 ? dispatch_prefill_tc<true>(t, kmap, vmap, num_work, st)
+                                  : dispatch_prefill_tc<false>(t, kmap, vmap, num_work, st);
   }
   if (fp8) return dispatch_prefill<128, true>(a, num_work, st);
   if (kv_dtype == HKB_KV_F16) {

@@ -7,54 +7,60 @@
 //
 // One CTA an SM works on one item: 2 query tiles of 128 rows each -- a tile is T = 128 / GP
 // consecutive tokens of GP query heads of one kv head, so both tiles and all their heads share
-// every K/V block the CTA stages -- and walks the keys in blocks of 64:
+// every K/V block the CTA stages -- and walks the keys in blocks of 128:
 //
-//   producers (2 warps)  gather the block's 16-token pages through the block table into a ring of
-//                        16 KB shared-memory slots with cp.async, rows of 128 bytes XOR-swizzled
-//                        the way the tensor core reads them (K blocks and V blocks alternate in
-//                        the ring), make them visible to the async proxy and arrive on the slot's
-//                        mbarrier;
-//   MMA warp (1 thread)  S = Q K^T for both tiles (8 tcgen05.mma of 128 x 64 x 16, Q and K from
-//                        shared memory) into two alternating 64-column TMEM buffers a tile, and
-//                        O += P V (4 tcgen05.mma of 128 x 128 x 16, P from TMEM, V from shared
-//                        memory read MN-major) into the tile's 128 accumulator columns; completion
-//                        is signalled by tcgen05.commit onto mbarriers;
-//   softmax (2 x 4 warps) a thread owns one query row: it reads its 64 scores from TMEM
+//   producers (2 warps)  gather the block's eight 16-token pages through the block table into a ring
+//                        of 32 KB shared-memory slots (one warp the K blocks, one the V blocks,
+//                        alternating in the ring): sixteen TMA tile copies a block
+//                        (cp.async.bulk.tensor over a 4-D map of the cache, 16 tokens x 64 dims a
+//                        copy, 128-byte swizzle, completion counted in bytes on the slot's
+//                        mbarrier), one lane a copy. The block that holds the last keys -- where
+//                        rows past the end must read as zeros -- and caches no tensor map describes
+//                        go through cp.async with the same swizzle, a proxy fence and an arrive;
+//   MMA warp (1 thread)  S = Q K^T (8 tcgen05.mma of 128 x 128 x 16, Q and K from shared memory)
+//                        into the tile's 128 score columns of TMEM, and O += P V (8 tcgen05.mma of
+//                        128 x 128 x 16, P from TMEM, V from shared memory read MN-major) into its
+//                        128 accumulator columns; the two tiles take turns on the tensor pipe: a
+//                        tile's P V product and its next block's scores are issued as soon as its
+//                        softmax warps hand P over, while the other tile's warps are in their
+//                        exponentials; completion is signalled by tcgen05.commit onto mbarriers;
+//   softmax (2 x 4 warps) a thread owns one query row: it reads its 128 scores from TMEM
 //                        (tcgen05.ld), masks the diagonal block, keeps the running maximum lazily
 //                        (the accumulator is rescaled only when a block's maximum exceeds the
 //                        reference by 2^8), writes P as packed 16-bit pairs over the scores it has
-//                        just read (tcgen05.st) and arrives; no shuffles: a row is a TMEM lane.
+//                        read (tcgen05.st) and arrives; no shuffles: a row is a TMEM lane.
 //
-// While the softmax warps of one tile work on block j, the tensor core computes block j+1's scores
-// and the other tile's products. Every wait is bounded: a barrier that does not flip within about a
-// second sets an error word (hkb_prefill_tc_error) and the CTA winds down -- its copies drained,
-// its TMEM freed -- instead of spinning.
+// All 512 TMEM columns are in use (two accumulators, two score tiles), which is why P lives where
+// the scores were. Every wait is bounded: a barrier that does not flip within about a second sets
+// an error word (hkb_prefill_tc_error) and the CTA winds down -- its copies drained, its TMEM
+// freed -- instead of spinning.
 #pragma once
+
+#include <cuda.h>   // CUtensorMap (the type only: the encoder is fetched through the runtime)
 
 #include "hkb_common.cuh"
 
 namespace hkb {
 namespace tc {
 
-constexpr int KVB = 64;                       // keys a block
+constexpr int KVB = 128;                      // keys a block
 constexpr int ROWS = 128;                     // rows of a query tile = TMEM lanes
 constexpr int D = 128;                        // head_dim
 constexpr int HALF_BYTES_Q = ROWS * 128;      // 64 dims of 128 rows, 128-byte rows
 constexpr int Q_BYTES = 2 * HALF_BYTES_Q;     // one query tile: 32 KB
-constexpr int HALF_BYTES_KV = KVB * 128;      // 64 dims of 64 tokens
-constexpr int SLOT_BYTES = 2 * HALF_BYTES_KV; // a K or a V block: 16 KB
-constexpr int NSLOT = 8;                      // ring slots: K blocks in the even ones, V blocks in the odd ones
-constexpr int LAG = 3;                        // copy groups a producer warp keeps in flight
+constexpr int HALF_BYTES_KV = KVB * 128;      // 64 dims of 128 tokens
+constexpr int SLOT_BYTES = 2 * HALF_BYTES_KV; // a K or a V block: 32 KB
+constexpr int NSLOT = 4;                      // ring slots: K blocks in the even ones, V blocks in the odd ones
 constexpr int SOFTMAX_WARPS = 8, MMA_WARP = 8, K_WARP = 9, V_WARP = 10, WARPS = 11;
 constexpr int THREADS = WARPS * 32;
 constexpr int TMEM_COLS = 512;
-// TMEM columns: O of tile 0 and 1, then two score buffers a tile (P is written over the scores)
+// TMEM columns: O of tile 0 and 1, then the scores of tile 0 and 1 (P is written over the scores)
 __host__ __device__ constexpr int o_col(int tile) { return tile * 128; }
-__host__ __device__ constexpr int s_col(int tile, int buf) { return 256 + tile * 128 + buf * 64; }
+__host__ __device__ constexpr int s_col(int tile) { return 256 + tile * 128; }
 
 struct Bars {                                  // mbarriers, 8 bytes each
   uint64_t full[NSLOT], empty[NSLOT];
-  uint64_t s_full[2][2], p_full[2][2], o_done[2], q_full[2];
+  uint64_t s_full[2], p_full[2], o_done[2], q_full[2];
   uint32_t tmem_base;
   int abort;
 };
@@ -75,6 +81,16 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.shared::cta.b64 st, [%0];\n}\n" ::"r"(bar) : "memory");
+}
+// one arrival that also announces `bytes` of asynchronous copies to come (the phase completes when they have landed)
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n}\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+// One TMA tile copy, global -> this CTA's shared memory, bytes counted on `bar`. No multicast. The
+// innermost coordinate times the element size is a multiple of 16 bytes (0 or 64 elements here).
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
+               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -203,14 +219,17 @@ struct Args {
   const int* work;
   int num_q_heads, num_kv_heads, group, tiles_per_page;
   float scale;
+  int tma;                  // K and V blocks by TMA (the two tensor maps are valid)
+  int k_pos[3], v_pos[3];   // which coordinate of the map (1..3) is the token, the kv head, the block
   unsigned long long* trace;   // TRACE builds only: 32 cycle counters a CTA (see Lap), else unused
 };
 
 // Where a CTA's cycles go, for the traced build (hkb_paged_prefill_trace): one thread of each role
 // adds the clocks between consecutive laps to a counter. Slots: softmax of tile g at 8 g + {0 wait
-// for the scores, 1 TMEM load, 2 maximum and exponentials, 3 wait for the previous product (and the
+// for the scores, 1 TMEM loads and maximum, 2 exponentials, 3 wait for the previous product (and the
 // rescale), 4 P store and arrive, 5 epilogue}; MMA warp 16 wait for Q, 17 wait for K, 18 issue of the
-// score products, 19 wait for V, 20 / 22 wait for P of tile 0 / 1, 21 issue of the P V products;
+// first score products, 19 wait for V, 20 / 22 wait for P of tile 0 / 1, 21 issue of the P V products
+// and the next block's scores;
 // producers 24 + 4 w + {0 wait for a free slot, 1 issue of the copies, 2 wait for copies to land};
 // 31 the CTA's whole time.
 template <bool TRACE>
@@ -222,11 +241,12 @@ struct Lap {
   }
 };
 
-// A producer warp's copy of one 64-token block (K or V) into a ring slot: 64 rows x 16 chunks of
-// 16 bytes, 32 copies a lane. Rows at or past `kv_limit` are zero-filled, never read.
-__device__ __forceinline__ void fill_slot(const Args& a, uint32_t slot, const uint8_t* base, int64_t sb, int64_t st,
+// Half of a 128-token block (64 rows: four 16-token pages) of K or of V into a ring slot, by one
+// producer warp: 64 rows x 16 chunks of 16 bytes, 32 copies a lane. Rows at or past `kv_limit` are
+// zero-filled, never read.
+__device__ __forceinline__ void fill_half(const Args& a, uint32_t slot, const uint8_t* base, int64_t sb, int64_t st,
                                           const int* table_row, int kv0, int kv_limit, int lane) {
-  // the block's four 16-token tiles: page id and offset of each, one lane a tile
+  // the four 16-token tiles: page id and offset of each, one lane a tile
   int my_id = 0, my_sub = 0;
   if (lane < 4) {
     const int tile = kv0 / TILE_TOKENS + lane;
@@ -236,23 +256,84 @@ __device__ __forceinline__ void fill_slot(const Args& a, uint32_t slot, const ui
       my_sub = tile % a.tiles_per_page;
     }
   }
-  const int c = lane & 15, half = c >> 3, cc = c & 7;
+  const int c = lane & 15, hi = lane >> 4;
+  // where this lane's chunk lands inside an 8-row group, for the four row phases it meets
+  uint32_t x[4];
 #pragma unroll
-  for (int t = 0; t < 4; ++t) {
-    const int id = __shfl_sync(0xffffffffu, my_id, t), sub = __shfl_sync(0xffffffffu, my_sub, t);
-    const uint8_t* p = base + (int64_t)id * sb + (int64_t)(sub * TILE_TOKENS) * st + c * 16;
+  for (int q = 0; q < 4; ++q) x[q] = (uint32_t)((c >> 3) * HALF_BYTES_KV + (((c & 7) ^ ((2 * q + hi) & 7)) << 4));
+  const uint32_t dst0 = slot + (uint32_t)((kv0 % KVB) + hi) * 128;
+  const int64_t lane_off = (int64_t)hi * st + c * 16, step = 2 * st;
+  if (kv0 + 64 <= kv_limit) {                     // every row is a key: nothing to predicate
 #pragma unroll
-    for (int it = 0; it < 8; ++it) {
-      const int r = t * 16 + it * 2 + (lane >> 4);                    // row of the block
-      const uint32_t dst = slot + half * HALF_BYTES_KV + r * 128 + ((cc ^ (r & 7)) << 4);
-      if (kv0 + r < kv_limit) cp_async16(dst, p + (int64_t)(it * 2 + (lane >> 4)) * st);
-      else asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(dst), "r"(0u) : "memory");
+    for (int t = 0; t < 4; ++t) {
+      const int id = __shfl_sync(0xffffffffu, my_id, t), sub = __shfl_sync(0xffffffffu, my_sub, t);
+      const uint8_t* p = base + (int64_t)id * sb + (int64_t)(sub * TILE_TOKENS) * st + lane_off;
+#pragma unroll
+      for (int it = 0; it < 8; ++it) cp_async16(dst0 + (t * 16 + it * 2) * 128 + x[it & 3], p + it * step);
+    }
+  } else {
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int id = __shfl_sync(0xffffffffu, my_id, t), sub = __shfl_sync(0xffffffffu, my_sub, t);
+      const uint8_t* p = base + (int64_t)id * sb + (int64_t)(sub * TILE_TOKENS) * st + lane_off;
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const uint32_t dst = dst0 + (t * 16 + it * 2) * 128 + x[it & 3];
+        if (kv0 + t * 16 + it * 2 + hi < kv_limit) cp_async16(dst, p + it * step);
+        else asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(dst), "r"(0u) : "memory");
+      }
     }
   }
 }
 
+// One half (64 columns) of a score row: causal mask, then either the maximum (MATH = 0) or the
+// exponentials, their sum and the packed 16-bit P (MATH = 1).
+template <bool F16>
+__device__ __forceinline__ float half_max(float (&s)[64], bool masked, bool valid, int key0, int pos) {
+  if (masked) {
+#pragma unroll
+    for (int i = 0; i < 64; ++i)
+      if (!valid || key0 + i > pos) s[i] = -INFINITY;
+  }
+  float mq[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {          // four independent chains of three-input max
+    mq[c] = max3(s[16 * c], s[16 * c + 1], s[16 * c + 2]);
+#pragma unroll
+    for (int i = 3; i < 15; i += 2) mq[c] = max3(mq[c], s[16 * c + i], s[16 * c + i + 1]);
+    mq[c] = fmaxf(mq[c], s[16 * c + 15]);
+  }
+  return fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
+}
+template <bool F16>
+__device__ __forceinline__ float half_exp(float (&s)[64], bool masked, bool valid, int key0, int pos, float qs, float off,
+                                          uint32_t (&p)[32]) {
+  if (masked) {
+#pragma unroll
+    for (int i = 0; i < 64; ++i)
+      if (!valid || key0 + i > pos) s[i] = -INFINITY;
+  }
+  // p = exp2(s * qs - m): packed fp32 pairs for the multiply-add and the sums (four chains), one
+  // MUFU a value, a packed convert a pair
+  const uint64_t qs2 = pack2(qs, qs), off2 = pack2(off, off);
+  uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float x0, x1;
+    unpack2(fma2(pack2(s[2 * i], s[2 * i + 1]), qs2, off2), x0, x1);
+    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+    acc[i & 3] = add2(acc[i & 3], pack2(p0, p1));
+    if (F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(p[i]) : "f"(p1), "f"(p0));
+    else asm("cvt.rn.bf16x2.f32 %0, %1, %2;\n" : "=r"(p[i]) : "f"(p1), "f"(p0));
+  }
+  float a0, a1;
+  unpack2(add2(add2(acc[0], acc[1]), add2(acc[2], acc[3])), a0, a1);
+  return a0 + a1;
+}
+
 template <int GP, bool F16, bool TRACE = false>
-__global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a) {
+__global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kmap,
+                                                                const __grid_constant__ CUtensorMap vmap) {
   extern __shared__ uint8_t raw_smem[];
   unsigned long long tr[8] = {0, 0, 0, 0, 0, 0, 0, 0};      // this thread's lap counters (TRACE builds)
   const long long t_begin = TRACE ? now() : 0;
@@ -288,11 +369,13 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a) {
   const int kv_limit = min(seq_len, ctx + min(row0 + 2 * T, q_len));
   const int n = max(nblk[0], nblk[1]);
 
-  // ---- set-up: barriers, TMEM, the query tiles ----
+  // ---- set-up: barriers and TMEM (the query tiles are staged by the softmax warps, below) ----
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NSLOT; ++i) { mbar_init(HKB_BAR(full) + 8 * i, 32); mbar_init(HKB_BAR(empty) + 8 * i, 1); }
-    for (int i = 0; i < 4; ++i) { mbar_init(HKB_BAR(s_full) + 8 * i, 1); mbar_init(HKB_BAR(p_full) + 8 * i, ROWS); }
-    for (int i = 0; i < 2; ++i) { mbar_init(HKB_BAR(o_done) + 8 * i, 1); mbar_init(HKB_BAR(q_full) + 8 * i, ROWS); }
+    for (int i = 0; i < NSLOT; ++i) { mbar_init(HKB_BAR(full) + 8 * i, 1); mbar_init(HKB_BAR(empty) + 8 * i, 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(HKB_BAR(s_full) + 8 * i, 1); mbar_init(HKB_BAR(p_full) + 8 * i, ROWS);
+      mbar_init(HKB_BAR(o_done) + 8 * i, 1); mbar_init(HKB_BAR(q_full) + 8 * i, ROWS);
+    }
     bars->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -333,7 +416,8 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a) {
       mbar_arrive(HKB_BAR(q_full) + 8 * g);
     }
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    const int tok = row0 + g * T + row % T, hq = hbase + row / T;
+    const uint32_t s_addr = lane_addr + s_col(g);
+    const int tok = row0 + g * T + row % T;
     const bool valid = tok < q_len;
     const int pos = ctx + tok;                              // the last key this row sees
     const float qs = a.scale * LOG2E;
@@ -341,31 +425,20 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a) {
     const int nb = nblk[g];
     bool ok = true;
     for (int j = 0; j < nb && ok; ++j) {
-      const int b = j & 1;
       Lap<TRACE> lap;
-      ok = warp_wait(HKB_BAR(s_full) + 8 * (g * 2 + b), (j >> 1) & 1, abort, 1);
+      ok = warp_wait(HKB_BAR(s_full) + 8 * g, j & 1, abort, 1);
       if (!ok) break;
       lap(tr[0]);
       tc_fence_after();
-      float s[KVB];
-      tmem_ld64(lane_addr + s_col(g, b), s);
-      lap(tr[1]);
       const int kv0 = j * KVB;
-      if (!valid || kv0 + KVB - 1 > pos) {                   // the diagonal block, or a row past the request
-#pragma unroll
-        for (int i = 0; i < KVB; ++i)
-          if (!valid || kv0 + i > pos) s[i] = -INFINITY;
-      }
-      // the row maximum: four independent chains of three-input max
-      float mq[4];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        mq[c] = max3(s[16 * c], s[16 * c + 1], s[16 * c + 2]);
-#pragma unroll
-        for (int i = 3; i < 15; i += 2) mq[c] = max3(mq[c], s[16 * c + i], s[16 * c + i + 1]);
-        mq[c] = fmaxf(mq[c], s[16 * c + 15]);
-      }
-      const float mx = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])) * qs;    // qs > 0
+      const bool masked = !valid || kv0 + KVB - 1 > pos;     // the diagonal block, or a row past the request
+      float s[64];
+      // pass 1: the row maximum over both halves
+      tmem_ld64(s_addr, s);
+      float mx = half_max<F16>(s, masked, valid, kv0, pos);
+      tmem_ld64(s_addr + 64, s);
+      mx = fmaxf(mx, half_max<F16>(s, masked, valid, kv0 + 64, pos)) * qs;     // qs > 0
+      lap(tr[1]);
       // lazy reference: it moves only when a block's maximum exceeds it by 2^8 (P <= 256 fits 16 bits)
       const bool need = mx > m + 8.f;
       const bool any_need = __any_sync(0xffffffffu, need);
@@ -375,28 +448,14 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a) {
         m = mx;
       }
       const float off = (m == -INFINITY) ? 0.f : -m;
-      // p = exp2(s * qs - m): packed fp32 pairs for the multiply-add and the sums (four chains), one
-      // MUFU a value, a packed convert a pair
-      const uint64_t qs2 = pack2(qs, qs), off2 = pack2(off, off);
-      uint32_t p[32];
-      uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        float x0, x1;
-        unpack2(fma2(pack2(s[2 * i], s[2 * i + 1]), qs2, off2), x0, x1);
-        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-        acc[i & 3] = add2(acc[i & 3], pack2(p0, p1));
-        if (F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(p[i]) : "f"(p1), "f"(p0));
-        else asm("cvt.rn.bf16x2.f32 %0, %1, %2;\n" : "=r"(p[i]) : "f"(p1), "f"(p0));
-      }
-      float sum;
-      {
-        float a0, a1;
-        unpack2(add2(add2(acc[0], acc[1]), add2(acc[2], acc[3])), a0, a1);
-        sum = a0 + a1;
-      }
+      // pass 2: the second half is still in registers; P of keys 64..127 goes to columns 32..63, which
+      // held scores of the first half -- read again below before anything is written there
+      uint32_t p_hi[32], p_lo[32];
+      float sum = half_exp<F16>(s, false, valid, kv0 + 64, pos, qs, off, p_hi);
+      tmem_ld64(s_addr, s);
+      sum += half_exp<F16>(s, masked, valid, kv0, pos, qs, off, p_lo);
       l = l * alpha + sum;
-      if (TRACE) asm volatile("" ::"r"(p[0]), "r"(p[31]), "f"(l));   // the math is done before the lap is taken
+      if (TRACE) asm volatile("" ::"r"(p_lo[0]), "r"(p_hi[31]), "f"(l));   // the math is done before the lap is taken
       lap(tr[2]);
       if (j > 0) {
         // the tile's previous product has landed: O may be touched, and stays untouched until P arrives
@@ -416,10 +475,11 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a) {
         }
       }
       lap(tr[3]);
-      tmem_st32(lane_addr + s_col(g, b), p);                  // P over the first 32 columns of the scores just read
+      tmem_st32(s_addr, p_lo);                                // P over the first 64 columns of the scores
+      tmem_st32(s_addr + 32, p_hi);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(HKB_BAR(p_full) + 8 * (g * 2 + b));
+      mbar_arrive(HKB_BAR(p_full) + 8 * g);
       lap(tr[4]);
     }
     Lap<TRACE> lap_end;
@@ -479,100 +539,121 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a) {
     for (int t = 0; t < 2 && ok; ++t)
       if (nblk[t] > 0) ok = warp_wait(HKB_BAR(q_full) + 8 * t, 0, abort, 8);   // the tile's query rows are in place
     lap(tr[0]);
-    auto scores = [&](int j) {    // S_t(j) = Q_t K_j^T for the tiles that reach block j
-      const int slot = (2 * j) % NSLOT;
-      ok = warp_wait(HKB_BAR(full) + 8 * slot, ((2 * j) / NSLOT) & 1, abort, 4);
-      if (!ok) return;
-      lap(tr[1]);
-      tc_fence_after();
-      if (lane == 0) {
-        const uint32_t kaddr = ring + slot * SLOT_BYTES;
-        // the eight products of a tile accumulate into one TMEM tile, a dependent chain: the two tiles'
-        // chains are issued alternately so that one's latency hides behind the other's work
+    // S_t(j) = Q_t K_j^T: eight products (two 64-dim halves x four 16-dim steps) into the tile's score columns
+    auto scores = [&](int t, int j) {
+      const uint32_t kaddr = ring + ((2 * j) % NSLOT) * SLOT_BYTES;
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
+      for (int h = 0; h < 2; ++h)
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {       // 16 dims = 32 bytes a step inside the 128-byte row
-            const uint64_t kd = smem_desc(kaddr + h * HALF_BYTES_KV + ks * 32, 16);
-#pragma unroll
-            for (int t = 0; t < 2; ++t)
-              if (j < nblk[t])
-                umma_ss(tmem + s_col(t, j & 1), smem_desc(q_smem + t * Q_BYTES + h * HALF_BYTES_Q + ks * 32, 16), kd, IDESC_S,
-                        (h | ks) ? 1u : 0u);
-          }
-#pragma unroll
-        for (int t = 0; t < 2; ++t)
-          if (j < nblk[t]) tc_commit(HKB_BAR(s_full) + 8 * (t * 2 + (j & 1)));
-        tc_commit(HKB_BAR(empty) + 8 * slot);   // the K block is free once these products are done
-      }
-      __syncwarp();
-      lap(tr[2]);
+        for (int ks = 0; ks < 4; ++ks)           // 16 dims = 32 bytes a step inside the 128-byte row
+          umma_ss(tmem + s_col(t), smem_desc(q_smem + t * Q_BYTES + h * HALF_BYTES_Q + ks * 32, 16),
+                  smem_desc(kaddr + h * HALF_BYTES_KV + ks * 32, 16), IDESC_S, (h | ks) ? 1u : 0u);
+      tc_commit(HKB_BAR(s_full) + 8 * t);
     };
-    if (ok) scores(0);
+    auto wait_block = [&](int use, int code) {     // block `use` of the ring (2 j: K_j, 2 j + 1: V_j) has landed
+      ok = warp_wait(HKB_BAR(full) + 8 * (use % NSLOT), (use / NSLOT) & 1, abort, code);
+      tc_fence_after();
+    };
+    if (ok) wait_block(0, 4);
+    lap(tr[1]);
+    if (ok && lane == 0) {
+      for (int t = 0; t < 2; ++t)
+        if (nblk[t] > 0) scores(t, 0);
+      // K_0's slot is handed back at once: the producer publishes K_1 only after it has issued K_2,
+      // which goes into this slot
+      tc_commit(HKB_BAR(empty) + 8 * 0);
+    }
+    __syncwarp();
+    lap(tr[2]);
     for (int j = 0; j < n && ok; ++j) {
-      if (j + 1 < n) scores(j + 1);
-      if (!ok) break;
-      const int slot = (2 * j + 1) % NSLOT;
-      ok = warp_wait(HKB_BAR(full) + 8 * slot, ((2 * j + 1) / NSLOT) & 1, abort, 5);
+      wait_block(2 * j + 1, 5);                    // V_j
       if (!ok) break;
       lap(tr[3]);
-      const uint32_t vaddr = ring + slot * SLOT_BYTES;
+      if (j + 1 < n) wait_block(2 * j + 2, 4);     // K_{j+1}
+      if (!ok) break;
+      lap(tr[1]);
+      const uint32_t vaddr = ring + ((2 * j + 1) % NSLOT) * SLOT_BYTES;
       for (int t = 0; t < 2 && ok; ++t) {
         if (j >= nblk[t]) continue;
-        ok = warp_wait(HKB_BAR(p_full) + 8 * (t * 2 + (j & 1)), (j >> 1) & 1, abort, 6);
+        ok = warp_wait(HKB_BAR(p_full) + 8 * t, j & 1, abort, 6);
+        if (!ok) break;
         lap(tr[t ? 6 : 4]);
-      }
-      if (!ok) break;
-      tc_fence_after();
-      if (lane == 0) {
-        // both tiles' P are in place: their two chains of four products, alternately
+        tc_fence_after();
+        if (lane == 0) {
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {         // 16 tokens a step: 8 TMEM columns of P, 16 rows of V
-          const uint64_t vd = smem_desc(vaddr + ks * 16 * 128, HALF_BYTES_KV);
-#pragma unroll
-          for (int t = 0; t < 2; ++t)
-            if (j < nblk[t]) umma_ts(tmem + o_col(t), tmem + s_col(t, j & 1) + ks * 8, vd, IDESC_PV, (j | ks) ? 1u : 0u);
+          for (int ks = 0; ks < 8; ++ks)           // 16 tokens a step: 8 TMEM columns of P, 16 rows of V
+            umma_ts(tmem + o_col(t), tmem + s_col(t) + ks * 8, smem_desc(vaddr + ks * 16 * 128, HALF_BYTES_KV), IDESC_PV,
+                    (j | ks) ? 1u : 0u);
+          tc_commit(HKB_BAR(o_done) + 8 * t);
+          // the tile's next scores go over the P just consumed: the tensor pipe runs products in the order issued
+          if (j + 1 < nblk[t]) scores(t, j + 1);
         }
-#pragma unroll
-        for (int t = 0; t < 2; ++t)
-          if (j < nblk[t]) tc_commit(HKB_BAR(o_done) + 8 * t);
+        __syncwarp();
+        lap(tr[5]);
       }
-      __syncwarp();
-      lap(tr[5]);
-      if (ok && lane == 0) tc_commit(HKB_BAR(empty) + 8 * slot);
+      if (ok && lane == 0) {
+        tc_commit(HKB_BAR(empty) + 8 * ((2 * j + 1) % NSLOT));                 // V_j
+        if (j + 1 < n) tc_commit(HKB_BAR(empty) + 8 * ((2 * j + 2) % NSLOT));  // K_{j+1}
+      }
       __syncwarp();
     }
     if (TRACE && lane == 0)
       for (int i = 0; i < 7; ++i) a.trace[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 32 + 16 + i] = tr[i];
   } else {
-    // ================= producers: warp K_WARP fills the K blocks, warp V_WARP the V blocks =================
+    // ================= producers: warp K_WARP brings the K blocks, warp V_WARP the V blocks =================
     const int which = warp - K_WARP;   // 0: K, 1: V
     const uint8_t* src = (which ? a.v + (int64_t)kvh * a.v_stride_head : a.k + (int64_t)kvh * a.k_stride_head);
     const int64_t sb = which ? a.v_stride_block : a.k_stride_block, st = which ? a.v_stride_token : a.k_stride_token;
+    const void* map = which ? static_cast<const void*>(&vmap) : static_cast<const void*>(&kmap);
+    const int p_tok = which ? a.v_pos[0] : a.k_pos[0], p_head = which ? a.v_pos[1] : a.k_pos[1],
+              p_blk = which ? a.v_pos[2] : a.k_pos[2];
     const int* table_row = a.block_table + (int64_t)req * a.table_stride;
     bool ok = true;
-    auto publish = [&](int j) {        // block j's copies of this lane have landed: hand the slot over
-      fence_async_smem();
-      mbar_arrive(HKB_BAR(full) + 8 * ((2 * j + which) % NSLOT));
-    };
-    int issued = 0;
     for (int j = 0; j < n && ok; ++j) {
       const int use = 2 * j + which, slot = use % NSLOT, lap = use / NSLOT;
+      const uint32_t slot_addr = ring + slot * SLOT_BYTES, bar = HKB_BAR(full) + 8 * slot;
+      const int kv0 = j * KVB;
       Lap<TRACE> tick;
       if (lap > 0) ok = warp_wait(HKB_BAR(empty) + 8 * slot, (lap - 1) & 1, abort, 7);
       if (!ok) break;
       tick(tr[0]);
-      fill_slot(a, ring + slot * SLOT_BYTES, src, sb, st, table_row, j * KVB, kv_limit, lane);
-      cp_async_commit();
-      ++issued;
-      tick(tr[1]);
-      if (j >= LAG - 1) { cp_async_wait<LAG - 1>(); publish(j - (LAG - 1)); }
+      if (a.tma && kv0 + KVB <= kv_limit) {
+        // all 128 rows are keys: 8 pages x 2 halves = 16 tile copies, one a lane
+        int id = 0, sub = 0;
+        if (lane < 8) {
+          const int tile = kv0 / TILE_TOKENS + lane;
+          const int page = min(tile / a.tiles_per_page, a.max_pages - 1);
+          id = min(max(__ldg(table_row + page), 0), a.num_blocks - 1);
+          sub = tile % a.tiles_per_page;
+        }
+        const int t = (lane >> 1) & 7;
+        id = __shfl_sync(0xffffffffu, id, t);
+        sub = __shfl_sync(0xffffffffu, sub, t);
+        if (lane == 0) mbar_arrive_expect_tx(bar, SLOT_BYTES);
+        __syncwarp();
+        if (lane < 16) {
+          int c[4];
+          c[0] = (lane & 1) * 64;
+          c[p_tok] = sub * TILE_TOKENS;
+          c[p_head] = kvh;
+          c[p_blk] = id;
+          tma_load_4d(slot_addr + (lane & 1) * HALF_BYTES_KV + t * TILE_TOKENS * 128, map, bar, c[0], c[1], c[2], c[3]);
+        }
+        tick(tr[1]);
+      } else {
+        // the block with the last keys (rows past them are zero-filled), or no tensor map: cp.async
+        fill_half(a, slot_addr, src, sb, st, table_row, kv0, kv_limit, lane);
+        fill_half(a, slot_addr, src, sb, st, table_row, kv0 + 64, kv_limit, lane);
+        cp_async_commit();
+        tick(tr[1]);
+        cp_async_wait<0>();
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar);
+      }
       tick(tr[2]);
     }
-    // drain: whatever was issued lands before the CTA leaves, and is handed over if all is well
     cp_async_wait<0>();
-    if (ok)
-      for (int j = max(0, issued - (LAG - 1)); j < issued; ++j) publish(j);
     if (TRACE && lane == 0)
       for (int i = 0; i < 3; ++i) a.trace[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 32 + 24 + 4 * which + i] = tr[i];
   }

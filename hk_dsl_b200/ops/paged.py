@@ -332,11 +332,15 @@ def decode_step_record(rec_out: torch.Tensor, rec_lse: torch.Tensor, query: torc
     holds the sequences' last position) and a merge of its splits into the rank's record --
     `rec_out` `(seqs, q_heads, head_dim)` fp32 normalised and `rec_lse` `(seqs, q_heads)` fp32
     natural-log sum-exp (-inf where the rank holds nothing of a sequence). Two launches.
-    `merge_partials` (or `SplitKVDecoder.merge`) folds the gathered records of all ranks."""
+    `merge_partials` (or `SplitKVDecoder.merge`) folds the gathered records of all ranks.
+    `rec_out` = `rec_lse` = None: the walk alone, one launch; the split partials stay in `scratch`
+    for `PeerExchange.push` to fold."""
     n = local_lens.shape[0]
     _, hq, d = query.shape
-    if rec_out.dtype != torch.float32 or rec_lse.dtype != torch.float32 or not rec_out.is_contiguous() \
-            or not rec_lse.is_contiguous() or rec_out.numel() < n * hq * d or rec_lse.numel() < n * hq:
+    walk_only = rec_out is None and rec_lse is None      # the partials stay in `scratch` for the caller to fold
+    if not walk_only and (rec_out is None or rec_lse is None or rec_out.dtype != torch.float32
+                          or rec_lse.dtype != torch.float32 or not rec_out.is_contiguous()
+                          or not rec_lse.is_contiguous() or rec_out.numel() < n * hq * d or rec_lse.numel() < n * hq):
         raise ValueError(f"hk.ops.paged: the record is contiguous fp32 ({n}, {hq}, {d}) and ({n}, {hq})")
     if num_splits < 2:
         raise ValueError("hk.ops.paged: a record is written by the merge of at least two splits")
@@ -349,7 +353,7 @@ def decode_step_record(rec_out: torch.Tensor, rec_lse: torch.Tensor, query: torc
     fp8 = code == _lib.KV_FP8_E4M3
     po, pl, _ = _scratch_ptrs(scratch, n, hq, d, num_splits, query.device)
     rc = _lib.load().hkb_decode_step_record(
-        rec_out.data_ptr(), rec_lse.data_ptr(), query.data_ptr(), query.stride(0), query.stride(1), *new,
+        None if walk_only else rec_out.data_ptr(), None if walk_only else rec_lse.data_ptr(), query.data_ptr(), query.stride(0), query.stride(1), *new,
         _cache_t(key_cache), _cache_t(value_cache), block_tables.data_ptr(), block_tables.stride(0),
         block_tables.shape[1], local_lens.data_ptr(), qsl, n, hq, hkv, d, bs, float(scale), code,
         _scale_ptr(k_scale, fp8, "k_scale"), _scale_ptr(v_scale, fp8, "v_scale"), num_splits,

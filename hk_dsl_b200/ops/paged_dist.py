@@ -64,6 +64,80 @@ def record_floats(num_seqs: int, num_q_heads: int, head_dim: int) -> int:
     return (n + 3) // 4 * 4
 
 
+class PeerExchange:
+    """The exchange of a KV split over peer memory (hkb_kvsplit_push / hkb_kvsplit_merge): every
+    rank's gather buffer and state block live in symmetric memory that all ranks of the box have
+    mapped, the fold of a rank's splits stores its record into every peer directly, and the final
+    merge waits (boundedly) for every rank's flag. No collective in the step.
+
+    With one rank (or no process group) the buffers are plain device tensors and the rank is its
+    own only peer: the same two kernels, usable on one GPU."""
+
+    #: polls of a flag before the merge gives up (about a tenth of a microsecond each: ~1 s)
+    SPIN_LIMIT = 10_000_000
+
+    def __init__(self, num_seqs: int, num_q_heads: int, head_dim: int, device, group=None):
+        import torch.distributed as dist
+
+        lib = _lib.load()
+        live = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if live else 1
+        self.rank = dist.get_rank(group) if live else 0
+        self.n, self.hq, self.d = num_seqs, num_q_heads, head_dim
+        gbytes = lib.hkb_exchange_gather_bytes(self.world, num_seqs, num_q_heads, head_dim)
+        if gbytes == 0:
+            raise ValueError(f"hk.ops.paged_dist: no peer exchange for {self.world} ranks (1 to 8), {num_seqs} sequences")
+        self.gather_bytes = (gbytes + 255) // 256 * 256
+        total = self.gather_bytes + 256
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm
+
+            self.buf = symm.empty(total, dtype=torch.uint8, device=device)
+            self.buf.zero_()
+            handle = symm.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
+            ptrs = [int(p) for p in handle.buffer_ptrs]
+            self._handle = handle
+            torch.cuda.synchronize(device)
+            dist.barrier(group)              # nobody pushes into a state block that is still being zeroed
+        else:
+            self.buf = torch.zeros(total, dtype=torch.uint8, device=device)
+            ptrs = [self.buf.data_ptr()]
+        x = _lib.ExchangeT()
+        x.world, x.rank = self.world, self.rank
+        for r in range(self.world):
+            x.gather[r] = ptrs[r]
+            x.state[r] = ptrs[r] + self.gather_bytes
+        self.x = x
+        self.state = self.buf[self.gather_bytes:self.gather_bytes + 80].view(torch.int32)   # flags, counters, error word
+
+    def push(self, scratch, num_splits: int) -> None:
+        """Fold this rank's splits (`scratch` of the walk) and store the record into every rank."""
+        po, pl = scratch
+        rc = _lib.load().hkb_kvsplit_push(self.x, po.data_ptr(), pl.data_ptr(), num_splits, self.n, self.hq, self.d,
+                                          paged._stream(po))
+        _lib.check("hkb_kvsplit_push", rc)
+
+    def merge(self, out: torch.Tensor, spin_limit: Optional[int] = None) -> torch.Tensor:
+        """Wait for every rank's record of this step and fold them into `out` (seqs, heads, d)."""
+        kind = {torch.bfloat16: 0, torch.float16: 2}.get(out.dtype)
+        if kind is None or tuple(out.shape) != (self.n, self.hq, self.d) or out.stride(2) != 1:
+            raise ValueError(f"hk.ops.paged_dist: the exchange writes ({self.n}, {self.hq}, {self.d}) bf16 or fp16, "
+                             f"out is {tuple(out.shape)} {out.dtype}")
+        rc = _lib.load().hkb_kvsplit_merge(self.x, out.data_ptr(), out.stride(0), out.stride(1), kind, self.n, self.hq,
+                                           self.d, int(spin_limit or self.SPIN_LIMIT), paged._stream(out))
+        _lib.check("hkb_kvsplit_merge", rc)
+        return out
+
+    def error(self) -> int:
+        """0, or 1 + the rank whose record a merge gave up waiting for (reads the device: a sync)."""
+        return int(self.state[19].item())
+
+    def reset(self) -> None:
+        """Zero the state block (flags, step counter, error word). After a miss every rank calls this
+        (and they meet at a barrier) before the next step."""
+        self.state.zero_()
+
+
 class SplitKVDecoder:
     """Decode of sequences whose KV is cut along the token axis across the ranks of `group`.
 
@@ -74,8 +148,15 @@ class SplitKVDecoder:
     on the current stream -> cross-rank merge. Every rank ends with the full answer."""
 
     def __init__(self, num_seqs: int, num_q_heads: int, num_kv_heads: int, head_dim: int, device,
-                 local_splits: int, group=None):
+                 local_splits: int, group=None, exchange: str = "nccl"):
+        """`exchange`: "nccl" -- `all_gather_into_tensor` of the ranks' records between two launches;
+        "peer" -- the records go over peer memory inside the launches (`PeerExchange`)."""
         import torch.distributed as dist
+
+        if exchange not in ("nccl", "peer"):
+            raise ValueError(f"hk.ops.paged_dist: exchange {exchange!r} is not 'nccl' or 'peer'")
+        self.exchange = exchange
+        self.peer = PeerExchange(num_seqs, num_q_heads, head_dim, device, group) if exchange == "peer" else None
 
         self.dist = dist
         self.group = group
@@ -140,7 +221,15 @@ class SplitKVDecoder:
     def decode(self, out, query, key_cache, value_cache, block_tables, local_lens, scale,
                kv_cache_dtype="auto", k_scale=None, v_scale=None, *, key=None, value=None,
                slot_mapping=None) -> torch.Tensor:
-        """The whole step: two launches, one all-gather, one launch."""
+        """The whole step: two launches, one all-gather, one launch -- or, over peer memory, three
+        launches and no collective (the walk; the fold of the local splits that stores this rank's
+        record into every rank; the bounded wait for all records and their fold)."""
+        if self.peer is not None:
+            paged.decode_step_record(None, None, query, key, value, key_cache, value_cache, slot_mapping, block_tables,
+                                     local_lens, scale, kv_cache_dtype, k_scale, v_scale, num_splits=self.local_splits,
+                                     scratch=self.scratch)
+            self.peer.push(self.scratch, self.local_splits)
+            return self.peer.merge(out)
         self.local_partial(query, key_cache, value_cache, block_tables, local_lens, scale,
                            kv_cache_dtype, k_scale, v_scale, key=key, value=value, slot_mapping=slot_mapping)
         self.gather()

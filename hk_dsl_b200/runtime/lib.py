@@ -33,6 +33,12 @@ class CacheT(Structure):
                 ("stride_head", c_int64), ("num_blocks", c_int64)]
 
 
+class ExchangeT(Structure):
+    """hkb_exchange_t: every rank's gather buffer and state block as mapped in this process."""
+
+    _fields_ = [("world", c_int), ("rank", c_int), ("gather", c_void_p * 8), ("state", c_void_p * 8)]
+
+
 class HkbError(RuntimeError):
     """A refused or failed hkb call; `.code` is the hkb_status."""
 
@@ -67,6 +73,10 @@ SIGNATURES = {
                                        CacheT, CacheT, c_void_p, c_int64, c_int, c_void_p, c_void_p,
                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
                                        c_int, c_void_p, c_void_p, c_void_p]),
+    "hkb_exchange_gather_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "hkb_exchange_state_bytes": (c_size_t, []),
+    "hkb_kvsplit_push": (c_int, [ExchangeT, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "hkb_kvsplit_merge": (c_int, [ExchangeT, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "hkb_arrivals_bytes": (c_size_t, [c_int, c_int]),
     "hkb_paged_prefill": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, CacheT, CacheT,
                                   c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int,

@@ -267,7 +267,8 @@ int hkb_decode_step(void* out, int64_t out_stride_tok, int64_t out_stride_head,
  * (contiguous, num_seqs x num_q_heads x head_dim) and rec_lse[i, h] its natural-log sum-exp
  * (-inf where the rank holds no token of sequence i). Records of all ranks, gathered, are folded
  * by hkb_merge with one part a rank. Two launches; num_splits >= 2 (the record is written by the
- * merge). Everything else as hkb_decode_step.
+ * merge). rec_out == NULL (and rec_lse NULL): the walk alone, one launch -- the partials stay in
+ * part_out / part_lse for the caller to fold (hkb_kvsplit_push). Everything else as hkb_decode_step.
  *
  * Replaces nothing in the reference, which cuts the KV axis inside one GPU only
  * (python/hk/ops/paged.py:171-194); it is that cut carried one level up.
@@ -285,6 +286,45 @@ int hkb_decode_step_record(float* rec_out, float* rec_lse,
                            int block_size, float scale, int kv_dtype,
                            const float* k_scale, const float* v_scale,
                            int num_splits, float* part_out, float* part_lse, void* stream);
+
+/*
+ * The exchange step of a KV axis cut across the GPUs of one box, over peer memory instead of a
+ * collective. Every rank allocates a gather buffer (hkb_exchange_gather_bytes) and a state block
+ * (hkb_exchange_state_bytes, ZERO before the first step) in memory that every other rank has mapped
+ * (CUDA IPC, or torch's symmetric memory); `gather[r]` / `state[r]` are rank r's two buffers as
+ * mapped in THIS process (for r == rank: the rank's own).
+ *
+ * A step, on one stream, the same on every rank:
+ *   hkb_paged_decode(..., num_splits >= 2, part_out, part_lse)   the walk, partials in local scratch
+ *   hkb_kvsplit_push(x, part_out, part_lse, num_splits, ...)     folds the rank's splits and stores its
+ *                                                               record (normalised fp32 out, natural-log
+ *                                                               lse) into every rank's gather buffer,
+ *                                                               then raises its flag on every rank
+ *   hkb_kvsplit_merge(x, out, ..., spin_limit)                   waits for every rank's flag of this
+ *                                                               step, folds the records into `out`
+ * No host value changes between steps (the step counter lives in the state block), so the three
+ * launches can be captured and replayed. The wait is bounded: a flag polled `spin_limit` times (about
+ * 0.1 us a poll) without arriving sets the error word -- the last int32 of the rank's state block -- to
+ * 1 + the rank that was missing, the CTA skips its fold and the kernel returns; `out` is then not
+ * valid and the host decides (the ranks' step counters are out of step after a miss: zero the state
+ * blocks on every rank before going on). Ranks must make the same calls in the same order.
+ * At most 8 ranks. Plain peer stores: no multicast, no multimem.
+ *
+ * Replaces nothing in the reference (its KV split stays inside one GPU,
+ * python/hk/ops/paged.py:171-194); it is what ncclAllGather + hkb_merge do for this path, as two kernels.
+ */
+typedef struct {
+  int world, rank;
+  void* gather[8];
+  void* state[8];
+} hkb_exchange_t;
+
+size_t hkb_exchange_gather_bytes(int world, int num_seqs, int num_q_heads, int head_dim);
+size_t hkb_exchange_state_bytes(void);
+int hkb_kvsplit_push(hkb_exchange_t x, const float* part_out, const float* part_lse, int num_splits,
+                     int num_seqs, int num_q_heads, int head_dim, void* stream);
+int hkb_kvsplit_merge(hkb_exchange_t x, void* out, int64_t out_stride_tok, int64_t out_stride_head, int out_kind,
+                      int num_seqs, int num_q_heads, int head_dim, int spin_limit, void* stream);
 
 /* Bytes of the arrival counters hkb_decode_step takes. */
 size_t hkb_arrivals_bytes(int num_seqs, int num_kv_heads);
@@ -305,9 +345,10 @@ int hkb_prefill_uses_tcgen05(int head_dim, int kv_dtype);
  * GQA group of 4, 16-byte-aligned query rows; HKB_ERR_UNSUPPORTED otherwise): besides the answer,
  * every CTA -- index kv_head * num_work + work item -- writes 32 uint64 cycle counters to
  * `trace` (device memory, num_work * num_kv_heads * 32 entries): softmax warps of query tile g at
- * 8 g + {0 waiting for scores, 1 TMEM load, 2 maximum and exponentials, 3 waiting for the
+ * 8 g + {0 waiting for scores, 1 TMEM loads and maximum, 2 exponentials, 3 waiting for the
  * previous product / rescale, 4 P store and arrive, 5 epilogue}; MMA warp at 16 + {0 wait for Q,
- * 1 wait for K, 2 issue of q.K, 3 wait for V, 4 / 6 wait for P of tile 0 / 1, 5 issue of p.V};
+ * 1 wait for K, 2 issue of the first q.K, 3 wait for V, 4 / 6 wait for P of tile 0 / 1, 5 issue of
+ * p.V and of the next block's q.K};
  * producer w (0 K, 1 V) at 24 + 4 w + {0 wait for a free slot, 1 issue of copies, 2 wait for
  * copies to land}; 31 the CTA's whole time. A measurement aid with no counterpart in the reference
  * (which attributes time by ablation, python/hk/ops/paged.py:524-533).

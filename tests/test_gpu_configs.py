@@ -276,3 +276,67 @@ def test_kv_split_step_writes_the_new_rows_on_the_rank_that_holds_them():
     assert (out.float() - whole).abs().max().item() < 2e-2
     want = _oracle(ref)
     orc.check(out, want)
+
+
+def test_peer_exchange_on_one_gpu_equals_the_step_and_replays_from_a_graph():
+    """The exchange over peer memory with the rank as its own only peer: walk (writing the new rows),
+    push, merge -- three launches, no collective -- gives the bits of the two-launch step when the
+    walk and the fold are the same kernels' arithmetic (the fold order differs: tolerance), step after
+    step (the gather halves and flags alternate by the step counter's parity), and from a CUDA graph."""
+    from hk_dsl_b200.ops import paged_dist
+
+    paged = _paged()
+    spec = W.CONFIGS["c5"]
+    lens = [3000 + 7, 1500]
+    st = W.build_step(spec, "cuda", lens=lens)
+    ref = W.build_step(spec, "cuda", lens=lens)
+    n, hq, d = st.query.shape
+    want = torch.empty_like(ref.out)
+    paged.decode_step(want, ref.query, ref.key, ref.value, ref.k_caches[0], ref.v_caches[0], ref.slot_mapping,
+                      ref.block_table, ref.seq_lens, ref.scale, num_splits=8)
+    dec = paged_dist.SplitKVDecoder(n, hq, st.kv_heads, d, "cuda", local_splits=8, exchange="peer")
+    assert dec.peer.world == 1 and dec.peer.error() == 0
+    out = torch.full_like(st.out, 7.0)
+    for step in range(3):                                   # parities 0, 1, 0
+        out.fill_(7.0)
+        dec.decode(out, st.query, st.k_caches[0], st.v_caches[0], st.block_table, st.seq_lens, st.scale,
+                   key=st.key, value=st.value, slot_mapping=st.slot_mapping)
+        torch.cuda.synchronize()
+        assert dec.peer.error() == 0
+        assert int(dec.peer.state[16].item()) == step + 1  # the step counter moved on
+        orc.check(out, want.float())
+    assert torch.equal(st.k_caches[0].view(torch.int16), ref.k_caches[0].view(torch.int16))   # the walk wrote the rows
+    orc.check(out, _oracle(ref))
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        dec.decode(out, st.query, st.k_caches[0], st.v_caches[0], st.block_table, st.seq_lens, st.scale)
+    for _ in range(3):
+        out.fill_(7.0)
+        g.replay()
+        torch.cuda.synchronize()
+        orc.check(out, want.float())
+    assert dec.peer.error() == 0
+
+
+def test_peer_exchange_a_record_that_never_arrives_is_reported_not_waited_for():
+    """The merge's wait is bounded: with no push before it (the flag of this step is never raised) it
+    gives up after `spin_limit` polls, sets the error word to 1 + the missing rank, leaves `out`
+    alone and returns; the GPU and the context stay usable, and after `reset` a whole step works."""
+    from hk_dsl_b200.ops import paged_dist
+
+    spec = W.CONFIGS["c5"]
+    st = W.build_step(spec, "cuda", lens=[600, 100])
+    n, hq, d = st.query.shape
+    dec = paged_dist.SplitKVDecoder(n, hq, st.kv_heads, d, "cuda", local_splits=4, exchange="peer")
+    out = torch.full_like(st.out, 7.0)
+    dec.peer.merge(out, spin_limit=200)                     # nothing was pushed
+    torch.cuda.synchronize()
+    assert dec.peer.error() == 1                            # rank 0's record was the one missing
+    assert (out == 7.0).all()
+    dec.peer.reset()
+    torch.cuda.synchronize()
+    dec.decode(out, st.query, st.k_caches[0], st.v_caches[0], st.block_table, st.seq_lens, st.scale,
+               key=st.key, value=st.value, slot_mapping=st.slot_mapping)
+    torch.cuda.synchronize()
+    assert dec.peer.error() == 0
+    orc.check(out, _oracle(st))

@@ -166,7 +166,7 @@ def test_fp8_cache_against_the_dequantised_oracle(group):
 def test_which_kernel_runs_and_that_no_wait_ran_out(monkeypatch):
     """head_dim 128 on a 16-bit cache runs the tcgen05 / tensor-memory kernel, everything else (and
     HKB_PREFILL_MMA_SYNC=1) the mma.sync one; both give the oracle's answer on the same inputs and
-    each other's within two bf16 ulps of the row maximum; the tensor-memory kernel's bounded waits
+    each other's within three bf16 ulps of the row maximum; the tensor-memory kernel's bounded waits
     left no error code behind -- in this test or in any that ran before it in this process."""
     from hk_dsl_b200.runtime import lib as hkb
 
@@ -182,7 +182,7 @@ def test_which_kernel_runs_and_that_no_wait_ran_out(monkeypatch):
     assert lib.hkb_prefill_uses_tcgen05(128, hkb.KV_BF16) == 0
     old, _, _ = _run(reqs, h_kv=2, group=4, seed=11)
     orc.check(old, want)
-    assert orc.ulps(new, old.float()) < 2.0
+    assert orc.ulps(new, old.float()) <= 3.0
     monkeypatch.delenv("HKB_PREFILL_MMA_SYNC")
     assert lib.hkb_prefill_tc_error(0) == 0
 
