@@ -253,7 +253,7 @@ def prefill_trace(case: str):
     for _ in range(2):
         rc = lib.hkb_paged_prefill_trace(out.data_ptr(), out.stride(0), out.stride(1), q.data_ptr(), q.stride(0), q.stride(1),
                                          cache(kc), cache(vc), table_d.data_ptr(), table_d.stride(0), table_d.shape[1],
-                                         lens_d.data_ptr(), starts_d.data_ptr(), work.data_ptr(), work.shape[0], hq, hkv, d, bs,
+                                         lens_d.data_ptr(), starts_d.data_ptr(), work.data_ptr(), work.shape[0], q.shape[0], hq, hkv, d, bs,
                                          d ** -0.5, hkb.KV_BF16, None, None, trace.data_ptr(),
                                          torch.cuda.current_stream().cuda_stream)
         hkb.check("hkb_paged_prefill_trace", rc)
@@ -267,6 +267,7 @@ def prefill_trace(case: str):
     blocks *= hkv
     names = {0: "softmax tile 0: wait for scores", 1: "softmax tile 0: loads + maximum", 2: "softmax tile 0: exponentials",
              3: "softmax tile 0: wait for previous product (+ rescale)", 4: "softmax tile 0: store P, arrive", 5: "softmax tile 0: epilogue",
+             6: "softmax tile 0: staging the query rows", 7: "softmax tile 0: CTA set-up before it",
              8: "softmax tile 1: wait for scores", 9: "softmax tile 1: loads + maximum", 10: "softmax tile 1: exponentials",
              11: "softmax tile 1: wait for previous product (+ rescale)", 12: "softmax tile 1: store P, arrive", 13: "softmax tile 1: epilogue",
              16: "mma: wait for Q", 17: "mma: wait for K", 18: "mma: issue first q.K", 19: "mma: wait for V", 20: "mma: wait for P of tile 0",

@@ -422,8 +422,32 @@ static bool make_cache_map(CUtensorMap* m, const hkb_cache_t& c, int block_size,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// A 3-D tensor map of the queries (tokens, heads, 128 dims, 16-bit), the token and head axes in order of
+// increasing stride; a copy is a box of 64 dims x `tile_tokens` tokens of one head. `pos`: the
+// coordinate index of (token, head).
+static bool make_query_map(CUtensorMap* m, const void* q, int64_t stride_tok, int64_t stride_head, int64_t num_tokens,
+                           int num_q_heads, int tile_tokens, int pos[2]) {
+  const EncodeTiledFn encode = tensor_map_encoder();
+  if (!encode || stride_tok <= 0 || stride_head <= 0 || num_tokens <= 0) return false;
+  struct Axis { cuuint64_t size, stride; int role; } ax[2] = {{(cuuint64_t)num_tokens, (cuuint64_t)stride_tok * 2, 0},
+                                                              {(cuuint64_t)num_q_heads, (cuuint64_t)stride_head * 2, 1}};
+  if (ax[1].stride < ax[0].stride) { const Axis t = ax[0]; ax[0] = ax[1]; ax[1] = t; }
+  for (int i = 0; i < 2; ++i)
+    if (ax[i].stride % 16 || ax[i].stride >= (1ull << 40) || ax[i].size > (1ull << 32)) return false;
+  cuuint64_t dims[3] = {128, ax[0].size, ax[1].size};
+  cuuint64_t strides[2] = {ax[0].stride, ax[1].stride};
+  cuuint32_t box[3] = {64, 1, 1}, elem[3] = {1, 1, 1};
+  for (int i = 0; i < 2; ++i) {
+    pos[ax[i].role] = i + 1;
+    if (ax[i].role == 0) box[i + 1] = (cuuint32_t)tile_tokens;
+  }
+  return encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int GP, bool F16, bool TRACE = false>
-static int launch_prefill_tc(const tc::Args& a, const CUtensorMap& kmap, const CUtensorMap& vmap, int num_work, cudaStream_t st) {
+static int launch_prefill_tc(const tc::Args& a, const CUtensorMap& kmap, const CUtensorMap& vmap, const CUtensorMap& qmap,
+                             int num_work, cudaStream_t st) {
   static bool armed[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -433,7 +457,7 @@ static int launch_prefill_tc(const tc::Args& a, const CUtensorMap& kmap, const C
   }
   if (e == cudaSuccess) {
     dim3 grid(num_work, a.num_kv_heads * (a.group / GP));
-    tc::prefill_tc_kernel<GP, F16, TRACE><<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(a, kmap, vmap);
+    tc::prefill_tc_kernel<GP, F16, TRACE><<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(a, kmap, vmap, qmap);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
@@ -441,11 +465,12 @@ static int launch_prefill_tc(const tc::Args& a, const CUtensorMap& kmap, const C
 }
 
 template <bool F16>
-static int dispatch_prefill_tc(const tc::Args& a, const CUtensorMap& kmap, const CUtensorMap& vmap, int num_work, cudaStream_t st) {
-  if (a.group % 8 == 0) return launch_prefill_tc<8, F16>(a, kmap, vmap, num_work, st);
-  if (a.group % 4 == 0) return launch_prefill_tc<4, F16>(a, kmap, vmap, num_work, st);
-  if (a.group % 2 == 0) return launch_prefill_tc<2, F16>(a, kmap, vmap, num_work, st);
-  return launch_prefill_tc<1, F16>(a, kmap, vmap, num_work, st);
+static int dispatch_prefill_tc(const tc::Args& a, const CUtensorMap& kmap, const CUtensorMap& vmap, const CUtensorMap& qmap,
+                               int num_work, cudaStream_t st) {
+  if (a.group % 8 == 0) return launch_prefill_tc<8, F16>(a, kmap, vmap, qmap, num_work, st);
+  if (a.group % 4 == 0) return launch_prefill_tc<4, F16>(a, kmap, vmap, qmap, num_work, st);
+  if (a.group % 2 == 0) return launch_prefill_tc<2, F16>(a, kmap, vmap, qmap, num_work, st);
+  return launch_prefill_tc<1, F16>(a, kmap, vmap, qmap, num_work, st);
 }
 
 }  // namespace hkb
@@ -481,12 +506,12 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
                                  hkb_cache_t kc, hkb_cache_t vc,
                                  const int32_t* block_table, int64_t table_stride, int max_pages,
                                  const int32_t* seq_lens, const int32_t* q_start,
-                                 const int32_t* work, int num_work,
+                                 const int32_t* work, int num_work, int num_tokens,
                                  int num_q_heads, int num_kv_heads, int head_dim, int block_size,
                                  float scale, int kv_dtype, const float* k_scale, const float* v_scale,
                                  void* stream) {
   using namespace hkb;
-  if (num_work < 0 || num_q_heads <= 0 || num_kv_heads <= 0) return HKB_ERR_SIZE;
+  if (num_work < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_tokens < 0) return HKB_ERR_SIZE;
   if (num_work == 0) return HKB_OK;
   if (!out || !q || !kc.ptr || !vc.ptr || !block_table || !seq_lens || !q_start || !work) return HKB_ERR_NULL;
   if (head_dim != 64 && head_dim != 128 && head_dim != 256) return HKB_ERR_HEAD_DIM;
@@ -536,20 +561,26 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
     t.scale = a.scale;
     t.trace = g_trace_for_next_call;
     // K and V blocks come by TMA where a tensor map describes the cache (HKB_PREFILL_NO_TMA=1: the cp.async gather, the comparison arm)
-    alignas(64) CUtensorMap kmap, vmap;
+    alignas(64) CUtensorMap kmap, vmap, qmap;
     const char* no_tma = std::getenv("HKB_PREFILL_NO_TMA");
+    const int gp = group % 8 == 0 ? 8 : group % 4 == 0 ? 4 : group % 2 == 0 ? 2 : 1;
+    // a query tile that runs past the tensor's last token reads zeros there (the map knows num_tokens);
+    // rows past a request's own tokens belong to the next request and are masked
+    const int64_t q_tokens = num_tokens;
     t.tma = !(no_tma && no_tma[0] == '1') && make_cache_map(&kmap, kc, block_size, num_kv_heads, t.k_pos) &&
-            make_cache_map(&vmap, vc, block_size, num_kv_heads, t.v_pos);
+            make_cache_map(&vmap, vc, block_size, num_kv_heads, t.v_pos) &&
+            make_query_map(&qmap, q, q_stride_tok, q_stride_head, q_tokens, num_q_heads, 128 / gp, t.q_pos);
     if (!t.tma) {
-      memset(&kmap, 0, sizeof(kmap)); memset(&vmap, 0, sizeof(vmap));
+      memset(&kmap, 0, sizeof(kmap)); memset(&vmap, 0, sizeof(vmap)); memset(&qmap, 0, sizeof(qmap));
       for (int i = 0; i < 3; ++i) t.k_pos[i] = t.v_pos[i] = i + 1;
+      t.q_pos[0] = 1; t.q_pos[1] = 2;
     }
     if (t.trace) {   // the traced build: the headline shape only (a bf16 cache, a GQA group of 4)
       if (kv_dtype != HKB_KV_BF16 || group % 4 || group % 8 == 0) return HKB_ERR_UNSUPPORTED;
-      return launch_prefill_tc<4, false, true>(t, kmap, vmap, num_work, st);
+      return launch_prefill_tc<4, false, true>(t, kmap, vmap, qmap, num_work, st);
     }
-    return kv_dtype == HKB_KV_F16 ? dispatch_prefill_tc<true>(t, kmap, vmap, num_work, st)
-                                  : dispatch_prefill_tc<false>(t, kmap, vmap, num_work, st);
+    return kv_dtype == HKB_KV_F16 ? dispatch_prefill_tc<true>(t, kmap, vmap, qmap, num_work, st)
+                                  : dispatch_prefill_tc<false>(t, kmap, vmap, qmap, num_work, st);
   }
   if (fp8) return dispatch_prefill<128, true>(a, num_work, st);
   if (kv_dtype == HKB_KV_F16) {
@@ -568,7 +599,7 @@ extern "C" int hkb_paged_prefill_trace(void* out, int64_t out_stride_tok, int64_
                                        hkb_cache_t kc, hkb_cache_t vc,
                                        const int32_t* block_table, int64_t table_stride, int max_pages,
                                        const int32_t* seq_lens, const int32_t* q_start,
-                                       const int32_t* work, int num_work,
+                                       const int32_t* work, int num_work, int num_tokens,
                                        int num_q_heads, int num_kv_heads, int head_dim, int block_size,
                                        float scale, int kv_dtype, const float* k_scale, const float* v_scale,
                                        unsigned long long* trace, void* stream) {
@@ -576,8 +607,8 @@ extern "C" int hkb_paged_prefill_trace(void* out, int64_t out_stride_tok, int64_
   if (!hkb_prefill_uses_tcgen05(head_dim, kv_dtype)) return HKB_ERR_UNSUPPORTED;
   g_trace_for_next_call = trace;
   const int rc = hkb_paged_prefill(out, out_stride_tok, out_stride_head, q, q_stride_tok, q_stride_head, kc, vc, block_table,
-                                   table_stride, max_pages, seq_lens, q_start, work, num_work, num_q_heads, num_kv_heads,
-                                   head_dim, block_size, scale, kv_dtype, k_scale, v_scale, stream);
+                                   table_stride, max_pages, seq_lens, q_start, work, num_work, num_tokens, num_q_heads,
+                                   num_kv_heads, head_dim, block_size, scale, kv_dtype, k_scale, v_scale, stream);
   g_trace_for_next_call = nullptr;
   return rc;
 }

@@ -92,6 +92,15 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* map, uint3
   asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
                ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+__device__ __forceinline__ uint4 ldg_stream16(const void* p) {   // volatile: keeps its place in the instruction stream
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
@@ -221,6 +230,7 @@ struct Args {
   float scale;
   int tma;                  // K and V blocks by TMA (the two tensor maps are valid)
   int k_pos[3], v_pos[3];   // which coordinate of the map (1..3) is the token, the kv head, the block
+  int q_pos[2];             // which coordinate of the query map (1..2) is the token, the head
   unsigned long long* trace;   // TRACE builds only: 32 cycle counters a CTA (see Lap), else unused
 };
 
@@ -305,6 +315,21 @@ __device__ __forceinline__ float half_max(float (&s)[64], bool masked, bool vali
   }
   return fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
 }
+// 2^x on the FMA pipe, for x <= 8 or so: x = n + f with n the nearest integer (the add of 1.5 * 2^23
+// leaves n in the low mantissa bits), a cubic for 2^f on [-0.5, 0.5] (fitted for the smallest largest
+// relative error, 7.5e-5 -- P is rounded to 16 bits, 2e-3, after it), n added to the exponent field.
+// The MUFU unit does 16 exponentials a clock an SM, as long as the tensor core takes for the two
+// products they feed: a share of them done here takes that unit off the critical path.
+__device__ __forceinline__ float poly_exp2(float x) {
+  x = fmaxf(x, -126.f);                         // a masked score (-inf) comes out as 2^-126: nothing
+  const float shifted = x + 12582912.f;
+  const float f = x - (shifted - 12582912.f);
+  const float p = fmaf(fmaf(fmaf(0.0551716685f, f, 0.2426111251f), f, 0.6932609677f), f, 0.9999280572f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(shifted) << 23));
+}
+// which pairs of a row take the polynomial: one in POLY_EVERY (0: none)
+constexpr int POLY_EVERY = 4;
+
 template <bool F16>
 __device__ __forceinline__ float half_exp(float (&s)[64], bool masked, bool valid, int key0, int pos, float qs, float off,
                                           uint32_t (&p)[32]) {
@@ -321,7 +346,8 @@ __device__ __forceinline__ float half_exp(float (&s)[64], bool masked, bool vali
   for (int i = 0; i < 32; ++i) {
     float x0, x1;
     unpack2(fma2(pack2(s[2 * i], s[2 * i + 1]), qs2, off2), x0, x1);
-    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+    const bool poly = POLY_EVERY > 0 && (i % (POLY_EVERY > 0 ? POLY_EVERY : 1)) == (POLY_EVERY > 0 ? POLY_EVERY : 1) - 1;
+    const float p0 = poly ? poly_exp2(x0) : fast_exp2(x0), p1 = poly ? poly_exp2(x1) : fast_exp2(x1);
     acc[i & 3] = add2(acc[i & 3], pack2(p0, p1));
     if (F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(p[i]) : "f"(p1), "f"(p0));
     else asm("cvt.rn.bf16x2.f32 %0, %1, %2;\n" : "=r"(p[i]) : "f"(p1), "f"(p0));
@@ -333,7 +359,8 @@ __device__ __forceinline__ float half_exp(float (&s)[64], bool masked, bool vali
 
 template <int GP, bool F16, bool TRACE = false>
 __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kmap,
-                                                                const __grid_constant__ CUtensorMap vmap) {
+                                                                const __grid_constant__ CUtensorMap vmap,
+                                                                const __grid_constant__ CUtensorMap qmap) {
   extern __shared__ uint8_t raw_smem[];
   unsigned long long tr[8] = {0, 0, 0, 0, 0, 0, 0, 0};      // this thread's lap counters (TRACE builds)
   const long long t_begin = TRACE ? now() : 0;
@@ -374,7 +401,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
     for (int i = 0; i < NSLOT; ++i) { mbar_init(HKB_BAR(full) + 8 * i, 1); mbar_init(HKB_BAR(empty) + 8 * i, 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(HKB_BAR(s_full) + 8 * i, 1); mbar_init(HKB_BAR(p_full) + 8 * i, ROWS);
-      mbar_init(HKB_BAR(o_done) + 8 * i, 1); mbar_init(HKB_BAR(q_full) + 8 * i, ROWS);
+      mbar_init(HKB_BAR(o_done) + 8 * i, 1); mbar_init(HKB_BAR(q_full) + 8 * i, a.tma ? 1 : ROWS);
     }
     bars->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -395,16 +422,15 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
     const bool out16 = ((reinterpret_cast<uintptr_t>(a.out) | (uintptr_t)(a.out_stride_tok * 2) | (uintptr_t)(a.out_stride_head * 2)) & 15) == 0;
     // This tile's query rows first (the producers are already fetching K and V): row r is head r / T,
     // token r % T of the tile; rows past the request are zeros. 128 threads x 16 chunks a row group.
-    if (nblk[g] > 0) {
+    if (TRACE) tr[7] = (unsigned long long)(now() - t_begin);   // set-up: barriers, TMEM, the CTA-wide barrier
+    Lap<TRACE> lap_q;
+    if (nblk[g] > 0 && !a.tma) {
       uint4 qv[16];
 #pragma unroll
       for (int it = 0; it < 16; ++it) {                      // all sixteen loads in flight, then the stores
         const int x = it * ROWS + (warp & 3) * 32 + lane, r = x >> 4, c = x & 15;
-        const int tk = row0 + g * T + r % T;
-        qv[it] = make_uint4(0u, 0u, 0u, 0u);
-        if (tk < q_len)
-          qv[it] = __ldg(reinterpret_cast<const uint4*>(a.q + (int64_t)(q0 + tk) * a.q_stride_tok +
-                                                        (int64_t)(hbase + r / T) * a.q_stride_head + c * 8));
+        const int tk = min(row0 + g * T + r % T, q_len - 1);  // rows past the request: any finite row will do, they are masked
+        qv[it] = ldg_stream16(a.q + (int64_t)(q0 + tk) * a.q_stride_tok + (int64_t)(hbase + r / T) * a.q_stride_head + c * 8);
       }
 #pragma unroll
       for (int it = 0; it < 16; ++it) {
@@ -415,6 +441,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
       fence_async_smem();
       mbar_arrive(HKB_BAR(q_full) + 8 * g);
     }
+    lap_q(tr[6]);
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t s_addr = lane_addr + s_col(g);
     const int tok = row0 + g * T + row % T;
@@ -530,7 +557,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
     }
     lap_end(tr[5]);
     if (TRACE && row == 0)
-      for (int i = 0; i < 6; ++i) a.trace[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 32 + 8 * g + i] = tr[i];
+      for (int i = 0; i < 8; ++i) a.trace[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 32 + 8 * g + i] = tr[i];
   } else if (warp == MMA_WARP) {
     // ================= MMA issue: one thread; the whole warp keeps step at the barriers =================
     constexpr uint32_t IDESC_S = instr_desc(F16, false, KVB), IDESC_PV = instr_desc(F16, true, D);
@@ -609,9 +636,40 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
               p_blk = which ? a.v_pos[2] : a.k_pos[2];
     const int* table_row = a.block_table + (int64_t)req * a.table_stride;
     bool ok = true;
+    if (a.tma && which == 1) {
+      // the V warp has nothing to do until the first scores exist: it brings the query tiles, one copy a
+      // (tile, head, 64-dim half): T token rows of 128 bytes, landing where row h * T + token belongs
+      for (int t = 0; t < 2; ++t) {
+        if (nblk[t] == 0) continue;
+        if (lane == 0) mbar_arrive_expect_tx(HKB_BAR(q_full) + 8 * t, Q_BYTES);
+        __syncwarp();
+        for (int x = lane; x < 2 * GP; x += 32) {
+          const int h = x >> 1, half = x & 1;
+          int c[3];
+          c[0] = half * 64;
+          c[a.q_pos[0]] = q0 + row0 + t * T;
+          c[a.q_pos[1]] = hbase + h;
+          tma_load_3d(q_smem + t * Q_BYTES + half * HALF_BYTES_Q + h * T * 128, &qmap, HKB_BAR(q_full) + 8 * t, c[0], c[1], c[2]);
+        }
+      }
+    }
+    // page ids of a block's eight 16-token tiles, fetched one block ahead of their use
+    auto page_ids = [&](int kv0, int& id, int& sub) {
+      id = 0; sub = 0;
+      if (lane < 8 && kv0 < kv_limit) {
+        const int tile = kv0 / TILE_TOKENS + lane;
+        const int page = min(tile / a.tiles_per_page, a.max_pages - 1);
+        id = min(max(__ldg(table_row + page), 0), a.num_blocks - 1);
+        sub = tile % a.tiles_per_page;
+      }
+    };
+    int next_id, next_sub;
+    page_ids(0, next_id, next_sub);
     for (int j = 0; j < n && ok; ++j) {
       const int use = 2 * j + which, slot = use % NSLOT, lap = use / NSLOT;
       const uint32_t slot_addr = ring + slot * SLOT_BYTES, bar = HKB_BAR(full) + 8 * slot;
+      int id = next_id, sub = next_sub;
+      page_ids((j + 1) * KVB, next_id, next_sub);
       const int kv0 = j * KVB;
       Lap<TRACE> tick;
       if (lap > 0) ok = warp_wait(HKB_BAR(empty) + 8 * slot, (lap - 1) & 1, abort, 7);
@@ -619,13 +677,6 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
       tick(tr[0]);
       if (a.tma && kv0 + KVB <= kv_limit) {
         // all 128 rows are keys: 8 pages x 2 halves = 16 tile copies, one a lane
-        int id = 0, sub = 0;
-        if (lane < 8) {
-          const int tile = kv0 / TILE_TOKENS + lane;
-          const int page = min(tile / a.tiles_per_page, a.max_pages - 1);
-          id = min(max(__ldg(table_row + page), 0), a.num_blocks - 1);
-          sub = tile % a.tiles_per_page;
-        }
         const int t = (lane >> 1) & 7;
         id = __shfl_sync(0xffffffffu, id, t);
         sub = __shfl_sync(0xffffffffu, sub, t);

@@ -421,7 +421,7 @@ def paged_prefill(out: torch.Tensor, query: torch.Tensor, key_cache: torch.Tenso
         out.data_ptr(), out.stride(0), out.stride(1), query.data_ptr(), query.stride(0), query.stride(1),
         _cache_t(key_cache), _cache_t(value_cache), block_tables.data_ptr(), block_tables.stride(0),
         block_tables.shape[1], seq_lens.data_ptr(), query_start_loc.data_ptr(), work.data_ptr(), work.shape[0],
-        hq, hkv, d, bs, float(scale), code, _scale_ptr(k_scale, fp8, "k_scale"), _scale_ptr(v_scale, fp8, "v_scale"),
+        query.shape[0], hq, hkv, d, bs, float(scale), code, _scale_ptr(k_scale, fp8, "k_scale"), _scale_ptr(v_scale, fp8, "v_scale"),
         _stream(query))
     _lib.check("hkb_paged_prefill", rc)
     return out

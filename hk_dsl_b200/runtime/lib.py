@@ -79,10 +79,10 @@ SIGNATURES = {
     "hkb_kvsplit_merge": (c_int, [ExchangeT, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "hkb_arrivals_bytes": (c_size_t, [c_int, c_int]),
     "hkb_paged_prefill": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, CacheT, CacheT,
-                                  c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                  c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                   c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p]),
     "hkb_paged_prefill_trace": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, CacheT, CacheT,
-                                        c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                        c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                         c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p,
                                         c_void_p]),
     "hkb_prefill_tile_rows": (c_int, [c_int, c_int]),

@@ -199,7 +199,9 @@ int hkb_merge(void* out, int64_t out_stride_tok, int64_t out_stride_head, int ou
  * hkb_prefill_tile_rows(num_q_heads, num_kv_heads) rows (the host builds it: query lengths
  * are host values in a prefill step; put long tiles first). Rows of requests that are not in
  * the work list are not written. bf16 caches, or fp8-e4m3 with per-tensor k_scale / v_scale
- * (device pointers to one float each; head_dim 128).
+ * (device pointers to one float each; head_dim 128). num_tokens: the rows q and out hold
+ * (q_start[last request + 1] at least): the tensor-memory kernel fetches query tiles with TMA and
+ * must know where the tensor ends.
  *
  * Replaces: paged_prefill_kernel and its work list (python/hk/ops/paged_prefill.py:59-620,
  * 879-968) as launched from python/hk/integration/vllm_backend.py:667-698.
@@ -209,7 +211,7 @@ int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_stride_head
                       hkb_cache_t k_cache, hkb_cache_t v_cache,
                       const int32_t* block_table, int64_t table_stride, int max_pages,
                       const int32_t* seq_lens, const int32_t* q_start,
-                      const int32_t* work, int num_work,
+                      const int32_t* work, int num_work, int num_tokens,
                       int num_q_heads, int num_kv_heads, int head_dim, int block_size,
                       float scale, int kv_dtype, const float* k_scale, const float* v_scale,
                       void* stream);
@@ -358,7 +360,7 @@ int hkb_paged_prefill_trace(void* out, int64_t out_stride_tok, int64_t out_strid
                             hkb_cache_t k_cache, hkb_cache_t v_cache,
                             const int32_t* block_table, int64_t table_stride, int max_pages,
                             const int32_t* seq_lens, const int32_t* q_start,
-                            const int32_t* work, int num_work,
+                            const int32_t* work, int num_work, int num_tokens,
                             int num_q_heads, int num_kv_heads, int head_dim, int block_size,
                             float scale, int kv_dtype, const float* k_scale, const float* v_scale,
                             unsigned long long* trace, void* stream);
