@@ -22,7 +22,7 @@ LIB = LIB_DIR / "libhkb.so"
 STAMP = LIB_DIR / "libhkb.stamp"
 
 SOURCES = ["hkb_api.cu", "hkb_scatter.cu", "hkb_decode.cu", "hkb_prefill.cu", "hkb_probe.cu", "hkb_exchange.cu"]
-HEADERS = ["hkb_common.cuh", "hkb_prefill_tc.cuh", "hkb_decode.cuh", "hkb_fold.cuh", "hkb_walk_cc.cuh", "hkb_walk_mma.cuh", "hkb_walk_stream.cuh"]
+HEADERS = ["hkb_common.cuh", "hkb_prefill_tc.cuh", "hkb_fold_wide.cuh", "hkb_decode.cuh", "hkb_fold.cuh", "hkb_walk_cc.cuh", "hkb_walk_mma.cuh", "hkb_walk_stream.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

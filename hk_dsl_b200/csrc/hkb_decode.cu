@@ -3,6 +3,7 @@
 #include "hkb_walk_cc.cuh"
 #include "hkb_walk_mma.cuh"
 #include "hkb_walk_stream.cuh"
+#include "hkb_fold_wide.cuh"
 
 #include <cstdlib>
 #include <mutex>
@@ -121,13 +122,11 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_kernel(const MergeArgs
     a.out_lse[(int64_t)row * a.num_q_heads + h] = den > 0.f ? mx + __logf(den) : -INFINITY;
 }
 
-// The same fold for many live parts a (sequence, head) -- a long sequence cut into a hundred
-// pieces: one CTA a (sequence, q head), its 8 warps take the parts round-robin (two in flight a
-// warp) and the warps' sums are added through shared memory in a fixed order.
+// The same fold for many parts a (sequence, head) -- a long sequence cut into a hundred pieces: one
+// CTA a (sequence, q head), three trips to memory in all (WideFold).
 template <int VEC>
 __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_wide_kernel(const MergeArgs a) {
-  __shared__ float s_mx[MERGE_WARPS];
-  __shared__ float s_acc[MERGE_WARPS][32 * VEC + 1];
+  __shared__ typename WideFold<VEC, MERGE_WARPS>::Smem sm;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.x, seq = blockIdx.y;
   int row = seq;
@@ -138,52 +137,9 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_wide_kernel(const Merg
   const bool empty = a.seq_lens && __ldg(a.seq_lens + seq) <= 0;
   const float* lse = a.part_lse + (int64_t)seq * a.lse_stride_seq + h;
   const float* po = a.part_out + (int64_t)seq * a.part_stride_seq + (int64_t)h * a.head_dim + lane * VEC;
-  float mx = -INFINITY;
-  for (int p = threadIdx.x; p < a.num_parts; p += MERGE_WARPS * 32) mx = fmaxf(mx, __ldg(lse + (int64_t)p * a.lse_stride_p));
-#pragma unroll
-  for (int x = 16; x > 0; x >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, x));
-  if (lane == 0) s_mx[warp] = mx;
-  __syncthreads();
-  mx = s_mx[0];
-#pragma unroll
-  for (int w = 1; w < MERGE_WARPS; ++w) mx = fmaxf(mx, s_mx[w]);
-  if (empty) mx = -INFINITY;
-
-  float acc[VEC];
-#pragma unroll
-  for (int v = 0; v < VEC; ++v) acc[v] = 0.f;
-  float den = 0.f;
-  if (mx != -INFINITY) {
-    for (int p = warp; p < a.num_parts; p += 2 * MERGE_WARPS) {
-      const int p2 = p + MERGE_WARPS;
-      const float l0 = __ldg(lse + (int64_t)p * a.lse_stride_p);
-      const float l1 = p2 < a.num_parts ? __ldg(lse + (int64_t)p2 * a.lse_stride_p) : -INFINITY;
-      const float w0 = l0 == -INFINITY ? 0.f : __expf(l0 - mx);   // an empty part's memory is never read
-      const float w1 = l1 == -INFINITY ? 0.f : __expf(l1 - mx);
-      float x0[VEC], x1[VEC];
-#pragma unroll
-      for (int v = 0; v < VEC; v += 2) {
-        float2 t0 = make_float2(0.f, 0.f), t1 = make_float2(0.f, 0.f);
-        if (w0 != 0.f) t0 = __ldg(reinterpret_cast<const float2*>(po + (int64_t)p * a.part_stride_p + v));
-        if (w1 != 0.f) t1 = __ldg(reinterpret_cast<const float2*>(po + (int64_t)p2 * a.part_stride_p + v));
-        x0[v] = t0.x; x0[v + 1] = t0.y; x1[v] = t1.x; x1[v + 1] = t1.y;
-      }
-#pragma unroll
-      for (int v = 0; v < VEC; ++v) acc[v] = fmaf(w1, x1[v], fmaf(w0, x0[v], acc[v]));
-      den += w0 + w1;
-    }
-  }
-#pragma unroll
-  for (int v = 0; v < VEC; ++v) s_acc[warp][lane * VEC + v] = acc[v];
-  if (lane == 0) s_acc[warp][32 * VEC] = den;
-  __syncthreads();
+  float acc[VEC], den, mx;
+  WideFold<VEC, MERGE_WARPS>::run(sm, lse, a.lse_stride_p, po, a.part_stride_p, a.num_parts, empty, acc, den, mx);
   if (warp != 0) return;
-  den = s_acc[0][32 * VEC];
-  for (int w = 1; w < MERGE_WARPS; ++w) {   // fixed order: the same bits every call
-#pragma unroll
-    for (int v = 0; v < VEC; ++v) acc[v] += s_acc[w][lane * VEC + v];
-    den += s_acc[w][32 * VEC];
-  }
   const float inv = den > 0.f ? 1.f / den : 0.f;
   const int64_t off = (int64_t)row * a.out_stride_tok + (int64_t)h * a.out_stride_head + lane * VEC;
   if (a.out_is_f32 == 1) {
@@ -442,6 +398,7 @@ static int merge_check(const void* out, int64_t out_stride_tok, int64_t out_stri
                        const float* part_out, int64_t part_stride_p, int64_t part_stride_seq, const float* part_lse,
                        int num_parts, int num_seqs, int num_q_heads, int head_dim) {
   if (num_seqs < 0 || num_q_heads <= 0 || num_parts < 1) return HKB_ERR_SIZE;
+  if (num_parts > HKB_MAX_SPLITS) return HKB_ERR_SPLITS;
   if (num_seqs == 0) return HKB_OK;
   if (!out || !part_out || !part_lse) return HKB_ERR_NULL;
   if (head_dim != 64 && head_dim != 128 && head_dim != 256) return HKB_ERR_HEAD_DIM;

@@ -21,7 +21,7 @@
 //
 // hk-dsl has no counterpart: it cuts the KV axis inside one GPU (python/hk/ops/paged.py:171-194)
 // and leaves tensor parallelism to the engine.
-#include "hkb_common.cuh"
+#include "hkb_fold_wide.cuh"
 
 extern thread_local int hkb_tls_cuda_error;
 
@@ -41,63 +41,21 @@ struct PushArgs {
   int64_t rec_floats;      // floats of one record (out then lse, padded to 4)
 };
 
-// One CTA a (sequence, head): its eight warps take the rank's splits round-robin (lse = -inf marks
-// a split without tokens; its memory is never read), the warps' sums are added through shared
-// memory in a fixed order, and warp 0 stores the normalised fp32 row and its lse into slot `rank`
-// of the step's half of every peer's gather buffer.
+// One CTA a (sequence, head): the fold of the rank's live splits (WideFold: lse = -inf marks a split
+// without tokens; its memory is never read), then warp 0 stores the normalised fp32 row and its lse
+// into slot `rank` of the step's half of every peer's gather buffer.
 template <int VEC>
 __global__ void __launch_bounds__(XCH_WARPS * 32) kvsplit_push_kernel(const PushArgs a) {
-  __shared__ float s_mx[XCH_WARPS];
-  __shared__ float s_acc[XCH_WARPS][32 * VEC + 1];
+  __shared__ typename WideFold<VEC, XCH_WARPS>::Smem sm;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.x, seq = blockIdx.y;
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch);
   const int64_t half_off = (int64_t)(epoch & 1u) * a.world * a.rec_floats + (int64_t)a.rank * a.rec_floats;
   const float* lse = a.part_lse + (int64_t)seq * a.num_splits * a.num_q_heads + h;
   const float* po = a.part_out + ((int64_t)seq * a.num_splits * a.num_q_heads + h) * a.head_dim + lane * VEC;
-  const int64_t lse_stride = a.num_q_heads, part_stride = (int64_t)a.num_q_heads * a.head_dim;
-  float mx = -INFINITY;
-  for (int p = threadIdx.x; p < a.num_splits; p += XCH_WARPS * 32) mx = fmaxf(mx, __ldg(lse + p * lse_stride));
-#pragma unroll
-  for (int x = 16; x > 0; x >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, x));
-  if (lane == 0) s_mx[warp] = mx;
-  __syncthreads();
-  mx = s_mx[0];
-#pragma unroll
-  for (int w = 1; w < XCH_WARPS; ++w) mx = fmaxf(mx, s_mx[w]);
-  float acc[VEC];
-#pragma unroll
-  for (int v = 0; v < VEC; ++v) acc[v] = 0.f;
-  float den = 0.f;
-  if (mx != -INFINITY) {
-    for (int p = warp; p < a.num_splits; p += 2 * XCH_WARPS) {      // two parts in flight a warp
-      const int p2 = p + XCH_WARPS;
-      const float l0 = __ldg(lse + p * lse_stride);
-      const float l1 = p2 < a.num_splits ? __ldg(lse + p2 * lse_stride) : -INFINITY;
-      const float w0 = l0 == -INFINITY ? 0.f : __expf(l0 - mx);
-      const float w1 = l1 == -INFINITY ? 0.f : __expf(l1 - mx);
-#pragma unroll
-      for (int v = 0; v < VEC; v += 2) {
-        float2 t0 = make_float2(0.f, 0.f), t1 = make_float2(0.f, 0.f);
-        if (w0 != 0.f) t0 = __ldg(reinterpret_cast<const float2*>(po + p * part_stride + v));
-        if (w1 != 0.f) t1 = __ldg(reinterpret_cast<const float2*>(po + p2 * part_stride + v));
-        acc[v] = fmaf(w1, t1.x, fmaf(w0, t0.x, acc[v]));
-        acc[v + 1] = fmaf(w1, t1.y, fmaf(w0, t0.y, acc[v + 1]));
-      }
-      den += w0 + w1;
-    }
-  }
-#pragma unroll
-  for (int v = 0; v < VEC; ++v) s_acc[warp][lane * VEC + v] = acc[v];
-  if (lane == 0) s_acc[warp][32 * VEC] = den;
-  __syncthreads();
+  float acc[VEC], den, mx;
+  WideFold<VEC, XCH_WARPS>::run(sm, lse, a.num_q_heads, po, (int64_t)a.num_q_heads * a.head_dim, a.num_splits, false, acc, den, mx);
   if (warp == 0) {
-    den = s_acc[0][32 * VEC];
-    for (int w = 1; w < XCH_WARPS; ++w) {   // fixed order: the same bits every call
-#pragma unroll
-      for (int v = 0; v < VEC; ++v) acc[v] += s_acc[w][lane * VEC + v];
-      den += s_acc[w][32 * VEC];
-    }
     const float inv = den > 0.f ? 1.f / den : 0.f;
     const float out_lse = den > 0.f ? mx + __logf(den) : -INFINITY;
     const int64_t row = ((int64_t)seq * a.num_q_heads + h) * a.head_dim + lane * VEC;
