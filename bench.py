@@ -827,7 +827,7 @@ def main():
             "splits": head["splits"], "cold_kv_detail": head["cold_kv_detail"], "cuda_graph": head["cuda_graph"],
             "parity": head["parity"], "read_probe": probe,
         }
-        for k in ("cuda_graph_note", "breakdown_us"):
+        for k in ("cuda_graph_note", "breakdown_us", "exchange", "exchange_error_word"):
             if k in head:
                 line[k] = head[k]
         if others:

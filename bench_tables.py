@@ -8,6 +8,7 @@ here is part of the bench line.
                                          measured bf16 tensor peak
     python bench_tables.py --prefill-trace [--case 1x0+8192]
                                          where the tensor-memory prefill kernel's cycles go, by role
+    python bench_tables.py --attrib      the decode walk with one stage left out: what each stage costs
 """
 
 from __future__ import annotations
@@ -281,13 +282,81 @@ def prefill_trace(case: str):
     return 0
 
 
+def attribution_table():
+    """What each stage of the decode walk costs on the headline shape (c2: batch 64, 32 q / 8 kv heads,
+    2k-8k tokens, bf16): the walk timed whole and with one stage left out (hkb_paged_decode_ablate),
+    each as a CUDA graph of 20 launches over cold caches, median of 7; the difference to the whole walk
+    is the stage's cost where stages do not overlap, and an upper bound where they do. The reference
+    builds the same table from its `ablate=` switches (tools/hk-bench/paged_attrib.py)."""
+    import torch
+
+    from hk_dsl_b200 import workloads as W
+    from hk_dsl_b200.ops import paged
+    from hk_dsl_b200.runtime import lib as hkb
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    spec = W.CONFIGS["c2"]
+    st = W.build_step(spec, dev)
+    n, hq, d = st.query.shape
+    splits = paged.plan_splits(n, st.kv_heads, st.block_table.shape[1], device=dev)
+    po, pl = paged.split_scratch(n, hq, d, splits, dev)
+    lib = hkb.load()
+    kc, vc = st.k_caches[0], st.v_caches[0]
+    cache = lambda c: hkb.CacheT(c.data_ptr(), c.stride(0), c.stride(1), c.stride(2), c.shape[0])
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def launch(mask):
+        rc = lib.hkb_paged_decode_ablate(st.out.data_ptr(), st.out.stride(0), st.out.stride(1), st.query.data_ptr(),
+                                         st.query.stride(0), st.query.stride(1), cache(kc), cache(vc),
+                                         st.block_table.data_ptr(), st.block_table.stride(0), st.block_table.shape[1],
+                                         st.seq_lens.data_ptr(), None, n, hq, st.kv_heads, d, spec.block_size, st.scale,
+                                         hkb.KV_BF16, None, None, splits, po.data_ptr(), pl.data_ptr(), mask,
+                                         torch.cuda.current_stream().cuda_stream)
+        hkb.check("hkb_paged_decode_ablate", rc)
+
+    names = {0: "the whole walk", 1: "without the page-table reads", 2: "without the K copies", 4: "without the V copies",
+             6: "without any copy (math on stale tiles)", 8: "without the q.K products", 16: "without the softmax",
+             32: "without the p.V products", 56: "without any math (copies only)"}
+    rows, whole = [], None
+    for mask, what in names.items():
+        for _ in range(3):
+            launch(mask)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(20):
+                launch(mask)
+        g.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(7):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3 / 20)
+        us = statistics.median(times)
+        whole = us if mask == 0 else whole
+        rows.append({"mask": mask, "walk": what, "us": round(us, 2), "saves_us": round(whole - us, 2),
+                     "kv_gbs_if_all_bytes_moved": round(st.kv_bytes / us / 1e3, 1)})
+    del stream
+    print(json.dumps({"table": "decode walk on c2 with one stage left out, us a launch (cold KV, graph of 20, median of 7)",
+                      "kv_bytes": st.kv_bytes, "splits": splits, "rows": rows}, indent=1), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--latency", action="store_true")
     ap.add_argument("--prefill", action="store_true")
     ap.add_argument("--case", default="", help="with --prefill: one shape, REQUESTSxCONTEXT+QLEN (a small case for a profiler)")
     ap.add_argument("--prefill-trace", action="store_true", help="cycles by role and phase of the tensor-memory prefill kernel")
+    ap.add_argument("--attrib", action="store_true", help="the decode walk with one stage left out: what each stage costs")
     args = ap.parse_args()
+    if args.attrib:
+        return attribution_table()
     if args.prefill_trace:
         return prefill_trace(args.case)
     if args.prefill:

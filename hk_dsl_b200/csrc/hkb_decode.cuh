@@ -47,6 +47,7 @@ struct DecodeArgs {
   const void* slots;
   int slot_is_i64;
   int block_size;
+  int xsplit;   // the caches are in the x-split layout (XSplitLoader); strides then describe blocks and heads only
 };
 
 // The range of 16-token tiles split `split` of a sequence with `n_tiles` tiles walks:
@@ -126,6 +127,72 @@ struct TileLoader {
     tile_ptrs(tile, page_id, kp, vp);
     copy_tile(smem_stage, kp, kst, lane_k, k_flat);
     copy_tile(smem_stage + TILE_BYTES, vp, vst, lane_v, v_flat);
+  }
+};
+
+// The same interface over vLLM's older "x-split" cache layout, read in place
+// (python/hk/ops/paged_prefill.py:768-772, `rocm_views`): K is (blocks, kv_heads, head_dim / x, page, x)
+// with x = 8 sixteen-bit elements -- a token's row is head_dim / 8 chunks of 16 bytes, page * 16 bytes
+// apart -- and V is (blocks, kv_heads, head_dim, page): V^T, a dim's tokens contiguous. The K tile
+// lands in shared memory exactly where TileLoader puts it (token rows, XOR-swizzled chunks), so the
+// score product is unchanged; the V tile lands as it is stored, [dim][16 tokens] in 32-byte rows
+// (the two 16-byte halves of a row swapped on every other group of four rows, which keeps the
+// eight rows of an ldmatrix on distinct banks), and the second product reads it without a transpose.
+template <int D>
+struct XSplitLoader {
+  static constexpr int ROWB = D * 2;
+  static constexpr int TILE_BYTES = TILE_TOKENS * ROWB;      // K tile and V^T tile: 4 KB each at head_dim 128
+  const uint8_t* kbase;
+  const uint8_t* vbase;
+  int64_t ksb, kst, vsb, vst;   // ksb / vsb: bytes between blocks; kst / vst are not used (the layout fixes them)
+  int tiles_per_page, num_blocks;
+  uint32_t kdst, vdst;          // this lane's shared-memory offsets in iteration 0
+  int klane, vlane;             // and its global offsets
+
+  __device__ __forceinline__ void prepare(int lane) {
+    // K: a chunk index c is 16 tokens x 16 bytes contiguous; a half-warp takes one chunk, token r = lane % 16
+    const int r = lane & 15;
+    kdst = (uint32_t)(r * ROWB);                 // + ((c ^ (r & 7)) << 4), c = 2 it + lane / 16
+    klane = r * 16;
+    // V^T: a dim row is 32 bytes (16 tokens); two lanes a row, 16 rows an iteration
+    const int d = lane >> 1, h = lane & 1;
+    vdst = (uint32_t)(d * 32 + ((h ^ ((d >> 2) & 1)) << 4));
+    vlane = h * 16;
+  }
+  __device__ __forceinline__ void tile_ptrs(int tile, int page_id, const uint8_t*& kp, const uint8_t*& vp) const {
+    const int id = min(max(page_id, 0), num_blocks - 1);
+    const int sub = tiles_per_page != 1 ? tile % tiles_per_page : 0;
+    kp = kbase + (int64_t)id * ksb + sub * (TILE_TOKENS * 16);
+    vp = vbase + (int64_t)id * vsb + sub * (TILE_TOKENS * 2);
+  }
+  __device__ __forceinline__ void issue_k(uint32_t dst, const uint8_t* kp, int lane) const {
+    const int chunk_stride = tiles_per_page * TILE_TOKENS * 16;      // page tokens x 16 bytes
+    const int r = lane & 15;
+#pragma unroll
+    for (int it = 0; it < D / 16; ++it) {                            // D / 8 chunks, two an iteration
+      const int c = 2 * it + (lane >> 4);
+      cp_async16(dst + kdst + ((c ^ (r & 7)) << 4), kp + (int64_t)c * chunk_stride + klane);
+    }
+  }
+  __device__ __forceinline__ void issue_v(uint32_t dst, const uint8_t* vp, int lane) const {
+    const int dim_stride = tiles_per_page * TILE_TOKENS * 2;         // page tokens x 2 bytes
+#pragma unroll
+    for (int it = 0; it < D / 16; ++it) {                            // 16 dim rows an iteration
+      const int d = it * 16 + (lane >> 1);
+      cp_async16(dst + it * 512 + vdst, vp + (int64_t)d * dim_stride + vlane);
+    }
+  }
+  __device__ __forceinline__ void issue_one(uint32_t smem_stage, int tile, int page_id, int lane, int which) const {
+    const uint8_t *kp, *vp;
+    tile_ptrs(tile, page_id, kp, vp);
+    if (which) issue_v(smem_stage + TILE_BYTES, vp, lane);
+    else issue_k(smem_stage, kp, lane);
+  }
+  __device__ __forceinline__ void issue(uint32_t smem_stage, int tile, int page_id, int lane) const {
+    const uint8_t *kp, *vp;
+    tile_ptrs(tile, page_id, kp, vp);
+    issue_k(smem_stage, kp, lane);
+    issue_v(smem_stage + TILE_BYTES, vp, lane);
   }
 };
 

@@ -15,6 +15,8 @@
 // shared-memory tile first (exact: e4m3 fits bf16), so both dtypes share the mma code.
 #pragma once
 
+#include <type_traits>
+
 #include "hkb_decode.cuh"
 
 namespace hkb {
@@ -66,13 +68,15 @@ __device__ __forceinline__ void store16(__nv_bfloat16* p, float x) {
   if (F16) *reinterpret_cast<__half*>(p) = __float2half_rn(x); else *p = __float2bfloat16(x);
 }
 
-template <int D, bool FP8, int NT, int WARPS, int NST, bool F16 = false>
+// VT: the caches are in the x-split layout (XSplitLoader): the V tile sits in shared memory as V^T.
+template <int D, bool FP8, int NT, int WARPS, int NST, bool F16 = false, bool VT = false>
 struct WalkMMA {
   static_assert(!(FP8 && F16), "an fp8 cache goes with bf16 activations");
+  static_assert(!(VT && FP8), "the x-split layout is read for 16-bit caches");
   static constexpr int ES = FP8 ? 1 : 2;
   static constexpr int ROWB = D * ES;     // bytes of a row as it sits in the cache
   static constexpr int ROWB16 = D * 2;    // bytes of a row as the mma reads it
-  using Loader = TileLoader<ROWB>;
+  using Loader = typename std::conditional<VT, XSplitLoader<D>, TileLoader<ROWB>>::type;
   static constexpr int STAGE_BYTES = 2 * Loader::TILE_BYTES;
   static constexpr int TILE16_BYTES = TILE_TOKENS * ROWB16;
   static constexpr int WIDEN_BYTES = FP8 ? 2 * TILE16_BYTES : 0;  // per warp
@@ -172,15 +176,29 @@ struct WalkMMA {
       pb[nt][0] = movmatrix_trans(pack16x2<F16>(p0, p1));
       pb[nt][1] = movmatrix_trans(pack16x2<F16>(p2, p3));
     }
-    // O^T += V^T P^T: A = V^T (16 dims x tokens), read transposed from the row-major V tile
+    // O^T += V^T P^T: A = V^T (16 dims x tokens), read transposed from the row-major V tile -- or, where
+    // the cache stores V^T, straight from the [dim][16 tokens] tile: matrix m of the ldmatrix is dims
+    // 8 (m & 1) .. + 7, tokens 8 (m >> 1) .. + 7
     if (!(ABL & ABL_PV)) {
-      const int r = (lane & 7) + (lane >> 4) * 8;
+      if (VT) {
+        const int dl = (lane & 7) + ((lane >> 3) & 1) * 8, th = lane >> 4;
 #pragma unroll
-      for (int dt = 0; dt < KD; ++dt) {
-        uint32_t a[4];
-        ldmatrix_x4_trans(a, vtile + tile_off<ROWB16>(r, dt * 2 + ((lane >> 3) & 1)));
+        for (int dt = 0; dt < KD; ++dt) {
+          const int d = dt * 16 + dl;
+          uint32_t a[4];
+          ldmatrix_x4(a, vtile + d * 32 + ((th ^ ((d >> 2) & 1)) << 4));
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) mma16<F16>(o[nt][dt], a, pb[nt]);
+          for (int nt = 0; nt < NT; ++nt) mma16<F16>(o[nt][dt], a, pb[nt]);
+        }
+      } else {
+        const int r = (lane & 7) + (lane >> 4) * 8;
+#pragma unroll
+        for (int dt = 0; dt < KD; ++dt) {
+          uint32_t a[4];
+          ldmatrix_x4_trans(a, vtile + tile_off<ROWB16>(r, dt * 2 + ((lane >> 3) & 1)));
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) mma16<F16>(o[nt][dt], a, pb[nt]);
+        }
       }
     } else {
 #pragma unroll
@@ -190,6 +208,24 @@ struct WalkMMA {
 
   // Zero the V rows of a tail tile that lie past seq_len: P is 0 there, but 0 * NaN is NaN.
   __device__ static __forceinline__ void scrub_tail(uint32_t vtile, int tok0, int seq_len, int lane) {
+    if (VT) {   // V^T tile: tokens are the columns of every dim row
+      const int live = seq_len - tok0;                       // 1..15 live tokens here
+      for (int x = lane; x < D * 2; x += 32) {               // (dim row, 16-byte half): 8 tokens each
+        const int d = x >> 1, h = x & 1;
+        const uint32_t addr = vtile + d * 32 + ((h ^ ((d >> 2) & 1)) << 4);
+        const int first = live - h * 8;                      // tokens of this half at or past `first` are dead
+        if (first >= 8) continue;
+        uint4 v = lds128(addr);
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (2 * i >= first) w[i] = 0u;
+          else if (2 * i + 1 >= first) w[i] &= 0xffffu;
+        }
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+      }
+      return;
+    }
     constexpr int CPR = ROWB16 / 16;
     for (int x = lane; x < TILE_TOKENS * CPR; x += 32) {
       const int r = x / CPR, c = x % CPR;
