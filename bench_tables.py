@@ -347,14 +347,78 @@ def attribution_table():
     return 0
 
 
+def layouts_table(only: str = ""):
+    """The decode (walk + merge) on the headline shape (c2) over the same KV values in the two cache
+    layouts the walk reads in place: (blocks, page, kv_heads, head_dim) and vLLM's x-split pair
+    (K (blocks, kv_heads, head_dim / 8, page, 8), V^T (blocks, kv_heads, head_dim, page)). Graph of 20
+    launches over KV larger than L2, median of 7; the two answers are compared bit for bit. `only`:
+    one layout ("nhd" or "x-split"), a short run for a profiler."""
+    import torch
+
+    from hk_dsl_b200 import workloads as W
+    from hk_dsl_b200.ops import paged
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    spec = W.CONFIGS["c2"]
+    st = W.build_step(spec, dev)
+    n, hq, d = st.query.shape
+    splits = paged.plan_splits(n, st.kv_heads, st.block_table.shape[1], device=dev)
+    scratch = paged.split_scratch(n, hq, d, splits, dev)
+    kc, vc = st.k_caches[0], st.v_caches[0]
+    k5, v4 = paged.x_split_caches(kc, vc)
+    outs = {"nhd": torch.empty_like(st.out), "x-split": torch.empty_like(st.out)}
+    calls = {
+        "nhd": lambda: paged.paged_attention_decode(outs["nhd"], st.query, kc, vc, st.block_table, st.seq_lens, st.scale,
+                                                    num_splits=splits, scratch=scratch),
+        "x-split": lambda: paged.paged_attention_decode_xsplit(outs["x-split"], st.query, k5, v4, st.block_table,
+                                                               st.seq_lens, st.scale, num_splits=splits, scratch=scratch),
+    }
+    rows = []
+    if only:
+        for _ in range(3):
+            calls[only]()
+        torch.cuda.synchronize()
+        return 0
+    for name, call in calls.items():
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(20):
+                call()
+        g.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(7):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3 / 20)
+        us = statistics.median(times)
+        rows.append({"layout": name, "us": round(us, 2), "kv_gbs": round(st.kv_bytes / us / 1e3, 1)})
+    same = bool(torch.equal(outs["nhd"].view(torch.int16), outs["x-split"].view(torch.int16)))
+    print(json.dumps({"table": "decode (walk + merge) on c2 by cache layout, us a step (cold KV, graph of 20, median of 7)",
+                      "kv_bytes": st.kv_bytes, "splits": splits, "answers_bitwise_equal": same, "rows": rows}, indent=1),
+          flush=True)
+    return 0 if same else 1
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--latency", action="store_true")
     ap.add_argument("--prefill", action="store_true")
-    ap.add_argument("--case", default="", help="with --prefill: one shape, REQUESTSxCONTEXT+QLEN (a small case for a profiler)")
+    ap.add_argument("--case", default="", help="with --prefill: one shape, REQUESTSxCONTEXT+QLEN; with --layouts: nhd or "
+                                               "x-split (a small case for a profiler)")
     ap.add_argument("--prefill-trace", action="store_true", help="cycles by role and phase of the tensor-memory prefill kernel")
     ap.add_argument("--attrib", action="store_true", help="the decode walk with one stage left out: what each stage costs")
+    ap.add_argument("--layouts", action="store_true", help="the decode over the usual and the x-split cache layout")
     args = ap.parse_args()
+    if args.layouts:
+        return layouts_table(args.case)
     if args.attrib:
         return attribution_table()
     if args.prefill_trace:

@@ -335,7 +335,21 @@ struct StepExtra {
   bool wrote = false;    // out: the walk wrote the new rows into the cache itself
   bool folded = false;   // out: the walk folded the partials itself
   int ablate = 0;        // ABL_* mask: an attribution run (hkb_paged_decode_ablate)
+  bool xsplit = false;   // the caches are in the x-split layout (hkb_paged_decode_xsplit)
 };
+
+// The stream walk over x-split caches: head_dim 128, 16-bit caches, the tensor-core worker at
+// every group (a group below 8 leaves columns of its one tile empty, as at a group of 4).
+template <bool F16>
+static int dispatch_xsplit(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
+  const dim3 grid = stream_grid(a.num_kv_heads);
+  if (a.group <= 8) {
+    using P = WalkMMA<128, false, 1, 4, 3, F16, true>;
+    return launch_stream<walk_stream_kernel<P, 4>>(WalkStream<P, 4>::SMEM_BYTES, 4 * 32, grid, a, num_seqs, st);
+  }
+  using P2 = WalkMMA<128, false, 2, 4, 3, F16, true>;
+  return launch_stream<walk_stream_kernel<P2, 4>>(WalkStream<P2, 4>::SMEM_BYTES, 4 * 32, grid, a, num_seqs, st);
+}
 
 // The stream walk with stages left out. Built for the headline shape only -- head_dim 128, a bf16
 // cache, a GQA group of 4 to 8 on the tensor-core worker, more than one split -- and for the masks
@@ -444,6 +458,11 @@ static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_hea
   a.arrivals = nullptr; a.new_k = nullptr; a.new_v = nullptr;
   a.new_k_stride_tok = a.new_k_stride_head = a.new_v_stride_tok = a.new_v_stride_head = 0;
   a.slots = nullptr; a.slot_is_i64 = 0; a.block_size = block_size;
+  a.xsplit = extra && extra->xsplit;
+  if (a.xsplit) {
+    if (head_dim != 128 || fp8 || num_splits < 2 || num_seqs > STREAM_MAX_SEQS) return HKB_ERR_UNSUPPORTED;
+    return f16 ? dispatch_xsplit<true>(a, num_seqs, (cudaStream_t)stream) : dispatch_xsplit<false>(a, num_seqs, (cudaStream_t)stream);
+  }
   if (extra && step_fusable(num_splits, num_seqs)) {
     if (extra->arrivals && !f16) {   // the fold on arrival writes bf16; fp16 steps keep the merge launch
       a.arrivals = extra->arrivals;
@@ -510,6 +529,37 @@ extern "C" int hkb_paged_decode(void* out, int64_t out_stride_tok, int64_t out_s
   return hkb::decode_impl(out, out_stride_tok, out_stride_head, q, q_stride_tok, q_stride_head, kc, vc, block_table,
                           table_stride, max_pages, seq_lens, q_start, num_seqs, num_q_heads, num_kv_heads, head_dim,
                           block_size, scale, kv_dtype, k_scale, v_scale, num_splits, part_out, part_lse, stream, nullptr);
+}
+
+// The walk of hkb_paged_decode over caches in vLLM's x-split layout, read in place: K is
+// (blocks, kv_heads, head_dim / 8, block_size, 8) and V is (blocks, kv_heads, head_dim, block_size),
+// 16-bit elements, heads and everything inside them contiguous; `*_stride_block` is elements between
+// blocks. Replaces python/hk/ops/paged_prefill.py:768-772 (`rocm_views`, strided views that the
+// reference's kernels read) and the decode over them (`_rocm_decode`,
+// python/hk/integration/vllm_prefill.py:1332-1356). Always split (num_splits >= 2): partials go to
+// `part_out` / `part_lse` as in hkb_paged_decode and hkb_merge folds them.
+extern "C" int hkb_paged_decode_xsplit(void* out, int64_t out_stride_tok, int64_t out_stride_head,
+                                       const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                                       const void* k_cache, int64_t k_stride_block,
+                                       const void* v_cache, int64_t v_stride_block, int64_t num_blocks,
+                                       const int32_t* block_table, int64_t table_stride, int max_pages,
+                                       const int32_t* seq_lens, const int32_t* q_start,
+                                       int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                                       int block_size, float scale, int kv_dtype,
+                                       int num_splits, float* part_out, float* part_lse, void* stream) {
+  if (block_size <= 0) return HKB_ERR_BLOCK_SIZE;
+  if (head_dim != 128 || (kv_dtype != HKB_KV_BF16 && kv_dtype != HKB_KV_F16)) return HKB_ERR_UNSUPPORTED;
+  if (num_splits < 2) return HKB_ERR_SPLITS;
+  if (num_seqs > hkb::STREAM_MAX_SEQS) return HKB_ERR_SIZE;
+  const int64_t head = (int64_t)head_dim * block_size;
+  if (num_kv_heads > 0 && (k_stride_block < head * num_kv_heads || v_stride_block < head * num_kv_heads)) return HKB_ERR_STRIDE;
+  hkb_cache_t kc{const_cast<void*>(k_cache), k_stride_block, 8, head, num_blocks};
+  hkb_cache_t vc{const_cast<void*>(v_cache), v_stride_block, 8, head, num_blocks};
+  hkb::StepExtra extra;
+  extra.xsplit = true;
+  return hkb::decode_impl(out, out_stride_tok, out_stride_head, q, q_stride_tok, q_stride_head, kc, vc, block_table,
+                          table_stride, max_pages, seq_lens, q_start, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                          block_size, scale, kv_dtype, nullptr, nullptr, num_splits, part_out, part_lse, stream, &extra);
 }
 
 namespace hkb {

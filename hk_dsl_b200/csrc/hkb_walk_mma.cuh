@@ -127,7 +127,8 @@ struct WalkMMA {
 #pragma unroll
       for (int kc = 0; kc < KD; ++kc) {
         uint32_t a[4];
-        ldmatrix_x4(a, ktile + tile_off<ROWB16>(r, kc * 2 + (lane >> 4)));
+        // the x-split K tile is [chunk][16 tokens][16 bytes]; the usual one token rows, chunks swizzled
+        ldmatrix_x4(a, ktile + (VT ? (kc * 2 + (lane >> 4)) * 256 + r * 16 : tile_off<ROWB16>(r, kc * 2 + (lane >> 4))));
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) mma16<F16>(sc[nt], a, qb[nt][kc]);
       }

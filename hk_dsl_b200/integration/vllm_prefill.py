@@ -314,6 +314,45 @@ _R_READ = frozenset(("query", "key", "value", "output", "kv_cache_dtype", "key_c
                      "sm_scale", "causal"))
 
 
+def _x_split_why_not(q, out, kc, vc, block_table, seq_lens, q_start) -> str:
+    """The decode-only checks for ROCM_ATTN's own cache pair -- K (blocks, kv_heads, head_dim / x,
+    page, x), V (blocks, kv_heads, head_dim, page) -- which the walk reads in place
+    (python/hk/integration/vllm_prefill.py:1287-1330 of the reference)."""
+    if q.dim() != 3:
+        return f"query {tuple(q.shape)}"
+    if q.dtype not in paged.ACT_DTYPES or out.dtype != q.dtype:
+        return f"query / output {q.dtype} / {out.dtype}"
+    why = paged.x_split_why_not(kc, vc, int(q.shape[-1]))
+    if why:
+        return why
+    if kc.dtype != q.dtype:
+        return f"x-split cache {kc.dtype} under {q.dtype} activations"
+    if q.shape[1] % kc.shape[1] or q.shape[1] // kc.shape[1] > paged.Q_TILE:
+        return "query heads not a multiple of kv heads, or more than 16 a kv head"
+    if seq_lens.shape[0] > 2048:
+        return f"{seq_lens.shape[0]} sequences (the x-split walk takes 2048)"
+    for t in (block_table, seq_lens, q_start):
+        if t is not None and (t.dtype != torch.int32 or not t.is_contiguous()):
+            return "metadata not contiguous int32"
+    if q.stride(-1) != 1 or out.stride(-1) != 1 or out.shape != q.shape:
+        return "q / output head_dim not contiguous"
+    return ""
+
+
+def _x_split_decode(q, out, kc, vc, block_table, seq_lens, q_start, scale) -> bool:
+    """The split decode over x-split caches; False if its scratch would have to grow under capture."""
+    n, hq, d = q.shape
+    reqs = seq_lens.shape[0]
+    hkv, page = int(kc.shape[1]), int(kc.shape[3])
+    splits = max(2, paged.plan_splits(reqs, hkv, block_table.shape[1] * (page // 16), device=q.device))
+    scratch = _scratch(q.device, reqs * splits, hq, d)
+    if scratch is None:
+        return False
+    paged.paged_attention_decode_xsplit(out, q, kc, vc, block_table, seq_lens, d ** -0.5 if scale is None else float(scale),
+                                        num_splits=splits, scratch=scratch, query_start_loc=q_start)
+    return True
+
+
 def rd_why_not(a: dict) -> str:
     """Why this decode-only chunked_prefill_paged_decode call is not taken, or ""."""
     if not ROCM_DECODE:
@@ -329,20 +368,27 @@ def rd_why_not(a: dict) -> str:
     if unknown:
         return f"{unknown} set (an argument hk does not know)"
     kc, vc = a["key_cache"], a["value_cache"]
-    if kc.dim() != 4 or vc.dim() != 4:
-        return "key_cache / value_cache: the x-split 5-D layout is not read in place"
+    if kc.dim() == 5:
+        return _x_split_why_not(a["query"], a["output"], kc, vc, a["block_table"], a["seq_lens"],
+                                a.get("query_start_loc"))
     return _common_why_not(a["query"], a["output"], kc, vc, a["block_table"], a["seq_lens"],
                            a.get("query_start_loc"), a.get("k_scale"), a.get("v_scale"))
 
 
 def chunked_prefill_paged_decode(*args, **kwargs):
     """vLLM's chunked_prefill_paged_decode: a decode-only call on 4-D (blocks, page, kv_heads,
-    head_dim) caches goes to the paged decode, anything else to the original."""
+    head_dim) caches, or on its own x-split K / V^T pair, goes to the paged decode, anything else
+    to the original."""
     a = kwargs if not args else _R_SIG.bind(*args, **kwargs).arguments
     why = rd_why_not(a)
     if not why:
-        if _decode(a["query"], a["output"], a["key_cache"], a["value_cache"], a["block_table"], a["seq_lens"],
-                   a.get("query_start_loc"), a.get("sm_scale"), a.get("k_scale"), a.get("v_scale")):
+        if a["key_cache"].dim() == 5:
+            ran = _x_split_decode(a["query"], a["output"], a["key_cache"], a["value_cache"], a["block_table"],
+                                  a["seq_lens"], a.get("query_start_loc"), a.get("sm_scale"))
+        else:
+            ran = _decode(a["query"], a["output"], a["key_cache"], a["value_cache"], a["block_table"], a["seq_lens"],
+                          a.get("query_start_loc"), a.get("sm_scale"), a.get("k_scale"), a.get("v_scale"))
+        if ran:
             PATCH.count("decode")
             if SHADOW:
                 _shadow(_ORIG_R, dict(a), "output", "query_start_loc")

@@ -157,7 +157,29 @@ def split_scratch(num_seqs: int, num_q_heads: int, head_dim: int, num_splits: in
             torch.empty(rows, num_q_heads, device=device, dtype=torch.float32))
 
 
-def _decode_call(out, query, key_cache, value_cache, block_tables, seq_lens, query_start_loc):
+def x_split_why_not(key_cache, value_cache, head_dim: int) -> str:
+    """Why these caches are not vLLM's x-split pair as the decode reads it, or "": K
+    (blocks, kv_heads, head_dim / 8, block_size, 8) and V (blocks, kv_heads, head_dim, block_size),
+    16-bit, everything inside a block contiguous (python/hk/ops/paged_prefill.py:768-772)."""
+    if key_cache.dim() != 5 or value_cache.dim() != 4:
+        return f"caches {tuple(key_cache.shape)} / {tuple(value_cache.shape)}: not the 5-D K, 4-D V pair"
+    nb, hkv, chunks, page, x = key_cache.shape
+    if key_cache.dtype not in ACT_DTYPES or value_cache.dtype != key_cache.dtype:
+        return f"x-split caches of {key_cache.dtype} / {value_cache.dtype} (16-bit only)"
+    if x != 8 or chunks * x != head_dim or head_dim != 128:
+        return f"x-split K {tuple(key_cache.shape)} at head size {head_dim} (x = 8, head size 128 only)"
+    if tuple(value_cache.shape) != (nb, hkv, head_dim, page):
+        return f"x-split V {tuple(value_cache.shape)} beside K {tuple(key_cache.shape)}"
+    if page % 16:
+        return f"block size {page} (a multiple of 16)"
+    if key_cache.stride()[1:] != (head_dim * page, page * 8, 8, 1) or value_cache.stride()[1:] != (head_dim * page, page, 1):
+        return "x-split caches not contiguous inside a block"
+    if key_cache.stride(0) < hkv * head_dim * page or value_cache.stride(0) < hkv * head_dim * page:
+        return "x-split blocks overlap"
+    return ""
+
+
+def _decode_call(out, query, key_cache, value_cache, block_tables, seq_lens, query_start_loc, x_split: bool = False):
     """Validate the tensors of a decode call; returns (seqs, q_heads, head_dim, block_size, kv_heads, q_start ptr)."""
     _need_cuda(out, query, key_cache, value_cache, block_tables, seq_lens)
     if query.dim() != 3 or query.dtype not in ACT_DTYPES or query.stride(2) != 1:
@@ -167,12 +189,18 @@ def _decode_call(out, query, key_cache, value_cache, block_tables, seq_lens, que
         raise ValueError(f"hk.ops.paged: out is {tuple(out.shape)} {out.dtype}; it must match query "
                          f"{tuple(query.shape)} {query.dtype}")
     _, hq, d = query.shape
-    if key_cache.dim() != 4 or value_cache.shape != key_cache.shape or key_cache.stride(3) != 1 \
-            or value_cache.stride(3) != 1 or key_cache.shape[3] != d or value_cache.dtype != key_cache.dtype:
-        raise ValueError(f"hk.ops.paged: key_cache {tuple(key_cache.shape)} / value_cache "
-                         f"{tuple(value_cache.shape)}; the decode reads two (blocks, block_size, kv_heads, {d}) "
-                         f"views of one dtype")
-    _, bs, hkv, _ = key_cache.shape
+    if x_split:
+        why = x_split_why_not(key_cache, value_cache, d)
+        if why:
+            raise ValueError(f"hk.ops.paged: {why}")
+        bs, hkv = key_cache.shape[3], key_cache.shape[1]
+    else:
+        if key_cache.dim() != 4 or value_cache.shape != key_cache.shape or key_cache.stride(3) != 1 \
+                or value_cache.stride(3) != 1 or key_cache.shape[3] != d or value_cache.dtype != key_cache.dtype:
+            raise ValueError(f"hk.ops.paged: key_cache {tuple(key_cache.shape)} / value_cache "
+                             f"{tuple(value_cache.shape)}; the decode reads two (blocks, block_size, kv_heads, {d}) "
+                             f"views of one dtype")
+        _, bs, hkv, _ = key_cache.shape
     if block_tables.dim() != 2 or block_tables.dtype != torch.int32 or block_tables.stride(1) != 1:
         raise TypeError(f"hk.ops.paged: block_tables is {tuple(block_tables.shape)} {block_tables.dtype}; "
                         f"(seqs, max_pages) int32 needed")
@@ -245,6 +273,50 @@ def paged_attention_decode(out: torch.Tensor, query: torch.Tensor, key_cache: to
                            num_splits, n, hq, d, seq_lens.data_ptr(), qsl, st)
         _lib.check("hkb_merge", rc)
     return out
+
+
+def paged_attention_decode_xsplit(out: torch.Tensor, query: torch.Tensor, key_cache: torch.Tensor,
+                                  value_cache: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor,
+                                  scale: float, *, num_splits: Optional[int] = None,
+                                  scratch: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                                  query_start_loc: Optional[torch.Tensor] = None,
+                                  max_seq_len: Optional[int] = None) -> torch.Tensor:
+    """`paged_attention_decode` over vLLM's x-split caches, read in place: `key_cache`
+    (blocks, kv_heads, head_dim / 8, block_size, 8), `value_cache` (blocks, kv_heads, head_dim,
+    block_size), bf16 or fp16, head_dim 128 (`x_split_why_not`). What the reference reaches through
+    `rocm_views` and `_rocm_decode` (python/hk/ops/paged_prefill.py:768-772,
+    python/hk/integration/vllm_prefill.py:1332-1356). Always the balanced tile stream: at least
+    two splits, at most 2048 sequences."""
+    n, hq, d, bs, hkv, qsl = _decode_call(out, query, key_cache, value_cache, block_tables, seq_lens, query_start_loc,
+                                          x_split=True)
+    if num_splits is None:
+        tiles = block_tables.shape[1] * (bs // 16) if max_seq_len is None else -(-max_seq_len // 16)
+        num_splits = plan_splits(n, hkv, tiles, device=query.device)
+    num_splits = max(2, int(num_splits))
+    po, pl, scratch = _scratch_ptrs(scratch, n, hq, d, num_splits, query.device)
+    lib = _lib.load()
+    st = _stream(query)
+    code = _lib.KV_F16 if query.dtype == torch.float16 else _lib.KV_BF16
+    rc = lib.hkb_paged_decode_xsplit(
+        out.data_ptr(), out.stride(0), out.stride(1), query.data_ptr(), query.stride(0), query.stride(1),
+        key_cache.data_ptr(), key_cache.stride(0), value_cache.data_ptr(), value_cache.stride(0), key_cache.shape[0],
+        block_tables.data_ptr(), block_tables.stride(0), block_tables.shape[1], seq_lens.data_ptr(), qsl,
+        n, hq, hkv, d, bs, float(scale), code, num_splits, po.data_ptr(), pl.data_ptr(), st)
+    _lib.check("hkb_paged_decode_xsplit", rc)
+    rc = lib.hkb_merge(out.data_ptr(), out.stride(0), out.stride(1), 2 if out.dtype == torch.float16 else 0, None,
+                       po.data_ptr(), hq * d, num_splits * hq * d, pl.data_ptr(), hq, num_splits * hq,
+                       num_splits, n, hq, d, seq_lens.data_ptr(), qsl, st)
+    _lib.check("hkb_merge", rc)
+    return out
+
+
+def x_split_caches(key_cache: torch.Tensor, value_cache: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """A (blocks, block_size, kv_heads, head_dim) cache pair copied into the x-split layout (for
+    tests and tools; an engine that uses the layout allocates it so)."""
+    nb, bs, hkv, d = key_cache.shape
+    k5 = key_cache.permute(0, 2, 1, 3).reshape(nb, hkv, bs, d // 8, 8).permute(0, 1, 3, 2, 4).contiguous()
+    v4 = value_cache.permute(0, 2, 3, 1).contiguous()
+    return k5, v4
 
 
 def step_arrivals(num_seqs: int, num_kv_heads: int, device) -> torch.Tensor:

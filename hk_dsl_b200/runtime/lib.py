@@ -56,6 +56,10 @@ SIGNATURES = {
                                  c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                  c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                  c_void_p]),
+    "hkb_paged_decode_xsplit": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64,
+                                        c_void_p, c_int64, c_void_p, c_int64, c_int64,
+                                        c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                        c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "hkb_paged_decode_ablate": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, CacheT, CacheT,
                                         c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                         c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,

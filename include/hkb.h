@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define HKB_VERSION 120 /* major*100 + minor */
+#define HKB_VERSION 121 /* major*100 + minor */
 
 /* KV element types (kv_dtype). Queries, new K/V rows and outputs are bf16, except with HKB_KV_F16. */
 #define HKB_KV_BF16 0
@@ -288,6 +288,29 @@ int hkb_decode_step_record(float* rec_out, float* rec_lse,
                            int block_size, float scale, int kv_dtype,
                            const float* k_scale, const float* v_scale,
                            int num_splits, float* part_out, float* part_lse, void* stream);
+
+/*
+ * hkb_paged_decode over caches in vLLM's older "x-split" layout, read in place
+ * (no copy, no re-layout): K is (blocks, kv_heads, head_dim / 8, block_size, 8)
+ * and V is (blocks, kv_heads, head_dim, block_size) -- V^T -- of 16-bit elements,
+ * everything inside a block contiguous; `*_stride_block` is elements between
+ * blocks. head_dim 128, bf16 or fp16 caches, num_splits >= 2 (the balanced tile
+ * stream), at most HKB_STREAM_MAX_SEQS sequences; anything else is
+ * HKB_ERR_UNSUPPORTED / HKB_ERR_SPLITS / HKB_ERR_SIZE before a launch. Partials
+ * as in hkb_paged_decode; hkb_merge folds them.
+ * Replaces: python/hk/ops/paged_prefill.py:768-772 (`rocm_views`, the strided
+ * views the reference's kernels read that layout through) and the decode over
+ * them, `_rocm_decode` (python/hk/integration/vllm_prefill.py:1332-1356).
+ */
+int hkb_paged_decode_xsplit(void* out, int64_t out_stride_tok, int64_t out_stride_head,
+                            const void* q, int64_t q_stride_tok, int64_t q_stride_head,
+                            const void* k_cache, int64_t k_stride_block,
+                            const void* v_cache, int64_t v_stride_block, int64_t num_blocks,
+                            const int32_t* block_table, int64_t table_stride, int max_pages,
+                            const int32_t* seq_lens, const int32_t* q_start,
+                            int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                            int block_size, float scale, int kv_dtype,
+                            int num_splits, float* part_out, float* part_lse, void* stream);
 
 /*
  * The exchange step of a KV axis cut across the GPUs of one box, over peer memory instead of a

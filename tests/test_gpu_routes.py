@@ -74,6 +74,35 @@ def test_unified_attention_stand_in_as_vllm_calls_it(route, order, group):
     assert route.PATCH.stats == {"prefill": 0, "decode": 1, "fallback": 0}
 
 
+def _stub_chunked_raises(query, key, value, output, kv_cache_dtype, key_cache, value_cache, block_table,
+                         query_start_loc, seq_lens, max_seq_len, max_query_len, k_scale, v_scale, alibi_slopes=None,
+                         sliding_window=None, sm_scale=None, output_scale=None, sinks=None, is_block_table_ptr=False,
+                         causal=True):
+    raise AssertionError("the call fell back to the engine's kernel")
+
+
+@pytest.mark.parametrize("page", [16, 32])
+def test_chunked_prefill_paged_decode_stand_in_on_x_split_caches(route, page, monkeypatch):
+    """ROCM_ATTN's own cache pair, read in place (python/hk/integration/vllm_prefill.py:1332-1356)."""
+    from hk_dsl_b200.ops import paged
+
+    monkeypatch.setattr(route, "_ORIG_R", _stub_chunked_raises)
+    monkeypatch.setattr(route, "_R_SIG", inspect.signature(_stub_chunked_raises))
+    monkeypatch.setattr(route, "ROCM_DECODE", True)
+    lens = [1, 33, 1000, 2063]
+    q, k, v, table, lens_t = _case(lens, group=4, page=page, seed=page)
+    want = orc.paged_decode_ref(q, k.transpose(1, 2), v.transpose(1, 2), table, lens_t)
+    k5, v4 = paged.x_split_caches(k.transpose(1, 2).cuda(), v.transpose(1, 2).cuda())
+    assert k5.shape == (k.shape[0], 2, 16, page, 8) and v4.shape == (k.shape[0], 2, 128, page)
+    out = torch.full(q.shape, 7.0, device="cuda", dtype=torch.bfloat16)
+    n = len(lens)
+    route.chunked_prefill_paged_decode(q.cuda(), None, None, out, "auto", k5, v4, table.cuda(),
+                                       torch.arange(n + 1, dtype=torch.int32, device="cuda"), lens_t.cuda(),
+                                       max(lens), 1, None, None, sm_scale=128 ** -0.5)
+    orc.check(out, want)
+    assert route.PATCH.stats == {"prefill": 0, "decode": 1, "fallback": 0}
+
+
 def test_the_stand_in_under_graph_capture_and_padding(route):
     """Captured once, replayed with other lengths; requests without a query write nothing."""
     lens = [500, 33, 0, 0]

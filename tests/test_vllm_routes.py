@@ -171,7 +171,18 @@ def test_chunked_prefill_paged_decode_route(monkeypatch):
     monkeypatch.setattr(vllm_prefill, "ROCM_DECODE", True)
     assert vllm_prefill.rd_why_not(a) == ""
     assert "sliding_window set" in vllm_prefill.rd_why_not(dict(a, sliding_window=128))
-    assert "5-D" in vllm_prefill.rd_why_not(dict(a, key_cache=torch.zeros(12, 2, 16, 16, 8, dtype=torch.bfloat16)))
+    # ROCM_ATTN's own pair -- K (blocks, kv_heads, head_dim / 8, page, 8), V (blocks, kv_heads, head_dim, page) -- is
+    # read in place; anything that only looks like it is named
+    k5, v4 = torch.zeros(12, 2, 16, 16, 8, dtype=torch.bfloat16), torch.zeros(12, 2, 128, 16, dtype=torch.bfloat16)
+    assert vllm_prefill.rd_why_not(dict(a, key_cache=k5, value_cache=v4)) == ""
+    assert "beside K" in vllm_prefill.rd_why_not(dict(a, key_cache=k5))
+    assert "x = 8" in vllm_prefill.rd_why_not(dict(a, key_cache=torch.zeros(12, 2, 8, 16, 16, dtype=torch.bfloat16),
+                                                   value_cache=v4))
+    assert "not contiguous" in vllm_prefill.rd_why_not(dict(a, key_cache=k5.transpose(2, 3).contiguous().transpose(2, 3),
+                                                            value_cache=v4))
+    assert "16-bit" in vllm_prefill.rd_why_not(dict(a, key_cache=k5.to(torch.float8_e4m3fn),
+                                                    value_cache=v4.to(torch.float8_e4m3fn)))
+    assert "under" in vllm_prefill.rd_why_not(dict(a, key_cache=k5.half(), value_cache=v4.half()))
     assert "not decode-only" in vllm_prefill.rd_why_not(dict(a, max_query_len=5))
 
 
