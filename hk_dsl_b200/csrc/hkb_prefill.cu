@@ -456,7 +456,11 @@ static int launch_prefill_tc(const tc::Args& a, const CUtensorMap& kmap, const C
     if (e == cudaSuccess) armed[dev] = true;
   }
   if (e == cudaSuccess) {
-    dim3 grid(num_work, a.num_kv_heads * (a.group / GP));
+    // a persistent grid: one CTA an SM at most, each walks its share of the (work item, head pass) pairs
+    const long long total = (long long)num_work * a.num_kv_heads * (a.group / GP);
+    int sms = hkb_sm_count(-1);
+    if (sms <= 0) sms = 148;
+    dim3 grid((unsigned)(total < sms ? total : sms));
     tc::prefill_tc_kernel<GP, F16, TRACE><<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(a, kmap, vmap, qmap);
     e = cudaGetLastError();
   }
@@ -556,7 +560,7 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
     t.k_stride_block = a.k_stride_block; t.k_stride_token = a.k_stride_token; t.k_stride_head = a.k_stride_head;
     t.v_stride_block = a.v_stride_block; t.v_stride_token = a.v_stride_token; t.v_stride_head = a.v_stride_head;
     t.num_blocks = a.num_blocks; t.block_table = a.block_table; t.table_stride = a.table_stride; t.max_pages = a.max_pages;
-    t.seq_lens = a.seq_lens; t.q_start = a.q_start; t.work = a.work;
+    t.seq_lens = a.seq_lens; t.q_start = a.q_start; t.work = a.work; t.num_work = num_work;
     t.num_q_heads = a.num_q_heads; t.num_kv_heads = a.num_kv_heads; t.group = a.group; t.tiles_per_page = a.tiles_per_page;
     t.scale = a.scale;
     t.trace = g_trace_for_next_call;

@@ -60,11 +60,12 @@ __host__ __device__ constexpr int s_col(int tile) { return 256 + tile * 128; }
 
 struct Bars {                                  // mbarriers, 8 bytes each
   uint64_t full[NSLOT], empty[NSLOT];
-  uint64_t s_full[2], p_full[2], o_done[2], q_full[2];
+  uint64_t s_full[2], p_full[2], o_done[2], q_full[2], q_empty[2];
   uint32_t tmem_base;
   int abort;
 };
-constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + 2 * Q_BYTES + NSLOT * SLOT_BYTES + 1024 /*Bars*/;
+constexpr int EPI_BYTES = SOFTMAX_WARPS * 4096;   // the epilogue's staging: 32 half rows of 128 bytes a softmax warp
+constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + 2 * Q_BYTES + NSLOT * SLOT_BYTES + EPI_BYTES + 1024 /*Bars*/;
 static_assert(sizeof(Bars) <= 1024, "barrier block");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory of one SM");
 
@@ -226,6 +227,7 @@ struct Args {
   const int* seq_lens;
   const int* q_start;
   const int* work;
+  int num_work;
   int num_q_heads, num_kv_heads, group, tiles_per_page;
   float scale;
   int tma;                  // K and V blocks by TMA (the two tensor maps are valid)
@@ -357,6 +359,14 @@ __device__ __forceinline__ float half_exp(float (&s)[64], bool masked, bool vali
   return a0 + a1;
 }
 
+// One work item as every role of the CTA sees it.
+struct Item {
+  int req, row0, q0, q_len, seq_len, ctx, kvh, hbase;
+  int nblk[2];     // key blocks each query tile attends to (tile 1 may be empty)
+  int kv_limit;    // keys the item reads
+  int n;           // blocks the CTA walks: max of the two
+};
+
 template <int GP, bool F16, bool TRACE = false>
 __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kmap,
                                                                 const __grid_constant__ CUtensorMap vmap,
@@ -371,37 +381,50 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
   uint8_t* gen = raw_smem + (base - smem_u32(raw_smem));
   const uint32_t q_smem = base;                              // two query tiles
   const uint32_t ring = base + 2 * Q_BYTES;
-  Bars* bars = reinterpret_cast<Bars*>(gen + 2 * Q_BYTES + NSLOT * SLOT_BYTES);
-  const uint32_t bars_u = base + 2 * Q_BYTES + NSLOT * SLOT_BYTES;
+  const uint32_t epi = ring + NSLOT * SLOT_BYTES;            // the epilogue's staging rows: 4 KB a softmax warp
+  Bars* bars = reinterpret_cast<Bars*>(gen + 2 * Q_BYTES + NSLOT * SLOT_BYTES + EPI_BYTES);
+  const uint32_t bars_u = epi + EPI_BYTES;
 #define HKB_BAR(field) (bars_u + (uint32_t)offsetof(Bars, field))
   volatile int* abort = &bars->abort;
 
-  // ---- the work item ----
+  // ---- the CTA's items: the grid is persistent (at most one CTA an SM); the (work item, head pass)
+  // pairs, work-major -- the list is sorted by keys, so consecutive pairs cost the same -- are dealt out
+  // in rounds of gridDim.x, every other round backwards, which evens the CTAs' sums out ----
   const int passes = a.group / GP;
-  const int kvh = blockIdx.y / passes;
-  const int hbase = kvh * a.group + (blockIdx.y % passes) * GP;
-  const int req = __ldg(a.work + 2 * blockIdx.x), row0 = __ldg(a.work + 2 * blockIdx.x + 1);
-  const int q0 = __ldg(a.q_start + req), q_len = __ldg(a.q_start + req + 1) - q0;
-  const int seq_len = __ldg(a.seq_lens + req);
-  const int ctx = seq_len - q_len;
-  if (q_len <= 0 || row0 >= q_len || ctx < 0) return;        // uniform: before any barrier or allocation
-  // keys tile t may attend to, and its blocks (tile 1 may be empty)
-  int nblk[2];
+  const int planes = a.num_kv_heads * passes;
+  const int total = a.num_work * planes;
+  const int G = (int)gridDim.x, cta = (int)blockIdx.x;
+  // 0: no more rounds; 1: nothing of this round for this CTA (or an item without rows); 2: `it` is set
+  auto item_at = [&](int round, Item& it) -> int {
+    if ((long long)round * G >= total) return 0;
+    const int idx = round * G + ((round & 1) ? G - 1 - cta : cta);
+    if (idx >= total) return 1;
+    const int w = idx / planes, plane = idx - w * planes;
+    it.kvh = plane / passes;
+    it.hbase = it.kvh * a.group + (plane % passes) * GP;
+    it.req = __ldg(a.work + 2 * w); it.row0 = __ldg(a.work + 2 * w + 1);
+    it.q0 = __ldg(a.q_start + it.req); it.q_len = __ldg(a.q_start + it.req + 1) - it.q0;
+    it.seq_len = __ldg(a.seq_lens + it.req);
+    it.ctx = it.seq_len - it.q_len;
+    if (it.q_len <= 0 || it.row0 >= it.q_len || it.ctx < 0) return 1;
 #pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int first = row0 + t * T;
-    const int lim = first < q_len ? min(seq_len, ctx + min(first + T, q_len)) : 0;
-    nblk[t] = (lim + KVB - 1) / KVB;
-  }
-  const int kv_limit = min(seq_len, ctx + min(row0 + 2 * T, q_len));
-  const int n = max(nblk[0], nblk[1]);
+    for (int t = 0; t < 2; ++t) {
+      const int first = it.row0 + t * T;
+      const int lim = first < it.q_len ? min(it.seq_len, it.ctx + min(first + T, it.q_len)) : 0;
+      it.nblk[t] = (lim + KVB - 1) / KVB;
+    }
+    it.kv_limit = min(it.seq_len, it.ctx + min(it.row0 + 2 * T, it.q_len));
+    it.n = max(it.nblk[0], it.nblk[1]);
+    return 2;
+  };
 
-  // ---- set-up: barriers and TMEM (the query tiles are staged by the softmax warps, below) ----
+  // ---- set-up: barriers and TMEM ----
   if (threadIdx.x == 0) {
     for (int i = 0; i < NSLOT; ++i) { mbar_init(HKB_BAR(full) + 8 * i, 1); mbar_init(HKB_BAR(empty) + 8 * i, 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(HKB_BAR(s_full) + 8 * i, 1); mbar_init(HKB_BAR(p_full) + 8 * i, ROWS);
       mbar_init(HKB_BAR(o_done) + 8 * i, 1); mbar_init(HKB_BAR(q_full) + 8 * i, a.tma ? 1 : ROWS);
+      mbar_init(HKB_BAR(q_empty) + 8 * i, 1);
     }
     bars->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -415,115 +438,139 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
 
+  // Barrier phases run on across items. Every role counts for itself, and all count alike: `blocks[t]`
+  // the key blocks of tile t so far (s_full, p_full, o_done complete once a block), `items[t]` the items
+  // in which tile t had rows (q_full, q_empty complete once an item), `kcnt` / `vcnt` the K / V blocks
+  // through the ring (block c of a kind sits in slot 2 (c % 2) + kind, on the slot's lap c / 2).
+  bool ok = true;
+  Item it;
   if (warp < SOFTMAX_WARPS) {
     // ================= softmax: thread = one query row of tile g =================
     const int g = warp >> 2, row = (warp & 3) * 32 + lane;
     // whether output rows can be written as 16-byte vectors (else as 4-byte words)
     const bool out16 = ((reinterpret_cast<uintptr_t>(a.out) | (uintptr_t)(a.out_stride_tok * 2) | (uintptr_t)(a.out_stride_head * 2)) & 15) == 0;
-    // This tile's query rows first (the producers are already fetching K and V): row r is head r / T,
-    // token r % T of the tile; rows past the request are zeros. 128 threads x 16 chunks a row group.
     if (TRACE) tr[7] = (unsigned long long)(now() - t_begin);   // set-up: barriers, TMEM, the CTA-wide barrier
-    Lap<TRACE> lap_q;
-    if (nblk[g] > 0 && !a.tma) {
-      uint4 qv[16];
-#pragma unroll
-      for (int it = 0; it < 16; ++it) {                      // all sixteen loads in flight, then the stores
-        const int x = it * ROWS + (warp & 3) * 32 + lane, r = x >> 4, c = x & 15;
-        const int tk = min(row0 + g * T + r % T, q_len - 1);  // rows past the request: any finite row will do, they are masked
-        qv[it] = ldg_stream16(a.q + (int64_t)(q0 + tk) * a.q_stride_tok + (int64_t)(hbase + r / T) * a.q_stride_head + c * 8);
-      }
-#pragma unroll
-      for (int it = 0; it < 16; ++it) {
-        const int x = it * ROWS + (warp & 3) * 32 + lane, r = x >> 4, c = x & 15;
-        const uint32_t dst = q_smem + g * Q_BYTES + (c >> 3) * HALF_BYTES_Q + r * 128 + (((c & 7) ^ (r & 7)) << 4);
-        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(dst), "r"(qv[it].x), "r"(qv[it].y), "r"(qv[it].z), "r"(qv[it].w) : "memory");
-      }
-      fence_async_smem();
-      mbar_arrive(HKB_BAR(q_full) + 8 * g);
-    }
-    lap_q(tr[6]);
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t s_addr = lane_addr + s_col(g);
-    const int tok = row0 + g * T + row % T;
-    const bool valid = tok < q_len;
-    const int pos = ctx + tok;                              // the last key this row sees
     const float qs = a.scale * LOG2E;
-    float m = -INFINITY, l = 0.f;
-    const int nb = nblk[g];
-    bool ok = true;
-    for (int j = 0; j < nb && ok; ++j) {
-      Lap<TRACE> lap;
-      ok = warp_wait(HKB_BAR(s_full) + 8 * g, j & 1, abort, 1);
-      if (!ok) break;
-      lap(tr[0]);
-      tc_fence_after();
-      const int kv0 = j * KVB;
-      const bool masked = !valid || kv0 + KVB - 1 > pos;     // the diagonal block, or a row past the request
-      float s[64];
-      // pass 1: the row maximum over both halves
-      tmem_ld64(s_addr, s);
-      float mx = half_max<F16>(s, masked, valid, kv0, pos);
-      tmem_ld64(s_addr + 64, s);
-      mx = fmaxf(mx, half_max<F16>(s, masked, valid, kv0 + 64, pos)) * qs;     // qs > 0
-      lap(tr[1]);
-      // lazy reference: it moves only when a block's maximum exceeds it by 2^8 (P <= 256 fits 16 bits)
-      const bool need = mx > m + 8.f;
-      const bool any_need = __any_sync(0xffffffffu, need);
-      float alpha = 1.f;
-      if (need) {
-        alpha = fast_exp2(m - mx);                           // m = -inf the first time: 0
-        m = mx;
-      }
-      const float off = (m == -INFINITY) ? 0.f : -m;
-      // pass 2: the second half is still in registers; P of keys 64..127 goes to columns 32..63, which
-      // held scores of the first half -- read again below before anything is written there
-      uint32_t p_hi[32], p_lo[32];
-      float sum = half_exp<F16>(s, false, valid, kv0 + 64, pos, qs, off, p_hi);
-      tmem_ld64(s_addr, s);
-      sum += half_exp<F16>(s, masked, valid, kv0, pos, qs, off, p_lo);
-      l = l * alpha + sum;
-      if (TRACE) asm volatile("" ::"r"(p_lo[0]), "r"(p_hi[31]), "f"(l));   // the math is done before the lap is taken
-      lap(tr[2]);
-      if (j > 0) {
-        // the tile's previous product has landed: O may be touched, and stays untouched until P arrives
-        ok = warp_wait(HKB_BAR(o_done) + 8 * g, (j - 1) & 1, abort, 2);
-        if (!ok) break;
-        tc_fence_after();
-        if (any_need) {
-#pragma unroll 1
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            float o[32];
-            uint32_t w[32];
-            tmem_ld32(lane_addr + o_col(g) + c0, o);
+    int blocks = 0, items = 0;
+    Item nxt;
+    int got_nxt = item_at(0, nxt);
+    for (int round = 1; ok && got_nxt; ++round) {
+      // the item after this one is looked up now: its three dependent loads are long done when it is needed
+      it = nxt;
+      const int got = got_nxt;
+      got_nxt = item_at(round, nxt);
+      if (got == 1 || it.nblk[g] == 0) continue;
+      const int row0 = it.row0, q_len = it.q_len, q0 = it.q0, hbase = it.hbase;
+      Lap<TRACE> lap_q;
+      if (!a.tma) {
+        // No tensor map for the queries: this tile's warps stage its rows themselves -- row r is head
+        // r / T, token r % T of the tile -- once the products of the item before have read the old ones.
+        if (items > 0) {
+          ok = warp_wait(HKB_BAR(q_empty) + 8 * g, (items - 1) & 1, abort, 9);
+          if (!ok) break;
+        }
+        uint4 qv[16];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(o[i] * alpha);
-            tmem_st32(lane_addr + o_col(g) + c0, w);
+        for (int x16 = 0; x16 < 16; ++x16) {                      // all sixteen loads in flight, then the stores
+          const int x = x16 * ROWS + (warp & 3) * 32 + lane, r = x >> 4, c = x & 15;
+          const int tk = min(row0 + g * T + r % T, q_len - 1);  // rows past the request: any finite row will do, they are masked
+          qv[x16] = ldg_stream16(a.q + (int64_t)(q0 + tk) * a.q_stride_tok + (int64_t)(hbase + r / T) * a.q_stride_head + c * 8);
+        }
+#pragma unroll
+        for (int x16 = 0; x16 < 16; ++x16) {
+          const int x = x16 * ROWS + (warp & 3) * 32 + lane, r = x >> 4, c = x & 15;
+          const uint32_t dst = q_smem + g * Q_BYTES + (c >> 3) * HALF_BYTES_Q + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(dst), "r"(qv[x16].x), "r"(qv[x16].y), "r"(qv[x16].z), "r"(qv[x16].w) : "memory");
+        }
+        fence_async_smem();
+        mbar_arrive(HKB_BAR(q_full) + 8 * g);
+      }
+      ++items;
+      lap_q(tr[6]);
+      const int tok = row0 + g * T + row % T;
+      const bool valid = tok < q_len;
+      const int pos = it.ctx + tok;                           // the last key this row sees
+      float m = -INFINITY, l = 0.f;
+      const int nb = it.nblk[g];
+      for (int j = 0; j < nb && ok; ++j) {
+        Lap<TRACE> lap;
+        ok = warp_wait(HKB_BAR(s_full) + 8 * g, (blocks + j) & 1, abort, 1);
+        if (!ok) break;
+        lap(tr[0]);
+        tc_fence_after();
+        const int kv0 = j * KVB;
+        const bool masked = !valid || kv0 + KVB - 1 > pos;     // the diagonal block, or a row past the request
+        float s[64];
+        // pass 1: the row maximum over both halves
+        tmem_ld64(s_addr, s);
+        float mx = half_max<F16>(s, masked, valid, kv0, pos);
+        tmem_ld64(s_addr + 64, s);
+        mx = fmaxf(mx, half_max<F16>(s, masked, valid, kv0 + 64, pos)) * qs;     // qs > 0
+        lap(tr[1]);
+        // lazy reference: it moves only when a block's maximum exceeds it by 2^8 (P <= 256 fits 16 bits)
+        const bool need = mx > m + 8.f;
+        const bool any_need = __any_sync(0xffffffffu, need);
+        float alpha = 1.f;
+        if (need) {
+          alpha = fast_exp2(m - mx);                           // m = -inf the first time: 0
+          m = mx;
+        }
+        const float off = (m == -INFINITY) ? 0.f : -m;
+        // pass 2: the second half is still in registers; P of keys 64..127 goes to columns 32..63, which
+        // held scores of the first half -- read again below before anything is written there
+        uint32_t p_hi[32], p_lo[32];
+        float sum = half_exp<F16>(s, false, valid, kv0 + 64, pos, qs, off, p_hi);
+        tmem_ld64(s_addr, s);
+        sum += half_exp<F16>(s, masked, valid, kv0, pos, qs, off, p_lo);
+        l = l * alpha + sum;
+        if (TRACE) asm volatile("" ::"r"(p_lo[0]), "r"(p_hi[31]), "f"(l));   // the math is done before the lap is taken
+        lap(tr[2]);
+        if (j > 0) {
+          // the tile's previous product has landed: O may be touched, and stays untouched until P arrives
+          ok = warp_wait(HKB_BAR(o_done) + 8 * g, (blocks + j - 1) & 1, abort, 2);
+          if (!ok) break;
+          tc_fence_after();
+          if (any_need) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+              float o[32];
+              uint32_t w[32];
+              tmem_ld32(lane_addr + o_col(g) + c0, o);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(o[i] * alpha);
+              tmem_st32(lane_addr + o_col(g) + c0, w);
+            }
           }
         }
+        lap(tr[3]);
+        tmem_st32(s_addr, p_lo);                                // P over the first 64 columns of the scores
+        tmem_st32(s_addr + 32, p_hi);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(HKB_BAR(p_full) + 8 * g);
+        lap(tr[4]);
       }
-      lap(tr[3]);
-      tmem_st32(s_addr, p_lo);                                // P over the first 64 columns of the scores
-      tmem_st32(s_addr + 32, p_hi);
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(HKB_BAR(p_full) + 8 * g);
-      lap(tr[4]);
-    }
-    Lap<TRACE> lap_end;
-    if (ok && nb > 0) {
-      ok = warp_wait(HKB_BAR(o_done) + 8 * g, (nb - 1) & 1, abort, 3);
-      if (ok) {
-        tc_fence_after();
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        // The tile's query rows in shared memory are dead (every product that read them has landed):
-        // each thread parks its output row there (256 bytes, 16-byte chunks XOR-ed by the row so that the
-        // 32 rows of a warp do not collide on banks), then the warp -- which owns exactly these 32
-        // rows -- writes them out two whole rows an instruction.
-        const uint32_t stage = q_smem + g * Q_BYTES + (warp & 3) * 32 * 256;
+      if (!ok) break;
+      Lap<TRACE> lap_end;
+      ok = warp_wait(HKB_BAR(o_done) + 8 * g, (blocks + nb - 1) & 1, abort, 3);
+      if (!ok) break;
+      blocks += nb;
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      // Each thread parks half of its output row (64 dims, 128 bytes; 16-byte chunks XOR-ed by the row so
+      // that the 32 rows of a warp do not collide on banks) in the warp's staging rows, then the warp --
+      // which owns exactly these 32 rows -- writes them out four half rows an instruction; then the
+      // other half. The accumulator is free for the next item as soon as the second half has been
+      // read: the first P of that item is handed over after this, by these same threads.
+      const uint32_t stage = epi + (uint32_t)warp * 4096u;
 #pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll
+        for (int c32 = 0; c32 < 2; ++c32) {
           float o[32];
-          tmem_ld32(lane_addr + o_col(g) + c0, o);
+          tmem_ld32(lane_addr + o_col(g) + half * 64 + c32 * 32, o);
           uint32_t w[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -532,20 +579,21 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
           }
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
-            const int chunk = (c0 >> 3) + q4;                 // 16-byte chunk of the row
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)),
+            const int chunk = c32 * 4 + q4;                     // 16-byte chunk of the half row
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(stage + lane * 128 + ((chunk ^ (lane & 7)) << 4)),
                          "r"(w[4 * q4]), "r"(w[4 * q4 + 1]), "r"(w[4 * q4 + 2]), "r"(w[4 * q4 + 3]) : "memory");
           }
         }
         __syncwarp();
 #pragma unroll 4
-        for (int it = 0; it < 16; ++it) {
-          const int rr = it * 2 + (lane >> 4), chunk = lane & 15;      // row of the warp, chunk of the row
+        for (int x8 = 0; x8 < 8; ++x8) {
+          const int rr = x8 * 4 + (lane >> 3), chunk = lane & 7;        // row of the warp, chunk of the half row
           const int r_tile = (warp & 3) * 32 + rr;
           const int tk = row0 + g * T + r_tile % T;
-          const uint4 v = lds128(stage + rr * 256 + ((chunk ^ (rr & 15)) << 4));
+          const uint4 v = lds128(stage + rr * 128 + ((chunk ^ (rr & 7)) << 4));
           if (tk < q_len) {
-            __nv_bfloat16* dst = a.out + (int64_t)(q0 + tk) * a.out_stride_tok + (int64_t)(hbase + r_tile / T) * a.out_stride_head + chunk * 8;
+            __nv_bfloat16* dst = a.out + (int64_t)(q0 + tk) * a.out_stride_tok + (int64_t)(hbase + r_tile / T) * a.out_stride_head +
+                                 half * 64 + chunk * 8;
             if (out16) *reinterpret_cast<uint4*>(dst) = v;
             else {
               uint32_t* d32 = reinterpret_cast<uint32_t*>(dst);
@@ -553,22 +601,22 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
             }
           }
         }
+        __syncwarp();
       }
+      tc_fence_before();
+      lap_end(tr[5]);
     }
-    lap_end(tr[5]);
     if (TRACE && row == 0)
-      for (int i = 0; i < 8; ++i) a.trace[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 32 + 8 * g + i] = tr[i];
+      for (int i = 0; i < 8; ++i) a.trace[(size_t)cta * 32 + 8 * g + i] = tr[i];
   } else if (warp == MMA_WARP) {
     // ================= MMA issue: one thread; the whole warp keeps step at the barriers =================
     constexpr uint32_t IDESC_S = instr_desc(F16, false, KVB), IDESC_PV = instr_desc(F16, true, D);
-    bool ok = true;
-    Lap<TRACE> lap;
-    for (int t = 0; t < 2 && ok; ++t)
-      if (nblk[t] > 0) ok = warp_wait(HKB_BAR(q_full) + 8 * t, 0, abort, 8);   // the tile's query rows are in place
-    lap(tr[0]);
-    // S_t(j) = Q_t K_j^T: eight products (two 64-dim halves x four 16-dim steps) into the tile's score columns
-    auto scores = [&](int t, int j) {
-      const uint32_t kaddr = ring + ((2 * j) % NSLOT) * SLOT_BYTES;
+    int blocks[2] = {0, 0}, items[2] = {0, 0}, kcnt = 0, vcnt = 0;
+    auto slot_of = [](int kind, int c) { return 2 * (c & 1) + kind; };
+    // S_t = Q_t K^T for the K block in ring slot `slot`: eight products (two 64-dim halves x four 16-dim
+    // steps) into the tile's score columns; the tile's query rows are free after the item's last one
+    auto scores = [&](int t, int slot, bool last) {
+      const uint32_t kaddr = ring + slot * SLOT_BYTES;
 #pragma unroll
       for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -576,144 +624,179 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
           umma_ss(tmem + s_col(t), smem_desc(q_smem + t * Q_BYTES + h * HALF_BYTES_Q + ks * 32, 16),
                   smem_desc(kaddr + h * HALF_BYTES_KV + ks * 32, 16), IDESC_S, (h | ks) ? 1u : 0u);
       tc_commit(HKB_BAR(s_full) + 8 * t);
+      if (last) tc_commit(HKB_BAR(q_empty) + 8 * t);
     };
-    auto wait_block = [&](int use, int code) {     // block `use` of the ring (2 j: K_j, 2 j + 1: V_j) has landed
-      ok = warp_wait(HKB_BAR(full) + 8 * (use % NSLOT), (use / NSLOT) & 1, abort, code);
+    auto wait_block = [&](int kind, int c, int code) {     // block c of K (kind 0) or V (kind 1) has landed
+      ok = warp_wait(HKB_BAR(full) + 8 * slot_of(kind, c), (c >> 1) & 1, abort, code);
       tc_fence_after();
     };
-    if (ok) wait_block(0, 4);
-    lap(tr[1]);
-    if (ok && lane == 0) {
-      for (int t = 0; t < 2; ++t)
-        if (nblk[t] > 0) scores(t, 0);
-      // K_0's slot is handed back at once: the producer publishes K_1 only after it has issued K_2,
-      // which goes into this slot
-      tc_commit(HKB_BAR(empty) + 8 * 0);
-    }
-    __syncwarp();
-    lap(tr[2]);
-    for (int j = 0; j < n && ok; ++j) {
-      wait_block(2 * j + 1, 5);                    // V_j
+    Item nxt;
+    int got_nxt = item_at(0, nxt);
+    for (int round = 1; ok && got_nxt; ++round) {
+      it = nxt;
+      const int got = got_nxt;
+      got_nxt = item_at(round, nxt);
+      if (got == 1) continue;
+      const int n = it.n;
+      Lap<TRACE> lap;
+      for (int t = 0; t < 2 && ok; ++t)
+        if (it.nblk[t] > 0) ok = warp_wait(HKB_BAR(q_full) + 8 * t, items[t] & 1, abort, 8);   // the tile's query rows are in place
       if (!ok) break;
-      lap(tr[3]);
-      if (j + 1 < n) wait_block(2 * j + 2, 4);     // K_{j+1}
+      lap(tr[0]);
+      wait_block(0, kcnt, 4);
       if (!ok) break;
       lap(tr[1]);
-      const uint32_t vaddr = ring + ((2 * j + 1) % NSLOT) * SLOT_BYTES;
-      for (int t = 0; t < 2 && ok; ++t) {
-        if (j >= nblk[t]) continue;
-        ok = warp_wait(HKB_BAR(p_full) + 8 * t, j & 1, abort, 6);
-        if (!ok) break;
-        lap(tr[t ? 6 : 4]);
-        tc_fence_after();
-        if (lane == 0) {
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks)           // 16 tokens a step: 8 TMEM columns of P, 16 rows of V
-            umma_ts(tmem + o_col(t), tmem + s_col(t) + ks * 8, smem_desc(vaddr + ks * 16 * 128, HALF_BYTES_KV), IDESC_PV,
-                    (j | ks) ? 1u : 0u);
-          tc_commit(HKB_BAR(o_done) + 8 * t);
-          // the tile's next scores go over the P just consumed: the tensor pipe runs products in the order issued
-          if (j + 1 < nblk[t]) scores(t, j + 1);
-        }
-        __syncwarp();
-        lap(tr[5]);
-      }
-      if (ok && lane == 0) {
-        tc_commit(HKB_BAR(empty) + 8 * ((2 * j + 1) % NSLOT));                 // V_j
-        if (j + 1 < n) tc_commit(HKB_BAR(empty) + 8 * ((2 * j + 2) % NSLOT));  // K_{j+1}
+      if (lane == 0) {
+        for (int t = 0; t < 2; ++t)
+          if (it.nblk[t] > 0) scores(t, slot_of(0, kcnt), it.nblk[t] == 1);
+        // the first K block's slot is handed back at once
+        tc_commit(HKB_BAR(empty) + 8 * slot_of(0, kcnt));
       }
       __syncwarp();
+      lap(tr[2]);
+      for (int j = 0; j < n && ok; ++j) {
+        wait_block(1, vcnt + j, 5);                    // V_j
+        if (!ok) break;
+        lap(tr[3]);
+        if (j + 1 < n) wait_block(0, kcnt + j + 1, 4);     // K_{j+1}
+        if (!ok) break;
+        lap(tr[1]);
+        const uint32_t vaddr = ring + slot_of(1, vcnt + j) * SLOT_BYTES;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j >= it.nblk[t]) continue;
+          // P of the block; for an item's first block this also says the tile's warps have read the
+          // accumulator of the item before out of TMEM (they arrive here after their epilogue)
+          ok = warp_wait(HKB_BAR(p_full) + 8 * t, (blocks[t] + j) & 1, abort, 6);
+          if (!ok) break;
+          lap(tr[t ? 6 : 4]);
+          tc_fence_after();
+          if (lane == 0) {
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)           // 16 tokens a step: 8 TMEM columns of P, 16 rows of V
+              umma_ts(tmem + o_col(t), tmem + s_col(t) + ks * 8, smem_desc(vaddr + ks * 16 * 128, HALF_BYTES_KV), IDESC_PV,
+                      (j | ks) ? 1u : 0u);
+            tc_commit(HKB_BAR(o_done) + 8 * t);
+            // the tile's next scores go over the P just consumed: the tensor pipe runs products in the order issued
+            if (j + 1 < it.nblk[t]) scores(t, slot_of(0, kcnt + j + 1), j + 2 == it.nblk[t]);
+          }
+          __syncwarp();
+          lap(tr[5]);
+        }
+        if (ok && lane == 0) {
+          tc_commit(HKB_BAR(empty) + 8 * slot_of(1, vcnt + j));                      // V_j
+          if (j + 1 < n) tc_commit(HKB_BAR(empty) + 8 * slot_of(0, kcnt + j + 1));   // K_{j+1}
+        }
+        __syncwarp();
+      }
+      kcnt += n; vcnt += n;
+      for (int t = 0; t < 2; ++t)
+        if (it.nblk[t] > 0) { blocks[t] += it.nblk[t]; ++items[t]; }
     }
     if (TRACE && lane == 0)
-      for (int i = 0; i < 7; ++i) a.trace[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 32 + 16 + i] = tr[i];
+      for (int i = 0; i < 7; ++i) a.trace[(size_t)cta * 32 + 16 + i] = tr[i];
   } else {
     // ================= producers: warp K_WARP brings the K blocks, warp V_WARP the V blocks =================
     const int which = warp - K_WARP;   // 0: K, 1: V
-    const uint8_t* src = (which ? a.v + (int64_t)kvh * a.v_stride_head : a.k + (int64_t)kvh * a.k_stride_head);
     const int64_t sb = which ? a.v_stride_block : a.k_stride_block, st = which ? a.v_stride_token : a.k_stride_token;
     const void* map = which ? static_cast<const void*>(&vmap) : static_cast<const void*>(&kmap);
     const int p_tok = which ? a.v_pos[0] : a.k_pos[0], p_head = which ? a.v_pos[1] : a.k_pos[1],
               p_blk = which ? a.v_pos[2] : a.k_pos[2];
-    const int* table_row = a.block_table + (int64_t)req * a.table_stride;
-    bool ok = true;
-    if (a.tma && which == 1) {
-      // the V warp has nothing to do until the first scores exist: it brings the query tiles, one copy a
-      // (tile, head, 64-dim half): T token rows of 128 bytes, landing where row h * T + token belongs
-      for (int t = 0; t < 2; ++t) {
-        if (nblk[t] == 0) continue;
-        if (lane == 0) mbar_arrive_expect_tx(HKB_BAR(q_full) + 8 * t, Q_BYTES);
-        __syncwarp();
-        for (int x = lane; x < 2 * GP; x += 32) {
-          const int h = x >> 1, half = x & 1;
-          int c[3];
-          c[0] = half * 64;
-          c[a.q_pos[0]] = q0 + row0 + t * T;
-          c[a.q_pos[1]] = hbase + h;
-          tma_load_3d(q_smem + t * Q_BYTES + half * HALF_BYTES_Q + h * T * 128, &qmap, HKB_BAR(q_full) + 8 * t, c[0], c[1], c[2]);
+    int cnt = 0, items[2] = {0, 0};
+    Item nxt;
+    int got_nxt = item_at(0, nxt);
+    for (int round = 1; ok && got_nxt; ++round) {
+      it = nxt;
+      const int got = got_nxt;
+      got_nxt = item_at(round, nxt);
+      if (got == 1) continue;
+      const int n = it.n, kvh = it.kvh, kv_limit = it.kv_limit;
+      const uint8_t* src = (which ? a.v + (int64_t)kvh * a.v_stride_head : a.k + (int64_t)kvh * a.k_stride_head);
+      const int* table_row = a.block_table + (int64_t)it.req * a.table_stride;
+      // page ids of a block's eight 16-token tiles, fetched one block ahead of their use
+      auto page_ids = [&](int kv0, int& id, int& sub) {
+        id = 0; sub = 0;
+        if (lane < 8 && kv0 < kv_limit) {
+          const int tile = kv0 / TILE_TOKENS + lane;
+          const int page = min(tile / a.tiles_per_page, a.max_pages - 1);
+          id = min(max(__ldg(table_row + page), 0), a.num_blocks - 1);
+          sub = tile % a.tiles_per_page;
         }
-      }
-    }
-    // page ids of a block's eight 16-token tiles, fetched one block ahead of their use
-    auto page_ids = [&](int kv0, int& id, int& sub) {
-      id = 0; sub = 0;
-      if (lane < 8 && kv0 < kv_limit) {
-        const int tile = kv0 / TILE_TOKENS + lane;
-        const int page = min(tile / a.tiles_per_page, a.max_pages - 1);
-        id = min(max(__ldg(table_row + page), 0), a.num_blocks - 1);
-        sub = tile % a.tiles_per_page;
-      }
-    };
-    int next_id, next_sub;
-    page_ids(0, next_id, next_sub);
-    for (int j = 0; j < n && ok; ++j) {
-      const int use = 2 * j + which, slot = use % NSLOT, lap = use / NSLOT;
-      const uint32_t slot_addr = ring + slot * SLOT_BYTES, bar = HKB_BAR(full) + 8 * slot;
-      int id = next_id, sub = next_sub;
-      page_ids((j + 1) * KVB, next_id, next_sub);
-      const int kv0 = j * KVB;
-      Lap<TRACE> tick;
-      if (lap > 0) ok = warp_wait(HKB_BAR(empty) + 8 * slot, (lap - 1) & 1, abort, 7);
-      if (!ok) break;
-      tick(tr[0]);
-      if (a.tma && kv0 + KVB <= kv_limit) {
-        // all 128 rows are keys: 8 pages x 2 halves = 16 tile copies, one a lane
-        const int t = (lane >> 1) & 7;
-        id = __shfl_sync(0xffffffffu, id, t);
-        sub = __shfl_sync(0xffffffffu, sub, t);
-        if (lane == 0) mbar_arrive_expect_tx(bar, SLOT_BYTES);
-        __syncwarp();
-        if (lane < 16) {
-          int c[4];
-          c[0] = (lane & 1) * 64;
-          c[p_tok] = sub * TILE_TOKENS;
-          c[p_head] = kvh;
-          c[p_blk] = id;
-          tma_load_4d(slot_addr + (lane & 1) * HALF_BYTES_KV + t * TILE_TOKENS * 128, map, bar, c[0], c[1], c[2], c[3]);
+      };
+      int next_id, next_sub;
+      page_ids(0, next_id, next_sub);
+      if (a.tma && which == 1) {
+        // the V warp has nothing to do until the first scores exist: it brings the query tiles, one copy a
+        // (tile, head, 64-dim half): T token rows of 128 bytes, landing where row h * T + token belongs --
+        // once the products of the item before have read the old ones
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (it.nblk[t] == 0) continue;
+          if (items[t] > 0) {
+            ok = warp_wait(HKB_BAR(q_empty) + 8 * t, (items[t] - 1) & 1, abort, 9);
+            if (!ok) break;
+          }
+          ++items[t];
+          if (lane == 0) mbar_arrive_expect_tx(HKB_BAR(q_full) + 8 * t, Q_BYTES);
+          __syncwarp();
+          for (int x = lane; x < 2 * GP; x += 32) {
+            const int h = x >> 1, half = x & 1;
+            int c[3];
+            c[0] = half * 64;
+            c[a.q_pos[0]] = it.q0 + it.row0 + t * T;
+            c[a.q_pos[1]] = it.hbase + h;
+            tma_load_3d(q_smem + t * Q_BYTES + half * HALF_BYTES_Q + h * T * 128, &qmap, HKB_BAR(q_full) + 8 * t, c[0], c[1], c[2]);
+          }
         }
-        tick(tr[1]);
-      } else {
-        // the block with the last keys (rows past them are zero-filled), or no tensor map: cp.async
-        fill_half(a, slot_addr, src, sb, st, table_row, kv0, kv_limit, lane);
-        fill_half(a, slot_addr, src, sb, st, table_row, kv0 + 64, kv_limit, lane);
-        cp_async_commit();
-        tick(tr[1]);
-        cp_async_wait<0>();
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar);
+        if (!ok) break;
       }
-      tick(tr[2]);
+      for (int j = 0; j < n && ok; ++j, ++cnt) {
+        const int slot = 2 * (cnt & 1) + which, lap = cnt >> 1;
+        const uint32_t slot_addr = ring + slot * SLOT_BYTES, bar = HKB_BAR(full) + 8 * slot;
+        int id = next_id, sub = next_sub;
+        page_ids((j + 1) * KVB, next_id, next_sub);
+        const int kv0 = j * KVB;
+        Lap<TRACE> tick;
+        if (lap > 0) ok = warp_wait(HKB_BAR(empty) + 8 * slot, (lap - 1) & 1, abort, 7);
+        if (!ok) break;
+        tick(tr[0]);
+        if (a.tma && kv0 + KVB <= kv_limit) {
+          // all 128 rows are keys: 8 pages x 2 halves = 16 tile copies, one a lane
+          const int t = (lane >> 1) & 7;
+          id = __shfl_sync(0xffffffffu, id, t);
+          sub = __shfl_sync(0xffffffffu, sub, t);
+          if (lane == 0) mbar_arrive_expect_tx(bar, SLOT_BYTES);
+          __syncwarp();
+          if (lane < 16) {
+            int c[4];
+            c[0] = (lane & 1) * 64;
+            c[p_tok] = sub * TILE_TOKENS;
+            c[p_head] = kvh;
+            c[p_blk] = id;
+            tma_load_4d(slot_addr + (lane & 1) * HALF_BYTES_KV + t * TILE_TOKENS * 128, map, bar, c[0], c[1], c[2], c[3]);
+          }
+          tick(tr[1]);
+        } else {
+          // the block with the last keys (rows past them are zero-filled), or no tensor map: cp.async
+          fill_half(a, slot_addr, src, sb, st, table_row, kv0, kv_limit, lane);
+          fill_half(a, slot_addr, src, sb, st, table_row, kv0 + 64, kv_limit, lane);
+          cp_async_commit();
+          tick(tr[1]);
+          cp_async_wait<0>();
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar);
+        }
+        tick(tr[2]);
+      }
     }
     cp_async_wait<0>();
     if (TRACE && lane == 0)
-      for (int i = 0; i < 3; ++i) a.trace[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 32 + 24 + 4 * which + i] = tr[i];
+      for (int i = 0; i < 3; ++i) a.trace[(size_t)cta * 32 + 24 + 4 * which + i] = tr[i];
   }
 
   // ---- wind-down ----
   tc_fence_before();
   __syncthreads();
-  if (TRACE && threadIdx.x == 0)
-    a.trace[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 32 + 31] = (unsigned long long)(now() - t_begin);
+  if (TRACE && threadIdx.x == 0) a.trace[(size_t)cta * 32 + 31] = (unsigned long long)(now() - t_begin);
   if (warp == MMA_WARP) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
