@@ -272,12 +272,15 @@ def prefill_trace(case: str):
              8: "softmax tile 1: wait for scores", 9: "softmax tile 1: loads + maximum", 10: "softmax tile 1: exponentials",
              11: "softmax tile 1: wait for previous product (+ rescale)", 12: "softmax tile 1: store P, arrive", 13: "softmax tile 1: epilogue",
              16: "mma: wait for Q", 17: "mma: wait for K", 18: "mma: issue first q.K", 19: "mma: wait for V", 20: "mma: wait for P of tile 0",
-             21: "mma: issue p.V and the next q.K", 22: "mma: wait for P of tile 1", 24: "K producer: wait for a free slot", 25: "K producer: issue copies",
+             21: "mma: issue p.V", 22: "mma: wait for P of tile 1", 23: "mma: issue the next q.K", 24: "K producer: wait for a free slot", 25: "K producer: issue copies",
              26: "K producer: wait for copies", 28: "V producer: wait for a free slot", 29: "V producer: issue copies",
              30: "V producer: wait for copies", 31: "CTA total"}
     rows = {names[i]: round(float(t[:, i].sum()) / blocks, 1) for i in sorted(names)}
+    life = t[:, 31][t[:, 31] > 0]          # the persistent grid's CTAs: lifetimes in cycles
     print(json.dumps({"table": "tensor-memory prefill, cycles a 128-key block (both query tiles), by role and phase",
-                      "case": case or "1x0+8192", "ctas": n_cta, "key_blocks": blocks,
+                      "case": case or "1x0+8192", "work_items": n_cta, "ctas": int(life.numel()), "key_blocks": blocks,
+                      "cta_lifetime_cycles": {"min": float(life.min()), "mean": round(float(life.mean()), 0),
+                                              "max": float(life.max())},
                       "ideal_tensor_cycles_a_block": 2048, "rows": rows}, indent=1), flush=True)
     return 0
 
@@ -344,6 +347,104 @@ def attribution_table():
     del stream
     print(json.dumps({"table": "decode walk on c2 with one stage left out, us a launch (cold KV, graph of 20, median of 7)",
                       "kv_bytes": st.kv_bytes, "splits": splits, "rows": rows}, indent=1), flush=True)
+    return 0
+
+
+def shards_table():
+    """One rank's share of the headline config (c2) cut by kv head over 1, 2, 4 and 8 GPUs, run on
+    ONE GPU: the decode step (`decode_step`: the walk writes the new rows, then the merge) and its
+    one-launch form (the walk also folds: `arrivals`), as a graph of 20 steps rotating through caches
+    past L2, median of 7. `of_ideal` = (the world-1 step / world) / this step: what the fixed costs of
+    a step -- launches, the walk's ramp and tail, the merge -- leave of perfect strong scaling."""
+    import torch
+
+    from hk_dsl_b200 import workloads as W
+    from hk_dsl_b200.ops import paged
+    from hk_dsl_b200.runtime import lib as hkb
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    spec = W.CONFIGS["c2"]
+    rows, base = [], None
+    for world in (1, 2, 4, 8):
+        kv1 = spec.kv_bytes(W.seq_lens_of(spec, int(spec.name[1:]))) // world
+        layers = max(2, min(16, -(-(300 << 20) // kv1)))
+        st = W.build_step(spec, dev, world=world, rank=0, layers=layers)
+        n, hq, d = st.query.shape
+        splits = paged.plan_splits(n, st.kv_heads, st.block_table.shape[1], device=dev)
+        scratch = paged.split_scratch(n, hq, d, splits, dev)
+        row = {"world": world, "kv_heads_here": st.kv_heads, "kv_bytes": st.kv_bytes, "parts": splits, "caches_rotated": layers}
+        for name, arrivals in (("two_launches", None), ("one_launch", paged.step_arrivals(n, st.kv_heads, dev))):
+            def call(l):
+                paged.decode_step(st.out, st.query, st.key, st.value, st.k_caches[l], st.v_caches[l], st.slot_mapping,
+                                  st.block_table, st.seq_lens, st.scale, num_splits=splits, scratch=scratch,
+                                  arrivals=arrivals)
+            for l in range(layers):
+                call(l)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for i in range(20):
+                    call(i % layers)
+            g.replay()
+            torch.cuda.synchronize()
+            times = []
+            for _ in range(7):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                g.replay()
+                b.record()
+                torch.cuda.synchronize()
+                times.append(a.elapsed_time(b) * 1e3 / 20)
+            us = statistics.median(times)
+            row[name + "_us"] = round(us, 2)
+            row[name + "_kv_gbs"] = round(st.kv_bytes / us / 1e3, 1)
+            del g
+        # the walk alone (cache already written, no merge), and the walk with its math left out: the copies' floor
+        lib, cache = hkb.load(), (lambda c: hkb.CacheT(c.data_ptr(), c.stride(0), c.stride(1), c.stride(2), c.shape[0]))
+
+        def walk(l, mask):
+            if mask == 0:
+                paged.paged_attention_decode(st.out, st.query, st.k_caches[l], st.v_caches[l], st.block_table, st.seq_lens,
+                                             st.scale, num_splits=splits, scratch=scratch, merge=False)
+                return
+            rc = lib.hkb_paged_decode_ablate(st.out.data_ptr(), st.out.stride(0), st.out.stride(1), st.query.data_ptr(),
+                                             st.query.stride(0), st.query.stride(1), cache(st.k_caches[l]), cache(st.v_caches[l]),
+                                             st.block_table.data_ptr(), st.block_table.stride(0), st.block_table.shape[1],
+                                             st.seq_lens.data_ptr(), None, n, hq, st.kv_heads, d, spec.block_size, st.scale,
+                                             hkb.KV_BF16, None, None, splits, scratch[0].data_ptr(), scratch[1].data_ptr(), mask,
+                                             torch.cuda.current_stream().cuda_stream)
+            hkb.check("hkb_paged_decode_ablate", rc)
+
+        for name, mask in (("walk_only", 0), ("copies_only", 56)):
+            for l in range(layers):
+                walk(l, mask)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for i in range(20):
+                    walk(i % layers, mask)
+            g.replay()
+            torch.cuda.synchronize()
+            times = []
+            for _ in range(7):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                g.replay()
+                b.record()
+                torch.cuda.synchronize()
+                times.append(a.elapsed_time(b) * 1e3 / 20)
+            row[name + "_us"] = round(statistics.median(times), 2)
+            del g
+        if world == 1:
+            base = min(row["two_launches_us"], row["one_launch_us"])
+        row["of_ideal_two_launches"] = round(base / world / row["two_launches_us"], 3)
+        row["of_ideal_one_launch"] = round(base / world / row["one_launch_us"], 3)
+        rows.append(row)
+        del st, scratch
+        torch.cuda.empty_cache()
+    print(json.dumps({"table": "c2 cut by kv head: one rank's decode step on one GPU, us a step (cold KV, graph of 20, median of 7)",
+                      "rows": rows}, indent=1), flush=True)
     return 0
 
 
@@ -415,8 +516,11 @@ def main():
                                                "x-split (a small case for a profiler)")
     ap.add_argument("--prefill-trace", action="store_true", help="cycles by role and phase of the tensor-memory prefill kernel")
     ap.add_argument("--attrib", action="store_true", help="the decode walk with one stage left out: what each stage costs")
+    ap.add_argument("--shards", action="store_true", help="one rank's share of c2 over 1/2/4/8 GPUs, on one GPU: the step's fixed costs")
     ap.add_argument("--layouts", action="store_true", help="the decode over the usual and the x-split cache layout")
     args = ap.parse_args()
+    if args.shards:
+        return shards_table()
     if args.layouts:
         return layouts_table(args.case)
     if args.attrib:

@@ -5,9 +5,13 @@
 // attention of a request's new tokens over its paged cache, the grid a host-built work list of
 // (request, query tile) items (paged_prefill.py:879-968).
 //
-// One CTA an SM works on one item: 2 query tiles of 128 rows each -- a tile is T = 128 / GP
-// consecutive tokens of GP query heads of one kv head, so both tiles and all their heads share
-// every K/V block the CTA stages -- and walks the keys in blocks of 128:
+// The grid is persistent: one CTA an SM, each walking its share of the (work item, head pass) pairs
+// (dealt out in rounds, every other round backwards: the list is sorted by keys, so the CTAs' sums
+// come out even). Barrier phases simply run on from item to item, so the producers fetch the next
+// item's query rows and first K/V blocks, and the MMA warps issue its first scores, while the softmax
+// warps are still in the epilogue of the current one. An item is 2 query tiles of 128 rows each -- a
+// tile is T = 128 / GP consecutive tokens of GP query heads of one kv head, so both tiles and all
+// their heads share every K/V block the CTA stages -- and its keys are walked in blocks of 128:
 //
 //   producers (2 warps)  gather the block's eight 16-token pages through the block table into a ring
 //                        of 32 KB shared-memory slots (one warp the K blocks, one the V blocks,
@@ -16,7 +20,9 @@
 //                        copy, 128-byte swizzle, completion counted in bytes on the slot's
 //                        mbarrier), one lane a copy. The block that holds the last keys -- where
 //                        rows past the end must read as zeros -- and caches no tensor map describes
-//                        go through cp.async with the same swizzle, a proxy fence and an arrive;
+//                        go through cp.async with the same swizzle, a proxy fence and an arrive.
+//                        The V warp also brings the query tiles (TMA over a 3-D map of q), once
+//                        the products of the item before have read the old ones;
 //   MMA warp (1 thread)  S = Q K^T (8 tcgen05.mma of 128 x 128 x 16, Q and K from shared memory)
 //                        into the tile's 128 score columns of TMEM, and O += P V (8 tcgen05.mma of
 //                        128 x 128 x 16, P from TMEM, V from shared memory read MN-major) into its
@@ -28,7 +34,9 @@
 //                        (tcgen05.ld), masks the diagonal block, keeps the running maximum lazily
 //                        (the accumulator is rescaled only when a block's maximum exceeds the
 //                        reference by 2^8), writes P as packed 16-bit pairs over the scores it has
-//                        read (tcgen05.st) and arrives; no shuffles: a row is a TMEM lane.
+//                        read (tcgen05.st) and arrives; no shuffles: a row is a TMEM lane. After
+//                        an item's last block it normalises the accumulator and writes the rows
+//                        out through staging rows of its own in shared memory.
 //
 // All 512 TMEM columns are in use (two accumulators, two score tiles), which is why P lives where
 // the scores were. Every wait is bounded: a barrier that does not flip within about a second sets
@@ -240,8 +248,8 @@ struct Args {
 // adds the clocks between consecutive laps to a counter. Slots: softmax of tile g at 8 g + {0 wait
 // for the scores, 1 TMEM loads and maximum, 2 exponentials, 3 wait for the previous product (and the
 // rescale), 4 P store and arrive, 5 epilogue}; MMA warp 16 wait for Q, 17 wait for K, 18 issue of the
-// first score products, 19 wait for V, 20 / 22 wait for P of tile 0 / 1, 21 issue of the P V products
-// and the next block's scores;
+// first score products, 19 wait for V, 20 / 22 wait for P of tile 0 / 1, 21 issue of the P V products,
+// 23 issue of the next block's scores;
 // producers 24 + 4 w + {0 wait for a free slot, 1 issue of the copies, 2 wait for copies to land};
 // 31 the CTA's whole time.
 template <bool TRACE>
@@ -362,9 +370,11 @@ __device__ __forceinline__ float half_exp(float (&s)[64], bool masked, bool vali
 // One work item as every role of the CTA sees it.
 struct Item {
   int req, row0, q0, q_len, seq_len, ctx, kvh, hbase;
-  int nblk[2];     // key blocks each query tile attends to (tile 1 may be empty)
-  int kv_limit;    // keys the item reads
-  int n;           // blocks the CTA walks: max of the two
+  int nblk0, nblk1;   // key blocks each query tile attends to (tile 1 may be empty)
+  int kv_limit;       // keys the item reads
+  int n;              // blocks the CTA walks: max of the two
+  // by select, not by index: the item stays in registers
+  __device__ __forceinline__ int nblk(int t) const { return t ? nblk1 : nblk0; }
 };
 
 template <int GP, bool F16, bool TRACE = false>
@@ -407,14 +417,12 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
     it.seq_len = __ldg(a.seq_lens + it.req);
     it.ctx = it.seq_len - it.q_len;
     if (it.q_len <= 0 || it.row0 >= it.q_len || it.ctx < 0) return 1;
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      const int first = it.row0 + t * T;
-      const int lim = first < it.q_len ? min(it.seq_len, it.ctx + min(first + T, it.q_len)) : 0;
-      it.nblk[t] = (lim + KVB - 1) / KVB;
-    }
+    const int lim0 = min(it.seq_len, it.ctx + min(it.row0 + T, it.q_len));
+    const int lim1 = it.row0 + T < it.q_len ? min(it.seq_len, it.ctx + min(it.row0 + 2 * T, it.q_len)) : 0;
+    it.nblk0 = (lim0 + KVB - 1) / KVB;
+    it.nblk1 = (lim1 + KVB - 1) / KVB;
     it.kv_limit = min(it.seq_len, it.ctx + min(it.row0 + 2 * T, it.q_len));
-    it.n = max(it.nblk[0], it.nblk[1]);
+    it.n = max(it.nblk0, it.nblk1);
     return 2;
   };
 
@@ -461,7 +469,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
       it = nxt;
       const int got = got_nxt;
       got_nxt = item_at(round, nxt);
-      if (got == 1 || it.nblk[g] == 0) continue;
+      if (got == 1 || it.nblk(g) == 0) continue;
       const int row0 = it.row0, q_len = it.q_len, q0 = it.q0, hbase = it.hbase;
       Lap<TRACE> lap_q;
       if (!a.tma) {
@@ -493,7 +501,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
       const bool valid = tok < q_len;
       const int pos = it.ctx + tok;                           // the last key this row sees
       float m = -INFINITY, l = 0.f;
-      const int nb = it.nblk[g];
+      const int nb = it.nblk(g);
       for (int j = 0; j < nb && ok; ++j) {
         Lap<TRACE> lap;
         ok = warp_wait(HKB_BAR(s_full) + 8 * g, (blocks + j) & 1, abort, 1);
@@ -610,8 +618,11 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
       for (int i = 0; i < 8; ++i) a.trace[(size_t)cta * 32 + 8 * g + i] = tr[i];
   } else if (warp == MMA_WARP) {
     // ================= MMA issue: one thread; the whole warp keeps step at the barriers =================
+    // (One warp for both tiles: a second issuing warp, one a tile, was measured -- 800 against 1000
+    // TFLOP/s on a long prompt. A tcgen05.mma of 128 x 128 x 16 takes the tensor pipe ~85 clocks here
+    // whoever issues it, and two threads' products interleave on the pipe without order.)
     constexpr uint32_t IDESC_S = instr_desc(F16, false, KVB), IDESC_PV = instr_desc(F16, true, D);
-    int blocks[2] = {0, 0}, items[2] = {0, 0}, kcnt = 0, vcnt = 0;
+    int blocks0 = 0, blocks1 = 0, items0 = 0, items1 = 0, kcnt = 0, vcnt = 0;   // scalars: the two tiles' loops are unrolled
     auto slot_of = [](int kind, int c) { return 2 * (c & 1) + kind; };
     // S_t = Q_t K^T for the K block in ring slot `slot`: eight products (two 64-dim halves x four 16-dim
     // steps) into the tile's score columns; the tile's query rows are free after the item's last one
@@ -639,16 +650,17 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
       if (got == 1) continue;
       const int n = it.n;
       Lap<TRACE> lap;
-      for (int t = 0; t < 2 && ok; ++t)
-        if (it.nblk[t] > 0) ok = warp_wait(HKB_BAR(q_full) + 8 * t, items[t] & 1, abort, 8);   // the tile's query rows are in place
+      // the tiles' query rows are in place
+      if (it.nblk0 > 0) ok = warp_wait(HKB_BAR(q_full), items0 & 1, abort, 8);
+      if (ok && it.nblk1 > 0) ok = warp_wait(HKB_BAR(q_full) + 8, items1 & 1, abort, 8);
       if (!ok) break;
       lap(tr[0]);
       wait_block(0, kcnt, 4);
       if (!ok) break;
       lap(tr[1]);
       if (lane == 0) {
-        for (int t = 0; t < 2; ++t)
-          if (it.nblk[t] > 0) scores(t, slot_of(0, kcnt), it.nblk[t] == 1);
+        if (it.nblk0 > 0) scores(0, slot_of(0, kcnt), it.nblk0 == 1);
+        if (it.nblk1 > 0) scores(1, slot_of(0, kcnt), it.nblk1 == 1);
         // the first K block's slot is handed back at once
         tc_commit(HKB_BAR(empty) + 8 * slot_of(0, kcnt));
       }
@@ -662,12 +674,13 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
         if (!ok) break;
         lap(tr[1]);
         const uint32_t vaddr = ring + slot_of(1, vcnt + j) * SLOT_BYTES;
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (j >= it.nblk[t]) continue;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (!ok || j >= it.nblk(t)) continue;
           // P of the block; for an item's first block this also says the tile's warps have read the
           // accumulator of the item before out of TMEM (they arrive here after their epilogue)
-          ok = warp_wait(HKB_BAR(p_full) + 8 * t, (blocks[t] + j) & 1, abort, 6);
-          if (!ok) break;
+          ok = warp_wait(HKB_BAR(p_full) + 8 * t, ((t ? blocks1 : blocks0) + j) & 1, abort, 6);
+          if (!ok) continue;
           lap(tr[t ? 6 : 4]);
           tc_fence_after();
           if (lane == 0) {
@@ -676,11 +689,12 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
               umma_ts(tmem + o_col(t), tmem + s_col(t) + ks * 8, smem_desc(vaddr + ks * 16 * 128, HALF_BYTES_KV), IDESC_PV,
                       (j | ks) ? 1u : 0u);
             tc_commit(HKB_BAR(o_done) + 8 * t);
-            // the tile's next scores go over the P just consumed: the tensor pipe runs products in the order issued
-            if (j + 1 < it.nblk[t]) scores(t, slot_of(0, kcnt + j + 1), j + 2 == it.nblk[t]);
           }
+          if (TRACE) { __syncwarp(); lap(tr[5]); }
+          // the tile's next scores go over the P just consumed: the tensor pipe runs products in the order issued
+          if (lane == 0 && j + 1 < it.nblk(t)) scores(t, slot_of(0, kcnt + j + 1), j + 2 == it.nblk(t));
           __syncwarp();
-          lap(tr[5]);
+          lap(tr[TRACE ? 7 : 5]);
         }
         if (ok && lane == 0) {
           tc_commit(HKB_BAR(empty) + 8 * slot_of(1, vcnt + j));                      // V_j
@@ -689,11 +703,11 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
         __syncwarp();
       }
       kcnt += n; vcnt += n;
-      for (int t = 0; t < 2; ++t)
-        if (it.nblk[t] > 0) { blocks[t] += it.nblk[t]; ++items[t]; }
+      blocks0 += it.nblk0; blocks1 += it.nblk1;
+      items0 += it.nblk0 > 0; items1 += it.nblk1 > 0;
     }
     if (TRACE && lane == 0)
-      for (int i = 0; i < 7; ++i) a.trace[(size_t)cta * 32 + 16 + i] = tr[i];
+      for (int i = 0; i < 8; ++i) a.trace[(size_t)cta * 32 + 16 + i] = tr[i];
   } else {
     // ================= producers: warp K_WARP brings the K blocks, warp V_WARP the V blocks =================
     const int which = warp - K_WARP;   // 0: K, 1: V
@@ -701,7 +715,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
     const void* map = which ? static_cast<const void*>(&vmap) : static_cast<const void*>(&kmap);
     const int p_tok = which ? a.v_pos[0] : a.k_pos[0], p_head = which ? a.v_pos[1] : a.k_pos[1],
               p_blk = which ? a.v_pos[2] : a.k_pos[2];
-    int cnt = 0, items[2] = {0, 0};
+    int cnt = 0, items0 = 0, items1 = 0;
     Item nxt;
     int got_nxt = item_at(0, nxt);
     for (int round = 1; ok && got_nxt; ++round) {
@@ -712,13 +726,14 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
       const int n = it.n, kvh = it.kvh, kv_limit = it.kv_limit;
       const uint8_t* src = (which ? a.v + (int64_t)kvh * a.v_stride_head : a.k + (int64_t)kvh * a.k_stride_head);
       const int* table_row = a.block_table + (int64_t)it.req * a.table_stride;
-      // page ids of a block's eight 16-token tiles, fetched one block ahead of their use
+      // page ids of a block's eight 16-token tiles, fetched one block ahead of their use (raw: the clamp
+      // waits for the load, so it is applied where the id is used)
       auto page_ids = [&](int kv0, int& id, int& sub) {
         id = 0; sub = 0;
         if (lane < 8 && kv0 < kv_limit) {
           const int tile = kv0 / TILE_TOKENS + lane;
           const int page = min(tile / a.tiles_per_page, a.max_pages - 1);
-          id = min(max(__ldg(table_row + page), 0), a.num_blocks - 1);
+          id = __ldg(table_row + page);
           sub = tile % a.tiles_per_page;
         }
       };
@@ -728,22 +743,22 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
         // the V warp has nothing to do until the first scores exist: it brings the query tiles, one copy a
         // (tile, head, 64-dim half): T token rows of 128 bytes, landing where row h * T + token belongs --
         // once the products of the item before have read the old ones
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (it.nblk[t] == 0) continue;
-          if (items[t] > 0) {
-            ok = warp_wait(HKB_BAR(q_empty) + 8 * t, (items[t] - 1) & 1, abort, 9);
-            if (!ok) break;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (!ok || it.nblk(t) == 0) continue;
+          const int before = t ? items1 : items0;
+          if (before > 0) {
+            ok = warp_wait(HKB_BAR(q_empty) + 8 * t, (before - 1) & 1, abort, 9);
+            if (!ok) continue;
           }
-          ++items[t];
+          if (t) ++items1; else ++items0;
           if (lane == 0) mbar_arrive_expect_tx(HKB_BAR(q_full) + 8 * t, Q_BYTES);
           __syncwarp();
           for (int x = lane; x < 2 * GP; x += 32) {
             const int h = x >> 1, half = x & 1;
-            int c[3];
-            c[0] = half * 64;
-            c[a.q_pos[0]] = it.q0 + it.row0 + t * T;
-            c[a.q_pos[1]] = it.hbase + h;
-            tma_load_3d(q_smem + t * Q_BYTES + half * HALF_BYTES_Q + h * T * 128, &qmap, HKB_BAR(q_full) + 8 * t, c[0], c[1], c[2]);
+            const int tok = it.q0 + it.row0 + t * T, head = it.hbase + h;
+            tma_load_3d(q_smem + t * Q_BYTES + half * HALF_BYTES_Q + h * T * 128, &qmap, HKB_BAR(q_full) + 8 * t, half * 64,
+                        a.q_pos[0] == 1 ? tok : head, a.q_pos[0] == 1 ? head : tok);
           }
         }
         if (!ok) break;
@@ -766,12 +781,14 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
           if (lane == 0) mbar_arrive_expect_tx(bar, SLOT_BYTES);
           __syncwarp();
           if (lane < 16) {
-            int c[4];
-            c[0] = (lane & 1) * 64;
-            c[p_tok] = sub * TILE_TOKENS;
-            c[p_head] = kvh;
-            c[p_blk] = id;
-            tma_load_4d(slot_addr + (lane & 1) * HALF_BYTES_KV + t * TILE_TOKENS * 128, map, bar, c[0], c[1], c[2], c[3]);
+            // coordinates 1..3 of the map are the token, the kv head and the block in the order the cache's
+            // strides put them (selects, not an indexed array: that would live in local memory)
+            id = min(max(id, 0), a.num_blocks - 1);
+            const int tok = sub * TILE_TOKENS;
+            const int c1 = p_tok == 1 ? tok : p_head == 1 ? kvh : id;
+            const int c2 = p_tok == 2 ? tok : p_head == 2 ? kvh : id;
+            const int c3 = p_tok == 3 ? tok : p_head == 3 ? kvh : id;
+            tma_load_4d(slot_addr + (lane & 1) * HALF_BYTES_KV + t * TILE_TOKENS * 128, map, bar, (lane & 1) * 64, c1, c2, c3);
           }
           tick(tr[1]);
         } else {
