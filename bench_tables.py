@@ -210,7 +210,7 @@ def prefill_table(only: str = ""):
     return 0
 
 
-def prefill_trace(case: str):
+def prefill_trace(case: str, fp8: bool = False):
     """Where the tensor-memory prefill kernel's cycles go on one shape (default 1x0+8192): the traced
     build's per-CTA counters (hkb_paged_prefill_trace), summed over CTAs and divided by the key blocks
     walked -- cycles a 128-key block for each role and phase."""
@@ -247,6 +247,11 @@ def prefill_trace(case: str):
     table_d, lens_d = table.to(dev), torch.tensor(seq, dtype=torch.int32, device=dev)
     starts_d = torch.tensor(starts, dtype=torch.int32, device=dev)
     kc, vc = k.transpose(1, 2), v.transpose(1, 2)
+    scales = (None, None)
+    if fp8:     # the same values as an fp8-e4m3 cache with per-tensor scales
+        ks, vs = (k.float().abs().max() / 448.0).reshape(1), (v.float().abs().max() / 448.0).reshape(1)
+        kc, vc = (kc.float() / ks).to(torch.float8_e4m3fn), (vc.float() / vs).to(torch.float8_e4m3fn)
+        scales = (ks.data_ptr(), vs.data_ptr())
     n_cta = work.shape[0] * hkv
     trace = torch.zeros(n_cta, 32, dtype=torch.int64, device=dev)
     lib = hkb.load()
@@ -255,7 +260,7 @@ def prefill_trace(case: str):
         rc = lib.hkb_paged_prefill_trace(out.data_ptr(), out.stride(0), out.stride(1), q.data_ptr(), q.stride(0), q.stride(1),
                                          cache(kc), cache(vc), table_d.data_ptr(), table_d.stride(0), table_d.shape[1],
                                          lens_d.data_ptr(), starts_d.data_ptr(), work.data_ptr(), work.shape[0], q.shape[0], hq, hkv, d, bs,
-                                         d ** -0.5, hkb.KV_BF16, None, None, trace.data_ptr(),
+                                         d ** -0.5, hkb.KV_FP8_E4M3 if fp8 else hkb.KV_BF16, scales[0], scales[1], trace.data_ptr(),
                                          torch.cuda.current_stream().cuda_stream)
         hkb.check("hkb_paged_prefill_trace", rc)
     torch.cuda.synchronize()
@@ -516,6 +521,7 @@ def main():
                                                "x-split (a small case for a profiler)")
     ap.add_argument("--prefill-trace", action="store_true", help="cycles by role and phase of the tensor-memory prefill kernel")
     ap.add_argument("--attrib", action="store_true", help="the decode walk with one stage left out: what each stage costs")
+    ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8"], help="with --prefill-trace: the cache type")
     ap.add_argument("--shards", action="store_true", help="one rank's share of c2 over 1/2/4/8 GPUs, on one GPU: the step's fixed costs")
     ap.add_argument("--layouts", action="store_true", help="the decode over the usual and the x-split cache layout")
     args = ap.parse_args()
@@ -526,7 +532,7 @@ def main():
     if args.attrib:
         return attribution_table()
     if args.prefill_trace:
-        return prefill_trace(args.case)
+        return prefill_trace(args.case, args.kv == "fp8")
     if args.prefill:
         return prefill_table(args.case)
     return latency_table()

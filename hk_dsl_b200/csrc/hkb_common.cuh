@@ -96,9 +96,12 @@ __device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
 // Position of 16-byte chunk `c` of row `r` inside a shared-memory tile whose rows
 // are ROW_BYTES long: chunks are XOR-swizzled by the row so that eight rows read
 // at the same column (ldmatrix) and eight columns of one row are both conflict-free.
+// (A 64-byte row -- an fp8 row of head size 64 -- has four chunks: the XOR is then with r & 3, which
+// keeps a chunk inside its row.)
 template <int ROW_BYTES>
 __device__ __forceinline__ uint32_t tile_off(int r, int c) {
-  return static_cast<uint32_t>(r * ROW_BYTES + ((c ^ (r & 7)) << 4));
+  constexpr int MASK = ROW_BYTES / 16 - 1 < 7 ? ROW_BYTES / 16 - 1 : 7;
+  return static_cast<uint32_t>(r * ROW_BYTES + ((c ^ (r & MASK)) << 4));
 }
 
 // The same tile in the layout the fp8 fragment loads want: rows of 128 bytes whose 32-byte
@@ -109,6 +112,21 @@ __device__ __forceinline__ uint32_t tile_off(int r, int c) {
 __device__ __forceinline__ uint32_t tile_off_u32(int r, int c) {
   const int f = (r & 3) ^ ((r >> 2) & 1);
   return r * 128 + (((((c >> 1) ^ f) << 1) | (c & 1)) << 4);
+}
+
+// The same idea for fp8 rows of any head size (ROWB = head_dim bytes). Rows of 128 bytes and more
+// keep the form above (f touches the low two bits of the unit index, so a 256-byte row's eight units
+// stay inside the row). A 64-byte row is two units, too few to tell four rows apart by a XOR inside
+// the row, so rows are placed in pairs: units are dealt to 32 slots of 32 bytes, slot
+// 4 (r / 2) + m with m = (r + ((r >> 2) & 1) + 2 u) & 3 -- the rows {0..3}, {4..7}, {0,2,4,6} and
+// {1,3,5,7} of one unit index u each fall on four different m, i.e. on different banks. Both forms
+// repeat every 8 rows (8 ROWB bytes on), which the loaders and the row + 8 loads rely on.
+template <int ROWB>
+__device__ __forceinline__ uint32_t tile_off_f8(int r, int c) {
+  static_assert(ROWB == 64 || ROWB == 128 || ROWB == 256, "fp8 rows of head sizes 64, 128, 256");
+  if (ROWB == 64) return (uint32_t)((4 * (r >> 1) + ((r + ((r >> 2) & 1) + 2 * (c >> 1)) & 3)) * 32 + (c & 1) * 16);
+  const int f = (r & 3) ^ ((r >> 2) & 1);
+  return r * ROWB + (((((c >> 1) ^ f) << 1) | (c & 1)) << 4);
 }
 
 }  // namespace hkb

@@ -279,7 +279,30 @@ static int dispatch_mma(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
   constexpr int NST = FP8 ? 4 : (D == 256 ? 2 : 3);
   dim3 grid(a.num_splits, a.num_kv_heads, num_seqs);
   if (use_stream(a, num_seqs)) {
-    if constexpr (D == 256) {
+    if constexpr (FP8 && D != 128) {
+      // fp8 rows of 64 and 256 bytes: the same worker on the layout tile_off_f8 gives them. Head size 256:
+      // a tile is as many bytes as a bf16 tile of head size 128, and the accumulators take as many registers
+      // as the bf16 walk's at 256 -- one CTA an SM, six rings; head size 64: 1 KB tiles, three CTAs an SM.
+      if constexpr (D == 256) {
+        constexpr int RINGS = 6;
+        grid = stream_grid(a.num_kv_heads, 1);
+        if (a.group <= 8) {
+          using P = WalkMMAF8<D, 1, 3, 1>;
+          return launch_stream<walk_stream_kernel<P, RINGS>>(WalkStream<P, RINGS>::SMEM_BYTES, RINGS * 32, grid, a, num_seqs, st);
+        }
+        using P2 = WalkMMAF8<D, 2, 3, 1>;
+        return launch_stream<walk_stream_kernel<P2, RINGS>>(WalkStream<P2, RINGS>::SMEM_BYTES, RINGS * 32, grid, a, num_seqs, st);
+      } else {
+        if (a.group <= 8) {
+          using P = WalkMMAF8<D, 1, 4, 3>;
+          return launch_stream<walk_stream_kernel<P, WARPS>>(WalkStream<P, WARPS>::SMEM_BYTES, WARPS * 32,
+                                                             stream_grid(a.num_kv_heads, 3), a, num_seqs, st);
+        }
+        using P2 = WalkMMAF8<D, 2, 4, 2>;
+        return launch_stream<walk_stream_kernel<P2, WARPS>>(WalkStream<P2, WARPS>::SMEM_BYTES, WARPS * 32,
+                                                            stream_grid(a.num_kv_heads), a, num_seqs, st);
+      }
+    } else if constexpr (D == 256) {
       constexpr int RINGS = 6;
       grid = stream_grid(a.num_kv_heads, 1);
       if (a.group <= 8) {
@@ -391,7 +414,6 @@ static int decode_check(const void* out, const void* q, int64_t q_stride_tok, in
   if (kv_dtype != HKB_KV_BF16 && kv_dtype != HKB_KV_FP8_E4M3 && kv_dtype != HKB_KV_F16) return HKB_ERR_DTYPE;
   const bool fp8 = kv_dtype == HKB_KV_FP8_E4M3;
   if (fp8 && (!k_scale || !v_scale)) return HKB_ERR_SCALE;
-  if (fp8 && head_dim != 128) return HKB_ERR_UNSUPPORTED;
   if (num_splits < 1 || num_splits > HKB_MAX_SPLITS) return HKB_ERR_SPLITS;
   if (num_splits > 1 && (!part_out || !part_lse)) return HKB_ERR_SPLITS;
   if (max_pages < 1 || kc.num_blocks < 1 || vc.num_blocks < 1) return HKB_ERR_SIZE;
@@ -493,7 +515,9 @@ static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_hea
     if (fp8) return mma ? dispatch_mma<128, true>(a, num_seqs, st) : dispatch_cc<128, true>(a, num_seqs, st);
     return mma ? dispatch_mma<128, false>(a, num_seqs, st) : dispatch_cc<128, false>(a, num_seqs, st);
   }
-  if (head_dim == 256) return dispatch_mma<256, false>(a, num_seqs, st);   // 512-byte rows: tensor-core tiles at every group
+  if (head_dim == 256)   // 512-byte rows (256 in fp8): tensor-core tiles at every group
+    return fp8 ? dispatch_mma<256, true>(a, num_seqs, st) : dispatch_mma<256, false>(a, num_seqs, st);
+  if (fp8) return dispatch_mma<64, true>(a, num_seqs, st);   // fp8: the tensor-core worker at every group
   return mma ? dispatch_mma<64, false>(a, num_seqs, st) : dispatch_cc<64, false>(a, num_seqs, st);
 }
 

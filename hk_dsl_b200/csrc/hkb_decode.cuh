@@ -62,9 +62,8 @@ __device__ __forceinline__ void split_range(int n_tiles, int splits, int split, 
 // copies of tile `t` (K rows then V rows) into ring stage `stage`. Page ids come
 // from `PageIds`, which keeps 32 ids a batch in registers, one batch ahead, so that
 // the table read is never on the critical path of a copy.
-template <int ROWB, bool UNIT32 = false>   // UNIT32: the 32-byte-unit swizzle of 128-byte rows (tile_off_u32)
+template <int ROWB, bool UNIT32 = false>   // UNIT32: the 32-byte-unit layout of fp8 rows (tile_off_f8)
 struct TileLoader {
-  static_assert(!UNIT32 || ROWB == 128, "the 32-byte-unit layout is for 128-byte rows");
   static constexpr int CPR = ROWB / 16;              // 16-byte chunks per row
   static constexpr int TILE_BYTES = TILE_TOKENS * ROWB;
   static constexpr int ITERS = TILE_TOKENS * CPR / 32;   // copies a lane issues a tile
@@ -83,7 +82,7 @@ struct TileLoader {
     const int rl = lane / CPR, c = lane % CPR;
 #pragma unroll
     for (int q = 0; q < NPAT; ++q)
-      dst[q] = UNIT32 ? tile_off_u32(RPI * q + rl, c) - RPI * q * ROWB : rl * ROWB + ((c ^ ((RPI * q + rl) & 7)) << 4);
+      dst[q] = UNIT32 ? tile_off_f8<UNIT32 ? ROWB : 128>(RPI * q + rl, c) - RPI * q * ROWB : tile_off<ROWB>(RPI * q + rl, c) - RPI * q * ROWB;
     lane_k = rl * (int)kst + c * 16;
     lane_v = rl * (int)vst + c * 16;
     k_flat = kst == ROWB;

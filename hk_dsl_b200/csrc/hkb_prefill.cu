@@ -71,7 +71,10 @@ struct Prefill {
   static constexpr int Q_BYTES = UNITS * TILE_BYTES;  // the CTA's query rows, read back as A fragments every block
   static constexpr int STAGE_BYTES = KV_TILES * 2 * TILE_BYTES;
   static constexpr int RAW_STAGE_BYTES = FP8 ? KV_TILES * 2 * RAW_TILE_BYTES : 0;   // fp8 tiles land here first
-  static constexpr int SMEM_BYTES = Q_BYTES + NST * (STAGE_BYTES + RAW_STAGE_BYTES);
+  // one landing buffer is enough: a warp widens the tiles it fetched and only then fetches the next block's
+  // into the same place (two would not fit beside head_dim 256's query rows and stages)
+  static constexpr int SMEM_BYTES = Q_BYTES + NST * STAGE_BYTES + RAW_STAGE_BYTES;
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory of one SM");
   static constexpr float RESCALE_LOG2 = 8.f;
 
   // A warp fills the K and the V tile of its 16 tokens of a stage; rows at or past `kv_limit` are
@@ -141,7 +144,7 @@ struct Prefill {
     const uint32_t ring = qsm + Q_BYTES;
     const uint32_t raw = ring + NST * STAGE_BYTES;   // fp8 only: where the copies land before they are widened
     const uint32_t land = FP8 ? raw : ring;
-    constexpr int LAND_BYTES = FP8 ? RAW_STAGE_BYTES : STAGE_BYTES;
+    constexpr int LAND_BYTES = FP8 ? 0 : STAGE_BYTES;   // fp8: the one landing buffer
 
     // Stage the warp's query rows (rows past the request: zeros) in the swizzled layout ldmatrix reads.
     const bool q16 = ((reinterpret_cast<uintptr_t>(a.q) | (uintptr_t)(a.q_stride_tok * 2) | (uintptr_t)(a.q_stride_head * 2)) & 15) == 0;
@@ -203,9 +206,12 @@ struct Prefill {
         // is past its work on block b-2, the stage's previous tenant (the barrier of iteration b-1).
         __syncwarp();
 #pragma unroll
-        for (int which = 0; which < 2; ++which)
-          WalkMMA<D, true, 1, 4, 4>::widen(raw + (b & 1) * RAW_STAGE_BYTES + (warp * 2 + which) * RAW_TILE_BYTES,
-                                           ring + (b & 1) * STAGE_BYTES + (warp * 2 + which) * TILE_BYTES, lane);
+        for (int which = 0; which < 2; ++which) {
+          if (WARPS == 8 && which != (warp & 1)) continue;          // eight warps: each fetched one tile (fill)
+          const int tile = WARPS == 8 ? warp : warp * 2 + which;
+          WalkMMA<D, true, 1, 4, 4>::widen(raw + tile * RAW_TILE_BYTES, ring + (b & 1) * STAGE_BYTES + tile * TILE_BYTES, lane);
+        }
+        __syncwarp();   // the landing tiles are read: the next block's copies may overwrite them
       }
       __syncthreads();   // block b has landed for every warp (and, the first time, the query rows); block b-1's stage is free
       if (b + 1 < n_blocks) fill(a, ld, land + ((b + 1) & 1) * LAND_BYTES, (b + 1) * KVB, kv_limit, table_row, warp, lane);
@@ -445,14 +451,14 @@ static bool make_query_map(CUtensorMap* m, const void* q, int64_t stride_tok, in
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int GP, bool F16, bool TRACE = false>
+template <int GP, bool F16, bool TRACE = false, bool FP8 = false>
 static int launch_prefill_tc(const tc::Args& a, const CUtensorMap& kmap, const CUtensorMap& vmap, const CUtensorMap& qmap,
                              int num_work, cudaStream_t st) {
   static bool armed[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e == cudaSuccess && dev >= 0 && dev < 64 && !armed[dev]) {
-    e = cudaFuncSetAttribute(tc::prefill_tc_kernel<GP, F16, TRACE>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+    e = cudaFuncSetAttribute(tc::prefill_tc_kernel<GP, F16, TRACE, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
     if (e == cudaSuccess) armed[dev] = true;
   }
   if (e == cudaSuccess) {
@@ -461,20 +467,20 @@ static int launch_prefill_tc(const tc::Args& a, const CUtensorMap& kmap, const C
     int sms = hkb_sm_count(-1);
     if (sms <= 0) sms = 148;
     dim3 grid((unsigned)(total < sms ? total : sms));
-    tc::prefill_tc_kernel<GP, F16, TRACE><<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(a, kmap, vmap, qmap);
+    tc::prefill_tc_kernel<GP, F16, TRACE, FP8><<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(a, kmap, vmap, qmap);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }
   return HKB_OK;
 }
 
-template <bool F16>
+template <bool F16, bool FP8 = false>
 static int dispatch_prefill_tc(const tc::Args& a, const CUtensorMap& kmap, const CUtensorMap& vmap, const CUtensorMap& qmap,
                                int num_work, cudaStream_t st) {
-  if (a.group % 8 == 0) return launch_prefill_tc<8, F16>(a, kmap, vmap, qmap, num_work, st);
-  if (a.group % 4 == 0) return launch_prefill_tc<4, F16>(a, kmap, vmap, qmap, num_work, st);
-  if (a.group % 2 == 0) return launch_prefill_tc<2, F16>(a, kmap, vmap, qmap, num_work, st);
-  return launch_prefill_tc<1, F16>(a, kmap, vmap, qmap, num_work, st);
+  if (a.group % 8 == 0) return launch_prefill_tc<8, F16, false, FP8>(a, kmap, vmap, qmap, num_work, st);
+  if (a.group % 4 == 0) return launch_prefill_tc<4, F16, false, FP8>(a, kmap, vmap, qmap, num_work, st);
+  if (a.group % 2 == 0) return launch_prefill_tc<2, F16, false, FP8>(a, kmap, vmap, qmap, num_work, st);
+  return launch_prefill_tc<1, F16, false, FP8>(a, kmap, vmap, qmap, num_work, st);
 }
 
 }  // namespace hkb
@@ -490,7 +496,7 @@ extern "C" int hkb_prefill_tile_rows(int num_q_heads, int num_kv_heads) {
 extern "C" int hkb_prefill_uses_tcgen05(int head_dim, int kv_dtype) {
   const char* v = std::getenv("HKB_PREFILL_MMA_SYNC");
   if (v && v[0] == '1') return 0;
-  return head_dim == 128 && (kv_dtype == HKB_KV_BF16 || kv_dtype == HKB_KV_F16) ? 1 : 0;
+  return head_dim == 128 && (kv_dtype == HKB_KV_BF16 || kv_dtype == HKB_KV_F16 || kv_dtype == HKB_KV_FP8_E4M3) ? 1 : 0;
 }
 
 extern "C" int hkb_prefill_tc_error(int clear) {
@@ -524,7 +530,6 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
   if (kv_dtype != HKB_KV_BF16 && kv_dtype != HKB_KV_FP8_E4M3 && kv_dtype != HKB_KV_F16) return HKB_ERR_DTYPE;
   const bool fp8 = kv_dtype == HKB_KV_FP8_E4M3;
   if (fp8 && (!k_scale || !v_scale)) return HKB_ERR_SCALE;
-  if (fp8 && head_dim != 128) return HKB_ERR_UNSUPPORTED;
   const int es = fp8 ? 1 : 2;
   if (max_pages < 1 || kc.num_blocks < 1 || vc.num_blocks < 1) return HKB_ERR_SIZE;
   const int group = num_q_heads / num_kv_heads;
@@ -563,6 +568,7 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
     t.seq_lens = a.seq_lens; t.q_start = a.q_start; t.work = a.work; t.num_work = num_work;
     t.num_q_heads = a.num_q_heads; t.num_kv_heads = a.num_kv_heads; t.group = a.group; t.tiles_per_page = a.tiles_per_page;
     t.scale = a.scale;
+    t.k_scale = a.k_scale; t.v_scale = a.v_scale;
     t.trace = g_trace_for_next_call;
     // K and V blocks come by TMA where a tensor map describes the cache (HKB_PREFILL_NO_TMA=1: the cp.async gather, the comparison arm)
     alignas(64) CUtensorMap kmap, vmap, qmap;
@@ -571,7 +577,8 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
     // a query tile that runs past the tensor's last token reads zeros there (the map knows num_tokens);
     // rows past a request's own tokens belong to the next request and are masked
     const int64_t q_tokens = num_tokens;
-    t.tma = !(no_tma && no_tma[0] == '1') && make_cache_map(&kmap, kc, block_size, num_kv_heads, t.k_pos) &&
+    // (an fp8 cache is widened by the producers on its way in: no tile copies, and the query rows are staged by the softmax warps)
+    t.tma = !fp8 && !(no_tma && no_tma[0] == '1') && make_cache_map(&kmap, kc, block_size, num_kv_heads, t.k_pos) &&
             make_cache_map(&vmap, vc, block_size, num_kv_heads, t.v_pos) &&
             make_query_map(&qmap, q, q_stride_tok, q_stride_head, q_tokens, num_q_heads, 128 / gp, t.q_pos);
     if (!t.tma) {
@@ -579,14 +586,19 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
       for (int i = 0; i < 3; ++i) t.k_pos[i] = t.v_pos[i] = i + 1;
       t.q_pos[0] = 1; t.q_pos[1] = 2;
     }
-    if (t.trace) {   // the traced build: the headline shape only (a bf16 cache, a GQA group of 4)
-      if (kv_dtype != HKB_KV_BF16 || group % 4 || group % 8 == 0) return HKB_ERR_UNSUPPORTED;
-      return launch_prefill_tc<4, false, true>(t, kmap, vmap, qmap, num_work, st);
+    if (t.trace) {   // the traced build: the headline shape only (a bf16 or an fp8 cache, a GQA group of 4)
+      if (kv_dtype == HKB_KV_F16 || group % 4 || group % 8 == 0) return HKB_ERR_UNSUPPORTED;
+      return fp8 ? launch_prefill_tc<4, true, true, true>(t, kmap, vmap, qmap, num_work, st)
+                 : launch_prefill_tc<4, false, true>(t, kmap, vmap, qmap, num_work, st);
     }
+    if (fp8) return dispatch_prefill_tc<true, true>(t, kmap, vmap, qmap, num_work, st);
     return kv_dtype == HKB_KV_F16 ? dispatch_prefill_tc<true>(t, kmap, vmap, qmap, num_work, st)
                                   : dispatch_prefill_tc<false>(t, kmap, vmap, qmap, num_work, st);
   }
-  if (fp8) return dispatch_prefill<128, true>(a, num_work, st);
+  if (fp8) {
+    if (head_dim == 256) return dispatch_prefill<256, true>(a, num_work, st);
+    return head_dim == 128 ? dispatch_prefill<128, true>(a, num_work, st) : dispatch_prefill<64, true>(a, num_work, st);
+  }
   if (kv_dtype == HKB_KV_F16) {
     if (head_dim == 256) return dispatch_prefill<256, false, true>(a, num_work, st);
     return head_dim == 128 ? dispatch_prefill<128, false, true>(a, num_work, st) : dispatch_prefill<64, false, true>(a, num_work, st);

@@ -238,6 +238,8 @@ struct Args {
   int num_work;
   int num_q_heads, num_kv_heads, group, tiles_per_page;
   float scale;
+  const float* k_scale;     // fp8 caches: the per-tensor scales (device floats); else unused
+  const float* v_scale;
   int tma;                  // K and V blocks by TMA (the two tensor maps are valid)
   int k_pos[3], v_pos[3];   // which coordinate of the map (1..3) is the token, the kv head, the block
   int q_pos[2];             // which coordinate of the query map (1..2) is the token, the head
@@ -303,6 +305,70 @@ __device__ __forceinline__ void fill_half(const Args& a, uint32_t slot, const ui
         else asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(dst), "r"(0u) : "memory");
       }
     }
+  }
+}
+
+// A 128-token block of an fp8-e4m3 cache into a ring slot as f16, by one producer warp: the bytes are
+// loaded into registers (a lane a 16-byte chunk = 16 dims, a row 8 lanes), converted exactly
+// (cvt.rn.f16x2.e4m3x2; the per-tensor scale is applied to the scores and to the output, not here)
+// and stored where the 16-bit path's copies would have landed.
+// Rows at or past `kv_limit` are zeros, never read.
+__device__ __forceinline__ uint32_t fp8x2_to_f16x2(uint32_t two_bytes) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(h2) : "h"((uint16_t)two_bytes));
+  return h2;
+}
+struct Fp8Rows { uint4 v[4]; };   // this lane's four rows (rl, rl + 4, rl + 8, rl + 12) of a 16-token tile
+__device__ __forceinline__ void fp8_tile_load(Fp8Rows& x, const Args& a, const uint8_t* base, int64_t sb, int64_t st,
+                                              int id8, int sub8, int t, int rows_live, int64_t lane_off, int rl) {
+  const int id = min(max(__shfl_sync(0xffffffffu, id8, t), 0), a.num_blocks - 1), sub = __shfl_sync(0xffffffffu, sub8, t);
+  const uint8_t* tp = base + (int64_t)id * sb + (int64_t)(sub * TILE_TOKENS) * st + lane_off;
+#pragma unroll
+  for (int y = 0; y < 4; ++y) {
+    x.v[y] = make_uint4(0u, 0u, 0u, 0u);
+    if (t * TILE_TOKENS + 4 * y + rl < rows_live) x.v[y] = ldg_stream16(tp + (int64_t)(4 * y) * st);
+  }
+}
+__device__ __forceinline__ void fp8_tile_store(const Fp8Rows& x, uint32_t dst, uint32_t xa0, uint32_t xa1, uint32_t xb0,
+                                               uint32_t xb1) {
+#pragma unroll
+  for (int y = 0; y < 4; ++y) {
+    const uint32_t w[4] = {x.v[y].x, x.v[y].y, x.v[y].z, x.v[y].w};
+    uint32_t h[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { h[2 * i] = fp8x2_to_f16x2(w[i]); h[2 * i + 1] = fp8x2_to_f16x2(w[i] >> 16); }
+    const uint32_t row = dst + (uint32_t)(4 * y) * 128;
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(row + ((y & 1) ? xb0 : xa0)), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(row + ((y & 1) ? xb1 : xa1)), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
+  }
+}
+__device__ __forceinline__ void fill_block_fp8(const Args& a, uint32_t slot, const uint8_t* base, int64_t sb, int64_t st,
+                                               int id8, int sub8, int kv0, int kv_limit, int lane) {
+  const int g = lane & 7, rl = lane >> 3;            // this lane's chunk of a row, and its row of four
+  const int c0 = 2 * (g & 3);                        // the first of the two 16-byte f16 chunks its 16 dims become
+  const uint32_t dst0 = slot + (uint32_t)(g >> 2) * HALF_BYTES_KV + (uint32_t)rl * 128;
+  // rows rl, rl + 4, rl + 8, ...: r & 7 is rl or rl + 4, so the two chunks' places inside a row take two values each
+  const uint32_t xa0 = (uint32_t)((c0 ^ rl) << 4), xa1 = (uint32_t)(((c0 + 1) ^ rl) << 4);
+  const uint32_t xb0 = (uint32_t)((c0 ^ (rl + 4)) << 4), xb1 = (uint32_t)(((c0 + 1) ^ (rl + 4)) << 4);
+  const int64_t lane_off = (int64_t)rl * st + g * 16;
+  const int rows_live = kv_limit - kv0;              // rows of the block that are keys
+  // three tiles' loads in flight while a fourth is converted (a trip to L2 is ~1000 clocks here, a tile's
+  // conversion ~200)
+  constexpr int NT = KVB / TILE_TOKENS;
+  Fp8Rows r0, r1, r2, r3;
+  fp8_tile_load(r0, a, base, sb, st, id8, sub8, 0, rows_live, lane_off, rl);
+  fp8_tile_load(r1, a, base, sb, st, id8, sub8, 1, rows_live, lane_off, rl);
+  fp8_tile_load(r2, a, base, sb, st, id8, sub8, 2, rows_live, lane_off, rl);
+#pragma unroll 1
+  for (int t = 0; t < NT; t += 4) {
+    fp8_tile_load(r3, a, base, sb, st, id8, sub8, t + 3, rows_live, lane_off, rl);
+    fp8_tile_store(r0, dst0 + (uint32_t)(t * TILE_TOKENS) * 128, xa0, xa1, xb0, xb1);
+    if (t + 4 < NT) fp8_tile_load(r0, a, base, sb, st, id8, sub8, t + 4, rows_live, lane_off, rl);
+    fp8_tile_store(r1, dst0 + (uint32_t)((t + 1) * TILE_TOKENS) * 128, xa0, xa1, xb0, xb1);
+    if (t + 4 < NT) fp8_tile_load(r1, a, base, sb, st, id8, sub8, t + 5, rows_live, lane_off, rl);
+    fp8_tile_store(r2, dst0 + (uint32_t)((t + 2) * TILE_TOKENS) * 128, xa0, xa1, xb0, xb1);
+    if (t + 4 < NT) fp8_tile_load(r2, a, base, sb, st, id8, sub8, t + 6, rows_live, lane_off, rl);
+    fp8_tile_store(r3, dst0 + (uint32_t)((t + 3) * TILE_TOKENS) * 128, xa0, xa1, xb0, xb1);
   }
 }
 
@@ -377,7 +443,10 @@ struct Item {
   __device__ __forceinline__ int nblk(int t) const { return t ? nblk1 : nblk0; }
 };
 
-template <int GP, bool F16, bool TRACE = false>
+// F16: the products' operands (Q, K, V, P) are f16, else bf16. FP8: the caches are fp8-e4m3 -- the
+// producers convert them to f16 on their way into the ring, the query rows (bf16) are converted to f16
+// as they are staged, so F16 is set; the output stays bf16 and carries v_scale, the scores carry k_scale.
+template <int GP, bool F16, bool TRACE = false, bool FP8 = false>
 __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kmap,
                                                                 const __grid_constant__ CUtensorMap vmap,
                                                                 const __grid_constant__ CUtensorMap qmap) {
@@ -385,6 +454,8 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
   unsigned long long tr[8] = {0, 0, 0, 0, 0, 0, 0, 0};      // this thread's lap counters (TRACE builds)
   const long long t_begin = TRACE ? now() : 0;
   constexpr int T = ROWS / GP;                 // tokens of one query tile
+  constexpr bool OUT_F16 = F16 && !FP8;
+  static_assert(!FP8 || F16, "an fp8 cache is widened to f16");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const uint32_t base = (smem_u32(raw_smem) + 1023u) & ~1023u;
@@ -460,7 +531,8 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
     if (TRACE) tr[7] = (unsigned long long)(now() - t_begin);   // set-up: barriers, TMEM, the CTA-wide barrier
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t s_addr = lane_addr + s_col(g);
-    const float qs = a.scale * LOG2E;
+    const float qs = a.scale * LOG2E * (FP8 ? __ldg(a.k_scale) : 1.f);
+    const float out_scale = FP8 ? __ldg(a.v_scale) : 1.f;
     int blocks = 0, items = 0;
     Item nxt;
     int got_nxt = item_at(0, nxt);
@@ -490,6 +562,14 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
         for (int x16 = 0; x16 < 16; ++x16) {
           const int x = x16 * ROWS + (warp & 3) * 32 + lane, r = x >> 4, c = x & 15;
           const uint32_t dst = q_smem + g * Q_BYTES + (c >> 3) * HALF_BYTES_Q + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+          if (FP8) {   // bf16 query rows beside an f16 cache tile: to f16, clamped to its range
+            uint32_t* w = reinterpret_cast<uint32_t*>(&qv[x16]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float lo = fminf(fmaxf(bf16lo(w[i]), -65504.f), 65504.f), hi = fminf(fmaxf(bf16hi(w[i]), -65504.f), 65504.f);
+              asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(w[i]) : "f"(hi), "f"(lo));
+            }
+          }
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(dst), "r"(qv[x16].x), "r"(qv[x16].y), "r"(qv[x16].z), "r"(qv[x16].w) : "memory");
         }
         fence_async_smem();
@@ -566,7 +646,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
       if (!ok) break;
       blocks += nb;
       tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const float inv = (l > 0.f ? 1.f / l : 0.f) * out_scale;
       // Each thread parks half of its output row (64 dims, 128 bytes; 16-byte chunks XOR-ed by the row so
       // that the 32 rows of a warp do not collide on banks) in the warp's staging rows, then the warp --
       // which owns exactly these 32 rows -- writes them out four half rows an instruction; then the
@@ -582,7 +662,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
           uint32_t w[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            if (F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(w[i]) : "f"(o[2 * i + 1] * inv), "f"(o[2 * i] * inv));
+            if (OUT_F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(w[i]) : "f"(o[2 * i + 1] * inv), "f"(o[2 * i] * inv));
             else asm("cvt.rn.bf16x2.f32 %0, %1, %2;\n" : "=r"(w[i]) : "f"(o[2 * i + 1] * inv), "f"(o[2 * i] * inv));
           }
 #pragma unroll
@@ -713,8 +793,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
     const int which = warp - K_WARP;   // 0: K, 1: V
     const int64_t sb = which ? a.v_stride_block : a.k_stride_block, st = which ? a.v_stride_token : a.k_stride_token;
     const void* map = which ? static_cast<const void*>(&vmap) : static_cast<const void*>(&kmap);
-    const int p_tok = which ? a.v_pos[0] : a.k_pos[0], p_head = which ? a.v_pos[1] : a.k_pos[1],
-              p_blk = which ? a.v_pos[2] : a.k_pos[2];
+    const int p_tok = which ? a.v_pos[0] : a.k_pos[0], p_head = which ? a.v_pos[1] : a.k_pos[1];   // the block id takes the third
     int cnt = 0, items0 = 0, items1 = 0;
     Item nxt;
     int got_nxt = item_at(0, nxt);
@@ -773,7 +852,13 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
         if (lap > 0) ok = warp_wait(HKB_BAR(empty) + 8 * slot, (lap - 1) & 1, abort, 7);
         if (!ok) break;
         tick(tr[0]);
-        if (a.tma && kv0 + KVB <= kv_limit) {
+        if (FP8) {
+          fill_block_fp8(a, slot_addr, src, sb, st, id, sub, kv0, kv_limit, lane);
+          tick(tr[1]);
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar);
+        } else if (a.tma && kv0 + KVB <= kv_limit) {
           // all 128 rows are keys: 8 pages x 2 halves = 16 tile copies, one a lane
           const int t = (lane >> 1) & 7;
           id = __shfl_sync(0xffffffffu, id, t);

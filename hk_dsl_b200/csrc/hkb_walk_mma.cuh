@@ -524,9 +524,9 @@ struct WalkMMAF8 {
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
     for (int s = 0; s < SPANS; ++s) {
-      st.koff[s] = tile_off_u32(g, 2 * s + (t >> 1)) + (t & 1) * 8;
-      st.voff[s][0] = tile_off_u32(2 * t, 2 * s + (g >> 2)) + (g & 3) * 4;
-      st.voff[s][1] = tile_off_u32(2 * t + 1, 2 * s + (g >> 2)) + (g & 3) * 4;
+      st.koff[s] = tile_off_f8<ROWB>(g, 2 * s + (t >> 1)) + (t & 1) * 8;
+      st.voff[s][0] = tile_off_f8<ROWB>(2 * t, 2 * s + (g >> 2)) + (g & 3) * 4;
+      st.voff[s][1] = tile_off_f8<ROWB>(2 * t + 1, 2 * s + (g >> 2)) + (g & 3) * 4;
     }
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -638,7 +638,7 @@ struct WalkMMAF8 {
     for (int x = lane; x < TILE_TOKENS * CPR; x += 32) {
       const int r = x / CPR, c = x % CPR;
       if (tok0 + r >= seq_len)
-        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(vtile + tile_off_u32(r, c)), "r"(0u) : "memory");
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(vtile + tile_off_f8<ROWB>(r, c)), "r"(0u) : "memory");
     }
   }
 

@@ -125,8 +125,6 @@ class HKAttentionImplCore:
             raise ValueError(f"{NAME}: {num_heads} query heads over {num_kv_heads} kv heads: the GQA group "
                              f"must be a whole number of at most {paged.Q_TILE}")
         validate_head_size(head_size)
-        if name.startswith("fp8") and head_size != 128:
-            raise NotImplementedError(f"{NAME} reads an fp8 cache at head_size 128 only, not {head_size}")
         self.num_heads = num_heads
         self.head_size = head_size
         self.scale = float(scale)

@@ -129,8 +129,6 @@ def _common_why_not(q, out, k, v, block_table, seq_lens, q_start, k_descale, v_d
         return why
     if q.dim() != 3 or q.shape[-1] not in paged.HEAD_DIMS:
         return f"head size {q.shape[-1]}"
-    if k.dtype in paged._FP8_DTYPES and q.shape[-1] != 128:
-        return f"fp8 cache at head size {q.shape[-1]} (128 only)"
     if k.dim() != 4:
         return f"cache {tuple(k.shape)}"
     why = page_why_not(int(k.shape[1]))

@@ -37,7 +37,7 @@ from ..runtime import lib as _lib
 KV_BLOCK = 16
 #: Most query rows (the GQA group) a kv head may have.
 Q_TILE = 16
-HEAD_DIMS = (64, 128, 256)       # head sizes the kernels take (fp8 caches: 128 only)
+HEAD_DIMS = (64, 128, 256)       # head sizes the kernels take, for 16-bit and fp8 caches alike
 DECODE_HEAD_DIMS = HEAD_DIMS
 MAX_SPLITS = _lib.MAX_SPLITS
 

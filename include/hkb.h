@@ -199,7 +199,7 @@ int hkb_merge(void* out, int64_t out_stride_tok, int64_t out_stride_head, int ou
  * hkb_prefill_tile_rows(num_q_heads, num_kv_heads) rows (the host builds it: query lengths
  * are host values in a prefill step; put long tiles first). Rows of requests that are not in
  * the work list are not written. bf16 caches, or fp8-e4m3 with per-tensor k_scale / v_scale
- * (device pointers to one float each; head_dim 128). num_tokens: the rows q and out hold
+ * (device pointers to one float each). num_tokens: the rows q and out hold
  * (q_start[last request + 1] at least): the tensor-memory kernel fetches query tiles with TMA and
  * must know where the tensor ends.
  *
@@ -360,8 +360,9 @@ size_t hkb_arrivals_bytes(int num_seqs, int num_kv_heads);
 int hkb_prefill_tile_rows(int num_q_heads, int num_kv_heads);
 
 /* 1 if hkb_paged_prefill runs its tcgen05 / tensor-memory kernel for this head size and cache
- * type (head_dim 128, bf16 or fp16), 0 if the mma.sync kernel (other head sizes, fp8 caches, or
- * HKB_PREFILL_MMA_SYNC=1 in the environment, the comparison arm). Like the reference, which picks
+ * type (head_dim 128: bf16, fp16, or fp8-e4m3 widened to f16 on its way into shared memory), 0 if
+ * the mma.sync kernel (other head sizes, or HKB_PREFILL_MMA_SYNC=1 in the environment, the
+ * comparison arm). Like the reference, which picks
  * its contraction form per architecture and shape (python/hk/ops/paged_prefill.py:59-120). */
 int hkb_prefill_uses_tcgen05(int head_dim, int kv_dtype);
 

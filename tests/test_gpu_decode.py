@@ -262,6 +262,22 @@ def test_fp8_cache_against_the_dequantised_oracle(group, splits):
     _check(_run(c, splits=splits), _reference(c))
 
 
+@pytest.mark.parametrize("head_dim", [64, 256])
+@pytest.mark.parametrize("group,h_kv", [(1, 2), (4, 2), (8, 1), (16, 1)])
+@pytest.mark.parametrize("splits", [1, 4, 32])
+def test_fp8_cache_at_head_sizes_64_and_256(head_dim, group, h_kv, splits):
+    """fp8 rows of 64 and 256 bytes: one split (the fixed grid, tiles widened in shared memory) and the
+    balanced stream (fragments built from the fp8 tile in its 32-byte-unit layout)."""
+    c = _case(LENS, head_dim=head_dim, h_kv=h_kv, group=group, fp8=True, seed=head_dim + group)
+    _check(_run(c, splits=splits), _reference(c))
+
+
+@pytest.mark.parametrize("head_dim", [64, 256])
+def test_fp8_pages_of_64_tokens_at_head_sizes_64_and_256(head_dim):
+    c = _case([1, 63, 65, 700, 2063], head_dim=head_dim, h_kv=2, group=4, page=64, fp8=True, seed=head_dim)
+    _check(_run(c, splits=8), _reference(c))
+
+
 # --------------------------------------------------------------------------- CUDA graphs
 
 @pytest.mark.parametrize("group", [4, 8])

@@ -136,12 +136,25 @@ def test_refusals():
     k8 = k.cuda().to(torch.float8_e4m3fn).transpose(1, 2)
     with pytest.raises(ValueError, match="k_scale"):          # an fp8 cache needs its scales
         paged.paged_prefill(out, q.cuda(), k8, k8, kv_cache_dtype="fp8", **kw)
-    q64, k64, _, _, _, _ = _case([(0, 40)], head_dim=64)
-    k64 = k64.cuda().to(torch.float8_e4m3fn).transpose(1, 2)
-    one = torch.ones(1, device="cuda")
-    with pytest.raises(HkbError, match="no kernel"):           # fp8 prefill is built for head_dim 128
-        paged.paged_prefill(torch.empty_like(q64).cuda(), q64.cuda(), k64, k64, kv_cache_dtype="fp8", k_scale=one,
-                            v_scale=one, **kw)
+
+
+@pytest.mark.parametrize("head_dim", [64, 256])
+@pytest.mark.parametrize("group", [1, 4, 8])
+def test_fp8_cache_at_head_sizes_64_and_256(head_dim, group):
+    from hk_dsl_b200.ops import paged
+
+    reqs = [(0, 300), (1000, 77), (33, 1), (64, 100)]
+    q, k, v, table, lens, q_start = _case(reqs, head_dim=head_dim, group=group, seed=40 + group)
+    ks, vs = torch.tensor([0.0125]), torch.tensor([0.011])
+    k8, v8 = orc.quantize_fp8(k, ks), orc.quantize_fp8(v, vs)
+    want = orc.paged_prefill_ref(q, orc.dequantize_fp8(k8, ks).transpose(1, 2), orc.dequantize_fp8(v8, vs).transpose(1, 2),
+                                 table, lens, q_start)
+    out = torch.full(q.shape, 7.0, device="cuda", dtype=torch.bfloat16)
+    work = paged.work_list([(r, n) for r, (_, n) in enumerate(reqs)], paged.prefill_tile_rows(q.shape[1], 2), "cuda")
+    paged.paged_prefill(out, q.cuda(), k8.cuda().transpose(1, 2), v8.cuda().transpose(1, 2), table.cuda(), lens.cuda(),
+                        q_start.cuda(), work, head_dim ** -0.5, "fp8", ks.cuda(), vs.cuda())
+    torch.cuda.synchronize()
+    orc.check(out, want)
 
 
 @pytest.mark.parametrize("group", [1, 4, 8])
@@ -163,6 +176,43 @@ def test_fp8_cache_against_the_dequantised_oracle(group):
     orc.check_baseline(out, want)
 
 
+@pytest.mark.parametrize("page", [16, 64])
+def test_fp8_cache_on_both_kernel_forms(page, monkeypatch):
+    """An fp8 cache on the tensor-memory kernel (the producers widen e4m3 to f16 on the way into the
+    ring) and on the mma.sync one: both within the oracle's bounds of the dequantised reference, and
+    within three bf16 ulps of each other; a long prompt, so the ring of slots laps, a cached prefix,
+    a chunk that ends inside a key block, and garbage past the end of the last page."""
+    from hk_dsl_b200.ops import paged
+    from hk_dsl_b200.runtime import lib as hkb
+
+    reqs = [(0, 1500), (700, 333), (129, 1)]
+    q, k, v, table, lens, q_start = _case(reqs, group=4, seed=31, page=page)
+    ks, vs = torch.tensor([0.02]), torch.tensor([0.015])
+    k8, v8 = orc.quantize_fp8(k, ks), orc.quantize_fp8(v, vs)
+    want = orc.paged_prefill_ref(q, orc.dequantize_fp8(k8, ks).transpose(1, 2), orc.dequantize_fp8(v8, vs).transpose(1, 2),
+                                 table, lens, q_start)
+    # bytes past each request's last token: 0x7f is NaN in e4m3
+    k8d, v8d = k8.cuda(), v8.cuda()
+    for r, (c, n) in enumerate(reqs):
+        last = c + n
+        blk, off = int(table[r, (last - 1) // page]), (last - 1) % page + 1
+        k8d.view(torch.uint8)[blk, :, off:] = 0x7f
+        v8d.view(torch.uint8)[blk, :, off:] = 0x7f
+    work = paged.work_list([(r, n) for r, (_, n) in enumerate(reqs)], paged.prefill_tile_rows(q.shape[1], 2), "cuda")
+    outs = []
+    for sync in ("0", "1"):
+        monkeypatch.setenv("HKB_PREFILL_MMA_SYNC", sync)
+        out = torch.full(q.shape, 7.0, device="cuda", dtype=torch.bfloat16)
+        paged.paged_prefill(out, q.cuda(), k8d.transpose(1, 2), v8d.transpose(1, 2), table.cuda(), lens.cuda(),
+                            q_start.cuda(), work, 128 ** -0.5, "fp8", ks.cuda(), vs.cuda())
+        torch.cuda.synchronize()
+        assert torch.isfinite(out.float()).all()
+        orc.check(out, want)
+        outs.append(out)
+    assert orc.ulps(outs[0], outs[1].float()) <= 3.0
+    assert hkb.load().hkb_prefill_tc_error(0) == 0
+
+
 def test_which_kernel_runs_and_that_no_wait_ran_out(monkeypatch):
     """head_dim 128 on a 16-bit cache runs the tcgen05 / tensor-memory kernel, everything else (and
     HKB_PREFILL_MMA_SYNC=1) the mma.sync one; both give the oracle's answer on the same inputs and
@@ -173,7 +223,8 @@ def test_which_kernel_runs_and_that_no_wait_ran_out(monkeypatch):
     lib = hkb.load()
     monkeypatch.delenv("HKB_PREFILL_MMA_SYNC", raising=False)
     assert lib.hkb_prefill_uses_tcgen05(128, hkb.KV_BF16) == 1 and lib.hkb_prefill_uses_tcgen05(128, hkb.KV_F16) == 1
-    assert lib.hkb_prefill_uses_tcgen05(128, hkb.KV_FP8_E4M3) == 0 and lib.hkb_prefill_uses_tcgen05(64, hkb.KV_BF16) == 0
+    assert lib.hkb_prefill_uses_tcgen05(128, hkb.KV_FP8_E4M3) == 1 and lib.hkb_prefill_uses_tcgen05(64, hkb.KV_BF16) == 0
+    assert lib.hkb_prefill_uses_tcgen05(256, hkb.KV_F16) == 0
     reqs = [(0, 700), (900, 300), (17, 1), (2048, 130)]
     new, want, _ = _run(reqs, h_kv=2, group=4, seed=11)
     orc.check(new, want)

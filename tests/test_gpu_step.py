@@ -123,6 +123,20 @@ def test_one_launch_equals_the_separate_launches(splits, group, h_kv, fp8):
         _check(o2.cpu(), _want(c))
 
 
+@pytest.mark.parametrize("head_dim", [64, 256])
+@pytest.mark.parametrize("group,h_kv", [(4, 2), (8, 1)])
+def test_fp8_step_at_head_sizes_64_and_256(head_dim, group, h_kv):
+    """The step's quantised cache write inside the walk, and its answer, at fp8 rows of 64 and 256 bytes."""
+    c = _step_case(LENS, seed=head_dim + group, head_dim=head_dim, h_kv=h_kv, group=group, fp8=True)
+    g = _cuda(c)
+    o1, k1, v1 = _separate(g, c, 4)
+    assert torch.equal(_bits(k1), _bits(g["k_want"])) and torch.equal(_bits(v1), _bits(g["v_want"]))
+    o2, k2, v2 = _joined(g, c, 4, fold=False)
+    assert torch.equal(_bits(k2), _bits(g["k_want"])) and torch.equal(_bits(v2), _bits(g["v_want"]))
+    assert torch.equal(o1.view(torch.int16), o2.view(torch.int16))
+    _check(o2.cpu(), _want(c))
+
+
 @pytest.mark.parametrize("splits", [64, 256])
 @pytest.mark.parametrize("group,h_kv", [(4, 2), (8, 1)])
 def test_many_pieces_fold_as_a_tree(splits, group, h_kv):
