@@ -72,7 +72,9 @@ struct Bars {                                  // mbarriers, 8 bytes each
   uint32_t tmem_base;
   int abort;
 };
-constexpr int EPI_BYTES = SOFTMAX_WARPS * 4096;   // the epilogue's staging: 32 half rows of 128 bytes a softmax warp
+constexpr int EPI_BYTES = SOFTMAX_WARPS * 4096;   // the epilogue's staging: 32 half rows of 128 bytes a softmax warp (fp8 caches:
+                                                  // 32 quarter rows of 64 bytes; the other 16 KB stage the producers' fp8 tiles)
+constexpr int FP8_STAGE_TILES = 4;                // 16-token fp8 tiles (2 KB) a producer keeps in flight
 constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + 2 * Q_BYTES + NSLOT * SLOT_BYTES + EPI_BYTES + 1024 /*Bars*/;
 static_assert(sizeof(Bars) <= 1024, "barrier block");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory of one SM");
@@ -308,68 +310,19 @@ __device__ __forceinline__ void fill_half(const Args& a, uint32_t slot, const ui
   }
 }
 
-// A 128-token block of an fp8-e4m3 cache into a ring slot as f16, by one producer warp: the bytes are
-// loaded into registers (a lane a 16-byte chunk = 16 dims, a row 8 lanes), converted exactly
-// (cvt.rn.f16x2.e4m3x2; the per-tensor scale is applied to the scores and to the output, not here)
-// and stored where the 16-bit path's copies would have landed.
-// Rows at or past `kv_limit` are zeros, never read.
+// fp8-e4m3 caches: a producer warp brings its blocks 16 tokens (a 2 KB tile) at a time -- cp.async into
+// a small staging ring of its own (FP8_STAGE_TILES tiles: three in flight while one is converted),
+// then shared memory -> registers -> f16 (cvt.rn.f16x2.e4m3x2, exact; the per-tensor scale is applied to
+// the scores and to the output, not here) -> the ring slot, where the 16-bit path's copies would have
+// landed. A lane owns a 16-byte chunk (16 dims) of four rows of every tile and reads back only what it
+// copied itself, so the staging needs no barrier. Rows at or past the keys' end are zeros, never read.
+// (Loading into registers instead, with the conversion unrolled over several tiles to keep loads in
+// flight, was measured first: 250-490 TFLOP/s, slower the larger the unrolled code -- the producers
+// share an instruction cache with the softmax warps' long unrolled loops.)
 __device__ __forceinline__ uint32_t fp8x2_to_f16x2(uint32_t two_bytes) {
   uint32_t h2;
   asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(h2) : "h"((uint16_t)two_bytes));
   return h2;
-}
-struct Fp8Rows { uint4 v[4]; };   // this lane's four rows (rl, rl + 4, rl + 8, rl + 12) of a 16-token tile
-__device__ __forceinline__ void fp8_tile_load(Fp8Rows& x, const Args& a, const uint8_t* base, int64_t sb, int64_t st,
-                                              int id8, int sub8, int t, int rows_live, int64_t lane_off, int rl) {
-  const int id = min(max(__shfl_sync(0xffffffffu, id8, t), 0), a.num_blocks - 1), sub = __shfl_sync(0xffffffffu, sub8, t);
-  const uint8_t* tp = base + (int64_t)id * sb + (int64_t)(sub * TILE_TOKENS) * st + lane_off;
-#pragma unroll
-  for (int y = 0; y < 4; ++y) {
-    x.v[y] = make_uint4(0u, 0u, 0u, 0u);
-    if (t * TILE_TOKENS + 4 * y + rl < rows_live) x.v[y] = ldg_stream16(tp + (int64_t)(4 * y) * st);
-  }
-}
-__device__ __forceinline__ void fp8_tile_store(const Fp8Rows& x, uint32_t dst, uint32_t xa0, uint32_t xa1, uint32_t xb0,
-                                               uint32_t xb1) {
-#pragma unroll
-  for (int y = 0; y < 4; ++y) {
-    const uint32_t w[4] = {x.v[y].x, x.v[y].y, x.v[y].z, x.v[y].w};
-    uint32_t h[8];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { h[2 * i] = fp8x2_to_f16x2(w[i]); h[2 * i + 1] = fp8x2_to_f16x2(w[i] >> 16); }
-    const uint32_t row = dst + (uint32_t)(4 * y) * 128;
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(row + ((y & 1) ? xb0 : xa0)), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(row + ((y & 1) ? xb1 : xa1)), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
-  }
-}
-__device__ __forceinline__ void fill_block_fp8(const Args& a, uint32_t slot, const uint8_t* base, int64_t sb, int64_t st,
-                                               int id8, int sub8, int kv0, int kv_limit, int lane) {
-  const int g = lane & 7, rl = lane >> 3;            // this lane's chunk of a row, and its row of four
-  const int c0 = 2 * (g & 3);                        // the first of the two 16-byte f16 chunks its 16 dims become
-  const uint32_t dst0 = slot + (uint32_t)(g >> 2) * HALF_BYTES_KV + (uint32_t)rl * 128;
-  // rows rl, rl + 4, rl + 8, ...: r & 7 is rl or rl + 4, so the two chunks' places inside a row take two values each
-  const uint32_t xa0 = (uint32_t)((c0 ^ rl) << 4), xa1 = (uint32_t)(((c0 + 1) ^ rl) << 4);
-  const uint32_t xb0 = (uint32_t)((c0 ^ (rl + 4)) << 4), xb1 = (uint32_t)(((c0 + 1) ^ (rl + 4)) << 4);
-  const int64_t lane_off = (int64_t)rl * st + g * 16;
-  const int rows_live = kv_limit - kv0;              // rows of the block that are keys
-  // three tiles' loads in flight while a fourth is converted (a trip to L2 is ~1000 clocks here, a tile's
-  // conversion ~200)
-  constexpr int NT = KVB / TILE_TOKENS;
-  Fp8Rows r0, r1, r2, r3;
-  fp8_tile_load(r0, a, base, sb, st, id8, sub8, 0, rows_live, lane_off, rl);
-  fp8_tile_load(r1, a, base, sb, st, id8, sub8, 1, rows_live, lane_off, rl);
-  fp8_tile_load(r2, a, base, sb, st, id8, sub8, 2, rows_live, lane_off, rl);
-#pragma unroll 1
-  for (int t = 0; t < NT; t += 4) {
-    fp8_tile_load(r3, a, base, sb, st, id8, sub8, t + 3, rows_live, lane_off, rl);
-    fp8_tile_store(r0, dst0 + (uint32_t)(t * TILE_TOKENS) * 128, xa0, xa1, xb0, xb1);
-    if (t + 4 < NT) fp8_tile_load(r0, a, base, sb, st, id8, sub8, t + 4, rows_live, lane_off, rl);
-    fp8_tile_store(r1, dst0 + (uint32_t)((t + 1) * TILE_TOKENS) * 128, xa0, xa1, xb0, xb1);
-    if (t + 4 < NT) fp8_tile_load(r1, a, base, sb, st, id8, sub8, t + 5, rows_live, lane_off, rl);
-    fp8_tile_store(r2, dst0 + (uint32_t)((t + 2) * TILE_TOKENS) * 128, xa0, xa1, xb0, xb1);
-    if (t + 4 < NT) fp8_tile_load(r2, a, base, sb, st, id8, sub8, t + 6, rows_live, lane_off, rl);
-    fp8_tile_store(r3, dst0 + (uint32_t)((t + 3) * TILE_TOKENS) * 128, xa0, xa1, xb0, xb1);
-  }
 }
 
 // One half (64 columns) of a score row: causal mask, then either the maximum (MATH = 0) or the
@@ -647,18 +600,21 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
       blocks += nb;
       tc_fence_after();
       const float inv = (l > 0.f ? 1.f / l : 0.f) * out_scale;
-      // Each thread parks half of its output row (64 dims, 128 bytes; 16-byte chunks XOR-ed by the row so
-      // that the 32 rows of a warp do not collide on banks) in the warp's staging rows, then the warp --
-      // which owns exactly these 32 rows -- writes them out four half rows an instruction; then the
-      // other half. The accumulator is free for the next item as soon as the second half has been
-      // read: the first P of that item is handed over after this, by these same threads.
-      const uint32_t stage = epi + (uint32_t)warp * 4096u;
+      // Each thread parks part of its output row (64 dims = 128 bytes; 32 dims in the fp8 build, whose
+      // producers use half of the staging space; 16-byte chunks XOR-ed by the row so that the 32 rows of
+      // a warp do not collide on banks) in the warp's staging rows, then the warp -- which owns exactly
+      // these 32 rows -- writes them out 512 bytes an instruction; then the next part. The accumulator
+      // is free for the next item as soon as its last part has been read: the first P of that item is
+      // handed over after this, by these same threads.
+      constexpr int PASS_DIMS = FP8 ? 32 : 64, ROWE = PASS_DIMS * 2, CPRE = ROWE / 16;   // dims, bytes, 16-byte chunks of a staged row
+      const uint32_t stage = epi + (uint32_t)warp * (32u * ROWE);
+      const int wswz = CPRE == 8 ? (lane & 7) : ((lane >> 1) & 3);     // a 64-byte row: two rows share a 128-byte bank line
 #pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
+      for (int pass = 0; pass < D / PASS_DIMS; ++pass) {
 #pragma unroll
-        for (int c32 = 0; c32 < 2; ++c32) {
+        for (int c32 = 0; c32 < PASS_DIMS / 32; ++c32) {
           float o[32];
-          tmem_ld32(lane_addr + o_col(g) + half * 64 + c32 * 32, o);
+          tmem_ld32(lane_addr + o_col(g) + pass * PASS_DIMS + c32 * 32, o);
           uint32_t w[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -667,21 +623,22 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
           }
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
-            const int chunk = c32 * 4 + q4;                     // 16-byte chunk of the half row
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(stage + lane * 128 + ((chunk ^ (lane & 7)) << 4)),
+            const int chunk = c32 * 4 + q4;                     // 16-byte chunk of the staged row
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(stage + lane * ROWE + ((chunk ^ wswz) << 4)),
                          "r"(w[4 * q4]), "r"(w[4 * q4 + 1]), "r"(w[4 * q4 + 2]), "r"(w[4 * q4 + 3]) : "memory");
           }
         }
         __syncwarp();
 #pragma unroll 4
-        for (int x8 = 0; x8 < 8; ++x8) {
-          const int rr = x8 * 4 + (lane >> 3), chunk = lane & 7;        // row of the warp, chunk of the half row
+        for (int x = 0; x < CPRE; ++x) {
+          const int rr = x * (32 / CPRE) + lane / CPRE, chunk = lane % CPRE;        // row of the warp, chunk of the staged row
           const int r_tile = (warp & 3) * 32 + rr;
           const int tk = row0 + g * T + r_tile % T;
-          const uint4 v = lds128(stage + rr * 128 + ((chunk ^ (rr & 7)) << 4));
+          const int rswz = CPRE == 8 ? (rr & 7) : ((rr >> 1) & 3);
+          const uint4 v = lds128(stage + rr * ROWE + ((chunk ^ rswz) << 4));
           if (tk < q_len) {
             __nv_bfloat16* dst = a.out + (int64_t)(q0 + tk) * a.out_stride_tok + (int64_t)(hbase + r_tile / T) * a.out_stride_head +
-                                 half * 64 + chunk * 8;
+                                 pass * PASS_DIMS + chunk * 8;
             if (out16) *reinterpret_cast<uint4*>(dst) = v;
             else {
               uint32_t* d32 = reinterpret_cast<uint32_t*>(dst);
@@ -842,6 +799,74 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
         }
         if (!ok) break;
       }
+      if constexpr (FP8) {
+        // the item's tiles as one stream: tile x = block x / 8, 16-token tile x % 8
+        constexpr int TPB = KVB / TILE_TOKENS;
+        const uint32_t stg = epi + EPI_BYTES / 2 + (uint32_t)which * (FP8_STAGE_TILES * 2048u);
+        const int g = lane & 7, rl = lane >> 3;            // this lane's chunk of a row, and its row of four
+        const int c0 = 2 * (g & 3);                        // the first of the two 16-byte f16 chunks its 16 dims become
+        const uint32_t lane_stg = (uint32_t)rl * 128 + g * 16;
+        const uint32_t lane_dst = (uint32_t)(g >> 2) * HALF_BYTES_KV + (uint32_t)rl * 128;
+        // rows rl, rl + 4, rl + 8, ...: r & 7 is rl or rl + 4, so the two chunks' places inside a row take two values each
+        const uint32_t xa0 = (uint32_t)((c0 ^ rl) << 4), xa1 = (uint32_t)(((c0 + 1) ^ rl) << 4);
+        const uint32_t xb0 = (uint32_t)((c0 ^ (rl + 4)) << 4), xb1 = (uint32_t)(((c0 + 1) ^ (rl + 4)) << 4);
+        const int64_t lane_off = (int64_t)rl * st + g * 16;
+        const int tiles = n * TPB;
+        int id_cur = next_id, sub_cur = next_sub, blk_cur = 0;    // lanes 0..7: the page ids of block blk_cur, and of the one after
+        page_ids(KVB, next_id, next_sub);
+        auto issue = [&](int x) {
+          const int jb = x / TPB, t = x % TPB;
+          if (jb != blk_cur) { id_cur = next_id; sub_cur = next_sub; blk_cur = jb; page_ids((jb + 1) * KVB, next_id, next_sub); }
+          const int id = min(max(__shfl_sync(0xffffffffu, id_cur, t), 0), a.num_blocks - 1), sub = __shfl_sync(0xffffffffu, sub_cur, t);
+          const uint8_t* tp = src + (int64_t)id * sb + (int64_t)(sub * TILE_TOKENS) * st + lane_off;
+          const uint32_t buf = stg + (uint32_t)(x % FP8_STAGE_TILES) * 2048u + lane_stg;
+#pragma unroll
+          for (int y = 0; y < 4; ++y) {
+            if (x * TILE_TOKENS + 4 * y + rl < kv_limit) cp_async16(buf + y * 512, tp + (int64_t)(4 * y) * st);
+            else asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(buf + y * 512), "r"(0u) : "memory");
+          }
+        };
+        for (int x = 0; x < FP8_STAGE_TILES - 1; ++x) { issue(x); cp_async_commit(); }     // an item has at least eight tiles
+        uint32_t slot_addr = 0, bar = 0;
+#pragma unroll 1
+        for (int x = 0; x < tiles && ok; ++x) {
+          Lap<TRACE> tick;
+          if (x + FP8_STAGE_TILES - 1 < tiles) issue(x + FP8_STAGE_TILES - 1);
+          cp_async_commit();                               // a group a tile (empty ones at the end): tile x is the fourth newest
+          cp_async_wait<FP8_STAGE_TILES - 1>();
+          const int t = x % TPB;
+          if (t == 0) {
+            const int slot = 2 * (cnt & 1) + which, lap = cnt >> 1;
+            slot_addr = ring + slot * SLOT_BYTES; bar = HKB_BAR(full) + 8 * slot;
+            tick(tr[1]);
+            if (lap > 0) ok = warp_wait(HKB_BAR(empty) + 8 * slot, (lap - 1) & 1, abort, 7);
+            if (!ok) break;
+            tick(tr[0]);
+          }
+          const uint32_t buf = stg + (uint32_t)(x % FP8_STAGE_TILES) * 2048u + lane_stg;
+          const uint32_t dst = slot_addr + lane_dst + (uint32_t)(t * TILE_TOKENS) * 128;
+          uint4 v4[4];      // the four rows' loads first (they keep their order among themselves, as do the stores)
+#pragma unroll
+          for (int y = 0; y < 4; ++y) v4[y] = lds128(buf + y * 512);
+#pragma unroll
+          for (int y = 0; y < 4; ++y) {
+            const uint32_t w[4] = {v4[y].x, v4[y].y, v4[y].z, v4[y].w};
+            uint32_t h[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { h[2 * i] = fp8x2_to_f16x2(w[i]); h[2 * i + 1] = fp8x2_to_f16x2(w[i] >> 16); }
+            const uint32_t row = dst + (uint32_t)(4 * y) * 128;
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(row + ((y & 1) ? xb0 : xa0)), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(row + ((y & 1) ? xb1 : xa1)), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
+          }
+          if (t == TPB - 1) {
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar);
+            ++cnt;
+          }
+          tick(tr[1]);
+        }
+      } else
       for (int j = 0; j < n && ok; ++j, ++cnt) {
         const int slot = 2 * (cnt & 1) + which, lap = cnt >> 1;
         const uint32_t slot_addr = ring + slot * SLOT_BYTES, bar = HKB_BAR(full) + 8 * slot;
@@ -852,13 +877,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
         if (lap > 0) ok = warp_wait(HKB_BAR(empty) + 8 * slot, (lap - 1) & 1, abort, 7);
         if (!ok) break;
         tick(tr[0]);
-        if (FP8) {
-          fill_block_fp8(a, slot_addr, src, sb, st, id, sub, kv0, kv_limit, lane);
-          tick(tr[1]);
-          fence_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar);
-        } else if (a.tma && kv0 + KVB <= kv_limit) {
+        if (a.tma && kv0 + KVB <= kv_limit) {
           // all 128 rows are keys: 8 pages x 2 halves = 16 tile copies, one a lane
           const int t = (lane >> 1) & 7;
           id = __shfl_sync(0xffffffffu, id, t);
