@@ -136,7 +136,7 @@ def latency_table():
     return 0
 
 
-def prefill_table(only: str = ""):
+def prefill_table(only: str = "", kv: str = "bf16"):
     """Paged prefill on 32 q / 8 kv heads, head_dim 128: causal flops = 4 * q_heads * head_dim *
     sum over query rows of the keys they see; timed with CUDA events, median of 7; against the
     measured bf16 tensor peak. `only` = "RxCTX+QLEN" (e.g. "1x0+8192") runs that one bf16 shape."""
@@ -159,7 +159,7 @@ def prefill_table(only: str = ""):
     if only:
         reps, _, rest = only.partition("x")
         ctx, _, qlen = rest.partition("+")
-        cases = [([(int(ctx), int(qlen))] * int(reps), "bf16")]
+        cases = [([(int(ctx), int(qlen))] * int(reps), kv)]
     for reqs, kind in cases:
         seq = [c + n for c, n in reqs]
         pages = [-(-s // bs) for s in seq]
@@ -205,7 +205,7 @@ def prefill_table(only: str = ""):
         flops = 4.0 * hq * d * keys_seen
         rows.append({"requests": len(reqs), "context": reqs[0][0], "q_len": reqs[0][1], "cache": kind, "ms": round(ms, 3),
                      "tflops": round(flops / ms / 1e9, 1), "frac_of_measured_bf16_peak": round(flops / ms / 1e9 / peak, 3)})
-    print(json.dumps({"table": "paged prefill, 32q/8kv heads, D128, block 16", "kernel": "mma.sync" if os.environ.get("HKB_PREFILL_MMA_SYNC") == "1" else "tcgen05 + TMEM for 16-bit caches, mma.sync for fp8", "peak_tflops": peak,
+    print(json.dumps({"table": "paged prefill, 32q/8kv heads, D128, block 16", "kernel": "mma.sync" if os.environ.get("HKB_PREFILL_MMA_SYNC") == "1" else "tcgen05 + TMEM", "peak_tflops": peak,
                       "rows": rows}), flush=True)
     return 0
 
@@ -521,7 +521,7 @@ def main():
                                                "x-split (a small case for a profiler)")
     ap.add_argument("--prefill-trace", action="store_true", help="cycles by role and phase of the tensor-memory prefill kernel")
     ap.add_argument("--attrib", action="store_true", help="the decode walk with one stage left out: what each stage costs")
-    ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8"], help="with --prefill-trace: the cache type")
+    ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8"], help="with --prefill-trace, or --prefill --case: the cache type")
     ap.add_argument("--shards", action="store_true", help="one rank's share of c2 over 1/2/4/8 GPUs, on one GPU: the step's fixed costs")
     ap.add_argument("--layouts", action="store_true", help="the decode over the usual and the x-split cache layout")
     args = ap.parse_args()
@@ -534,7 +534,7 @@ def main():
     if args.prefill_trace:
         return prefill_trace(args.case, args.kv == "fp8")
     if args.prefill:
-        return prefill_table(args.case)
+        return prefill_table(args.case, args.kv)
     return latency_table()
 
 

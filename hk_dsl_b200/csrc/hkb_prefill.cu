@@ -467,7 +467,7 @@ static int launch_prefill_tc(const tc::Args& a, const CUtensorMap& kmap, const C
     int sms = hkb_sm_count(-1);
     if (sms <= 0) sms = 148;
     dim3 grid((unsigned)(total < sms ? total : sms));
-    tc::prefill_tc_kernel<GP, F16, TRACE, FP8><<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(a, kmap, vmap, qmap);
+    tc::prefill_tc_kernel<GP, F16, TRACE, FP8><<<grid, tc::threads_of(FP8), tc::SMEM_BYTES, st>>>(a, kmap, vmap, qmap);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) { hkb_tls_cuda_error = (int)e; return HKB_ERR_CUDA; }

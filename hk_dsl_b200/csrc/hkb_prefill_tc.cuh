@@ -61,6 +61,12 @@ constexpr int SLOT_BYTES = 2 * HALF_BYTES_KV; // a K or a V block: 32 KB
 constexpr int NSLOT = 4;                      // ring slots: K blocks in the even ones, V blocks in the odd ones
 constexpr int SOFTMAX_WARPS = 8, MMA_WARP = 8, K_WARP = 9, V_WARP = 10, WARPS = 11;
 constexpr int THREADS = WARPS * 32;
+// fp8 caches: of a block's eight 16-token tiles the kind's own producer warp widens the first FP8_MAIN; below 8
+// a third producer warp takes the rest of both kinds. Measured at 8 x 2048: two warps (8) 544-548 TFLOP/s,
+// three (6 + 2) 511, four (two a kind, 13 warps: the CTA is rounded up to 16 warps of 128 registers and the
+// softmax warps spill) 516 -- the widening does not get faster with more warps, so two it is.
+constexpr int FP8_MAIN = 8;
+__host__ __device__ constexpr int threads_of(bool fp8) { return fp8 && FP8_MAIN < 8 ? THREADS + 32 : THREADS; }
 constexpr int TMEM_COLS = 512;
 // TMEM columns: O of tile 0 and 1, then the scores of tile 0 and 1 (P is written over the scores)
 __host__ __device__ constexpr int o_col(int tile) { return tile * 128; }
@@ -73,8 +79,9 @@ struct Bars {                                  // mbarriers, 8 bytes each
   int abort;
 };
 constexpr int EPI_BYTES = SOFTMAX_WARPS * 4096;   // the epilogue's staging: 32 half rows of 128 bytes a softmax warp (fp8 caches:
-                                                  // 32 quarter rows of 64 bytes; the other 16 KB stage the producers' fp8 tiles)
-constexpr int FP8_STAGE_TILES = 4;                // 16-token fp8 tiles (2 KB) a producer keeps in flight
+                                                  // the producers' staging rings instead, 8 KB each)
+constexpr int FP8_STAGE_TILES = 8;                // 16-token fp8 tiles (2 KB) in a producer's staging ring: seven in flight, one being widened
+static_assert((FP8_MAIN < 8 ? 3 : 2) * FP8_STAGE_TILES * 2048 <= EPI_BYTES, "the producers' staging rings live in the epilogue's space");
 constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + 2 * Q_BYTES + NSLOT * SLOT_BYTES + EPI_BYTES + 1024 /*Bars*/;
 static_assert(sizeof(Bars) <= 1024, "barrier block");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory of one SM");
@@ -120,11 +127,16 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 }
 // Wait for the phase of `parity` to complete; gives up (and raises the CTA's abort flag) after
 // about 2^31 clocks, or as soon as another thread of the CTA has given up.
+// NAP: sleep ~64 ns between polls. A polling warp takes issue slots from the warps of its scheduler; where
+// the waits are long and another role is short of issue slots (fp8 caches: the producers' conversion), the
+// waiters step aside.
+template <bool NAP = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort, int code) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = now();
   while (true) {
     if (mbar_try(bar, parity)) return true;
+    if (NAP) __nanosleep(64);
     if (*abort) return false;
     if (now() - t0 > (1ll << 31)) {
       *abort = code;
@@ -135,8 +147,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 // The same for a whole warp: every lane polls, and all lanes take the same way out (the TMEM loads
 // and stores that follow are warp-collective).
+template <bool NAP = false>
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort, int code) {
-  const bool ok = mbar_wait(bar, parity, abort, code);
+  const bool ok = mbar_wait<NAP>(bar, parity, abort, code);
   return __all_sync(0xffffffffu, ok);
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
@@ -311,14 +324,15 @@ __device__ __forceinline__ void fill_half(const Args& a, uint32_t slot, const ui
 }
 
 // fp8-e4m3 caches: a producer warp brings its blocks 16 tokens (a 2 KB tile) at a time -- cp.async into
-// a small staging ring of its own (FP8_STAGE_TILES tiles: three in flight while one is converted),
+// a staging ring of its own (FP8_STAGE_TILES tiles: all but one in flight while that one is converted),
 // then shared memory -> registers -> f16 (cvt.rn.f16x2.e4m3x2, exact; the per-tensor scale is applied to
 // the scores and to the output, not here) -> the ring slot, where the 16-bit path's copies would have
 // landed. A lane owns a 16-byte chunk (16 dims) of four rows of every tile and reads back only what it
 // copied itself, so the staging needs no barrier. Rows at or past the keys' end are zeros, never read.
-// (Loading into registers instead, with the conversion unrolled over several tiles to keep loads in
-// flight, was measured first: 250-490 TFLOP/s, slower the larger the unrolled code -- the producers
-// share an instruction cache with the softmax warps' long unrolled loops.)
+// (Measured on the way, TFLOP/s at 8 x 2048: loading into registers instead of staging, with the
+// conversion unrolled over several tiles to keep loads in flight, 250-490; widening by byte permutes,
+// shifts and one packed multiply by 2^8 instead of the convert instruction -- 5 instructions a pair of
+// values against 2 -- 426 against 548: the producers are bound by the instructions they issue.)
 __device__ __forceinline__ uint32_t fp8x2_to_f16x2(uint32_t two_bytes) {
   uint32_t h2;
   asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(h2) : "h"((uint16_t)two_bytes));
@@ -400,7 +414,7 @@ struct Item {
 // producers convert them to f16 on their way into the ring, the query rows (bf16) are converted to f16
 // as they are staged, so F16 is set; the output stays bf16 and carries v_scale, the scores carry k_scale.
 template <int GP, bool F16, bool TRACE = false, bool FP8 = false>
-__global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kmap,
+__global__ void __launch_bounds__(threads_of(FP8), 1) prefill_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kmap,
                                                                 const __grid_constant__ CUtensorMap vmap,
                                                                 const __grid_constant__ CUtensorMap qmap) {
   extern __shared__ uint8_t raw_smem[];
@@ -452,7 +466,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
 
   // ---- set-up: barriers and TMEM ----
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NSLOT; ++i) { mbar_init(HKB_BAR(full) + 8 * i, 1); mbar_init(HKB_BAR(empty) + 8 * i, 1); }
+    for (int i = 0; i < NSLOT; ++i) { mbar_init(HKB_BAR(full) + 8 * i, FP8 && FP8_MAIN < 8 ? 2 : 1); mbar_init(HKB_BAR(empty) + 8 * i, 1); }   // (fp8 with a third producer: a slot is filled by two warps)
     for (int i = 0; i < 2; ++i) {
       mbar_init(HKB_BAR(s_full) + 8 * i, 1); mbar_init(HKB_BAR(p_full) + 8 * i, ROWS);
       mbar_init(HKB_BAR(o_done) + 8 * i, 1); mbar_init(HKB_BAR(q_full) + 8 * i, a.tma ? 1 : ROWS);
@@ -501,7 +515,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
         // No tensor map for the queries: this tile's warps stage its rows themselves -- row r is head
         // r / T, token r % T of the tile -- once the products of the item before have read the old ones.
         if (items > 0) {
-          ok = warp_wait(HKB_BAR(q_empty) + 8 * g, (items - 1) & 1, abort, 9);
+          ok = warp_wait<FP8>(HKB_BAR(q_empty) + 8 * g, (items - 1) & 1, abort, 9);
           if (!ok) break;
         }
         uint4 qv[16];
@@ -537,7 +551,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
       const int nb = it.nblk(g);
       for (int j = 0; j < nb && ok; ++j) {
         Lap<TRACE> lap;
-        ok = warp_wait(HKB_BAR(s_full) + 8 * g, (blocks + j) & 1, abort, 1);
+        ok = warp_wait<FP8>(HKB_BAR(s_full) + 8 * g, (blocks + j) & 1, abort, 1);
         if (!ok) break;
         lap(tr[0]);
         tc_fence_after();
@@ -570,7 +584,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
         lap(tr[2]);
         if (j > 0) {
           // the tile's previous product has landed: O may be touched, and stays untouched until P arrives
-          ok = warp_wait(HKB_BAR(o_done) + 8 * g, (blocks + j - 1) & 1, abort, 2);
+          ok = warp_wait<FP8>(HKB_BAR(o_done) + 8 * g, (blocks + j - 1) & 1, abort, 2);
           if (!ok) break;
           tc_fence_after();
           if (any_need) {
@@ -595,19 +609,20 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
       }
       if (!ok) break;
       Lap<TRACE> lap_end;
-      ok = warp_wait(HKB_BAR(o_done) + 8 * g, (blocks + nb - 1) & 1, abort, 3);
+      ok = warp_wait<FP8>(HKB_BAR(o_done) + 8 * g, (blocks + nb - 1) & 1, abort, 3);
       if (!ok) break;
       blocks += nb;
       tc_fence_after();
       const float inv = (l > 0.f ? 1.f / l : 0.f) * out_scale;
-      // Each thread parks part of its output row (64 dims = 128 bytes; 32 dims in the fp8 build, whose
-      // producers use half of the staging space; 16-byte chunks XOR-ed by the row so that the 32 rows of
-      // a warp do not collide on banks) in the warp's staging rows, then the warp -- which owns exactly
+      // Each thread parks half of its output row (64 dims = 128 bytes; 16-byte chunks XOR-ed by the row so
+      // that the 32 rows of a warp do not collide on banks) in the warp's staging rows, then the warp -- which owns exactly
       // these 32 rows -- writes them out 512 bytes an instruction; then the next part. The accumulator
       // is free for the next item as soon as its last part has been read: the first P of that item is
       // handed over after this, by these same threads.
-      constexpr int PASS_DIMS = FP8 ? 32 : 64, ROWE = PASS_DIMS * 2, CPRE = ROWE / 16;   // dims, bytes, 16-byte chunks of a staged row
-      const uint32_t stage = epi + (uint32_t)warp * (32u * ROWE);
+      constexpr int PASS_DIMS = 64, ROWE = PASS_DIMS * 2, CPRE = ROWE / 16;   // dims, bytes, 16-byte chunks of a staged row
+      // (fp8 caches: the staging space belongs to the producers; the tile's own query rows are dead by now -- every
+      // product that read them has landed -- and these same warps stage the next item's after this)
+      const uint32_t stage = FP8 ? q_smem + g * Q_BYTES + (uint32_t)(warp & 3) * (32u * ROWE) : epi + (uint32_t)warp * (32u * ROWE);
       const int wswz = CPRE == 8 ? (lane & 7) : ((lane >> 1) & 3);     // a 64-byte row: two rows share a 128-byte bank line
 #pragma unroll 1
       for (int pass = 0; pass < D / PASS_DIMS; ++pass) {
@@ -675,7 +690,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
       if (last) tc_commit(HKB_BAR(q_empty) + 8 * t);
     };
     auto wait_block = [&](int kind, int c, int code) {     // block c of K (kind 0) or V (kind 1) has landed
-      ok = warp_wait(HKB_BAR(full) + 8 * slot_of(kind, c), (c >> 1) & 1, abort, code);
+      ok = warp_wait<FP8>(HKB_BAR(full) + 8 * slot_of(kind, c), (c >> 1) & 1, abort, code);
       tc_fence_after();
     };
     Item nxt;
@@ -688,8 +703,8 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
       const int n = it.n;
       Lap<TRACE> lap;
       // the tiles' query rows are in place
-      if (it.nblk0 > 0) ok = warp_wait(HKB_BAR(q_full), items0 & 1, abort, 8);
-      if (ok && it.nblk1 > 0) ok = warp_wait(HKB_BAR(q_full) + 8, items1 & 1, abort, 8);
+      if (it.nblk0 > 0) ok = warp_wait<FP8>(HKB_BAR(q_full), items0 & 1, abort, 8);
+      if (ok && it.nblk1 > 0) ok = warp_wait<FP8>(HKB_BAR(q_full) + 8, items1 & 1, abort, 8);
       if (!ok) break;
       lap(tr[0]);
       wait_block(0, kcnt, 4);
@@ -716,7 +731,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
           if (!ok || j >= it.nblk(t)) continue;
           // P of the block; for an item's first block this also says the tile's warps have read the
           // accumulator of the item before out of TMEM (they arrive here after their epilogue)
-          ok = warp_wait(HKB_BAR(p_full) + 8 * t, ((t ? blocks1 : blocks0) + j) & 1, abort, 6);
+          ok = warp_wait<FP8>(HKB_BAR(p_full) + 8 * t, ((t ? blocks1 : blocks0) + j) & 1, abort, 6);
           if (!ok) continue;
           lap(tr[t ? 6 : 4]);
           tc_fence_after();
@@ -747,7 +762,8 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
       for (int i = 0; i < 8; ++i) a.trace[(size_t)cta * 32 + 16 + i] = tr[i];
   } else {
     // ================= producers: warp K_WARP brings the K blocks, warp V_WARP the V blocks =================
-    const int which = warp - K_WARP;   // 0: K, 1: V
+    const int which = (warp - K_WARP) & 1;   // 0: K, 1: V
+    const int part = (warp - K_WARP) >> 1;   // fp8 caches only: 1 = the third producer, which helps with both kinds
     const int64_t sb = which ? a.v_stride_block : a.k_stride_block, st = which ? a.v_stride_token : a.k_stride_token;
     const void* map = which ? static_cast<const void*>(&vmap) : static_cast<const void*>(&kmap);
     const int p_tok = which ? a.v_pos[0] : a.k_pos[0], p_head = which ? a.v_pos[1] : a.k_pos[1];   // the block id takes the third
@@ -801,42 +817,59 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
       }
       if constexpr (FP8) {
         // the item's tiles as one stream: tile x = block x / 8, 16-token tile x % 8
-        constexpr int TPB = KVB / TILE_TOKENS;
-        const uint32_t stg = epi + EPI_BYTES / 2 + (uint32_t)which * (FP8_STAGE_TILES * 2048u);
-        const int g = lane & 7, rl = lane >> 3;            // this lane's chunk of a row, and its row of four
-        const int c0 = 2 * (g & 3);                        // the first of the two 16-byte f16 chunks its 16 dims become
-        const uint32_t lane_stg = (uint32_t)rl * 128 + g * 16;
-        const uint32_t lane_dst = (uint32_t)(g >> 2) * HALF_BYTES_KV + (uint32_t)rl * 128;
-        // rows rl, rl + 4, rl + 8, ...: r & 7 is rl or rl + 4, so the two chunks' places inside a row take two values each
-        const uint32_t xa0 = (uint32_t)((c0 ^ rl) << 4), xa1 = (uint32_t)(((c0 + 1) ^ rl) << 4);
-        const uint32_t xb0 = (uint32_t)((c0 ^ (rl + 4)) << 4), xb1 = (uint32_t)(((c0 + 1) ^ (rl + 4)) << 4);
-        const int64_t lane_off = (int64_t)rl * st + g * 16;
-        const int tiles = n * TPB;
+        // Of a block's eight 16-token tiles the kind's own warp takes the first MAIN, a third producer (if MAIN < 8)
+        // the rest of both kinds: its stream a block is K tiles MAIN.., then V tiles MAIN.. . A slot is complete
+        // when every warp that fills it has arrived.
+        constexpr int TPB = KVB / TILE_TOKENS, MAIN = FP8_MAIN, REST = TPB - MAIN > 0 ? TPB - MAIN : 1;
+        const int per_blk = part ? 2 * REST : MAIN;        // this warp's tiles a block
+        const uint32_t stg = epi + (uint32_t)(warp - K_WARP) * (FP8_STAGE_TILES * 2048u);
+        // A lane owns one 16-byte chunk (16 dims) of four rows of every tile. 16-byte accesses are served a
+        // quarter warp at a time, so eight consecutive lanes must fall on eight different 16-byte bank groups:
+        // a quarter warp takes the four chunks of one 64-dim half of two adjacent rows -- the 128-byte swizzle
+        // of the slot puts an even and an odd row's chunks on complementary groups, and the staging rows swap
+        // their halves on odd rows for the same reason.
+        const int gq = lane & 3, rp = (lane >> 2) & 1, hq = (lane >> 3) & 1, rq = lane >> 4;
+        const int g = hq * 4 + gq;                         // the row's 16-byte fp8 chunk: dims 16 g .. + 15
+        const int row0 = 2 * rq + rp;                      // rows row0 + 4 y of the tile, y = 0..3
+        const int c0 = 2 * gq;                             // the first of the two 16-byte f16 chunks its 16 dims become
+        const uint32_t lane_stg = (uint32_t)row0 * 128 + (uint32_t)((g ^ (rp * 4)) << 4);
+        const uint32_t lane_dst = (uint32_t)hq * HALF_BYTES_KV + (uint32_t)row0 * 128;
+        // r & 7 of rows row0, row0 + 4, ...: row0 or row0 + 4, so the two chunks' places inside a row take two values each
+        const uint32_t xa0 = (uint32_t)((c0 ^ row0) << 4), xa1 = (uint32_t)(((c0 + 1) ^ row0) << 4);
+        const uint32_t xb0 = (uint32_t)((c0 ^ (row0 + 4)) << 4), xb1 = (uint32_t)(((c0 + 1) ^ (row0 + 4)) << 4);
+        const int tiles = n * per_blk;                     // this warp's tiles of the item, as one stream
+        // tile x of the stream: which kind (0 K, 1 V) and which tile of the block
+        auto kind_of = [&](int r) { return part ? r / REST : which; };
+        auto tile_of = [&](int r) { return part ? MAIN + r % REST : r; };
         int id_cur = next_id, sub_cur = next_sub, blk_cur = 0;    // lanes 0..7: the page ids of block blk_cur, and of the one after
         page_ids(KVB, next_id, next_sub);
         auto issue = [&](int x) {
-          const int jb = x / TPB, t = x % TPB;
+          const int jb = x / per_blk, r = x % per_blk, kind = kind_of(r), t = tile_of(r);
           if (jb != blk_cur) { id_cur = next_id; sub_cur = next_sub; blk_cur = jb; page_ids((jb + 1) * KVB, next_id, next_sub); }
           const int id = min(max(__shfl_sync(0xffffffffu, id_cur, t), 0), a.num_blocks - 1), sub = __shfl_sync(0xffffffffu, sub_cur, t);
-          const uint8_t* tp = src + (int64_t)id * sb + (int64_t)(sub * TILE_TOKENS) * st + lane_off;
+          const int64_t sbk = kind ? a.v_stride_block : a.k_stride_block, stk = kind ? a.v_stride_token : a.k_stride_token;
+          const uint8_t* tp = (kind ? a.v + (int64_t)kvh * a.v_stride_head : a.k + (int64_t)kvh * a.k_stride_head) +
+                              (int64_t)id * sbk + (int64_t)(sub * TILE_TOKENS + row0) * stk + g * 16;
           const uint32_t buf = stg + (uint32_t)(x % FP8_STAGE_TILES) * 2048u + lane_stg;
+          const int tok0 = jb * KVB + t * TILE_TOKENS;
 #pragma unroll
           for (int y = 0; y < 4; ++y) {
-            if (x * TILE_TOKENS + 4 * y + rl < kv_limit) cp_async16(buf + y * 512, tp + (int64_t)(4 * y) * st);
+            if (tok0 + 4 * y + row0 < kv_limit) cp_async16(buf + y * 512, tp + (int64_t)(4 * y) * stk);
             else asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(buf + y * 512), "r"(0u) : "memory");
           }
         };
-        for (int x = 0; x < FP8_STAGE_TILES - 1; ++x) { issue(x); cp_async_commit(); }     // an item has at least eight tiles
+        for (int x = 0; x < FP8_STAGE_TILES - 1; ++x) { if (x < tiles) issue(x); cp_async_commit(); }
         uint32_t slot_addr = 0, bar = 0;
 #pragma unroll 1
         for (int x = 0; x < tiles && ok; ++x) {
           Lap<TRACE> tick;
           if (x + FP8_STAGE_TILES - 1 < tiles) issue(x + FP8_STAGE_TILES - 1);
-          cp_async_commit();                               // a group a tile (empty ones at the end): tile x is the fourth newest
+          cp_async_commit();                               // a group a tile (empty ones at the end): tile x is the oldest one pending
           cp_async_wait<FP8_STAGE_TILES - 1>();
-          const int t = x % TPB;
-          if (t == 0) {
-            const int slot = 2 * (cnt & 1) + which, lap = cnt >> 1;
+          const int r = x % per_blk, kind = kind_of(r), t = tile_of(r);
+          const bool first = part ? r % REST == 0 : r == 0, last = part ? r % REST == REST - 1 : r == MAIN - 1;
+          if (first) {                                     // the first tile this warp puts into the kind's slot of this block
+            const int slot = 2 * (cnt & 1) + kind, lap = cnt >> 1;
             slot_addr = ring + slot * SLOT_BYTES; bar = HKB_BAR(full) + 8 * slot;
             tick(tr[1]);
             if (lap > 0) ok = warp_wait(HKB_BAR(empty) + 8 * slot, (lap - 1) & 1, abort, 7);
@@ -858,12 +891,12 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
             asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(row + ((y & 1) ? xb0 : xa0)), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
             asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(row + ((y & 1) ? xb1 : xa1)), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
           }
-          if (t == TPB - 1) {
+          if (last) {      // this warp's share of the slot is in place
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar);
-            ++cnt;
           }
+          if (r == per_blk - 1) ++cnt;
           tick(tr[1]);
         }
       } else
@@ -910,7 +943,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const Args a, co
       }
     }
     cp_async_wait<0>();
-    if (TRACE && lane == 0)
+    if (TRACE && lane == 0 && part == 0)
       for (int i = 0; i < 3; ++i) a.trace[(size_t)cta * 32 + 24 + 4 * which + i] = tr[i];
   }
 
