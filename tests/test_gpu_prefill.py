@@ -213,6 +213,35 @@ def test_fp8_cache_on_both_kernel_forms(page, monkeypatch):
     assert hkb.load().hkb_prefill_tc_error(0) == 0
 
 
+@pytest.mark.parametrize("seed", range(8))
+def test_many_items_a_cta_in_every_mix(seed):
+    """More work items than SMs, so a persistent CTA walks several in a row: items whose second query tile
+    is empty beside items with both, one-block items beside long ones, one-token requests, prefixes that
+    end inside a key block -- the barrier phases must carry over every such sequence of items. Seeded
+    random batches (six of the eight hold more items than a B200 has SMs), NaN past the ends in half of them."""
+    import random
+
+    from hk_dsl_b200.runtime import lib as hkb
+
+    rng = random.Random(100 + seed)
+    group = rng.choice([1, 2, 4, 8])
+    h_kv = rng.choice([2, 4, 8]) if group <= 4 else rng.choice([1, 2])
+    page = rng.choice([16, 16, 32, 64])
+    reqs = []
+    for _ in range(rng.randint(12, 40)):
+        kind = rng.random()
+        if kind < 0.2:
+            reqs.append((rng.randint(0, 700), 1))                       # a decode inside the batch
+        elif kind < 0.6:
+            reqs.append((rng.choice([0, 0, 17, 128, 300]), rng.randint(2, 140)))   # short chunks: second tile often empty
+        else:
+            reqs.append((rng.randint(0, 900), rng.randint(141, 520)))
+    got, want, _ = _run(reqs, h_kv=h_kv, group=group, page=page, seed=200 + seed, nan_past=(seed % 2 == 0))
+    assert torch.isfinite(got.float()).all()
+    orc.check(got, want)
+    assert hkb.load().hkb_prefill_tc_error(0) == 0
+
+
 def test_which_kernel_runs_and_that_no_wait_ran_out(monkeypatch):
     """head_dim 128 on a 16-bit cache runs the tcgen05 / tensor-memory kernel, everything else (and
     HKB_PREFILL_MMA_SYNC=1) the mma.sync one; both give the oracle's answer on the same inputs and
