@@ -381,13 +381,13 @@ def run_config(ctx, name: str, *, headline: bool, probe_gbs=None):
     dec = None
     exchange = None
     if kvsplit:
-        # the ranks' records go over peer memory (two kernels of this build, no collective) where the
+        # the ranks' records go over peer memory (one kernel of this build after the walk, no collective) where the
         # box maps it; HKB_KVSPLIT_EXCHANGE=nccl, or a box that cannot, takes the all-gather
         exchange = os.environ.get("HKB_KVSPLIT_EXCHANGE", "peer")
         try:
             dec = paged_dist.SplitKVDecoder(n, st.q_heads, st.kv_heads, d, dev, splits, exchange=exchange)
         except Exception as ex:  # noqa: BLE001
-            if exchange != "peer":
+            if not exchange.startswith("peer"):
                 raise
             exchange = f"nccl (peer memory unavailable: {type(ex).__name__}: {str(ex).splitlines()[0][:120]})"
             dec = paged_dist.SplitKVDecoder(n, st.q_heads, st.kv_heads, d, dev, splits, exchange="nccl")
@@ -404,7 +404,7 @@ def run_config(ctx, name: str, *, headline: bool, probe_gbs=None):
     # walk writes the new rows itself, then the merge. A KV-split step: walk (+ rows), merge of the
     # local splits into this rank's record, [exchange], merge of the ranks' records.
     joined = not kvsplit and splits > 1 and n <= 2048
-    launches_per_step = 3 if kvsplit else (2 if joined else 1 + 1 + (1 if splits > 1 else 0))
+    launches_per_step = (2 if exchange == "peer" and dec is not None and dec.peer is not None else 3) if kvsplit else (2 if joined else 1 + 1 + (1 if splits > 1 else 0))
 
     def walk(l):
         if kvsplit:
@@ -586,13 +586,15 @@ def kvsplit_breakdown(ctx, spec, st, dec, layers, K, owns_new):
 
 
 def peer_breakdown(ctx, spec, st, dec, layers, K, owns_new):
-    """The three launches of a KV-split step over peer memory, eagerly, a CUDA event between them: the
-    walk (it writes the new rows), the push (fold of the local splits + stores into every rank), the
-    merge (its wait for the slowest rank's record included). Means over K steps, max over ranks."""
+    """The launches of a KV-split step over peer memory, eagerly, a CUDA event between them: the walk (it
+    writes the new rows), then the exchange -- one kernel (fold of the local splits, stores into every
+    rank, the wait for every rank's rows, the fold), or as two (push, merge) with HKB_KVSPLIT_EXCHANGE=peer2.
+    Means over K steps, max over ranks."""
     torch = ctx.torch
     from hk_dsl_b200.ops import paged
 
-    names = ("walk_us", "push_us", "wait_and_merge_us")
+    one = dec.exchange == "peer"
+    names = ("walk_us", "exchange_us") if one else ("walk_us", "push_us", "wait_and_merge_us")
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(K)]
     new = dict(key=st.key, value=st.value, slot_mapping=st.slot_mapping) if owns_new else dict(key=None, value=None, slot_mapping=None)
     ctx.barrier()
@@ -603,10 +605,14 @@ def peer_breakdown(ctx, spec, st, dec, layers, K, owns_new):
                                  new["slot_mapping"], st.block_table, st.seq_lens, st.scale, spec.kv_cache_dtype,
                                  st.k_scale, st.v_scale, num_splits=dec.local_splits, scratch=dec.scratch)
         ev[i][1].record()
-        dec.peer.push(dec.scratch, dec.local_splits)
-        ev[i][2].record()
-        dec.peer.merge(st.out)
-        ev[i][3].record()
+        if one:
+            dec.peer.exchange(dec.scratch, dec.local_splits, st.out)
+            ev[i][2].record()
+        else:
+            dec.peer.push(dec.scratch, dec.local_splits)
+            ev[i][2].record()
+            dec.peer.merge(st.out)
+            ev[i][3].record()
     ctx.barrier()
     out = {nm: ctx.max_over_ranks(statistics.fmean(ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(K)) * 1e3)
            for j, nm in enumerate(names)}

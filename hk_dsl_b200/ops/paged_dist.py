@@ -65,13 +65,14 @@ def record_floats(num_seqs: int, num_q_heads: int, head_dim: int) -> int:
 
 
 class PeerExchange:
-    """The exchange of a KV split over peer memory (hkb_kvsplit_push / hkb_kvsplit_merge): every
-    rank's gather buffer and state block live in symmetric memory that all ranks of the box have
-    mapped, the fold of a rank's splits stores its record into every peer directly, and the final
-    merge waits (boundedly) for every rank's flag. No collective in the step.
+    """The exchange of a KV split over peer memory: every rank's gather buffer and state block live
+    in symmetric memory that all ranks of the box have mapped, the fold of a rank's splits stores its
+    record into every peer directly, and the final fold waits (boundedly) for every rank's flags. No
+    collective in the step. `exchange` does it in one launch (hkb_kvsplit_exchange: a flag a row);
+    `push` + `merge` are the two-launch form (hkb_kvsplit_push / hkb_kvsplit_merge: a flag a rank).
 
     With one rank (or no process group) the buffers are plain device tensors and the rank is its
-    own only peer: the same two kernels, usable on one GPU."""
+    own only peer: the same kernels, usable on one GPU."""
 
     #: polls of a flag before the merge gives up (about a tenth of a microsecond each: ~1 s)
     SPIN_LIMIT = 10_000_000
@@ -88,7 +89,8 @@ class PeerExchange:
         if gbytes == 0:
             raise ValueError(f"hk.ops.paged_dist: no peer exchange for {self.world} ranks (1 to 8), {num_seqs} sequences")
         self.gather_bytes = (gbytes + 255) // 256 * 256
-        total = self.gather_bytes + 256
+        self.state_bytes = lib.hkb_exchange_state_bytes_rows(num_seqs, num_q_heads)
+        total = self.gather_bytes + (self.state_bytes + 255) // 256 * 256
         if self.world > 1:
             import torch.distributed._symmetric_memory as symm
 
@@ -108,7 +110,8 @@ class PeerExchange:
             x.gather[r] = ptrs[r]
             x.state[r] = ptrs[r] + self.gather_bytes
         self.x = x
-        self.state = self.buf[self.gather_bytes:self.gather_bytes + 80].view(torch.int32)   # flags, counters, error word
+        # the ranks' flags, the counters and the error word, then the rows' flags
+        self.state = self.buf[self.gather_bytes:self.gather_bytes + self.state_bytes].view(torch.int32)
 
     def push(self, scratch, num_splits: int) -> None:
         """Fold this rank's splits (`scratch` of the walk) and store the record into every rank."""
@@ -126,6 +129,20 @@ class PeerExchange:
         rc = _lib.load().hkb_kvsplit_merge(self.x, out.data_ptr(), out.stride(0), out.stride(1), kind, self.n, self.hq,
                                            self.d, int(spin_limit or self.SPIN_LIMIT), paged._stream(out))
         _lib.check("hkb_kvsplit_merge", rc)
+        return out
+
+    def exchange(self, scratch, num_splits: int, out: torch.Tensor, spin_limit: Optional[int] = None) -> torch.Tensor:
+        """`push` and `merge` in one launch: fold this rank's splits, store the rows into every rank,
+        wait for every rank's rows and fold them into `out` (seqs, heads, d)."""
+        po, pl = scratch
+        kind = {torch.bfloat16: 0, torch.float16: 2}.get(out.dtype)
+        if kind is None or tuple(out.shape) != (self.n, self.hq, self.d) or out.stride(2) != 1:
+            raise ValueError(f"hk.ops.paged_dist: the exchange writes ({self.n}, {self.hq}, {self.d}) bf16 or fp16, "
+                             f"out is {tuple(out.shape)} {out.dtype}")
+        rc = _lib.load().hkb_kvsplit_exchange(self.x, po.data_ptr(), pl.data_ptr(), num_splits, out.data_ptr(),
+                                              out.stride(0), out.stride(1), kind, self.n, self.hq, self.d,
+                                              int(spin_limit or self.SPIN_LIMIT), paged._stream(out))
+        _lib.check("hkb_kvsplit_exchange", rc)
         return out
 
     def error(self) -> int:
@@ -150,13 +167,14 @@ class SplitKVDecoder:
     def __init__(self, num_seqs: int, num_q_heads: int, num_kv_heads: int, head_dim: int, device,
                  local_splits: int, group=None, exchange: str = "nccl"):
         """`exchange`: "nccl" -- `all_gather_into_tensor` of the ranks' records between two launches;
-        "peer" -- the records go over peer memory inside the launches (`PeerExchange`)."""
+        "peer" -- the records go over peer memory inside ONE launch after the walk (`PeerExchange.exchange`);
+        "peer2" -- the same in two launches (`push`, `merge`), the comparison arm."""
         import torch.distributed as dist
 
-        if exchange not in ("nccl", "peer"):
-            raise ValueError(f"hk.ops.paged_dist: exchange {exchange!r} is not 'nccl' or 'peer'")
+        if exchange not in ("nccl", "peer", "peer2"):
+            raise ValueError(f"hk.ops.paged_dist: exchange {exchange!r} is not 'nccl', 'peer' or 'peer2'")
         self.exchange = exchange
-        self.peer = PeerExchange(num_seqs, num_q_heads, head_dim, device, group) if exchange == "peer" else None
+        self.peer = PeerExchange(num_seqs, num_q_heads, head_dim, device, group) if exchange != "nccl" else None
 
         self.dist = dist
         self.group = group
@@ -221,13 +239,15 @@ class SplitKVDecoder:
     def decode(self, out, query, key_cache, value_cache, block_tables, local_lens, scale,
                kv_cache_dtype="auto", k_scale=None, v_scale=None, *, key=None, value=None,
                slot_mapping=None) -> torch.Tensor:
-        """The whole step: two launches, one all-gather, one launch -- or, over peer memory, three
-        launches and no collective (the walk; the fold of the local splits that stores this rank's
-        record into every rank; the bounded wait for all records and their fold)."""
+        """The whole step: two launches, one all-gather, one launch -- or, over peer memory, two
+        launches and no collective (the walk; then one kernel that folds the local splits, stores this
+        rank's rows into every rank, waits -- boundedly -- for every rank's rows and folds them)."""
         if self.peer is not None:
             paged.decode_step_record(None, None, query, key, value, key_cache, value_cache, slot_mapping, block_tables,
                                      local_lens, scale, kv_cache_dtype, k_scale, v_scale, num_splits=self.local_splits,
                                      scratch=self.scratch)
+            if self.exchange == "peer":
+                return self.peer.exchange(self.scratch, self.local_splits, out)
             self.peer.push(self.scratch, self.local_splits)
             return self.peer.merge(out)
         self.local_partial(query, key_cache, value_cache, block_tables, local_lens, scale,

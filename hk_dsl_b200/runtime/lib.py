@@ -81,6 +81,9 @@ SIGNATURES = {
     "hkb_exchange_state_bytes": (c_size_t, []),
     "hkb_kvsplit_push": (c_int, [ExchangeT, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "hkb_kvsplit_merge": (c_int, [ExchangeT, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "hkb_exchange_state_bytes_rows": (c_size_t, [c_int, c_int]),
+    "hkb_kvsplit_exchange": (c_int, [ExchangeT, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64, c_int,
+                                     c_int, c_int, c_int, c_int, c_void_p]),
     "hkb_arrivals_bytes": (c_size_t, [c_int, c_int]),
     "hkb_paged_prefill": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, CacheT, CacheT,
                                   c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,

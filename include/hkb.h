@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define HKB_VERSION 121 /* major*100 + minor */
+#define HKB_VERSION 122 /* major*100 + minor */
 
 /* KV element types (kv_dtype). Queries, new K/V rows and outputs are bf16, except with HKB_KV_F16. */
 #define HKB_KV_BF16 0
@@ -350,6 +350,20 @@ int hkb_kvsplit_push(hkb_exchange_t x, const float* part_out, const float* part_
                      int num_seqs, int num_q_heads, int head_dim, void* stream);
 int hkb_kvsplit_merge(hkb_exchange_t x, void* out, int64_t out_stride_tok, int64_t out_stride_head, int out_kind,
                       int num_seqs, int num_q_heads, int head_dim, int spin_limit, void* stream);
+
+/*
+ * hkb_kvsplit_push and hkb_kvsplit_merge in one launch: a CTA a (sequence, head) folds the
+ * rank's splits, stores its row of the record into every rank, raises the row's own flag on
+ * every rank, waits (at most spin_limit polls a rank; a miss sets the error word, skips the
+ * row and returns) for the same row of every rank and folds them into `out`. The state
+ * blocks must be hkb_exchange_state_bytes_rows(num_seqs, num_q_heads) bytes (the 20 words of
+ * hkb_exchange_state_bytes, then a flag a (parity, rank, row)), zeroed once. Do not mix the
+ * two forms on one state block within a step. No counterpart in the reference (as above).
+ */
+size_t hkb_exchange_state_bytes_rows(int num_seqs, int num_q_heads);
+int hkb_kvsplit_exchange(hkb_exchange_t x, const float* part_out, const float* part_lse, int num_splits,
+                         void* out, int64_t out_stride_tok, int64_t out_stride_head, int out_kind,
+                         int num_seqs, int num_q_heads, int head_dim, int spin_limit, void* stream);
 
 /* Bytes of the arrival counters hkb_decode_step takes. */
 size_t hkb_arrivals_bytes(int num_seqs, int num_kv_heads);

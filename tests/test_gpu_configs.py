@@ -278,9 +278,10 @@ def test_kv_split_step_writes_the_new_rows_on_the_rank_that_holds_them():
     orc.check(out, want)
 
 
-def test_peer_exchange_on_one_gpu_equals_the_step_and_replays_from_a_graph():
+@pytest.mark.parametrize("exchange", ["peer", "peer2"])
+def test_peer_exchange_on_one_gpu_equals_the_step_and_replays_from_a_graph(exchange):
     """The exchange over peer memory with the rank as its own only peer: walk (writing the new rows),
-    push, merge -- three launches, no collective -- gives the bits of the two-launch step when the
+    then the exchange in one launch (or push, merge) -- no collective -- gives the bits of the two-launch step when the
     walk and the fold are the same kernels' arithmetic (the fold order differs: tolerance), step after
     step (the gather halves and flags alternate by the step counter's parity), and from a CUDA graph."""
     from hk_dsl_b200.ops import paged_dist
@@ -294,7 +295,7 @@ def test_peer_exchange_on_one_gpu_equals_the_step_and_replays_from_a_graph():
     want = torch.empty_like(ref.out)
     paged.decode_step(want, ref.query, ref.key, ref.value, ref.k_caches[0], ref.v_caches[0], ref.slot_mapping,
                       ref.block_table, ref.seq_lens, ref.scale, num_splits=8)
-    dec = paged_dist.SplitKVDecoder(n, hq, st.kv_heads, d, "cuda", local_splits=8, exchange="peer")
+    dec = paged_dist.SplitKVDecoder(n, hq, st.kv_heads, d, "cuda", local_splits=8, exchange=exchange)   # one launch / two
     assert dec.peer.world == 1 and dec.peer.error() == 0
     out = torch.full_like(st.out, 7.0)
     for step in range(3):                                   # parities 0, 1, 0
@@ -335,6 +336,46 @@ def test_peer_exchange_a_record_that_never_arrives_is_reported_not_waited_for():
     assert (out == 7.0).all()
     dec.peer.reset()
     torch.cuda.synchronize()
+    dec.decode(out, st.query, st.k_caches[0], st.v_caches[0], st.block_table, st.seq_lens, st.scale,
+               key=st.key, value=st.value, slot_mapping=st.slot_mapping)
+    torch.cuda.synchronize()
+    assert dec.peer.error() == 0
+    orc.check(out, _oracle(st))
+
+
+def test_peer_exchange_in_one_launch_gives_up_on_rows_that_never_arrive():
+    """hkb_kvsplit_exchange waits for a flag a (rank, row). Here this rank is told it is rank 0 of two whose
+    second rank is itself (both peers' buffers are its own) -- so nobody ever raises rank 1's flags: every
+    CTA gives up after `spin_limit` polls, the error word reads 1 + 1, `out` is untouched, the context stays
+    usable, and after `reset` a whole step with the true single rank works."""
+    from hk_dsl_b200.ops import paged_dist
+    from hk_dsl_b200.runtime import lib as hkb
+
+    spec = W.CONFIGS["c5"]
+    st = W.build_step(spec, "cuda", lens=[600, 100])
+    n, hq, d = st.query.shape
+    dec = paged_dist.SplitKVDecoder(n, hq, st.kv_heads, d, "cuda", local_splits=4, exchange="peer")
+    out = torch.full_like(st.out, 7.0)
+    dec.walk(st.query, st.k_caches[0], st.v_caches[0], st.block_table, st.seq_lens, st.scale)
+    lib = hkb.load()
+    # a gather buffer sized for two ranks, beside a state block of its own
+    gbytes = lib.hkb_exchange_gather_bytes(2, n, hq, d)
+    sbytes = lib.hkb_exchange_state_bytes_rows(n, hq)
+    buf = torch.zeros(gbytes + 256 + sbytes, dtype=torch.uint8, device="cuda")
+    x = hkb.ExchangeT()
+    x.world, x.rank = 2, 0
+    for r in range(2):
+        x.gather[r] = buf.data_ptr()
+        x.state[r] = buf.data_ptr() + (gbytes + 255) // 256 * 256
+    po, pl = dec.scratch
+    rc = lib.hkb_kvsplit_exchange(x, po.data_ptr(), pl.data_ptr(), dec.local_splits, out.data_ptr(), out.stride(0),
+                                  out.stride(1), 0, n, hq, d, 200, torch.cuda.current_stream().cuda_stream)
+    hkb.check("hkb_kvsplit_exchange", rc)
+    torch.cuda.synchronize()
+    state = buf[(gbytes + 255) // 256 * 256:][:80].view(torch.int32)
+    assert int(state[19].item()) == 2                       # rank 1's rows were the ones missing
+    assert int(state[16].item()) == 1 and int(state[17].item()) == 0   # the step counter moved on, the CTA counter is back at zero
+    assert (out == 7.0).all()
     dec.decode(out, st.query, st.k_caches[0], st.v_caches[0], st.block_table, st.seq_lens, st.scale,
                key=st.key, value=st.value, slot_mapping=st.slot_mapping)
     torch.cuda.synchronize()

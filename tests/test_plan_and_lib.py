@@ -22,7 +22,7 @@ def test_every_declared_symbol_is_exported():
     loaded = lib.load()
     for name in declared:
         assert getattr(loaded, name) is not None
-    assert loaded.hkb_version() == 121
+    assert loaded.hkb_version() == 122
 
 
 def test_status_text_and_refusals_need_no_gpu():
