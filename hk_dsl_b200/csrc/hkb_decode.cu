@@ -481,10 +481,6 @@ static int decode_impl(void* out, int64_t out_stride_tok, int64_t out_stride_hea
   a.new_k_stride_tok = a.new_k_stride_head = a.new_v_stride_tok = a.new_v_stride_head = 0;
   a.slots = nullptr; a.slot_is_i64 = 0; a.block_size = block_size;
   a.xsplit = extra && extra->xsplit;
-  {
-    const char* v = std::getenv("HKB_STREAM_MIN_RANGE");
-    a.min_range = v ? std::atoi(v) : 1;
-  }
   if (a.xsplit) {
     if (head_dim != 128 || fp8 || num_splits < 2 || num_seqs > STREAM_MAX_SEQS) return HKB_ERR_UNSUPPORTED;
     return f16 ? dispatch_xsplit<true>(a, num_seqs, (cudaStream_t)stream) : dispatch_xsplit<false>(a, num_seqs, (cudaStream_t)stream);

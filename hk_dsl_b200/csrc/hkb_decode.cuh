@@ -47,7 +47,6 @@ struct DecodeArgs {
   const void* slots;
   int slot_is_i64;
   int block_size;
-  int min_range;   // the stream's smallest piece, in 16-token tiles (1: spread a small batch over as many rings as it has tiles)
   int xsplit;   // the caches are in the x-split layout (XSplitLoader); strides then describe blocks and heads only
 };
 

@@ -96,7 +96,7 @@ struct WalkStream {
     __syncthreads();
     const int total = base[num_seqs], longest = base[num_seqs + 1];
     const int plane_rings = gridDim.x * RINGS;
-    int range = max((total + plane_rings - 1) / plane_rings, max(a.min_range, STREAM_MIN_RANGE));
+    int range = max((total + plane_rings - 1) / plane_rings, STREAM_MIN_RANGE);
     range = max(range, (longest + parts - 2) / max(parts - 1, 1));
 
     const bool fold = WPR == 1 && a.arrivals != nullptr;
