@@ -152,18 +152,20 @@ def test_a_host_sync_inside_a_safe_patch_raises_under_capture_naming_it():
     torch.cuda.synchronize()
 
 
+@pytest.mark.parametrize("d", [128, 64, 256])
 @pytest.mark.parametrize("kv_cache_dtype", ["auto", "fp8"])
 @pytest.mark.parametrize("layout", ["five", "side_by_side"])
-def test_backend_forward_writes_the_cache_then_decodes(kv_cache_dtype, layout, monkeypatch):
+def test_backend_forward_writes_the_cache_then_decodes(kv_cache_dtype, layout, d, monkeypatch):
     """One decode step as the engine drives it: new K/V rows scattered by slot, then attention
-    over the updated cache; and the same step replayed from a CUDA graph."""
+    over the updated cache; and the same step replayed from a CUDA graph. Head sizes 64, 128 and 256,
+    16-bit and fp8 caches."""
     from hk_dsl_b200.integration import vllm_backend
 
     monkeypatch.delenv("HK_SPLITS", raising=False)
-    hq, hkv, d, page = 32, 8, 128, 16
+    hq, hkv, page = 32, 8, 16
     lens = [17, 700, 1, 2063, 256]
     n = len(lens)
-    q, k, v, table, lens_t = _case(lens, hkv=hkv, group=4, seed=21)
+    q, k, v, table, lens_t = _case(lens, hkv=hkv, group=4, d=d, seed=21)
     g = torch.Generator().manual_seed(99)
     key = torch.randn(n, hkv, d, generator=g).to(torch.bfloat16)
     value = torch.randn(n, hkv, d, generator=g).to(torch.bfloat16)
