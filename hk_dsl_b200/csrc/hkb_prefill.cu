@@ -577,13 +577,18 @@ extern "C" int hkb_paged_prefill(void* out, int64_t out_stride_tok, int64_t out_
     // a query tile that runs past the tensor's last token reads zeros there (the map knows num_tokens);
     // rows past a request's own tokens belong to the next request and are masked
     const int64_t q_tokens = num_tokens;
-    // (an fp8 cache is widened by the producers on its way in: no tile copies, and the query rows are staged by the softmax warps)
-    t.tma = !fp8 && !(no_tma && no_tma[0] == '1') && make_cache_map(&kmap, kc, block_size, num_kv_heads, t.k_pos) &&
-            make_cache_map(&vmap, vc, block_size, num_kv_heads, t.v_pos) &&
-            make_query_map(&qmap, q, q_stride_tok, q_stride_head, q_tokens, num_q_heads, 128 / gp, t.q_pos);
+    // (an fp8 cache is widened by the producers on its way in: no tile copies for K and V; the query tiles still come by TMA)
+    const bool tma_ok = !(no_tma && no_tma[0] == '1');
+    t.tma_q = tma_ok && make_query_map(&qmap, q, q_stride_tok, q_stride_head, q_tokens, num_q_heads, 128 / gp, t.q_pos);
+    t.tma = t.tma_q && !fp8 && make_cache_map(&kmap, kc, block_size, num_kv_heads, t.k_pos) &&
+            make_cache_map(&vmap, vc, block_size, num_kv_heads, t.v_pos);
     if (!t.tma) {
-      memset(&kmap, 0, sizeof(kmap)); memset(&vmap, 0, sizeof(vmap)); memset(&qmap, 0, sizeof(qmap));
+      memset(&kmap, 0, sizeof(kmap)); memset(&vmap, 0, sizeof(vmap));
       for (int i = 0; i < 3; ++i) t.k_pos[i] = t.v_pos[i] = i + 1;
+      if (!fp8) t.tma_q = 0;      // 16-bit caches: all three by TMA, or none (the comparison arm)
+    }
+    if (!t.tma_q) {
+      memset(&qmap, 0, sizeof(qmap));
       t.q_pos[0] = 1; t.q_pos[1] = 2;
     }
     if (t.trace) {   // the traced build: the headline shape only (a bf16 or an fp8 cache, a GQA group of 4)

@@ -74,14 +74,15 @@ __host__ __device__ constexpr int s_col(int tile) { return 256 + tile * 128; }
 
 struct Bars {                                  // mbarriers, 8 bytes each
   uint64_t full[NSLOT], empty[NSLOT];
-  uint64_t s_full[2], p_full[2], o_done[2], q_full[2], q_empty[2];
+  uint64_t s_full[2], p_full[2], o_done[2], q_full[2], q_empty[2], q_ready[2];
   uint32_t tmem_base;
   int abort;
 };
 constexpr int EPI_BYTES = SOFTMAX_WARPS * 4096;   // the epilogue's staging: 32 half rows of 128 bytes a softmax warp (fp8 caches:
-                                                  // the producers' staging rings instead, 8 KB each)
-constexpr int FP8_STAGE_TILES = 8;                // 16-token fp8 tiles (2 KB) in a producer's staging ring: seven in flight, one being widened
-static_assert((FP8_MAIN < 8 ? 3 : 2) * FP8_STAGE_TILES * 2048 <= EPI_BYTES, "the producers' staging rings live in the epilogue's space");
+                                                  // 32 quarter rows of 64 bytes; the upper 16 KB are the producers' staging rings)
+constexpr int FP8_STAGE_TILES = 4;                // 16-token fp8 tiles (2 KB) in a producer's staging ring: three in flight, one being widened
+                                                  // (seven in flight measured the same: the producers are not waiting for their copies)
+static_assert((FP8_MAIN < 8 ? 3 : 2) * FP8_STAGE_TILES * 2048 <= EPI_BYTES / 2, "the producers' staging rings live in the upper half of the epilogue's space");
 constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + 2 * Q_BYTES + NSLOT * SLOT_BYTES + EPI_BYTES + 1024 /*Bars*/;
 static_assert(sizeof(Bars) <= 1024, "barrier block");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory of one SM");
@@ -256,6 +257,7 @@ struct Args {
   const float* k_scale;     // fp8 caches: the per-tensor scales (device floats); else unused
   const float* v_scale;
   int tma;                  // K and V blocks by TMA (the two tensor maps are valid)
+  int tma_q;                // the query tiles by TMA (the query map is valid)
   int k_pos[3], v_pos[3];   // which coordinate of the map (1..3) is the token, the kv head, the block
   int q_pos[2];             // which coordinate of the query map (1..2) is the token, the head
   unsigned long long* trace;   // TRACE builds only: 32 cycle counters a CTA (see Lap), else unused
@@ -469,8 +471,8 @@ __global__ void __launch_bounds__(threads_of(FP8), 1) prefill_tc_kernel(const Ar
     for (int i = 0; i < NSLOT; ++i) { mbar_init(HKB_BAR(full) + 8 * i, FP8 && FP8_MAIN < 8 ? 2 : 1); mbar_init(HKB_BAR(empty) + 8 * i, 1); }   // (fp8 with a third producer: a slot is filled by two warps)
     for (int i = 0; i < 2; ++i) {
       mbar_init(HKB_BAR(s_full) + 8 * i, 1); mbar_init(HKB_BAR(p_full) + 8 * i, ROWS);
-      mbar_init(HKB_BAR(o_done) + 8 * i, 1); mbar_init(HKB_BAR(q_full) + 8 * i, a.tma ? 1 : ROWS);
-      mbar_init(HKB_BAR(q_empty) + 8 * i, 1);
+      mbar_init(HKB_BAR(o_done) + 8 * i, 1); mbar_init(HKB_BAR(q_full) + 8 * i, a.tma_q ? 1 : ROWS);
+      mbar_init(HKB_BAR(q_empty) + 8 * i, 1); mbar_init(HKB_BAR(q_ready) + 8 * i, ROWS);
     }
     bars->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -511,7 +513,7 @@ __global__ void __launch_bounds__(threads_of(FP8), 1) prefill_tc_kernel(const Ar
       if (got == 1 || it.nblk(g) == 0) continue;
       const int row0 = it.row0, q_len = it.q_len, q0 = it.q0, hbase = it.hbase;
       Lap<TRACE> lap_q;
-      if (!a.tma) {
+      if (!a.tma_q) {
         // No tensor map for the queries: this tile's warps stage its rows themselves -- row r is head
         // r / T, token r % T of the tile -- once the products of the item before have read the old ones.
         if (items > 0) {
@@ -541,6 +543,32 @@ __global__ void __launch_bounds__(threads_of(FP8), 1) prefill_tc_kernel(const Ar
         }
         fence_async_smem();
         mbar_arrive(HKB_BAR(q_full) + 8 * g);
+      } else if (FP8) {
+        // The rows came by TMA as they are in memory, bf16, under the item before's tail; the products run
+        // on f16 beside the widened cache: each thread converts the sixteen chunks it would have staged, in
+        // place, and the MMA warp waits for all 128 threads (q_ready) instead of for the copy.
+        ok = warp_wait<FP8>(HKB_BAR(q_full) + 8 * g, items & 1, abort, 8);
+        if (!ok) break;
+        uint4 qv[16];
+#pragma unroll
+        for (int x16 = 0; x16 < 16; ++x16) {
+          const int x = x16 * ROWS + (warp & 3) * 32 + lane, r = x >> 4, c = x & 15;
+          qv[x16] = lds128(q_smem + g * Q_BYTES + (c >> 3) * HALF_BYTES_Q + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+        }
+#pragma unroll
+        for (int x16 = 0; x16 < 16; ++x16) {
+          const int x = x16 * ROWS + (warp & 3) * 32 + lane, r = x >> 4, c = x & 15;
+          uint32_t* w = reinterpret_cast<uint32_t*>(&qv[x16]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float lo = fminf(fmaxf(bf16lo(w[i]), -65504.f), 65504.f), hi = fminf(fmaxf(bf16hi(w[i]), -65504.f), 65504.f);
+            asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(w[i]) : "f"(hi), "f"(lo));
+          }
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(q_smem + g * Q_BYTES + (c >> 3) * HALF_BYTES_Q + r * 128 + (((c & 7) ^ (r & 7)) << 4)),
+                       "r"(qv[x16].x), "r"(qv[x16].y), "r"(qv[x16].z), "r"(qv[x16].w) : "memory");
+        }
+        fence_async_smem();
+        mbar_arrive(HKB_BAR(q_ready) + 8 * g);
       }
       ++items;
       lap_q(tr[6]);
@@ -614,15 +642,14 @@ __global__ void __launch_bounds__(threads_of(FP8), 1) prefill_tc_kernel(const Ar
       blocks += nb;
       tc_fence_after();
       const float inv = (l > 0.f ? 1.f / l : 0.f) * out_scale;
-      // Each thread parks half of its output row (64 dims = 128 bytes; 16-byte chunks XOR-ed by the row so
-      // that the 32 rows of a warp do not collide on banks) in the warp's staging rows, then the warp -- which owns exactly
+      // Each thread parks half of its output row (64 dims = 128 bytes; a quarter in the fp8 build; 16-byte
+      // chunks XOR-ed by the row so that the 32 rows of a warp do not collide on banks) in the warp's staging rows, then the warp -- which owns exactly
       // these 32 rows -- writes them out 512 bytes an instruction; then the next part. The accumulator
       // is free for the next item as soon as its last part has been read: the first P of that item is
       // handed over after this, by these same threads.
-      constexpr int PASS_DIMS = 64, ROWE = PASS_DIMS * 2, CPRE = ROWE / 16;   // dims, bytes, 16-byte chunks of a staged row
-      // (fp8 caches: the staging space belongs to the producers; the tile's own query rows are dead by now -- every
-      // product that read them has landed -- and these same warps stage the next item's after this)
-      const uint32_t stage = FP8 ? q_smem + g * Q_BYTES + (uint32_t)(warp & 3) * (32u * ROWE) : epi + (uint32_t)warp * (32u * ROWE);
+      // (fp8 caches: half of the staging space belongs to the producers, so a quarter of a row at a time)
+      constexpr int PASS_DIMS = FP8 ? 32 : 64, ROWE = PASS_DIMS * 2, CPRE = ROWE / 16;   // dims, bytes, 16-byte chunks of a staged row
+      const uint32_t stage = epi + (uint32_t)warp * (32u * ROWE);
       const int wswz = CPRE == 8 ? (lane & 7) : ((lane >> 1) & 3);     // a 64-byte row: two rows share a 128-byte bank line
 #pragma unroll 1
       for (int pass = 0; pass < D / PASS_DIMS; ++pass) {
@@ -703,8 +730,9 @@ __global__ void __launch_bounds__(threads_of(FP8), 1) prefill_tc_kernel(const Ar
       const int n = it.n;
       Lap<TRACE> lap;
       // the tiles' query rows are in place
-      if (it.nblk0 > 0) ok = warp_wait<FP8>(HKB_BAR(q_full), items0 & 1, abort, 8);
-      if (ok && it.nblk1 > 0) ok = warp_wait<FP8>(HKB_BAR(q_full) + 8, items1 & 1, abort, 8);
+      const uint32_t q_bar = FP8 && a.tma_q ? HKB_BAR(q_ready) : HKB_BAR(q_full);   // fp8: the rows as converted in place
+      if (it.nblk0 > 0) ok = warp_wait<FP8>(q_bar, items0 & 1, abort, 8);
+      if (ok && it.nblk1 > 0) ok = warp_wait<FP8>(q_bar + 8, items1 & 1, abort, 8);
       if (!ok) break;
       lap(tr[0]);
       wait_block(0, kcnt, 4);
@@ -791,7 +819,7 @@ __global__ void __launch_bounds__(threads_of(FP8), 1) prefill_tc_kernel(const Ar
       };
       int next_id, next_sub;
       page_ids(0, next_id, next_sub);
-      if (a.tma && which == 1) {
+      if (a.tma_q && which == 1 && part == 0) {
         // the V warp has nothing to do until the first scores exist: it brings the query tiles, one copy a
         // (tile, head, 64-dim half): T token rows of 128 bytes, landing where row h * T + token belongs --
         // once the products of the item before have read the old ones
@@ -822,7 +850,7 @@ __global__ void __launch_bounds__(threads_of(FP8), 1) prefill_tc_kernel(const Ar
         // when every warp that fills it has arrived.
         constexpr int TPB = KVB / TILE_TOKENS, MAIN = FP8_MAIN, REST = TPB - MAIN > 0 ? TPB - MAIN : 1;
         const int per_blk = part ? 2 * REST : MAIN;        // this warp's tiles a block
-        const uint32_t stg = epi + (uint32_t)(warp - K_WARP) * (FP8_STAGE_TILES * 2048u);
+        const uint32_t stg = epi + EPI_BYTES / 2 + (uint32_t)(warp - K_WARP) * (FP8_STAGE_TILES * 2048u);
         // A lane owns one 16-byte chunk (16 dims) of four rows of every tile. 16-byte accesses are served a
         // quarter warp at a time, so eight consecutive lanes must fall on eight different 16-byte bank groups:
         // a quarter warp takes the four chunks of one 64-dim half of two adjacent rows -- the 128-byte swizzle
