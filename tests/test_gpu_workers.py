@@ -31,3 +31,19 @@ def test_decode_and_step_tests_under_another_worker(env):
     r = subprocess.run(cmd, cwd=ROOT, env={**os.environ, **env}, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
                        timeout=900)
     assert r.returncode == 0, r.stdout[-3000:]
+
+
+@pytest.mark.parametrize("env", [
+    {"HKB_PREFILL_NO_TMA": "1"},                              # K, V and the query tiles by cp.async / vector loads
+    {"HKB_PREFILL_MMA_SYNC": "1"},                            # the mma.sync form at head_dim 128 too
+], ids=lambda e: ",".join(f"{k}={v}" for k, v in e.items()))
+def test_prefill_tests_under_the_other_forms(env):
+    """The tensor-memory prefill kernel without TMA (its cp.async gather and the softmax warps' own staging
+    of the query rows, which in the persistent grid wait for the item before), and the mma.sync kernel in
+    its place: the prefill tests in a child process of each setting (the test that asks which kernel runs
+    sets the variable itself and is left out)."""
+    cmd = [sys.executable, "-m", "pytest", "-x", "-q", "-p", "no:cacheprovider", "tests/test_gpu_prefill.py", "tests/test_gpu_f16.py",
+           "-k", "not which_kernel and not both_kernel_forms"]
+    r = subprocess.run(cmd, cwd=ROOT, env={**os.environ, **env}, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                       timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:]
