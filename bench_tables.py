@@ -453,6 +453,68 @@ def shards_table():
     return 0
 
 
+def exchange_table(only: str = ""):
+    """The KV-split step's exchange on ONE GPU (the rank is its own only peer: no NVLink in it, the
+    kernels' own cost): the long-context config's shape (c5: 2 sequences x 131072 tokens, 32 q / 8 kv
+    heads, 256 local splits), walk then exchange in one launch (hkb_kvsplit_exchange) or in two
+    (hkb_kvsplit_push, hkb_kvsplit_merge), each a graph of 20 steps, median of 7. `only`: "one" or
+    "two", a short eager run for a profiler."""
+    import torch
+
+    from hk_dsl_b200 import workloads as W
+    from hk_dsl_b200.ops import paged, paged_dist
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    spec = W.CONFIGS["c5"]
+    st = W.build_step(spec, dev)
+    n, hq, d = st.query.shape
+    splits = paged.plan_splits(n, st.kv_heads, st.block_table.shape[1], device=dev)
+    rows = []
+    for name, exchange in (("one", "peer"), ("two", "peer2")):
+        if only and only != name:
+            continue
+        dec = paged_dist.SplitKVDecoder(n, hq, st.kv_heads, d, dev, splits, exchange=exchange)
+
+        def step():
+            dec.decode(st.out, st.query, st.k_caches[0], st.v_caches[0], st.block_table, st.seq_lens, st.scale,
+                       key=st.key, value=st.value, slot_mapping=st.slot_mapping)
+
+        def walk():
+            paged.decode_step_record(None, None, st.query, st.key, st.value, st.k_caches[0], st.v_caches[0], st.slot_mapping,
+                                     st.block_table, st.seq_lens, st.scale, num_splits=dec.local_splits, scratch=dec.scratch)
+
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        if only:
+            return 0
+        us = {}
+        for what, call in (("step", step), ("walk", walk)):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(20):
+                    call()
+            g.replay()
+            torch.cuda.synchronize()
+            times = []
+            for _ in range(7):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                g.replay()
+                b.record()
+                torch.cuda.synchronize()
+                times.append(a.elapsed_time(b) * 1e3 / 20)
+            us[what] = statistics.median(times)
+            del g
+        assert dec.peer.error() == 0
+        rows.append({"exchange": "one launch" if name == "one" else "two launches", "step_us": round(us["step"], 2),
+                     "walk_us": round(us["walk"], 2), "exchange_us": round(us["step"] - us["walk"], 2)})
+    print(json.dumps({"table": "c5 on one GPU as a KV split of one rank: walk + exchange, us a step (graph of 20, median of 7)",
+                      "local_splits": splits, "rows": rows}, indent=1), flush=True)
+    return 0
+
+
 def layouts_table(only: str = ""):
     """The decode (walk + merge) on the headline shape (c2) over the same KV values in the two cache
     layouts the walk reads in place: (blocks, page, kv_heads, head_dim) and vLLM's x-split pair
@@ -522,9 +584,12 @@ def main():
     ap.add_argument("--prefill-trace", action="store_true", help="cycles by role and phase of the tensor-memory prefill kernel")
     ap.add_argument("--attrib", action="store_true", help="the decode walk with one stage left out: what each stage costs")
     ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8"], help="with --prefill-trace, or --prefill --case: the cache type")
+    ap.add_argument("--exchange", action="store_true", help="the KV-split exchange kernels on one GPU (one launch against two)")
     ap.add_argument("--shards", action="store_true", help="one rank's share of c2 over 1/2/4/8 GPUs, on one GPU: the step's fixed costs")
     ap.add_argument("--layouts", action="store_true", help="the decode over the usual and the x-split cache layout")
     args = ap.parse_args()
+    if args.exchange:
+        return exchange_table(args.case)
     if args.shards:
         return shards_table()
     if args.layouts:

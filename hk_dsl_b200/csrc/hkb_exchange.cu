@@ -227,11 +227,16 @@ __global__ void __launch_bounds__(XCH_WARPS * 32) kvsplit_exchange_kernel(const 
   const int64_t flag_at = ((int64_t)(epoch & 1u) * 8 + a.rank) * rows + row_id;
   if (lane < a.world) *reinterpret_cast<volatile uint32_t*>(x.row_flags[lane] + flag_at) = epoch + 1u;
   // a lane a rank polls that rank's flag of this row and step: bounded, and a miss is reported, not waited out
+  // (an acquire load at system scope: the rows' reads below cannot move ahead of it -- the other lanes' reads
+  // follow the warp vote -- which is what a second system-scope fence was here for, at a few microseconds)
   bool ok = true;
   if (lane < a.world) {
-    const volatile uint32_t* f = reinterpret_cast<const volatile uint32_t*>(x.my_row_flags + ((int64_t)(epoch & 1u) * 8 + lane) * rows + row_id);
+    const uint32_t* f = x.my_row_flags + ((int64_t)(epoch & 1u) * 8 + lane) * rows + row_id;
     int polls = 0;
-    while (*f != epoch + 1u) {
+    while (true) {
+      uint32_t seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(f) : "memory");
+      if (seen == epoch + 1u) break;
       if (++polls > x.spin_limit) {
         ok = false;
         atomicCAS(x.error, 0, 1 + lane);
@@ -241,7 +246,6 @@ __global__ void __launch_bounds__(XCH_WARPS * 32) kvsplit_exchange_kernel(const 
     }
   }
   ok = __all_sync(0xffffffffu, ok);
-  __threadfence_system();          // the rows were written before the flags: order this warp's reads after the flags
   if (ok) {
     const float* base = x.my_gather + half;
     float lp[8];

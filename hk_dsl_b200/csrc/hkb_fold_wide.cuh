@@ -5,7 +5,7 @@
 // a part; with sixteen parts a warp that is tens of microseconds for a kernel that moves 100 KB.
 // Here the trips are three in all: (1) every thread fetches one lse into shared memory; (2) the
 // live parts are listed (ascending, so the order of the sums is fixed); (3) the warps take the live
-// rows round-robin, four rows in flight a warp. The warps' sums are added through shared memory in
+// rows round-robin, FLIGHT rows in flight a warp. The warps' sums are added through shared memory in
 // warp order: the same bits every call.
 #pragma once
 
@@ -15,6 +15,7 @@ namespace hkb {
 
 template <int VEC, int WARPS>
 struct WideFold {
+  static constexpr int FLIGHT = 8;   // rows a warp requests before it uses any (a sequence in 64 live pieces: one round)
   struct Smem {
     float lse[HKB_MAX_SPLITS];
     int live[HKB_MAX_SPLITS];
@@ -61,11 +62,11 @@ struct WideFold {
     den = 0.f;
     if (mx != -INFINITY) {
       const int count = sm.count;
-      for (int i = warp; i < count; i += 4 * WARPS) {
-        float w[4];
-        float2 x[4][VEC / 2];
+      for (int i = warp; i < count; i += FLIGHT * WARPS) {
+        float w[FLIGHT];
+        float2 x[FLIGHT][VEC / 2];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {       // four rows requested before any is used
+        for (int u = 0; u < FLIGHT; ++u) {       // all requested before any is used
           const int ii = i + u * WARPS;
           w[u] = 0.f;
 #pragma unroll
@@ -80,7 +81,7 @@ struct WideFold {
           }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < FLIGHT; ++u) {
 #pragma unroll
           for (int v = 0; v < VEC / 2; ++v) {
             acc[2 * v] = fmaf(w[u], x[u][v].x, acc[2 * v]);
