@@ -229,21 +229,7 @@ struct WalkStream {
     typename P::State st;
     int seq_c = lo, seq_base = base[lo], seq_end = base[lo + 1];
     int n_tiles = seq_end - seq_base, seq_len = max(__ldg(a.seq_lens + lo), 0);
-    // A ring that walks several short sequences enters each with a load of its query rows, and waits for
-    // it while its tiles sit ready: the rows of the sequence AFTER the one entered are asked into L1 now
-    // (the KV copies bypass L1, so the lines stay), and that load is a hit when its turn comes.
-    auto prefetch_q = [&](int seq) {
-      if (seq >= num_seqs || nh <= 0) return;
-      const int row = a.q_start ? __ldg(a.q_start + seq) : seq;
-      constexpr int LINES = P::HEAD_DIM * 2 / 128;                 // 128-byte lines a head's row
-      if (lane < nh * LINES) {
-        const char* p = reinterpret_cast<const char*>(a.q + (int64_t)row * a.q_stride_tok + (int64_t)(hq0 + lane / LINES) * a.q_stride_head) +
-                        (lane % LINES) * 128;
-        asm volatile("prefetch.global.L1 [%0];\n" ::"l"(p));
-      }
-    };
     if (nh > 0) P::begin(st, a, a.q_start ? __ldg(a.q_start + lo) : lo, hq0, nh, lane, qs);
-    prefetch_q(lo + 1);
     housekeeping();
     int sc = 0, sl = P::STAGES - 1;   // ring stages of the compute and of the loader
     int owe_seq[2] = {-1, -1}, owe_p[2] = {0, 0}, owe_np[2] = {0, 0};   // folds to run after the last tile
@@ -278,7 +264,6 @@ struct WalkStream {
         seq_len = max(__ldg(a.seq_lens + seq_c), 0);
         const int row = a.q_start ? __ldg(a.q_start + seq_c) : seq_c;
         if (nh > 0) P::begin(st, a, row, hq0, nh, lane, qs);
-        prefetch_q(seq_c + 1);
       }
       const int t = g - seq_base;
       if (nh > 0) {
