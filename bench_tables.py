@@ -278,7 +278,7 @@ def prefill_trace(case: str, fp8: bool = False):
              11: "softmax tile 1: wait for previous product (+ rescale)", 12: "softmax tile 1: store P, arrive", 13: "softmax tile 1: epilogue",
              16: "mma: wait for Q", 17: "mma: wait for K", 18: "mma: issue first q.K", 19: "mma: wait for V", 20: "mma: wait for P of tile 0",
              21: "mma: issue p.V", 22: "mma: wait for P of tile 1", 23: "mma: issue the next q.K", 24: "K producer: wait for a free slot", 25: "K producer: issue copies",
-             26: "K producer: wait for copies", 28: "V producer: wait for a free slot", 29: "V producer: issue copies",
+             26: "K producer: wait for copies", 27: "K producer (fp8 caches): load staged tile, widen, store", 28: "V producer: wait for a free slot", 29: "V producer: issue copies",
              30: "V producer: wait for copies", 31: "CTA total"}
     rows = {names[i]: round(float(t[:, i].sum()) / blocks, 1) for i in sorted(names)}
     life = t[:, 31][t[:, 31] > 0]          # the persistent grid's CTAs: lifetimes in cycles

@@ -893,7 +893,9 @@ __global__ void __launch_bounds__(threads_of(FP8), 1) prefill_tc_kernel(const Ar
           Lap<TRACE> tick;
           if (x + FP8_STAGE_TILES - 1 < tiles) issue(x + FP8_STAGE_TILES - 1);
           cp_async_commit();                               // a group a tile (empty ones at the end): tile x is the oldest one pending
+          tick(tr[1]);
           cp_async_wait<FP8_STAGE_TILES - 1>();
+          tick(tr[2]);
           const int r = x % per_blk, kind = kind_of(r), t = tile_of(r);
           const bool first = part ? r % REST == 0 : r == 0, last = part ? r % REST == REST - 1 : r == MAIN - 1;
           if (first) {                                     // the first tile this warp puts into the kind's slot of this block
@@ -925,7 +927,7 @@ __global__ void __launch_bounds__(threads_of(FP8), 1) prefill_tc_kernel(const Ar
             if (lane == 0) mbar_arrive(bar);
           }
           if (r == per_blk - 1) ++cnt;
-          tick(tr[1]);
+          tick(tr[3]);
         }
       } else
       for (int j = 0; j < n && ok; ++j, ++cnt) {
@@ -972,7 +974,7 @@ __global__ void __launch_bounds__(threads_of(FP8), 1) prefill_tc_kernel(const Ar
     }
     cp_async_wait<0>();
     if (TRACE && lane == 0 && part == 0)
-      for (int i = 0; i < 3; ++i) a.trace[(size_t)cta * 32 + 24 + 4 * which + i] = tr[i];
+      for (int i = 0; i < (FP8 && which == 0 ? 4 : 3); ++i) a.trace[(size_t)cta * 32 + 24 + 4 * which + i] = tr[i];   // (fp8, K: + the widening)
   }
 
   // ---- wind-down ----
