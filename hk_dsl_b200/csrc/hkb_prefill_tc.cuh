@@ -705,14 +705,28 @@ __global__ void __launch_bounds__(threads_of(FP8), 1) prefill_tc_kernel(const Ar
     auto slot_of = [](int kind, int c) { return 2 * (c & 1) + kind; };
     // S_t = Q_t K^T for the K block in ring slot `slot`: eight products (two 64-dim halves x four 16-dim
     // steps) into the tile's score columns; the tile's query rows are free after the item's last one
+    // Every matrix descriptor the kernel will ever use, once: the query tiles and the four ring slots do
+    // not move. The issuing thread then has nothing to compute between two products -- building the
+    // 64-bit descriptors in the loop, a dozen dependent instructions a product on ONE thread, was what
+    // an "86-clock tcgen05.mma" mostly consisted of.
+    uint64_t qd0[8], qd1[8], kd0[8], kd1[8], vd0[8], vd1[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int h = i >> 2, ks = i & 3;          // S: two 64-dim halves x four 16-dim steps (32 bytes inside the 128-byte row)
+      qd0[i] = smem_desc(q_smem + h * HALF_BYTES_Q + ks * 32, 16);
+      qd1[i] = smem_desc(q_smem + Q_BYTES + h * HALF_BYTES_Q + ks * 32, 16);
+      kd0[i] = smem_desc(ring + h * HALF_BYTES_KV + ks * 32, 16);                      // K blocks sit in slots 0 and 2
+      kd1[i] = smem_desc(ring + 2 * SLOT_BYTES + h * HALF_BYTES_KV + ks * 32, 16);
+      vd0[i] = smem_desc(ring + SLOT_BYTES + i * 16 * 128, HALF_BYTES_KV);             // V blocks in slots 1 and 3: 16 tokens a step
+      vd1[i] = smem_desc(ring + 3 * SLOT_BYTES + i * 16 * 128, HALF_BYTES_KV);
+    }
+    // S_t = Q_t K^T for the K block in ring slot `slot`: eight products into the tile's score columns; the
+    // tile's query rows are free after the item's last one
     auto scores = [&](int t, int slot, bool last) {
-      const uint32_t kaddr = ring + slot * SLOT_BYTES;
+      const bool hi = slot >= 2;
 #pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)           // 16 dims = 32 bytes a step inside the 128-byte row
-          umma_ss(tmem + s_col(t), smem_desc(q_smem + t * Q_BYTES + h * HALF_BYTES_Q + ks * 32, 16),
-                  smem_desc(kaddr + h * HALF_BYTES_KV + ks * 32, 16), IDESC_S, (h | ks) ? 1u : 0u);
+      for (int i = 0; i < 8; ++i)
+        umma_ss(tmem + s_col(t), t ? qd1[i] : qd0[i], hi ? kd1[i] : kd0[i], IDESC_S, i ? 1u : 0u);
       tc_commit(HKB_BAR(s_full) + 8 * t);
       if (last) tc_commit(HKB_BAR(q_empty) + 8 * t);
     };
@@ -753,7 +767,7 @@ __global__ void __launch_bounds__(threads_of(FP8), 1) prefill_tc_kernel(const Ar
         if (j + 1 < n) wait_block(0, kcnt + j + 1, 4);     // K_{j+1}
         if (!ok) break;
         lap(tr[1]);
-        const uint32_t vaddr = ring + slot_of(1, vcnt + j) * SLOT_BYTES;
+        const bool v_hi = slot_of(1, vcnt + j) == 3;
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (!ok || j >= it.nblk(t)) continue;
@@ -766,9 +780,12 @@ __global__ void __launch_bounds__(threads_of(FP8), 1) prefill_tc_kernel(const Ar
           if (lane == 0) {
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)           // 16 tokens a step: 8 TMEM columns of P, 16 rows of V
-              umma_ts(tmem + o_col(t), tmem + s_col(t) + ks * 8, smem_desc(vaddr + ks * 16 * 128, HALF_BYTES_KV), IDESC_PV,
-                      (j | ks) ? 1u : 0u);
+              umma_ts(tmem + o_col(t), tmem + s_col(t) + ks * 8, v_hi ? vd1[ks] : vd0[ks], IDESC_PV, (j | ks) ? 1u : 0u);
             tc_commit(HKB_BAR(o_done) + 8 * t);
+            // the block's last P V product has been issued: the V slot goes back now, before the scores that
+            // follow (a commit covers every product issued so far; the scores do not read V, and waiting for
+            // them too handed the slot back ~700 clocks later, with the MMA warp then waiting for the next V)
+            if (t == 1 || j >= it.nblk1) tc_commit(HKB_BAR(empty) + 8 * slot_of(1, vcnt + j));
           }
           if (TRACE) { __syncwarp(); lap(tr[5]); }
           // the tile's next scores go over the P just consumed: the tensor pipe runs products in the order issued
@@ -777,7 +794,6 @@ __global__ void __launch_bounds__(threads_of(FP8), 1) prefill_tc_kernel(const Ar
           lap(tr[TRACE ? 7 : 5]);
         }
         if (ok && lane == 0) {
-          tc_commit(HKB_BAR(empty) + 8 * slot_of(1, vcnt + j));                      // V_j
           if (j + 1 < n) tc_commit(HKB_BAR(empty) + 8 * slot_of(0, kcnt + j + 1));   // K_{j+1}
         }
         __syncwarp();
