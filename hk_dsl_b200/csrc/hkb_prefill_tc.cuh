@@ -372,8 +372,14 @@ __device__ __forceinline__ float poly_exp2(float x) {
   const float p = fmaf(fmaf(fmaf(0.0551716685f, f, 0.2426111251f), f, 0.6932609677f), f, 0.9999280572f);
   return __int_as_float(__float_as_int(p) + (__float_as_int(shifted) << 23));
 }
-// which pairs of a row take the polynomial: one in POLY_EVERY (0: none)
-constexpr int POLY_EVERY = 4;
+// which pairs of a row take the polynomial: one in POLY_EVERY (0: none). Measured with the libraries run in
+// turn on one B200 (TFLOP/s at 1 x 8192 / 8 x 2048 / 32 x 512): none 1070-1080 / 758-770 / 318-388; every 3rd
+// 1011-1027 / 677-688 / 322-341; 4th 1042-1061 / 727-764 / 360-366; 5th 1081-1086 / 821-826 / 392-404;
+// 6th 1061-1063 / 729-736 / 361-371; 7th 1084-1089 / 746-750 / 368-381; 8th 1092-1108 / 843-855 / 408-410;
+// 10th 1114-1116 / 843-850 / 414; 12th 1105 / 840-845 / 410; 16th 1108-1111 / 832-841 / 396-406. Not a smooth
+// curve: where the polynomial's nine dependent instructions fall among the MUFU pairs decides how well the
+// row's instruction stream packs.
+constexpr int POLY_EVERY = 10;
 
 template <bool F16>
 __device__ __forceinline__ float half_exp(float (&s)[64], bool masked, bool valid, int key0, int pos, float qs, float off,
