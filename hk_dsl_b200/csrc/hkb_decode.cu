@@ -324,16 +324,20 @@ static int dispatch_mma(const DecodeArgs& a, int num_seqs, cudaStream_t st) {
     } else {
       grid = stream_grid(a.num_kv_heads);
       if constexpr (FP8) {
-        // The fp8 stream builds its mma fragments straight from the fp8 tile (WalkMMAF8). Three CTAs an
-        // SM (168 registers a thread, 12 warps) for a group of up to 8: the walk of an fp8 tile is a
-        // chain of dependent shared-memory loads, converts, mma and shuffles, and with half the bytes
-        // a tile it needs more warps in flight than the bf16 walk to keep HBM busy (6.2 against 4.9
-        // TB/s at two CTAs; four CTAs at 128 registers spill and fall to 4.3; widening tiles to bf16
-        // in shared memory first reads 2.8).
+        // The fp8 stream builds its mma fragments straight from the fp8 tile (WalkMMAF8). Twelve warps
+        // an SM (168 registers a thread) for a group of up to 8: the walk of an fp8 tile is a chain of
+        // dependent shared-memory loads, converts, mma and shuffles, and with half the bytes a tile it
+        // needs more warps in flight than the bf16 walk to keep HBM busy (6.2 against 4.9 TB/s at eight
+        // warps; sixteen at 128 registers spill and fall to 4.3; widening tiles to bf16 in shared memory
+        // first reads 2.8). Twelve warps as two CTAs of six rings with three stages each: measured with
+        // the libraries run in turn on one B200, batch 64 x 2k-8k tokens: 5856-5895 GB/s, against 5703-5761
+        // for three CTAs of four rings and four stages, 5753 for one CTA of twelve rings, 5366-5430 with
+        // two stages a ring.
         if (a.group <= 8) {
-          using P = WalkMMAF8<D, 1, 4, 3>;
-          return launch_stream<walk_stream_kernel<P, WARPS>>(WalkStream<P, WARPS>::SMEM_BYTES, WARPS * 32,
-                                                             stream_grid(a.num_kv_heads, 3), a, num_seqs, st);
+          constexpr int RINGS = 6;
+          using P = WalkMMAF8<D, 1, 3, 2>;
+          return launch_stream<walk_stream_kernel<P, RINGS>>(WalkStream<P, RINGS>::SMEM_BYTES, RINGS * 32,
+                                                             stream_grid(a.num_kv_heads, 2), a, num_seqs, st);
         }
         using P2 = WalkMMAF8<D, 2, NST, 2>;
         return launch_stream<walk_stream_kernel<P2, WARPS>>(WalkStream<P2, WARPS>::SMEM_BYTES, WARPS * 32, grid, a, num_seqs, st);
