@@ -241,7 +241,7 @@ struct WalkMMA {
   static constexpr int PASS_HEADS = HEADS;      // query heads a ring serves a pass
   static constexpr int STAGES = NST;
   static constexpr int HEAD_DIM = D;
-  static constexpr int MIN_CTAS = D == 256 ? 1 : 2;   // CTAs an SM the stream kernel is compiled and launched for
+  static constexpr int MIN_CTAS = (D == 256 || WARPS >= 6) ? 1 : 2;   // CTAs an SM the stream kernel is compiled and launched for (one, where a CTA has six rings or more)
   __host__ __device__ static constexpr int passes(int) { return 1; }
 
   struct State {
