@@ -4,7 +4,7 @@
 // (request, kv head, split) (python/hk/ops/paged.py:171-194, 552-559): short sequences get
 // tiny splits, long ones long splits, and every workgroup pays its own start-up. On B200 that
 // costs a few microseconds a CTA wave and leaves a tail. Here the grid is sized to the
-// machine instead -- about two four-warp CTAs an SM -- and the work is dealt in equal shares:
+// machine instead -- eight to twelve warps an SM, as one to three CTAs -- and the work is dealt in equal shares:
 //
 //   * each kv head (x head chunk) is a plane with its own CTAs; inside a plane all sequences'
 //     16-token tiles form ONE line, total = sum_i ceil(seq_len_i / 16) tiles, computed by every
